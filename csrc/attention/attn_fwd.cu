@@ -1,0 +1,396 @@
+// Attention forward with online softmax on sm_100a tensor cores.
+//
+// One CTA owns a 128-row query tile of one (batch, head).  Per 128-row KV tile:
+//   S  = Q·Kᵀ            tcgen05.mma, fp32 in TMEM (two S buffers)
+//   P  = exp2(S·c − m)   eight softmax warps, two threads per row (64 columns each); the
+//                        running max is exchanged through shared memory, P goes to shared
+//                        memory as bf16 in the 128-byte-swizzled K-major layout
+//   PV = P·V             tcgen05.mma into a fresh TMEM buffer (two PV buffers)
+//   O  = O·α + PV        in registers, deferred by one tile so that it overlaps the next
+//                        QKᵀ and softmax
+// Warp 8 is the TMA producer (double-buffered K and V), warp 9 issues the MMAs and owns
+// TMEM.  Causal masking assumes seq_q == seq_k; KV tiles above the diagonal are skipped and
+// heavy query tiles are scheduled first.
+//
+// Outputs O (bf16, [B,S,H,D] strided) and the log-sum-exp per row (fp32 [B,H,S]).
+//
+// Reference parity: fused_attention_online.wgsl (crates/st-backend-wgpu/src/shaders),
+// scaled_dot_attention_kernel (crates/st-core/src/backend/cuda_attention.cu:80-258),
+// fused_attention_cpu (crates/st-tensor/src/pure.rs:11845-11919).
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+
+namespace {
+using namespace st;
+
+constexpr int BLK = 128;           // query rows and KV rows per tile
+constexpr int NUM_THREADS = 320;   // 8 softmax warps + producer + MMA
+
+struct AttnFwdParams {
+  __nv_bfloat16* O;
+  float* lse;
+  long long o_sb, o_ss, o_sh;  // element strides of O for batch, sequence, head
+  int B, H, Sq, Sk;
+  float scale_log2;            // softmax scale * log2(e)
+  int causal;
+  unsigned* err;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void pair_sync(int quad) {
+  asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
+}
+
+template <int D>
+struct FwdSmem {
+  static constexpr int TILE = BLK * D * 2;       // bytes of a Q / K / V tile
+  static constexpr int P_TILE = BLK * BLK * 2;   // bytes of a P tile
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = Q_OFF + TILE;
+  static constexpr int V_OFF = K_OFF + 2 * TILE;
+  static constexpr int P_OFF = V_OFF + 2 * TILE;
+  static constexpr int BAR_OFF = P_OFF + 2 * P_TILE;
+  static constexpr int XCH_OFF = BAR_OFF + 256;           // 2 x 2 x 128 floats (max exchange)
+  static constexpr int TOTAL = XCH_OFF + 2 * 2 * BLK * 4;
+};
+
+template <int D>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using L = FwdSmem<D>;
+  constexpr int DH = D / 2;            // output columns per softmax thread
+  constexpr int KB = D / 64;           // 64-wide (128-byte) blocks along D
+  constexpr uint32_t S_COL = 0, PV_COL = 256;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base (uniform exit)
+    if (threadIdx.x == 0) report_error(p.err, ERR_BOUNDS, 0xA7F1u);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* v_full = bars + 3;      // 2
+  uint64_t* k_empty = bars + 5;     // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* p_full = bars + 11;     // 2 (256 arrivals)
+  uint64_t* pv_full = bars + 13;    // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);  // [2 buffers][2 halves][128]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BLK;
+  int n_kv = (p.Sk + BLK - 1) / BLK;
+  if (p.causal) n_kv = min(n_kv, q_tile + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&k_full[i]), 1);
+      mbar_init(smem_u32(&v_full[i]), 1);
+      mbar_init(smem_u32(&k_empty[i]), 1);
+      mbar_init(smem_u32(&v_empty[i]), 1);
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&p_full[i]), 256);
+      mbar_init(smem_u32(&pv_full[i]), 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ---------------------------- TMA producer -----------------------------------------
+    if (lane == 0) {
+      const uint32_t qb = smem_u32(q_full);
+      mbar_arrive_expect_tx(qb, L::TILE);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb)
+        tma_load_4d(smem_u32(smem + L::Q_OFF + kb * (BLK * 128)), &tmQ, qb, kb * 64, h, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(&k_empty[st]), ph ^ 1u, abort_flag)) break;
+        const uint32_t kf = smem_u32(&k_full[st]);
+        mbar_arrive_expect_tx(kf, L::TILE);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem_u32(smem + L::K_OFF + st * L::TILE + kb * (BLK * 128)), &tmK, kf,
+                      kb * 64, h, j * BLK, b);
+        if (!mbar_wait(smem_u32(&v_empty[st]), ph ^ 1u, abort_flag)) break;
+        const uint32_t vf = smem_u32(&v_full[st]);
+        mbar_arrive_expect_tx(vf, L::TILE);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem_u32(smem + L::V_OFF + st * L::TILE + kb * (BLK * 128)), &tmV, vf,
+                      kb * 64, h, j * BLK, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------------------- MMA issuer -------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BLK, D, false, true);
+      const uint32_t sq = smem_u32(smem + L::Q_OFF);
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
+      auto issue_qk = [&](int jj) -> bool {
+        const int st = jj & 1;
+        if (!mbar_wait(smem_u32(&k_full[st]), (jj >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
+        const uint32_t d_tmem = tmem_base + S_COL + (jj & 1) * BLK;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_smem_desc_sw128(sq + kb * (BLK * 128) + k * 32, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sk + kb * (BLK * 128) + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+        umma_commit(smem_u32(&s_full[jj & 1]));
+        umma_commit(smem_u32(&k_empty[st]));
+        return true;
+      };
+      if (ok && n_kv > 0) ok = issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(&p_full[st]), ph, abort_flag)) break;
+        if (!mbar_wait(smem_u32(&v_full[st]), ph, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t sp = smem_u32(smem + L::P_OFF + st * L::P_TILE);
+        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
+        const uint32_t d_tmem = tmem_base + PV_COL + st * D;
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {
+          // A = P (K-major, two 64-column blocks); B = V (MN-major: D contiguous, KV rows = K)
+          const uint64_t da = make_smem_desc_sw128(sp + (kk >> 2) * (BLK * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sv + kk * (16 * 128), BLK * 128, 1024);
+          umma_bf16_ss(d_tmem, da, db, idesc_pv, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&pv_full[st]));
+        umma_commit(smem_u32(&v_empty[st]));
+      }
+    }
+  } else {
+    // ---------------------------- softmax / output warps -------------------------------
+    const int quad = warp & 3;
+    const int half = warp >> 2;
+    const int r = quad * 32 + lane;
+    const int row_g = q0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
+    float o[DH];
+#pragma unroll
+    for (int c = 0; c < DH; ++c) o[c] = 0.0f;
+    bool ok = true;
+
+    auto accumulate = [&](int jj, float a) -> bool {
+      const int pb = jj & 1;
+      if (!mbar_wait_warp(smem_u32(&pv_full[pb]), (jj >> 1) & 1, abort_flag)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < DH / 32; ++ch) {
+        uint32_t t[32];
+        tmem_ld_32x32(tmem_base + lane_off + PV_COL + pb * D + half * DH + ch * 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[ch * 32 + c] = o[ch * 32 + c] * a + __uint_as_float(t[c]);
+      }
+      return true;
+    };
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int buf = j & 1;
+      if (!mbar_wait_warp(smem_u32(&s_full[buf]), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[64];
+      {
+        uint32_t t0[32], t1[32];
+        const uint32_t ta = tmem_base + lane_off + S_COL + buf * BLK + half * 64;
+        tmem_ld_32x32(ta, t0);
+        tmem_ld_32x32(ta + 32, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) { sr[c] = t0[c]; sr[32 + c] = t1[c]; }
+      }
+      const int col0 = j * BLK + half * 64;
+      const bool need_mask = (p.causal && (j == q_tile)) || (col0 + 64 > p.Sk);
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int col = col0 + c;
+          const bool dead = (col >= p.Sk) || (p.causal && col > row_g);
+          float s = dead ? -INFINITY : __uint_as_float(sr[c]);
+          sr[c] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      }
+      float* xb = xch + buf * (2 * BLK);
+      xb[half * BLK + r] = mx;
+      pair_sync(quad);
+      mx = fmaxf(mx, xb[(half ^ 1) * BLK + r]);
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = fast_exp2(m - m_safe);
+      float rs = 0.0f;
+      uint8_t* pt = smem + L::P_OFF + buf * L::P_TILE + half * (BLK * 128);
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        float e[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          e[q] = fast_exp2(__uint_as_float(sr[c8 * 8 + q]) * p.scale_log2 - m_safe);
+          rs += e[q];
+        }
+        uint4 u;
+        u.x = pack_bf16x2(e[0], e[1]); u.y = pack_bf16x2(e[2], e[3]);
+        u.z = pack_bf16x2(e[4], e[5]); u.w = pack_bf16x2(e[6], e[7]);
+        *reinterpret_cast<uint4*>(pt + sw128_offset(r, c8)) = u;
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&p_full[buf]));
+      if (j > 0) {
+        if (!accumulate(j - 1, alpha_prev)) { ok = false; break; }
+      }
+      alpha_prev = alpha;
+    }
+    if (ok && n_kv > 0) ok = accumulate(n_kv - 1, alpha_prev);
+
+    if (ok) {
+      // combine the two halves' row sums, normalise and store
+      float* xb = xch;  // all earlier exchanges on this buffer were consumed before pair_sync below
+      pair_sync(quad);
+      xb[half * BLK + r] = l;
+      pair_sync(quad);
+      const float l_tot = l + xb[(half ^ 1) * BLK + r];
+      const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+      if (row_g < p.Sq) {
+        __nv_bfloat16* op = p.O + (long long)b * p.o_sb + (long long)row_g * p.o_ss +
+                            (long long)h * p.o_sh + half * DH;
+#pragma unroll
+        for (int c8 = 0; c8 < DH / 8; ++c8) {
+          uint4 u;
+          u.x = pack_bf16x2(o[c8 * 8 + 0] * inv, o[c8 * 8 + 1] * inv);
+          u.y = pack_bf16x2(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+          u.z = pack_bf16x2(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+          u.w = pack_bf16x2(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+          reinterpret_cast<uint4*>(op)[c8] = u;
+        }
+        if (half == 0)
+          p.lse[((long long)b * p.H + h) * p.Sq + row_g] =
+              (l_tot > 0.0f) ? (m + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) report_error(p.err, ERR_MBAR_TIMEOUT, 0xA7F0u);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+namespace st {
+// 4-D tensor map over a [B, S, H, D] bf16 view with arbitrary B/S/H strides (D contiguous):
+// dims {D, H, S, B}, box {64, 1, rows, 1}.
+bool encode_bshd_tmap(CUtensorMap* out, const void* base, int B, int S, int H, int D,
+                      long long sb, long long ss, long long sh, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)sh * 2, (uint64_t)ss * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return encode_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+}
+}  // namespace st
+
+struct StAttnFwdArgs {
+  const void* Q; const void* K; const void* V; void* O; float* lse;
+  long long q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh;
+  int B, H, Sq, Sk, D;
+  float scale;
+  int causal;
+};
+
+ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
+  if (!a || !a->Q || !a->K || !a->V || !a->O || !a->lse) return st::fail(ST_ERR_INVALID, "attn_fwd: null pointer");
+  if (a->D != 64 && a->D != 128) return st::fail(ST_ERR_INVALID, "attn_fwd: head_dim must be 64 or 128");
+  if (a->causal && a->Sq != a->Sk) return st::fail(ST_ERR_INVALID, "attn_fwd: causal needs seq_q == seq_k");
+  const long long strides[] = {a->q_sb, a->q_ss, a->q_sh, a->k_sb, a->k_ss, a->k_sh,
+                               a->v_sb, a->v_ss, a->v_sh, a->o_sb, a->o_ss, a->o_sh};
+  for (long long s : strides)
+    if (s & 7) return st::fail(ST_ERR_INVALID, "attn_fwd: strides must be multiples of 8 elements");
+  if ((reinterpret_cast<uintptr_t>(a->Q) | reinterpret_cast<uintptr_t>(a->K) |
+       reinterpret_cast<uintptr_t>(a->V) | reinterpret_cast<uintptr_t>(a->O)) & 15)
+    return st::fail(ST_ERR_INVALID, "attn_fwd: pointers must be 16-byte aligned");
+  CUtensorMap tq, tk, tv;
+  if (!st::encode_bshd_tmap(&tq, a->Q, a->B, a->Sq, a->H, a->D, a->q_sb, a->q_ss, a->q_sh, BLK) ||
+      !st::encode_bshd_tmap(&tk, a->K, a->B, a->Sk, a->H, a->D, a->k_sb, a->k_ss, a->k_sh, BLK) ||
+      !st::encode_bshd_tmap(&tv, a->V, a->B, a->Sk, a->H, a->D, a->v_sb, a->v_ss, a->v_sh, BLK))
+    return ST_ERR_CUDA;
+  AttnFwdParams p;
+  p.O = static_cast<__nv_bfloat16*>(a->O);
+  p.lse = a->lse;
+  p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh;
+  p.B = a->B; p.H = a->H; p.Sq = a->Sq; p.Sk = a->Sk;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.causal = a->causal;
+  p.err = st::error_word();
+  dim3 grid((a->Sq + BLK - 1) / BLK, a->H, a->B);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
+  if (a->D == 128) {
+    static bool cfg = false;
+    if (!cfg) {
+      ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL));
+      cfg = true;
+    }
+    attn_fwd_kernel<128><<<grid, NUM_THREADS, FwdSmem<128>::TOTAL, s>>>(tq, tk, tv, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL));
+      cfg = true;
+    }
+    attn_fwd_kernel<64><<<grid, NUM_THREADS, FwdSmem<64>::TOTAL, s>>>(tq, tk, tv, p);
+  }
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}

@@ -108,6 +108,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// Whole-warp variant: every lane waits and the warp agrees on the outcome, so that the
+// warp-collective tcgen05 instructions that follow are never issued by a partial warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------------------------------
 // proxies / fences
 // ---------------------------------------------------------------------------------------

@@ -219,7 +219,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = tm * BM, n0 = tn * BN;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
+      if (!mbar_wait_warp(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;

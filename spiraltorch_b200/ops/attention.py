@@ -1,0 +1,147 @@
+"""Scaled-dot-product attention, forward and backward, on the tcgen05 kernels
+(``csrc/attention/attn_fwd.cu``, ``csrc/attention/attn_bwd.cu``).
+
+Tensors are ``[B, S, H, D]`` views (D contiguous, any B/S/H strides), so Q, K and V can be
+slices of one fused QKV projection output and O feeds the output projection without a copy.
+CPU tensors use an fp32 PyTorch statement of the same math (also the test oracle).
+
+Reference parity: ``Tensor::scaled_dot_attention`` (crates/st-tensor/src/pure.rs:4061-4157,
+online-softmax ``fused_attention_cpu`` :11845-11919); the backward has no counterpart in
+the reference (its attention is forward-only).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import native
+
+launch_count = 0
+
+
+class _FwdArgs(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("Q", "K", "V", "O", "lse")] + \
+               [(n, ctypes.c_longlong) for n in ("q_sb", "q_ss", "q_sh", "k_sb", "k_ss", "k_sh",
+                                                "v_sb", "v_ss", "v_sh", "o_sb", "o_ss", "o_sh")] + \
+               [(n, ctypes.c_int) for n in ("B", "H", "Sq", "Sk", "D")] + \
+               [("scale", ctypes.c_float), ("causal", ctypes.c_int)]
+
+
+class _BwdArgs(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("Q", "K", "V", "O", "dO", "lse", "delta", "dQ_acc",
+                                               "dQ", "dK", "dV")] + \
+               [(n, ctypes.c_longlong) for n in ("q_sb", "q_ss", "q_sh", "k_sb", "k_ss", "k_sh",
+                                                "v_sb", "v_ss", "v_sh", "o_sb", "o_ss", "o_sh",
+                                                "do_sb", "do_ss", "do_sh",
+                                                "dq_sb", "dq_ss", "dq_sh", "dk_sb", "dk_ss", "dk_sh",
+                                                "dv_sb", "dv_ss", "dv_sh")] + \
+               [(n, ctypes.c_int) for n in ("B", "H", "Sq", "Sk", "D")] + \
+               [("scale", ctypes.c_float), ("causal", ctypes.c_int)]
+
+
+def attention_reference(q, k, v, causal: bool, scale: float, bias: Optional[torch.Tensor] = None):
+    """fp32 reference: q,k,v ``[B,S,H,D]`` → (o ``[B,S,H,D]`` fp32, lse ``[B,H,S]``)."""
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if bias is not None:
+        s = s + bias
+    if causal:
+        sq, sk = s.shape[-2:]
+        mask = torch.ones(sq, sk, dtype=torch.bool, device=s.device).tril(sk - sq)
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3)
+    return o, lse
+
+
+def _check_layout(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 4 or t.stride(-1) != 1 or t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be a bf16 [B,S,H,D] view with contiguous D")
+
+
+def attention_forward(q, k, v, causal: bool = True, scale: Optional[float] = None):
+    """Returns ``(o, lse)``; ``o`` is contiguous ``[B,S,H,D]`` bf16, ``lse`` fp32 ``[B,H,S]``."""
+    global launch_count
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if not native.use_native(q):
+        o, lse = attention_reference(q, k, v, causal, scale)
+        return o.to(q.dtype), lse
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_layout(t, n)
+    o = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    a = _FwdArgs()
+    a.Q, a.K, a.V, a.O, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    a.q_sb, a.q_ss, a.q_sh = q.stride(0), q.stride(1), q.stride(2)
+    a.k_sb, a.k_ss, a.k_sh = k.stride(0), k.stride(1), k.stride(2)
+    a.v_sb, a.v_ss, a.v_sh = v.stride(0), v.stride(1), v.stride(2)
+    a.o_sb, a.o_ss, a.o_sh = o.stride(0), o.stride(1), o.stride(2)
+    a.B, a.H, a.Sq, a.Sk, a.D = B, H, Sq, Sk, D
+    a.scale, a.causal = float(scale), int(causal)
+    native.check(native.lib().st_attn_fwd(ctypes.byref(a), native.stream_ptr(q.device)), "st_attn_fwd")
+    launch_count += 1
+    return o, lse
+
+
+def attention_backward(q, k, v, o, lse, do, causal: bool = True, scale: Optional[float] = None,
+                       dq=None, dk=None, dv=None):
+    """Returns ``(dq, dk, dv)`` (bf16, ``[B,S,H,D]``); outputs may be preallocated strided views."""
+    global launch_count
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if not native.use_native(q):
+        with torch.enable_grad():
+            qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+            of, _ = attention_reference(qf, kf, vf, causal, scale)
+            g = torch.autograd.grad(of, (qf, kf, vf), do.float())
+        return tuple(x.to(q.dtype) for x in g)
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (do, "do")):
+        _check_layout(t, n)
+    dev = q.device
+    dq = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=dev) if dq is None else dq
+    dk = torch.empty((B, Sk, H, D), dtype=torch.bfloat16, device=dev) if dk is None else dk
+    dv = torch.empty((B, Sk, H, D), dtype=torch.bfloat16, device=dev) if dv is None else dv
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+    dq_acc = torch.zeros((B, H, Sq, D), dtype=torch.float32, device=dev)
+    a = _BwdArgs()
+    a.Q, a.K, a.V, a.O, a.dO = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr()
+    a.lse, a.delta, a.dQ_acc = lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr()
+    a.dQ, a.dK, a.dV = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    for pre, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", do), ("dq", dq), ("dk", dk), ("dv", dv)):
+        setattr(a, pre + "_sb", t.stride(0))
+        setattr(a, pre + "_ss", t.stride(1))
+        setattr(a, pre + "_sh", t.stride(2))
+    a.B, a.H, a.Sq, a.Sk, a.D = B, H, Sq, Sk, D
+    a.scale, a.causal = float(scale), int(causal)
+    native.check(native.lib().st_attn_bwd(ctypes.byref(a), native.stream_ptr(dev)), "st_attn_bwd")
+    launch_count += 3
+    return dq, dk, dv
+
+
+class _AttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = attention_forward(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        if do.stride(-1) != 1 or do.dtype != q.dtype:
+            do = do.to(q.dtype).contiguous()
+        dq, dk, dv = attention_backward(q, k, v, o, lse, do, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention(q, k, v, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
+    """Differentiable attention on ``[B,S,H,D]`` tensors."""
+    return _AttentionFn.apply(q, k, v, causal, scale)

@@ -1,0 +1,197 @@
+"""RoPE, GELU/ReLU, column sums, embedding and row softmax (``csrc/elementwise/elementwise.cu``).
+
+Reference parity: ``tensor_utils.wgsl`` entry points ``embedding_gather``,
+``embedding_scatter_add``, ``relu``/``relu_backward``, ``sum_axis0``; ``fused_gelu_back.wgsl``;
+``row_softmax`` / ``row_softmax_hardmax`` (crates/st-tensor/src/pure.rs:3277,11921);
+RoPE cache util (crates/st-core/src/util/rope_lru.rs).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import native
+
+launch_count = 0
+_rope_cache: dict = {}
+
+
+def rope_tables(seq_len: int, head_dim: int, base: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables ``[seq_len, head_dim/2]`` fp32 (cached per device)."""
+    key = (seq_len, head_dim, float(base), str(device))
+    hit = _rope_cache.get(key)
+    if hit is None:
+        inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+        ang = torch.arange(seq_len, dtype=torch.float64)[:, None] * inv[None, :]
+        hit = (ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous())
+        _rope_cache[key] = hit
+    return hit
+
+
+def rope_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, backward: bool):
+    """x: [T, heads, D]; rotate-half convention; position = t % seq_len."""
+    T, Hh, D = x.shape
+    half = D // 2
+    pos = torch.arange(T, device=x.device) % seq_len
+    c = cos[pos][:, None, :]
+    s = sin[pos][:, None, :] * (-1.0 if backward else 1.0)
+    a, b = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(x.dtype)
+
+
+def rope_(x: torch.Tensor, heads: int, head_dim: int, seq_len: int, base: float = 10000.0,
+          backward: bool = False) -> torch.Tensor:
+    """In-place RoPE on the first ``heads*head_dim`` columns of each row of ``x`` ``[T, ld]``."""
+    global launch_count
+    T = x.shape[0]
+    cos, sin = rope_tables(seq_len, head_dim, base, x.device)
+    if not native.use_native(x):
+        view = x[:, : heads * head_dim].reshape(T, heads, head_dim)
+        view.copy_(rope_reference(view, cos, sin, seq_len, backward))
+        return x
+    assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
+    st = native.lib().st_rope(native.ptr(x), native.ptr(cos), native.ptr(sin), ctypes.c_longlong(T),
+                              ctypes.c_int(heads), ctypes.c_int(head_dim), ctypes.c_longlong(x.stride(0)),
+                              ctypes.c_int(seq_len), ctypes.c_int(0), ctypes.c_int(int(backward)),
+                              native.stream_ptr(x.device))
+    native.check(st, "st_rope")
+    launch_count += 1
+    return x
+
+
+def act_forward(x: torch.Tensor, kind: str) -> torch.Tensor:
+    global launch_count
+    if not native.use_native(x) or x.dtype != torch.bfloat16 or x.numel() % 8 or not x.is_contiguous():
+        if x.is_cuda:
+            x = x.contiguous()
+        return torch.relu(x) if kind == "relu" else torch.nn.functional.gelu(x, approximate="tanh")
+    y = torch.empty_like(x)
+    st = native.lib().st_act_fwd(native.ptr(x), native.ptr(y), ctypes.c_longlong(x.numel()),
+                                 ctypes.c_int(int(kind == "relu")), native.stream_ptr(x.device))
+    native.check(st, "st_act_fwd")
+    launch_count += 1
+    return y
+
+
+def act_backward(x: torch.Tensor, dy: torch.Tensor, kind: str) -> torch.Tensor:
+    global launch_count
+    if not native.use_native(x) or x.dtype != torch.bfloat16 or x.numel() % 8 or not x.is_contiguous() \
+            or not dy.is_contiguous() or dy.dtype != x.dtype:
+        from .gemm import gelu_tanh_grad
+        g = (x > 0).to(dy.dtype) if kind == "relu" else gelu_tanh_grad(x.float()).to(dy.dtype)
+        return dy * g
+    dx = torch.empty_like(x)
+    st = native.lib().st_act_bwd(native.ptr(x), native.ptr(dy), native.ptr(dx), ctypes.c_longlong(x.numel()),
+                                 ctypes.c_int(int(kind == "relu")), native.stream_ptr(x.device))
+    native.check(st, "st_act_bwd")
+    launch_count += 1
+    return dx
+
+
+class _ActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, kind):
+        ctx.save_for_backward(x)
+        ctx.kind = kind
+        return act_forward(x, kind)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return act_backward(x, dy.contiguous(), ctx.kind), None
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    return _ActFn.apply(x, "gelu")
+
+
+def relu(x: torch.Tensor) -> torch.Tensor:
+    return _ActFn.apply(x, "relu")
+
+
+def colsum(x2: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """fp32 column sums of a bf16 ``[rows, cols]`` matrix (bias gradients)."""
+    global launch_count
+    rows, cols = x2.shape
+    if out is None:
+        out = torch.zeros(cols, dtype=torch.float32, device=x2.device)
+    elif not accumulate:
+        out.zero_()
+    if not native.use_native(x2) or x2.dtype != torch.bfloat16 or x2.stride(-1) != 1:
+        out += x2.float().sum(0)
+        return out
+    st = native.lib().st_colsum(native.ptr(x2), native.ptr(out), ctypes.c_longlong(rows), ctypes.c_int(cols),
+                                ctypes.c_longlong(x2.stride(0)), native.stream_ptr(x2.device))
+    native.check(st, "st_colsum")
+    launch_count += 1
+    return out
+
+
+def embedding_forward(idx: torch.Tensor, weight: torch.Tensor, pos: Optional[torch.Tensor] = None,
+                      seq_len: int = 0, vocab_start: int = 0) -> torch.Tensor:
+    """``out[t] = weight[idx[t] - vocab_start]`` (zeros outside the shard) ``+ pos[t % seq_len]``."""
+    global launch_count
+    flat = idx.reshape(-1)
+    T, d = flat.numel(), weight.shape[1]
+    if not native.use_native(weight):
+        local = flat - vocab_start
+        ok = (local >= 0) & (local < weight.shape[0])
+        out = weight[local.clamp(0, weight.shape[0] - 1)] * ok[:, None].to(weight.dtype)
+        if pos is not None:
+            out = out + pos[torch.arange(T, device=flat.device) % seq_len]
+        return out
+    assert weight.dtype == torch.bfloat16 and weight.is_contiguous()
+    flat = flat.to(torch.int64).contiguous()
+    out = torch.empty((T, d), dtype=torch.bfloat16, device=weight.device)
+    st = native.lib().st_embedding_fwd(native.ptr(flat), native.ptr(weight), native.ptr(pos), native.ptr(out),
+                                       ctypes.c_longlong(T), ctypes.c_int(d), ctypes.c_int(vocab_start),
+                                       ctypes.c_int(weight.shape[0]), ctypes.c_int(seq_len),
+                                       native.stream_ptr(weight.device))
+    native.check(st, "st_embedding_fwd")
+    launch_count += 1
+    return out
+
+
+def embedding_backward(idx: torch.Tensor, dy2: torch.Tensor, dweight: torch.Tensor,
+                       dpos: Optional[torch.Tensor] = None, seq_len: int = 0, vocab_start: int = 0) -> None:
+    """Scatter-add ``dy2`` (bf16 ``[T, d]``) into fp32 ``dweight`` (and ``dpos``)."""
+    global launch_count
+    flat = idx.reshape(-1)
+    T, d = dy2.shape
+    if not native.use_native(dy2):
+        local = flat - vocab_start
+        ok = (local >= 0) & (local < dweight.shape[0])
+        dweight.index_add_(0, local[ok], dy2[ok].to(dweight.dtype))
+        if dpos is not None:
+            dpos.index_add_(0, torch.arange(T, device=flat.device) % seq_len, dy2.to(dpos.dtype))
+        return
+    assert dweight.dtype == torch.float32 and dy2.dtype == torch.bfloat16 and dy2.is_contiguous()
+    flat = flat.to(torch.int64).contiguous()
+    st = native.lib().st_embedding_bwd(native.ptr(flat), native.ptr(dy2), native.ptr(dweight), native.ptr(dpos),
+                                       ctypes.c_longlong(T), ctypes.c_int(d), ctypes.c_int(vocab_start),
+                                       ctypes.c_int(dweight.shape[0]), ctypes.c_int(seq_len),
+                                       native.stream_ptr(dy2.device))
+    native.check(st, "st_embedding_bwd")
+    launch_count += 1
+
+
+def row_softmax(x: torch.Tensor, hardmax: bool = False):
+    """fp32 row softmax of a 2-D tensor; with ``hardmax`` also returns the one-hot arg-max mask
+    (lowest index wins ties)."""
+    global launch_count
+    if not native.use_native(x):
+        y = torch.softmax(x.float(), dim=-1)
+        if not hardmax:
+            return y
+        idx = x.float().argmax(dim=-1, keepdim=True)
+        return y, torch.zeros_like(y).scatter_(1, idx, 1.0)
+    xf = x.float().contiguous()
+    y = torch.empty_like(xf)
+    h = torch.empty_like(xf) if hardmax else None
+    st = native.lib().st_row_softmax_f32(native.ptr(xf), native.ptr(y), native.ptr(h), ctypes.c_int(xf.shape[0]),
+                                         ctypes.c_int(xf.shape[1]), native.stream_ptr(x.device))
+    native.check(st, "st_row_softmax_f32")
+    launch_count += 1
+    return (y, h) if hardmax else y
