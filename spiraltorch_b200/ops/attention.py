@@ -71,7 +71,7 @@ def attention_forward(q, k, v, causal: bool = True, scale: Optional[float] = Non
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     if not native.use_native(q):
         o, lse = attention_reference(q, k, v, causal, scale)
-        return o.to(q.dtype), lse
+        return o.to(q.dtype).contiguous(), lse
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_layout(t, n)
     o = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
@@ -101,7 +101,14 @@ def attention_backward(q, k, v, o, lse, do, causal: bool = True, scale: Optional
             qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
             of, _ = attention_reference(qf, kf, vf, causal, scale)
             g = torch.autograd.grad(of, (qf, kf, vf), do.float())
-        return tuple(x.to(q.dtype) for x in g)
+        outs = []
+        for grad, given in zip(g, (dq, dk, dv)):
+            if given is None:
+                outs.append(grad.to(q.dtype))
+            else:
+                given.copy_(grad.to(given.dtype))
+                outs.append(given)
+        return tuple(outs)
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (do, "do")):
         _check_layout(t, n)
     dev = q.device

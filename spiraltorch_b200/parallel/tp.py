@@ -1,0 +1,67 @@
+"""Tensor-parallel communication context (sequence-parallel activations).
+
+Activations between transformer sub-blocks live as row shards ``[T/world, d]``.  A
+column-parallel linear needs the gathered rows (all-gather → GEMM); a row-parallel linear
+produces partial sums that are reduced and scattered back to row shards (GEMM →
+reduce-scatter).  Two implementations share one interface:
+
+* ``mode="nccl"`` – ``torch.distributed`` all-gather / reduce-scatter followed or preceded
+  by the GEMM kernel.  This is the measured baseline.
+* ``mode="fused"`` – the peer-memory kernels of ``csrc/comm`` where the transfer runs tile
+  by tile inside the GEMM launch (see :mod:`spiraltorch_b200.parallel.fused`).
+
+With a world size of 1 both collectives are the identity.
+
+The reference has no tensor parallelism (its only multi-rank path is data parallel,
+crates/spiral-selfsup/src/trainer/distributed.rs); this module is new functionality.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class TPContext:
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, mode: str = "nccl"):
+        self.group = group
+        if group is None or not dist.is_initialized():
+            self.world, self.rank = 1, 0
+        else:
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.mode = mode
+        self.bytes_gathered = 0
+        self.bytes_scattered = 0
+        self.collective_calls = 0
+
+    # -- row collectives -------------------------------------------------------------------
+    def all_gather_rows(self, shard: torch.Tensor) -> torch.Tensor:
+        """[T/world, d] → [T, d] (rank-major row order)."""
+        if self.world == 1:
+            return shard
+        shard = shard.contiguous()
+        out = torch.empty((shard.shape[0] * self.world, *shard.shape[1:]), dtype=shard.dtype,
+                          device=shard.device)
+        dist.all_gather_into_tensor(out, shard, group=self.group)
+        self.bytes_gathered += out.numel() * out.element_size()
+        self.collective_calls += 1
+        return out
+
+    def reduce_scatter_rows(self, full: torch.Tensor) -> torch.Tensor:
+        """[T, d] partial sums on every rank → [T/world, d] reduced row shard."""
+        if self.world == 1:
+            return full
+        full = full.contiguous()
+        out = torch.empty((full.shape[0] // self.world, *full.shape[1:]), dtype=full.dtype,
+                          device=full.device)
+        dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group)
+        self.bytes_scattered += full.numel() * full.element_size()
+        self.collective_calls += 1
+        return out
+
+    def all_reduce_(self, t: torch.Tensor, op=dist.ReduceOp.SUM) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, op=op, group=self.group)
+            self.collective_calls += 1
+        return t
