@@ -341,6 +341,22 @@ class GPTModel(nn.Module):
             out[name] = t.float().cpu()
         return out
 
+    def load_unsharded(self, full: dict) -> None:
+        """Load full (tensor-parallel-free) tensors, keeping this rank's shard of each."""
+        W, r = self.tp.world, self.tp.rank
+        hl, D, H = self.heads_local, self.cfg.head_dim, self.cfg.n_heads
+        with torch.no_grad():
+            for name, p in self.p.items():
+                t = full[name]
+                if W > 1:
+                    if name.endswith("qkv.weight"):
+                        t = t.view(3, H, D, -1)[:, r * hl:(r + 1) * hl].reshape(3 * hl * D, -1)
+                    elif name.endswith("fc1.weight") or name == "embed.weight":
+                        t = t.chunk(W, dim=0)[r]
+                    elif name.endswith("proj.weight") or name.endswith("fc2.weight"):
+                        t = t.chunk(W, dim=1)[r]
+                p.copy_(t.to(p.dtype))
+
     def describe(self) -> dict:
         d = asdict(self.cfg)
         d.update(params=self.cfg.param_count(), tp=self.tp.world, flat_elems_per_rank=self.flat_elems)

@@ -31,6 +31,7 @@ class TPContext:
         else:
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.mode = mode
+        self._gloo = (self.world > 1 and dist.get_backend(group) == "gloo")
         self.bytes_gathered = 0
         self.bytes_scattered = 0
         self.collective_calls = 0
@@ -43,7 +44,11 @@ class TPContext:
         shard = shard.contiguous()
         out = torch.empty((shard.shape[0] * self.world, *shard.shape[1:]), dtype=shard.dtype,
                           device=shard.device)
-        dist.all_gather_into_tensor(out, shard, group=self.group)
+        if self._gloo:  # CPU test path
+            parts = list(out.chunk(self.world, dim=0))
+            dist.all_gather(parts, shard, group=self.group)
+        else:
+            dist.all_gather_into_tensor(out, shard, group=self.group)
         self.bytes_gathered += out.numel() * out.element_size()
         self.collective_calls += 1
         return out
@@ -55,7 +60,12 @@ class TPContext:
         full = full.contiguous()
         out = torch.empty((full.shape[0] // self.world, *full.shape[1:]), dtype=full.dtype,
                           device=full.device)
-        dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group)
+        if self._gloo:  # CPU test path: all-reduce then keep the local rows
+            tmp = full.clone()
+            dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=self.group)
+            out.copy_(tmp.chunk(self.world, dim=0)[self.rank])
+        else:
+            dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group)
         self.bytes_scattered += full.numel() * full.element_size()
         self.collective_calls += 1
         return out
