@@ -88,6 +88,14 @@ bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const vo
                  CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode();
   if (!fn) return false;
+  // The driver entry point needs a current context on the calling thread.  Threads that
+  // have only used the runtime API lazily (e.g. an autograd worker) may not have one yet:
+  // a no-op runtime call binds the primary context of the current device.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bdim[5];

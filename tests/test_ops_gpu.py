@@ -1,0 +1,228 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from spiraltorch_b200.ops import attention as A
+from spiraltorch_b200.ops import elementwise as E
+from spiraltorch_b200.ops import gemm as G
+from spiraltorch_b200.ops import loss as L
+from spiraltorch_b200.ops import native
+from spiraltorch_b200.ops import norm as N
+from spiraltorch_b200.ops import optim as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+def _no_device_error():
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 776, 520), (4096, 128, 1024), (77, 40, 8)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV).bfloat16()
+    c = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = (a.float().T if a_mn else a.float()) @ (b.float() if b_mn else b.float().T)
+    assert _rel(c, ref) < 1e-2
+    _no_device_error()
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(2)
+    M, N, K = 384, 520, 264
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = torch.randn(N, K, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    res = torch.randn(M, N, device=DEV).bfloat16()
+    aux = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    out = G.gemm(a, b, bias=bias, act="gelu", residual=res, alpha=0.5, aux_out=aux)
+    pre = 0.5 * (a.float() @ b.float().T) + bias.float()
+    ref = torch.nn.functional.gelu(pre, approximate="tanh") + res.float()
+    assert _rel(out, ref) < 1e-2 and _rel(aux, pre) < 1e-2
+    out = G.gemm(a, b, act="gelu_bwd", aux_in=res)
+    assert _rel(out, (a.float() @ b.float().T) * G.gelu_tanh_grad(res.float())) < 1e-2
+    out = G.gemm(a, b, bias=bias, act="relu")
+    assert _rel(out, torch.relu(a.float() @ b.float().T + bias.float())) < 1e-2
+    acc = torch.ones(M, N, device=DEV)
+    G.gemm(a, b, out=acc, accumulate=True)
+    assert _rel(acc, 1 + a.float() @ b.float().T) < 1e-2
+    ab = torch.randn(5, 200, 64, device=DEV).bfloat16()
+    bb = torch.randn(5, 136, 64, device=DEV).bfloat16()
+    assert _rel(G.gemm(ab, bb), ab.float() @ bb.float().transpose(1, 2)) < 1e-2
+    _no_device_error()
+
+
+def test_linear_autograd():
+    torch.manual_seed(3)
+    x = torch.randn(256, 128, device=DEV).bfloat16().requires_grad_(True)
+    w = torch.randn(192, 128, device=DEV).bfloat16().requires_grad_(True)
+    b = torch.randn(192, device=DEV).bfloat16().requires_grad_(True)
+    y = G.linear(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    (xf @ wf.T + bf).backward(dy.float())
+    assert _rel(x.grad, xf.grad) < 2e-2 and _rel(w.grad, wf.grad) < 2e-2 and _rel(b.grad, bf.grad) < 2e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("B,S,H,causal", [(1, 128, 1, True), (2, 512, 3, False), (1, 300, 2, True), (2, 1024, 2, True)])
+def test_attention_fwd_bwd(D, B, S, H, causal):
+    torch.manual_seed(4)
+    qkv = torch.randn(B, S, 3, H, D, device=DEV).bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    do = torch.randn(B, S, H, D, device=DEV).bfloat16()
+    o, lse = A.attention_forward(q, k, v, causal)
+    dq, dk, dv = A.attention_backward(q, k, v, o, lse, do, causal)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ro, rl = A.attention_reference(qf, kf, vf, causal, 1 / math.sqrt(D))
+    g = torch.autograd.grad(ro, (qf, kf, vf), do.float())
+    assert (o.float() - ro).abs().max().item() < 2e-2
+    assert (lse - rl).abs().max().item() < 1e-3
+    for mine, ref in zip((dq, dk, dv), g):
+        assert _rel(mine, ref) < 2e-2
+    _no_device_error()
+
+
+@pytest.mark.parametrize("rms", [True, False])
+@pytest.mark.parametrize("rows,d", [(64, 768), (1000, 2048), (33, 8192), (7, 264)])
+def test_norm_fwd_bwd(rms, rows, d):
+    torch.manual_seed(5)
+    x = torch.randn(rows, d, device=DEV).bfloat16()
+    res = torch.randn(rows, d, device=DEV).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    beta = None if rms else (0.1 * torch.randn(d, device=DEV)).bfloat16()
+    dy = torch.randn(rows, d, device=DEV).bfloat16()
+    y, s, mean, rstd = N.norm_forward(x, gamma, beta, 1e-5, rms, residual=res)
+    ry, rs, rmean, rrstd = N.norm_reference(x, gamma, beta, 1e-5, rms, residual=res)
+    assert _rel(y, ry) < 1e-2 and _rel(s, rs) < 1e-2 and _rel(rstd, rrstd) < 1e-3
+    dg = torch.zeros(d, device=DEV)
+    db = None if rms else torch.zeros(d, device=DEV)
+    dx = N.norm_backward(dy, s, gamma, mean, rstd, rms, dg, db, False, dres=res)
+    xs = s.float().requires_grad_(True)
+    gf = gamma.float().requires_grad_(True)
+    bf = None if rms else beta.float().requires_grad_(True)
+    yy = N.norm_reference(xs, gf, bf, 1e-5, rms)[0]
+    yy.backward(dy.float())
+    assert _rel(dx, xs.grad + res.float()) < 2e-2
+    assert _rel(dg, gf.grad) < 2e-2
+    if not rms:
+        assert _rel(db, bf.grad) < 2e-2
+
+
+def test_rope_roundtrip_and_reference():
+    torch.manual_seed(6)
+    T, H, D, S = 512, 6, 128, 128
+    x = torch.randn(T, 3 * H * D, device=DEV).bfloat16()
+    ref = x.clone()
+    cos, sin = E.rope_tables(S, D, 10000.0, DEV)
+    view = ref[:, : 2 * H * D].reshape(T, 2 * H, D)
+    expect = E.rope_reference(view, cos, sin, S, False)
+    y = E.rope_(x.clone(), 2 * H, D, S)
+    assert _rel(y[:, : 2 * H * D].reshape(T, 2 * H, D), expect) < 1e-2
+    assert torch.equal(y[:, 2 * H * D:], x[:, 2 * H * D:])
+    back = E.rope_(y.clone(), 2 * H, D, S, backward=True)
+    assert _rel(back, x) < 2e-2
+
+
+@pytest.mark.parametrize("V", [50304, 256, 1000])
+def test_cross_entropy(V):
+    torch.manual_seed(7)
+    rows = 257
+    ld = (V + 7) // 8 * 8
+    buf = (3 * torch.randn(rows, ld, device=DEV)).bfloat16()
+    logits = buf[:, :V]
+    tgt = torch.randint(0, V, (rows,), device=DEV)
+    tgt[5] = L.IGNORE_INDEX
+    lf = logits.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, tgt, ignore_index=L.IGNORE_INDEX)
+    ref.backward()
+    x = logits.clone() if V % 8 == 0 else logits
+    x = x.detach().requires_grad_(True)
+    loss = L.cross_entropy(x, tgt)
+    loss.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3
+    assert (x.grad.float() - lf.grad).abs().max().item() < 2e-4 + 1e-2 * lf.grad.abs().max().item()
+
+
+def test_embedding_and_colsum_and_softmax():
+    torch.manual_seed(8)
+    V, d, T, S = 300, 256, 1024, 128
+    w = torch.randn(V, d, device=DEV).bfloat16()
+    pos = torch.randn(S, d, device=DEV).bfloat16()
+    idx = torch.randint(0, V, (T,), device=DEV)
+    out = E.embedding_forward(idx, w, pos, S)
+    assert _rel(out, w[idx].float() + pos[torch.arange(T, device=DEV) % S].float()) < 1e-2
+    shard = E.embedding_forward(idx, w[100:200].contiguous(), None, 0, vocab_start=100)
+    ok = (idx >= 100) & (idx < 200)
+    assert torch.equal(shard[~ok], torch.zeros_like(shard[~ok])) and torch.equal(shard[ok], w[idx[ok]])
+    dy = torch.randn(T, d, device=DEV).bfloat16()
+    dw = torch.zeros(V, d, device=DEV)
+    dpos = torch.zeros(S, d, device=DEV)
+    E.embedding_backward(idx, dy, dw, dpos, S)
+    rw = torch.zeros(V, d, device=DEV).index_add_(0, idx, dy.float())
+    assert _rel(dw, rw) < 1e-3
+    assert _rel(dpos, dy.float().view(-1, S, d).sum(0)) < 1e-3
+    cs = E.colsum(dy)
+    assert _rel(cs, dy.float().sum(0)) < 1e-3
+    x = torch.randn(37, 1000, device=DEV)
+    y, h = E.row_softmax(x, hardmax=True)
+    assert _rel(y, torch.softmax(x, -1)) < 1e-4
+    assert torch.equal(h.argmax(-1), x.argmax(-1)) and h.sum().item() == 37
+    for kind in ("gelu", "relu"):
+        t = torch.randn(64, 256, device=DEV).bfloat16().requires_grad_(True)
+        f = E.gelu if kind == "gelu" else E.relu
+        f(t).backward(dy[:64])
+        tf = t.detach().float().requires_grad_(True)
+        rf = torch.nn.functional.gelu(tf, approximate="tanh") if kind == "gelu" else torch.relu(tf)
+        rf.backward(dy[:64].float())
+        assert _rel(t.grad, tf.grad) < 2e-2
+
+
+def test_fused_optimizers():
+    torch.manual_seed(9)
+    n = 100_003
+    g = torch.randn(n, device=DEV)
+    master = torch.randn(n, device=DEV)
+    m, v = torch.rand(n, device=DEV), torch.rand(n, device=DEV)
+    w = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ref = [t.clone() for t in (g, master, m, v)]
+    coef = torch.tensor([0.5], device=DEV)
+    O.adamw_step(g, master, m, v, w, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3,
+                 grad_scale=0.25, scale_tensor=coef, zero_grad=True)
+    O.adamw_reference(ref[0], ref[1], ref[2], ref[3], None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, 0.125, False)
+    assert _rel(master, ref[1]) < 1e-5 and _rel(m, ref[2]) < 1e-5 and _rel(v, ref[3]) < 1e-5
+    assert _rel(w, master) < 1e-2 and g.abs().max().item() == 0
+    ss = torch.zeros(1, device=DEV)
+    x = torch.randn(50_001, device=DEV)
+    O.sumsq(x, ss)
+    assert abs(ss.item() - x.pow(2).sum().item()) / x.pow(2).sum().item() < 1e-4
+    c, nrm = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
+    O.clip_coef(ss, 1.0, 1.0, c, nrm)
+    assert abs(c.item() - 1.0 / (x.norm().item() + 1e-6)) < 1e-5
+    # Amegagrad tapes against the CPU restatement
+    wt = torch.randn(33, 70, device=DEV) * 0.3
+    gt = torch.zeros_like(wt)
+    wave = torch.randn_like(wt)
+    wc, gc = wt.cpu().clone(), gt.cpu().clone()
+    kw = dict(curvature=-1.0, tol=1e-6, saturation=1e6, porosity=0.2)
+    O.hyper_accumulate(gt, wave, **kw)
+    O.hyper_accumulate(gc, wave.cpu(), **kw)
+    assert _rel(gt.cpu(), gc) < 1e-5
+    rt = torch.randn_like(wt)
+    rc = rt.cpu().clone()
+    O.hyper_apply(wt, gt, rt, curvature=-1.0, lr=0.05, lr_real=0.01, tol=1e-6, saturation=1e6, porosity=0.2)
+    O.hyper_apply(wc, gc, rc, curvature=-1.0, lr=0.05, lr_real=0.01, tol=1e-6, saturation=1e6, porosity=0.2)
+    assert _rel(wt.cpu(), wc) < 1e-4 and gt.abs().max().item() == 0 and rt.abs().max().item() == 0
+    pr = O.project_to_poincare(wave, -0.5)
+    assert _rel(pr.cpu(), O.project_to_poincare(wave.cpu(), -0.5)) < 1e-5
