@@ -291,3 +291,46 @@ ST_API int st_norm_bwd(int rms, const void* dy, const void* x, const void* gamma
   return st::norm_bwd_launch(rms, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, accumulate,
                              scratch, rows, d, reinterpret_cast<cudaStream_t>(stream_v));
 }
+
+// ------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (see norm_noalloc.h).
+// ------------------------------------------------------------------------------------------
+#include "norm_noalloc.h"
+#include <cstdio>
+
+// Scratch for the per-CTA dgamma / dbeta partials.  In host code this name is only a handle
+// for cudaGetSymbolAddress; the kernels get the real device address as an argument.
+static __device__ __align__(256) float g_norm_bwd_static_scratch[ST_NORM_BWD_NOALLOC_MAX_ELEMS];
+
+namespace {
+constexpr int kNoallocMaxDevices = 16;
+float* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+}  // namespace
+
+ST_API int st_norm_bwd_noalloc(int rms, const void* dy, const void* x, const void* gamma,
+                               const float* mean, const float* rstd, const void* dres, void* dx,
+                               float* dgamma, float* dbeta, int accumulate, int rows, int d,
+                               void* stream_v) {
+  if (rows <= 0 || d <= 0) return st::fail(ST_ERR_INVALID, "norm_bwd_noalloc: non-positive dimension");
+  const long long need = 2ll * st::norm_bwd_grid(rows) * d;
+  if (need > (long long)ST_NORM_BWD_NOALLOC_MAX_ELEMS) {
+    char buf[200];
+    snprintf(buf, sizeof(buf),
+             "norm_bwd_noalloc: rows=%d d=%d needs %lld scratch floats, the built-in buffer holds %d; "
+             "use st_norm_bwd with a caller-provided scratch buffer",
+             rows, d, need, (int)ST_NORM_BWD_NOALLOC_MAX_ELEMS);
+    return st::fail(ST_ERR_TOO_LARGE, buf);
+  }
+  int dev = 0;
+  ST_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoallocMaxDevices) return st::fail(ST_ERR_INVALID, "norm_bwd_noalloc: device index out of range");
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // once per device, with that device current: resolve the array's device address
+    float* p = nullptr;
+    ST_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_static_scratch));
+    if (p == nullptr) return st::fail(ST_ERR_CUDA, "norm_bwd_noalloc: cudaGetSymbolAddress returned null");
+    g_noalloc_ptr[dev] = p;
+  }
+  return st::norm_bwd_launch(rms, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, accumulate,
+                             g_noalloc_ptr[dev], rows, d, reinterpret_cast<cudaStream_t>(stream_v));
+}

@@ -1,0 +1,84 @@
+"""The allocation-free norm backward (``st_norm_bwd_noalloc``) must agree with ``st_norm_bwd``.
+
+Some users of the library cannot allocate device memory when they need this op (a serving
+loop that pre-carved all device memory, a host application with its own allocator), so the
+library offers a variant whose scratch lives in a fixed array inside the ``.so``.  The test
+calls the exported C symbol directly through ctypes, twice in a row (the array keeps the
+previous call's contents, so the second call checks that stale data does no harm), and
+compares with the regular entry point that takes a caller-provided scratch buffer.  It also
+checks that an over-sized problem is refused with a clear message and nothing is written.
+This file sorts last so that a run that stops at the first failure has already run
+everything else.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from spiraltorch_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+
+
+def _vp(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _run_pair(lib, rms, rows, d, seed):
+    torch.manual_seed(seed)
+    dev = "cuda"
+    x = torch.randn(rows, d, device=dev).bfloat16()
+    dy = torch.randn(rows, d, device=dev).bfloat16()
+    dres = torch.randn(rows, d, device=dev).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(d, device=dev)).bfloat16()
+    xf = x.float()
+    if rms:
+        mean = torch.zeros(rows, device=dev)
+        rstd = torch.rsqrt(xf.pow(2).mean(-1) + 1e-5)
+    else:
+        mean = xf.mean(-1)
+        rstd = torch.rsqrt(xf.var(-1, unbiased=False) + 1e-5)
+    stream = native.stream_ptr(torch.device(dev))
+    outs = []
+    for which in ("scratch", "noalloc"):
+        dx = torch.empty_like(x)
+        dgamma = torch.full((d,), 0.5, device=dev)
+        dbeta = torch.full((d,), -0.25, device=dev)
+        common = [ctypes.c_int(int(rms)), _vp(dy), _vp(x), _vp(gamma), _vp(mean), _vp(rstd), _vp(dres), _vp(dx),
+                  _vp(dgamma), _vp(None if rms else dbeta), ctypes.c_int(1)]
+        if which == "scratch":
+            lib.st_norm_bwd_scratch_elems.restype = ctypes.c_longlong
+            n = lib.st_norm_bwd_scratch_elems(ctypes.c_int(rows), ctypes.c_int(d))
+            scratch = torch.empty(int(n), device=dev)
+            st = lib.st_norm_bwd(*common, _vp(scratch), ctypes.c_int(rows), ctypes.c_int(d), stream)
+        else:
+            st = lib.st_norm_bwd_noalloc(*common, ctypes.c_int(rows), ctypes.c_int(d), stream)
+        assert st == 0, native.last_error()
+        torch.cuda.synchronize()
+        outs.append((dx, dgamma, dbeta))
+    (dx0, dg0, db0), (dx1, dg1, db1) = outs
+    assert torch.equal(dx0, dx1)
+    assert torch.allclose(dg0, dg1, rtol=1e-5, atol=1e-5)
+    if not rms:
+        assert torch.allclose(db0, db1, rtol=1e-5, atol=1e-5)
+
+
+def test_noalloc_matches_scratch_entry_point_twice_in_a_row():
+    lib = native.lib()
+    _run_pair(lib, True, 1000, 2048, seed=1)
+    _run_pair(lib, False, 333, 768, seed=2)     # second call: the array still holds call one's partials
+    _run_pair(lib, True, 64, 8192, seed=3)
+
+
+def test_noalloc_rejects_oversized_problem():
+    lib = native.lib()
+    d, rows = 8192, 4096
+    x = torch.zeros(8, device="cuda")
+    sentinel = torch.full((8,), 7.0, device="cuda")
+    st = lib.st_norm_bwd_noalloc(ctypes.c_int(1), _vp(x), _vp(x), _vp(x), _vp(x), _vp(x), _vp(None), _vp(sentinel),
+                                 _vp(sentinel), _vp(None), ctypes.c_int(0), ctypes.c_int(rows), ctypes.c_int(d),
+                                 native.stream_ptr(torch.device("cuda")))
+    assert st == 3
+    assert "built-in buffer holds" in native.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(sentinel, torch.full((8,), 7.0, device="cuda"))
