@@ -1,0 +1,211 @@
+// Launchers for the tensor-parallel fused GEMMs (the kernel lives in gemm/gemm_kernel.cuh):
+//
+//   st_ag_gemm   Y[T, N_local] = epilogue(gather(X_shard)[T, K] · Wᵀ)   all-gather → GEMM
+//   st_gemm_rs   Y_shard[T/W, N] = reduce-scatter(A[T, K_local] · Wᵀ)   GEMM → reduce-scatter
+//
+// Both take B either K-major ([N, K], forward) or MN-major ([K, N], data gradient).  Peer
+// pointers and signal areas come from symmetric allocations made by the Python side
+// (spiraltorch_b200/parallel/symm.py).  With world == 1 the launchers degenerate to the
+// local case (the "peer" is this GPU), which is how the single-GPU tests exercise them.
+//
+// The reference has no tensor parallelism; the baseline these are measured against is
+// NCCL all-gather / reduce-scatter around the same GEMM kernel.
+#include "../gemm/gemm_kernel.cuh"
+#include <cstring>
+
+struct StPeerGroup {
+  int world, rank;
+  unsigned epoch;
+  unsigned long long signals[st::kMaxRanks];
+  unsigned long long signals_mc;
+};
+namespace st {
+void fill_peer_group(PeerGroup& g, const StPeerGroup& s);
+}
+
+namespace {
+using namespace st;
+using namespace st::gemm;
+
+constexpr int BN = 256;
+constexpr int STAGES = 4;
+
+template <bool B_MN, int COMM>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, const GemmParams& p,
+           const GemmComm& cm, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, false, B_MN, COMM>;
+  static bool configured = false;
+  if (!configured) {
+    ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured = true;
+  }
+  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, p, cm);
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}
+
+bool make_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
+               long long lda, long long ldb, int b_mn) {
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  dims[0] = K; dims[1] = M; dims[2] = 1; box[0] = BK; box[1] = BM; box[2] = 1;
+  strides[0] = (uint64_t)lda * 2; strides[1] = (uint64_t)lda * 2 * M;
+  if (!encode_tmap(tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+    return false;
+  if (!b_mn) {
+    dims[0] = K; dims[1] = N; box[0] = BK; box[1] = BN;
+    strides[1] = (uint64_t)ldb * 2 * N;
+  } else {
+    dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK;
+    strides[1] = (uint64_t)ldb * 2 * K;
+  }
+  strides[0] = (uint64_t)ldb * 2;
+  return encode_tmap(tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+struct StAgGemmArgs {
+  StPeerGroup g;
+  unsigned long long x_shard;                  // bf16 [T/W, K] contiguous (this rank's rows)
+  unsigned long long gather_peers[st::kMaxRanks];  // bf16 [T, K] on every rank (symmetric)
+  unsigned long long gather_mc;                // multicast alias of the gather buffer or 0
+  unsigned long long B;                        // bf16 weights: [N, K] or, b_mn, [K, N]
+  unsigned long long C;                        // bf16 [T, N]
+  unsigned long long bias, aux_out, aux_in;    // optional epilogue operands (bf16)
+  long long ldb, ldc, ld_aux_out, ld_aux_in;
+  int T, N, K;
+  int b_mn, act;
+  float alpha;
+  int sub_per_chunk;   // arrival-flag granularity per rank shard
+  int comm_ctas;       // CTAs that only push (taken from the SM budget)
+  int slot_enter, slot_arrive;
+};
+
+ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
+  if (!a) return st::fail(ST_ERR_INVALID, "ag_gemm: null args");
+  const int W = a->g.world;
+  if (W < 1 || W > st::kMaxRanks) return st::fail(ST_ERR_INVALID, "ag_gemm: bad world size");
+  if (a->T % (W * BM) != 0) return st::fail(ST_ERR_INVALID, "ag_gemm: T must be a multiple of world*128");
+  const int rows = a->T / W;
+  if (a->sub_per_chunk < 1 || rows % (a->sub_per_chunk * BM) != 0)
+    return st::fail(ST_ERR_INVALID, "ag_gemm: shard rows must be a multiple of sub_per_chunk*128");
+  if (a->K % 8 || a->ldb % 8) return st::fail(ST_ERR_INVALID, "ag_gemm: K and ldb must be multiples of 8");
+  if (a->comm_ctas < 1) return st::fail(ST_ERR_INVALID, "ag_gemm: needs at least one communication CTA");
+  const void* gathered = reinterpret_cast<const void*>(a->gather_peers[a->g.rank]);
+  CUtensorMap tmA, tmB;
+  if (!make_maps(&tmA, &tmB, gathered, reinterpret_cast<const void*>(a->B), a->T, a->N, a->K, a->K, a->ldb, a->b_mn))
+    return ST_ERR_CUDA;
+  GemmParams p{};
+  p.C = reinterpret_cast<void*>(a->C);
+  p.ldc = a->ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(a->aux_out);
+  p.ld_aux_out = a->ld_aux_out;
+  p.aux_in = reinterpret_cast<const __nv_bfloat16*>(a->aux_in);
+  p.ld_aux_in = a->ld_aux_in;
+  p.M = a->T; p.N = a->N; p.K = a->K;
+  p.alpha = a->alpha; p.act = a->act;
+  p.batch = 1;
+  p.err = st::error_word();
+  GemmComm cm{};
+  st::fill_peer_group(cm.g, a->g);
+  cm.rows_per_chunk = rows;
+  cm.sub_per_chunk = a->sub_per_chunk;
+  cm.slot_enter = a->slot_enter;
+  cm.slot_arrive = a->slot_arrive;
+  cm.src_shard = reinterpret_cast<const __nv_bfloat16*>(a->x_shard);
+  for (int i = 0; i < st::kMaxRanks; ++i) cm.gather_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->gather_peers[i]);
+  cm.gather_mc = reinterpret_cast<__nv_bfloat16*>(a->gather_mc);
+  const int tiles = (a->T / BM) * ((a->N + BN - 1) / BN);
+  int comm = a->comm_ctas;
+  int sms = st::sm_count();
+  if (comm > sms / 2) comm = sms / 2;
+  int gemm_ctas = sms - comm;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  cm.gemm_ctas = gemm_ctas;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OutMaps tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  p.use_tma_store = ((a->ldc & 7) == 0 && (a->C & 15) == 0) ? 1 : 0;
+  if (p.use_tma_store) {
+    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)a->T, 1};
+    uint64_t strides[2] = {(uint64_t)a->ldc * 2, (uint64_t)a->ldc * 2 * a->T};
+    uint32_t box[3] = {64, 32, 1};
+    if (!encode_tmap(&tmC.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, reinterpret_cast<const void*>(a->C), dims,
+                     strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return ST_ERR_CUDA;
+  }
+  if (a->b_mn) return launch<true, COMM_AG>(tmA, tmB, tmC, p, cm, gemm_ctas + comm, stream);
+  return launch<false, COMM_AG>(tmA, tmB, tmC, p, cm, gemm_ctas + comm, stream);
+}
+
+struct StGemmRsArgs {
+  StPeerGroup g;
+  unsigned long long A;                          // bf16 [T, K_local]
+  unsigned long long B;                          // bf16 [N, K_local] or, b_mn, [K_local, N]
+  unsigned long long stage_peers[st::kMaxRanks]; // bf16 [W][T/W, N] staging on every rank (symmetric)
+  unsigned long long out;                        // bf16 [T/W, N] reduced shard (local)
+  unsigned long long residual;                   // optional bf16 [T/W, N] added in the reduction
+  long long lda, ldb;
+  int T, N, K;
+  int b_mn;
+  float alpha;
+  int slot_enter, slot_done;
+  unsigned done_target;                          // cumulative warp arrivals expected per row block
+};
+
+ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
+  if (!a) return st::fail(ST_ERR_INVALID, "gemm_rs: null args");
+  const int W = a->g.world;
+  if (W < 1 || W > st::kMaxRanks) return st::fail(ST_ERR_INVALID, "gemm_rs: bad world size");
+  if (a->T % (W * BM) != 0) return st::fail(ST_ERR_INVALID, "gemm_rs: T must be a multiple of world*128");
+  if (a->N % 8 || a->K % 8 || a->lda % 8 || a->ldb % 8)
+    return st::fail(ST_ERR_INVALID, "gemm_rs: N, K, lda, ldb must be multiples of 8");
+  CUtensorMap tmA, tmB;
+  if (!make_maps(&tmA, &tmB, reinterpret_cast<const void*>(a->A), reinterpret_cast<const void*>(a->B), a->T,
+                 a->N, a->K, a->lda, a->ldb, a->b_mn))
+    return ST_ERR_CUDA;
+  GemmParams p{};
+  p.C = nullptr;  // the epilogue addresses the owners' staging areas
+  p.ldc = a->N;
+  p.M = a->T; p.N = a->N; p.K = a->K;
+  p.alpha = a->alpha;
+  p.batch = 1;
+  p.err = st::error_word();
+  GemmComm cm{};
+  st::fill_peer_group(cm.g, a->g);
+  cm.rows_per_chunk = a->T / W;
+  cm.sub_per_chunk = 1;
+  cm.slot_enter = a->slot_enter;
+  cm.slot_done = a->slot_done;
+  cm.done_target = a->done_target;
+  for (int i = 0; i < st::kMaxRanks; ++i) cm.stage_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->stage_peers[i]);
+  cm.rs_out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  cm.rs_residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  const int tiles = (a->T / BM) * ((a->N + BN - 1) / BN);
+  int grid = st::sm_count();
+  if (grid > tiles) grid = tiles;
+  cm.gemm_ctas = grid;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OutMaps tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  p.use_tma_store = 1;
+  const int rows = a->T / W;
+  for (int q = 0; q < W; ++q) {
+    // this rank's slot inside owner q's staging area
+    const char* base = reinterpret_cast<const char*>(a->stage_peers[q]) + (size_t)a->g.rank * rows * a->N * 2;
+    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)rows, 1};
+    uint64_t strides[2] = {(uint64_t)a->N * 2, (uint64_t)a->N * 2 * rows};
+    uint32_t box[3] = {64, 32, 1};
+    if (!encode_tmap(&tmC.m[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return ST_ERR_CUDA;
+  }
+  if (a->b_mn) return launch<true, COMM_RS>(tmA, tmB, tmC, p, cm, grid, stream);
+  return launch<false, COMM_RS>(tmA, tmB, tmC, p, cm, grid, stream);
+}
+
+// Number of warp arrivals one launch of st_gemm_rs adds to every row-block counter.
+ST_API int st_gemm_rs_arrivals_per_launch(int world, int N) { return world * ((N + BN - 1) / BN) * 4; }

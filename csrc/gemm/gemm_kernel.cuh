@@ -1,0 +1,668 @@
+// The persistent tcgen05 GEMM kernel, shared by the plain launcher (gemm_sm100.cu) and the
+// tensor-parallel launchers (csrc/comm/tp_gemm.cu).
+//
+// COMM selects what else the launch does:
+//   COMM_NONE  C = epilogue(alpha * A·Bᵀ)
+//   COMM_AG    all-gather → GEMM.  A is the gathered activation [T, K]; its row chunks are
+//              produced by `comm_ctas` extra CTAs of the SAME launch on every rank, which
+//              push the local shard into every rank's gather buffer (multimem.st through
+//              NVSwitch, or peer stores) and publish per-sub-chunk arrival flags.  The TMA
+//              producer of a GEMM CTA waits (bounded) for the flag of the rows it is about
+//              to load; tiles are ordered local chunk first, then in ring order.
+//   COMM_RS    GEMM → reduce-scatter.  The epilogue writes each partial tile straight into
+//              the staging slot of the rank that owns those rows (peer stores over NVLink),
+//              then bumps that owner's per-row-block counter; tiles are ordered so that the
+//              local chunk comes last.  After its tiles a CTA reduces row blocks of the
+//              local chunk as soon as all ranks' partials have landed (fp32 sum of the
+//              staging slots, optional residual add) and writes the bf16 shard.
+#pragma once
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "../comm/comm.cuh"
+
+namespace st {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_BWD = 3, ACT_RELU_BWD = 4 };
+enum Comm : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+
+struct GemmComm {
+  PeerGroup g;
+  int rows_per_chunk;   // rows owned by each rank (T / world), multiple of BM
+  int sub_per_chunk;    // arrival-flag granularity (AG): sub-chunks per rank shard
+  int gemm_ctas;        // CTAs that run GEMM tiles; CTAs beyond them only push (AG)
+  int slot_enter;       // entry rendezvous slot (world words)
+  // ---- AG ----
+  const __nv_bfloat16* src_shard;          // [rows_per_chunk, K] contiguous
+  __nv_bfloat16* gather_peers[kMaxRanks];  // [T, K] contiguous on every rank
+  __nv_bfloat16* gather_mc;                // multicast alias or null
+  int slot_arrive;      // flags: slot_arrive + src * sub_per_chunk + sub
+  // ---- RS ----
+  __nv_bfloat16* stage_peers[kMaxRanks];   // on each owner: [world][rows_per_chunk, N]
+  int slot_done;        // counters: slot_done + row block within the chunk
+  unsigned done_target; // counter value meaning "every rank's tiles of this row block landed"
+  __nv_bfloat16* rs_out;                   // [rows_per_chunk, N] reduced local shard
+  const __nv_bfloat16* rs_residual;        // optional, added during the reduction
+};
+
+struct GemmParams {
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* aux_out;
+  long long ld_aux_out;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux_in;
+  int M, N, K;
+  float alpha;
+  int act;
+  int out_fp32;
+  int accumulate;
+  int batch;
+  long long batch_stride_c;
+  int use_tma_store;   // bf16 output without accumulation: stage through smem, store by TMA
+  unsigned* err;
+};
+
+// Tensor maps of the output: [0] for a plain GEMM, one per owner rank for GEMM → reduce-scatter.
+struct OutMaps {
+  CUtensorMap m[kMaxRanks];
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int CSTAGE_OFFSET = STAGES * STAGE_BYTES;       // 4 warps x 2 buffers x 4 KiB
+  static constexpr int CSTAGE_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_OFFSET = CSTAGE_OFFSET + CSTAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // groups of 8 M-tiles share the same B tiles while they are L2-resident
+  constexpr int GM = 8;
+  const int group_size = GM * tiles_n;
+  const int g = t / group_size;
+  const int first_m = g * GM;
+  const int gm = min(GM, tiles_m - first_m);
+  const int r = t - g * group_size;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+// Tile index → (batch, tm, tn); with a communication plan the M dimension is walked chunk by
+// chunk in ring order (`chunk_shift` = 0 starts at the local chunk, 1 ends with it).
+template <int COMM>
+__device__ __forceinline__ void map_tile(int t, int tiles_m, int tiles_n, int tiles_per_batch,
+                                         const GemmComm& c, int& b, int& tm, int& tn) {
+  if constexpr (COMM == COMM_NONE) {
+    b = t / tiles_per_batch;
+    tile_coords(t - b * tiles_per_batch, tiles_m, tiles_n, tm, tn);
+  } else {
+    b = 0;
+    const int tiles_m_chunk = c.rows_per_chunk / BM;
+    const int per_chunk = tiles_m_chunk * tiles_n;
+    const int ci = t / per_chunk;
+    int lm;
+    tile_coords(t - ci * per_chunk, tiles_m_chunk, tiles_n, lm, tn);
+    const int shift = (COMM == COMM_AG) ? 0 : 1;
+    const int chunk = (c.g.rank + shift + ci) % c.g.world;
+    tm = chunk * tiles_m_chunk + lm;
+  }
+}
+
+__device__ __forceinline__ void epilogue_bar() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int COMM>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ OutMaps tmC, const GemmParams p, const GemmComm cm) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ------------------------------------------------------------------------------------------
+  // AG: CTAs past the GEMM grid push this rank's shard to every rank and publish the flags.
+  // ------------------------------------------------------------------------------------------
+  if constexpr (COMM == COMM_AG) {
+    if (static_cast<int>(blockIdx.x) >= cm.gemm_ctas) {
+      __shared__ int s_ok;
+      const int W = cm.g.world, R = cm.g.rank;
+      const int cta = blockIdx.x - cm.gemm_ctas;
+      const int n_comm = gridDim.x - cm.gemm_ctas;
+      if (threadIdx.x == 0) {
+        bool ok = true;
+        if (cta == 0) {
+          fence_sys();
+          for (int q = 0; q < W; ++q) st_release_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
+        }
+        // peers must have left the previous launch that read this gather buffer
+        for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
+        s_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!s_ok) {
+        if (threadIdx.x == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
+        return;
+      }
+      const long long sub_elems = (long long)(cm.rows_per_chunk / cm.sub_per_chunk) * p.K;
+      if (cm.gather_mc) {
+        // NVLS: one multimem.st reaches every rank; eight independent 16-byte loads per thread
+        // are in flight before the stores are issued
+        for (int s = cta; s < cm.sub_per_chunk; s += n_comm) {
+          const __nv_bfloat16* src = cm.src_shard + (long long)s * sub_elems;
+          const long long dst_off = ((long long)R * cm.rows_per_chunk) * p.K + (long long)s * sub_elems;
+          constexpr int U = 8;
+          for (long long i0 = threadIdx.x * 8ll; i0 < sub_elems; i0 += NUM_THREADS * 8ll * U) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const long long i = i0 + (long long)u * NUM_THREADS * 8;
+              if (i < sub_elems) v[u] = *reinterpret_cast<const uint4*>(src + i);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const long long i = i0 + (long long)u * NUM_THREADS * 8;
+              if (i < sub_elems) multimem_st_v4(cm.gather_mc + dst_off + i, v[u]);
+            }
+          }
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            fence_sys();
+            for (int q = 0; q < W; ++q)
+              st_release_sys(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * cm.sub_per_chunk + s, cm.g.epoch);
+          }
+        }
+      } else if (threadIdx.x == 0) {
+        // no multicast: one thread drives TMA bulk copies, local HBM → shared memory ring →
+        // every rank's gather buffer (plain peer stores by the copy engine of this SM)
+        constexpr int NB = 5;
+        constexpr uint32_t CH = 32768;
+        uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + NB * CH);
+        volatile int local_abort = 0;
+        for (int i = 0; i < NB; ++i) mbar_init(smem_u32(&cbar[i]), 1);
+        fence_barrier_init();
+        uint32_t phase_bits = 0;
+        for (int s = cta; s < cm.sub_per_chunk; s += n_comm) {
+          const char* src = reinterpret_cast<const char*>(cm.src_shard + (long long)s * sub_elems);
+          const long long dst_off = (((long long)R * cm.rows_per_chunk) * p.K + (long long)s * sub_elems) * 2;
+          const long long bytes = sub_elems * 2;
+          const int n_ch = (int)((bytes + CH - 1) / CH);
+          auto issue_load = [&](int c) {
+            const int b = c % NB;
+            const uint32_t sz = (uint32_t)min((long long)CH, bytes - (long long)c * CH);
+            mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
+            bulk_load_g2s(smem_u32(smem + b * CH), src + (long long)c * CH, sz, smem_u32(&cbar[b]));
+          };
+          for (int c = 0; c < n_ch && c < NB; ++c) issue_load(c);
+          bool ok = true;
+          for (int c = 0; c < n_ch; ++c) {
+            const int b = c % NB;
+            if (!mbar_wait(smem_u32(&cbar[b]), (phase_bits >> b) & 1u, &local_abort)) { ok = false; break; }
+            phase_bits ^= (1u << b);
+            const uint32_t sz = (uint32_t)min((long long)CH, bytes - (long long)c * CH);
+            for (int q = 0; q < W; ++q)
+              bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[(R + q) % W]) + dst_off + (long long)c * CH,
+                             smem_u32(smem + b * CH), sz);
+            tma_store_commit();
+            // the buffer of the previous chunk may be refilled once its stores have read it
+            if (c >= 1 && c - 1 + NB < n_ch) {
+              tma_store_wait_read<1>();
+              issue_load(c - 1 + NB);
+            }
+          }
+          tma_store_wait<0>();
+          if (!ok) {
+            report_error(p.err, ERR_MBAR_TIMEOUT, 0xA604u);
+            break;
+          }
+          fence_proxy_async_global();
+          fence_sys();
+          for (int q = 0; q < W; ++q)
+            st_release_sys(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * cm.sub_per_chunk + s, cm.g.epoch);
+        }
+      }
+      return;
+    }
+  }
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = tiles_m * tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int grid_stride = (COMM == COMM_AG) ? cm.gemm_ctas : gridDim.x;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                                 : (2 * BN <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tfull_bar[a]), 1);
+      mbar_init(smem_u32(&tempty_bar[a]), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if constexpr (COMM == COMM_RS) {
+      // tell every peer that this rank has left the previous launch that used the staging area
+      if (blockIdx.x == 0) {
+        fence_sys();
+        for (int q = 0; q < cm.g.world; ++q)
+          st_release_sys(cm.g.signals[q] + cm.slot_enter + cm.g.rank, cm.g.epoch);
+      }
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += grid_stride) {
+        int b, tm, tn;
+        map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        if constexpr (COMM == COMM_AG) {
+          const int src = m0 / cm.rows_per_chunk;
+          const int sub = (m0 - src * cm.rows_per_chunk) / (cm.rows_per_chunk / cm.sub_per_chunk);
+          if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * cm.sub_per_chunk + sub,
+                            cm.g.epoch)) {
+            *abort_flag = 1;
+            report_error(p.err, ERR_FLAG_TIMEOUT, 0xA601u);
+            break;
+          }
+          fence_proxy_async_global();
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_3d(sa, &tmA, fb, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sa + j * (64 * BK * 2), &tmA, fb, m0 + 64 * j, k0, b);
+          }
+          if constexpr (!B_MN) {
+            tma_load_3d(sb, &tmB, fb, k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * (64 * BK * 2), &tmB, fb, n0 + 64 * j, k0, b);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += grid_stride, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            else
+              da = make_smem_desc_sw128(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            if constexpr (!B_MN)
+              db = make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            else
+              db = make_smem_desc_sw128(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem stage when MMAs finish
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps -----------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int iter = 0;
+    int store_seq = 0;          // TMA stores issued by this warp (selects the staging buffer)
+    bool alive = true;
+    if constexpr (COMM == COMM_RS) {
+      // peers' staging areas are free once every peer has entered this launch
+      bool ok = true;
+      if (lane == 0)
+        for (int q = 0; q < cm.g.world && ok; ++q)
+          ok = wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_enter + q, cm.g.epoch);
+      alive = __all_sync(0xffffffffu, ok);
+      if (!alive) {
+        *abort_flag = 1;
+        if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA602u);
+      }
+    }
+    for (int t = blockIdx.x; t < total_tiles && alive; t += grid_stride, ++iter) {
+      int b, tm, tn;
+      map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      if (!mbar_wait_warp(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      void* c_ptr = p.C;
+      long long c_base = (long long)b * p.batch_stride_c + (long long)row * p.ldc;
+      int owner = 0;
+      if constexpr (COMM == COMM_RS) {
+        owner = m0 / cm.rows_per_chunk;
+        c_ptr = cm.stage_peers[owner];
+        c_base = ((long long)cm.g.rank * cm.rows_per_chunk + (row - owner * cm.rows_per_chunk)) * p.ldc;
+      }
+      // TMA mode: after the second half of a 64-column chunk (or the last valid half) one lane
+      // hands the warp's staged 32 x 64 block to the copy engine
+      auto issue_store = [&](int c, int col0) {
+        if ((c & 1) == 0 && col0 + 32 < p.N) return;
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const CUtensorMap* om = &tmC.m[COMM == COMM_RS ? owner : 0];
+          const int r0 = (COMM == COMM_RS ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
+          tma_store_3d(om, smem_u32(smem + L::CSTAGE_OFFSET + (quad * 2 + (store_seq & 1)) * 4096),
+                       n0 + (c >> 1) * 64, r0, b);
+          tma_store_commit();
+        }
+        ++store_seq;
+      };
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (p.use_tma_store && (c & 1) == 0 && store_seq >= 2) {
+          // the staging buffer about to be rewritten was handed to TMA two stores ago
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        if (!row_ok) {
+          // rows past M: nothing to compute; in TMA mode the warp still issues its store
+          // (the copy clips rows and columns that fall outside the tensor)
+          if (p.use_tma_store) issue_store(c, col0);
+          continue;
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (p.aux_out) {
+          __nv_bfloat16* a = p.aux_out + (long long)row * p.ld_aux_out + col0;
+          if (full && (p.ld_aux_out & 7) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              reinterpret_cast<uint4*>(a)[q] = u;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) a[j] = __float2bfloat16(v[j]);
+          }
+        }
+        if (p.act == ACT_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+        } else if (p.act == ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        } else if (p.act == ACT_GELU_BWD || p.act == ACT_RELU_BWD) {
+          const __nv_bfloat16* a = p.aux_in + (long long)row * p.ld_aux_in + col0;
+          float x[32];
+          if (full && (p.ld_aux_in & 7) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u = reinterpret_cast<const uint4*>(a)[q];
+              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+              x[q * 8 + 0] = f0.x; x[q * 8 + 1] = f0.y; x[q * 8 + 2] = f1.x; x[q * 8 + 3] = f1.y;
+              x[q * 8 + 4] = f2.x; x[q * 8 + 5] = f2.y; x[q * 8 + 6] = f3.x; x[q * 8 + 7] = f3.y;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) x[j] = (col0 + j < p.N) ? __bfloat162float(a[j]) : 0.0f;
+          }
+          if (p.act == ACT_GELU_BWD) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(x[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = x[j] > 0.0f ? v[j] : 0.0f;
+          }
+        }
+        if (p.residual) {
+          const __nv_bfloat16* rs = p.residual + (long long)row * p.ldr + col0;
+          if (full && (p.ldr & 7) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u = reinterpret_cast<const uint4*>(rs)[q];
+              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+              v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+              v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+          }
+        }
+        if (p.use_tma_store) {
+          // stage this warp's 32 rows x 64 columns (128-byte swizzle) and store them by TMA
+          const int half = c & 1;
+          uint8_t* cs = smem + L::CSTAGE_OFFSET + (quad * 2 + (store_seq & 1)) * 4096;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            *reinterpret_cast<uint4*>(cs + sw128_offset(lane, half * 4 + q)) = o;
+          }
+        } else if (p.out_fp32) {
+          float* cp = reinterpret_cast<float*>(c_ptr) + c_base + col0;
+          if (full && (p.ldc & 3) == 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              if (p.accumulate == 2) {  // split-K: several CTAs add into the same tile
+                atomicAdd(reinterpret_cast<float4*>(cp) + q, o);
+                continue;
+              }
+              if (p.accumulate) {
+                float4 old = reinterpret_cast<float4*>(cp)[q];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              reinterpret_cast<float4*>(cp)[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) cp[j] = p.accumulate ? cp[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(c_ptr) + c_base + col0;
+          if (full && (p.ldc & 7) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (p.accumulate) {
+                uint4 u = reinterpret_cast<const uint4*>(cp)[q];
+                float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                       f3 = unpack_bf16x2(u.w);
+                v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+                v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              reinterpret_cast<uint4*>(cp)[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) {
+                float o = v[j];
+                if (p.accumulate) o += __bfloat162float(cp[j]);
+                cp[j] = __float2bfloat16(o);
+              }
+          }
+        }
+        if (p.use_tma_store) issue_store(c, col0);
+      }
+      // hand the accumulator back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      if constexpr (COMM == COMM_RS) {
+        // this warp's 32 rows of the tile are stored: publish them to the owner (the counter
+        // counts warp arrivals, so no CTA-wide barrier is needed here)
+        if (lane == 0) {
+          if (p.use_tma_store) {
+            tma_store_wait<0>();          // the bulk stores of this tile have been performed
+            fence_proxy_async_global();
+          }
+          fence_sys();
+          red_release_sys_add(cm.g.signals[owner] + cm.slot_done + (m0 - owner * cm.rows_per_chunk) / BM, 1u);
+        }
+      }
+    }
+    if (p.use_tma_store && lane == 0) tma_store_wait<0>();
+
+    if constexpr (COMM == COMM_RS) {
+      // ---- reduce the local chunk: row blocks are dealt round-robin to the CTAs -------------
+      const int W = cm.g.world, R = cm.g.rank;
+      const int blocks = cm.rows_per_chunk / BM;
+      const int ew = warp - 2;  // 0..3
+      const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
+      for (int rb = blockIdx.x; rb < blocks && alive; rb += gridDim.x) {
+        bool ok = true;
+        if (lane == 0) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_done + rb, cm.done_target);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          *abort_flag = 1;
+          if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA603u);
+          break;
+        }
+        const __nv_bfloat16* stage = cm.stage_peers[R];
+        for (int rr = ew; rr < BM; rr += 4) {
+          const long long row_off = (long long)(rb * BM + rr) * p.ldc;
+          for (int c8 = lane * 8; c8 < p.N; c8 += 32 * 8) {
+            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int q = 0; q < W; ++q) {
+              const uint4 u = *reinterpret_cast<const uint4*>(stage + q * slot_stride + row_off + c8);
+              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+              s[0] += f0.x; s[1] += f0.y; s[2] += f1.x; s[3] += f1.y;
+              s[4] += f2.x; s[5] += f2.y; s[6] += f3.x; s[7] += f3.y;
+            }
+            if (cm.rs_residual) {
+              const uint4 u = *reinterpret_cast<const uint4*>(cm.rs_residual + row_off + c8);
+              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+              s[0] += f0.x; s[1] += f0.y; s[2] += f1.x; s[3] += f1.y;
+              s[4] += f2.x; s[5] += f2.y; s[6] += f3.x; s[7] += f3.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+            o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+            *reinterpret_cast<uint4*>(cm.rs_out + row_off + c8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) report_error(p.err, ERR_MBAR_TIMEOUT, 0x6E00u);
+    // give copies that are still in flight a bounded time to land before smem is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm
+}  // namespace st

@@ -180,20 +180,16 @@ class GPTModel(nn.Module):
             h1 = resid
         else:
             y1, h1, m1, r1 = self._norm_fwd(x, f"h{l}.norm1", residual=resid)
-        y1_full = tp.all_gather_rows(y1)
-        qkv = gemm_ops.gemm(y1_full, P[f"h{l}.qkv.weight"])
+        qkv, y1_full = tp.ag_gemm(y1, P[f"h{l}.qkv.weight"], key=(l, "y1"))
         if cfg.positional == "rope":
             ew.rope_(qkv, 2 * hl, D, S, cfg.rope_base)
         qkv5 = qkv.view(B, S, 3, hl, D)
         o, lse = attn_ops.attention_forward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], True)
-        attn_partial = gemm_ops.gemm(o.view(B * S, hl * D), P[f"h{l}.proj.weight"])
-        attn_out = tp.reduce_scatter_rows(attn_partial)
+        attn_out = tp.gemm_rs(o.view(B * S, hl * D), P[f"h{l}.proj.weight"])
         y2, h2, m2, r2 = self._norm_fwd(attn_out, f"h{l}.norm2", residual=h1)
-        y2_full = tp.all_gather_rows(y2)
-        u = torch.empty((y2_full.shape[0], self.ffn_local), dtype=y2_full.dtype, device=y2_full.device)
-        a = gemm_ops.gemm(y2_full, P[f"h{l}.fc1.weight"], act="gelu", aux_out=u)
-        mlp_partial = gemm_ops.gemm(a, P[f"h{l}.fc2.weight"])
-        mlp_out = tp.reduce_scatter_rows(mlp_partial)
+        u = torch.empty((y2.shape[0] * tp.world, self.ffn_local), dtype=y2.dtype, device=y2.device)
+        a, y2_full = tp.ag_gemm(y2, P[f"h{l}.fc1.weight"], key=(l, "y2"), act="gelu", aux_out=u)
+        mlp_out = tp.gemm_rs(a, P[f"h{l}.fc2.weight"])
         if keep:
             act.h1, act.stat1, act.y1_full, act.qkv, act.o, act.lse = h1, (m1, r1), y1_full, qkv, o, lse
             act.h2, act.stat2, act.y2_full, act.u, act.a = h2, (m2, r2), y2_full, u, a
@@ -206,16 +202,13 @@ class GPTModel(nn.Module):
         g = gemm_ops.gemm
         w1, w2 = P[f"h{l}.fc1.weight"], P[f"h{l}.fc2.weight"]
         wqkv, wo = P[f"h{l}.qkv.weight"], P[f"h{l}.proj.weight"]
-        dmlp_full = tp.all_gather_rows(d_out)
-        du = g(dmlp_full, w2, b_mn=True, act="gelu_bwd", aux_in=act.u)
+        du, dmlp_full = tp.ag_gemm(d_out, w2, b_mn=True, key="bwd_mlp", act="gelu_bwd", aux_in=act.u)
         g(dmlp_full, act.a, a_mn=True, b_mn=True, out=w2.main_grad, accumulate=True)
-        dy2_partial = g(du, w1, b_mn=True)
         g(du, act.y2_full, a_mn=True, b_mn=True, out=w1.main_grad, accumulate=True)
-        dy2 = tp.reduce_scatter_rows(dy2_partial)
+        dy2 = tp.gemm_rs(du, w1, b_mn=True)
         d_h2 = self._norm_bwd(dy2, act.h2, act.stat2, f"h{l}.norm2", dres=d_out)
-        dh2_full = tp.all_gather_rows(d_h2)
         o2 = act.o.view(B * S, hl * D)
-        do = g(dh2_full, wo, b_mn=True)
+        do, dh2_full = tp.ag_gemm(d_h2, wo, b_mn=True, key="bwd_attn")
         g(dh2_full, o2, a_mn=True, b_mn=True, out=wo.main_grad, accumulate=True)
         dqkv = torch.empty_like(act.qkv)
         qkv5, dqkv5 = act.qkv.view(B, S, 3, hl, D), dqkv.view(B, S, 3, hl, D)
@@ -224,9 +217,8 @@ class GPTModel(nn.Module):
                                     dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
         if cfg.positional == "rope":
             ew.rope_(dqkv, 2 * hl, D, S, cfg.rope_base, backward=True)
-        dy1_partial = g(dqkv, wqkv, b_mn=True)
         g(dqkv, act.y1_full, a_mn=True, b_mn=True, out=wqkv.main_grad, accumulate=True)
-        dy1 = tp.reduce_scatter_rows(dy1_partial)
+        dy1 = tp.gemm_rs(dqkv, wqkv, b_mn=True)
         return self._norm_bwd(dy1, act.h1, act.stat1, f"h{l}.norm1", dres=d_h2)
 
     # ------------------------------------------------------------------------------------------
@@ -247,8 +239,7 @@ class GPTModel(nn.Module):
             resid, x, act = self._layer_forward(l, resid, x, B, S, keep=keep)
             acts.append(act)
         yf, hf, mf, rf = self._norm_fwd(x, "norm_f", residual=resid)
-        yf_full = tp.all_gather_rows(yf)
-        logits = gemm_ops.gemm(yf_full, emb)
+        logits, yf_full = tp.ag_gemm(yf, emb, key="head")
         if targets is None:
             return logits, None
         tgt = targets.reshape(-1).to(torch.int64).contiguous()
@@ -277,9 +268,8 @@ class GPTModel(nn.Module):
             coef = coef * dloss.to(torch.float32).reshape(1)
         dlogits = loss_ops._grad_(logits, tgt, lse, coef.contiguous(), 1.0, self.vocab_start)
         g = gemm_ops.gemm
-        dyf_partial = g(dlogits, emb, b_mn=True)
         g(dlogits, yf_full, a_mn=True, b_mn=True, out=emb.main_grad, accumulate=True)
-        dyf = tp.reduce_scatter_rows(dyf_partial)
+        dyf = tp.gemm_rs(dlogits, emb, b_mn=True)
         d = self._norm_bwd(dyf, hf, statf, "norm_f")
         for l in reversed(range(cfg.n_layers)):
             d = self._layer_backward(l, acts[l], d, B, S)

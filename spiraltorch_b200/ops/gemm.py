@@ -41,6 +41,27 @@ class _GemmArgs(ctypes.Structure):
     ]
 
 
+#: split the K loop of weight-gradient GEMMs whose tile count fills the SMs badly (the partial
+#: sums meet in fp32 atomics, so the summation order is not fixed); SPIRAL_DETERMINISTIC_REDUCTION
+#: turns it off
+import os as _os
+SPLIT_K = _os.environ.get("SPIRAL_DETERMINISTIC_REDUCTION", "0") in ("0", "", "false")
+_NUM_SMS = 148
+
+
+def _split_k(M: int, N: int, K: int) -> int:
+    tiles = ((M + 127) // 128) * ((N + 255) // 256 if N > 128 else 1)
+    best, best_eff = 1, tiles / (-(-tiles // _NUM_SMS) * _NUM_SMS)
+    for s in (2, 3, 4):
+        if K % (s * 64) or K // s < 2048:
+            continue
+        work = tiles * s
+        eff = work / (-(-work // _NUM_SMS) * _NUM_SMS)
+        if eff > best_eff + 0.04:
+            best, best_eff = s, eff
+    return best
+
+
 def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.gelu(x, approximate="tanh")
 
@@ -160,6 +181,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.a_mn_major, args.b_mn_major = int(a_mn), int(b_mn)
     args.out_fp32 = int(out.dtype == torch.float32)
     args.accumulate = int(accumulate)
+    split = _split_k(M, N, K) if (SPLIT_K and accumulate and a_mn and b_mn and not batched and
+                                  out.dtype == torch.float32 and N % 32 == 0 and out.stride(0) % 4 == 0
+                                  and bias is None and residual is None and act_id == 0) else 1
+    if split > 1:
+        # weight-gradient shape with a poor tile count: split the long reduction over `split`
+        # CTAs per tile (expressed as a batch over K) and add the partials with fp32 atomics
+        kc = K // split
+        args.K, args.batch = kc, split
+        args.batch_stride_a, args.batch_stride_b, args.batch_stride_c = kc * a.stride(0), kc * b.stride(0), 0
+        args.accumulate = 2
     args.act = act_id
     args.alpha = float(alpha)
     args.max_ctas = int(max_ctas)

@@ -70,6 +70,22 @@ class TPContext:
         self.collective_calls += 1
         return out
 
+    # -- parallel linears (collective + GEMM); the fused context overrides these ------------
+    def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, key=None, **epilogue):
+        """Column-parallel product ``all_gather_rows(x_shard) @ op(w)``; returns ``(y, x_full)``."""
+        from ..ops.gemm import gemm
+        x_full = self.all_gather_rows(x_shard)
+        return gemm(x_full, w, b_mn=b_mn, **epilogue), x_full
+
+    def gemm_rs(self, a_full: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-parallel product ``reduce_scatter_rows(a_full @ op(w))`` (+ ``residual``)."""
+        from ..ops.gemm import gemm
+        if self.world == 1:
+            return gemm(a_full, w, b_mn=b_mn, residual=residual)
+        y = self.reduce_scatter_rows(gemm(a_full, w, b_mn=b_mn))
+        return y if residual is None else y + residual
+
     def all_reduce_(self, t: torch.Tensor, op=dist.ReduceOp.SUM) -> torch.Tensor:
         if self.world > 1:
             dist.all_reduce(t, op=op, group=self.group)

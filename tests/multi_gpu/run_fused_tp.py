@@ -1,0 +1,178 @@
+"""Two-or-more-rank check of the fused kernels against the NCCL path (launched by torchrun).
+
+Prints FUSED_TP_OK on rank 0 when (a) ag_gemm / gemm_rs match all-gather / reduce-scatter + GEMM,
+(b) the data-parallel bucket step matches all-reduce-mean + AdamW, (c) a small GPT step gives the
+same loss and gradients under the fused and the NCCL tensor-parallel contexts.  Also prints
+device-timed comparisons of the fused kernels and the NCCL+GEMM sequence (max over ranks).
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from spiraltorch_b200.models.gpt import GPTConfig, GPTModel  # noqa: E402
+from spiraltorch_b200.ops import gemm as G  # noqa: E402
+from spiraltorch_b200.ops import native  # noqa: E402
+from spiraltorch_b200.ops import optim as O  # noqa: E402
+from spiraltorch_b200.parallel.symm import FusedDPStep, FusedTPContext, PeerSignals  # noqa: E402
+from spiraltorch_b200.parallel.tp import TPContext  # noqa: E402
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+def timed(fn, iters=10):
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+class Sections:
+    """Runs test sections; after each one all ranks agree on success so that nobody leaves a
+    collective (or a peer-memory kernel) half-way when another rank hit an assertion."""
+
+    def __init__(self, dev):
+        self.dev, self.ok = dev, True
+
+    def run(self, name, fn):
+        if not self.ok:
+            return
+        good = 1
+        try:
+            fn()
+            torch.cuda.synchronize()
+            native.raise_on_device_error()
+        except Exception:  # noqa: BLE001
+            import traceback
+            print(f"[rank {dist.get_rank()}] section {name} FAILED", flush=True)
+            traceback.print_exc()
+            good = 0
+        t = torch.tensor([good], device=self.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        self.ok = bool(t.item())
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    big = os.environ.get("ST_FUSED_BENCH", "1") == "1"
+    nccl = TPContext(dist.group.WORLD)
+    fused = FusedTPContext(dist.group.WORLD, device=dev)
+    if rank == 0:
+        print(f"world={world} multicast={'yes' if fused.signals.buf.mc_ptr else 'no'}", flush=True)
+    sec = Sections(dev)
+
+    def sec_tp_kernels():
+        torch.manual_seed(100 + rank)
+        T, K, N = 2048 * world, 1024, 768
+        x = torch.randn(T // world, K, device=dev).bfloat16()
+        w = torch.randn(N, K, device=dev).bfloat16()
+        wt = torch.randn(K, N, device=dev).bfloat16()
+        a_full = torch.randn(T, K, device=dev).bfloat16()
+        checks = []  # every collective first, comparisons afterwards (keeps the ranks in lock-step)
+        for rep in range(3):
+            y_ref, xf_ref = nccl.ag_gemm(x, w)
+            y, xf = fused.ag_gemm(x, w, key="a")
+            checks.append(("gathered rows", xf.clone(), xf_ref, 0.0))
+            checks.append(("ag_gemm", y, y_ref, 1e-2))
+            y2_ref, _ = nccl.ag_gemm(x, wt, b_mn=True)
+            y2, _ = fused.ag_gemm(x, wt, b_mn=True, key="b")
+            checks.append(("ag_gemm b_mn", y2, y2_ref, 1e-2))
+            z_ref = nccl.gemm_rs(a_full, w)
+            z = fused.gemm_rs(a_full, w)
+            checks.append(("gemm_rs", z, z_ref, 2e-2))
+            z2_ref = nccl.gemm_rs(a_full, wt, b_mn=True)
+            z2 = fused.gemm_rs(a_full, wt, b_mn=True)
+            checks.append(("gemm_rs b_mn", z2, z2_ref, 2e-2))
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        for name, got, ref, tol in checks:
+            err = rel(got, ref)
+            assert err <= tol, (name, err)
+
+    sec.run("tp_kernels", sec_tp_kernels)
+    def sec_dp_step():
+        # data-parallel bucket step against all-reduce-mean + AdamW
+        n = 8 * world * 4096
+        grad = fused.heap.empty(n, torch.float32)
+        wbuf = fused.heap.empty(n, torch.bfloat16)
+        grad.tensor.copy_(torch.randn(n, device=dev))
+        torch.manual_seed(7)
+        wbuf.tensor.copy_(torch.randn(n, device=dev).bfloat16())
+        g_ref = grad.tensor.clone()
+        dist.all_reduce(g_ref)
+        g_ref /= world
+        master = wbuf.tensor.float().clone()
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        dp = FusedDPStep(fused.heap, fused.signals, grad, wbuf, kind="adamw", bucket_elems=n // 2)
+        dist.barrier()
+        dp.step(lr=1e-2, weight_decay=0.1)
+        O.adamw_reference(g_ref, master, m, v, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, False)
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        assert rel(wbuf.tensor, master) < 1e-2, rel(wbuf.tensor, master)
+        assert grad.tensor.abs().max().item() == 0
+
+    sec.run("dp_step", sec_dp_step)
+    def sec_gpt():
+        # small GPT step: fused vs NCCL context
+        cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=4, ffn=1024, seq_len=512, init_std=0.05)
+        ma = GPTModel(cfg, device=dev, seed=5, tp=nccl)
+        mb = GPTModel(cfg, device=dev, seed=5, tp=fused)
+        gen = torch.Generator().manual_seed(11)
+        tokens = torch.randint(0, 1024, (2 * world, 512), generator=gen).to(dev)
+        targets = torch.randint(0, 1024, (2 * world, 512), generator=gen).to(dev)
+        for _ in range(2):
+            la = ma.forward_backward(tokens, targets)
+            lb = mb.forward_backward(tokens, targets)
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        assert abs(la.item() - lb.item()) < 2e-2, (la.item(), lb.item())
+        r = ((ma.flat_grad - mb.flat_grad).norm() / ma.flat_grad.norm()).item()
+        assert r < 3e-2, r
+
+    sec.run("gpt", sec_gpt)
+    def sec_bench():
+        if big:
+            T, d, F = 16384, 2048, 8192 // world
+            xs = torch.randn(T // world, d, device=dev).bfloat16()
+            w1 = torch.randn(F, d, device=dev).bfloat16()
+            af = torch.randn(T, F, device=dev).bfloat16()
+            w2 = torch.randn(d, F, device=dev).bfloat16()
+            t_n = timed(lambda: nccl.ag_gemm(xs, w1))
+            t_f = timed(lambda: fused.ag_gemm(xs, w1, key="bench"))
+            t_g = timed(lambda: G.gemm(af[:, :d].contiguous() if False else torch.empty(0, device=dev), w1) if False else G.gemm(fused._gather_buffer("bench", T, d).tensor.view(T, d), w1))
+            r_n = timed(lambda: nccl.gemm_rs(af, w2))
+            r_f = timed(lambda: fused.gemm_rs(af, w2))
+            r_g = timed(lambda: G.gemm(af, w2))
+            if rank == 0:
+                print(f"AG->GEMM T{T} K{d} N{F}: nccl+gemm {t_n:.3f} ms, fused {t_f:.3f} ms, gemm only {t_g:.3f} ms", flush=True)
+                print(f"GEMM->RS T{T} K{F} N{d}: gemm+nccl {r_n:.3f} ms, fused {r_f:.3f} ms, gemm only {r_g:.3f} ms", flush=True)
+
+    sec.run("bench", sec_bench)
+    dist.barrier()
+    if rank == 0 and sec.ok:
+        print("FUSED_TP_OK", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if sec.ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,104 @@
+"""Fused compute+collective kernels on one GPU (world size 1: the peer is the local device) and,
+when at least two GPUs are visible, on two ranks launched with torchrun."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from spiraltorch_b200.ops import gemm as G
+from spiraltorch_b200.ops import native
+from spiraltorch_b200.ops import optim as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+def test_ag_gemm_and_gemm_rs_world1():
+    from spiraltorch_b200.parallel.symm import FusedTPContext
+    torch.manual_seed(0)
+    tp = FusedTPContext(None, device=DEV)
+    T, K, N = 1024, 512, 768
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    for rep in range(3):  # repeated launches exercise the epoch / cumulative-counter logic
+        aux = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        y, x_full = tp.ag_gemm(x, w, key="t", act="gelu", aux_out=aux)
+        ref_pre = x.float() @ w.float().T
+        assert torch.equal(x_full, x)
+        assert _rel(aux, ref_pre) < 1e-2
+        assert _rel(y, torch.nn.functional.gelu(ref_pre, approximate="tanh")) < 1e-2
+        wt = torch.randn(K, N, device=DEV).bfloat16()
+        y2, _ = tp.ag_gemm(x, wt, b_mn=True, key="t2")
+        assert _rel(y2, x.float() @ wt.float()) < 1e-2
+        res = torch.randn(T, N, device=DEV).bfloat16()
+        z = tp.gemm_rs(x, w, residual=res)
+        assert _rel(z, ref_pre + res.float()) < 1e-2
+        z2 = tp.gemm_rs(x, wt, b_mn=True)
+        assert _rel(z2, x.float() @ wt.float()) < 1e-2
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
+
+
+def test_dp_step_world1_matches_adamw_and_sgd():
+    from spiraltorch_b200.parallel.symm import FusedDPStep, PeerSignals, SymmetricHeap
+    torch.manual_seed(1)
+    heap = SymmetricHeap(None, torch.device(DEV))
+    sig = PeerSignals(heap)
+    n = 8 * 1000
+    for kind in ("adamw", "sgd"):
+        grad = heap.empty(n, torch.float32)
+        w = heap.empty(n, torch.bfloat16)
+        grad.tensor.copy_(torch.randn(n, device=DEV))
+        w.tensor.copy_(torch.randn(n, device=DEV).bfloat16())
+        g0 = grad.tensor.clone()
+        master = w.tensor.float().clone()
+        m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        dp = FusedDPStep(heap, sig, grad, w, kind=kind, bucket_elems=4096)
+        coef = torch.tensor([0.5], device=DEV)
+        dp.step(lr=1e-2, weight_decay=0.1, grad_scale=2.0, scale_tensor=coef, momentum=0.9)
+        if kind == "adamw":
+            O.adamw_reference(g0, master, m, v, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, False)
+        else:
+            gg = g0 * 1.0 + 0.1 * master
+            m.mul_(0.9).add_(gg)
+            master.sub_(1e-2 * m)
+        assert _rel(w.tensor, master) < 1e-2
+        got_master = torch.cat([b[2] for b in dp.buckets])
+        assert _rel(got_master, master) < 1e-5
+        assert grad.tensor.abs().max().item() == 0
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
+
+
+def test_gpt_fused_context_matches_plain_world1():
+    from spiraltorch_b200.models.gpt import GPTConfig, GPTModel
+    from spiraltorch_b200.parallel.symm import FusedTPContext
+    cfg = GPTConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=2, ffn=512, seq_len=256, init_std=0.05)
+    a = GPTModel(cfg, device=DEV, seed=3)
+    b = GPTModel(cfg, device=DEV, seed=3, tp=FusedTPContext(None, device=DEV))
+    tokens = torch.randint(0, 512, (2, 256), device=DEV)
+    targets = torch.randint(0, 512, (2, 256), device=DEV)
+    la = a.forward_backward(tokens, targets)
+    lb = b.forward_backward(tokens, targets)
+    assert abs(la.item() - lb.item()) < 2e-2
+    rel = (a.flat_grad - b.flat_grad).norm() / a.flat_grad.norm()
+    assert rel.item() < 2e-2
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_kernels_two_ranks():
+    script = os.path.join(os.path.dirname(__file__), "multi_gpu", "run_fused_tp.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29533", script],
+                          capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "FUSED_TP_OK" in proc.stdout

@@ -226,3 +226,15 @@ def test_fused_optimizers():
     assert _rel(wt.cpu(), wc) < 1e-4 and gt.abs().max().item() == 0 and rt.abs().max().item() == 0
     pr = O.project_to_poincare(wave, -0.5)
     assert _rel(pr.cpu(), O.project_to_poincare(wave.cpu(), -0.5)) < 1e-5
+
+
+def test_gemm_weight_gradient_split_k():
+    torch.manual_seed(10)
+    T, M, N = 8192, 2048, 512
+    dy = torch.randn(T, M, device=DEV).bfloat16()
+    x = torch.randn(T, N, device=DEV).bfloat16()
+    assert G._split_k(M, N, T) > 1  # this shape takes the split-K path
+    acc = torch.full((M, N), 0.5, device=DEV)
+    G.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    assert _rel(acc, 0.5 + dy.float().T @ x.float()) < 1e-2
+    _no_device_error()
