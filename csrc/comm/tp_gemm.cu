@@ -31,8 +31,8 @@ constexpr int BN = 256;
 constexpr int STAGES = 4;
 
 template <bool B_MN, int COMM>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, const GemmParams& p,
-           const GemmComm& cm, int grid, cudaStream_t stream) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, const CUtensorMap& tmA_local,
+           const GemmParams& p, const GemmComm& cm, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, false, B_MN, COMM>;
   static bool configured = false;
@@ -40,7 +40,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, c
     ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, p, cm);
+  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, tmA_local, p, cm);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
@@ -137,8 +137,17 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
                      strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return ST_ERR_CUDA;
   }
-  if (a->b_mn) return launch<true, COMM_AG>(tmA, tmB, tmC, p, cm, gemm_ctas + comm, stream);
-  return launch<false, COMM_AG>(tmA, tmB, tmC, p, cm, gemm_ctas + comm, stream);
+  CUtensorMap tmA_local;
+  {
+    uint64_t dims[3] = {(uint64_t)a->K, (uint64_t)rows, 1};
+    uint64_t strides[2] = {(uint64_t)a->K * 2, (uint64_t)a->K * 2 * rows};
+    uint32_t box[3] = {BK, BM, 1};
+    if (!encode_tmap(&tmA_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, reinterpret_cast<const void*>(a->x_shard),
+                     dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return ST_ERR_CUDA;
+  }
+  if (a->b_mn) return launch<true, COMM_AG>(tmA, tmB, tmC, tmA_local, p, cm, gemm_ctas + comm, stream);
+  return launch<false, COMM_AG>(tmA, tmB, tmC, tmA_local, p, cm, gemm_ctas + comm, stream);
 }
 
 struct StGemmRsArgs {
@@ -203,8 +212,8 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
                      CU_TENSOR_MAP_SWIZZLE_128B))
       return ST_ERR_CUDA;
   }
-  if (a->b_mn) return launch<true, COMM_RS>(tmA, tmB, tmC, p, cm, grid, stream);
-  return launch<false, COMM_RS>(tmA, tmB, tmC, p, cm, grid, stream);
+  if (a->b_mn) return launch<true, COMM_RS>(tmA, tmB, tmC, tmA, p, cm, grid, stream);
+  return launch<false, COMM_RS>(tmA, tmB, tmC, tmA, p, cm, grid, stream);
 }
 
 // Number of warp arrivals one launch of st_gemm_rs adds to every row-block counter.

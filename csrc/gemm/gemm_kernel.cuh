@@ -127,7 +127,8 @@ __device__ __forceinline__ void epilogue_bar() {
 template <int BN, int STAGES, bool A_MN, bool B_MN, int COMM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ OutMaps tmC, const GemmParams p, const GemmComm cm) {
+                 const __grid_constant__ OutMaps tmC, const __grid_constant__ CUtensorMap tmA_local,
+                 const GemmParams p, const GemmComm cm) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -298,10 +299,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int b, tm, tn;
         map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        const CUtensorMap* mapA = &tmA;
+        int m_coord = m0;
         if constexpr (COMM == COMM_AG) {
           const int src = m0 / cm.rows_per_chunk;
           const int sub = (m0 - src * cm.rows_per_chunk) / (cm.rows_per_chunk / cm.sub_per_chunk);
-          if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * cm.sub_per_chunk + sub,
+          if (src == cm.g.rank) {
+            // the local rows are read from the shard itself; nothing to wait for
+            mapA = &tmA_local;
+            m_coord = m0 - src * cm.rows_per_chunk;
+          } else if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * cm.sub_per_chunk + sub,
                             cm.g.epoch)) {
             *abort_flag = 1;
             report_error(p.err, ERR_FLAG_TIMEOUT, 0xA601u);
@@ -320,11 +327,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sb = sa + L::A_BYTES;
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma_load_3d(sa, &tmA, fb, k0, m0, b);
+            tma_load_3d(sa, mapA, fb, k0, m_coord, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_3d(sa + j * (64 * BK * 2), &tmA, fb, m0 + 64 * j, k0, b);
+              tma_load_3d(sa + j * (64 * BK * 2), mapA, fb, m_coord + 64 * j, k0, b);
           }
           if constexpr (!B_MN) {
             tma_load_3d(sb, &tmB, fb, k0, n0, b);
@@ -612,7 +619,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int blocks = cm.rows_per_chunk / BM;
       const int ew = warp - 2;  // 0..3
       const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
-      for (int rb = blockIdx.x; rb < blocks && alive; rb += gridDim.x) {
+      // work item = (row block, 256-column slab); each warp owns 32 rows of the block, each lane
+      // 8 columns; eight rows are in flight per slot so that the reduction is bandwidth- and not
+      // latency-bound
+      const int slabs = (p.N + 255) / 256;
+      const int items = blocks * slabs;
+      const __nv_bfloat16* stage = cm.stage_peers[R];
+      for (int it = blockIdx.x; it < items && alive; it += gridDim.x) {
+        const int rb = it / slabs;
+        const int c8 = (it - rb * slabs) * 256 + lane * 8;
         bool ok = true;
         if (lane == 0) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_done + rb, cm.done_target);
         ok = __all_sync(0xffffffffu, ok);
@@ -621,29 +636,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA603u);
           break;
         }
-        const __nv_bfloat16* stage = cm.stage_peers[R];
-        for (int rr = ew; rr < BM; rr += 4) {
-          const long long row_off = (long long)(rb * BM + rr) * p.ldc;
-          for (int c8 = lane * 8; c8 < p.N; c8 += 32 * 8) {
-            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int q = 0; q < W; ++q) {
-              const uint4 u = *reinterpret_cast<const uint4*>(stage + q * slot_stride + row_off + c8);
-              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
-                     f3 = unpack_bf16x2(u.w);
-              s[0] += f0.x; s[1] += f0.y; s[2] += f1.x; s[3] += f1.y;
-              s[4] += f2.x; s[5] += f2.y; s[6] += f3.x; s[7] += f3.y;
+        if (c8 >= p.N) continue;
+#pragma unroll 1
+        for (int r0 = ew * 32; r0 < ew * 32 + 32; r0 += 8) {
+          float sum[8][8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[i][j] = 0.0f;
+          const long long base_off = (long long)(rb * BM + r0) * p.ldc + c8;
+          for (int q = 0; q <= W; ++q) {
+            const __nv_bfloat16* src;
+            if (q < W) src = stage + q * slot_stride + base_off;
+            else if (cm.rs_residual) src = cm.rs_residual + base_off;
+            else break;
+            uint4 u[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u[i] = *reinterpret_cast<const uint4*>(src + (long long)i * p.ldc);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float2 f0 = unpack_bf16x2(u[i].x), f1 = unpack_bf16x2(u[i].y), f2 = unpack_bf16x2(u[i].z),
+                     f3 = unpack_bf16x2(u[i].w);
+              sum[i][0] += f0.x; sum[i][1] += f0.y; sum[i][2] += f1.x; sum[i][3] += f1.y;
+              sum[i][4] += f2.x; sum[i][5] += f2.y; sum[i][6] += f3.x; sum[i][7] += f3.y;
             }
-            if (cm.rs_residual) {
-              const uint4 u = *reinterpret_cast<const uint4*>(cm.rs_residual + row_off + c8);
-              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
-                     f3 = unpack_bf16x2(u.w);
-              s[0] += f0.x; s[1] += f0.y; s[2] += f1.x; s[3] += f1.y;
-              s[4] += f2.x; s[5] += f2.y; s[6] += f3.x; s[7] += f3.y;
-            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
             uint4 o;
-            o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
-            o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
-            *reinterpret_cast<uint4*>(cm.rs_out + row_off + c8) = o;
+            o.x = pack_bf16x2(sum[i][0], sum[i][1]); o.y = pack_bf16x2(sum[i][2], sum[i][3]);
+            o.z = pack_bf16x2(sum[i][4], sum[i][5]); o.w = pack_bf16x2(sum[i][6], sum[i][7]);
+            *reinterpret_cast<uint4*>(cm.rs_out + base_off + (long long)i * p.ldc) = o;
           }
         }
       }

@@ -39,7 +39,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps
   int grid = tiles < st::sm_count() ? tiles : st::sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   GemmComm none{};
-  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, p, none);
+  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, tmA, p, none);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }

@@ -156,7 +156,7 @@ class FusedTPContext(TPContext):
     """Tensor-parallel context whose column-/row-parallel linears run as fused kernels."""
 
     def __init__(self, group: Optional[dist.ProcessGroup], device=None, comm_ctas: int = 12,
-                 sub_per_chunk: int = 4):
+                 sub_per_chunk: int = 16):
         super().__init__(group, mode="fused")
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = device
