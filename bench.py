@@ -98,7 +98,8 @@ class ClockSampler:
 
 def launch_total() -> int:
     from spiraltorch_b200.ops import attention, elementwise, gemm, loss, norm, optim
-    return sum(m.launch_count for m in (attention, elementwise, gemm, loss, norm, optim))
+    from spiraltorch_b200.parallel import symm
+    return sum(m.launch_count for m in (attention, elementwise, gemm, loss, norm, optim, symm))
 
 
 def main() -> int:
@@ -143,11 +144,21 @@ def main() -> int:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
     tp_mode = args.tp_mode
-    if tp_mode == "auto":
-        tp_mode = "nccl"
     if world > 1:
         from spiraltorch_b200.parallel import fused as fused_tp
-        tp = fused_tp.make_context(dist.group.WORLD, tp_mode)
+        if tp_mode == "auto":
+            # fused all-gather->GEMM / GEMM->reduce-scatter kernels; NCCL collectives only if the
+            # symmetric-memory set-up is not available on this box
+            try:
+                tp = fused_tp.make_context(dist.group.WORLD, "fused")
+                tp_mode = "fused"
+            except Exception as exc:  # noqa: BLE001
+                if rank == 0:
+                    print(f"fused tensor-parallel context unavailable ({exc!r}); using NCCL", file=sys.stderr)
+                tp = fused_tp.make_context(dist.group.WORLD, "nccl")
+                tp_mode = "nccl"
+        else:
+            tp = fused_tp.make_context(dist.group.WORLD, tp_mode)
     else:
         tp = TPContext()
 

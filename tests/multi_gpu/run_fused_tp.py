@@ -133,7 +133,7 @@ def main():
     sec.run("dp_step", sec_dp_step)
     def sec_gpt():
         # small GPT step: fused vs NCCL context
-        cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=4, ffn=1024, seq_len=512, init_std=0.05)
+        cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=8, ffn=1024, seq_len=512, init_std=0.05)
         ma = GPTModel(cfg, device=dev, seed=5, tp=nccl)
         mb = GPTModel(cfg, device=dev, seed=5, tp=fused)
         gen = torch.Generator().manual_seed(11)
