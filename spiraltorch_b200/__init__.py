@@ -1,0 +1,25 @@
+"""spiraltorch-b200: a Blackwell-native framework with the public API of SpiralTorch.
+
+``import spiraltorch_b200 as st`` (or ``import spiraltorch as st``) gives ``st.Tensor``, ``st.nn``,
+``st.optim``, ``st.SpiralSession``, ``st.plugin``, ``st.selfsup``, ``st.build_info()`` and
+``st.describe_device()``.  CUDA work runs on hand-written sm_100a kernels (``csrc/``).
+"""
+from . import config, distributed, nn, optim, plugin, selfsup
+from .nn.io import VERSION as __version__
+from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad
+from .session import SpiralSession, build_info, describe_device
+from .tensor import NonFiniteValue, Tensor, TensorError, set_default_device, set_finite_checks
+
+
+def hypergrad(rows: int, cols: int, *, curvature: float = -1.0, learning_rate: float = 1e-2, topos=None):
+    """``st.hypergrad(rows, cols, curvature=..., learning_rate=...)`` notation of the reference."""
+    return Hypergrad(curvature, learning_rate, rows, cols, topos=topos)
+
+
+def realgrad(rows: int, cols: int, *, learning_rate: float = 1e-2):
+    return Realgrad(learning_rate, rows, cols)
+
+
+def init_backend(name: str = "auto") -> str:
+    """Resolve a backend label to the backend that will run (``cpu`` or ``cuda``)."""
+    return SpiralSession(name).effective_backend

@@ -1,0 +1,11 @@
+"""``spiraltorch.nn``: modules, losses, trainer, data and weight files of the public API."""
+from .data import DataLoader, Dataset, from_samples
+from .io import load, load_bincode, load_json, save, save_bincode, save_json
+from .losses import (CategoricalCrossEntropy, ContrastiveLoss, CrossEntropy, FocalLoss, HyperbolicCrossEntropy,
+                     Loss, MeanSquaredError, SoftmaxCrossEntropy, TripletLoss)
+from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, Identity, LayerNorm, Linear,
+                      LoraLinear, Lstm, Module, NonLiner, Parameter, Pool2d, Relu, Scaler, Sequential, SpiralRnn,
+                      WaveGate, WaveRnn, ZConv, ZPooling, ZSpaceBatchNorm1d, ZSpaceCoherenceScan,
+                      ZSpaceCoherenceWaveBlock, ZSpaceLayerNorm, ZSpaceMixer, ZSpaceSoftmax, conv_output_shape,
+                      pool_output_shape)
+from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
