@@ -1,0 +1,317 @@
+"""Vision stack: image transforms, the fused classification preprocessing pipeline, NeRF volume
+rendering and the canvas projector — CUDA kernels in ``csrc/vision/vision.cu`` with PyTorch CPU
+statements of the same arithmetic (the test oracle).
+
+Reference parity: ``TransformDispatcher`` (crates/st-backend-wgpu/src/transform.rs:281) and the CPU
+transforms of ``st-vision``; ``nerf_raymarch.wgsl`` / ``nerf_volume_utils.wgsl`` and the CPU NeRF
+trainer (crates/st-vision/src/nerf/trainer.rs); ``CanvasProjector`` (crates/st-tensor/src/pure/
+wasm_canvas.rs).  Images are fp32 ``[B, C, H, W]`` (a 3-D ``[C, H, W]`` image is treated as B = 1);
+outputs are headless device buffers.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from .ops import native
+
+launch_count = 0
+
+
+class _PreArgs(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("B", "C", "src_h", "src_w", "resize_h", "resize_w", "out_h", "out_w",
+                                            "crop_y", "crop_x", "flip", "do_jitter")] + \
+               [(n, ctypes.c_float) for n in ("brightness", "contrast", "saturation", "hue")] + \
+               [("mean", ctypes.c_float * 4)]
+
+
+@dataclass
+class ColorJitter:
+    brightness: float = 1.0
+    contrast: float = 1.0
+    saturation: float = 1.0
+    hue: float = 0.0                      # radians
+    means: Optional[Sequence[float]] = None   # per-channel means for the contrast step (image means if None)
+
+    @staticmethod
+    def balanced() -> "ColorJitter":
+        return ColorJitter(1.1, 1.1, 1.1, 0.05)
+
+    @staticmethod
+    def vivid() -> "ColorJitter":
+        return ColorJitter(1.25, 1.3, 1.5, 0.15)
+
+
+def _as4d(img: torch.Tensor):
+    if img.dim() == 3:
+        return img.unsqueeze(0), True
+    if img.dim() != 4:
+        raise ValueError("images must be [C,H,W] or [B,C,H,W]")
+    return img, False
+
+
+def _bilinear_ref(img: torch.Tensor, rh: int, rw: int) -> torch.Tensor:
+    B, C, sh, sw = img.shape
+    sy = (torch.arange(rh, device=img.device, dtype=torch.float32) + 0.5) * (sh / rh) - 0.5
+    sx = (torch.arange(rw, device=img.device, dtype=torch.float32) + 0.5) * (sw / rw) - 0.5
+    y0 = sy.floor().clamp(0, sh - 1)
+    x0 = sx.floor().clamp(0, sw - 1)
+    y1 = (y0 + 1).clamp(max=sh - 1).long()
+    x1 = (x0 + 1).clamp(max=sw - 1).long()
+    ly, lx = (sy - y0)[:, None], (sx - x0)[None, :]
+    y0, x0 = y0.long(), x0.long()
+    tl, tr = img[:, :, y0][:, :, :, x0], img[:, :, y0][:, :, :, x1]
+    bl, br = img[:, :, y1][:, :, :, x0], img[:, :, y1][:, :, :, x1]
+    top = tl * (1 - lx) + tr * lx
+    bot = bl * (1 - lx) + br * lx
+    return top * (1 - ly) + bot * ly
+
+
+def _jitter_ref(img: torch.Tensor, j: ColorJitter, means) -> torch.Tensor:
+    C = img.shape[1]
+    out = img * j.brightness
+    if j.contrast != 1.0:
+        m = torch.tensor([means[min(c, 3)] for c in range(C)], device=img.device).view(1, C, 1, 1)
+        out = (out - m) * j.contrast + m
+    if C >= 3:
+        r, g, b = out[:, 0], out[:, 1], out[:, 2]
+        if j.saturation != 1.0:
+            gray = r * 0.29899597 + g * 0.587096 + b * 0.11390703
+            r, g, b = [(ch - gray) * j.saturation + gray for ch in (r, g, b)]
+        if j.hue != 0.0:
+            ch, sh = math.cos(j.hue), math.sin(j.hue)
+            y = 0.299 * r + 0.587 * g + 0.114 * b
+            u = -0.14713 * r - 0.28886 * g + 0.436 * b
+            v = 0.615 * r - 0.51499 * g - 0.10001 * b
+            up, vp = u * ch - v * sh, u * sh + v * ch
+            r, g, b = y + 1.13983 * vp, y - 0.39465 * up - 0.58060 * vp, y + 2.03211 * up
+        out = torch.cat([torch.stack([r, g, b], 1), out[:, 3:]], 1)
+    return out
+
+
+def preprocess(img: torch.Tensor, *, resize: Optional[tuple[int, int]] = None, crop: Optional[tuple[int, int]] = None,
+               jitter: Optional[ColorJitter] = None, flip: bool = False) -> torch.Tensor:
+    """resize → centre crop → colour jitter → horizontal flip; one fused kernel launch on CUDA."""
+    global launch_count
+    x, squeeze = _as4d(img)
+    x = x.float().contiguous()
+    B, C, sh, sw = x.shape
+    rh, rw = resize if resize else (sh, sw)
+    oh, ow = crop if crop else (rh, rw)
+    if oh > rh or ow > rw:
+        raise ValueError("crop size exceeds the (resized) image")
+    cy, cx = (rh - oh) // 2, (rw - ow) // 2
+    means = [0.0] * 4
+    if jitter is not None:
+        if jitter.means is not None:
+            means = list(jitter.means) + [0.0] * (4 - len(jitter.means))
+        elif jitter.contrast != 1.0:
+            mm = (x * jitter.brightness).mean(dim=(0, 2, 3)).tolist()
+            means = (mm + [0.0] * 4)[:4]
+    if not native.use_native(x):
+        y = _bilinear_ref(x, rh, rw) if (rh, rw) != (sh, sw) else x
+        y = y[:, :, cy:cy + oh, cx:cx + ow]
+        if jitter is not None:
+            y = _jitter_ref(y, jitter, means)
+        if flip:
+            y = y.flip(-1)
+        y = y.contiguous()
+    else:
+        a = _PreArgs()
+        a.B, a.C, a.src_h, a.src_w, a.resize_h, a.resize_w = B, C, sh, sw, rh, rw
+        a.out_h, a.out_w, a.crop_y, a.crop_x, a.flip = oh, ow, cy, cx, int(flip)
+        a.do_jitter = int(jitter is not None)
+        j = jitter or ColorJitter()
+        a.brightness, a.contrast, a.saturation, a.hue = j.brightness, j.contrast, j.saturation, j.hue
+        for i in range(4):
+            a.mean[i] = means[i]
+        y = torch.empty((B, C, oh, ow), dtype=torch.float32, device=x.device)
+        st = native.lib().st_preprocess(native.ptr(x), native.ptr(y), ctypes.byref(a), native.stream_ptr(x.device))
+        native.check(st, "st_preprocess")
+        launch_count += 1
+    return y[0] if squeeze else y
+
+
+def resize(img, height: int, width: int):
+    return preprocess(img, resize=(height, width))
+
+
+def center_crop(img, height: int, width: int):
+    return preprocess(img, crop=(height, width))
+
+
+def horizontal_flip(img):
+    return preprocess(img, flip=True)
+
+
+def color_jitter(img, jitter: ColorJitter):
+    return preprocess(img, jitter=jitter)
+
+
+def classification_pipeline(img, size: int = 224, resize_to: int = 256, jitter: Optional[ColorJitter] = None,
+                            flip: bool = True):
+    """The reference's classification preprocessing (docs/performance/transforms.md:59-64)."""
+    return preprocess(img, resize=(resize_to, resize_to), crop=(size, size),
+                      jitter=jitter or ColorJitter.balanced(), flip=flip)
+
+
+# ---- NeRF ------------------------------------------------------------------------------------------
+def nerf_sample(rays: torch.Tensor, samples: int, stratified: bool = False, seed: int = 0):
+    """``rays [R, 8]`` (origin, direction, t_min, t_max) → ``(points [R,S,3], t [R,S], deltas [R,S])``."""
+    global launch_count
+    R = rays.shape[0]
+    rays = rays.float().contiguous()
+    if not native.use_native(rays):
+        t_min, t_max = rays[:, 6:7], rays[:, 7:8]
+        interval = (t_max - t_min).clamp(min=1e-3) / samples
+        i = torch.arange(samples, device=rays.device, dtype=torch.float32)[None, :]
+        if stratified:
+            base = (torch.arange(R, dtype=torch.int64)[:, None] * 9781 + seed * 6271) & 0xFFFFFFFF
+            step = (1103515245 * ((base + torch.arange(samples, dtype=torch.int64)[None, :]) & 0xFFFFFFFF) + 12345) & 0xFFFFFFFF
+            off = (((step >> 9) & 0x7FFFFF).float() / float(0x7FFFFF)).to(rays.device)
+        else:
+            off = torch.full((R, samples), 0.5, device=rays.device)
+        t = t_min + (i + off.clamp(0, 0.999)) * interval
+        nxt = torch.cat([t_min + (i[:, 1:]) * interval, t_max], 1) if samples > 1 else t_max
+        deltas = (nxt - t).clamp(min=1e-3)
+        pts = rays[:, None, 0:3] + rays[:, None, 3:6] * t[..., None]
+        return pts, t, deltas
+    pts = torch.empty((R, samples, 3), dtype=torch.float32, device=rays.device)
+    t = torch.empty((R, samples), dtype=torch.float32, device=rays.device)
+    d = torch.empty_like(t)
+    st = native.lib().st_nerf_sample(native.ptr(rays), native.ptr(pts), native.ptr(t), native.ptr(d), ctypes.c_int(R),
+                                     ctypes.c_int(samples), ctypes.c_int(int(stratified)), ctypes.c_uint(seed),
+                                     native.stream_ptr(rays.device))
+    native.check(st, "st_nerf_sample")
+    launch_count += 1
+    return pts, t, d
+
+
+def _composite_ref(sigma, rad, deltas, delta_scale):
+    alpha = 1 - torch.exp(-sigma.clamp(min=0) * deltas * delta_scale)
+    T = torch.cumprod(torch.cat([torch.ones_like(alpha[:, :1]), 1 - alpha[:, :-1]], 1), 1)
+    w = T * alpha
+    return torch.cat([(w[..., None] * rad).sum(1), w.sum(1, keepdim=True)], 1)
+
+
+class _Composite(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sigma, rad, deltas, delta_scale):
+        global launch_count
+        R, S = sigma.shape
+        accum = torch.empty((R, 4), dtype=torch.float32, device=sigma.device)
+        st = native.lib().st_nerf_composite_fwd(native.ptr(sigma), native.ptr(rad), native.ptr(deltas),
+                                                native.ptr(accum), ctypes.c_int(R), ctypes.c_int(S),
+                                                ctypes.c_float(delta_scale), native.stream_ptr(sigma.device))
+        native.check(st, "st_nerf_composite_fwd")
+        launch_count += 1
+        ctx.save_for_backward(sigma, rad, deltas, accum)
+        ctx.delta_scale = delta_scale
+        return accum
+
+    @staticmethod
+    def backward(ctx, d_accum):
+        global launch_count
+        sigma, rad, deltas, accum = ctx.saved_tensors
+        R, S = sigma.shape
+        ds, dr = torch.empty_like(sigma), torch.empty_like(rad)
+        st = native.lib().st_nerf_composite_bwd(native.ptr(sigma), native.ptr(rad), native.ptr(deltas),
+                                                native.ptr(accum), native.ptr(d_accum.contiguous().float()),
+                                                native.ptr(ds), native.ptr(dr), ctypes.c_int(R), ctypes.c_int(S),
+                                                ctypes.c_float(ctx.delta_scale), native.stream_ptr(sigma.device))
+        native.check(st, "st_nerf_composite_bwd")
+        launch_count += 1
+        return ds, dr, None, None
+
+
+def nerf_composite(sigma: torch.Tensor, radiance: torch.Tensor, deltas: torch.Tensor, delta_scale: float = 1.0):
+    """Front-to-back compositing → ``[R, 4]`` (rgb, opacity); differentiable in sigma and radiance."""
+    if not native.use_native(sigma):
+        return _composite_ref(sigma.float(), radiance.float(), deltas.float(), delta_scale)
+    return _Composite.apply(sigma.float().contiguous(), radiance.float().contiguous(), deltas.float().contiguous(),
+                            float(delta_scale))
+
+
+class NerfField(torch.nn.Module):
+    """Small MLP radiance field with frequency encoding (crates/st-vision/src/nerf/field.rs)."""
+
+    def __init__(self, hidden: int = 64, frequencies: int = 6, layers: int = 3):
+        super().__init__()
+        self.frequencies = frequencies
+        dims = [3 + 6 * frequencies] + [hidden] * layers
+        self.net = torch.nn.Sequential(*[m for a, b in zip(dims[:-1], dims[1:]) for m in (torch.nn.Linear(a, b), torch.nn.ReLU())])
+        self.head = torch.nn.Linear(hidden, 4)
+
+    def encode(self, p):
+        feats = [p]
+        for k in range(self.frequencies):
+            feats += [torch.sin((2.0 ** k) * p), torch.cos((2.0 ** k) * p)]
+        return torch.cat(feats, -1)
+
+    def forward(self, points):
+        out = self.head(self.net(self.encode(points)))
+        return out[..., 0], torch.sigmoid(out[..., 1:4])
+
+
+def nerf_render(field: NerfField, rays: torch.Tensor, samples: int = 32, stratified: bool = False, seed: int = 0):
+    pts, _, deltas = nerf_sample(rays, samples, stratified, seed)
+    sigma, rad = field(pts)
+    return nerf_composite(sigma, rad, deltas)
+
+
+# ---- canvas ------------------------------------------------------------------------------------------
+PALETTES = {"grayscale": 0, "spiral": 1, "diverging": 2}
+
+
+def canvas_paint(x: torch.Tensor, palette: str = "spiral", lo: Optional[float] = None, hi: Optional[float] = None):
+    """Paint a 2-D tensor into an RGBA8 image ``[H, W, 4]`` (uint8), normalising to ``[lo, hi]``."""
+    global launch_count
+    xf = x.float().contiguous()
+    lo = float(xf[torch.isfinite(xf)].min()) if lo is None else lo
+    hi = float(xf[torch.isfinite(xf)].max()) if hi is None else hi
+    pal = PALETTES[palette]
+    if not native.use_native(xf):
+        t = ((xf - lo) / (hi - lo) if hi > lo else torch.zeros_like(xf))
+        t = torch.where(torch.isfinite(t), t.clamp(0, 1), torch.zeros_like(t))
+        if pal == 0:
+            r = g = b = t
+        elif pal == 1:
+            r, g, b = (1.6 * t).clamp(max=1), t * t, (0.35 + 0.9 * (1 - (2 * t - 1).abs())).clamp(max=1)
+        else:
+            r = torch.where(t < 0.5, 2 * t, torch.ones_like(t))
+            b = torch.where(t < 0.5, torch.ones_like(t), 2 * (1 - t))
+            g = 1 - (2 * t - 1).abs()
+        rgba = torch.stack([r, g, b, torch.ones_like(t)], -1)
+        return (rgba * 255 + 0.5).to(torch.uint8)
+    out = torch.empty((*xf.shape, 4), dtype=torch.uint8, device=xf.device)
+    st = native.lib().st_canvas_paint(native.ptr(xf), native.ptr(out), ctypes.c_longlong(xf.numel()),
+                                      ctypes.c_float(lo), ctypes.c_float(hi), ctypes.c_int(pal),
+                                      native.stream_ptr(xf.device))
+    native.check(st, "st_canvas_paint")
+    launch_count += 1
+    return out
+
+
+def canvas_fft(field: torch.Tensor, axis: str = "2d") -> torch.Tensor:
+    """Row / column / 2-D FFT of a (complex or real) vector field (library FFT: not a named hot path)."""
+    f = field if torch.is_complex(field) else field.to(torch.complex64)
+    if axis == "row":
+        return torch.fft.fft(f, dim=-1)
+    if axis == "col":
+        return torch.fft.fft(f, dim=-2)
+    return torch.fft.fft2(f)
+
+
+def temporal_volume_render(volume: torch.Tensor, density_scale: float = 1.0) -> torch.Tensor:
+    """Front-to-back compositing of a ``[D, H, W]`` (or ``[D, H, W, 3]``) Z volume along depth."""
+    if volume.dim() == 3:
+        volume = volume[..., None].expand(-1, -1, -1, 3)
+    D, H, W, _ = volume.shape
+    rad = volume.permute(1, 2, 0, 3).reshape(H * W, D, 3).float().contiguous()
+    sigma = rad.mean(-1) * density_scale
+    deltas = torch.ones_like(sigma)
+    return nerf_composite(sigma, rad, deltas).reshape(H, W, 4)
