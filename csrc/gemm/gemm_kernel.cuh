@@ -50,7 +50,22 @@ struct GemmComm {
   const __nv_bfloat16* rs_residual;        // optional, added during the reduction
 };
 
+// Implicit-GEMM convolution (3x3, stride 1, padding 1, NHWC activations).
+//   mode 1 (forward / data gradient): the A tile of 128 output pixels is a 4-D TMA box
+//          {64 channels, W, Hb, Nb} taken at the tap's (kh-1, kw-1) offset; pixels outside the image
+//          are zero-filled by TMA.  K = 9 * C runs tap-major, matching weights stored [OC][tap][C].
+//   mode 2 (weight gradient): K runs over pixels; the B tile (64 pixels x 64-channel blocks of the
+//          shifted input) is the 4-D box, A is dYᵀ; the batch index enumerates (tap, K split).
+struct ConvGeom {
+  int mode;
+  int H, W;          // image size
+  int Hb, Nb;        // rows / images per pixel block (mode 1: 128 pixels, mode 2: 64 pixels)
+  int c_chunks;      // input channels / 64 (mode 1)
+  int taps;          // 9
+};
+
 struct GemmParams {
+  ConvGeom conv;
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
@@ -326,19 +341,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
           const int k0 = kb * BK;
-          if constexpr (!A_MN) {
-            tma_load_3d(sa, mapA, fb, k0, m_coord, b);
-          } else {
+          if (p.conv.mode == 1) {
+            // A: 128 output pixels (Nb images x Hb rows x W) shifted by the tap, 64 channels
+            const int tap = kb / p.conv.c_chunks, cc = kb - tap * p.conv.c_chunks;
+            const int hblocks = p.conv.H / p.conv.Hb;
+            const int img0 = (tm / hblocks) * p.conv.Nb, h0 = (tm % hblocks) * p.conv.Hb;
+            tma_load_4d(sa, mapA, fb, cc * 64, tap % 3 - 1, h0 + tap / 3 - 1, img0);
+            tma_load_3d(sb, &tmB, fb, k0, n0, 0);
+          } else if (p.conv.mode == 2) {
+            // batch index = tap + taps * split; K block = 64 consecutive pixels
+            const int tap = b % p.conv.taps, split = b / p.conv.taps;
+            const int kg = split * k_blocks + kb;                  // global pixel block
+            const int hblocks = p.conv.H / p.conv.Hb;
+            const int img0 = (kg / hblocks) * p.conv.Nb, h0 = (kg % hblocks) * p.conv.Hb;
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_3d(sa + j * (64 * BK * 2), mapA, fb, m_coord + 64 * j, k0, b);
-          }
-          if constexpr (!B_MN) {
-            tma_load_3d(sb, &tmB, fb, k0, n0, b);
-          } else {
+              tma_load_3d(sa + j * (64 * BK * 2), mapA, fb, m_coord + 64 * j, kg * BK, 0);
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (64 * BK * 2), &tmB, fb, n0 + 64 * j, k0, b);
+              tma_load_4d(sb + j * (64 * BK * 2), &tmB, fb, n0 + 64 * j, tap % 3 - 1, h0 + tap / 3 - 1, img0);
+          } else {
+            if constexpr (!A_MN) {
+              tma_load_3d(sa, mapA, fb, k0, m_coord, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_3d(sa + j * (64 * BK * 2), mapA, fb, m_coord + 64 * j, k0, b);
+            }
+            if constexpr (!B_MN) {
+              tma_load_3d(sb, &tmB, fb, k0, n0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * (64 * BK * 2), &tmB, fb, n0 + 64 * j, k0, b);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -420,7 +456,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
       void* c_ptr = p.C;
-      long long c_base = (long long)b * p.batch_stride_c + (long long)row * p.ldc;
+      const int cbatch = (p.conv.mode == 2) ? (b % p.conv.taps) : b;
+      long long c_base = (long long)cbatch * p.batch_stride_c + (long long)row * p.ldc;
       int owner = 0;
       if constexpr (COMM == COMM_RS) {
         owner = m0 / cm.rows_per_chunk;
