@@ -34,6 +34,7 @@ class ConvClassifier(nn.Module):
         super().__init__()
         self.num_classes, self.in_channels, self.image, self.dtype = num_classes, in_channels, image, dtype
         self.classes_pad = (num_classes + 7) // 8 * 8
+        self.grad_ready_hook = None
         shapes = []
         ic = in_channels
         for s, oc in enumerate(STAGES):
@@ -70,7 +71,7 @@ class ConvClassifier(nn.Module):
     # ------------------------------------------------------------------------------------------
     def forward_backward(self, images, labels, loss_scale: float = 1.0, backward: bool = True, layer_done=None):
         with torch.no_grad():
-            return self._forward_backward(images, labels, loss_scale, backward, layer_done)
+            return self._forward_backward(images, labels, loss_scale, backward, layer_done or self.grad_ready_hook)
 
     def _forward_backward(self, images: torch.Tensor, labels: Optional[torch.Tensor], loss_scale: float = 1.0,
                           backward: bool = True, layer_done=None):
@@ -104,9 +105,9 @@ class ConvClassifier(nn.Module):
         dlogits = loss_ops._grad_(logits, tgt, lse, coef, 1.0, 0)
         gemm_ops.gemm(dlogits, feat, a_mn=True, b_mn=True, out=P["head.weight"].main_grad, accumulate=True)
         ew.colsum(dlogits, P["head.bias"].main_grad, accumulate=True)
-        if layer_done:
-            layer_done("head")
         dfeat = gemm_ops.gemm(dlogits, P["head.weight"], b_mn=True)
+        if layer_done:
+            layer_done("head")          # only after the last read of the head weights
         d = C.global_avgpool_backward(dfeat, H, W)
         k = len(acts) - 1                           # index of the pooled output of the last stage
         for s in reversed(range(4)):
@@ -122,10 +123,10 @@ class ConvClassifier(nn.Module):
                 ic = xin.shape[-1]
                 C.conv3x3_wgrad(d, xin, w.main_grad)
                 ew.colsum(d.reshape(-1, d.shape[-1]), P[f"conv{s}_{i}.bias"].main_grad, accumulate=True)
-                if layer_done:
-                    layer_done(f"conv{s}_{i}")
-                if k - 1 > 0 or ic % 64 == 0 and k - 1 > 0:
+                if k - 1 > 0:
                     d = C.conv3x3(d, C.dgrad_weights(w, ic), relu_mask_of=xin)
+                if layer_done:
+                    layer_done(f"conv{s}_{i}")   # after the data gradient has read the weights
                 k -= 1
         return loss
 

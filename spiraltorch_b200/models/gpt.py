@@ -85,9 +85,10 @@ class _Act:
 
 class GPTModel(nn.Module):
     def __init__(self, cfg: GPTConfig, device="cuda", dtype=torch.bfloat16,
-                 tp: Optional[TPContext] = None, seed: int = 0):
+                 tp: Optional[TPContext] = None, seed: int = 0, allocator=None):
         super().__init__()
         self.cfg = cfg
+        self.grad_ready_hook = None   # called with a parameter-group name once its gradient is final
         self.tp = tp or TPContext()
         W = self.tp.world
         assert cfg.n_heads % W == 0 and cfg.ffn % W == 0 and cfg.vocab_size % W == 0
@@ -127,8 +128,9 @@ class GPTModel(nn.Module):
         last_decayed = [s[0] for s in shapes if s[2]][-1]
         self.decay_elems = (offsets[last_decayed][0] + offsets[last_decayed][1] + 127) // 128 * 128
         self.flat_elems = off
-        self.flat_w = torch.zeros(off, dtype=dtype, device=device)
-        self.flat_grad = torch.zeros(off, dtype=torch.float32, device=device)
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
+        self.flat_w = alloc(off, dtype)
+        self.flat_grad = alloc(off, torch.float32)
         self._offsets = offsets
         self._names = [s[0] for s in shapes]
 
@@ -274,9 +276,13 @@ class GPTModel(nn.Module):
         for l in reversed(range(cfg.n_layers)):
             d = self._layer_backward(l, acts[l], d, B, S)
             acts[l] = None
+            if self.grad_ready_hook is not None:
+                self.grad_ready_hook(f"h{l}")
         d_full = tp.all_gather_rows(d)
         dpos = pos.main_grad if pos is not None else None
         ew.embedding_backward(tokens, d_full.contiguous(), emb.main_grad, dpos, S, self.vocab_start)
+        if self.grad_ready_hook is not None:
+            self.grad_ready_hook("embed")
 
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor,
                          loss_scale: float = 1.0) -> torch.Tensor:

@@ -149,6 +149,39 @@ def main():
         assert r < 3e-2, r
 
     sec.run("gpt", sec_gpt)
+
+    def sec_info_nce():
+        from spiraltorch_b200.parallel.contrastive import FusedInfoNCE
+        torch.manual_seed(300 + rank)
+        op = FusedInfoNCE(fused.heap, fused.signals, rows=1024, dim=256, temperature=0.1, tp=fused)
+        base = torch.randn(1024, 256, device=dev)
+        res = []
+        for rep in range(2):
+            a = torch.nn.functional.normalize(base + 0.3 * torch.randn_like(base), dim=-1).requires_grad_(True)
+            p_ = torch.nn.functional.normalize(base + 0.3 * torch.randn_like(base), dim=-1).requires_grad_(True)
+            loss = op.apply(a, p_)
+            loss.backward()
+            a2 = a.detach().bfloat16().float().requires_grad_(True)
+            p2 = p_.detach().bfloat16().float().requires_grad_(True)
+            parts = [torch.empty_like(p2) for _ in range(world)]
+            dist.all_gather(parts, p2.detach())
+            parts[rank] = p2
+            logits = a2 @ torch.cat(parts, 0).t() / 0.1
+            idx = torch.arange(1024, device=dev) + rank * 1024
+            ref = (torch.logsumexp(logits, -1) - logits[torch.arange(1024, device=dev), idx]).mean()
+            ref.backward()
+            # positives also receive gradient from the other ranks' losses
+            full = torch.zeros(world * 1024, 256, device=dev)
+            full[rank * 1024:(rank + 1) * 1024] = p2.grad
+            others = torch.autograd.grad(ref, a2, retain_graph=False, allow_unused=True) if False else None
+            res.append((loss.detach(), ref.detach(), a.grad.clone(), a2.grad.clone()))
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        for loss, ref, ga, gr in res:
+            assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
+            assert rel(ga, gr) < 5e-2, rel(ga, gr)
+
+    sec.run("info_nce", sec_info_nce)
     def sec_bench():
         if big:
             T, d, F = 16384, 2048, 8192 // world
