@@ -1,0 +1,225 @@
+#!/usr/bin/env python
+"""Per-kernel micro-benchmarks against the library op on the same GPU, with roofline fractions.
+
+    python benchmarks/kernels.py gemm attn_fwd attn_bwd conv norm adamw ce [--iters 10] [--json out.json]
+    python benchmarks/kernels.py gemm --profile      # 2 launches of ours only: the target of an ncu capture
+
+Every timing: 3 warm-up launches, then ``iters`` launches each preceded by a write of a 256 MiB
+buffer (L2 flush), timed with CUDA events on the launching stream; the median is reported.
+Roofline denominators come from ``MEASURED_PEAKS.json`` at the repository root (written by the
+round driver); without it the documented fallbacks 6.65 TB/s and 1.59 PFLOP/s are used and the
+output says "of fallback".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from spiraltorch_b200.ops import attention as A  # noqa: E402
+from spiraltorch_b200.ops import conv as C  # noqa: E402
+from spiraltorch_b200.ops import gemm as G  # noqa: E402
+from spiraltorch_b200.ops import loss as L  # noqa: E402
+from spiraltorch_b200.ops import norm as N  # noqa: E402
+from spiraltorch_b200.ops import optim as O  # noqa: E402
+
+DEV = "cuda"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def timed(fn, iters):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def row(name, shape, ours_ms, lib_ms, flops=None, bytes_=None):
+    hbm, tf, kind = peaks()
+    r = {"kernel": name, "shape": shape, "ours_ms": round(ours_ms, 4), "library_ms": None if lib_ms is None else round(lib_ms, 4)}
+    if lib_ms:
+        r["speedup_vs_library"] = round(lib_ms / ours_ms, 3)
+    if flops:
+        r["tflops"] = round(flops / ours_ms / 1e9, 1)
+        r[f"frac_of_{kind}_bf16_peak"] = round(flops / ours_ms / 1e9 / tf, 3)
+    if bytes_:
+        r["gbs"] = round(bytes_ / ours_ms / 1e6, 1)
+        r[f"frac_of_{kind}_hbm"] = round(bytes_ / ours_ms / 1e6 / hbm, 3)
+    print(json.dumps(r), flush=True)
+    return r
+
+
+def bench_gemm(iters, profile):
+    out = []
+    shapes = [(16384, 6144, 2048, False, False), (16384, 2048, 8192, False, False), (16384, 8192, 2048, False, True),
+              (8192, 2048, 16384, True, True), (16384, 50304, 2048, False, False), (16384, 2304, 768, False, False)]
+    if profile:
+        shapes = [(16384, 6144, 2048, False, False)]
+    for M, Nn, K, a_mn, b_mn in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device=DEV).bfloat16()
+        b = torch.randn((K, Nn) if b_mn else (Nn, K), device=DEV).bfloat16()
+        c = torch.empty(M, Nn, device=DEV, dtype=torch.bfloat16)
+        ours = lambda: G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c)  # noqa: E731
+        if profile:
+            ours(); ours(); torch.cuda.synchronize()
+            return out
+        af, bf = (a.t() if a_mn else a), (b if b_mn else b.t())
+        t1, t2 = timed(ours, iters), timed(lambda: torch.matmul(af, bf, out=c), iters)
+        out.append(row("gemm_bf16" + ("_amn" if a_mn else "") + ("_bmn" if b_mn else ""), [M, Nn, K], t1, t2,
+                       flops=2.0 * M * Nn * K))
+    return out
+
+
+def bench_attn(iters, profile, backward):
+    out = []
+    cfgs = [(8, 2048, 16, 128), (32, 512, 12, 64)] if not profile else [(4, 2048, 16, 128)]
+    for B, S, H, D in cfgs:
+        qkv = torch.randn(B, S, 3, H, D, device=DEV).bfloat16()
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        do = torch.randn(B, S, H, D, device=DEV).bfloat16()
+        o, lse = A.attention_forward(q, k, v, True)
+        if backward:
+            ours = lambda: A.attention_backward(q, k, v, o, lse, do, True)  # noqa: E731
+        else:
+            ours = lambda: A.attention_forward(q, k, v, True)  # noqa: E731
+        if profile:
+            ours(); ours(); torch.cuda.synchronize()
+            return out
+        qt, kt, vt = (t.transpose(1, 2).detach().requires_grad_(backward) for t in (q, k, v))
+        if backward:
+            oo = torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+            lib = lambda: torch.autograd.grad(oo, (qt, kt, vt), do.transpose(1, 2), retain_graph=True)  # noqa: E731
+        else:
+            lib = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True)  # noqa: E731
+        fl = (10.0 if backward else 4.0) * B * H * S * S * D / 2
+        out.append(row("attn_bwd" if backward else "attn_fwd", [B, S, H, D], timed(ours, iters), timed(lib, iters), flops=fl))
+    return out
+
+
+def bench_conv(iters, profile):
+    out = []
+    cfgs = [(256, 32, 64, 128), (256, 16, 128, 256), (256, 8, 256, 512), (256, 64, 64, 64)] if not profile else [(64, 32, 64, 128)]
+    for Nb, H, Ci, Co in cfgs:
+        x = torch.randn(Nb, H, H, Ci, device=DEV).bfloat16()
+        w = (torch.randn(Co, 9 * Ci, device=DEV) * 0.05).bfloat16()
+        b = torch.randn(Co, device=DEV).bfloat16()
+        ours = lambda: C.conv3x3(x, w, b, relu=True)  # noqa: E731
+        if profile:
+            ours(); ours(); torch.cuda.synchronize()
+            return out
+        xc = x.permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+        wc = w.reshape(Co, 3, 3, Ci).permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+        lib = lambda: torch.relu_(torch.nn.functional.conv2d(xc, wc, b, padding=1))  # noqa: E731
+        fl = 2.0 * Nb * H * H * 9 * Ci * Co
+        out.append(row("conv3x3_bias_relu_fwd", [Nb, H, H, Ci, Co], timed(ours, iters), timed(lib, iters), flops=fl))
+        dy = torch.randn(Nb, H, H, Co, device=DEV).bfloat16()
+        dw = torch.zeros(Co, 9 * Ci, device=DEV)
+        t = timed(lambda: C.conv3x3_wgrad(dy, x, dw), iters)
+        dyc = dy.permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+        tl = timed(lambda: torch.ops.aten.convolution_backward(dyc, xc, wc, None, [1, 1], [1, 1], [1, 1], False, [0, 0], 1,
+                                                               [False, True, False]), iters)
+        out.append(row("conv3x3_wgrad", [Nb, H, H, Ci, Co], t, tl, flops=fl))
+    return out
+
+
+def bench_norm(iters, profile):
+    out = []
+    rows, d = (16384, 2048) if not profile else (65536, 2048)
+    x = torch.randn(rows, d, device=DEV).bfloat16()
+    g = torch.ones(d, device=DEV).bfloat16()
+    dy = torch.randn(rows, d, device=DEV).bfloat16()
+    y, _, mean, rstd = N.norm_forward(x, g, None, 1e-5, True)
+    dg = torch.zeros(d, device=DEV)
+    fwd = lambda: N.norm_forward(x, g, None, 1e-5, True)  # noqa: E731
+    bwd = lambda: N.norm_backward(dy, x, g, mean, rstd, True, dg, None, False)  # noqa: E731
+    if profile:
+        fwd(); bwd(); fwd(); bwd(); torch.cuda.synchronize()
+        return out
+    out.append(row("rmsnorm_fwd", [rows, d], timed(fwd, iters), timed(lambda: torch.nn.functional.rms_norm(x, (d,), g, 1e-5), iters),
+                   bytes_=rows * d * 4))
+    out.append(row("rmsnorm_bwd", [rows, d], timed(bwd, iters), None, bytes_=rows * d * 6))
+    return out
+
+
+def bench_adamw(iters, profile):
+    n = 256 * 1024 * 1024 if not profile else 64 * 1024 * 1024
+    g, m, v, master = (torch.randn(n, device=DEV) for _ in range(4))
+    v.abs_()
+    w = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ours = lambda: O.adamw_step(g, master, m, v, w, lr=1e-3, step=2, weight_decay=0.1, zero_grad=False)  # noqa: E731
+    if profile:
+        ours(); ours(); torch.cuda.synchronize()
+        return []
+    p = master.clone().requires_grad_(True)
+    p.grad = g.clone()
+    opt = torch.optim.AdamW([p], lr=1e-3, fused=True)
+    return [row("adamw_fused_master_bf16", [n], timed(ours, iters), timed(opt.step, iters), bytes_=n * (4 * 7 + 2))]
+
+
+def bench_ce(iters, profile):
+    T, V = (16384, 50304) if not profile else (8192, 50304)
+    logits = torch.randn(T, V, device=DEV).bfloat16()
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    ours = lambda: L._stats(logits, tgt, 0)  # noqa: E731
+    if profile:
+        ours(); ours(); torch.cuda.synchronize()
+        return []
+    lib = lambda: torch.nn.functional.cross_entropy(logits.float(), tgt)  # noqa: E731
+    return [row("cross_entropy_stats", [T, V], timed(ours, iters), timed(lib, iters), bytes_=T * V * 2)]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernels", nargs="*", default=["gemm", "attn_fwd", "attn_bwd", "conv", "norm", "adamw", "ce"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--profile", action="store_true", help="launch ours twice and exit (ncu target)")
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    table = {"gemm": lambda: bench_gemm(args.iters, args.profile),
+             "attn_fwd": lambda: bench_attn(args.iters, args.profile, False),
+             "attn_bwd": lambda: bench_attn(args.iters, args.profile, True),
+             "conv": lambda: bench_conv(args.iters, args.profile),
+             "norm": lambda: bench_norm(args.iters, args.profile),
+             "adamw": lambda: bench_adamw(args.iters, args.profile),
+             "ce": lambda: bench_ce(args.iters, args.profile)}
+    rows = []
+    for k in args.kernels:
+        rows += table[k]()
+    from spiraltorch_b200.ops import native
+    native.raise_on_device_error()
+    if args.json:
+        json.dump({"peaks": dict(zip(("hbm_gbs", "bf16_tflops", "source"), peaks())), "rows": rows}, open(args.json, "w"), indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

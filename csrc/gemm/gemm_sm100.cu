@@ -117,7 +117,7 @@ ST_API int st_gemm_bf16(const StGemmArgs* a, void* stream_v) {
       return ST_ERR_CUDA;
   }
 
-  GemmParams p;
+  GemmParams p{};  // zero-initialised: unset optional features (convolution geometry, epilogue operands) stay off
   p.C = a->C;
   p.ldc = a->ldc;
   p.bias = static_cast<const __nv_bfloat16*>(a->bias);
