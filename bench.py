@@ -112,6 +112,9 @@ def main() -> int:
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--tp-mode", default=os.environ.get("ST_TP_MODE", "auto"), choices=["auto", "nccl", "fused"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: changes the model (result invalid)")
+    ap.add_argument("--kernel-table", default=None,
+                    help="after the timed regions, run one extra step under torch.profiler on rank 0 and write "
+                         "the per-kernel device-time table to this path (analysis only, never a bench value)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -216,6 +219,19 @@ def main() -> int:
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     native.raise_on_device_error()
+
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        if rank == 0:
+            with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+                trainer.device_step(*dev_batches[0])
+                torch.cuda.synchronize(device)
+            with open(args.kernel_table, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=60))
+        else:
+            trainer.device_step(*dev_batches[0])
+        barrier()
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)

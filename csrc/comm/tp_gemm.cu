@@ -89,6 +89,7 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   if (W < 1 || W > st::kMaxRanks) return st::fail(ST_ERR_INVALID, "ag_gemm: bad world size");
   if (a->T % (W * BM) != 0) return st::fail(ST_ERR_INVALID, "ag_gemm: T must be a multiple of world*128");
   const int rows = a->T / W;
+  if (a->sub_per_chunk > kMaxSubChunks) return st::fail(ST_ERR_INVALID, "ag_gemm: at most 16 sub-chunks per shard");
   if (a->sub_per_chunk < 1 || rows % (a->sub_per_chunk * BM) != 0)
     return st::fail(ST_ERR_INVALID, "ag_gemm: shard rows must be a multiple of sub_per_chunk*128");
   if (a->K % 8 || a->ldb % 8) return st::fail(ST_ERR_INVALID, "ag_gemm: K and ldb must be multiples of 8");

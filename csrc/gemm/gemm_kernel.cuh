@@ -4,11 +4,12 @@
 // COMM selects what else the launch does:
 //   COMM_NONE  C = epilogue(alpha * A·Bᵀ)
 //   COMM_AG    all-gather → GEMM.  A is the gathered activation [T, K]; its row chunks are
-//              produced by `comm_ctas` extra CTAs of the SAME launch on every rank, which
-//              push the local shard into every rank's gather buffer (multimem.st through
-//              NVSwitch, or peer stores) and publish per-sub-chunk arrival flags.  The TMA
-//              producer of a GEMM CTA waits (bounded) for the flag of the rows it is about
-//              to load; tiles are ordered local chunk first, then in ring order.
+//              produced by `comm_ctas` CTAs of the SAME launch on every rank, which push the
+//              local shard into every rank's gather buffer (bulk copies through shared
+//              memory, plain peer writes over NVLink, destinations in ring order) and count
+//              per-sub-chunk arrivals.  The TMA producer of a GEMM CTA waits (bounded) for
+//              the counter of the rows it is about to load; tiles are ordered local chunk
+//              first, then in ring order.
 //   COMM_RS    GEMM → reduce-scatter.  The epilogue writes each partial tile straight into
 //              the staging slot of the rank that owns those rows (peer stores over NVLink),
 //              then bumps that owner's per-row-block counter; tiles are ordered so that the
@@ -30,6 +31,7 @@ constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warp
 
 enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_BWD = 3, ACT_RELU_BWD = 4 };
 enum Comm : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+constexpr int kMaxSubChunks = 16;   // arrival counters reserved per source rank (AG)
 
 struct GemmComm {
   PeerGroup g;
@@ -41,7 +43,7 @@ struct GemmComm {
   const __nv_bfloat16* src_shard;          // [rows_per_chunk, K] contiguous
   __nv_bfloat16* gather_peers[kMaxRanks];  // [T, K] contiguous on every rank
   __nv_bfloat16* gather_mc;                // multicast alias or null
-  int slot_arrive;      // flags: slot_arrive + src * sub_per_chunk + sub
+  int slot_arrive;      // arrival flags (epoch valued): slot_arrive + src * kMaxSubChunks + sub
   // ---- RS ----
   __nv_bfloat16* stage_peers[kMaxRanks];   // on each owner: [world][rows_per_chunk, N]
   int slot_done;        // counters: slot_done + row block within the chunk
@@ -152,106 +154,139 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
 
   // ------------------------------------------------------------------------------------------
-  // AG: CTAs past the GEMM grid push this rank's shard to every rank and publish the flags.
+  // AG: the first `n_comm` CTAs of the grid push this rank's shard into every rank's gather
+  // buffer and publish arrival flags; the remaining CTAs run the GEMM tiles.
+  //
+  // Schedule.  The shard is cut into `sub_per_chunk` sub-chunks; a work item is one sub-chunk
+  // for one destination.  Items are ordered destination-major in ring order (rank-1, rank-2,
+  // ..., finally this rank's own buffer) and dealt round-robin to the communication CTAs: in
+  // every phase the W senders address W different receivers, and a receiver gets the chunks in
+  // the order in which its GEMM tiles consume them (rank+1 first).  Thread 0 of a CTA drives
+  // the copy, local HBM → shared-memory ring (bulk load) → destination (bulk store, plain peer
+  // writes); thread 32 publishes the flag of an item once its stores are complete, so that the
+  // system-scope release never stalls the copy pipeline.
   // ------------------------------------------------------------------------------------------
+  int gemm_bid = blockIdx.x;
   if constexpr (COMM == COMM_AG) {
-    if (static_cast<int>(blockIdx.x) >= cm.gemm_ctas) {
-      __shared__ int s_ok;
-      const int W = cm.g.world, R = cm.g.rank;
-      const int cta = blockIdx.x - cm.gemm_ctas;
-      const int n_comm = gridDim.x - cm.gemm_ctas;
+    const int n_comm = gridDim.x - cm.gemm_ctas;
+    gemm_bid = static_cast<int>(blockIdx.x) - n_comm;
+    if (gemm_bid < 0) {
+      __shared__ volatile int s_done_items;   // items of this CTA whose stores are complete
+      __shared__ volatile int s_finished;     // the copy thread has returned from its loop
       if (threadIdx.x == 0) {
-        bool ok = true;
-        if (cta == 0) {
-          fence_sys();
-          for (int q = 0; q < W; ++q) st_release_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
-        }
-        // peers must have left the previous launch that read this gather buffer
-        for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
-        s_ok = ok ? 1 : 0;
+        s_done_items = 0;
+        s_finished = 0;
       }
       __syncthreads();
-      if (!s_ok) {
-        if (threadIdx.x == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
+      if (threadIdx.x != 0 && threadIdx.x != 32) return;
+      const int W = cm.g.world, R = cm.g.rank;
+      const int cta = blockIdx.x;
+      const int SUBS = cm.sub_per_chunk;
+      const int items = W * SUBS;
+      const int my_items = (items - cta + n_comm - 1) / n_comm;     // items cta, cta + n_comm, ...
+      auto dest_of = [&](int item) {
+        const int q = item / SUBS;
+        return q < W - 1 ? (R - 1 - q + W) % W : R;
+      };
+      if (threadIdx.x == 32) {
+        // ---- publisher ----
+        int sent = 0;
+        const uint64_t t0 = globaltimer_ns();
+        for (;;) {
+          const int fin = s_finished;
+          const int d = s_done_items;
+          if (sent < d) {
+            __threadfence_block();
+            fence_proxy_async_global();
+            for (; sent < d; ++sent) {
+              const int item = cta + sent * n_comm;
+              st_release_sys(cm.g.signals[dest_of(item)] + cm.slot_arrive + R * kMaxSubChunks + item % SUBS,
+                             cm.g.epoch);
+            }
+          }
+          if (sent >= my_items || (fin && sent >= s_done_items)) break;
+          if (globaltimer_ns() - t0 > (uint64_t)(W + 2) * ST_WAIT_TIMEOUT_NS) break;   // the copy thread reports the cause
+          __nanosleep(64);
+        }
         return;
       }
-      const long long sub_elems = (long long)(cm.rows_per_chunk / cm.sub_per_chunk) * p.K;
-      if (cm.gather_mc) {
-        // NVLS: one multimem.st reaches every rank; eight independent 16-byte loads per thread
-        // are in flight before the stores are issued
-        for (int s = cta; s < cm.sub_per_chunk; s += n_comm) {
-          const __nv_bfloat16* src = cm.src_shard + (long long)s * sub_elems;
-          const long long dst_off = ((long long)R * cm.rows_per_chunk) * p.K + (long long)s * sub_elems;
-          constexpr int U = 8;
-          for (long long i0 = threadIdx.x * 8ll; i0 < sub_elems; i0 += NUM_THREADS * 8ll * U) {
-            uint4 v[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const long long i = i0 + (long long)u * NUM_THREADS * 8;
-              if (i < sub_elems) v[u] = *reinterpret_cast<const uint4*>(src + i);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const long long i = i0 + (long long)u * NUM_THREADS * 8;
-              if (i < sub_elems) multimem_st_v4(cm.gather_mc + dst_off + i, v[u]);
-            }
-          }
-          __syncthreads();
-          if (threadIdx.x == 0) {
-            fence_sys();
-            for (int q = 0; q < W; ++q)
-              st_release_sys(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * cm.sub_per_chunk + s, cm.g.epoch);
-          }
+      // ---- copy thread ----
+      bool ok = true;
+      if (cta == 0) {
+        fence_sys();
+        for (int q = 0; q < W; ++q) st_release_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
+      }
+      // peers must have left the previous launch that read this gather buffer
+      for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
+      if (!ok) {
+        report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
+        s_finished = 1;
+        return;
+      }
+      constexpr int NB = 6;            // ring buffers
+      constexpr int LAG = 4;           // stores that may still be in flight when older ones are published
+      constexpr uint32_t CH = 32768;
+      const long long sub_bytes = (long long)(cm.rows_per_chunk / SUBS) * p.K * 2;
+      const int n_ch = (int)((sub_bytes + CH - 1) / CH);            // chunks per item
+      uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + NB * CH);
+      volatile int local_abort = 0;
+      for (int i = 0; i < NB; ++i) mbar_init(smem_u32(&cbar[i]), 1);
+      fence_barrier_init();
+      const char* src_base = reinterpret_cast<const char*>(cm.src_shard);
+      const long long dst_base = (long long)R * cm.rows_per_chunk * p.K * 2;
+      const int total = my_items * n_ch;
+      // chunk c of this CTA → (item, byte offset inside the shard, size)
+      auto chunk_of = [&](int c, int& item, uint32_t& sz) {
+        const int k = c / n_ch, j = c - k * n_ch;
+        item = cta + k * n_comm;
+        const long long o = (long long)j * CH;
+        sz = (uint32_t)min((long long)CH, sub_bytes - o);
+        return (long long)(item % SUBS) * sub_bytes + o;
+      };
+      auto issue_load = [&](int c) {
+        const int b = c % NB;
+        int item;
+        uint32_t sz;
+        const long long off = chunk_of(c, item, sz);
+        mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
+        bulk_load_g2s(smem_u32(smem + b * CH), src_base + off, sz, smem_u32(&cbar[b]));
+      };
+      for (int c = 0; c < total && c < NB; ++c) issue_load(c);
+      uint32_t phase_bits = 0;
+      for (int c = 0; c < total; ++c) {
+        const int b = c % NB;
+        if (!mbar_wait(smem_u32(&cbar[b]), (phase_bits >> b) & 1u, &local_abort)) { ok = false; break; }
+        phase_bits ^= (1u << b);
+        int item;
+        uint32_t sz;
+        const long long off = chunk_of(c, item, sz);
+        bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[dest_of(item)]) + dst_base + off,
+                       smem_u32(smem + b * CH), sz);
+        tma_store_commit();
+        // the buffer of the previous chunk may be refilled once its store has read it
+        if (c >= 1 && c - 1 + NB < total) {
+          tma_store_wait_read<1>();
+          issue_load(c - 1 + NB);
         }
-      } else if (threadIdx.x == 0) {
-        // no multicast: one thread drives TMA bulk copies, local HBM → shared memory ring →
-        // every rank's gather buffer (plain peer stores by the copy engine of this SM)
-        constexpr int NB = 5;
-        constexpr uint32_t CH = 32768;
-        uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + NB * CH);
-        volatile int local_abort = 0;
-        for (int i = 0; i < NB; ++i) mbar_init(smem_u32(&cbar[i]), 1);
-        fence_barrier_init();
-        uint32_t phase_bits = 0;
-        for (int s = cta; s < cm.sub_per_chunk; s += n_comm) {
-          const char* src = reinterpret_cast<const char*>(cm.src_shard + (long long)s * sub_elems);
-          const long long dst_off = (((long long)R * cm.rows_per_chunk) * p.K + (long long)s * sub_elems) * 2;
-          const long long bytes = sub_elems * 2;
-          const int n_ch = (int)((bytes + CH - 1) / CH);
-          auto issue_load = [&](int c) {
-            const int b = c % NB;
-            const uint32_t sz = (uint32_t)min((long long)CH, bytes - (long long)c * CH);
-            mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
-            bulk_load_g2s(smem_u32(smem + b * CH), src + (long long)c * CH, sz, smem_u32(&cbar[b]));
-          };
-          for (int c = 0; c < n_ch && c < NB; ++c) issue_load(c);
-          bool ok = true;
-          for (int c = 0; c < n_ch; ++c) {
-            const int b = c % NB;
-            if (!mbar_wait(smem_u32(&cbar[b]), (phase_bits >> b) & 1u, &local_abort)) { ok = false; break; }
-            phase_bits ^= (1u << b);
-            const uint32_t sz = (uint32_t)min((long long)CH, bytes - (long long)c * CH);
-            for (int q = 0; q < W; ++q)
-              bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[(R + q) % W]) + dst_off + (long long)c * CH,
-                             smem_u32(smem + b * CH), sz);
-            tma_store_commit();
-            // the buffer of the previous chunk may be refilled once its stores have read it
-            if (c >= 1 && c - 1 + NB < n_ch) {
-              tma_store_wait_read<1>();
-              issue_load(c - 1 + NB);
-            }
+        if (c >= LAG) {
+          tma_store_wait<LAG>();        // every store up to chunk c - LAG is complete
+          const int cc = c - LAG;
+          if (cc % n_ch == n_ch - 1) {
+            fence_proxy_async_global();
+            __threadfence_block();
+            s_done_items = cc / n_ch + 1;
           }
-          tma_store_wait<0>();
-          if (!ok) {
-            report_error(p.err, ERR_MBAR_TIMEOUT, 0xA604u);
-            break;
-          }
-          fence_proxy_async_global();
-          fence_sys();
-          for (int q = 0; q < W; ++q)
-            st_release_sys(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * cm.sub_per_chunk + s, cm.g.epoch);
         }
       }
+      tma_store_wait<0>();
+      if (!ok) {
+        report_error(p.err, ERR_MBAR_TIMEOUT, 0xA604u);
+      } else {
+        fence_proxy_async_global();
+        __threadfence_block();
+        s_done_items = my_items;
+      }
+      s_finished = 1;
       return;
     }
   }
@@ -310,7 +345,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += grid_stride) {
+      for (int t = gemm_bid; t < total_tiles && ok; t += grid_stride) {
         int b, tm, tn;
         map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
@@ -323,8 +358,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // the local rows are read from the shard itself; nothing to wait for
             mapA = &tmA_local;
             m_coord = m0 - src * cm.rows_per_chunk;
-          } else if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * cm.sub_per_chunk + sub,
-                            cm.g.epoch)) {
+          } else if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * kMaxSubChunks + sub,
+                                   cm.g.epoch)) {
             *abort_flag = 1;
             report_error(p.err, ERR_FLAG_TIMEOUT, 0xA601u);
             break;
@@ -391,7 +426,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += grid_stride, ++iter) {
+      for (int t = gemm_bid; t < total_tiles && ok; t += grid_stride, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
@@ -432,6 +467,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int iter = 0;
     int store_seq = 0;          // TMA stores issued by this warp (selects the staging buffer)
+    int tile_seq0 = 0;          // value of store_seq when the current tile started
+    constexpr int kPubBatch = 3;
+    int pend_owner[kPubBatch], pend_block[kPubBatch], n_pend = 0;   // RS: tiles stored, not yet published
     bool alive = true;
     if constexpr (COMM == COMM_RS) {
       // peers' staging areas are free once every peer has entered this launch
@@ -445,7 +483,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA602u);
       }
     }
-    for (int t = blockIdx.x; t < total_tiles && alive; t += grid_stride, ++iter) {
+    for (int t = gemm_bid; t < total_tiles && alive; t += grid_stride, ++iter) {
       int b, tm, tn;
       map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
@@ -453,6 +491,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!mbar_wait_warp(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag)) break;
       tc_fence_after();
+      tile_seq0 = store_seq;
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
       void* c_ptr = p.C;
@@ -636,19 +675,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       if constexpr (COMM == COMM_RS) {
-        // this warp's 32 rows of the tile are stored: publish them to the owner (the counter
-        // counts warp arrivals, so no CTA-wide barrier is needed here)
+        // Publish this warp's 32 rows to the owner (the counter counts warp arrivals, so no
+        // CTA-wide barrier is needed).  Waiting for the stores of the tile just issued would put
+        // an NVLink round trip into every tile, and so would a system-scope release per tile:
+        // finished tiles are queued and published kPubBatch at a time behind one fence, after
+        // the wait that leaves only the newest tile's store groups outstanding.
         if (lane == 0) {
           if (p.use_tma_store) {
-            tma_store_wait<0>();          // the bulk stores of this tile have been performed
-            fence_proxy_async_global();
+            if (n_pend == kPubBatch) {
+              const int groups = store_seq - tile_seq0;      // bulk groups committed for this tile
+              switch (groups) {
+                case 0: tma_store_wait<0>(); break;
+                case 1: tma_store_wait<1>(); break;
+                case 2: tma_store_wait<2>(); break;
+                case 3: tma_store_wait<3>(); break;
+                default: tma_store_wait<4>(); break;
+              }
+              fence_proxy_async_global();
+              fence_sys();
+              for (int i = 0; i < n_pend; ++i)
+                red_relaxed_sys_add(cm.g.signals[pend_owner[i]] + cm.slot_done + pend_block[i], 1u);
+              n_pend = 0;
+            }
+            pend_owner[n_pend] = owner;
+            pend_block[n_pend] = (m0 - owner * cm.rows_per_chunk) / BM;
+            ++n_pend;
+          } else {
+            red_release_sys_add(cm.g.signals[owner] + cm.slot_done + (m0 - owner * cm.rows_per_chunk) / BM, 1u);
           }
-          fence_sys();
-          red_release_sys_add(cm.g.signals[owner] + cm.slot_done + (m0 - owner * cm.rows_per_chunk) / BM, 1u);
         }
       }
     }
     if (p.use_tma_store && lane == 0) tma_store_wait<0>();
+    if constexpr (COMM == COMM_RS) {
+      if (lane == 0 && n_pend > 0) {
+        fence_proxy_async_global();
+        fence_sys();
+        for (int i = 0; i < n_pend; ++i)
+          red_relaxed_sys_add(cm.g.signals[pend_owner[i]] + cm.slot_done + pend_block[i], 1u);
+      }
+    }
 
     if constexpr (COMM == COMM_RS) {
       // ---- reduce the local chunk: row blocks are dealt round-robin to the CTAs -------------
@@ -682,14 +748,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 8; ++j) sum[i][j] = 0.0f;
           const long long base_off = (long long)(rb * BM + r0) * p.ldc + c8;
-          for (int q = 0; q <= W; ++q) {
-            const __nv_bfloat16* src;
-            if (q < W) src = stage + q * slot_stride + base_off;
-            else if (cm.rs_residual) src = cm.rs_residual + base_off;
-            else break;
-            uint4 u[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) u[i] = *reinterpret_cast<const uint4*>(src + (long long)i * p.ldc);
+          // sources: the W staging slots, then the optional residual; two sources (16 independent
+          // 16-byte loads per lane) are in flight at a time
+          const int n_src = W + (cm.rs_residual ? 1 : 0);
+          auto src_ptr = [&](int q) {
+            return (q < W ? stage + q * slot_stride : cm.rs_residual) + base_off;
+          };
+          auto add_rows = [&](const uint4 (&u)[8]) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float2 f0 = unpack_bf16x2(u[i].x), f1 = unpack_bf16x2(u[i].y), f2 = unpack_bf16x2(u[i].z),
@@ -697,6 +762,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               sum[i][0] += f0.x; sum[i][1] += f0.y; sum[i][2] += f1.x; sum[i][3] += f1.y;
               sum[i][4] += f2.x; sum[i][5] += f2.y; sum[i][6] += f3.x; sum[i][7] += f3.y;
             }
+          };
+          int q = 0;
+          for (; q + 1 < n_src; q += 2) {
+            const __nv_bfloat16* s0 = src_ptr(q);
+            const __nv_bfloat16* s1 = src_ptr(q + 1);
+            uint4 u0[8], u1[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u0[i] = *reinterpret_cast<const uint4*>(s0 + (long long)i * p.ldc);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u1[i] = *reinterpret_cast<const uint4*>(s1 + (long long)i * p.ldc);
+            add_rows(u0);
+            add_rows(u1);
+          }
+          if (q < n_src) {
+            const __nv_bfloat16* s0 = src_ptr(q);
+            uint4 u0[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u0[i] = *reinterpret_cast<const uint4*>(s0 + (long long)i * p.ldc);
+            add_rows(u0);
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {

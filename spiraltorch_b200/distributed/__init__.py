@@ -1,5 +1,6 @@
 """Distributed training surface: rendezvous, training devices and the error vocabulary."""
-from .device import CpuDevice, DistributedDevice, MetricReduce, ProcessGroupDevice, TrainingDevice
+from .device import (CpuDevice, DistributedDevice, MetricReduce, NativeDistributedDevice, ProcessGroupDevice,
+                     TrainingDevice)
 from .rendezvous import (BufferLengthMismatch, CollectiveTimeout, DistributedError, DuplicateContribution,
                          DuplicateRank, EmptyWorldSize, NonFiniteInput, NonFiniteReduction, ParticipantLeft,
                          PeerTensorFailure, RankOutOfBounds, UnknownRank, WorldSizeMismatch, join)

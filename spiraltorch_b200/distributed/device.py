@@ -128,6 +128,64 @@ class DistributedDevice(TrainingDevice):
         return ck
 
 
+class NativeDistributedDevice(DistributedDevice):
+    """Thread-rank device whose all-reduce runs in the C++ host runtime on ``float32`` buffers
+    (``csrc/host/host_runtime.cpp``): the wait happens outside the interpreter lock, the sum is
+    accumulated in double precision, and the error vocabulary is the one of :mod:`rendezvous`."""
+
+    def __init__(self, group: str, rank: int, world_size: int):
+        from ..runtime.host import NativeRendezvous
+        self._native = NativeRendezvous(group, rank, world_size)
+        self._timeout = rdv.DEFAULT_COLLECTIVE_TIMEOUT
+        self.fail_mean_scale = None
+
+    def rank(self) -> int:
+        return self._native.rank
+
+    def world_size(self) -> int:
+        return self._native.world_size
+
+    def close(self) -> None:
+        self._native.close()
+
+    def _all_reduce(self, values: list[float]) -> list[float]:
+        t = torch.tensor(values, dtype=torch.float32)
+        self._native.all_reduce_sum_(t, self._timeout)
+        return t.tolist()
+
+    def synchronize_gradients(self, buffer: torch.Tensor) -> None:
+        flat = buffer.detach().reshape(-1).to("cpu", torch.float32).contiguous().clone()
+        self._native.all_reduce_sum_(flat, self._timeout)
+        ok = 1.0
+        try:
+            if self.fail_mean_scale is not None and self.fail_mean_scale():
+                raise RuntimeError("injected mean-scale failure")
+            flat /= self.world_size()
+            if not bool(torch.isfinite(flat).all()):
+                raise ValueError("non-finite mean")
+        except Exception:  # noqa: BLE001
+            ok = 0.0
+        ready = torch.tensor([ok], dtype=torch.float32)
+        self._native.all_reduce_sum_(ready, self._timeout)
+        if ready.item() < self.world_size():
+            raise PeerTensorFailure(failed_ranks=int(self.world_size() - ready.item()), world_size=self.world_size())
+        buffer.copy_(flat.reshape(buffer.shape).to(buffer.dtype))
+
+    def aggregate_metrics(self, buffer: torch.Tensor, reduce: MetricReduce = MetricReduce.MEAN) -> None:
+        flat = buffer.detach().reshape(-1).to("cpu", torch.float32).contiguous().clone()
+        self._native.all_reduce_sum_(flat, self._timeout)
+        if reduce is MetricReduce.MEAN:
+            flat /= self.world_size()
+        buffer.copy_(flat.reshape(buffer.shape).to(buffer.dtype))
+
+    def checkpoint(self) -> dict:
+        ck = TrainingDevice.checkpoint(self)
+        ck["provider"] = "spiral_selfsup.distributed"
+        ck["state"] = {"group_id": self._native.group_id, "strategy": "all_reduce_mean",
+                       "collective_timeout_nanos": str(int(self._timeout * 1e9))}
+        return ck
+
+
 class ProcessGroupDevice(TrainingDevice):
     """Process-rank device over ``torch.distributed`` with the same all-or-nothing contract."""
 

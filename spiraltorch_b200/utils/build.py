@@ -121,6 +121,43 @@ def build_native(force: bool = False, verbose: bool = False, jobs: int | None = 
     return LIB_PATH
 
 
+HOST_LIB_PATH = NATIVE_DIR / "libst_host.so"
+HOST_STAMP_PATH = NATIVE_DIR / "libst_host.stamp"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-fvisibility=hidden", "-Wall"]
+
+
+def host_sources() -> list[Path]:
+    return sorted((CSRC / "host").glob("*.cpp"))
+
+
+def _host_hash() -> str:
+    h = hashlib.sha256()
+    for p in host_sources():
+        h.update(p.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()
+
+
+def build_host(force: bool = False) -> Path:
+    """Compile the CUDA-free host runtime (worker pool, rendezvous, loader) with the C++ compiler."""
+    if not force and HOST_LIB_PATH.exists() and HOST_STAMP_PATH.exists() and \
+            HOST_STAMP_PATH.read_text().strip() == _host_hash():
+        return HOST_LIB_PATH
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("no C++ compiler found: cannot build the host runtime")
+    NATIVE_DIR.mkdir(parents=True, exist_ok=True)
+    tmp = HOST_LIB_PATH.with_suffix(".so.tmp")
+    cmd = [cxx, *HOST_FLAGS, *[str(s) for s in host_sources()], "-o", str(tmp)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"host runtime build failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp, HOST_LIB_PATH)
+    HOST_STAMP_PATH.write_text(_host_hash())
+    return HOST_LIB_PATH
+
+
 if __name__ == "__main__":
+    print(build_host(force="--force" in sys.argv))
     path = build_native(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)

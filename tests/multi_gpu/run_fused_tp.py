@@ -183,21 +183,52 @@ def main():
 
     sec.run("info_nce", sec_info_nce)
     def sec_bench():
-        if big:
-            T, d, F = 16384, 2048, 8192 // world
-            xs = torch.randn(T // world, d, device=dev).bfloat16()
-            w1 = torch.randn(F, d, device=dev).bfloat16()
-            af = torch.randn(T, F, device=dev).bfloat16()
-            w2 = torch.randn(d, F, device=dev).bfloat16()
+        if not big:
+            return
+        import json
+        peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                                  "MEASURED_PEAKS.json")
+        tf_peak = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+        link_gbs = 770.0                      # measured peer copy bandwidth per direction
+        T, d = int(os.environ.get("ST_FUSED_BENCH_T", "16384")), 2048
+        # the four tensor-parallel linears of the 1.3B model at this world size
+        ag_shapes = [("qkv", 6144 // world), ("ffn1", 8192 // world)]
+        rs_shapes = [("attn_out", 2048 // world), ("ffn2", 8192 // world)]
+        xs = torch.randn(T // world, d, device=dev).bfloat16()
+        gathered = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        t_ag = timed(lambda: dist.all_gather_into_tensor(gathered, xs))
+        for name, N in ag_shapes:
+            w1 = torch.randn(N, d, device=dev).bfloat16()
             t_n = timed(lambda: nccl.ag_gemm(xs, w1))
             t_f = timed(lambda: fused.ag_gemm(xs, w1, key="bench"))
-            t_g = timed(lambda: G.gemm(af[:, :d].contiguous() if False else torch.empty(0, device=dev), w1) if False else G.gemm(fused._gather_buffer("bench", T, d).tensor.view(T, d), w1))
+            t_g = timed(lambda: G.gemm(gathered, w1))
+            flops = 2.0 * T * N * d
+            nv_bytes = T * d * 2 * (world - 1) / world
+            roof = max(flops / tf_peak / 1e9, nv_bytes / link_gbs / 1e6)       # ms
+            if rank == 0:
+                print(json.dumps({"op": "ag_gemm", "layer": name, "world": world, "T": T, "K": d, "N": N,
+                                  "fused_ms": round(t_f, 4), "nccl_plus_gemm_ms": round(t_n, 4),
+                                  "gemm_only_ms": round(t_g, 4), "nccl_all_gather_ms": round(t_ag, 4),
+                                  "roofline_ms": round(roof, 4), "frac_of_roofline": round(roof / t_f, 3),
+                                  "speedup_vs_nccl": round(t_n / t_f, 3)}), flush=True)
+        part = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        shard = torch.empty(T // world, d, device=dev, dtype=torch.bfloat16)
+        t_rs = timed(lambda: dist.reduce_scatter_tensor(shard, part))
+        for name, Kl in rs_shapes:
+            af = torch.randn(T, Kl, device=dev).bfloat16()
+            w2 = torch.randn(d, Kl, device=dev).bfloat16()
             r_n = timed(lambda: nccl.gemm_rs(af, w2))
             r_f = timed(lambda: fused.gemm_rs(af, w2))
             r_g = timed(lambda: G.gemm(af, w2))
+            flops = 2.0 * T * d * Kl
+            nv_bytes = T * d * 2 * (world - 1) / world
+            roof = max(flops / tf_peak / 1e9, nv_bytes / link_gbs / 1e6)
             if rank == 0:
-                print(f"AG->GEMM T{T} K{d} N{F}: nccl+gemm {t_n:.3f} ms, fused {t_f:.3f} ms, gemm only {t_g:.3f} ms", flush=True)
-                print(f"GEMM->RS T{T} K{F} N{d}: gemm+nccl {r_n:.3f} ms, fused {r_f:.3f} ms, gemm only {r_g:.3f} ms", flush=True)
+                print(json.dumps({"op": "gemm_rs", "layer": name, "world": world, "T": T, "K": Kl, "N": d,
+                                  "fused_ms": round(r_f, 4), "gemm_plus_nccl_ms": round(r_n, 4),
+                                  "gemm_only_ms": round(r_g, 4), "nccl_reduce_scatter_ms": round(t_rs, 4),
+                                  "roofline_ms": round(roof, 4), "frac_of_roofline": round(roof / r_f, 3),
+                                  "speedup_vs_nccl": round(r_n / r_f, 3)}), flush=True)
 
     sec.run("bench", sec_bench)
     dist.barrier()

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import spiraltorch as st
-from spiraltorch_b200.distributed import (BufferLengthMismatch, CollectiveTimeout, CpuDevice, DistributedDevice,
+from spiraltorch_b200.distributed import (BufferLengthMismatch, CollectiveTimeout, CpuDevice, DistributedDevice, NativeDistributedDevice,
                                           DuplicateContribution, DuplicateRank, EmptyWorldSize, MetricReduce,
                                           NonFiniteInput, NonFiniteReduction, ParticipantLeft, PeerTensorFailure,
                                           RankOutOfBounds, WorldSizeMismatch, join)
@@ -143,7 +143,8 @@ def test_duplicate_contribution_is_rejected_without_aborting_the_round():
     b.close()
 
 
-def test_distributed_device_mean_and_two_phase_commit():
+@pytest.mark.parametrize("DistributedDevice", [DistributedDevice, NativeDistributedDevice])
+def test_distributed_device_mean_and_two_phase_commit(DistributedDevice):
     devs = [DistributedDevice("g-dev", r, 2).with_collective_timeout(5) for r in range(2)]
     bufs = [torch.tensor([1.0, 3.0]), torch.tensor([3.0, 5.0])]
     _, errs = _run(2, lambda r: devs[r].synchronize_gradients(bufs[r]))
@@ -165,7 +166,8 @@ def test_distributed_device_mean_and_two_phase_commit():
     assert CpuDevice().world_size() == 1
 
 
-def test_two_rank_trainer_step_equals_local_step_on_averaged_gradient():
+@pytest.mark.parametrize("DistributedDevice", [DistributedDevice, NativeDistributedDevice])
+def test_two_rank_trainer_step_equals_local_step_on_averaged_gradient(DistributedDevice):
     """crates/spiral-selfsup/tests/module_trainer_accumulators.rs:83-115."""
     xs = [st.Tensor.randn(4, 3, seed=10 + r) for r in range(2)]
     ys = [st.Tensor.randn(4, 2, seed=20 + r) for r in range(2)]
