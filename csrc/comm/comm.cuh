@@ -12,6 +12,11 @@ namespace st {
 
 constexpr int kMaxRanks = 8;
 
+// Plain system-scope store: for flags written after one fence_sys() (the fence orders everything
+// before it; W release stores would each pay their own fence and serialise ~3 us apiece).
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -92,7 +97,7 @@ struct PeerGroup {
 // with room for `world` words.
 __device__ __forceinline__ bool peer_barrier(const PeerGroup& g, int slot_base) {
   fence_sys();
-  for (int p = 0; p < g.world; ++p) st_release_sys(g.signals[p] + slot_base + g.rank, g.epoch);
+  for (int p = 0; p < g.world; ++p) st_relaxed_sys(g.signals[p] + slot_base + g.rank, g.epoch);
   for (int p = 0; p < g.world; ++p)
     if (!wait_flag_ge(g.signals[g.rank] + slot_base + p, g.epoch)) return false;
   return true;

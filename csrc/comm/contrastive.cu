@@ -75,7 +75,7 @@ info_nce_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       if (cta == 0) {
         fence_sys();
-        for (int q = 0; q < W; ++q) st_release_sys(p.g.signals[q] + p.slot_enter + Rk, p.g.epoch);
+        for (int q = 0; q < W; ++q) st_relaxed_sys(p.g.signals[q] + p.slot_enter + Rk, p.g.epoch);
       }
       for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(p.g.signals[Rk] + p.slot_enter + q, p.g.epoch);
       s_ok = ok ? 1 : 0;

@@ -52,7 +52,7 @@ dp_step_kernel(const DpStepArgs a) {
     if (W > 1) {
       if (blockIdx.x == 0) {
         fence_sys();
-        for (int p = 0; p < W; ++p) st_release_sys(a.g.signals[p] + a.slot_enter + R, a.g.epoch);
+        for (int p = 0; p < W; ++p) st_relaxed_sys(a.g.signals[p] + a.slot_enter + R, a.g.epoch);
       }
       for (int p = 0; p < W && ok; ++p) ok = wait_flag_ge(a.g.signals[R] + a.slot_enter + p, a.g.epoch);
     }
@@ -142,7 +142,7 @@ dp_step_kernel(const DpStepArgs a) {
       if (done == gridDim.x - 1) {
         *a.cta_counter = 0;  // every CTA of this launch has already counted itself
         fence_sys();
-        for (int p = 0; p < W; ++p) st_release_sys(a.g.signals[p] + a.slot_exit + R, a.g.epoch);
+        for (int p = 0; p < W; ++p) st_relaxed_sys(a.g.signals[p] + a.slot_exit + R, a.g.epoch);
       }
       for (int p = 0; p < W && ok; ++p) ok = wait_flag_ge(a.g.signals[R] + a.slot_exit + p, a.g.epoch);
     }

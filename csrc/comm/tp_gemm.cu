@@ -81,7 +81,18 @@ struct StAgGemmArgs {
   int sub_per_chunk;   // arrival-flag granularity per rank shard
   int comm_ctas;       // CTAs that only push (taken from the SM budget)
   int slot_enter, slot_arrive;
+  unsigned arrive_target;  // peer-store path: this launch's epoch; multicast path: cumulative arrivals
+                           // (launches so far * st_ag_arrivals_per_launch) of the counter area
+  unsigned long long trace;  // optional device buffer of [grid][4] 64-bit time stamps, or 0
 };
+
+// Communication CTAs a launch really uses (= arrivals each sub-chunk counter receives per launch
+// on the multicast path).
+ST_API int st_ag_arrivals_per_launch(int comm_ctas) {
+  int sms = st::sm_count();
+  if (sms <= 0) sms = 148;
+  return comm_ctas > sms / 2 ? sms / 2 : comm_ctas;
+}
 
 ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   if (!a) return st::fail(ST_ERR_INVALID, "ag_gemm: null args");
@@ -116,6 +127,9 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   cm.sub_per_chunk = a->sub_per_chunk;
   cm.slot_enter = a->slot_enter;
   cm.slot_arrive = a->slot_arrive;
+  cm.arrive_target = a->arrive_target;
+  cm.trace = reinterpret_cast<unsigned long long*>(a->trace);
+  cm.sub_major = a->gather_mc ? 1 : 0;   // multicast delivers sub-chunk s of every rank at the same time
   cm.src_shard = reinterpret_cast<const __nv_bfloat16*>(a->x_shard);
   for (int i = 0; i < st::kMaxRanks; ++i) cm.gather_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->gather_peers[i]);
   cm.gather_mc = reinterpret_cast<__nv_bfloat16*>(a->gather_mc);
@@ -164,6 +178,9 @@ struct StGemmRsArgs {
   float alpha;
   int slot_enter, slot_done;
   unsigned done_target;                          // cumulative warp arrivals expected per row block
+  unsigned long long stage_mc;                   // multicast alias of the staging area or 0: when set,
+                                                 // partial tiles stay local and owners pull the sum
+  unsigned long long trace;                      // optional [grid][4] 64-bit time stamps, or 0
 };
 
 ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
@@ -203,7 +220,20 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
   memset(&tmC, 0, sizeof(tmC));
   p.use_tma_store = 1;
   const int rows = a->T / W;
-  for (int q = 0; q < W; ++q) {
+  cm.stage_mc = reinterpret_cast<const __nv_bfloat16*>(a->stage_mc);
+  cm.rs_pull = a->stage_mc ? 1 : 0;
+  cm.trace = reinterpret_cast<unsigned long long*>(a->trace);
+  if (cm.rs_pull) {
+    // one map over this rank's whole staging buffer [T, N]
+    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)a->T, 1};
+    uint64_t strides[2] = {(uint64_t)a->N * 2, (uint64_t)a->N * 2 * a->T};
+    uint32_t box[3] = {64, 32, 1};
+    if (!encode_tmap(&tmC.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                     reinterpret_cast<const void*>(a->stage_peers[a->g.rank]), dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return ST_ERR_CUDA;
+  }
+  for (int q = 0; q < W && !cm.rs_pull; ++q) {
     // this rank's slot inside owner q's staging area
     const char* base = reinterpret_cast<const char*>(a->stage_peers[q]) + (size_t)a->g.rank * rows * a->N * 2;
     uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)rows, 1};

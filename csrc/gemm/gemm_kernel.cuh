@@ -43,12 +43,20 @@ struct GemmComm {
   const __nv_bfloat16* src_shard;          // [rows_per_chunk, K] contiguous
   __nv_bfloat16* gather_peers[kMaxRanks];  // [T, K] contiguous on every rank
   __nv_bfloat16* gather_mc;                // multicast alias or null
-  int slot_arrive;      // arrival flags (epoch valued): slot_arrive + src * kMaxSubChunks + sub
+  int slot_arrive;      // arrival words: slot_arrive + src * kMaxSubChunks + sub
+  unsigned arrive_target;  // value an arrival word must reach: the epoch (peer-store path, one
+                           // writer per word) or a cumulative count (multicast path, n_comm writers)
+  unsigned long long* trace;  // optional [gridDim.x][4] globaltimer stamps (start, entry, tiles/push done, end)
+  int sub_major;        // tile order of the remote chunks: 0 chunk by chunk (ring), 1 sub-chunk by sub-chunk
   // ---- RS ----
   __nv_bfloat16* stage_peers[kMaxRanks];   // on each owner: [world][rows_per_chunk, N]
   int slot_done;        // counters: slot_done + row block within the chunk
   unsigned done_target; // counter value meaning "every rank's tiles of this row block landed"
   __nv_bfloat16* rs_out;                   // [rows_per_chunk, N] reduced local shard
+  const __nv_bfloat16* stage_mc;           // RS pull mode: multicast alias of the [T, N] staging
+  int rs_pull;          // 0: partial tiles are stored into the owner's staging slots and summed by the
+                        //    owner; 1: partial tiles stay in local staging [T, N] and the owner reads
+                        //    its rows through the multicast alias (summed in the switch, fp32)
   const __nv_bfloat16* rs_residual;        // optional, added during the reduction
 };
 
@@ -128,6 +136,19 @@ __device__ __forceinline__ void map_tile(int t, int tiles_m, int tiles_n, int ti
     b = 0;
     const int tiles_m_chunk = c.rows_per_chunk / BM;
     const int per_chunk = tiles_m_chunk * tiles_n;
+    if (COMM == COMM_AG && c.sub_major && t >= per_chunk) {
+      // remote rows: for every sub-chunk index, the W-1 remote chunks in ring order
+      const int msub = tiles_m_chunk / c.sub_per_chunk;       // M tiles per sub-chunk
+      const int per_sub = msub * tiles_n;
+      const int r = t - per_chunk;
+      const int blk = r / per_sub;
+      const int s = blk / (c.g.world - 1);
+      const int ci = 1 + blk % (c.g.world - 1);
+      const int rr = r - blk * per_sub;
+      tn = rr / msub;
+      tm = ((c.g.rank + ci) % c.g.world) * tiles_m_chunk + s * msub + rr % msub;
+      return;
+    }
     const int ci = t / per_chunk;
     int lm;
     tile_coords(t - ci * per_chunk, tiles_m_chunk, tiles_n, lm, tn);
@@ -178,10 +199,78 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         s_finished = 0;
       }
       __syncthreads();
-      if (threadIdx.x != 0 && threadIdx.x != 32) return;
       const int W = cm.g.world, R = cm.g.rank;
       const int cta = blockIdx.x;
       const int SUBS = cm.sub_per_chunk;
+      if (cm.gather_mc) {
+        // ---- NVLS path: one multimem.st reaches every rank's gather buffer, so this GPU sends
+        // its shard once.  Every communication CTA stores the same 1/n_comm slice of each
+        // sub-chunk (warps 0-4); warp 5 lane 0 counts the arrivals on every rank once the five
+        // data warps have stored their part, so the data warps never wait for a fence.
+        __shared__ int s_cnt[kMaxSubChunks];
+        __shared__ int s_enter_ok;
+        if (threadIdx.x < kMaxSubChunks) s_cnt[threadIdx.x] = 0;
+        if (threadIdx.x == 0) {
+          bool ok = true;
+          if (cta == 0) {
+            fence_sys();
+            for (int q = 0; q < W; ++q) st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
+          }
+          for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
+          if (!ok) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
+          s_enter_ok = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (!s_enter_ok) return;
+        constexpr int DATA_WARPS = 5, DT = DATA_WARPS * 32, U = 8;
+        const long long vecs = (long long)(cm.rows_per_chunk / SUBS) * p.K / 8;     // 16-byte vectors per sub-chunk
+        const long long slice = (vecs + n_comm - 1) / n_comm;
+        const long long lo = min(vecs, (long long)cta * slice), hi = min(vecs, lo + slice);
+        if (warp < DATA_WARPS) {
+          const uint4* src0 = reinterpret_cast<const uint4*>(cm.src_shard);
+          uint4* dst0 = reinterpret_cast<uint4*>(cm.gather_mc) + (long long)R * cm.rows_per_chunk * p.K / 8;
+          for (int sc = 0; sc < SUBS; ++sc) {
+            const uint4* src = src0 + sc * vecs;
+            uint4* dst = dst0 + sc * vecs;
+            for (long long i0 = lo + threadIdx.x; i0 < hi; i0 += (long long)DT * U) {
+              uint4 v[U];
+#pragma unroll
+              for (int u = 0; u < U; ++u)
+                if (i0 + (long long)u * DT < hi) v[u] = src[i0 + (long long)u * DT];
+#pragma unroll
+              for (int u = 0; u < U; ++u)
+                if (i0 + (long long)u * DT < hi) multimem_st_v4(dst + i0 + (long long)u * DT, v[u]);
+            }
+            __syncwarp();
+            if (lane == 0) {
+              __threadfence_block();
+              atomicAdd(&s_cnt[sc], 1);
+            }
+          }
+        } else if (lane == 0) {
+          bool ok = true;
+          for (int sc = 0; sc < SUBS && ok; ++sc) {
+            const uint64_t t0 = globaltimer_ns();
+            while (*reinterpret_cast<volatile int*>(&s_cnt[sc]) < DATA_WARPS) {
+              if (globaltimer_ns() - t0 > ST_WAIT_TIMEOUT_NS) { ok = false; break; }
+              __nanosleep(32);
+            }
+            if (!ok) break;
+            __threadfence_block();
+            fence_sys();
+            for (int q = 0; q < W; ++q)
+              red_relaxed_sys_add(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * kMaxSubChunks + sc, 1u);
+          }
+          if (!ok) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA605u);
+          // words of sub-chunk slots this shape does not use advance too: one cumulative target
+          // then serves every shape launched through this signal area
+          for (int sc = SUBS; sc < kMaxSubChunks && ok; ++sc)
+            for (int q = 0; q < W; ++q)
+              red_relaxed_sys_add(cm.g.signals[q] + cm.slot_arrive + R * kMaxSubChunks + sc, 1u);
+        }
+        return;
+      }
+      if (threadIdx.x != 0 && threadIdx.x != 32) return;
       const int items = W * SUBS;
       const int my_items = (items - cta + n_comm - 1) / n_comm;     // items cta, cta + n_comm, ...
       auto dest_of = [&](int item) {
@@ -201,7 +290,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (; sent < d; ++sent) {
               const int item = cta + sent * n_comm;
               st_release_sys(cm.g.signals[dest_of(item)] + cm.slot_arrive + R * kMaxSubChunks + item % SUBS,
-                             cm.g.epoch);
+                             cm.arrive_target);
             }
           }
           if (sent >= my_items || (fin && sent >= s_done_items)) break;
@@ -212,9 +301,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // ---- copy thread ----
       bool ok = true;
+      if (cm.trace) cm.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
       if (cta == 0) {
         fence_sys();
-        for (int q = 0; q < W; ++q) st_release_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
+        for (int q = 0; q < W; ++q) st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
       }
       // peers must have left the previous launch that read this gather buffer
       for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
@@ -223,9 +313,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         s_finished = 1;
         return;
       }
-      constexpr int NB = 6;            // ring buffers
-      constexpr int LAG = 4;           // stores that may still be in flight when older ones are published
-      constexpr uint32_t CH = 32768;
+      if (cm.trace) cm.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
+      constexpr int NB = 12;           // ring buffers
+      constexpr int LOADS = 6;         // bulk loads kept in flight; the other NB - LOADS buffers may
+                                       // be held by stores that are still being read
+      constexpr int LAG = 16;          // newest stores that may be incomplete when older ones are published
+      constexpr uint32_t CH = 16384;
       const long long sub_bytes = (long long)(cm.rows_per_chunk / SUBS) * p.K * 2;
       const int n_ch = (int)((sub_bytes + CH - 1) / CH);            // chunks per item
       uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + NB * CH);
@@ -251,7 +344,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
         bulk_load_g2s(smem_u32(smem + b * CH), src_base + off, sz, smem_u32(&cbar[b]));
       };
-      for (int c = 0; c < total && c < NB; ++c) issue_load(c);
+      for (int c = 0; c < total && c < LOADS; ++c) issue_load(c);
       uint32_t phase_bits = 0;
       for (int c = 0; c < total; ++c) {
         const int b = c % NB;
@@ -263,10 +356,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[dest_of(item)]) + dst_base + off,
                        smem_u32(smem + b * CH), sz);
         tma_store_commit();
-        // the buffer of the previous chunk may be refilled once its store has read it
-        if (c >= 1 && c - 1 + NB < total) {
-          tma_store_wait_read<1>();
-          issue_load(c - 1 + NB);
+        // chunk c + LOADS goes into the buffer last used by chunk c + LOADS - NB: all but the
+        // newest NB - LOADS store groups must have finished reading shared memory
+        if (c + LOADS < total) {
+          tma_store_wait_read<NB - LOADS>();
+          issue_load(c + LOADS);
         }
         if (c >= LAG) {
           tma_store_wait<LAG>();        // every store up to chunk c - LAG is complete
@@ -286,6 +380,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __threadfence_block();
         s_done_items = my_items;
       }
+      if (cm.trace) cm.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
       s_finished = 1;
       return;
     }
@@ -326,7 +421,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (blockIdx.x == 0) {
         fence_sys();
         for (int q = 0; q < cm.g.world; ++q)
-          st_release_sys(cm.g.signals[q] + cm.slot_enter + cm.g.rank, cm.g.epoch);
+          st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + cm.g.rank, cm.g.epoch);
       }
     }
   }
@@ -359,7 +454,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mapA = &tmA_local;
             m_coord = m0 - src * cm.rows_per_chunk;
           } else if (!wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_arrive + src * kMaxSubChunks + sub,
-                                   cm.g.epoch)) {
+                                   cm.arrive_target)) {
             *abort_flag = 1;
             report_error(p.err, ERR_FLAG_TIMEOUT, 0xA601u);
             break;
@@ -471,6 +566,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int kPubBatch = 3;
     int pend_owner[kPubBatch], pend_block[kPubBatch], n_pend = 0;   // RS: tiles stored, not yet published
     bool alive = true;
+    const bool tracer = (COMM != COMM_NONE) && cm.trace && quad == 2 && lane == 0;   // warp 2
+    if (tracer) cm.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
     if constexpr (COMM == COMM_RS) {
       // peers' staging areas are free once every peer has entered this launch
       bool ok = true;
@@ -483,6 +580,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA602u);
       }
     }
+    if (tracer) cm.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
     for (int t = gemm_bid; t < total_tiles && alive; t += grid_stride, ++iter) {
       int b, tm, tn;
       map_tile<COMM>(t, tiles_m, tiles_n, tiles_per_batch, cm, b, tm, tn);
@@ -500,8 +598,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int owner = 0;
       if constexpr (COMM == COMM_RS) {
         owner = m0 / cm.rows_per_chunk;
-        c_ptr = cm.stage_peers[owner];
-        c_base = ((long long)cm.g.rank * cm.rows_per_chunk + (row - owner * cm.rows_per_chunk)) * p.ldc;
+        if (cm.rs_pull) {
+          c_ptr = cm.stage_peers[cm.g.rank];
+          c_base = (long long)row * p.ldc;
+        } else {
+          c_ptr = cm.stage_peers[owner];
+          c_base = ((long long)cm.g.rank * cm.rows_per_chunk + (row - owner * cm.rows_per_chunk)) * p.ldc;
+        }
       }
       // TMA mode: after the second half of a 64-column chunk (or the last valid half) one lane
       // hands the warp's staged 32 x 64 block to the copy engine
@@ -510,8 +613,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          const CUtensorMap* om = &tmC.m[COMM == COMM_RS ? owner : 0];
-          const int r0 = (COMM == COMM_RS ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
+          const bool to_owner = (COMM == COMM_RS) && !cm.rs_pull;
+          const CUtensorMap* om = &tmC.m[to_owner ? owner : 0];
+          const int r0 = (to_owner ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
           tma_store_3d(om, smem_u32(smem + L::CSTAGE_OFFSET + (quad * 2 + (store_seq & 1)) * 4096),
                        n0 + (c >> 1) * 64, r0, b);
           tma_store_commit();
@@ -707,6 +811,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (p.use_tma_store && lane == 0) tma_store_wait<0>();
+    if (tracer) cm.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
     if constexpr (COMM == COMM_RS) {
       if (lane == 0 && n_pend > 0) {
         fence_proxy_async_global();
@@ -740,6 +845,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         if (c8 >= p.N) continue;
+        if (cm.rs_pull) {
+          // every rank's partial rows sit at the same offset of its staging buffer: one
+          // multimem.ld_reduce returns their fp32 sum (rounded to bf16 once) through the switch
+          const __nv_bfloat16* mc = cm.stage_mc + ((long long)R * cm.rows_per_chunk + rb * BM) * p.ldc + c8;
+          const long long out_off = (long long)(rb * BM) * p.ldc + c8;
+#pragma unroll 1
+          for (int r0 = ew * 32; r0 < ew * 32 + 32; r0 += 16) {
+            uint4 u[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) u[i] = multimem_ld_reduce_bf16x8(mc + (long long)(r0 + i) * p.ldc);
+            if (cm.rs_residual) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(cm.rs_residual + out_off + (long long)(r0 + i) * p.ldc);
+                float2 a0 = unpack_bf16x2(u[i].x), a1 = unpack_bf16x2(u[i].y), a2 = unpack_bf16x2(u[i].z),
+                       a3 = unpack_bf16x2(u[i].w);
+                float2 b0 = unpack_bf16x2(rv.x), b1 = unpack_bf16x2(rv.y), b2 = unpack_bf16x2(rv.z),
+                       b3 = unpack_bf16x2(rv.w);
+                u[i].x = pack_bf16x2(a0.x + b0.x, a0.y + b0.y);
+                u[i].y = pack_bf16x2(a1.x + b1.x, a1.y + b1.y);
+                u[i].z = pack_bf16x2(a2.x + b2.x, a2.y + b2.y);
+                u[i].w = pack_bf16x2(a3.x + b3.x, a3.y + b3.y);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              *reinterpret_cast<uint4*>(cm.rs_out + out_off + (long long)(r0 + i) * p.ldc) = u[i];
+          }
+          continue;
+        }
 #pragma unroll 1
         for (int r0 = ew * 32; r0 < ew * 32 + 32; r0 += 8) {
           float sum[8][8];
@@ -795,6 +930,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------- teardown -------------------------------------------
+  if constexpr (COMM != COMM_NONE) {
+    if (cm.trace && threadIdx.x == 64) cm.trace[blockIdx.x * 4 + 3] = globaltimer_ns();
+  }
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {

@@ -49,7 +49,8 @@ class _AgGemmArgs(ctypes.Structure):
                 ("T", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
                 ("b_mn", ctypes.c_int), ("act", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("sub_per_chunk", ctypes.c_int), ("comm_ctas", ctypes.c_int),
-                ("slot_enter", ctypes.c_int), ("slot_arrive", ctypes.c_int)]
+                ("slot_enter", ctypes.c_int), ("slot_arrive", ctypes.c_int), ("arrive_target", ctypes.c_uint),
+                ("trace", ctypes.c_ulonglong)]
 
 
 class _GemmRsArgs(ctypes.Structure):
@@ -58,7 +59,8 @@ class _GemmRsArgs(ctypes.Structure):
                 ("residual", ctypes.c_ulonglong), ("lda", ctypes.c_longlong), ("ldb", ctypes.c_longlong),
                 ("T", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn", ctypes.c_int),
                 ("alpha", ctypes.c_float), ("slot_enter", ctypes.c_int), ("slot_done", ctypes.c_int),
-                ("done_target", ctypes.c_uint)]
+                ("done_target", ctypes.c_uint), ("stage_mc", ctypes.c_ulonglong),
+                ("trace", ctypes.c_ulonglong)]
 
 
 class _DpStepArgs(ctypes.Structure):
@@ -155,17 +157,28 @@ class PeerSignals:
 class FusedTPContext(TPContext):
     """Tensor-parallel context whose column-/row-parallel linears run as fused kernels."""
 
-    def __init__(self, group: Optional[dist.ProcessGroup], device=None, comm_ctas: int = 12,
+    def __init__(self, group: Optional[dist.ProcessGroup], device=None, comm_ctas: Optional[int] = None,
                  sub_per_chunk: int = 16):
         super().__init__(group, mode="fused")
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = device
         self.heap = SymmetricHeap(group, device)
         self.signals = PeerSignals(self.heap)
+        if comm_ctas is None:
+            # one CTA sustains about 40 GB/s of peer writes through its shared-memory ring, and the
+            # bytes a rank must send grow with (world-1)/world while its GEMM share shrinks
+            env = os.environ.get("ST_TP_COMM_CTAS")
+            comm_ctas = int(env) if env else {1: 4, 2: 12, 3: 16, 4: 16}.get(self.world, 24)
         self.comm_ctas = comm_ctas
         self.sub_per_chunk = sub_per_chunk
         self.slot_enter = self.signals.alloc(MAX_RANKS)
-        self.slot_arrive = self.signals.alloc(MAX_RANKS * 16)
+        self.slot_arrive = self.signals.alloc(MAX_RANKS * 16)       # epoch-valued flags (peer-store path)
+        self.slot_arrive_cnt = self.signals.alloc(MAX_RANKS * 16)   # cumulative counters (multicast path)
+        self._ag_arrivals = 0
+        # NVLS variants (multimem.st push, multimem.ld_reduce pull) are correct but measured slower
+        # than the peer-store paths at 4 GPUs; they stay opt-in
+        self.use_nvls = os.environ.get("ST_TP_NVLS", "0") == "1"
+        self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
         self._stage: dict = {}
@@ -206,7 +219,7 @@ class FusedTPContext(TPContext):
         a.g = self.signals.next_group()
         a.x_shard = x_shard.data_ptr()
         a.gather_peers = gbuf.peers_array()
-        a.gather_mc = gbuf.mc()
+        a.gather_mc = gbuf.mc() if (self.use_nvls and self.world > 1) else 0
         a.B, a.C = w.data_ptr(), y.data_ptr()
         a.bias = 0 if bias is None else bias.data_ptr()
         a.aux_out = 0 if aux_out is None else aux_out.data_ptr()
@@ -219,7 +232,13 @@ class FusedTPContext(TPContext):
         a.act = gemm_ops._ACT_NAMES[act]
         a.alpha = alpha
         a.sub_per_chunk, a.comm_ctas = sub, self.comm_ctas
-        a.slot_enter, a.slot_arrive = self.slot_enter, self.slot_arrive
+        a.slot_enter = self.slot_enter
+        a.trace = 0 if self.trace is None else self.trace.data_ptr()
+        if a.gather_mc:
+            self._ag_arrivals += native.lib().st_ag_arrivals_per_launch(ctypes.c_int(self.comm_ctas))
+            a.slot_arrive, a.arrive_target = self.slot_arrive_cnt, self._ag_arrivals & 0xFFFFFFFF
+        else:
+            a.slot_arrive, a.arrive_target = self.slot_arrive, a.g.epoch
         native.check(native.lib().st_ag_gemm(ctypes.byref(a), native.stream_ptr(x_shard.device)), "st_ag_gemm")
         launch_count += 1
         self.bytes_gathered += T * K * 2
@@ -253,6 +272,8 @@ class FusedTPContext(TPContext):
         r.alpha = alpha
         r.slot_enter, r.slot_done = self.slot_enter, slot
         r.done_target = cum & 0xFFFFFFFF
+        r.stage_mc = sbuf.mc() if (self.use_nvls and self.world > 1) else 0
+        r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")
         launch_count += 1
         self.bytes_scattered += T * N * 2

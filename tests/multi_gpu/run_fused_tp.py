@@ -107,7 +107,9 @@ def main():
             err = rel(got, ref)
             assert err <= tol, (name, err)
 
-    sec.run("tp_kernels", sec_tp_kernels)
+    only_bench = os.environ.get("ST_FUSED_ONLY_BENCH", "0") == "1"
+    if not only_bench:
+        sec.run("tp_kernels", sec_tp_kernels)
     def sec_dp_step():
         # data-parallel bucket step against all-reduce-mean + AdamW
         n = 8 * world * 4096
@@ -130,7 +132,8 @@ def main():
         assert rel(wbuf.tensor, master) < 1e-2, rel(wbuf.tensor, master)
         assert grad.tensor.abs().max().item() == 0
 
-    sec.run("dp_step", sec_dp_step)
+    if not only_bench:
+        sec.run("dp_step", sec_dp_step)
     def sec_gpt():
         # small GPT step: fused vs NCCL context
         cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=8, ffn=1024, seq_len=512, init_std=0.05)
@@ -148,7 +151,8 @@ def main():
         r = ((ma.flat_grad - mb.flat_grad).norm() / ma.flat_grad.norm()).item()
         assert r < 3e-2, r
 
-    sec.run("gpt", sec_gpt)
+    if not only_bench:
+        sec.run("gpt", sec_gpt)
 
     def sec_info_nce():
         from spiraltorch_b200.parallel.contrastive import FusedInfoNCE
@@ -181,7 +185,8 @@ def main():
             assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
             assert rel(ga, gr) < 5e-2, rel(ga, gr)
 
-    sec.run("info_nce", sec_info_nce)
+    if not only_bench:
+        sec.run("info_nce", sec_info_nce)
     def sec_bench():
         if not big:
             return
@@ -190,10 +195,44 @@ def main():
                                   "MEASURED_PEAKS.json")
         tf_peak = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
         link_gbs = 770.0                      # measured peer copy bandwidth per direction
-        T, d = int(os.environ.get("ST_FUSED_BENCH_T", "16384")), 2048
+        for T in [int(v) for v in os.environ.get("ST_FUSED_BENCH_T", "16384").split(",")]:
+            for nvls in [int(v) for v in os.environ.get("ST_FUSED_BENCH_NVLS", "0").split(",")]:
+                fused.use_nvls = bool(nvls)
+                bench_one(T, nvls, tf_peak, link_gbs)
+
+    def trace_report(label, fn):
+        """One launch with per-CTA phase stamps: prints, for rank 0, when (relative to the first CTA's
+        start, in us) the slowest CTA finished each phase."""
+        if os.environ.get("ST_FUSED_TRACE", "0") != "1":
+            return
+        fused.trace = torch.zeros(160, 4, dtype=torch.int64, device=dev)
+        dist.barrier()
+        torch.cuda.synchronize()
+        fn()
+        torch.cuda.synchronize()
+        tr = fused.trace.cpu()
+        fused.trace = None
+        if rank == 0:
+            used = tr[tr[:, 0] > 0]
+            t0 = used[:, 0].min().item()
+            comm = used[used[:, 3] == 0]
+            gem = used[used[:, 3] > 0]
+            msg = f"TRACE {label}: "
+            if len(comm):
+                msg += (f"comm ctas {len(comm)} entry<= {(comm[:, 1].max().item() - t0) / 1e3:.1f} "
+                        f"push done {(comm[:, 2].min().item() - t0) / 1e3:.1f}..{(comm[:, 2].max().item() - t0) / 1e3:.1f}; ")
+            msg += (f"gemm ctas {len(gem)} start<= {(gem[:, 0].max().item() - t0) / 1e3:.1f} "
+                    f"entry<= {(gem[:, 1].max().item() - t0) / 1e3:.1f} "
+                    f"tiles done {(gem[:, 2].min().item() - t0) / 1e3:.1f}..{(gem[:, 2].max().item() - t0) / 1e3:.1f} "
+                    f"end {(gem[:, 3].min().item() - t0) / 1e3:.1f}..{(gem[:, 3].max().item() - t0) / 1e3:.1f}")
+            print(msg, flush=True)
+
+    def bench_one(T, nvls, tf_peak, link_gbs):
+        import json
+        d = 2048
         # the four tensor-parallel linears of the 1.3B model at this world size
-        ag_shapes = [("qkv", 6144 // world), ("ffn1", 8192 // world)]
-        rs_shapes = [("attn_out", 2048 // world), ("ffn2", 8192 // world)]
+        ag_shapes = [("qkv", 6144 // world), ("ffn1", 8192 // world), ("probe_push_only", 256)]
+        rs_shapes = [("attn_out", 2048 // world), ("ffn2", 8192 // world), ("probe_comm_only", 64)]
         xs = torch.randn(T // world, d, device=dev).bfloat16()
         gathered = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
         t_ag = timed(lambda: dist.all_gather_into_tensor(gathered, xs))
@@ -201,12 +240,13 @@ def main():
             w1 = torch.randn(N, d, device=dev).bfloat16()
             t_n = timed(lambda: nccl.ag_gemm(xs, w1))
             t_f = timed(lambda: fused.ag_gemm(xs, w1, key="bench"))
+            trace_report("ag_gemm " + name, lambda: fused.ag_gemm(xs, w1, key="bench"))
             t_g = timed(lambda: G.gemm(gathered, w1))
             flops = 2.0 * T * N * d
             nv_bytes = T * d * 2 * (world - 1) / world
             roof = max(flops / tf_peak / 1e9, nv_bytes / link_gbs / 1e6)       # ms
             if rank == 0:
-                print(json.dumps({"op": "ag_gemm", "layer": name, "world": world, "T": T, "K": d, "N": N,
+                print(json.dumps({"op": "ag_gemm", "nvls": nvls, "layer": name, "world": world, "T": T, "K": d, "N": N,
                                   "fused_ms": round(t_f, 4), "nccl_plus_gemm_ms": round(t_n, 4),
                                   "gemm_only_ms": round(t_g, 4), "nccl_all_gather_ms": round(t_ag, 4),
                                   "roofline_ms": round(roof, 4), "frac_of_roofline": round(roof / t_f, 3),
@@ -219,12 +259,13 @@ def main():
             w2 = torch.randn(d, Kl, device=dev).bfloat16()
             r_n = timed(lambda: nccl.gemm_rs(af, w2))
             r_f = timed(lambda: fused.gemm_rs(af, w2))
+            trace_report("gemm_rs " + name, lambda: fused.gemm_rs(af, w2))
             r_g = timed(lambda: G.gemm(af, w2))
             flops = 2.0 * T * d * Kl
             nv_bytes = T * d * 2 * (world - 1) / world
             roof = max(flops / tf_peak / 1e9, nv_bytes / link_gbs / 1e6)
             if rank == 0:
-                print(json.dumps({"op": "gemm_rs", "layer": name, "world": world, "T": T, "K": Kl, "N": d,
+                print(json.dumps({"op": "gemm_rs", "nvls": nvls, "layer": name, "world": world, "T": T, "K": Kl, "N": d,
                                   "fused_ms": round(r_f, 4), "gemm_plus_nccl_ms": round(r_n, 4),
                                   "gemm_only_ms": round(r_g, 4), "nccl_reduce_scatter_ms": round(t_rs, 4),
                                   "roofline_ms": round(roof, 4), "frac_of_roofline": round(roof / r_f, 3),

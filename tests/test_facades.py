@@ -1,0 +1,375 @@
+"""Host-side subsystems: telemetry hub, hyper-parameter search, soft logic / phase sync / refract
+lowering, compression, recommenders, RL agents, robotics runtime, safety policy, metric registry."""
+import math
+
+import pytest
+import torch
+
+from spiraltorch_b200 import compress, hpo, metrics, plugin, rec, rl, robotics, safety, softlogic, telemetry
+from spiraltorch_b200.nn.trainer import StepMetrics
+
+
+# ---- telemetry -----------------------------------------------------------------------------------
+def test_monitoring_hub_drift_and_regression_alerts():
+    prom = telemetry.PrometheusExporter()
+    seen = []
+    hub = telemetry.MonitoringHub(drift_threshold=3.0, drift_warmup=8, perf_warmup=8)
+    hub.with_exporter(prom).with_exporter(telemetry.CallbackExporter(lambda n, v, l: seen.append(n)))
+    g = torch.Generator().manual_seed(0)
+    for i in range(40):
+        x = 1.0 + 0.01 * float(torch.randn((), generator=g))
+        alerts = hub.observe(StepMetrics(10.0, 100.0, 0.0, {"grad_norm": x, "step_loss": 1.0}), reward=1.0)
+        assert not alerts, (i, alerts)
+    # the feature jumps far outside its frozen baseline; the loss regresses three steps in a row
+    kinds = []
+    for i in range(40):
+        for a in hub.observe(StepMetrics(10.0, 100.0, 0.0, {"grad_norm": 5.0, "step_loss": 3.0}), reward=1.0):
+            kinds.append((a.kind, a.severity))
+    assert ("feature_drift", "warning") in kinds and ("performance_regression", "critical") in kinds
+    assert hub.latest_alerts() and hub.last_observation() is not None
+    text = prom.render()
+    assert "# TYPE spiraltorch_runtime_step_time_ms gauge" in text
+    assert "spiraltorch_extra_grad_norm 5.0" in text and "spiraltorch_performance_step_loss 3.0" in text
+    assert "runtime_reward" in seen
+
+
+def test_monitoring_alerts_reach_plugin_bus_and_prometheus_file(tmp_path):
+    got = []
+    sid = plugin.subscribe("Telemetry", got.append)
+    hub = telemetry.MonitoringHub(2.0, 4, 4)
+    for v in [1.0, 1.01, 0.99, 1.0] + [9.0] * 40:
+        hub.observe(StepMetrics(extra={"f": v}))
+    plugin.unsubscribe("Telemetry", sid)
+    assert any(e.get("alert") == "feature_drift" for e in got)
+    ex = telemetry.PrometheusExporter("st")
+    ex.record_gauge("x", 1.5, [("rank", "0")])
+    ex.write(tmp_path / "metrics.prom")
+    assert 'st_x{rank="0"} 1.5' in (tmp_path / "metrics.prom").read_text()
+
+
+def test_chrono_timeline_and_step_timer():
+    tl = telemetry.ChronoTimeline(4)
+    for i in range(6):
+        f = tl.record(0.5, {"observed_curvature": -1.0 - 0.1 * i, "total_energy": 10.0 - i, "homotopy_energy": 2.0})
+    assert len(tl) == 4 and tl.latest().step == 5
+    assert abs(f.curvature_drift + 0.2) < 1e-6 and abs(f.energy_decay - 2.0) < 1e-6
+    assert abs(f.homotopy_ratio() - 2.0 / 5.0) < 1e-6
+    s = tl.summarise(3)
+    assert s.frames == 3 and s.min_energy == 5.0 and s.max_energy == 7.0 and abs(s.mean_drift + 0.2) < 1e-6
+    assert tl.rewind_steps(2) == 2 and tl.latest().step == 3
+    with telemetry.StepTimer("cpu") as t:
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    m = t.metrics(step_loss=0.5)
+    assert m.step_time_ms > 0 and m.extra == {"step_loss": 0.5}
+
+
+# ---- hpo -------------------------------------------------------------------------------------------
+def _space():
+    return hpo.SearchSpace([hpo.ParamSpec.Float("lr", 1e-4, 1e-1), hpo.ParamSpec.Int("layers", 1, 6),
+                            hpo.ParamSpec.Categorical("act", ["relu", "gelu"])])
+
+
+@pytest.mark.parametrize("make", [lambda: hpo.RandomStrategy(7), lambda: hpo.BayesianStrategy(7, 0.2),
+                                  lambda: hpo.PopulationStrategy(7, 4, 2, 0.5)])
+def test_search_loop_is_deterministic_and_resumable(make):
+    def run(loop, n):
+        out = []
+        for _ in range(n):
+            t = loop.suggest()
+            loop.space().validate_suggestion(t.suggestion)
+            loop.observe(t.id, (t.suggestion["lr"] - 0.01) ** 2 + 0.01 * t.suggestion["layers"])
+            out.append(t.suggestion)
+        return out
+
+    a = run(hpo.SearchLoop(_space(), make()), 12)
+    loop = hpo.SearchLoop(_space(), make())
+    first = run(loop, 5)
+    resumed = hpo.SearchLoop.from_state(_space(), loop.checkpoint())
+    assert first + run(resumed, 7) == a
+    best = resumed.best_trial()
+    assert best is not None and best.metric == min(t.metric for t in resumed.completed())
+    assert resumed.summary().completed == 12 and resumed.summary().has_best()
+
+
+def test_search_space_validation_and_scheduler():
+    with pytest.raises(hpo.SearchError):
+        hpo.SearchSpace([]).validate()
+    with pytest.raises(hpo.SearchError):
+        hpo.SearchSpace([hpo.ParamSpec.Float("a", 1.0, 0.0)]).validate()
+    with pytest.raises(hpo.SearchError):
+        hpo.SearchSpace([hpo.ParamSpec.Int("a", 0, 1), hpo.ParamSpec.Int("a", 0, 1)]).validate()
+    loop = hpo.SearchLoop(_space(), hpo.RandomStrategy(1), hpo.Objective("maximize"), hpo.ResourceConfig(max_concurrent=2))
+    t0, t1 = loop.suggest(), loop.suggest()
+    with pytest.raises(hpo.SearchError):
+        loop.suggest()
+    loop.observe(t0.id, 1.0)
+    loop.observe(t1.id, 3.0)
+    assert loop.best_trial().id == t1.id
+    with pytest.raises(hpo.SearchError):
+        loop.observe(t1.id, 0.0)
+    now = [0.0]
+    sch = hpo.ResourceScheduler(hpo.ResourceConfig(4, min_interval_ms=100), clock=lambda: now[0])
+    assert sch.try_reserve() and not sch.try_reserve()
+    now[0] = 0.2
+    assert sch.try_reserve()
+
+
+# ---- softlogic / sync / refract -----------------------------------------------------------------
+def test_softmodes_and_beam():
+    rules = [softlogic.SoftRule("a", 1.0, 2.0), softlogic.SoftRule("b", 3.0, -1.0)]
+    assert softlogic.apply_softmode(rules, "sum") == -1.0
+    assert abs(softlogic.apply_softmode(rules, "normalize") - (0.25 * 2 - 0.75)) < 1e-6
+    sm = torch.softmax(torch.tensor([2.0, -1.0]), 0)
+    assert abs(softlogic.apply_softmode(rules, "softmax") - float(sm[0] + 3 * sm[1])) < 1e-6
+    p = 1 - (1 - 1 / (1 + math.exp(-2.0))) * (1 - 1 / (1 + math.exp(1.0)))
+    assert abs(softlogic.apply_softmode(rules, "prob") - math.log(p / (1 - p))) < 1e-5
+    assert softlogic.apply_softmode([], "sum") == 0.0
+    pick = softlogic.beam_select(0, lambda c: [1, 2] if c == 0 else [], lambda c: float("nan") if c == 1 else 0.5, 2, 2)
+    assert pick == 2
+    expand = lambda c: [c * 2, c * 2 + 1] if c < 16 else []  # noqa: E731
+    # a narrow beam drops the branch that leads to 21 (1 -> 2 -> 5 -> 10 -> 21); a wide one keeps it
+    assert softlogic.beam_select(1, expand, lambda c: -abs(c - 21), 3, 6) == 26
+    assert softlogic.beam_select(1, expand, lambda c: -abs(c - 21), 8, 6) == 21
+
+
+def test_phase_sync_merge_rules():
+    ps = softlogic.PhaseSync(0.05)
+    sync = softlogic.SyncBlock("s", ["a:b"], 0.1)
+    C = softlogic.PhaseCandidate
+    # inside the tolerance window beats a higher-trust candidate outside it
+    sel = ps.merge(sync, [C("far", 0.5, 1.0, 1.0), C("near", 0.05, 0.2, 0.0)])
+    assert sel.graph_id == "near" and sel.pairs == ["a:b"]
+    # equal scores: higher trust, then smaller delta, then resonance
+    sel = ps.merge(sync, [C("x", 0.02, 0.5, 0.0), C("y", 0.02, 0.5, 0.3)])
+    assert sel.graph_id == "y"
+    assert abs(sel.score - (0.6 * 0.5 + 0.3 * 0.8 + 0.1 * math.tanh(0.3))) < 1e-6
+    assert ps.merge(sync, []) is None
+    with pytest.raises(ValueError, match="duplicated"):
+        ps.merge(sync, [C("x", 0.0, 0.1, 0.0), C("x", 0.0, 0.1, 0.0)])
+    with pytest.raises(ValueError, match="at least one pair"):
+        ps.merge(softlogic.SyncBlock("s", []), [])
+    with pytest.raises(ValueError):
+        softlogic.PhaseSync.try_new(-1.0)
+
+
+def test_refract_lowering_commits_or_rolls_back():
+    calls = []
+
+    class B(softlogic.KdslBackend):
+        def __init__(self, fail=False):
+            self.fail = fail
+
+        def begin_refract(self, block): calls.append("begin")
+        def set_precision(self, p): calls.append(("precision", p))
+        def tune_op(self, op, flags):
+            if self.fail:
+                raise RuntimeError("no such op")
+            calls.append(("tune", op, tuple(flags)))
+        def commit_refract(self, block): calls.append("commit")
+        def rollback_refract(self, block): calls.append("rollback")
+
+    blk = softlogic.RefractBlock("main", ("graph", "gpt"), precision="bf16", backend="cuda",
+                                 policies=[softlogic.RefractOpPolicy("matmul", ["tile256"])])
+    softlogic.lower_refract(blk, B())
+    assert calls == ["begin", ("precision", "bf16"), ("tune", "matmul", ("tile256",)), "commit"]
+    calls.clear()
+    with pytest.raises(RuntimeError, match="refract block 'main' failed"):
+        softlogic.lower_refract(blk, B(fail=True))
+    assert calls[-1] == "rollback" and "commit" not in calls
+    with pytest.raises(ValueError):
+        softlogic.validate_refract_block(softlogic.RefractBlock("bad name", ("graph", "g")))
+    with pytest.raises(ValueError):
+        softlogic.validate_refract_block(softlogic.RefractBlock("b", ("graph", "g"), precision="fp64"))
+    got = []
+    sid = plugin.subscribe("Telemetry", got.append)
+    payload = softlogic.emit_feedback(softlogic.FeedbackBlock("fb", "out.json", ["loss", "absent"]), {"loss": 0.5})
+    plugin.unsubscribe("Telemetry", sid)
+    assert payload["metrics"] == {"loss": 0.5} and payload["missing"] == ["absent"] and got
+
+
+# ---- compression -----------------------------------------------------------------------------------
+def test_qat_observer_and_structured_pruning():
+    obs = compress.QatObserver(compress.QatConfig(bit_width=4), "symmetric")
+    obs.observe(torch.tensor([1.0, 2.0, 3.0]))
+    obs.observe(torch.tensor([-4.0, 5.0]))
+    w = torch.tensor([0.5, -0.5, 1.5, -1.5, 9.0])
+    rep = obs.quantize(w)
+    assert rep.bit_width == 4 and rep.scale > 0 and rep.zero_point == 0.0 and rep.observed_steps == 2
+    levels = torch.unique(torch.round((w - rep.min_value) / rep.scale))
+    assert len(levels) <= 16 and w.max() <= rep.max_value + 1e-6
+    asym = compress.QatObserver(leveling="asymmetric")
+    asym.observe(torch.tensor([0.0, 4.0]))
+    r2 = asym.quantize(torch.tensor([1.0, 2.0]))
+    assert r2.min_value < 0 < r2.max_value and r2.quant_error < 1e-3
+
+    w = torch.arange(1, 65, dtype=torch.float32)
+    rep = compress.StructuredPruner().apply(w, compress.StructuredPruningConfig(block_size=8, target_sparsity=0.5))
+    assert rep.pruned_blocks == 4 and rep.kept_blocks == 4 and rep.achieved_sparsity == 0.5
+    assert torch.all(w[:32] == 0) and torch.all(w[32:] > 0)
+    assert abs(rep.l2_error - math.sqrt(sum(i * i for i in range(1, 33)))) < 1e-2
+    tiny = torch.tensor([1e-6] * 4 + [1.0] * 4)
+    rep = compress.StructuredPruner().apply(tiny, compress.StructuredPruningConfig(4, 0.0, 1e-4))
+    assert rep.pruned_blocks == 1 and torch.all(tiny[:4] == 0)
+    with pytest.raises(compress.OptimisationError):
+        compress.StructuredPruner().apply(w, compress.StructuredPruningConfig(0, 0.5))
+    full = compress.compress(torch.randn(256), qat=compress.QatObserver(), pruning=compress.StructuredPruningConfig(32, 0.25))
+    assert full.original_params == 256 and full.remaining_params <= 192 and full.quantization and full.pruning
+
+
+# ---- recommenders ----------------------------------------------------------------------------------
+def test_spiral_recommender_learns_and_ranks():
+    R = rec.RatingTriple
+    ratings = [R(0, 0, 5.0), R(0, 1, 1.0), R(1, 0, 4.0), R(1, 2, 2.0), R(2, 1, 5.0), R(2, 2, 4.0)]
+    m = rec.SpiralRecommender(3, 3, 4, 0.05, 0.01)
+    assert abs(m.predict(0, 0) - sum(math.sin(f) * 0.05 * math.cos(f) * 0.05 for f in range(1, 5))) < 1e-6
+    first = m.train_epoch(ratings)
+    for _ in range(300):
+        last = m.train_epoch(ratings)
+    assert last.rmse < 0.5 * first.rmse and last.samples == 6
+    top = m.recommend_top_k(0, 2, exclude=[1])
+    assert [r.item for r in top][0] == 0 and all(r.item != 1 for r in top)
+    with pytest.raises(rec.SpiralRecError):
+        m.train_epoch([R(9, 0, 1.0)])
+    with pytest.raises(rec.SpiralRecError):
+        m.train_epoch([])
+    nb = rec.NeighborhoodModel.fit(3, 3, ratings + [R(0, 0, 3.0)], 0.1)
+    assert abs(float(nb.matrix[0, 0]) - 4.0) < 1e-6
+    assert len(nb.recommend(0, 2)) == 2
+    kg = rec.KnowledgeGraphRecommender(2, 4, 0.5)
+    kg.add_edge("user_item", 0, 0)
+    kg.add_edge("item_item", 0, 1)
+    kg.add_edge("item_item", 1, 2)
+    out = kg.recommend(0, 3, hops=2)
+    assert [r.item for r in out] == [1, 2] and out[0].score > out[1].score and kg.item_degree(1) == 2
+
+
+# ---- rl ----------------------------------------------------------------------------------------------
+def test_dqn_ppo_sac_and_policy_gradient():
+    dqn = rl.DqnAgent(4, 2, 0.9, 0.5)
+    dqn.set_epsilon(0.0)
+    for _ in range(50):
+        dqn.update_batch([0, 1, 2], [1, 1, 1], [0.0, 0.0, 1.0], [1, 2, 3], [False, False, True])
+    assert dqn.greedy_action(0) == 1 and abs(dqn.q_values(2)[1] - 1.0) < 1e-3 and abs(dqn.q_values(1)[1] - 0.9) < 1e-2
+    assert dqn.select_action(0) == 1
+    dqn.configure_epsilon_schedule(rl.EpsilonGreedySchedule(1.0, 0.0, 10))
+    tr = dqn.select_action_trace(0)
+    assert tr.epsilon == 1.0 and dqn.epsilon < 1.0 and dqn.schedule_step() == 1
+    with pytest.raises(rl.SpiralRlError):
+        rl.DqnAgent(4, 2, 1.5, 0.1)
+    with pytest.raises(rl.SpiralRlError):
+        dqn.update_batch([0], [0, 1], [0.0], [1])
+
+    ppo = rl.PpoAgent(3, 2, 0.1, 0.2)
+    s = [1.0, 0.5, -0.5]
+    lp = ppo.log_prob(s, 1)
+    ppo.update(s, 1, 2.0, lp)
+    assert ppo.log_prob(s, 1) > lp and ppo.value(s) > 0
+
+    sac = rl.SacAgent(3, 4, 0.5)
+    acts = {sac.sample_action(s) for _ in range(50)}
+    assert acts <= {0, 1, 2, 3} and len(acts) > 1
+    sac.jitter(0.1)
+    assert float(sac.policy_weights.abs().max()) <= 1.0
+
+    pg = rl.SpiralPolicyGradient(2, 2, 0.5, 0.9)
+    assert abs(float(pg.weights[0, 0]) - math.cos(1.0) * 0.01) < 1e-7
+    for _ in range(60):
+        for s_, a_, r_ in [([1.0, 0.0], 0, 1.0), ([1.0, 0.0], 1, -1.0), ([0.0, 1.0], 1, 1.0), ([0.0, 1.0], 0, -1.0)]:
+            pg.record_transition(s_, a_, r_)
+        rep = pg.finish_episode()
+    assert rep.steps == 4 and pg.select_action([1.0, 0.0]) == 0 and pg.select_action([0.0, 1.0]) == 1
+    with pytest.raises(rl.SpiralRlError):
+        pg.finish_episode()
+    pg.enable_hypergrad(-1.0, 0.05)
+    pg.attach_hyper_surprise(0.01)
+    pg.record_transition([1.0, 0.0], 0, 1.0)
+    pg.record_transition([1.0, 0.0], 1, -3.0)
+    rep = pg.finish_episode()
+    assert rep.hypergrad_applied and rep.hyper_surprise["scale"] < 1.0 and pg.telemetry().hypergrad
+
+
+# ---- robotics ------------------------------------------------------------------------------------------
+def test_robotics_runtime_step_and_safety():
+    now = [0.0]
+    hub = robotics.SensorFusionHub(clock=lambda: now[0])
+    hub.register_channel("imu", 3)
+    hub.register_channel("lidar", 1, smoothing=0.5, optional=True, max_staleness=0.5)
+    hub.calibrate("imu", bias=[0.1, 0.1, 0.1], scale=2.0)
+    frame = hub.fuse({"imu": [0.2, 0.4, 0.3], "lidar": [1.0]})
+    assert all(abs(a - b) < 1e-6 for a, b in zip(frame.coordinates["imu"], [0.2, 0.6, 0.4]))
+    now[0] = 1.0
+    frame = hub.fuse({"imu": [0.2, 0.4, 0.3], "lidar": [0.0]})
+    assert 0.0 < frame.coordinates["lidar"][0] < 1.0 and frame.health["lidar"].stale
+    with pytest.raises(robotics.RoboticsError):
+        hub.fuse({"lidar": [0.0]})
+    with pytest.raises(robotics.RoboticsError):
+        hub.register_channel("imu", 3)
+    assert abs(robotics.ZSpaceGeometry.non_euclidean(-1.0).metric_norm([3.0, 4.0]) - 5.0 / (1 + 25 / 6)) < 1e-6
+    assert abs(robotics.ZSpaceGeometry.general_relativity([[2.0, 0.0], [0.0, 2.0]], 0.5).metric_norm([3.0, 4.0])
+               - math.sqrt(50.0) * 0.5) < 1e-5
+
+    hub2 = robotics.SensorFusionHub()
+    hub2.register_channel("arm", 2)
+    rt = robotics.RoboticsRuntime(hub2, robotics.DesireLagrangianField({"arm": robotics.Desire(1.0, 0.1, 2.0)}),
+                                  robotics.PsiTelemetry(window=4, failure_energy=5.0, norm_limit=10.0))
+    rt.attach_policy_gradient(robotics.PolicyGradientController(0.05, 0.5))
+    plug = robotics.DriftSafetyPlugin("drift", hazard_cut=0.8)
+    rt.attach_safety_plugin(plug)
+    rt.enable_recording(2)
+    ok = rt.step({"arm": [1.0, 0.0]})
+    assert not ok.halted and ok.energy.total == 0.0 and ok.commands["learning_rate"] == 0.05
+    hot = rt.step({"arm": [3.0, 0.0]})
+    assert abs(hot.energy.total - 3.8) < 1e-5 and hot.commands["learning_rate"] < 0.05
+    assert hot.halted and hot.safety[0].refused and hot.commands["halt"] == 1.0
+    over = rt.step({"arm": [30.0, 0.0]})
+    assert over.telemetry.failsafe and "norm_overflow" in over.telemetry.anomalies
+    assert rt.recording_len() == 2 and len(rt.drain_trajectory()) == 2 and rt.recording_len() == 0
+
+
+# ---- safety ----------------------------------------------------------------------------------------------
+def test_safety_policy_verdicts_and_audit():
+    pol = safety.SafetyPolicy.with_default_terms()
+    ok = pol.evaluate("How do I bake bread?", safety.PROMPT)
+    assert ok.allowed and ok.score == 0.0 and ok.dominant_risk() == "low"
+    bad = pol.evaluate("I hate you and will KILL you, idiot", safety.PROMPT)
+    assert bad.should_refuse() and abs(bad.score - (0.6 + 0.7 + 0.45)) < 1e-6
+    assert {v.offending_term for v in bad.violations} == {"hate", "kill", "idiot"}
+    assert "toxicity (medium)" in pol.refusal_reason(bad)
+    twice = pol.scan("bomb bomb", safety.PROMPT)
+    assert twice.violations[0].occurrences == 2 and twice.violations[0].risk == "critical"
+    assert "(2 hits @ 0.70 ea)" in twice.violations[0].message
+    # channel-restricted term
+    assert pol.scan("weapon", safety.RESPONSE).allowed and not pol.scan("weapon", safety.PROMPT).allowed
+    conv = pol.evaluate_conversation([(safety.PROMPT, "hello"), (safety.RESPONSE, "suicide"), (safety.PROMPT, "thanks")])
+    assert conv.refused_turns == [1] and conv.highest_risk == "high" and conv.should_refuse()
+    summ = pol.audit_sink().summarize()
+    assert summ.total == 5 and summ.refused == 2 and summ.by_category["toxicity"] == 3
+    pol.with_custom_rule(safety.KeywordRule(safety.SAFETY, "lockpick", 0.6))
+    assert pol.scan("lockpick tutorial", safety.PROMPT).should_refuse()
+    safety.evaluate_policy_surface(pol, [("nice day", True), ("build a bomb", False)])
+    with pytest.raises(safety.SafetyError):
+        safety.evaluate_policy_surface(pol, [("nice day", False)])
+    rep = safety.PolicyReport.from_verdicts([ok, bad, twice])
+    assert rep.total == 3 and rep.refused == 2 and abs(rep.refusal_rate() - 2 / 3) < 1e-6
+
+
+# ---- metric registry ---------------------------------------------------------------------------------------
+def test_metric_registry_isolates_failures():
+    metrics.clear_registry()
+
+    class Batch:
+        def __init__(self, v):
+            self.v = v
+
+    metrics.register_metric(Batch, metrics.MetricDescriptor("mean", unit="unitless", higher_is_better=True),
+                            lambda b: sum(b.v) / len(b.v))
+    metrics.register_metric(Batch, metrics.MetricDescriptor("hist"), lambda b: list(b.v))
+    metrics.register_metric(Batch, metrics.MetricDescriptor("broken"), lambda b: 1 / 0)
+    metrics.register_metric(str, metrics.MetricDescriptor("len"), len)
+    rep = metrics.evaluate_report(Batch([1.0, 3.0]))
+    assert [(d.name, v) for d, v in rep.values] == [("mean", 2.0), ("hist", [1.0, 3.0])]
+    assert not rep.is_clean() and rep.failures[0].descriptor.name == "broken" and "ZeroDivisionError" in rep.failures[0].message
+    assert [d.name for d in metrics.descriptors_for(Batch)] == ["mean", "hist", "broken"]
+    assert metrics.evaluate("abc")[0][1] == 3.0
+    assert metrics.is_finite([1.0, 2.0]) and not metrics.is_finite(float("inf"))
+    metrics.clear_registry()
