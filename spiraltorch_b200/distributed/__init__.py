@@ -4,3 +4,5 @@ from .device import (CpuDevice, DistributedDevice, MetricReduce, NativeDistribut
 from .rendezvous import (BufferLengthMismatch, CollectiveTimeout, DistributedError, DuplicateContribution,
                          DuplicateRank, EmptyWorldSize, NonFiniteInput, NonFiniteReduction, ParticipantLeft,
                          PeerTensorFailure, RankOutOfBounds, UnknownRank, WorldSizeMismatch, join)
+from .arena import (AgentConfig, AmebaAutograd, AutogradError, CollectiveArena, CollectiveError,
+                    CollectiveExecutionReport, DistributedTrainer, DistributedTrainerError)

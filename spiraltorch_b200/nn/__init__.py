@@ -1,4 +1,6 @@
 """``spiraltorch.nn``: modules, losses, trainer, data and weight files of the public API."""
+from .amp import (AutocastGuard, GradScaler, OptimizerMode, SpectralLrAdapter, WarmupCosineScheduler,
+                  ZSpaceParameterOptimizer, autocast_enabled)
 from .data import DataLoader, Dataset, from_samples
 from .io import load, load_bincode, load_json, save, save_bincode, save_json
 from .losses import (CategoricalCrossEntropy, ContrastiveLoss, CrossEntropy, FocalLoss, HyperbolicCrossEntropy,

@@ -130,3 +130,68 @@ def test_selfsup_objectives():
     assert st.selfsup.masked_mse(p, t, [[1], [2]]) == pytest.approx((4 + 36) / 2)
     with pytest.raises(IndexError):
         st.selfsup.masked_mse(p, t, [[9], []])
+
+
+def test_grad_scaler_and_warmup_cosine_schedule():
+    import math
+    import spiraltorch_b200 as st
+    from spiraltorch_b200.nn import amp
+
+    assert not amp.autocast_enabled()
+    with amp.AutocastGuard.enable():
+        assert amp.autocast_enabled()
+        with amp.AutocastGuard.disable():
+            assert not amp.autocast_enabled()
+        assert amp.autocast_enabled()
+    assert not amp.autocast_enabled()
+
+    layer = st.nn.Linear("amp", 2, 2)
+    opt = amp.ZSpaceParameterOptimizer(0.05)
+    opt.set_mode(amp.OptimizerMode.realgrad(0.05))
+    opt.prepare_module(layer)
+    scaler = amp.GradScaler(2.0, 2.0, 0.5, 2).with_limits(1.0, 16.0)
+    x = st.Tensor(1, 2, [0.3, -0.7])
+    before = layer.weight.value.clone()
+    loss_grad = layer.forward(x)
+    layer.backward(x, scaler.scale_tensor(loss_grad))
+    assert scaler.step(opt, layer) is True and not torch.equal(layer.weight.value, before)
+    # the unscaled step equals a step taken without a scaler
+    ref = st.nn.Linear("amp", 2, 2)
+    ref.attach_realgrad(0.05)
+    ref.backward(x, ref.forward(x))
+    ref.apply_step(0.05)
+    assert torch.allclose(ref.weight.value, layer.weight.value, atol=1e-6)
+    layer.zero_accumulators()
+    layer.backward(x, scaler.scale_tensor(layer.forward(x)))
+    assert scaler.step(opt, layer) and scaler.scale() == 4.0          # grown after 2 clean steps
+    # overflow: step skipped, scale backed off, accumulators cleared
+    held = layer.weight.value.clone()
+    layer.zero_accumulators()
+    layer.backward(x, st.Tensor(1, 2, [3e38, 3e38]).scale(1.0))
+    for p in layer.parameters():
+        for a in p.accumulators():
+            a.mul_(1e30)
+    assert scaler.step(opt, layer) is False and scaler.scale() == 2.0 and torch.equal(layer.weight.value, held)
+    with pytest.raises(st.TensorError):
+        amp.GradScaler(1.0, 1.0, 0.5, 2)
+    with pytest.raises(st.TensorError):
+        scaler.try_scale_loss(float("inf"))
+
+    sch = amp.WarmupCosineScheduler(1e-2, 1e-4, 4, 12)
+    lrs = [sch.step() for _ in range(14)]
+    assert abs(lrs[0] - (1e-4 + (1e-2 - 1e-4) / 4)) < 1e-9 and abs(lrs[3] - 1e-2) < 1e-9
+    assert abs(lrs[7] - (1e-4 + (1e-2 - 1e-4) * 0.5 * (1 + math.cos(math.pi * 0.5)))) < 1e-9
+    assert abs(lrs[11] - 1e-4) < 1e-9 and lrs[13] == lrs[11] and all(a >= b for a, b in zip(lrs[3:], lrs[4:]))
+    opt2 = amp.ZSpaceParameterOptimizer(1e-2)
+    sch2 = amp.WarmupCosineScheduler(1e-2, 0.0, 0, 10)
+    lr = sch2.step_optimizer(opt2, layer)
+    assert abs(opt2.fallback_learning_rate() - lr) < 1e-9
+    with pytest.raises(st.TensorError):
+        amp.WarmupCosineScheduler(1e-2, 0.0, 5, 4)
+    ad = amp.SpectralLrAdapter()
+    opt2.set_adapter(ad)
+    layer.zero_accumulators()
+    layer.backward(x, layer.forward(x))
+    opt2.step(layer)
+    assert ad.min_scale <= ad.scale_for("w", torch.randn(4, 4)) <= ad.max_scale
+    assert amp.SpectralLrAdapter.from_state(ad.state()).avg_energy == ad.avg_energy

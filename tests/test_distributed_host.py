@@ -194,3 +194,80 @@ def test_two_rank_trainer_step_equals_local_step_on_averaged_gradient(Distribute
         assert torch.allclose(m.bias.value, local.bias.value, atol=1e-6)
     for d in devs:
         d.close()
+
+
+def test_collective_arena_is_transactional_and_reports_digests():
+    from spiraltorch_b200.distributed import arena as A
+    ar = A.CollectiveArena()
+    rows = [[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]]
+    rep = ar.all_reduce_sum(rows)
+    assert rows == [[9.0, 12.0]] * 3 and rep.participants == 3 and rep.width == 2 and rep.committed
+    rep.validate()
+    assert len(rep.input_sha256) == 64 and rep.input_sha256 != rep.output_sha256
+    again = ar.all_reduce_sum([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])
+    assert again.input_sha256 == rep.input_sha256 and again.output_sha256 == rep.output_sha256
+    bad = [[1.0, 2.0], [float("nan"), 4.0]]
+    with pytest.raises(A.CollectiveError) as ei:
+        ar.all_reduce_sum(bad)
+    assert ei.value.kind == "NonFiniteInput" and ei.value.fields["participant"] == 1 and bad[0] == [1.0, 2.0]
+    with pytest.raises(A.CollectiveError) as ei:
+        ar.all_reduce_sum([[3e38], [3e38]])
+    assert ei.value.kind == "NonFiniteReduction"
+    with pytest.raises(A.CollectiveError):
+        ar.all_reduce_sum([[1.0], [1.0, 2.0]])
+    with pytest.raises(A.CollectiveError):
+        ar.all_reduce_sum([])
+    targets = [[0.0, 0.0], [1.0, 1.0]]
+    ar.broadcast([7.0, 8.0], targets)
+    assert targets == [[7.0, 8.0], [7.0, 8.0]]
+    # the lease puts the batches back unless committed
+    ar.enqueue_gradient([1.0, 2.0])
+    ar.enqueue_gradient([3.0, 4.0])
+    with ar.lease_gradient_batches() as lease:
+        assert len(lease.batches()) == 2 and ar.pending() == 0
+    assert ar.pending() == 2
+    with ar.lease_gradient_batches() as lease:
+        lease.commit()
+    assert ar.pending() == 0
+
+
+def test_distributed_trainer_and_gossip_autograd():
+    from spiraltorch_b200.distributed import arena as A
+    tr = A.DistributedTrainer(2, 3, 0.1)
+    tr.broadcast_parameters([1.0, 1.0, 1.0])
+    grads = [[1.0, 2.0, 3.0], [3.0, 2.0, 1.0]]
+    tr.apply_step(grads)
+    assert grads == [[1.0, 2.0, 3.0], [3.0, 2.0, 1.0]]
+    assert all(abs(p - (1.0 - 0.05 * 4.0)) < 1e-6 for p in tr.parameters())
+    before = tr.parameters()
+    with pytest.raises(A.DistributedTrainerError):
+        tr.apply_step([[float("inf"), 0.0, 0.0], [0.0, 0.0, 0.0]])
+    assert tr.parameters() == before
+    assert tr.merge_async_gradients() is False
+    tr.submit_async_gradient([1.0] * 6)
+    tr.submit_async_gradient([3.0] * 6)
+    assert tr.merge_async_gradients() is True
+    assert all(abs(p - (0.8 - 0.1 * 2.0)) < 1e-6 for p in tr.parameters())
+    with pytest.raises(A.DistributedTrainerError):
+        tr.submit_async_gradient([1.0])
+
+    # line graph 0 - 1 - 2: a gradient seeded at 0 reaches 1 damped once and 2 damped twice
+    mesh = A.AmebaAutograd(max_hops=4, tolerance=1e-6)
+    mesh.register_agent(A.AgentConfig(0, 2).with_neighbors([1]).with_learning_rate(0.1).with_damping(0.5))
+    mesh.register_agent(A.AgentConfig(1, 2).with_neighbors([0, 2]).with_learning_rate(0.1).with_damping(0.5))
+    mesh.register_agent(A.AgentConfig(2, 2).with_neighbors([1]).with_learning_rate(0.1).with_damping(0.5))
+    mesh.seed_gradient(0, [1.0, -2.0])
+    assert mesh.propagate_round() == 1 and mesh.pending_messages() == 1
+    assert mesh.drain() == 2 and mesh.pending_messages() == 0
+    assert mesh.weights(0) == pytest.approx([-0.1, 0.2])
+    assert mesh.weights(1) == pytest.approx([-0.05, 0.1])
+    assert mesh.weights(2) == pytest.approx([-0.025, 0.05])
+    with pytest.raises(A.AutogradError):
+        mesh.register_agent(A.AgentConfig(0, 2))
+    with pytest.raises(A.AutogradError):
+        mesh.register_agent(A.AgentConfig(5, 2).with_damping(1.5))
+    mesh.register_agent(A.AgentConfig(9, 2).with_neighbors([42]))
+    mesh.seed_gradient(9, [1.0, 1.0])
+    with pytest.raises(A.AutogradError, match="unknown neighbour"):
+        mesh.propagate_round()
+    assert mesh.weights(9) == [0.0, 0.0] and mesh.pending_messages() == 1
