@@ -1,0 +1,308 @@
+"""Z-space specific models: RBF-kernel attention over (band, sheet, echo) indices with uncertainty
+propagation, an attention-free coherence sequencer, and the Z-space VAE with its own optimisers.
+
+Restated from crates/st-nn/src/z_rba/attention.rs:51-640 (``ZIndex``, ``ZMetricWeights``,
+``ArdParameters``, product RBF kernel added to the scaled dot-product logits, variance output
+``Σ_j p_ij² |σ_j|``), crates/st-nn/src/zspace_coherence/sequencer.rs (coherence-weighted mixing
+instead of attention) and crates/st-nn/src/zspace_coherence/vae.rs:296-1100 (linear encoder to
+``(mu, logvar)``, reparameterised sample, linear decoder, reconstruction + KL, SGD / Adam /
+RMSprop updates).  Everything is batched tensor math on the caller's device.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from ..tensor import Tensor, TensorError
+from .modules import _mm, _t
+
+
+@dataclass(frozen=True)
+class ZIndex:
+    band: int
+    sheet: int
+    echo: int
+
+
+@dataclass
+class ZMetricWeights:
+    w_band: float = 1.0
+    w_sheet: float = 0.7
+    w_echo: float = 0.5
+
+    def normalised(self) -> "ZMetricWeights":
+        s = self.w_band + self.w_sheet + self.w_echo
+        if not math.isfinite(s) or s <= 1.1920929e-07:
+            return ZMetricWeights()
+        return ZMetricWeights(self.w_band / s, self.w_sheet / s, self.w_echo / s)
+
+    def validate(self) -> None:
+        for v in (self.w_band, self.w_sheet, self.w_echo):
+            if not math.isfinite(v) or v < 0:
+                raise TensorError("zrba_metric_weight must be finite and non-negative")
+
+
+@dataclass
+class ArdParameters:
+    ell_band: float = 1.0
+    ell_sheet: float = 1.0
+    ell_echo: float = 1.0
+    sigma2: float = 1.0
+
+    def __post_init__(self):
+        self.ell_band, self.ell_sheet, self.ell_echo = (max(v, 1e-2) for v in (self.ell_band, self.ell_sheet, self.ell_echo))
+
+
+class ZFrame:
+    """Geometry of the index grid: linear band / sheet distances, circular echo distance."""
+
+    def __init__(self, echoes: int = 8, band_step: float = 1.0, sheet_step: float = 1.0):
+        self.echoes, self.band_step, self.sheet_step = max(1, echoes), band_step, sheet_step
+
+    def distances(self, idx: Sequence[ZIndex], device) -> tuple:
+        b = torch.tensor([i.band for i in idx], dtype=torch.float32, device=device)
+        s = torch.tensor([i.sheet for i in idx], dtype=torch.float32, device=device)
+        e = torch.tensor([i.echo for i in idx], dtype=torch.float32, device=device)
+        db = (b[:, None] - b[None, :]).abs() * self.band_step
+        ds = (s[:, None] - s[None, :]).abs() * self.sheet_step
+        de = (e[:, None] - e[None, :]).abs() % self.echoes
+        return db, ds, torch.minimum(de, self.echoes - de)
+
+
+@dataclass
+class ZTensor:
+    mu: Tensor
+    sigma: Tensor
+    indices: list
+
+    def __post_init__(self):
+        if self.mu.shape() != self.sigma.shape():
+            raise TensorError(f"mu {self.mu.shape()} and sigma {self.sigma.shape()} must have the same shape")
+        if len(self.indices) != self.mu.shape()[0]:
+            raise TensorError("one ZIndex per row is required")
+
+
+@dataclass
+class AttentionTelemetry:
+    entropy: list = field(default_factory=list)
+    dominant_probability: list = field(default_factory=list)
+    kernel_mass: list = field(default_factory=list)
+
+
+@dataclass
+class ZRBFAttentionOutput:
+    mean: Tensor
+    variance: Tensor
+    telemetry: AttentionTelemetry
+
+
+class ZRBFAttention:
+    def __init__(self, d_model: int, n_heads: int, metric: Optional[ZMetricWeights] = None, ard: bool = False, device="cpu"):
+        if d_model <= 0 or n_heads <= 0 or d_model % n_heads:
+            raise TensorError(f"d_model {d_model} must be a positive multiple of n_heads {n_heads}")
+        self.d_model, self.n_heads, self.head_dim = d_model, n_heads, d_model // n_heads
+        self.metric = metric or ZMetricWeights()
+        self.metric.validate()
+        self.ard = ard
+        seed = torch.arange(d_model * d_model, dtype=torch.float32).reshape(d_model, d_model)
+        init = torch.tanh(torch.sin(seed) * 0.02 + 0.02 * torch.cos(seed)).to(device)
+        self.query, self.key, self.value, self.output = (init.clone() for _ in range(4))
+        self.head_params = [ArdParameters(1.0 * (1 + 0.1 * h), 0.8 * (1 + 0.1 * h), 0.6 * (1 + 0.1 * h), 1.0) if ard
+                            else ArdParameters() for h in range(n_heads)]
+
+    def forward(self, inp: ZTensor, frame: ZFrame) -> ZRBFAttentionOutput:
+        mu, sigma = _t(inp.mu).float(), _t(inp.sigma).float()
+        rows, cols = mu.shape
+        if cols != self.d_model:
+            raise TensorError(f"input has {cols} columns, expected {self.d_model}")
+        if not bool(torch.isfinite(mu).all() and torch.isfinite(sigma).all()):
+            raise TensorError("zrba_attention input is not finite")
+        tel = AttentionTelemetry()
+        if rows == 0:
+            z = torch.zeros(0, self.d_model, device=mu.device)
+            return ZRBFAttentionOutput(Tensor._wrap(z), Tensor._wrap(z.clone()), tel)
+        with torch.no_grad():
+            q, k, v = (_mm(mu, w.to(mu.device)) for w in (self.query, self.key, self.value))
+            H, D = self.n_heads, self.head_dim
+            qh, kh, vh = (t.reshape(rows, H, D).transpose(0, 1) for t in (q, k, v))          # [H, rows, D]
+            logits = qh @ kh.transpose(1, 2) / math.sqrt(D)
+            w = self.metric.normalised()
+            db, ds, de = frame.distances(inp.indices, mu.device)
+            kern = torch.stack([p.sigma2 * torch.exp(-0.5 * (db * max(w.w_band, 1e-6) / max(p.ell_band, 1e-3)) ** 2)
+                                * torch.exp(-0.5 * (ds * max(w.w_sheet, 1e-6) / max(p.ell_sheet, 1e-3)) ** 2)
+                                * torch.exp(-0.5 * (de * max(w.w_echo, 1e-6) / max(p.ell_echo, 1e-3)) ** 2)
+                                for p in self.head_params])
+            prob = torch.softmax(logits + kern, -1)
+            heads = (prob @ vh).transpose(0, 1).reshape(rows, self.d_model)
+            sig = sigma.abs().reshape(rows, H, D).transpose(0, 1)
+            var = ((prob ** 2) @ sig).transpose(0, 1).reshape(rows, self.d_model)
+            mean = _mm(heads, self.output.to(mu.device))
+            ent = -(prob * torch.log(prob.clamp(min=1e-30))).sum(-1).mean(-1)
+            tel.entropy = ent.tolist()
+            tel.dominant_probability = prob.amax(dim=(1, 2)).tolist()
+            tel.kernel_mass = kern.mean(dim=(1, 2)).tolist()
+        if not bool(torch.isfinite(mean).all() and torch.isfinite(var).all()):
+            raise TensorError("zrba_attention_output is not finite")
+        return ZRBFAttentionOutput(Tensor._wrap(mean), Tensor._wrap(var), tel)
+
+
+class ZSpaceCoherenceSequencer:
+    """Attention-free sequence mixing: each step is a convex blend of the running coherent state and
+    the new token, the blend weight coming from their cosine coherence under curvature ``c``."""
+
+    def __init__(self, dim: int, curvature: float = -1.0, memory: float = 0.9):
+        if dim <= 0 or not curvature < 0 or not 0.0 <= memory < 1.0:
+            raise TensorError("sequencer needs dim > 0, curvature < 0 and memory in [0, 1)")
+        self.dim, self.curvature, self.memory = dim, curvature, memory
+
+    def forward(self, x: Tensor) -> tuple:
+        """``x``: ``(steps, dim)`` → ``(mixed (steps, dim), coherence weights (steps, 1))``."""
+        t = _t(x).float()
+        if t.shape[1] != self.dim:
+            raise TensorError(f"input has {t.shape[1]} columns, expected {self.dim}")
+        state = torch.zeros(self.dim, device=t.device)
+        out, coh = [], []
+        scale = math.sqrt(-self.curvature)
+        for row in t:
+            c = torch.nn.functional.cosine_similarity(state, row, dim=0, eps=1e-12) if bool(state.any()) else torch.tensor(0.0)
+            gate = torch.sigmoid(scale * c) * self.memory
+            state = gate * state + (1.0 - gate) * row
+            out.append(state)
+            coh.append(gate)
+        return Tensor._wrap(torch.stack(out)), Tensor._wrap(torch.stack(coh).reshape(-1, 1))
+
+
+@dataclass
+class ZSpaceVaeState:
+    mu: torch.Tensor
+    logvar: torch.Tensor
+    latent: torch.Tensor
+    reconstruction: torch.Tensor
+    recon_loss: float
+    kl_loss: float
+
+
+class ZSpaceVae:
+    OPTIMIZERS = ("sgd", "adam", "rmsprop")
+
+    def __init__(self, input_dim: int, latent_dim: int, seed: int = 0, device="cpu"):
+        if input_dim <= 0 or latent_dim <= 0:
+            raise TensorError(f"invalid dimensions ({input_dim}, {latent_dim})")
+        g = torch.Generator().manual_seed(seed)
+        s = 1.0 / math.sqrt(input_dim)
+        mk = lambda r, c, sc: (torch.randn(r, c, generator=g) * sc).to(device)  # noqa: E731
+        self.p = {"enc_mu": mk(input_dim, latent_dim, s), "enc_logvar": mk(input_dim, latent_dim, s * 0.1),
+                  "dec": mk(latent_dim, input_dim, 1.0 / math.sqrt(latent_dim)),
+                  "b_mu": torch.zeros(latent_dim, device=device), "b_logvar": torch.zeros(latent_dim, device=device),
+                  "b_dec": torch.zeros(input_dim, device=device)}
+        self.input_dim, self.latent_dim = input_dim, latent_dim
+        self._gen = torch.Generator().manual_seed(seed + 1)
+        self._kind, self._step = "sgd", 0
+        self._m = {k: torch.zeros_like(v) for k, v in self.p.items()}
+        self._v = {k: torch.zeros_like(v) for k, v in self.p.items()}
+        self._hyper = {"beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "decay": 0.99}
+
+    def optimizer_kind(self) -> str:
+        return self._kind
+
+    def optimizer_step(self) -> int:
+        return self._step
+
+    def configure_optimizer_by_name(self, name: str, **hyper) -> None:
+        name = name.lower()
+        if name not in self.OPTIMIZERS:
+            raise TensorError(f"unknown optimiser '{name}'")
+        self._kind = name
+        self._hyper.update(hyper)
+        self.reset_optimizer()
+
+    def reset_optimizer(self) -> None:
+        self._step = 0
+        for d in (self._m, self._v):
+            for t in d.values():
+                t.zero_()
+
+    def encode(self, x: torch.Tensor):
+        return x @ self.p["enc_mu"] + self.p["b_mu"], x @ self.p["enc_logvar"] + self.p["b_logvar"]
+
+    def decode(self, z: torch.Tensor) -> torch.Tensor:
+        return z @ self.p["dec"] + self.p["b_dec"]
+
+    def _losses(self, x, p, eps):
+        mu = x @ p["enc_mu"] + p["b_mu"]
+        logvar = (x @ p["enc_logvar"] + p["b_logvar"]).clamp(-10.0, 10.0)
+        z = mu + torch.exp(0.5 * logvar) * eps
+        rec = z @ p["dec"] + p["b_dec"]
+        recon = ((rec - x) ** 2).sum(-1).mean()
+        kl = (-0.5 * (1 + logvar - mu ** 2 - logvar.exp()).sum(-1)).mean()
+        return mu, logvar, z, rec, recon, kl
+
+    def forward(self, x, sample: bool = True) -> ZSpaceVaeState:
+        x = _t(x).float().reshape(-1, self.input_dim)
+        eps = torch.randn(x.shape[0], self.latent_dim, generator=self._gen).to(x.device) if sample else \
+            torch.zeros(x.shape[0], self.latent_dim, device=x.device)
+        with torch.no_grad():
+            mu, logvar, z, rec, recon, kl = self._losses(x, self.p, eps)
+        return ZSpaceVaeState(mu, logvar, z, rec, float(recon), float(kl))
+
+    def forward_mean(self, x) -> ZSpaceVaeState:
+        return self.forward(x, sample=False)
+
+    def train_batch(self, x, learning_rate: float = 1e-2, beta: float = 1.0) -> ZSpaceVaeState:
+        x = _t(x).float().reshape(-1, self.input_dim)
+        if not bool(torch.isfinite(x).all()):
+            raise TensorError("non-finite VAE input")
+        eps = torch.randn(x.shape[0], self.latent_dim, generator=self._gen).to(x.device)
+        leaves = {k: v.detach().clone().requires_grad_(True) for k, v in self.p.items()}
+        with torch.enable_grad():
+            mu, logvar, z, rec, recon, kl = self._losses(x, leaves, eps)
+            grads = torch.autograd.grad(recon + beta * kl, list(leaves.values()))
+        self._step += 1
+        h = self._hyper
+        for (k, w), g in zip(self.p.items(), grads):
+            if self._kind == "sgd":
+                upd = g
+            elif self._kind == "adam":
+                self._m[k].mul_(h["beta1"]).add_(g, alpha=1 - h["beta1"])
+                self._v[k].mul_(h["beta2"]).addcmul_(g, g, value=1 - h["beta2"])
+                upd = (self._m[k] / (1 - h["beta1"] ** self._step)) / \
+                      ((self._v[k] / (1 - h["beta2"] ** self._step)).sqrt() + h["eps"])
+            else:
+                self._v[k].mul_(h["decay"]).addcmul_(g, g, value=1 - h["decay"])
+                upd = g / (self._v[k].sqrt() + h["eps"])
+            w.sub_(learning_rate * upd)
+        return ZSpaceVaeState(mu.detach(), logvar.detach(), z.detach(), rec.detach(), float(recon.detach()), float(kl.detach()))
+
+    train_step = train_batch
+
+    def evaluate_batch(self, x) -> dict:
+        st = self.forward_mean(x)
+        return {"recon_loss": st.recon_loss, "kl_loss": st.kl_loss, "samples": st.mu.shape[0]}
+
+    def state_dict(self) -> dict:
+        return {k: v.detach().cpu().clone() for k, v in self.p.items()}
+
+    def load_state_dict(self, state: dict) -> None:
+        for k, v in state.items():
+            if k not in self.p or self.p[k].shape != v.shape:
+                raise TensorError(f"unexpected VAE parameter '{k}' with shape {tuple(v.shape)}")
+            self.p[k].copy_(v)
+
+    def save(self, path) -> None:
+        import json
+        from ..config import atomic_write
+        atomic_write(path, json.dumps({"input_dim": self.input_dim, "latent_dim": self.latent_dim, "optimizer": self._kind,
+                                       "parameters": {k: {"shape": list(v.shape), "data": v.flatten().tolist()}
+                                                      for k, v in self.state_dict().items()}}))
+
+    @classmethod
+    def load(cls, path) -> "ZSpaceVae":
+        import json
+        blob = json.load(open(path))
+        vae = cls(blob["input_dim"], blob["latent_dim"])
+        vae.load_state_dict({k: torch.tensor(v["data"]).reshape(v["shape"]) for k, v in blob["parameters"].items()})
+        vae._kind = blob.get("optimizer", "sgd")
+        return vae

@@ -290,3 +290,52 @@ def test_session_and_dataloader():
     info = st.build_info()
     assert "cuda" in info["features"] and st.describe_device()["backends"]["cpu"]["ready"]
     s.close()
+
+
+def test_spiral_lightning_plans():
+    from spiraltorch_b200.nn import lightning as L
+    sess = st.SpiralSession("cpu", seed=3)
+    model = st.nn.Sequential()
+    model.add(st.nn.Linear("fc", 4, 2))
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(4, 2, generator=g)
+    def batches(n):
+        out = []
+        for _ in range(n):
+            x = torch.randn(8, 4, generator=g)
+            out.append((st.Tensor._wrap(x), st.Tensor._wrap(x @ w)))
+        return out
+    lt = L.SpiralLightning(sess, 8, 2)
+    stats = lt.fit_epochs(model, st.nn.MeanSquaredError(), [batches(3), batches(3)])
+    assert len(stats) == 2 and stats[0].batches == 3
+    cfg2 = L.LightningConfig.builder(8, 2).roundtable(st.nn.RoundtableConfig(top_k=2, mid_k=1, bottom_k=1)).build()
+    rep = lt.fit_plan(model, st.nn.MeanSquaredError(), [
+        L.LightningStage(L.LightningConfig(8, 2), [batches(4) for _ in range(3)], "warm"),
+        L.LightningStage(cfg2, [batches(4) for _ in range(3)], "refine")])
+    assert rep.total_epochs() == 6 and rep.total_batches() == 24 and [s.label for s in rep.stages] == ["warm", "refine"]
+    best = min(rep.epochs(), key=lambda e: e.average_loss)
+    assert rep.best_epoch() is best and rep.stages[rep.best_stage_index()].best_epoch() is best
+    assert lt.schedule().describe()["top_k"] == 2 if "top_k" in lt.schedule().describe() else True
+
+    # self-supervised plan: an encoder learns to align two noisy views
+    enc = st.nn.Sequential()
+    enc.add(st.nn.Linear("enc", 6, 4))
+    def views(n):
+        out = []
+        for _ in range(n):
+            base = torch.randn(16, 6, generator=g)
+            out.append((st.Tensor._wrap(base + 0.05 * torch.randn(16, 6, generator=g)),
+                        st.Tensor._wrap(base + 0.05 * torch.randn(16, 6, generator=g))))
+        return out
+    lt2 = L.SpiralLightning(sess, 32, 4)
+    got = []
+    sid = st.plugin.subscribe("Telemetry", got.append)
+    plan = lt2.fit_selfsup_plan(enc, [L.SelfSupStage(L.LightningConfig(32, 4), [views(4) for _ in range(6)], 0.2, True, "ssl")])
+    st.plugin.unsubscribe("Telemetry", sid)
+    eps = plan.stages[0].epochs
+    assert plan.total_epochs() == 6 and eps[0].telemetry.batches == 4
+    assert eps[-1].telemetry.mean_loss < eps[0].telemetry.mean_loss
+    assert 0.0 <= eps[-1].telemetry.mean_accuracy <= 1.0 and any(e.get("selfsup") == "info_nce" for e in got)
+    loss = L.InfoNCELoss(0.1)
+    with pytest.raises(st.TensorError):
+        loss.forward(st.Tensor.zeros(3, 4), None)

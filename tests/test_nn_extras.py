@@ -1,0 +1,111 @@
+"""Graph layers, Z-RBA attention, coherence sequencer and the Z-space VAE (CPU)."""
+import math
+
+import pytest
+import torch
+
+import spiraltorch_b200 as st
+from spiraltorch_b200.nn import gnn, zspace
+
+
+def test_graph_context_and_convolution():
+    A = torch.tensor([[0.0, 1.0, 0.0], [1.0, 0.0, 1.0], [0.0, 1.0, 0.0]])
+    ctx = gnn.GraphContext.from_adjacency(A)
+    d = torch.tensor([2.0, 3.0, 2.0]).rsqrt()
+    expect = d[:, None] * (A + torch.eye(3)) * d[None, :]
+    assert torch.allclose(ctx.norm_adjacency, expect)
+    row = gnn.GraphContext(A, 1.0, "row")
+    assert torch.allclose(torch.tensor(row.row_sums()), torch.ones(3))
+    conv = gnn.ZSpaceGraphConvolution("gc", ctx, 2, 2)
+    assert [p.name for p in conv.parameters()] == ["gc::weight", "gc::bias"]
+    assert conv.weight.value.flatten().tolist() == pytest.approx([0.01, 0.02, 0.03, 0.04])
+    x = st.Tensor(3, 2, [1.0, 0.0, 0.0, 1.0, 1.0, 1.0])
+    y = conv.forward(x)
+    assert torch.allclose(y.torch(), (expect @ x.torch()) @ conv.weight.value, atol=1e-6)
+    conv.set_aggregation(gnn.NeighborhoodAggregation.multi_hop_mean(2))
+    y2 = conv.forward(x)
+    sup = (x.torch() + expect @ x.torch() + expect @ expect @ x.torch()) / 3
+    assert torch.allclose(y2.torch(), sup @ conv.weight.value, atol=1e-6)
+    # backward accumulates into the hypergrad tapes and a step changes the weights
+    before = conv.weight.value.clone()
+    conv.backward(x, st.Tensor._wrap(torch.ones(3, 2)))
+    conv.apply_step(0.01)
+    assert not torch.equal(before, conv.weight.value)
+    with pytest.raises(st.TensorError):
+        conv.forward(st.Tensor.zeros(4, 2))
+    with pytest.raises(st.TensorError):
+        gnn.GraphContext(torch.ones(2, 3))
+
+
+def test_graph_regressors_learn():
+    torch.manual_seed(0)
+    A = (torch.rand(6, 6) > 0.5).float()
+    A = ((A + A.t()) > 0).float()
+    A.fill_diagonal_(0)
+    ctx = gnn.GraphContext.from_adjacency(A)
+    net = gnn.ZSpaceGraphNetwork("g", ctx, [3, 4, 1], learning_rate=0.05)
+    reg = gnn.ZSpaceGraphRegressor(net, gnn.GraphReadout.mean())
+    x = st.Tensor._wrap(torch.randn(6, 3))
+    target = st.Tensor(1, 1, [0.7])
+    loss = st.nn.MeanSquaredError()
+    first = float(loss.forward(reg.forward(x), target).torch())
+    for _ in range(60):
+        pred = reg.forward(x)
+        reg.backward(x, loss.backward(pred, target))
+        reg.apply_step(0.05)
+        reg.zero_accumulators()
+    assert float(loss.forward(reg.forward(x), target).torch()) < 0.5 * first
+    batch = gnn.GraphBatch([2, 4])
+    breg = gnn.ZSpaceGraphBatchRegressor(net, gnn.GraphReadout.max(), batch)
+    out = breg.forward(x)
+    assert out.shape() == (2, 1)
+    with pytest.raises(st.TensorError):
+        breg.forward_batch(x, gnn.GraphBatch([2, 3]))
+    assert gnn.GraphReadout.sum().forward(st.Tensor(2, 2, [1, 2, 3, 4])).tolist() == [[4.0, 6.0]]
+
+
+def test_zrba_attention_kernel_and_variance():
+    att = zspace.ZRBFAttention(8, 2, ard=True)
+    idx = [zspace.ZIndex(0, 0, 0), zspace.ZIndex(0, 0, 1), zspace.ZIndex(3, 2, 4), zspace.ZIndex(3, 2, 7)]
+    mu = st.Tensor.randn(4, 8, seed=1)
+    sigma = st.Tensor._wrap(torch.full((4, 8), 0.5))
+    out = att.forward(zspace.ZTensor(mu, sigma, idx), zspace.ZFrame(echoes=8))
+    assert out.mean.shape() == (4, 8) and out.variance.shape() == (4, 8)
+    v = out.variance.torch()
+    assert bool((v > 0).all()) and bool((v <= 0.5 + 1e-6).all())     # Σ p² σ ≤ σ
+    assert len(out.telemetry.entropy) == 2 and all(0 < e <= math.log(4) + 1e-6 for e in out.telemetry.entropy)
+    # the echo distance is circular: 0 and 7 are neighbours on a ring of 8
+    _, _, de = zspace.ZFrame(8).distances([zspace.ZIndex(0, 0, 0), zspace.ZIndex(0, 0, 7)], "cpu")
+    assert de[0, 1].item() == 1.0
+    with pytest.raises(st.TensorError):
+        zspace.ZRBFAttention(7, 2)
+    with pytest.raises(st.TensorError):
+        zspace.ZTensor(mu, sigma, idx[:2])
+
+
+def test_coherence_sequencer_and_vae(tmp_path):
+    seq = zspace.ZSpaceCoherenceSequencer(4, curvature=-1.0, memory=0.8)
+    x = st.Tensor._wrap(torch.tensor([[1.0, 0, 0, 0], [1.0, 0, 0, 0], [0, 1.0, 0, 0]]))
+    mixed, coh = seq.forward(x)
+    assert mixed.shape() == (3, 4) and coh.shape() == (3, 1)
+    c = coh.torch().flatten()
+    assert c[0] == pytest.approx(0.4) and c[1] > c[2]          # aligned token keeps more of the state
+
+    torch.manual_seed(0)
+    basis = torch.randn(2, 6)
+    data = torch.randn(64, 2) @ basis
+    for kind in zspace.ZSpaceVae.OPTIMIZERS:
+        vae = zspace.ZSpaceVae(6, 2, seed=3)
+        vae.configure_optimizer_by_name(kind)
+        first = vae.evaluate_batch(data)["recon_loss"]
+        lr = 0.01 if kind == "sgd" else 0.02
+        for _ in range(200):
+            vae.train_batch(data, learning_rate=lr, beta=0.01)
+        assert vae.evaluate_batch(data)["recon_loss"] < 0.5 * first, kind
+        assert vae.optimizer_step() == 200 and vae.optimizer_kind() == kind
+    p = tmp_path / "vae.json"
+    vae.save(p)
+    again = zspace.ZSpaceVae.load(p)
+    assert torch.allclose(again.forward_mean(data).reconstruction, vae.forward_mean(data).reconstruction)
+    with pytest.raises(st.TensorError):
+        vae.configure_optimizer_by_name("lion")
