@@ -1,0 +1,195 @@
+"""Command-line entry points (the console scripts of the reference's ``[project.scripts]``,
+bindings/st-py/pyproject.toml): a model-zoo launcher, an HPO driver (``spiral-train``,
+bindings/st-py/spiral/cli.py), a weight exporter (``spiral-export``, spiral/export.py), a plugin
+event recorder and a runtime pre-flight report.
+
+    python -m spiraltorch_b200.cli model-zoo mlp_regression --run-dir runs/mlp
+    python -m spiraltorch_b200.cli model-zoo gpt-1.3b --gpus 8            # prints the torchrun command
+    python -m spiraltorch_b200.cli train --trials 8 --strategy bayesian --param lr=float:1e-3:1e-1
+    python -m spiraltorch_b200.cli export weights.json weights.bin
+    python -m spiraltorch_b200.cli runtime-preflight
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parents[1]
+
+ZOO = {
+    "mlp_regression": ("cpu", "MLP regression, CPU fp32, SGD (plumbing check)", None),
+    "char-lm": ("dp", "byte-level char LM, data-parallel, fused gradient all-reduce + AdamW", "charlm"),
+    "conv-classifier": ("dp", "conv-pool classifier, data-parallel, fused conv kernels + SGD momentum", "conv"),
+    "contrastive": ("dp", "InfoNCE encoder, fused cross-rank similarity kernel + AdamW", "contrastive"),
+    "gpt-1.3b": ("tp", "GPT 1.3B, tensor-parallel with fused all-gather→GEMM / GEMM→reduce-scatter", None),
+}
+
+
+def _torchrun(script: str, gpus: int, extra: list) -> list:
+    cmd = [sys.executable]
+    if gpus > 1:
+        cmd += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}", "--master-addr", "127.0.0.1",
+                "--master-port", os.environ.get("MASTER_PORT", "29500")]
+    return cmd + [str(REPO / script)] + extra
+
+
+def cmd_model_zoo(args) -> int:
+    if args.list or not args.model:
+        for name, (_, desc, _) in ZOO.items():
+            print(f"{name:18s} {desc}")
+        return 0
+    if args.model not in ZOO:
+        print(f"unknown model '{args.model}'; try --list", file=sys.stderr)
+        return 2
+    kind, _, key = ZOO[args.model]
+    if kind == "cpu":
+        from .models import mlp_regression
+        return mlp_regression.main(["--backend", args.backend] + (["--run-dir", args.run_dir] if args.run_dir else []))
+    if kind == "dp":
+        cmd = _torchrun("benchmarks/dp_models.py", args.gpus, ["--model", key, "--steps", str(args.steps)])
+    else:
+        cmd = _torchrun("bench.py", args.gpus, ["--gpus", str(args.gpus), "--steps", str(args.steps)])
+    print(" ".join(cmd))
+    if args.dry_run:
+        return 0
+    import subprocess
+    return subprocess.call(cmd)
+
+
+def _parse_param(spec: str):
+    from . import hpo
+    name, rest = spec.split("=", 1)
+    kind, *vals = rest.split(":")
+    if kind == "float":
+        return hpo.ParamSpec.Float(name, float(vals[0]), float(vals[1]))
+    if kind == "int":
+        return hpo.ParamSpec.Int(name, int(vals[0]), int(vals[1]))
+    if kind == "cat":
+        return hpo.ParamSpec.Categorical(name, vals)
+    raise SystemExit(f"bad --param '{spec}' (use name=float:lo:hi | name=int:lo:hi | name=cat:a:b:c)")
+
+
+def cmd_train(args) -> int:
+    """HPO over the MLP regression recipe: each trial trains with the suggested hyper-parameters."""
+    from . import hpo
+    from .models import mlp_regression
+    space = hpo.SearchSpace([_parse_param(p) for p in (args.param or ["lr=float:1e-3:1e-1"])])
+    strategy = {"random": lambda: hpo.RandomStrategy(args.seed), "bayesian": lambda: hpo.BayesianStrategy(args.seed, 0.3),
+                "population": lambda: hpo.PopulationStrategy(args.seed)}[args.strategy]()
+    state_path = Path(args.state) if args.state else None
+    if state_path and state_path.exists():
+        loop = hpo.SearchLoop.from_state(space, json.loads(state_path.read_text()))
+    else:
+        loop = hpo.SearchLoop(space, strategy, hpo.Objective("minimize"))
+    while len(loop.completed()) < args.trials:
+        t = loop.suggest()
+        hp = t.suggestion
+        out = mlp_regression.run(None, "cpu", steps=int(hp.get("steps", args.steps)), batch=int(hp.get("batch", 32)),
+                                 lr=float(hp.get("lr", 1e-2)), seed=args.seed, quiet=True)
+        loop.observe(t.id, out["final_loss"])
+        print(json.dumps({"trial": t.id, "params": hp, "final_loss": out["final_loss"]}))
+        if state_path:
+            from .config import atomic_write
+            atomic_write(state_path, json.dumps(loop.checkpoint()))
+    best = loop.best_trial()
+    print(json.dumps({"best_trial": best.id, "params": best.suggestion, "final_loss": best.metric}))
+    return 0
+
+
+def cmd_export(args) -> int:
+    """Convert a weight file between the JSON, bincode and manifest formats (suffix decides)."""
+    from .nn import io as nn_io
+    state = nn_io.load(args.src)
+    nn_io.save(args.dst, state)
+    print(f"{args.src} -> {args.dst}: {len(state)} tensors")
+    return 0
+
+
+def cmd_plugin(args) -> int:
+    """Record plugin-bus events of a model-zoo run into a JSONL file."""
+    from . import plugin
+    from .models import mlp_regression
+    with plugin.record(args.out, args.events.split(",") if args.events else None):
+        mlp_regression.run(None, "cpu", steps=args.steps, quiet=True)
+    print(f"events written to {args.out}")
+    return 0
+
+
+def cmd_preflight(args) -> int:
+    from . import build_info, describe_device
+    report = {"build": build_info(), "device": describe_device(args.backend)}
+    try:
+        from .utils import build
+        report["native"] = {"cuda_library": str(build.LIB_PATH), "cuda_library_present": build.LIB_PATH.exists(),
+                            "host_library_present": build.HOST_LIB_PATH.exists(), "nvcc": build.find_nvcc()}
+    except Exception as exc:  # noqa: BLE001
+        report["native"] = {"error": repr(exc)}
+    print(json.dumps(report, indent=2, default=str))
+    return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="spiraltorch")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    z = sub.add_parser("model-zoo", help="run a model-zoo recipe")
+    z.add_argument("model", nargs="?")
+    z.add_argument("--list", action="store_true")
+    z.add_argument("--backend", default="cpu")
+    z.add_argument("--run-dir", default=None)
+    z.add_argument("--gpus", type=int, default=1)
+    z.add_argument("--steps", type=int, default=10)
+    z.add_argument("--dry-run", action="store_true", help="print the launch command only")
+    z.set_defaults(fn=cmd_model_zoo)
+    t = sub.add_parser("train", help="hyper-parameter search over the MLP regression recipe")
+    t.add_argument("--trials", type=int, default=4)
+    t.add_argument("--steps", type=int, default=100)
+    t.add_argument("--seed", type=int, default=0)
+    t.add_argument("--strategy", default="bayesian", choices=["random", "bayesian", "population"])
+    t.add_argument("--param", action="append")
+    t.add_argument("--state", default=None, help="checkpoint file: resumed if present, updated after every trial")
+    t.set_defaults(fn=cmd_train)
+    e = sub.add_parser("export", help="convert weights between .json / .bin / .manifest.json")
+    e.add_argument("src")
+    e.add_argument("dst")
+    e.set_defaults(fn=cmd_export)
+    p = sub.add_parser("plugin", help="record plugin events of a short run")
+    p.add_argument("--out", default="events.jsonl")
+    p.add_argument("--events", default=None)
+    p.add_argument("--steps", type=int, default=16)
+    p.set_defaults(fn=cmd_plugin)
+    r = sub.add_parser("runtime-preflight", help="report device, build and native-library status")
+    r.add_argument("--backend", default="auto")
+    r.set_defaults(fn=cmd_preflight)
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return args.fn(args)
+
+
+def model_zoo_main() -> int:
+    return main(["model-zoo"] + sys.argv[1:])
+
+
+def train_main() -> int:
+    return main(["train"] + sys.argv[1:])
+
+
+def export_main() -> int:
+    return main(["export"] + sys.argv[1:])
+
+
+def plugin_main() -> int:
+    return main(["plugin"] + sys.argv[1:])
+
+
+def preflight_main() -> int:
+    return main(["runtime-preflight"] + sys.argv[1:])
+
+
+if __name__ == "__main__":
+    sys.exit(main())

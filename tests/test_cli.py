@@ -1,0 +1,48 @@
+"""Command-line entry points (CPU)."""
+import json
+
+from spiraltorch_b200 import cli
+
+
+def test_model_zoo_listing_and_dry_run(capsys, tmp_path):
+    assert cli.main(["model-zoo", "--list"]) == 0
+    out = capsys.readouterr().out
+    assert "gpt-1.3b" in out and "conv-classifier" in out and "mlp_regression" in out
+    assert cli.main(["model-zoo", "gpt-1.3b", "--gpus", "8", "--dry-run"]) == 0
+    cmd = capsys.readouterr().out
+    assert "torch.distributed.run" in cmd and "--nproc-per-node=8" in cmd and "bench.py" in cmd and "127.0.0.1" in cmd
+    assert cli.main(["model-zoo", "char-lm", "--gpus", "1", "--dry-run"]) == 0
+    assert "dp_models.py --model charlm" in capsys.readouterr().out
+    assert cli.main(["model-zoo", "nope"]) == 2
+    run_dir = tmp_path / "mlp"
+    assert cli.main(["model-zoo", "mlp_regression", "--run-dir", str(run_dir)]) == 0
+    assert json.loads((run_dir / "run.json").read_text())["schema"] == "st.modelzoo.run.v1"
+    keys = set(json.loads((run_dir / "weights.json").read_text())["parameters"]) if "parameters" in \
+        json.loads((run_dir / "weights.json").read_text()) else set()
+    assert not keys or {"fc1::weight", "head::bias"} <= keys
+
+
+def test_train_export_plugin_preflight(capsys, tmp_path):
+    state = tmp_path / "hpo.json"
+    assert cli.main(["train", "--trials", "3", "--steps", "40", "--param", "lr=float:1e-3:1e-1", "--state", str(state)]) == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert len(lines) == 4 and "best_trial" in lines[-1] and lines[-1]["final_loss"] == min(l["final_loss"] for l in lines[:3])
+    # resuming a finished search runs no new trial
+    assert cli.main(["train", "--trials", "3", "--state", str(state)]) == 0
+    assert len(capsys.readouterr().out.strip().splitlines()) == 1
+
+    run_dir = tmp_path / "mlp"
+    cli.main(["model-zoo", "mlp_regression", "--run-dir", str(run_dir)])
+    capsys.readouterr()
+    assert cli.main(["export", str(run_dir / "weights.json"), str(tmp_path / "w.bin")]) == 0
+    assert "4 tensors" in capsys.readouterr().out and (tmp_path / "w.bin").stat().st_size > 0
+    assert cli.main(["export", str(tmp_path / "w.bin"), str(tmp_path / "back.json")]) == 0
+
+    ev = tmp_path / "events.jsonl"
+    assert cli.main(["plugin", "--out", str(ev), "--steps", "8", "--events", "EpochEnd,TrainerStep"]) == 0
+    kinds = {json.loads(l)["type"] for l in ev.read_text().splitlines()}
+    assert kinds == {"EpochEnd", "TrainerStep"}
+    capsys.readouterr()
+    assert cli.main(["runtime-preflight", "--backend", "cpu"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert "build" in rep and "device" in rep and "native" in rep
