@@ -28,6 +28,9 @@ from ..optim.amegagrad import AmegaHypergrad, AmegaRealgrad
 from ..tensor import Tensor, TensorError
 
 
+from ..ops import recurrent as _rec  # noqa: E402
+
+
 def _t(x) -> torch.Tensor:
     return x.torch() if isinstance(x, Tensor) else torch.as_tensor(x, dtype=torch.float32)
 
@@ -496,9 +499,7 @@ class Lstm(_Recurrent):
         c = torch.zeros_like(h)
         for t in range(self.steps):
             z = xs[:, t] @ p[f"{self.name}::w_ih"] + h @ p[f"{self.name}::w_hh"] + p[f"{self.name}::bias"]
-            i, f, g, o = z[:, :H], z[:, H:2 * H], z[:, 2 * H:3 * H], z[:, 3 * H:]
-            c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
-            h = torch.sigmoid(o) * torch.tanh(c)
+            h, c = _rec.lstm_gate(z, c)           # fused gate kernel (and its BPTT step) on CUDA
         return h
 
 
@@ -517,7 +518,7 @@ class WaveRnn(_Recurrent):
         for t in range(self.steps):
             skip = hs[t - self.dilation] if t >= self.dilation else torch.zeros_like(h)
             z = xs[:, t] @ p[f"{self.name}::w_ih"] + (h + skip) @ p[f"{self.name}::w_hh"] + p[f"{self.name}::bias"]
-            h = torch.tanh(z[:, :H]) * torch.sigmoid(z[:, H:])
+            h = _rec.wave_gate(z)
             hs.append(h)
         return h
 
