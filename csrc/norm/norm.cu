@@ -17,7 +17,10 @@ namespace {
 using namespace st;
 
 constexpr int NT = 256;     // threads per CTA
-constexpr int MAXV = 4;     // 16-byte vectors per thread held in registers (d <= 8192)
+constexpr int MAXV = 4;     // most 16-byte vectors per thread held in registers (d <= 8192)
+// The kernels are instantiated for 1, 2 or 4 vectors per thread (d <= 2048 / 4096 / 8192): the
+// per-thread arrays are sized by the template argument, so the common d = 2048 case needs a
+// quarter of the registers and four times as many CTAs stay resident per SM.
 
 __device__ __forceinline__ float block_sum(float v, float* sh) {
   v = warp_sum(v);
@@ -48,7 +51,7 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 
 // RMS: y = x * rstd * gamma.   LN: y = (x - mean) * rstd * gamma + beta.
 // Optional fused residual: x := x + residual is written to `sum_out` before normalising.
-template <bool RMS>
+template <bool RMS, int MV>
 __global__ void __launch_bounds__(NT)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                 const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
@@ -60,10 +63,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   if (row >= rows) return;
   const int nvec = d >> 3;
   const __nv_bfloat16* xr = x + (size_t)row * d;
-  float v[MAXV][8];
+  float v[MV][8];
   float s = 0.0f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int i = 0; i < MV; ++i) {
     const int vi = threadIdx.x + i * NT;
     if (vi < nvec) {
       load8(xr + vi * 8, v[i]);
@@ -90,7 +93,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     mean = block_sum(s, sh) / d;
     float q = 0.0f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < MV; ++i) {
       const int vi = threadIdx.x + i * NT;
       if (vi < nvec) {
 #pragma unroll
@@ -108,7 +111,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     rstd_out[row] = rstd;
   }
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int i = 0; i < MV; ++i) {
     const int vi = threadIdx.x + i * NT;
     if (vi < nvec) {
       float g[8], o[8];
@@ -128,7 +131,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 }
 
 // dx for one row and the CTA's running dgamma/dbeta.
-template <bool RMS>
+template <bool RMS, int MV>
 __global__ void __launch_bounds__(NT)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -137,9 +140,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 float* __restrict__ partial_dbeta, int rows, int d) {
   __shared__ float sh[NT / 32];
   const int nvec = d >> 3;
-  float g[MAXV][8], dg[MAXV][8], db[MAXV][8];
+  float g[MV][8], dg[MV][8], db[MV][8];
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int i = 0; i < MV; ++i) {
     const int vi = threadIdx.x + i * NT;
     if (vi < nvec) load8(gamma + vi * 8, g[i]);
 #pragma unroll
@@ -151,10 +154,10 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mean = RMS ? 0.0f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[MAXV][8], gy[MAXV][8];
+    float xh[MV][8], gy[MV][8];
     float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < MV; ++i) {
       const int vi = threadIdx.x + i * NT;
       if (vi < nvec) {
         float xv[8], dv[8];
@@ -174,7 +177,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float m1 = block_sum(s1, sh) / d;
     const float m2 = RMS ? 0.0f : block_sum(s2, sh) / d;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < MV; ++i) {
       const int vi = threadIdx.x + i * NT;
       if (vi < nvec) {
         float o[8];
@@ -191,7 +194,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     }
   }
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int i = 0; i < MV; ++i) {
     const int vi = threadIdx.x + i * NT;
     if (vi < nvec) {
       float* pg = partial_dgamma + (size_t)blockIdx.x * d + vi * 8;
@@ -206,14 +209,30 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-// out[c] (+)= sum_p partial[p, c]
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       int parts, int d, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
-  float s = 0.0f;
-  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * d + c];
-  out[c] = accumulate ? out[c] + s : s;
+// out[c] (+)= sum_p partial[p, c].  A CTA owns 32 columns; its 8 thread rows sum every 8th partial
+// (each a coalesced 128-byte read) and are combined through shared memory.
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts, int d, int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, k = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s0 = 0.0f, s1 = 0.0f;
+  if (c < d) {
+    int p = k;
+    for (; p + 8 < parts; p += 16) {
+      s0 += partial[(size_t)p * d + c];
+      s1 += partial[(size_t)(p + 8) * d + c];
+    }
+    if (p < parts) s0 += partial[(size_t)p * d + c];
+  }
+  sh[k][cx] = s0 + s1;
+  __syncthreads();
+  if (k == 0 && c < d) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sh[i][cx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 }  // namespace
@@ -221,6 +240,12 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, float*
 namespace st {
 int norm_bwd_grid(int rows) {
   int g = sm_count() * 2;
+  return rows < g ? rows : g;
+}
+// CTAs for the regular entry: as many as stay resident (register footprint grows with d)
+int norm_bwd_grid_for(int rows, int d) {
+  const int per_sm = d <= 2048 ? 4 : 2;
+  int g = sm_count() * per_sm;
   return rows < g ? rows : g;
 }
 }  // namespace st
@@ -243,25 +268,29 @@ ST_API int st_norm_fwd(int rms, const void* x, const void* residual, const void*
   auto B = static_cast<const __nv_bfloat16*>(beta);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto S = static_cast<__nv_bfloat16*>(sum_out);
-  if (rms)
-    norm_fwd_kernel<true><<<rows, NT, 0, s>>>(X, R, G, B, Y, S, mean, rstd, rows, d, eps);
-  else
-    norm_fwd_kernel<false><<<rows, NT, 0, s>>>(X, R, G, B, Y, S, mean, rstd, rows, d, eps);
+#define ST_NORM_FWD(RMSV, MVV) norm_fwd_kernel<RMSV, MVV><<<rows, NT, 0, s>>>(X, R, G, B, Y, S, mean, rstd, rows, d, eps)
+  const int mv = d <= NT * 8 ? 1 : (d <= NT * 16 ? 2 : 4);
+  if (rms) {
+    if (mv == 1) ST_NORM_FWD(true, 1); else if (mv == 2) ST_NORM_FWD(true, 2); else ST_NORM_FWD(true, 4);
+  } else {
+    if (mv == 1) ST_NORM_FWD(false, 1); else if (mv == 2) ST_NORM_FWD(false, 2); else ST_NORM_FWD(false, 4);
+  }
+#undef ST_NORM_FWD
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
 
 // Number of fp32 scratch elements st_norm_bwd needs for `rows` x `d`.
 ST_API long long st_norm_bwd_scratch_elems(int rows, int d) {
-  return 2ll * st::norm_bwd_grid(rows) * d;
+  return 2ll * st::norm_bwd_grid_for(rows, d) * d;
 }
 
 int st::norm_bwd_launch(int rms, const void* dy, const void* x, const void* gamma,
                         const float* mean, const float* rstd, const void* dres, void* dx,
                         float* dgamma, float* dbeta, int accumulate, float* scratch, int rows,
-                        int d, cudaStream_t s) {
+                        int d, int grid, cudaStream_t s) {
   if (int e = check_dims(rows, d)) return e;
-  const int grid = st::norm_bwd_grid(rows);
+  if (grid < 1) return st::fail(ST_ERR_INVALID, "norm_bwd: grid must be positive");
   float* pg = scratch;
   float* pb = scratch + (size_t)grid * d;
   auto DY = static_cast<const __nv_bfloat16*>(dy);
@@ -269,15 +298,18 @@ int st::norm_bwd_launch(int rms, const void* dy, const void* x, const void* gamm
   auto G = static_cast<const __nv_bfloat16*>(gamma);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (rms)
-    norm_bwd_kernel<true><<<grid, NT, 0, s>>>(DY, X, G, mean, rstd, DR, DX, pg, nullptr, rows, d);
-  else
-    norm_bwd_kernel<false><<<grid, NT, 0, s>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, rows, d);
+#define ST_NORM_BWD(RMSV, MVV, PB) norm_bwd_kernel<RMSV, MVV><<<grid, NT, 0, s>>>(DY, X, G, mean, rstd, DR, DX, pg, PB, rows, d)
+  const int mv = d <= NT * 8 ? 1 : (d <= NT * 16 ? 2 : 4);
+  if (rms) {
+    if (mv == 1) ST_NORM_BWD(true, 1, nullptr); else if (mv == 2) ST_NORM_BWD(true, 2, nullptr); else ST_NORM_BWD(true, 4, nullptr);
+  } else {
+    if (mv == 1) ST_NORM_BWD(false, 1, pb); else if (mv == 2) ST_NORM_BWD(false, 2, pb); else ST_NORM_BWD(false, 4, pb);
+  }
+#undef ST_NORM_BWD
   ST_CUDA_CHECK(cudaGetLastError());
-  const int t = 256;
-  reduce_partials_kernel<<<(d + t - 1) / t, t, 0, s>>>(pg, dgamma, grid, d, accumulate);
+  reduce_partials_kernel<<<(d + 31) / 32, 256, 0, s>>>(pg, dgamma, grid, d, accumulate);
   if (!rms && dbeta)
-    reduce_partials_kernel<<<(d + t - 1) / t, t, 0, s>>>(pb, dbeta, grid, d, accumulate);
+    reduce_partials_kernel<<<(d + 31) / 32, 256, 0, s>>>(pb, dbeta, grid, d, accumulate);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
@@ -289,7 +321,7 @@ ST_API int st_norm_bwd(int rms, const void* dy, const void* x, const void* gamma
                        int d, void* stream_v) {
   if (!scratch) return st::fail(ST_ERR_INVALID, "norm_bwd: scratch buffer is required");
   return st::norm_bwd_launch(rms, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, accumulate,
-                             scratch, rows, d, reinterpret_cast<cudaStream_t>(stream_v));
+                             scratch, rows, d, st::norm_bwd_grid_for(rows, d), reinterpret_cast<cudaStream_t>(stream_v));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -332,5 +364,5 @@ ST_API int st_norm_bwd_noalloc(int rms, const void* dy, const void* x, const voi
     g_noalloc_ptr[dev] = p;
   }
   return st::norm_bwd_launch(rms, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, accumulate,
-                             g_noalloc_ptr[dev], rows, d, reinterpret_cast<cudaStream_t>(stream_v));
+                             g_noalloc_ptr[dev], rows, d, st::norm_bwd_grid(rows), reinterpret_cast<cudaStream_t>(stream_v));
 }
