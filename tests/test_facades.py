@@ -373,3 +373,61 @@ def test_metric_registry_isolates_failures():
     assert metrics.evaluate("abc")[0][1] == 3.0
     assert metrics.is_finite([1.0, 2.0]) and not metrics.is_finite(float("inf"))
     metrics.clear_registry()
+
+
+# ---- SpiralK DSL / autotune store ----------------------------------------------------------------------------
+def test_kdsl_program_store_and_registry(tmp_path):
+    from spiraltorch_b200 import kdsl
+    ctx = kdsl.Ctx(r=1024, c=65536, k=512, sg=True, sgc=32, kc=4, tile_cols=1024, radix=4, segments=2)
+    out = kdsl.Program.parse("wg: 256; radix: log2(k);").evaluate(ctx)
+    assert out.hard == {"wg": 256, "radix": 9}
+    assert kdsl.Program.parse("radix: clamp(16, 2, 8);").evaluate(ctx).hard["radix"] == 8
+    prog = kdsl.Program.parse("""
+        let total = 0;
+        for i in 0..4 { set total = total + i; }
+        radix: total;
+        # reference heuristics file shape
+        mk:   sel(sg && (k<=128), 2, sel(k<=2048, 1, 0));
+        tile: sel(log2(c)>15.0, 2048, sel(log2(c)>13.0, 1024, 256));
+        ctile: sel(tile>=1024, tile/2, tile);
+        if c > 100000 { wg: 512; } else { wg: 128; }
+        soft(mk,   2, 0.25, sg && (k<=128));
+        soft(mk,   1, 0.20, (k>128)&&(k<=2048));
+        soft(tile, 2048, 0.20, log2(c)>15.0);
+    """)
+    out = prog.evaluate(ctx)
+    assert out.hard == {"radix": 6, "mk": 1, "tile": 2048, "ctile": 1024, "wg": 128}
+    assert [(s.field, s.value, s.weight) for s in out.soft] == [("mk", 1.0, 0.2), ("tile", 2048.0, 0.2)]
+    for bad in ("wg 256;", "bogus: 1;", "wg: foo;", "wg: 1/0;", "while true { }", "wg: (1;"):
+        with pytest.raises(kdsl.KdslError):
+            kdsl.Program.parse(bad).evaluate(ctx)
+
+    assert kdsl.wilson_lower_bound(0, 0) == 0.0
+    assert abs(kdsl.wilson_lower_bound(90, 100) - 0.8256) < 1e-3
+    assert kdsl.should_rewrite(kdsl.WilsonMetrics(10.0, 8.0, 95, 100), 0.1, 0.8)
+    assert not kdsl.should_rewrite(kdsl.WilsonMetrics(10.0, 9.9, 95, 100), 0.1, 0.8)
+    assert not kdsl.should_rewrite(kdsl.WilsonMetrics(10.0, 8.0, 3, 5), 0.1, 0.8)
+
+    store = tmp_path / "sub" / "kernels.json"
+    assert kdsl.record_best(store, "gemm", {"m": 4096, "n": 4096, "k": 1024}, 0.30, {"bn": 256, "stages": 4})
+    assert not kdsl.record_best(store, "gemm", {"m": 4096, "n": 4096, "k": 1024}, 0.35, {"bn": 128, "stages": 6})
+    assert kdsl.record_best(store, "gemm", {"m": 4096, "n": 4096, "k": 1024}, 0.25, {"bn": 128, "stages": 6})
+    kdsl.record_best(store, "gemm", {"m": 128, "n": 128, "k": 64}, 0.01, {"bn": 128, "stages": 6})
+    best = kdsl.lookup_best(store, "gemm", {"m": 4000, "n": 4096, "k": 1024})
+    assert best["params"] == {"bn": 128, "stages": 6} and best["score"] == 0.25
+    sim = kdsl.lookup_similar(store, "gemm", {"m": 100, "n": 128, "k": 64}, 2)
+    assert sim[0][0]["context"]["m"] == 128 and sim[0][1] < sim[1][1]
+    assert kdsl.lookup_best(store, "conv", {}) is None
+    for i in range(40):
+        kdsl.record_best(store, "many", {"i": i}, 1.0, {})
+    assert len(kdsl.load_store(store)["many"]["entries"]) == kdsl.BUCKET_HISTORY_LIMIT
+
+    key = kdsl.AutotuneKey(kdsl.DeviceProfile("NVIDIA B200", 0x100, 32, 227, "12.9"), kdsl.KernelProfile(7, "gemm:bf16:nt"))
+    assert key.encode() == "NVIDIA-B200|0100|32|227|12.9|0000000000000007|gemm:bf16:nt"
+    reg = kdsl.AutotuneRegistry.with_capacity(3)
+    for tf in (900.0, 1500.0, 1200.0, 1100.0):
+        reg.record(key, kdsl.TelemetrySample(tf, 5000.0, 0.1, {"bn": int(tf)}, regress=tf < 1000))
+    log = reg.log(key)
+    assert len(log) == 3 and log.best_by_tflops().tflops == 1500.0 and log.best_tile() == {"bn": 1500}
+    assert log.summary()["samples"] == 3 and log.regression_rate() == 0.0
+    assert kdsl.DeviceProfile.current().encode()
