@@ -11,7 +11,9 @@ from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, I
                       ZSpaceCoherenceWaveBlock, ZSpaceLayerNorm, ZSpaceMixer, ZSpaceSoftmax, conv_output_shape,
                       pool_output_shape)
 from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
-from . import amp, gnn, lightning, zspace
+from . import amp, fields, gnn, lightning, zspace
+from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,
+                     DynamicSchrodingerField, ToposResonator, ZRelativity, ZSpaceProjector)
 from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregation, ZSpaceGraphBatchRegressor,
                   ZSpaceGraphConvolution, ZSpaceGraphNetwork, ZSpaceGraphRegressor)
 from .lightning import (InfoNCELoss, LightningConfig, LightningReport, LightningStage, SelfSupStage, SpiralLightning)

@@ -109,3 +109,63 @@ def test_coherence_sequencer_and_vae(tmp_path):
     assert torch.allclose(again.forward_mean(data).reconstruction, vae.forward_mean(data).reconstruction)
     with pytest.raises(st.TensorError):
         vae.configure_optimizer_by_name("lion")
+
+
+def test_field_layers_match_their_definitions():
+    from spiraltorch_b200.nn import fields as F
+    v = torch.tensor([[0.5, 2.0, -3.0, 1.0]])
+    out = F.porous_mix(v, 1.0, 0.5)
+    assert out[0, 0] == 0.5 and out[0, 3] == 1.0
+    assert out[0, 1].item() == pytest.approx(1.0 * (1 - 0.125 * (1.0 / 3.0)))
+    assert out[0, 2].item() == pytest.approx(-(1 - 0.125 * 0.5))
+    assert torch.equal(F.porous_mix(v, 1.0, 0.0), torch.tensor([[0.5, 1.0, -1.0, 1.0]]))
+
+    res = F.ToposResonator("tr", 3, feedback=0.5, iterations=3, saturation=10.0)
+    x = st.Tensor(1, 3, [0.2, -0.4, 1.0])
+    assert res.forward(x).tolist()[0] == pytest.approx([0.2 * 1.75, -0.4 * 1.75, 1.75])     # 1 + 0.5 + 0.25
+
+    kg = F.DynamicKleinGordonField("kg", 4, dt=0.1, stiffness=1.0, self_interaction=0.2)
+    s = torch.tensor([[0.1, 0.4, -0.2, 0.3, 0.0, 0.1, 0.0, -0.1]])
+    field, mom = s[:, :4], s[:, 4:]
+    force = lambda f: (torch.roll(f, 1, 1) - 2 * f + torch.roll(f, -1, 1)) - f - 0.2 * f ** 3   # noqa: E731
+    half = mom + 0.05 * force(field)
+    nf = field + 0.1 * half
+    expect = torch.cat([nf, half + 0.05 * force(nf)], 1)
+    assert torch.allclose(kg.forward(st.Tensor._wrap(s)).torch(), expect, atol=1e-6)
+    with pytest.raises(st.TensorError):
+        kg.forward(st.Tensor.zeros(1, 4))
+
+    hj = F.DynamicHamiltonJacobiField("hj", 4, dt=0.1, kinetic=2.0, viscosity=0.05)
+    a = torch.tensor([[0.0, 1.0, 0.0, -1.0]])
+    grad = (torch.roll(a, -1, 1) - torch.roll(a, 1, 1)) * 0.5
+    lap = torch.roll(a, 1, 1) - 2 * a + torch.roll(a, -1, 1)
+    assert torch.allclose(hj.forward(st.Tensor._wrap(a)).torch(), a - 0.1 * grad ** 2 + 0.05 * lap, atol=1e-6)
+
+    sch = F.DynamicSchrodingerField("s", 2, dt=0.5, hopping=0.0, damping=0.2)
+    sch.potential.value.copy_(torch.tensor([[1.0, 2.0]]))
+    y = sch.forward(st.Tensor(1, 2, [1.0, 2.0])).torch()
+    d = math.exp(-0.05)
+    assert torch.allclose(y, torch.tensor([[d * math.cos(0.5), 2 * d * math.cos(1.0), -d * math.sin(0.5), -2 * d * math.sin(1.0)]]), atol=1e-6)
+    hop = F.DynamicSchrodingerField("h", 2, dt=1.0, hopping=0.3).forward(st.Tensor(1, 2, [1.0, 0.0])).torch()
+    assert hop[0, 0].item() == pytest.approx(math.cos(0.3)) and hop[0, 3].item() == pytest.approx(-math.sin(0.3))
+
+    cw = F.ContinuousWavelet("cw", 32, scales=3)
+    sig = torch.cos(torch.arange(32.0) * 0.8).reshape(1, -1)
+    w = cw.forward(st.Tensor._wrap(sig))
+    assert w.shape() == (1, 3) and float(w.torch().abs().max()) > 0
+    proj = F.ZSpaceProjector("zp", 4, 3, curvature=-4.0)
+    out = proj.forward(st.Tensor._wrap(torch.randn(5, 4) * 50)).torch()
+    assert bool((out.norm(dim=1) < 0.5).all())
+    rel = F.ZRelativity("zr", 3)
+    rel.rapidity.value.copy_(torch.tensor([[0.0, 1.0, -1.0]]))
+    g = math.sqrt(1 - math.tanh(1.0) ** 2)
+    assert rel.forward(st.Tensor(1, 3, [1.0, 1.0, 1.0])).tolist()[0] == pytest.approx([1.0, g, g])
+    c1 = F.Conv1d("c1", 2, 3, 3, 8, padding=1)
+    xin = torch.randn(4, 16)
+    ref = torch.nn.functional.conv1d(xin.reshape(4, 2, 8), c1.weight.value.reshape(3, 2, 3), c1.bias.value.flatten(), padding=1)
+    assert torch.allclose(c1.forward(st.Tensor._wrap(xin)).torch(), ref.reshape(4, 24), atol=1e-5)
+    # backward through the module protocol reaches the parameters
+    for layer, xx in ((kg, st.Tensor._wrap(s)), (res, x), (c1, st.Tensor._wrap(xin))):
+        yy = layer.forward(xx)
+        gx = layer.backward(xx, st.Tensor._wrap(torch.ones_like(yy.torch())))
+        assert gx.shape() == xx.shape() and any(p.accumulators() for p in layer.parameters())
