@@ -30,17 +30,24 @@ using namespace st::gemm;
 constexpr int BN = 256;
 constexpr int STAGES = 4;
 
-template <bool B_MN, int COMM>
+// The all-gather variant runs a 3-stage operand pipeline so that the push ring (and its barriers)
+// fits behind the GEMM's shared memory; it has two extra warps.
+constexpr int AG_STAGES = 3;
+constexpr int AG_EXTRA_SMEM = AG_RING_SLOTS * AG_RING_CHUNK + 64;
+
+template <bool B_MN, int COMM, int ST = STAGES>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, const CUtensorMap& tmA_local,
            const GemmParams& p, const GemmComm& cm, int grid, cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, STAGES, false, B_MN, COMM>;
+  using L = SmemLayout<BN, ST>;
+  constexpr int SMEM = L::TOTAL + ((COMM == COMM_AG && ST == AG_STAGES) ? AG_EXTRA_SMEM : 0);
+  static_assert(SMEM <= 232448, "dynamic shared memory above the 227 KB limit");
+  auto kern = gemm_bf16_kernel<BN, ST, false, B_MN, COMM>;
   static bool configured = false;
   if (!configured) {
-    ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, tmA_local, p, cm);
+  kern<<<grid, COMM == COMM_AG ? NUM_THREADS_AG : NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmC, tmA_local, p, cm);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
@@ -78,20 +85,19 @@ struct StAgGemmArgs {
   int T, N, K;
   int b_mn, act;
   float alpha;
-  int sub_per_chunk;   // arrival-flag granularity per rank shard
-  int comm_ctas;       // CTAs that only push (taken from the SM budget)
-  int slot_enter, slot_arrive;
-  unsigned arrive_target;  // peer-store path: this launch's epoch; multicast path: cumulative arrivals
-                           // (launches so far * st_ag_arrivals_per_launch) of the counter area
-  unsigned long long trace;  // optional device buffer of [grid][4] 64-bit time stamps, or 0
+  int sub_per_chunk;   // arrival granularity per rank shard (1, 2, 4, 8 or 16)
+  int comm_ctas;       // unused (every CTA pushes a slice of the shard)
+  int slot_enter, slot_arrive;   // slot_arrive: counter area of THIS sub_per_chunk value (world * 16 words)
+  unsigned arrive_target;  // cumulative arrivals per counter: launches with this sub_per_chunk so far
+                           // times st_ag_arrivals_per_launch()
+  unsigned long long trace;  // optional device buffer of [2 * grid][4] 64-bit time stamps, or 0
+  int stages;                // 0: choose by world size; 3 or 4: force that operand-pipeline depth
 };
 
-// Communication CTAs a launch really uses (= arrivals each sub-chunk counter receives per launch
-// on the multicast path).
-ST_API int st_ag_arrivals_per_launch(int comm_ctas) {
-  int sms = st::sm_count();
-  if (sms <= 0) sms = 148;
-  return comm_ctas > sms / 2 ? sms / 2 : comm_ctas;
+// Arrivals every (source, sub-chunk) counter receives per launch: one per CTA of the grid.
+ST_API int st_ag_arrivals_per_launch() {
+  const int sms = st::sm_count();
+  return sms > 0 ? sms : 148;
 }
 
 ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
@@ -104,7 +110,6 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   if (a->sub_per_chunk < 1 || rows % (a->sub_per_chunk * BM) != 0)
     return st::fail(ST_ERR_INVALID, "ag_gemm: shard rows must be a multiple of sub_per_chunk*128");
   if (a->K % 8 || a->ldb % 8) return st::fail(ST_ERR_INVALID, "ag_gemm: K and ldb must be multiples of 8");
-  if (a->comm_ctas < 1) return st::fail(ST_ERR_INVALID, "ag_gemm: needs at least one communication CTA");
   const void* gathered = reinterpret_cast<const void*>(a->gather_peers[a->g.rank]);
   CUtensorMap tmA, tmB;
   if (!make_maps(&tmA, &tmB, gathered, reinterpret_cast<const void*>(a->B), a->T, a->N, a->K, a->K, a->ldb, a->b_mn))
@@ -129,17 +134,12 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   cm.slot_arrive = a->slot_arrive;
   cm.arrive_target = a->arrive_target;
   cm.trace = reinterpret_cast<unsigned long long*>(a->trace);
-  cm.sub_major = a->gather_mc ? 1 : 0;   // multicast delivers sub-chunk s of every rank at the same time
+  cm.sub_major = 0;
   cm.src_shard = reinterpret_cast<const __nv_bfloat16*>(a->x_shard);
   for (int i = 0; i < st::kMaxRanks; ++i) cm.gather_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->gather_peers[i]);
   cm.gather_mc = reinterpret_cast<__nv_bfloat16*>(a->gather_mc);
-  const int tiles = (a->T / BM) * ((a->N + BN - 1) / BN);
-  int comm = a->comm_ctas;
-  int sms = st::sm_count();
-  if (comm > sms / 2) comm = sms / 2;
-  int gemm_ctas = sms - comm;
-  if (gemm_ctas > tiles) gemm_ctas = tiles;
-  cm.gemm_ctas = gemm_ctas;
+  const int grid = st_ag_arrivals_per_launch();   // every SM pushes, whether or not it has tiles
+  cm.gemm_ctas = grid;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   OutMaps tmC;
   memset(&tmC, 0, sizeof(tmC));
@@ -161,8 +161,15 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
                      dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return ST_ERR_CUDA;
   }
-  if (a->b_mn) return launch<true, COMM_AG>(tmA, tmB, tmC, tmA_local, p, cm, gemm_ctas + comm, stream);
-  return launch<false, COMM_AG>(tmA, tmB, tmC, tmA_local, p, cm, gemm_ctas + comm, stream);
+  // communication-bound (many ranks, thin per-rank GEMM): deeper push ring, 3 operand stages;
+  // compute-bound: full 4-stage operand pipeline, small ring
+  const bool comm_bound = a->stages == 3 || (a->stages == 0 && W >= 6);
+  if (comm_bound) {
+    if (a->b_mn) return launch<true, COMM_AG, AG_STAGES>(tmA, tmB, tmC, tmA_local, p, cm, grid, stream);
+    return launch<false, COMM_AG, AG_STAGES>(tmA, tmB, tmC, tmA_local, p, cm, grid, stream);
+  }
+  if (a->b_mn) return launch<true, COMM_AG, 4>(tmA, tmB, tmC, tmA_local, p, cm, grid, stream);
+  return launch<false, COMM_AG, 4>(tmA, tmB, tmC, tmA_local, p, cm, grid, stream);
 }
 
 struct StGemmRsArgs {

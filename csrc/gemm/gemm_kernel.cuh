@@ -3,13 +3,13 @@
 //
 // COMM selects what else the launch does:
 //   COMM_NONE  C = epilogue(alpha * A·Bᵀ)
-//   COMM_AG    all-gather → GEMM.  A is the gathered activation [T, K]; its row chunks are
-//              produced by `comm_ctas` CTAs of the SAME launch on every rank, which push the
-//              local shard into every rank's gather buffer (bulk copies through shared
-//              memory, plain peer writes over NVLink, destinations in ring order) and count
-//              per-sub-chunk arrivals.  The TMA producer of a GEMM CTA waits (bounded) for
-//              the counter of the rows it is about to load; tiles are ordered local chunk
-//              first, then in ring order.
+//   COMM_AG    all-gather → GEMM.  A is the gathered activation [T, K].  Every CTA of the launch
+//              has two extra warps that push a 1/gridDim slice of this rank's shard into every
+//              rank's gather buffer (bulk copies through a small shared-memory ring, plain peer
+//              writes over NVLink, destinations in ring order) and count per-sub-chunk arrivals,
+//              while its other warps run GEMM tiles.  The TMA producer waits (bounded) for the
+//              counter of the rows it is about to load; the local rows are read from the shard
+//              itself; tiles are ordered local chunk first, then in ring order.
 //   COMM_RS    GEMM → reduce-scatter.  The epilogue writes each partial tile straight into
 //              the staging slot of the rank that owns those rows (peer stores over NVLink),
 //              then bumps that owner's per-row-block counter; tiles are ordered so that the
@@ -28,6 +28,9 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int NUM_THREADS_AG = 256;  // all-gather variant: + warp 6 (shard push) and warp 7 (arrival publisher)
+constexpr int AG_RING_CHUNK = 16384;  // bytes per bulk copy of the push ring
+constexpr int AG_RING_SLOTS = 3;      // the ring sits behind the barriers of the 3-stage GEMM layout
 
 enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_GELU_BWD = 3, ACT_RELU_BWD = 4 };
 enum Comm : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
@@ -163,7 +166,7 @@ __device__ __forceinline__ void epilogue_bar() {
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int COMM>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(COMM == COMM_AG ? NUM_THREADS_AG : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ OutMaps tmC, const __grid_constant__ CUtensorMap tmA_local,
                  const GemmParams p, const GemmComm cm) {
@@ -174,217 +177,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // ------------------------------------------------------------------------------------------
-  // AG: the first `n_comm` CTAs of the grid push this rank's shard into every rank's gather
-  // buffer and publish arrival flags; the remaining CTAs run the GEMM tiles.
-  //
-  // Schedule.  The shard is cut into `sub_per_chunk` sub-chunks; a work item is one sub-chunk
-  // for one destination.  Items are ordered destination-major in ring order (rank-1, rank-2,
-  // ..., finally this rank's own buffer) and dealt round-robin to the communication CTAs: in
-  // every phase the W senders address W different receivers, and a receiver gets the chunks in
-  // the order in which its GEMM tiles consume them (rank+1 first).  Thread 0 of a CTA drives
-  // the copy, local HBM → shared-memory ring (bulk load) → destination (bulk store, plain peer
-  // writes); thread 32 publishes the flag of an item once its stores are complete, so that the
-  // system-scope release never stalls the copy pipeline.
-  // ------------------------------------------------------------------------------------------
-  int gemm_bid = blockIdx.x;
-  if constexpr (COMM == COMM_AG) {
-    const int n_comm = gridDim.x - cm.gemm_ctas;
-    gemm_bid = static_cast<int>(blockIdx.x) - n_comm;
-    if (gemm_bid < 0) {
-      __shared__ volatile int s_done_items;   // items of this CTA whose stores are complete
-      __shared__ volatile int s_finished;     // the copy thread has returned from its loop
-      if (threadIdx.x == 0) {
-        s_done_items = 0;
-        s_finished = 0;
-      }
-      __syncthreads();
-      const int W = cm.g.world, R = cm.g.rank;
-      const int cta = blockIdx.x;
-      const int SUBS = cm.sub_per_chunk;
-      if (cm.gather_mc) {
-        // ---- NVLS path: one multimem.st reaches every rank's gather buffer, so this GPU sends
-        // its shard once.  Every communication CTA stores the same 1/n_comm slice of each
-        // sub-chunk (warps 0-4); warp 5 lane 0 counts the arrivals on every rank once the five
-        // data warps have stored their part, so the data warps never wait for a fence.
-        __shared__ int s_cnt[kMaxSubChunks];
-        __shared__ int s_enter_ok;
-        if (threadIdx.x < kMaxSubChunks) s_cnt[threadIdx.x] = 0;
-        if (threadIdx.x == 0) {
-          bool ok = true;
-          if (cta == 0) {
-            fence_sys();
-            for (int q = 0; q < W; ++q) st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
-          }
-          for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
-          if (!ok) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
-          s_enter_ok = ok ? 1 : 0;
-        }
-        __syncthreads();
-        if (!s_enter_ok) return;
-        constexpr int DATA_WARPS = 5, DT = DATA_WARPS * 32, U = 8;
-        const long long vecs = (long long)(cm.rows_per_chunk / SUBS) * p.K / 8;     // 16-byte vectors per sub-chunk
-        const long long slice = (vecs + n_comm - 1) / n_comm;
-        const long long lo = min(vecs, (long long)cta * slice), hi = min(vecs, lo + slice);
-        if (warp < DATA_WARPS) {
-          const uint4* src0 = reinterpret_cast<const uint4*>(cm.src_shard);
-          uint4* dst0 = reinterpret_cast<uint4*>(cm.gather_mc) + (long long)R * cm.rows_per_chunk * p.K / 8;
-          for (int sc = 0; sc < SUBS; ++sc) {
-            const uint4* src = src0 + sc * vecs;
-            uint4* dst = dst0 + sc * vecs;
-            for (long long i0 = lo + threadIdx.x; i0 < hi; i0 += (long long)DT * U) {
-              uint4 v[U];
-#pragma unroll
-              for (int u = 0; u < U; ++u)
-                if (i0 + (long long)u * DT < hi) v[u] = src[i0 + (long long)u * DT];
-#pragma unroll
-              for (int u = 0; u < U; ++u)
-                if (i0 + (long long)u * DT < hi) multimem_st_v4(dst + i0 + (long long)u * DT, v[u]);
-            }
-            __syncwarp();
-            if (lane == 0) {
-              __threadfence_block();
-              atomicAdd(&s_cnt[sc], 1);
-            }
-          }
-        } else if (lane == 0) {
-          bool ok = true;
-          for (int sc = 0; sc < SUBS && ok; ++sc) {
-            const uint64_t t0 = globaltimer_ns();
-            while (*reinterpret_cast<volatile int*>(&s_cnt[sc]) < DATA_WARPS) {
-              if (globaltimer_ns() - t0 > ST_WAIT_TIMEOUT_NS) { ok = false; break; }
-              __nanosleep(32);
-            }
-            if (!ok) break;
-            __threadfence_block();
-            fence_sys();
-            for (int q = 0; q < W; ++q)
-              red_relaxed_sys_add(cm.g.signals[(R + q) % W] + cm.slot_arrive + R * kMaxSubChunks + sc, 1u);
-          }
-          if (!ok) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA605u);
-          // words of sub-chunk slots this shape does not use advance too: one cumulative target
-          // then serves every shape launched through this signal area
-          for (int sc = SUBS; sc < kMaxSubChunks && ok; ++sc)
-            for (int q = 0; q < W; ++q)
-              red_relaxed_sys_add(cm.g.signals[q] + cm.slot_arrive + R * kMaxSubChunks + sc, 1u);
-        }
-        return;
-      }
-      if (threadIdx.x != 0 && threadIdx.x != 32) return;
-      const int items = W * SUBS;
-      const int my_items = (items - cta + n_comm - 1) / n_comm;     // items cta, cta + n_comm, ...
-      auto dest_of = [&](int item) {
-        const int q = item / SUBS;
-        return q < W - 1 ? (R - 1 - q + W) % W : R;
-      };
-      if (threadIdx.x == 32) {
-        // ---- publisher ----
-        int sent = 0;
-        const uint64_t t0 = globaltimer_ns();
-        for (;;) {
-          const int fin = s_finished;
-          const int d = s_done_items;
-          if (sent < d) {
-            __threadfence_block();
-            fence_proxy_async_global();
-            for (; sent < d; ++sent) {
-              const int item = cta + sent * n_comm;
-              st_release_sys(cm.g.signals[dest_of(item)] + cm.slot_arrive + R * kMaxSubChunks + item % SUBS,
-                             cm.arrive_target);
-            }
-          }
-          if (sent >= my_items || (fin && sent >= s_done_items)) break;
-          if (globaltimer_ns() - t0 > (uint64_t)(W + 2) * ST_WAIT_TIMEOUT_NS) break;   // the copy thread reports the cause
-          __nanosleep(64);
-        }
-        return;
-      }
-      // ---- copy thread ----
-      bool ok = true;
-      if (cm.trace) cm.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
-      if (cta == 0) {
-        fence_sys();
-        for (int q = 0; q < W; ++q) st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
-      }
-      // peers must have left the previous launch that read this gather buffer
-      for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
-      if (!ok) {
-        report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
-        s_finished = 1;
-        return;
-      }
-      if (cm.trace) cm.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
-      constexpr int NB = 12;           // ring buffers
-      constexpr int LOADS = 6;         // bulk loads kept in flight; the other NB - LOADS buffers may
-                                       // be held by stores that are still being read
-      constexpr int LAG = 16;          // newest stores that may be incomplete when older ones are published
-      constexpr uint32_t CH = 16384;
-      const long long sub_bytes = (long long)(cm.rows_per_chunk / SUBS) * p.K * 2;
-      const int n_ch = (int)((sub_bytes + CH - 1) / CH);            // chunks per item
-      uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + NB * CH);
-      volatile int local_abort = 0;
-      for (int i = 0; i < NB; ++i) mbar_init(smem_u32(&cbar[i]), 1);
-      fence_barrier_init();
-      const char* src_base = reinterpret_cast<const char*>(cm.src_shard);
-      const long long dst_base = (long long)R * cm.rows_per_chunk * p.K * 2;
-      const int total = my_items * n_ch;
-      // chunk c of this CTA → (item, byte offset inside the shard, size)
-      auto chunk_of = [&](int c, int& item, uint32_t& sz) {
-        const int k = c / n_ch, j = c - k * n_ch;
-        item = cta + k * n_comm;
-        const long long o = (long long)j * CH;
-        sz = (uint32_t)min((long long)CH, sub_bytes - o);
-        return (long long)(item % SUBS) * sub_bytes + o;
-      };
-      auto issue_load = [&](int c) {
-        const int b = c % NB;
-        int item;
-        uint32_t sz;
-        const long long off = chunk_of(c, item, sz);
-        mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
-        bulk_load_g2s(smem_u32(smem + b * CH), src_base + off, sz, smem_u32(&cbar[b]));
-      };
-      for (int c = 0; c < total && c < LOADS; ++c) issue_load(c);
-      uint32_t phase_bits = 0;
-      for (int c = 0; c < total; ++c) {
-        const int b = c % NB;
-        if (!mbar_wait(smem_u32(&cbar[b]), (phase_bits >> b) & 1u, &local_abort)) { ok = false; break; }
-        phase_bits ^= (1u << b);
-        int item;
-        uint32_t sz;
-        const long long off = chunk_of(c, item, sz);
-        bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[dest_of(item)]) + dst_base + off,
-                       smem_u32(smem + b * CH), sz);
-        tma_store_commit();
-        // chunk c + LOADS goes into the buffer last used by chunk c + LOADS - NB: all but the
-        // newest NB - LOADS store groups must have finished reading shared memory
-        if (c + LOADS < total) {
-          tma_store_wait_read<NB - LOADS>();
-          issue_load(c + LOADS);
-        }
-        if (c >= LAG) {
-          tma_store_wait<LAG>();        // every store up to chunk c - LAG is complete
-          const int cc = c - LAG;
-          if (cc % n_ch == n_ch - 1) {
-            fence_proxy_async_global();
-            __threadfence_block();
-            s_done_items = cc / n_ch + 1;
-          }
-        }
-      }
-      tma_store_wait<0>();
-      if (!ok) {
-        report_error(p.err, ERR_MBAR_TIMEOUT, 0xA604u);
-      } else {
-        fence_proxy_async_global();
-        __threadfence_block();
-        s_done_items = my_items;
-      }
-      if (cm.trace) cm.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
-      s_finished = 1;
-      return;
-    }
-  }
+  const int gemm_bid = blockIdx.x;
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
   uint64_t* full_bar = bars;
@@ -399,7 +192,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_per_batch = tiles_m * tiles_n;
   const int total_tiles = tiles_per_batch * p.batch;
   const int k_blocks = (p.K + BK - 1) / BK;
-  const int grid_stride = (COMM == COMM_AG) ? cm.gemm_ctas : gridDim.x;
+  const int grid_stride = gridDim.x;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                  : (2 * BN <= 256) ? 256 : 512;
 
@@ -413,6 +206,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(smem_u32(&tempty_bar[a]), 4);
     }
     *abort_flag = 0;
+    if constexpr (COMM == COMM_AG) {
+      tmem_slot[2] = 0;   // items whose stores are complete (push warp → publisher warp)
+      tmem_slot[3] = 0;   // push warp has finished
+    }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -557,10 +354,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------- epilogue warps -----------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int iter = 0;
+    // staging buffers per warp: two, except in the 4-stage all-gather variant, whose push ring takes
+    // the upper half of the staging area
+    constexpr int CSB = (COMM == COMM_AG && STAGES == 4) ? 1 : 2;
     int store_seq = 0;          // TMA stores issued by this warp (selects the staging buffer)
     int tile_seq0 = 0;          // value of store_seq when the current tile started
     constexpr int kPubBatch = 3;
@@ -616,7 +416,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const bool to_owner = (COMM == COMM_RS) && !cm.rs_pull;
           const CUtensorMap* om = &tmC.m[to_owner ? owner : 0];
           const int r0 = (to_owner ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
-          tma_store_3d(om, smem_u32(smem + L::CSTAGE_OFFSET + (quad * 2 + (store_seq & 1)) * 4096),
+          tma_store_3d(om, smem_u32(smem + L::CSTAGE_OFFSET + (quad * CSB + (store_seq % CSB)) * 4096),
                        n0 + (c >> 1) * 64, r0, b);
           tma_store_commit();
         }
@@ -629,9 +429,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
-        if (p.use_tma_store && (c & 1) == 0 && store_seq >= 2) {
-          // the staging buffer about to be rewritten was handed to TMA two stores ago
-          if (lane == 0) tma_store_wait_read<1>();
+        if (p.use_tma_store && (c & 1) == 0 && store_seq >= CSB) {
+          // the staging buffer about to be rewritten was handed to TMA CSB stores ago
+          if (lane == 0) tma_store_wait_read<CSB - 1>();
           __syncwarp();
         }
         if (!row_ok) {
@@ -714,7 +514,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.use_tma_store) {
           // stage this warp's 32 rows x 64 columns (128-byte swizzle) and store them by TMA
           const int half = c & 1;
-          uint8_t* cs = smem + L::CSTAGE_OFFSET + (quad * 2 + (store_seq & 1)) * 4096;
+          uint8_t* cs = smem + L::CSTAGE_OFFSET + (quad * CSB + (store_seq % CSB)) * 4096;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 o;
@@ -926,6 +726,134 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+    }
+  } else if constexpr (COMM == COMM_AG) {
+    // ---------------------------------------------------------------------------------------
+    // All-gather: EVERY CTA pushes its 1/gridDim slice of this rank's shard while its other warps
+    // run GEMM tiles (one SM sustains only ~20 GB/s of peer writes, so the push is spread over
+    // all of them instead of a few dedicated CTAs).  A work item is one sub-chunk for one
+    // destination; items go destination-major in ring order (rank-1, rank-2, ..., own buffer
+    // last), so in every phase the W senders address W different receivers and a receiver gets
+    // the chunks in the order its GEMM tiles consume them.  Warp 6 lane 0 drives bulk copies
+    // local HBM → shared-memory ring → destination; warp 7 lane 0 adds one arrival per finished
+    // item to the destination's counter, so the system-scope release never stalls the copies.
+    // ---------------------------------------------------------------------------------------
+    volatile int* s_done_items = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    volatile int* s_finished = reinterpret_cast<volatile int*>(tmem_slot + 3);
+    const int W = cm.g.world, R = cm.g.rank;
+    const int SUBS = cm.sub_per_chunk;
+    const int items = W * SUBS;
+    auto dest_of = [&](int item) {
+      const int q = item / SUBS;
+      return q < W - 1 ? (R - 1 - q + W) % W : R;
+    };
+    if (warp == 7 && lane == 0) {
+      int sent = 0;
+      const uint64_t t0 = globaltimer_ns();
+      for (;;) {
+        const int fin = *s_finished;
+        const int d = *s_done_items;
+        if (sent < d) {
+          // one fence for everything that completed since the last look, then plain atomics
+          __threadfence_block();
+          fence_proxy_async_global();
+          fence_sys();
+          for (; sent < d; ++sent)
+            red_relaxed_sys_add(cm.g.signals[dest_of(sent)] + cm.slot_arrive + R * kMaxSubChunks + sent % SUBS, 1u);
+        }
+        if (sent >= items || (fin && sent >= *s_done_items)) break;
+        if (globaltimer_ns() - t0 > (uint64_t)(W + 2) * ST_WAIT_TIMEOUT_NS) break;   // the copy thread reports the cause
+        __nanosleep(64);
+      }
+    } else if (warp == 6 && lane == 0) {
+      bool ok = true;
+      if (cm.trace) cm.trace[(gridDim.x + blockIdx.x) * 4 + 0] = globaltimer_ns();
+      if (blockIdx.x == 0) {
+        fence_sys();
+        for (int q = 0; q < W; ++q) st_relaxed_sys(cm.g.signals[q] + cm.slot_enter + R, cm.g.epoch);
+      }
+      // peers must have left the previous launch that read this gather buffer
+      for (int q = 0; q < W && ok; ++q) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_enter + q, cm.g.epoch);
+      if (cm.trace) cm.trace[(gridDim.x + blockIdx.x) * 4 + 1] = globaltimer_ns();
+      if (!ok) {
+        report_error(p.err, ERR_FLAG_TIMEOUT, 0xA600u);
+      } else {
+        // 3-stage variant (communication-bound shapes): 3 x 16 KB behind the barriers; 4-stage variant
+        // (compute-bound shapes): 2 x 8 KB in the upper half of the output staging area
+        constexpr int NB = (STAGES == 4) ? 2 : AG_RING_SLOTS;
+        constexpr uint32_t CH = (STAGES == 4) ? 8192 : AG_RING_CHUNK;
+        uint8_t* ring = (STAGES == 4) ? smem + L::CSTAGE_OFFSET + 16384 : smem + L::BAR_OFFSET + 256;
+        uint64_t* cbar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET + 128);
+        const long long sub_bytes = (long long)(cm.rows_per_chunk / SUBS) * p.K * 2;
+        long long slice = (sub_bytes + gridDim.x - 1) / gridDim.x;
+        slice = (slice + 127) & ~127ll;
+        const long long lo = min(sub_bytes, (long long)blockIdx.x * slice);
+        const long long hi = min(sub_bytes, lo + slice);
+        const int n_ch = (int)((hi - lo + CH - 1) / CH);     // chunks per item for this CTA (may be 0)
+        if (n_ch == 0) {
+          *s_done_items = items;                              // nothing to copy: the arrivals still count
+        } else {
+          volatile int local_abort = 0;
+          for (int i = 0; i < NB; ++i) mbar_init(smem_u32(&cbar[i]), 1);
+          fence_barrier_init();
+          const char* src_base = reinterpret_cast<const char*>(cm.src_shard);
+          const long long dst_base = (long long)R * cm.rows_per_chunk * p.K * 2;
+          const int total = items * n_ch;
+          auto chunk_of = [&](int c, int& item, uint32_t& sz) {
+            item = c / n_ch;
+            const long long o = lo + (long long)(c - item * n_ch) * CH;
+            sz = (uint32_t)min((long long)CH, hi - o);
+            return (long long)(item % SUBS) * sub_bytes + o;
+          };
+          auto issue_load = [&](int c) {
+            int item;
+            uint32_t sz;
+            const long long off = chunk_of(c, item, sz);
+            const int b = c % NB;
+            mbar_arrive_expect_tx(smem_u32(&cbar[b]), sz);
+            bulk_load_g2s(smem_u32(ring + b * CH), src_base + off, sz, smem_u32(&cbar[b]));
+          };
+          // one load ahead of the store being issued; a buffer is reloaded once the store that
+          // used it has finished reading shared memory (NB - 1 stores may be in flight)
+          issue_load(0);
+          uint32_t phase_bits = 0;
+          for (int c = 0; c < total; ++c) {
+            const int b = c % NB;
+            if (c + 1 < total) {
+              if (c + 1 >= NB) tma_store_wait_read<NB - 2>();   // store c + 1 - NB has released its buffer
+              issue_load(c + 1);
+            }
+            if (!mbar_wait(smem_u32(&cbar[b]), (phase_bits >> b) & 1u, &local_abort)) { ok = false; break; }
+            phase_bits ^= (1u << b);
+            int item;
+            uint32_t sz;
+            const long long off = chunk_of(c, item, sz);
+            bulk_store_s2g(reinterpret_cast<char*>(cm.gather_peers[dest_of(item)]) + dst_base + off,
+                           smem_u32(ring + b * CH), sz);
+            tma_store_commit();
+            if (c >= NB - 1) {
+              tma_store_wait<NB - 1>();                       // every store up to chunk c - (NB - 1) is complete
+              const int cc = c - (NB - 1);
+              if (cc % n_ch == n_ch - 1) {
+                fence_proxy_async_global();
+                __threadfence_block();
+                *s_done_items = cc / n_ch + 1;
+              }
+            }
+          }
+          tma_store_wait<0>();
+          if (!ok) {
+            report_error(p.err, ERR_MBAR_TIMEOUT, 0xA604u);
+          } else {
+            fence_proxy_async_global();
+            __threadfence_block();
+            *s_done_items = items;
+          }
+        }
+      }
+      if (cm.trace) cm.trace[(gridDim.x + blockIdx.x) * 4 + 2] = globaltimer_ns();
+      __threadfence_block();
+      *s_finished = 1;
     }
   }
 

@@ -50,7 +50,7 @@ class _AgGemmArgs(ctypes.Structure):
                 ("b_mn", ctypes.c_int), ("act", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("sub_per_chunk", ctypes.c_int), ("comm_ctas", ctypes.c_int),
                 ("slot_enter", ctypes.c_int), ("slot_arrive", ctypes.c_int), ("arrive_target", ctypes.c_uint),
-                ("trace", ctypes.c_ulonglong)]
+                ("trace", ctypes.c_ulonglong), ("stages", ctypes.c_int)]
 
 
 class _GemmRsArgs(ctypes.Structure):
@@ -158,7 +158,7 @@ class FusedTPContext(TPContext):
     """Tensor-parallel context whose column-/row-parallel linears run as fused kernels."""
 
     def __init__(self, group: Optional[dist.ProcessGroup], device=None, comm_ctas: Optional[int] = None,
-                 sub_per_chunk: int = 16):
+                 sub_per_chunk: int = 4):
         super().__init__(group, mode="fused")
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = device
@@ -172,12 +172,14 @@ class FusedTPContext(TPContext):
         self.comm_ctas = comm_ctas
         self.sub_per_chunk = sub_per_chunk
         self.slot_enter = self.signals.alloc(MAX_RANKS)
-        self.slot_arrive = self.signals.alloc(MAX_RANKS * 16)       # epoch-valued flags (peer-store path)
-        self.slot_arrive_cnt = self.signals.alloc(MAX_RANKS * 16)   # cumulative counters (multicast path)
-        self._ag_arrivals = 0
+        # arrival counters of the all-gather: one area (world x 16 words) and one cumulative count per
+        # sub-chunk granularity, because a launch only touches the words of its own granularity
+        self.slot_arrive = {s: self.signals.alloc(MAX_RANKS * 16) for s in (1, 2, 4, 8, 16)}
+        self._ag_arrivals = {s: 0 for s in (1, 2, 4, 8, 16)}
         # NVLS variants (multimem.st push, multimem.ld_reduce pull) are correct but measured slower
         # than the peer-store paths at 4 GPUs; they stay opt-in
         self.use_nvls = os.environ.get("ST_TP_NVLS", "0") == "1"
+        self.ag_stages = int(os.environ.get("ST_TP_AG_STAGES", "0"))   # 0 = by world size
         self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
@@ -215,11 +217,12 @@ class FusedTPContext(TPContext):
         sub = self.sub_per_chunk
         while sub > 1 and rows % (sub * 128) != 0:
             sub //= 2
+        assert sub in self.slot_arrive, "sub_per_chunk must be a power of two up to 16"
         a = _AgGemmArgs()
         a.g = self.signals.next_group()
         a.x_shard = x_shard.data_ptr()
         a.gather_peers = gbuf.peers_array()
-        a.gather_mc = gbuf.mc() if (self.use_nvls and self.world > 1) else 0
+        a.gather_mc = 0
         a.B, a.C = w.data_ptr(), y.data_ptr()
         a.bias = 0 if bias is None else bias.data_ptr()
         a.aux_out = 0 if aux_out is None else aux_out.data_ptr()
@@ -234,11 +237,9 @@ class FusedTPContext(TPContext):
         a.sub_per_chunk, a.comm_ctas = sub, self.comm_ctas
         a.slot_enter = self.slot_enter
         a.trace = 0 if self.trace is None else self.trace.data_ptr()
-        if a.gather_mc:
-            self._ag_arrivals += native.lib().st_ag_arrivals_per_launch(ctypes.c_int(self.comm_ctas))
-            a.slot_arrive, a.arrive_target = self.slot_arrive_cnt, self._ag_arrivals & 0xFFFFFFFF
-        else:
-            a.slot_arrive, a.arrive_target = self.slot_arrive, a.g.epoch
+        a.stages = self.ag_stages
+        self._ag_arrivals[sub] += native.lib().st_ag_arrivals_per_launch()
+        a.slot_arrive, a.arrive_target = self.slot_arrive[sub], self._ag_arrivals[sub] & 0xFFFFFFFF
         native.check(native.lib().st_ag_gemm(ctypes.byref(a), native.stream_ptr(x_shard.device)), "st_ag_gemm")
         launch_count += 1
         self.bytes_gathered += T * K * 2

@@ -205,7 +205,7 @@ def main():
         start, in us) the slowest CTA finished each phase."""
         if os.environ.get("ST_FUSED_TRACE", "0") != "1":
             return
-        fused.trace = torch.zeros(160, 4, dtype=torch.int64, device=dev)
+        fused.trace = torch.zeros(320, 4, dtype=torch.int64, device=dev)
         dist.barrier()
         torch.cuda.synchronize()
         fn()
