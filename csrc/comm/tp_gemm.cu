@@ -185,8 +185,7 @@ struct StGemmRsArgs {
   float alpha;
   int slot_enter, slot_done;
   unsigned done_target;                          // cumulative warp arrivals expected per row block
-  unsigned long long stage_mc;                   // multicast alias of the staging area or 0: when set,
-                                                 // partial tiles stay local and owners pull the sum
+  unsigned long long stage_mc;                   // unused
   unsigned long long trace;                      // optional [grid][4] 64-bit time stamps, or 0
 };
 
@@ -227,22 +226,11 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
   memset(&tmC, 0, sizeof(tmC));
   p.use_tma_store = 1;
   const int rows = a->T / W;
-  cm.stage_mc = reinterpret_cast<const __nv_bfloat16*>(a->stage_mc);
-  cm.rs_pull = a->stage_mc ? 1 : 0;
   cm.trace = reinterpret_cast<unsigned long long*>(a->trace);
-  if (cm.rs_pull) {
-    // one map over this rank's whole staging buffer [T, N]
-    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)a->T, 1};
-    uint64_t strides[2] = {(uint64_t)a->N * 2, (uint64_t)a->N * 2 * a->T};
-    uint32_t box[3] = {64, 32, 1};
-    if (!encode_tmap(&tmC.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                     reinterpret_cast<const void*>(a->stage_peers[a->g.rank]), dims, strides, box,
-                     CU_TENSOR_MAP_SWIZZLE_128B))
-      return ST_ERR_CUDA;
-  }
-  for (int q = 0; q < W && !cm.rs_pull; ++q) {
-    // this rank's slot inside owner q's staging area
-    const char* base = reinterpret_cast<const char*>(a->stage_peers[q]) + (size_t)a->g.rank * rows * a->N * 2;
+  for (int q = 0; q < W; ++q) {
+    // this rank's slot inside owner q's staging area; for the rows this rank owns, the output itself
+    const char* base = q == a->g.rank ? reinterpret_cast<const char*>(a->out)
+                                      : reinterpret_cast<const char*>(a->stage_peers[q]) + (size_t)a->g.rank * rows * a->N * 2;
     uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)rows, 1};
     uint64_t strides[2] = {(uint64_t)a->N * 2, (uint64_t)a->N * 2 * rows};
     uint32_t box[3] = {64, 32, 1};
@@ -254,5 +242,6 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
   return launch<false, COMM_RS>(tmA, tmB, tmC, tmA, p, cm, grid, stream);
 }
 
-// Number of warp arrivals one launch of st_gemm_rs adds to every row-block counter.
-ST_API int st_gemm_rs_arrivals_per_launch(int world, int N) { return world * ((N + BN - 1) / BN) * 4; }
+// Number of warp arrivals one launch of st_gemm_rs adds to every row-block counter: four epilogue
+// warps per tile of every OTHER rank (the owner does not count its own tiles).
+ST_API int st_gemm_rs_arrivals_per_launch(int world, int N) { return (world - 1) * ((N + BN - 1) / BN) * 4; }

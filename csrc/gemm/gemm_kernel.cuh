@@ -10,12 +10,13 @@
 //              while its other warps run GEMM tiles.  The TMA producer waits (bounded) for the
 //              counter of the rows it is about to load; the local rows are read from the shard
 //              itself; tiles are ordered local chunk first, then in ring order.
-//   COMM_RS    GEMM → reduce-scatter.  The epilogue writes each partial tile straight into
-//              the staging slot of the rank that owns those rows (peer stores over NVLink),
-//              then bumps that owner's per-row-block counter; tiles are ordered so that the
-//              local chunk comes last.  After its tiles a CTA reduces row blocks of the
-//              local chunk as soon as all ranks' partials have landed (fp32 sum of the
-//              staging slots, optional residual add) and writes the bf16 shard.
+//   COMM_RS    GEMM → reduce-scatter.  Tiles are ordered so that the chunk this rank owns comes last.
+//              For the other chunks the epilogue TMA-stores each partial tile straight into the
+//              owner's staging slot (peer writes over NVLink) and counts the tile on the owner's
+//              per-row-block counter.  For its own chunk the epilogue waits (bounded) until every
+//              peer's partial of the row block has landed, adds them and the optional residual to
+//              the accumulator in fp32, and writes the final bf16 rows — there is no separate
+//              reduction pass and the local partial is never staged.
 #pragma once
 #include "../common/host.h"
 #include "../common/ptx.cuh"
@@ -56,10 +57,6 @@ struct GemmComm {
   int slot_done;        // counters: slot_done + row block within the chunk
   unsigned done_target; // counter value meaning "every rank's tiles of this row block landed"
   __nv_bfloat16* rs_out;                   // [rows_per_chunk, N] reduced local shard
-  const __nv_bfloat16* stage_mc;           // RS pull mode: multicast alias of the [T, N] staging
-  int rs_pull;          // 0: partial tiles are stored into the owner's staging slots and summed by the
-                        //    owner; 1: partial tiles stay in local staging [T, N] and the owner reads
-                        //    its rows through the multicast alias (summed in the switch, fp32)
   const __nv_bfloat16* rs_residual;        // optional, added during the reduction
 };
 
@@ -396,11 +393,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int cbatch = (p.conv.mode == 2) ? (b % p.conv.taps) : b;
       long long c_base = (long long)cbatch * p.batch_stride_c + (long long)row * p.ldc;
       int owner = 0;
+      bool local_tile = false;
       if constexpr (COMM == COMM_RS) {
         owner = m0 / cm.rows_per_chunk;
-        if (cm.rs_pull) {
-          c_ptr = cm.stage_peers[cm.g.rank];
-          c_base = (long long)row * p.ldc;
+        local_tile = owner == cm.g.rank;
+        if (local_tile) {
+          // Everything this warp still owes its peers is published first: they wait for it before
+          // they can finish, exactly as this rank is about to wait for them.
+          if (lane == 0 && n_pend > 0) {
+            if (p.use_tma_store) tma_store_wait<0>();
+            fence_proxy_async_global();
+            fence_sys();
+            for (int i = 0; i < n_pend; ++i)
+              red_relaxed_sys_add(cm.g.signals[pend_owner[i]] + cm.slot_done + pend_block[i], 1u);
+            n_pend = 0;
+          }
+          // this rank owns these rows: wait until every peer's partial of the row block has landed,
+          // then the column loop adds them (and the residual) and writes the final rows
+          bool okc = true;
+          if (lane == 0)
+            okc = wait_flag_ge(cm.g.signals[cm.g.rank] + cm.slot_done + (m0 - owner * cm.rows_per_chunk) / BM,
+                               cm.done_target);
+          okc = __all_sync(0xffffffffu, okc);
+          if (!okc) {
+            *abort_flag = 1;
+            if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA603u);
+            break;
+          }
+          c_ptr = cm.rs_out;
+          c_base = (long long)(row - owner * cm.rows_per_chunk) * p.ldc;
         } else {
           c_ptr = cm.stage_peers[owner];
           c_base = ((long long)cm.g.rank * cm.rows_per_chunk + (row - owner * cm.rows_per_chunk)) * p.ldc;
@@ -413,9 +434,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          const bool to_owner = (COMM == COMM_RS) && !cm.rs_pull;
-          const CUtensorMap* om = &tmC.m[to_owner ? owner : 0];
-          const int r0 = (to_owner ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
+          const CUtensorMap* om = &tmC.m[COMM == COMM_RS ? owner : 0];
+          const int r0 = (COMM == COMM_RS ? m0 - owner * cm.rows_per_chunk : m0) + quad * 32;
           tma_store_3d(om, smem_u32(smem + L::CSTAGE_OFFSET + (quad * CSB + (store_seq % CSB)) * 4096),
                        n0 + (c >> 1) * 64, r0, b);
           tma_store_commit();
@@ -444,6 +464,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
         const bool full = (col0 + 32 <= p.N);
+        if constexpr (COMM == COMM_RS) {
+          if (local_tile) {
+            // staged partials of the other ranks (slot q of this rank's staging area), then the residual
+            const long long off = (long long)(row - owner * cm.rows_per_chunk) * p.ldc + col0;
+            const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
+            const int n_src = cm.g.world + (cm.rs_residual ? 1 : 0);
+            for (int q = 0; q < n_src; ++q) {
+              if (q == cm.g.rank) continue;
+              const __nv_bfloat16* src = (q < cm.g.world ? cm.stage_peers[cm.g.rank] + q * slot_stride : cm.rs_residual) + off;
+              if (full) {
+                uint4 u[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) u[i] = reinterpret_cast<const uint4*>(src)[i];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float2 f0 = unpack_bf16x2(u[i].x), f1 = unpack_bf16x2(u[i].y), f2 = unpack_bf16x2(u[i].z),
+                         f3 = unpack_bf16x2(u[i].w);
+                  v[i * 8 + 0] += f0.x; v[i * 8 + 1] += f0.y; v[i * 8 + 2] += f1.x; v[i * 8 + 3] += f1.y;
+                  v[i * 8 + 4] += f2.x; v[i * 8 + 5] += f2.y; v[i * 8 + 6] += f3.x; v[i * 8 + 7] += f3.y;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) v[j] += __bfloat162float(src[j]);
+              }
+            }
+          }
+        }
         if (p.bias) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -584,7 +631,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // an NVLink round trip into every tile, and so would a system-scope release per tile:
         // finished tiles are queued and published kPubBatch at a time behind one fence, after
         // the wait that leaves only the newest tile's store groups outstanding.
-        if (lane == 0) {
+        if (lane == 0 && !local_tile) {
           if (p.use_tma_store) {
             if (n_pend == kPubBatch) {
               const int groups = store_seq - tile_seq0;      // bulk groups committed for this tile
@@ -621,112 +668,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
 
-    if constexpr (COMM == COMM_RS) {
-      // ---- reduce the local chunk: row blocks are dealt round-robin to the CTAs -------------
-      const int W = cm.g.world, R = cm.g.rank;
-      const int blocks = cm.rows_per_chunk / BM;
-      const int ew = warp - 2;  // 0..3
-      const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
-      // work item = (row block, 256-column slab); each warp owns 32 rows of the block, each lane
-      // 8 columns; eight rows are in flight per slot so that the reduction is bandwidth- and not
-      // latency-bound
-      const int slabs = (p.N + 255) / 256;
-      const int items = blocks * slabs;
-      const __nv_bfloat16* stage = cm.stage_peers[R];
-      for (int it = blockIdx.x; it < items && alive; it += gridDim.x) {
-        const int rb = it / slabs;
-        const int c8 = (it - rb * slabs) * 256 + lane * 8;
-        bool ok = true;
-        if (lane == 0) ok = wait_flag_ge(cm.g.signals[R] + cm.slot_done + rb, cm.done_target);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          *abort_flag = 1;
-          if (lane == 0) report_error(p.err, ERR_FLAG_TIMEOUT, 0xA603u);
-          break;
-        }
-        if (c8 >= p.N) continue;
-        if (cm.rs_pull) {
-          // every rank's partial rows sit at the same offset of its staging buffer: one
-          // multimem.ld_reduce returns their fp32 sum (rounded to bf16 once) through the switch
-          const __nv_bfloat16* mc = cm.stage_mc + ((long long)R * cm.rows_per_chunk + rb * BM) * p.ldc + c8;
-          const long long out_off = (long long)(rb * BM) * p.ldc + c8;
-#pragma unroll 1
-          for (int r0 = ew * 32; r0 < ew * 32 + 32; r0 += 16) {
-            uint4 u[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) u[i] = multimem_ld_reduce_bf16x8(mc + (long long)(r0 + i) * p.ldc);
-            if (cm.rs_residual) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(cm.rs_residual + out_off + (long long)(r0 + i) * p.ldc);
-                float2 a0 = unpack_bf16x2(u[i].x), a1 = unpack_bf16x2(u[i].y), a2 = unpack_bf16x2(u[i].z),
-                       a3 = unpack_bf16x2(u[i].w);
-                float2 b0 = unpack_bf16x2(rv.x), b1 = unpack_bf16x2(rv.y), b2 = unpack_bf16x2(rv.z),
-                       b3 = unpack_bf16x2(rv.w);
-                u[i].x = pack_bf16x2(a0.x + b0.x, a0.y + b0.y);
-                u[i].y = pack_bf16x2(a1.x + b1.x, a1.y + b1.y);
-                u[i].z = pack_bf16x2(a2.x + b2.x, a2.y + b2.y);
-                u[i].w = pack_bf16x2(a3.x + b3.x, a3.y + b3.y);
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              *reinterpret_cast<uint4*>(cm.rs_out + out_off + (long long)(r0 + i) * p.ldc) = u[i];
-          }
-          continue;
-        }
-#pragma unroll 1
-        for (int r0 = ew * 32; r0 < ew * 32 + 32; r0 += 8) {
-          float sum[8][8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sum[i][j] = 0.0f;
-          const long long base_off = (long long)(rb * BM + r0) * p.ldc + c8;
-          // sources: the W staging slots, then the optional residual; two sources (16 independent
-          // 16-byte loads per lane) are in flight at a time
-          const int n_src = W + (cm.rs_residual ? 1 : 0);
-          auto src_ptr = [&](int q) {
-            return (q < W ? stage + q * slot_stride : cm.rs_residual) + base_off;
-          };
-          auto add_rows = [&](const uint4 (&u)[8]) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float2 f0 = unpack_bf16x2(u[i].x), f1 = unpack_bf16x2(u[i].y), f2 = unpack_bf16x2(u[i].z),
-                     f3 = unpack_bf16x2(u[i].w);
-              sum[i][0] += f0.x; sum[i][1] += f0.y; sum[i][2] += f1.x; sum[i][3] += f1.y;
-              sum[i][4] += f2.x; sum[i][5] += f2.y; sum[i][6] += f3.x; sum[i][7] += f3.y;
-            }
-          };
-          int q = 0;
-          for (; q + 1 < n_src; q += 2) {
-            const __nv_bfloat16* s0 = src_ptr(q);
-            const __nv_bfloat16* s1 = src_ptr(q + 1);
-            uint4 u0[8], u1[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) u0[i] = *reinterpret_cast<const uint4*>(s0 + (long long)i * p.ldc);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) u1[i] = *reinterpret_cast<const uint4*>(s1 + (long long)i * p.ldc);
-            add_rows(u0);
-            add_rows(u1);
-          }
-          if (q < n_src) {
-            const __nv_bfloat16* s0 = src_ptr(q);
-            uint4 u0[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) u0[i] = *reinterpret_cast<const uint4*>(s0 + (long long)i * p.ldc);
-            add_rows(u0);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint4 o;
-            o.x = pack_bf16x2(sum[i][0], sum[i][1]); o.y = pack_bf16x2(sum[i][2], sum[i][3]);
-            o.z = pack_bf16x2(sum[i][4], sum[i][5]); o.w = pack_bf16x2(sum[i][6], sum[i][7]);
-            *reinterpret_cast<uint4*>(cm.rs_out + base_off + (long long)i * p.ldc) = o;
-          }
-        }
-      }
-    }
   } else if constexpr (COMM == COMM_AG) {
     // ---------------------------------------------------------------------------------------
     // All-gather: EVERY CTA pushes its 1/gridDim slice of this rank's shard while its other warps

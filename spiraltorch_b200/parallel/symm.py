@@ -176,9 +176,6 @@ class FusedTPContext(TPContext):
         # sub-chunk granularity, because a launch only touches the words of its own granularity
         self.slot_arrive = {s: self.signals.alloc(MAX_RANKS * 16) for s in (1, 2, 4, 8, 16)}
         self._ag_arrivals = {s: 0 for s in (1, 2, 4, 8, 16)}
-        # NVLS variants (multimem.st push, multimem.ld_reduce pull) are correct but measured slower
-        # than the peer-store paths at 4 GPUs; they stay opt-in
-        self.use_nvls = os.environ.get("ST_TP_NVLS", "0") == "1"
         self.ag_stages = int(os.environ.get("ST_TP_AG_STAGES", "0"))   # 0 = by world size
         self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
@@ -273,7 +270,7 @@ class FusedTPContext(TPContext):
         r.alpha = alpha
         r.slot_enter, r.slot_done = self.slot_enter, slot
         r.done_target = cum & 0xFFFFFFFF
-        r.stage_mc = sbuf.mc() if (self.use_nvls and self.world > 1) else 0
+        r.stage_mc = 0
         r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")
         launch_count += 1

@@ -431,3 +431,79 @@ def test_kdsl_program_store_and_registry(tmp_path):
     assert len(log) == 3 and log.best_by_tflops().tflops == 1500.0 and log.best_tile() == {"bn": 1500}
     assert log.summary()["samples"] == 3 and log.regression_rate() == 0.0
     assert kdsl.DeviceProfile.current().encode()
+
+
+# ---- measures, engine hooks, operator registry, backend policy, blackcat ---------------------------------------
+def test_measures_engine_and_blackcat():
+    import spiraltorch_b200 as st
+    from spiraltorch_b200 import engine, measure
+    from spiraltorch_b200.runtime import blackcat
+
+    d = [st.Tensor(1, 3, [0.98, 0.01, 0.01]), st.Tensor(1, 3, [0.1, 0.2, 0.7])]
+    uni = measure.z_space_barycenter([0.0, 0.0], d, 0.5, 0.0)
+    assert uni.density.tolist()[0] == pytest.approx([1 / 3] * 3, abs=1e-6) and uni.kl_energy == 0.0 and uni.objective < 0
+    one = measure.z_space_barycenter([1.0], [st.Tensor(1, 2, [0.9, 0.1])], -0.999, 0.0)
+    assert one.density.tolist()[0][0] > 0.999 and abs(sum(one.density.tolist()[0]) - 1) < 1e-6
+    mix = measure.z_space_barycenter([1.0, 1.0], d, 0.0, 1.0, st.Tensor(2, 2, [0, 1, 1, 0]))
+    geo = torch.tensor([[0.98 * 0.1, 0.01 * 0.2, 0.01 * 0.7]]).sqrt()
+    assert torch.allclose(mix.density.torch(), geo / geo.sum(), atol=1e-6) and mix.coupling_energy > 0
+    with pytest.raises(st.TensorError):
+        measure.z_space_barycenter([1.0], d, 0.0, 0.0)
+    with pytest.raises(st.TensorError):
+        measure.z_space_barycenter([0.0, 0.0], d, 0.0, 0.0)
+    w = measure.nirt_weight_update([0.5, 0.5], [1.0, -1.0], 0.5, 0.2)
+    assert w == pytest.approx([0.6, 0.4]) and abs(sum(w) - 1) < 1e-9
+    assert measure.nirt_weight_update([0.1, 0.9], [-1.0, 0.0], 1.0, 1.0) == pytest.approx([0.0, 1.0])
+    with pytest.raises(st.TensorError):
+        measure.nirt_weight_update([0.5, 0.5], [2.0, 0.0], 0.5, 0.1)
+
+    g = torch.tensor([1.0, -2.0, 3.0])
+    assert engine.call_onebit_allreduce(g, 4) is False and g.tolist() == [1.0, -2.0, 3.0]
+    engine.register_onebit_allreduce(lambda grad, world: grad.copy_(torch.sign(grad) * grad.abs().mean()))
+    assert engine.call_onebit_allreduce(g, 4) and g.tolist() == [2.0, -2.0, 2.0]
+    engine.register_onebit_allreduce(None)
+    p = torch.arange(10.0)
+    assert engine.call_zero_partition(p, 1, 4) is p
+    engine.register_zero_partition(engine.default_zero_partition)
+    assert [engine.call_zero_partition(p, r, 4).tolist() for r in range(4)] == [[0, 1, 2], [3, 4, 5], [6, 7, 8], [9]]
+    engine.register_zero_partition(None)
+
+    reg = engine.OperatorRegistry()
+    reg.register(engine.OperatorSpec("axpy", 2, lambda x, y: x.scale(2.0).add(y),
+                                     lambda x, y, go: [go.scale(2.0), go], "2x + y"))
+    out = reg.call("axpy", st.Tensor(1, 2, [1, 2]), st.Tensor(1, 2, [10, 20]))
+    assert out.tolist() == [[12.0, 24.0]] and reg.names() == ["axpy"]
+    gx, gy = reg.call_backward("axpy", [st.Tensor(1, 2, [1, 2]), st.Tensor(1, 2, [10, 20])], st.Tensor(1, 2, [1, 1]))
+    assert gx.tolist() == [[2.0, 2.0]] and gy.tolist() == [[1.0, 1.0]]
+    with pytest.raises(st.TensorError):
+        reg.call("axpy", st.Tensor(1, 1, [1]))
+    with pytest.raises(st.TensorError):
+        reg.register(engine.OperatorSpec("axpy", 1, lambda x: x))
+    assert reg.unregister("axpy") and not reg.unregister("axpy")
+
+    assert engine.backend_for("matmul") == "auto"
+    with engine.push_backend_policy(engine.BackendPolicy(matmul="cpu", attention="cuda")):
+        assert engine.backend_for("matmul") == "cpu"
+        with engine.push_backend_policy(engine.BackendPolicy(matmul="cuda")):
+            assert engine.backend_for("matmul") == "cuda" and engine.backend_for("attention") == "cuda"
+        assert engine.backend_for("matmul") == "cpu"
+    assert engine.backend_for("matmul") == "auto"
+    with pytest.raises(st.TensorError):
+        engine.push_backend_policy(engine.BackendPolicy(matmul="wgpu"))
+
+    # the bandit learns that "big" tiles are faster in context A and "small" in context B
+    cat = blackcat.BlackCat({"tile": ["small", "big"]}, context_dim=2, exploration=0.5)
+    ctx_a, ctx_b = [1.0, 0.0], [0.0, 1.0]
+    for i in range(60):
+        ctx = ctx_a if i % 2 == 0 else ctx_b
+        pick = cat.choose(ctx)["tile"]
+        fast = (pick == "big") == (ctx is ctx_a)
+        cat.post_step(StepMetrics(step_time_ms=5.0 if fast else 20.0, mem_peak_mb=100.0))
+    assert cat.choose(ctx_a)["tile"] == "big" and cat.choose(ctx_b)["tile"] == "small"
+    assert cat.observations("tile", "big") + cat.observations("tile", "small") == 60
+    u = cat.post_step(StepMetrics(step_time_ms=10.0, mem_peak_mb=1024.0, retry_rate=0.0))
+    assert u == pytest.approx(-(0.5 + 0.3))
+    n = cat.observations("tile", "small") + cat.observations("tile", "big")
+    cat.post_step(StepMetrics(step_time_ms=10.0))                      # no pending selection: nothing credited
+    assert cat.observations("tile", "small") + cat.observations("tile", "big") == n
+    assert cat.choose([1.0]) == {} and cat.post_step(StepMetrics(step_time_ms=float("nan"))) == -math.inf
