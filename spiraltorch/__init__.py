@@ -11,6 +11,6 @@ from spiraltorch_b200 import (SpiralSession, Tensor, build_info, config, describ
                               init_backend, nn, optim, plugin, realgrad, selfsup)
 
 __version__ = _impl.__version__
-for _name in ("nn", "optim", "plugin", "selfsup", "config", "distributed", "autograd", "compress", "engine", "measure", "hpo", "kdsl", "metrics", "rec", "rl",
+for _name in ("nn", "optim", "plugin", "selfsup", "config", "distributed", "autograd", "compress", "engine", "measure", "hpo", "kdsl", "language", "text", "metrics", "rec", "rl",
               "robotics", "runtime", "safety", "softlogic", "telemetry"):
     _sys.modules[f"{__name__}.{_name}"] = getattr(_impl, _name)

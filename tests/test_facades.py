@@ -507,3 +507,51 @@ def test_measures_engine_and_blackcat():
     cat.post_step(StepMetrics(step_time_ms=10.0))                      # no pending selection: nothing credited
     assert cat.observations("tile", "small") + cat.observations("tile", "big") == n
     assert cat.choose([1.0]) == {} and cat.post_step(StepMetrics(step_time_ms=float("nan"))) == -math.inf
+
+
+def test_language_control_and_text_resonator():
+    from spiraltorch_b200 import language, text, telemetry
+    assert language.entropy([0.5, 0.5]) == pytest.approx(math.log(2))
+    with pytest.raises(Exception):
+        language.entropy([0.5, 0.2])
+    tc = language.TemperatureController(1.0, target_entropy=1.0, eta=0.5, min=0.1, max=2.0)
+    assert tc.update([1.0, 0.0, 0.0]) == pytest.approx(1.5)             # too peaked -> warmer
+    for _ in range(10):
+        tc.update([1.0, 0.0, 0.0])
+    assert tc.value() == 2.0
+    assert tc.update([0.25] * 4) < 2.0                                   # too flat -> cooler
+    with pytest.raises(Exception):
+        language.TemperatureController(5.0, 1.0, 0.1, 0.1, 2.0)
+
+    V, C = 6, 2
+    g = torch.Generator().manual_seed(0)
+    syn, par = torch.randn(V, V, generator=g) * 0.1, torch.randn(V, V, generator=g) * 0.1
+    syn[0, 3] = 3.0                                                        # token 3 follows token 0
+    rep = torch.zeros(V)
+    rep[1] = 5.0                                                           # token 1 is repressed
+    sem = torch.zeros(V, C)
+    sem[4, 1] = 2.0
+    lag = language.DesireLagrangian(syn, par, rep, sem, language.TemperatureController(1.0, 1.2, 0.05, 0.2, 3.0))
+    logits = torch.tensor([0.0, 2.0, 0.0, 0.0, 0.0, 0.0])
+    base = lag.step(logits, 0, [1.0, 0.0], language.DesireWeights())
+    assert base.phase == language.OBSERVATION and max(range(V), key=lambda i: base.probabilities[i]) == 1
+    sol = lag.step(logits, 0, [0.0, 1.0], language.DesireWeights(alpha=1.0, gamma=1.0, lam=1.0))
+    p = dict(zip(sol.indices, sol.probabilities))
+    assert sol.phase == language.INTEGRATION and p[3] > p[1] and p[4] > p[2] and abs(sum(sol.probabilities) - 1) < 1e-5
+    lag2 = language.DesireLagrangian(syn, par, rep, sem, language.TemperatureController(1.0, 1.2, 0.05, 0.2, 3.0), top_k=3)
+    lag2.with_schedules(alpha=language.warmup(0.0, 1.0, 4)).with_horizons(2, None)
+    phases = [lag2.step_with_scheduler(logits, 0, [1.0, 0.0]).phase for _ in range(4)]
+    assert phases[:2] == [language.OBSERVATION] * 2 and phases[3] == language.INJECTION
+    assert len(lag2.step_with_scheduler(logits, 0, [1.0, 0.0]).indices) == 3
+    with pytest.raises(Exception):
+        lag.step(logits[:3], 0, [1.0, 0.0], language.DesireWeights())
+
+    tl = telemetry.ChronoTimeline(16)
+    for i in range(8):
+        tl.record(0.1, {"observed_curvature": -1.0 + 0.01 * i, "total_energy": 2.0})
+    tr = text.TextResonator()
+    nar = tr.describe_timeline(tl)
+    assert "energetic" in nar.summary and "rising" in nar.summary and "stable" in nar.summary
+    wave = tr.synthesize_wave(tl, sample_rate=1000, seconds_per_frame=0.01)
+    assert len(wave.samples) == 80 and max(abs(s) for s in wave.samples) <= 1.0
+    assert tr.describe_timeline(telemetry.ChronoTimeline()) is None
