@@ -131,6 +131,52 @@ def cmd_preflight(args) -> int:
     return 0
 
 
+def _write_ppm(path: str, rgb) -> None:
+    """``rgb``: uint8 tensor ``[H, W, 3]`` → binary PPM (P6)."""
+    h, w, _ = rgb.shape
+    with open(path, "wb") as fh:
+        fh.write(f"P6 {w} {h} 255\n".encode())
+        fh.write(bytes(rgb.contiguous().cpu().flatten().tolist()))
+
+
+def cmd_z_volume(args) -> int:
+    """Render a synthetic Z volume (depth slices of a travelling wave) through the temporal volume
+    renderer and the canvas palette into a PPM image (the role of the reference's
+    ``tools/visualize-z-volume``, headless: the image goes to a file)."""
+    import torch
+    from . import vision
+    dev = "cuda" if (args.backend != "cpu" and torch.cuda.is_available()) else "cpu"
+    d, h, w = args.depth, args.size, args.size
+    z = torch.linspace(0, 1, d, device=dev)[:, None, None]
+    y = torch.linspace(-1, 1, h, device=dev)[None, :, None]
+    x = torch.linspace(-1, 1, w, device=dev)[None, None, :]
+    volume = torch.sin(6.0 * (x * x + y * y).sqrt() - 6.0 * z).mul(0.5).add(0.5) * torch.exp(-2.0 * z)
+    image = vision.temporal_volume_render(volume, density_scale=args.density)[..., :3].mean(-1)      # composited luminance
+    rgba = vision.canvas_paint(image, palette=args.palette)
+    _write_ppm(args.out, rgba[..., :3])
+    print(json.dumps({"out": args.out, "shape": [h, w], "device": dev, "mean": float(image.mean())}))
+    return 0
+
+
+def cmd_xai(args) -> int:
+    """Grad-CAM of a (randomly initialised or loaded) ResNet backbone on one image; writes the heat map
+    as a PPM (the role of the reference's ``tools/xai-cli``)."""
+    import torch
+    from . import vision
+    from .models import vision_backbones as V
+    dev = "cuda" if (args.backend != "cpu" and torch.cuda.is_available()) else "cpu"
+    torch.manual_seed(args.seed)
+    dtype = torch.bfloat16 if dev == "cuda" else torch.float32
+    model = V.ResNet(num_classes=args.classes, widths=(64, 128), device=dev, dtype=dtype)
+    img = torch.randn(1, 3, args.size, args.size, device=dev)
+    cam = V.grad_cam(model, img)
+    heat = torch.nn.functional.interpolate(cam[:, None], size=(args.size, args.size), mode="bilinear")[0, 0]
+    rgba = vision.canvas_paint(heat, palette="diverging" if args.palette is None else args.palette)
+    _write_ppm(args.out, rgba[..., :3])
+    print(json.dumps({"out": args.out, "cam_shape": list(cam.shape[1:]), "device": dev, "peak": float(cam.max())}))
+    return 0
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="spiraltorch")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -160,6 +206,22 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--events", default=None)
     p.add_argument("--steps", type=int, default=16)
     p.set_defaults(fn=cmd_plugin)
+    zv = sub.add_parser("z-volume", help="render a synthetic Z volume to a PPM image")
+    zv.add_argument("--out", default="z_volume.ppm")
+    zv.add_argument("--size", type=int, default=64)
+    zv.add_argument("--depth", type=int, default=16)
+    zv.add_argument("--density", type=float, default=1.0)
+    zv.add_argument("--palette", default="spiral")
+    zv.add_argument("--backend", default="auto")
+    zv.set_defaults(fn=cmd_z_volume)
+    xa = sub.add_parser("xai", help="Grad-CAM heat map of a ResNet backbone")
+    xa.add_argument("--out", default="gradcam.ppm")
+    xa.add_argument("--size", type=int, default=32)
+    xa.add_argument("--classes", type=int, default=10)
+    xa.add_argument("--seed", type=int, default=0)
+    xa.add_argument("--palette", default=None)
+    xa.add_argument("--backend", default="auto")
+    xa.set_defaults(fn=cmd_xai)
     r = sub.add_parser("runtime-preflight", help="report device, build and native-library status")
     r.add_argument("--backend", default="auto")
     r.set_defaults(fn=cmd_preflight)

@@ -46,3 +46,15 @@ def test_train_export_plugin_preflight(capsys, tmp_path):
     assert cli.main(["runtime-preflight", "--backend", "cpu"]) == 0
     rep = json.loads(capsys.readouterr().out)
     assert "build" in rep and "device" in rep and "native" in rep
+
+
+def test_z_volume_and_xai_tools(capsys, tmp_path):
+    out = tmp_path / "vol.ppm"
+    assert cli.main(["z-volume", "--out", str(out), "--size", "16", "--depth", "4", "--backend", "cpu"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    data = out.read_bytes()
+    assert data.startswith(b"P6 16 16 255\n") and len(data) == len(b"P6 16 16 255\n") + 16 * 16 * 3 and info["mean"] > 0
+    cam = tmp_path / "cam.ppm"
+    assert cli.main(["xai", "--out", str(cam), "--size", "16", "--classes", "4", "--backend", "cpu"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["cam_shape"] == [8, 8] and cam.read_bytes().startswith(b"P6 16 16 255\n")
