@@ -158,6 +158,48 @@ __device__ __forceinline__ void map_tile(int t, int tiles_m, int tiles_n, int ti
   }
 }
 
+// ---- reduce-scatter: sources added to a tile of the rows this rank owns ----------------------
+constexpr int kRsBatch = 4;   // sources whose loads are in flight together (4 x 64 B per lane each)
+
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
+// Source s of the local reduction: the staged partials of the other ranks in rank order (this
+// rank's own slot is skipped), then the residual.
+__device__ __forceinline__ const __nv_bfloat16* rs_src(const GemmComm& cm, int s, long long slot_stride) {
+  const int q = s + (s >= cm.g.rank ? 1 : 0);
+  return q < cm.g.world ? cm.stage_peers[cm.g.rank] + q * slot_stride
+                        : cm.rs_residual;
+}
+
+__device__ __forceinline__ void rs_load_batch(const GemmComm& cm, long long slot_stride, int s0, int n_srcs, long long off,
+                                              uint4 (&buf)[kRsBatch][4]) {
+#pragma unroll
+  for (int i = 0; i < kRsBatch; ++i) {
+    if (s0 + i < n_srcs) {
+      const uint4* sp = reinterpret_cast<const uint4*>(rs_src(cm, s0 + i, slot_stride) + off);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) buf[i][k] = sp[k];
+    }
+  }
+}
+
+__device__ __forceinline__ void rs_add_batch(int s0, int n_srcs, const uint4 (&buf)[kRsBatch][4], float* v) {
+#pragma unroll
+  for (int i = 0; i < kRsBatch; ++i) {
+    if (s0 + i < n_srcs) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 f0 = unpack_bf16x2(buf[i][k].x), f1 = unpack_bf16x2(buf[i][k].y), f2 = unpack_bf16x2(buf[i][k].z),
+               f3 = unpack_bf16x2(buf[i][k].w);
+        v[k * 8 + 0] += f0.x; v[k * 8 + 1] += f0.y; v[k * 8 + 2] += f1.x; v[k * 8 + 3] += f1.y;
+        v[k * 8 + 4] += f2.x; v[k * 8 + 5] += f2.y; v[k * 8 + 6] += f3.x; v[k * 8 + 7] += f3.y;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void epilogue_bar() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
@@ -363,6 +405,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int kPubBatch = 3;
     int pend_owner[kPubBatch], pend_block[kPubBatch], n_pend = 0;   // RS: tiles stored, not yet published
     bool alive = true;
+    bool saw_local = false;     // RS tracing: the first local tile has been stamped
     const bool tracer = (COMM != COMM_NONE) && cm.trace && quad == 2 && lane == 0;   // warp 2
     if (tracer) cm.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
     if constexpr (COMM == COMM_RS) {
@@ -394,10 +437,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       long long c_base = (long long)cbatch * p.batch_stride_c + (long long)row * p.ldc;
       int owner = 0;
       bool local_tile = false;
+      int n_srcs = 0;             // RS local tile: staged partials + residual to add
+      long long red_off = 0;      // element offset of this lane's row segment inside a source
+      bool pf_valid = false;      // pf holds the first batch of the next column group
+      uint4 pf[kRsBatch][4];
+      const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
       if constexpr (COMM == COMM_RS) {
         owner = m0 / cm.rows_per_chunk;
         local_tile = owner == cm.g.rank;
         if (local_tile) {
+          if (tracer && !saw_local) cm.trace[(gridDim.x + blockIdx.x) * 4 + 0] = globaltimer_ns();
           // Everything this warp still owes its peers is published first: they wait for it before
           // they can finish, exactly as this rank is about to wait for them.
           if (lane == 0 && n_pend > 0) {
@@ -422,6 +471,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           c_ptr = cm.rs_out;
           c_base = (long long)(row - owner * cm.rows_per_chunk) * p.ldc;
+          if (tracer && !saw_local) {
+            saw_local = true;
+            cm.trace[(gridDim.x + blockIdx.x) * 4 + 1] = globaltimer_ns();
+          }
+          // Sources to add: the other ranks' staged partials (slot q of this rank's staging area), then
+          // the residual.  The whole row segment goes to L2 now; the first batch of the first column
+          // group is loaded before the accumulator is read, and every later group's first batch is
+          // loaded while the previous group is converted and stored.
+          n_srcs = cm.g.world - 1 + (cm.rs_residual ? 1 : 0);
+          red_off = c_base + n0;
+          if (row_ok) {
+            const int lines = (min(BN, p.N - n0) * 2 + 127) / 128;
+            for (int s_ = 0; s_ < n_srcs; ++s_)
+              for (int l_ = 0; l_ < lines; ++l_) prefetch_l2(rs_src(cm, s_, slot_stride) + red_off + l_ * 64);
+            pf_valid = n0 + 32 <= p.N;
+            if (pf_valid) rs_load_batch(cm, slot_stride, 0, n_srcs, red_off, pf);
+          }
         } else {
           c_ptr = cm.stage_peers[owner];
           c_base = ((long long)cm.g.rank * cm.rows_per_chunk + (row - owner * cm.rows_per_chunk)) * p.ldc;
@@ -466,25 +532,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool full = (col0 + 32 <= p.N);
         if constexpr (COMM == COMM_RS) {
           if (local_tile) {
-            // staged partials of the other ranks (slot q of this rank's staging area), then the residual
-            const long long off = (long long)(row - owner * cm.rows_per_chunk) * p.ldc + col0;
-            const long long slot_stride = (long long)cm.rows_per_chunk * p.ldc;
-            const int n_src = cm.g.world + (cm.rs_residual ? 1 : 0);
-            for (int q = 0; q < n_src; ++q) {
-              if (q == cm.g.rank) continue;
-              const __nv_bfloat16* src = (q < cm.g.world ? cm.stage_peers[cm.g.rank] + q * slot_stride : cm.rs_residual) + off;
-              if (full) {
-                uint4 u[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) u[i] = reinterpret_cast<const uint4*>(src)[i];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float2 f0 = unpack_bf16x2(u[i].x), f1 = unpack_bf16x2(u[i].y), f2 = unpack_bf16x2(u[i].z),
-                         f3 = unpack_bf16x2(u[i].w);
-                  v[i * 8 + 0] += f0.x; v[i * 8 + 1] += f0.y; v[i * 8 + 2] += f1.x; v[i * 8 + 3] += f1.y;
-                  v[i * 8 + 4] += f2.x; v[i * 8 + 5] += f2.y; v[i * 8 + 6] += f3.x; v[i * 8 + 7] += f3.y;
-                }
-              } else {
+            const long long off = red_off + c * 32;
+            if (full) {
+              if (!pf_valid) rs_load_batch(cm, slot_stride, 0, n_srcs, off, pf);
+              rs_add_batch(0, n_srcs, pf, v);
+              for (int s0 = kRsBatch; s0 < n_srcs; s0 += kRsBatch) {
+                uint4 more[kRsBatch][4];
+                rs_load_batch(cm, slot_stride, s0, n_srcs, off, more);
+                rs_add_batch(s0, n_srcs, more, v);
+              }
+              pf_valid = (c + 1 < BN / 32) && (col0 + 64 <= p.N);
+              if (pf_valid) rs_load_batch(cm, slot_stride, 0, n_srcs, off + 32, pf);
+            } else {
+              pf_valid = false;
+              for (int s_ = 0; s_ < n_srcs; ++s_) {
+                const __nv_bfloat16* src = rs_src(cm, s_, slot_stride) + off;
                 for (int j = 0; j < 32; ++j)
                   if (col0 + j < p.N) v[j] += __bfloat162float(src[j]);
               }

@@ -196,9 +196,7 @@ def main():
         tf_peak = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
         link_gbs = 770.0                      # measured peer copy bandwidth per direction
         for T in [int(v) for v in os.environ.get("ST_FUSED_BENCH_T", "16384").split(",")]:
-            for nvls in [int(v) for v in os.environ.get("ST_FUSED_BENCH_NVLS", "0").split(",")]:
-                fused.use_nvls = bool(nvls)
-                bench_one(T, nvls, tf_peak, link_gbs)
+            bench_one(T, 0, tf_peak, link_gbs)
 
     def trace_report(label, fn):
         """One launch with per-CTA phase stamps: prints, for rank 0, when (relative to the first CTA's
@@ -218,7 +216,10 @@ def main():
             comm = used[used[:, 3] == 0]
             gem = used[used[:, 3] > 0]
             msg = f"TRACE {label}: "
-            if len(comm):
+            if len(comm) and label.startswith("gemm_rs"):
+                msg += (f"first local tile reached {(comm[:, 0].min().item() - t0) / 1e3:.1f}..{(comm[:, 0].max().item() - t0) / 1e3:.1f} "
+                        f"peers' partials ready {(comm[:, 1].min().item() - t0) / 1e3:.1f}..{(comm[:, 1].max().item() - t0) / 1e3:.1f}; ")
+            elif len(comm):
                 msg += (f"comm ctas {len(comm)} entry<= {(comm[:, 1].max().item() - t0) / 1e3:.1f} "
                         f"push done {(comm[:, 2].min().item() - t0) / 1e3:.1f}..{(comm[:, 2].max().item() - t0) / 1e3:.1f}; ")
             msg += (f"gemm ctas {len(gem)} start<= {(gem[:, 0].max().item() - t0) / 1e3:.1f} "

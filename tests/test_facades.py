@@ -555,3 +555,41 @@ def test_language_control_and_text_resonator():
     wave = tr.synthesize_wave(tl, sample_rate=1000, seconds_per_frame=0.01)
     assert len(wave.samples) == 80 and max(abs(s) for s in wave.samples) <= 1.0
     assert tr.describe_timeline(telemetry.ChronoTimeline()) is None
+
+
+def test_scale_stack_and_fractal_field():
+    import math
+    from spiraltorch_b200 import frac
+    field = torch.zeros(16, 16)
+    field[:, 8:] = 1.0                                   # one straight interface
+    stack = frac.ScaleStack.from_scalar_field(field, [1.0, 2.0, 3.0], 0.5)
+    gates = [g for _, g in stack.samples]
+    assert gates == pytest.approx([2 / 16, 4 / 16, 6 / 16])
+    bins = stack.persistence_measure()
+    assert len(bins) == 3 and bins[0][:2] == (0.0, 1.0)
+    assert stack.interface_density() == pytest.approx(2 / 16)
+    dim = stack.estimate_boundary_dimension(2.0, 3)
+    assert dim == pytest.approx(1.0, abs=0.05)           # a line in the plane
+    assert stack.coherence_break_scale(0.2) == 2.0 and stack.coherence_break_scale(0.9) is None
+    with pytest.raises(ValueError):
+        frac.ScaleStack.from_scalar_field(field, [2.0, 1.0], 0.5)
+    sem = torch.zeros(8, 8, 3)
+    sem[:, :4, 0] = 1.0
+    sem[:, 4:, 1] = 1.0
+    s2 = frac.ScaleStack.from_semantic_field(sem, [1.0], 0.5, feature_axis=2, metric="cosine")
+    assert s2.samples[0][1] == pytest.approx(2 / 8)
+    gen = frac.FractalFieldGenerator(3, 2.0, 0.5, 16)
+    fld = gen.branching_field(-2.0, 0.25, 12)
+    assert fld.shape == (12,) and fld.real.abs().max() > 0 and fld.imag.abs().max() > 0
+    # one octave at x = 0: c = 1 escapes after 3 iterations (0 -> 1 -> 2 -> 5)
+    one = frac.FractalFieldGenerator(1, 2.0, 0.5, 8).branching_field(0.0, 1.0, 1)
+    assert one[0].real == pytest.approx(3 / 8) and abs(one[0].imag) < 1e-6
+    with pytest.raises(ValueError):
+        frac.FractalFieldGenerator(0, 2.0, 0.5, 4)
+    x = torch.randn(3, 4, 32)
+    y = frac.fracdiff_gl_nd(x, 0.6, axis=2)
+    assert torch.allclose(y[1, 2], frac.fracdiff_gl(x[1, 2], 0.6), atol=1e-5)
+    g = torch.randn(32)
+    xv = torch.randn(32)
+    assert torch.dot(frac.fracdiff_gl(xv, 0.6), g) == pytest.approx(float(torch.dot(xv, frac.fracdiff_gl_vjp(g, 0.6))), rel=1e-4)
+    assert len(frac.gl_coeffs_adaptive(0.5, 1e-3, 4096)) < 200
