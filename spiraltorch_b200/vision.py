@@ -315,3 +315,140 @@ def temporal_volume_render(volume: torch.Tensor, density_scale: float = 1.0) -> 
     sigma = rad.mean(-1) * density_scale
     deltas = torch.ones_like(sigma)
     return nerf_composite(sigma, rad, deltas).reshape(H, W, 4)
+
+
+# ----------------------------------------------------------------------------------------------
+# Video pipeline: decoded frames → Z-space volume with temporal smoothing and per-frame digests
+# (crates/st-vision/src/video/mod.rs:66-560)
+# ----------------------------------------------------------------------------------------------
+
+
+class VideoPipelineConfig:
+    def __init__(self, temporal_alpha: float = 0.35, resonance_decay: float = 0.25, motion_gain: float = 1.0,
+                 digest_window: int = 16, quiescence_threshold: float = 0.05):
+        self.temporal_alpha = min(max(temporal_alpha, 0.0), 1.0)
+        self.resonance_decay = min(max(resonance_decay, 0.0), 1.0)
+        self.motion_gain = max(motion_gain, 0.0) if math.isfinite(motion_gain) else 1.0
+        self.digest_window = max(int(digest_window), 1)
+        self.quiescence_threshold = max(quiescence_threshold, 0.0)
+
+
+def _energy(t: torch.Tensor) -> float:
+    return float(t.abs().mean()) if t.numel() else 0.0
+
+
+def _digest(samples, threshold: float) -> dict:
+    """Statistics of (timestamp, motion energy, resonance energy) samples."""
+    if not samples:
+        return {"frames": 0, "duration": 0.0, "mean_motion_energy": 0.0, "motion_std": 0.0,
+                "mean_resonance_energy": 0.0, "resonance_std": 0.0, "mean_resonance_decay": 0.0,
+                "min_resonance_energy": 0.0, "max_resonance_energy": 0.0, "peak_motion_energy": 0.0,
+                "peak_motion_timestamp": 0.0, "peak_resonance_energy": 0.0, "peak_resonance_timestamp": 0.0,
+                "quiescence_ratio": 0.0}
+    ts = [s[0] for s in samples]
+    mo = torch.tensor([s[1] for s in samples], dtype=torch.float64)
+    en = torch.tensor([s[2] for s in samples], dtype=torch.float64)
+    duration = sum(max(b - a, 0.0) for a, b in zip(ts, ts[1:]))
+    decay = [(a - b) / abs(a) if abs(a) > 1.1920929e-07 else 0.0 for a, b in zip(en.tolist(), en.tolist()[1:])]
+    pm, pr = int(torch.argmax(mo)), int(torch.argmax(en))
+    return {"frames": len(samples), "duration": duration,
+            "mean_motion_energy": float(mo.mean()), "motion_std": float(mo.std(unbiased=False)),
+            "mean_resonance_energy": float(en.mean()), "resonance_std": float(en.std(unbiased=False)),
+            "mean_resonance_decay": sum(decay) / len(samples),
+            "min_resonance_energy": float(en.min()), "max_resonance_energy": float(en.max()),
+            "peak_motion_energy": float(mo[pm]), "peak_motion_timestamp": ts[pm],
+            "peak_resonance_energy": float(en[pr]), "peak_resonance_timestamp": ts[pr],
+            "quiescence_ratio": float((mo <= threshold).double().mean())}
+
+
+class VideoPipeline:
+    """Consumes ``(timestamp, frame[H, W])`` pairs from any iterable decoder.  Each frame and its
+    motion embedding (gain × difference to the previous frame) form a two-slice stream frame that is
+    blended into the running Z-space volume with ``temporal_alpha``; the pipeline reports per-depth
+    energies, their exponentially smoothed weights, the Hann-windowed depth spectrum, a resonance
+    envelope (EMA of the volume) and running / windowed temporal digests, and keeps an atlas timeline.
+    Frames stay on the device they arrive on."""
+
+    def __init__(self, decoder, config: Optional[VideoPipelineConfig] = None):
+        self.decoder = iter(decoder)
+        self.config = config or VideoPipelineConfig()
+        self.frame_index = 0
+        self.volume: Optional[torch.Tensor] = None         # [depth, H, W]
+        self._previous: Optional[torch.Tensor] = None
+        self._weights: Optional[torch.Tensor] = None
+        self._envelope: Optional[torch.Tensor] = None
+        self._samples: list = []
+        self.timeline: list = []
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> dict:
+        out = self.next_frame()
+        if out is None:
+            raise StopIteration
+        return out
+
+    def next_frame(self) -> Optional[dict]:
+        try:
+            timestamp, frame = next(self.decoder)
+        except StopIteration:
+            return None
+        frame = frame.float()
+        if frame.dim() != 2:
+            raise ValueError(f"decoded frame must be [H, W], got {tuple(frame.shape)}")
+        cfg = self.config
+        motion = (torch.zeros_like(frame) if self._previous is None
+                  else (frame - self._previous) * max(cfg.motion_gain, 1.1920929e-07))
+        self._previous = frame
+        stream = torch.stack([frame, motion])
+        if self.volume is None or self.volume.shape != stream.shape:
+            self.volume = stream.clone()
+        else:
+            self.volume = torch.lerp(self.volume, stream, cfg.temporal_alpha)
+        per_depth = self.volume.abs().mean(dim=(1, 2))
+        if not bool(torch.isfinite(per_depth).all()):
+            raise ValueError("temporal_resonance_weight is not finite")
+        if self._weights is None or self._weights.shape != per_depth.shape:
+            self._weights = per_depth.clone()
+        else:
+            self._weights = torch.lerp(self._weights, per_depth, cfg.resonance_decay)
+        depth = self.volume.shape[0]
+        window = torch.hann_window(depth, periodic=False, device=frame.device) if depth > 1 else torch.ones(1, device=frame.device)
+        spectral = torch.fft.rfft(per_depth * window).abs()
+        flat = self.volume.reshape(depth, -1)
+        self._envelope = flat.clone() if self._envelope is None or self._envelope.shape != flat.shape \
+            else torch.lerp(self._envelope, flat, cfg.resonance_decay)
+        motion_energy, resonance_energy = _energy(motion), _energy(self._envelope)
+        self._samples.append((float(timestamp), motion_energy, resonance_energy))
+        w = self._weights
+        pos = w[w > 1.1920929e-07]
+        p = pos / pos.sum() if pos.numel() else pos
+        entropy = float(-(p * p.log()).sum()) if p.numel() else 0.0
+        top = int(torch.argmax(w))
+        atlas = {"timestamp": float(timestamp), "collapse_total": resonance_energy,
+                 "z_signal": top / (depth - 1) if depth > 1 else float(w[0]),
+                 "loop_support": max(motion_energy, 0.0),
+                 "metrics": {"z.motion_energy": motion_energy, "z.resonance_energy": resonance_energy,
+                             "z.weight_entropy": entropy},
+                 "notes": ["video.pipeline.z_dynamics"]}
+        self.timeline.append(atlas)
+        self.frame_index += 1
+        return {"frame_index": self.frame_index - 1, "atlas_frame": atlas, "volume": self.volume,
+                "motion_embedding": motion, "resonance_envelope": self._envelope,
+                "z_dynamics": {"smoothed_weights": w.tolist(), "per_depth_energy": per_depth.tolist(),
+                               "spectral_response": spectral.tolist()},
+                "temporal_digest": self.temporal_digest(),
+                "window_digest": self.temporal_digest_window(cfg.digest_window)}
+
+    def last_volume(self) -> Optional[torch.Tensor]:
+        return self.volume
+
+    def atlas_timeline(self) -> list:
+        return list(self.timeline)
+
+    def temporal_digest(self) -> dict:
+        return _digest(self._samples, self.config.quiescence_threshold)
+
+    def temporal_digest_window(self, window: int) -> dict:
+        return _digest(self._samples[-window:] if window > 0 else [], self.config.quiescence_threshold)

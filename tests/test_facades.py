@@ -593,3 +593,23 @@ def test_scale_stack_and_fractal_field():
     xv = torch.randn(32)
     assert torch.dot(frac.fracdiff_gl(xv, 0.6), g) == pytest.approx(float(torch.dot(xv, frac.fracdiff_gl_vjp(g, 0.6))), rel=1e-4)
     assert len(frac.gl_coeffs_adaptive(0.5, 1e-3, 4096)) < 200
+
+
+def test_video_pipeline_digests():
+    from spiraltorch_b200 import vision
+    frames = [(0.0, torch.zeros(4, 6)), (0.5, torch.ones(4, 6)), (1.0, torch.ones(4, 6)), (1.5, torch.ones(4, 6) * 3)]
+    pipe = vision.VideoPipeline(frames, vision.VideoPipelineConfig(temporal_alpha=0.5, resonance_decay=0.5, digest_window=2))
+    outs = list(pipe)
+    assert [o["frame_index"] for o in outs] == [0, 1, 2, 3]
+    assert outs[0]["motion_embedding"].abs().sum() == 0
+    assert torch.allclose(outs[1]["motion_embedding"], torch.ones(4, 6))
+    assert torch.allclose(outs[1]["volume"][0], torch.full((4, 6), 0.5))       # lerp(0, 1, 0.5)
+    assert torch.allclose(outs[2]["volume"][1], torch.full((4, 6), 0.25))      # motion 1 then 0
+    d = outs[3]["temporal_digest"]
+    assert d["frames"] == 4 and d["duration"] == pytest.approx(1.5)
+    assert d["peak_motion_energy"] == pytest.approx(2.0) and d["peak_motion_timestamp"] == 1.5
+    assert d["quiescence_ratio"] == pytest.approx(0.5)                         # frames 0 and 2 are still
+    assert outs[3]["window_digest"]["frames"] == 2
+    assert len(outs[3]["z_dynamics"]["per_depth_energy"]) == 2 and len(pipe.atlas_timeline()) == 4
+    assert outs[3]["atlas_frame"]["metrics"]["z.weight_entropy"] > 0
+    assert pipe.next_frame() is None
