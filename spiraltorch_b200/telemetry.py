@@ -17,7 +17,7 @@ import threading
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Iterable, Optional
+from typing import Callable, Dict, Iterable, List, Optional, Sequence
 
 from . import plugin
 from .nn.trainer import StepMetrics
@@ -415,3 +415,182 @@ class StepTimer:
         else:
             ms, peak = (self._t1 - self._t0) * 1e3, 0.0
         return StepMetrics(step_time_ms=ms, mem_peak_mb=peak, retry_rate=0.0, extra={k: float(v) for k, v in extra.items()})
+
+
+# ----------------------------------------------------------------------------------------------
+# Atlas: frames of named metrics grouped into districts, bounded routes and their summaries
+# (crates/st-core/src/telemetry/atlas.rs:129-700, :1070-1400, :2007-2030)
+# ----------------------------------------------------------------------------------------------
+
+_SURFACE = {"py", "python", "bindings", "session", "timeline", "config", "psychoid", "canvas"}
+_CONCOURSE = {"trainer", "maintainer", "atlas", "loop", "chrono", "policy", "resonator", "softlogic", "psi", "desire"}
+_SUBSTRATE = {"tensor", "backend", "core", "z", "collapse", "geometry", "kdsl", "realgrad"}
+
+
+def metric_root_token(name: str) -> str:
+    """Leading namespace token of a metric id: ``psi.total`` → ``psi``, ``canvas_energy`` → ``canvas``."""
+    import re
+    return next((t for t in re.split(r"[.:/\-_]", name.strip()) if t), "")
+
+
+def infer_district(name: str) -> str:
+    token = metric_root_token(name).lower()
+    if token in _SURFACE:
+        return "Surface"
+    if token in _CONCOURSE:
+        return "Concourse"
+    if token in _SUBSTRATE:
+        return "Substrate"
+    return "Unknown"
+
+
+@dataclass
+class AtlasFrame:
+    timestamp: float
+    loop_support: float = 0.0
+    collapse_total: Optional[float] = None
+    z_signal: Optional[float] = None
+    script_hint: Optional[str] = None
+    metrics: Dict[str, float] = field(default_factory=dict)
+    districts: Dict[str, str] = field(default_factory=dict)      # explicit district per metric
+    notes: List[str] = field(default_factory=list)
+    concepts: List[tuple] = field(default_factory=list)          # (term, sense)
+
+    def __post_init__(self):
+        if not math.isfinite(self.timestamp):
+            self.timestamp = 0.0
+
+    def push_metric(self, name: str, value: float, district: Optional[str] = None) -> None:
+        if math.isfinite(value):
+            self.metrics[name] = float(value)
+            if district:
+                self.districts[name] = district
+
+    def metric_value(self, name: str) -> Optional[float]:
+        return self.metrics.get(name)
+
+    def metrics_with_prefix(self, prefix: str) -> Dict[str, float]:
+        return {k: v for k, v in self.metrics.items() if k.startswith(prefix)}
+
+    def district_of(self, name: str) -> str:
+        return self.districts.get(name) or infer_district(name)
+
+
+class AtlasRoute:
+    """Bounded sequence of frames; frames without a positive timestamp are dropped."""
+
+    def __init__(self):
+        self.frames: List[AtlasFrame] = []
+
+    def __len__(self) -> int:
+        return len(self.frames)
+
+    def latest(self) -> Optional[AtlasFrame]:
+        return self.frames[-1] if self.frames else None
+
+    def push_bounded(self, frame: AtlasFrame, capacity: int = 0) -> None:
+        if frame.timestamp <= 0.0:
+            return
+        self.frames.append(frame)
+        if capacity > 0 and len(self.frames) > capacity:
+            del self.frames[: len(self.frames) - capacity]
+
+    def summary(self) -> "AtlasRouteSummary":
+        return AtlasRouteSummary(self.frames)
+
+
+class AtlasRouteSummary:
+    """Loop-support statistics, collapse / z-signal trends (latest − first), per-district metric
+    focus (coverage, mean, latest, delta, momentum = delta / (coverage − 1), std) and concept counts."""
+
+    def __init__(self, frames: Sequence[AtlasFrame]):
+        self.frames = len(frames)
+        self.latest_timestamp = frames[-1].timestamp if frames else 0.0
+        loops = [max(f.loop_support, 0.0) for f in frames]
+        self.loop_min = min(loops) if loops else 0.0
+        self.loop_max = max(loops) if loops else 0.0
+        self.mean_loop = sum(loops) / len(loops) if loops else 0.0
+        self.loop_std = math.sqrt(max(sum(l * l for l in loops) / len(loops) - self.mean_loop ** 2, 0.0)) if loops else 0.0
+        self.loop_trend = loops[-1] - loops[0] if len(loops) > 1 else None
+        collapse = [f.collapse_total for f in frames if f.collapse_total is not None and math.isfinite(f.collapse_total)]
+        zsig = [f.z_signal for f in frames if f.z_signal is not None and math.isfinite(f.z_signal)]
+        self.latest_collapse_total = collapse[-1] if collapse else None
+        self.collapse_trend = collapse[-1] - collapse[0] if len(collapse) > 1 else None
+        self.latest_z_signal = zsig[-1] if zsig else None
+        self.z_signal_trend = zsig[-1] - zsig[0] if len(zsig) > 1 else None
+        self.script_hint = next((f.script_hint for f in reversed(frames) if f.script_hint), None)
+        self.total_notes = sum(len(f.notes) for f in frames)
+        self.latest_notes = [n for f in frames for n in f.notes][-16:]
+        series: Dict[tuple, List[float]] = {}
+        for f in frames:
+            for name, value in f.metrics.items():
+                series.setdefault((f.district_of(name), name), []).append(value)
+        self.districts: Dict[str, List[dict]] = {}
+        for (district, name), vals in sorted(series.items()):
+            mean = sum(vals) / len(vals)
+            delta = vals[-1] - vals[0]
+            self.districts.setdefault(district, []).append({
+                "name": name, "coverage": len(vals), "mean": mean, "latest": vals[-1], "delta": delta,
+                "momentum": delta / (len(vals) - 1) if len(vals) > 1 else 0.0,
+                "std_dev": math.sqrt(max(sum(v * v for v in vals) / len(vals) - mean * mean, 0.0))})
+        self.concept_counts: Dict[tuple, int] = {}
+        for f in frames:
+            for term, sense in f.concepts:
+                self.concept_counts[(term, sense)] = self.concept_counts.get((term, sense), 0) + 1
+
+    def is_empty(self) -> bool:
+        return self.frames == 0
+
+    def latest_note(self) -> Optional[str]:
+        return self.latest_notes[-1] if self.latest_notes else None
+
+    def beacons(self, limit: int = 0) -> List[dict]:
+        """Metrics that moved, strongest first (intensity = max(|delta|, |momentum|))."""
+        out = []
+        for district, focus_list in self.districts.items():
+            for fc in focus_list:
+                intensity = max(abs(fc["delta"]), abs(fc["momentum"]))
+                if fc["coverage"] == 0 or intensity <= 1e-6:
+                    continue
+                trend = "steady" if abs(fc["delta"]) <= 1e-6 else ("rising" if fc["delta"] > 0 else "falling")
+                vol = fc["std_dev"]
+                variance = ("with calm variance" if vol <= 1e-6 else "with mild variance" if vol < 0.25
+                            else "with adaptive variance" if vol < 0.75 else "with turbulent variance")
+                verb = {"rising": "is surging", "falling": "is easing", "steady": "holds steady"}[trend]
+                tempo = "flat momentum" if abs(fc["momentum"]) <= 1e-6 else "momentum"
+                out.append({"district": district, "metric": fc["name"], "coverage": fc["coverage"], "mean": fc["mean"],
+                            "latest": fc["latest"], "delta": fc["delta"], "momentum": fc["momentum"],
+                            "volatility": vol, "intensity": intensity, "trend": trend,
+                            "narrative": f"{district}::{fc['name']} {verb} (Δ {fc['delta']:+.3f}, {tempo} "
+                                         f"{fc['momentum']:+.3f}, σ {vol:.3f}) {variance}."})
+        out.sort(key=lambda b: (-b["intensity"], b["metric"]))
+        return out[:limit] if limit > 0 else out
+
+    def beacon_for(self, metric: str) -> Optional[dict]:
+        return next((b for b in self.beacons() if b["metric"] == metric), None)
+
+    def concept_heatmap(self) -> dict:
+        senses: Dict[str, int] = {}
+        terms: Dict[str, int] = {}
+        for (term, sense), n in self.concept_counts.items():
+            senses[sense] = senses.get(sense, 0) + n
+            terms[term] = terms.get(term, 0) + n
+        return {"sense_counts": senses, "term_counts": terms, "total_mentions": sum(terms.values()),
+                "total_terms": len(terms)}
+
+    def flux(self) -> Optional[dict]:
+        if self.frames == 0:
+            return None
+        heat = self.concept_heatmap()
+        return {"coverage": self.frames, "loop_range": max(self.loop_max - self.loop_min, 0.0),
+                "loop_variability": self.loop_std, "collapse_drift": self.collapse_trend or 0.0,
+                "z_signal_drift": self.z_signal_trend or 0.0, "note_density": self.total_notes / self.frames,
+                "concept_density": heat["total_mentions"] / self.frames}
+
+    def to_json(self) -> dict:
+        return {"frames": self.frames, "latest_timestamp": self.latest_timestamp, "mean_loop": self.mean_loop,
+                "loop_std": self.loop_std, "loop_min": self.loop_min, "loop_max": self.loop_max,
+                "latest_collapse_total": self.latest_collapse_total, "collapse_trend": self.collapse_trend,
+                "latest_z_signal": self.latest_z_signal, "z_signal_trend": self.z_signal_trend,
+                "script_hint": self.script_hint, "total_notes": self.total_notes, "latest_notes": self.latest_notes,
+                "districts": self.districts, "beacons": self.beacons(8), "flux": self.flux()}

@@ -613,3 +613,34 @@ def test_video_pipeline_digests():
     assert len(outs[3]["z_dynamics"]["per_depth_energy"]) == 2 and len(pipe.atlas_timeline()) == 4
     assert outs[3]["atlas_frame"]["metrics"]["z.weight_entropy"] > 0
     assert pipe.next_frame() is None
+
+
+def test_atlas_route_summary():
+    from spiraltorch_b200 import telemetry as T
+    assert T.metric_root_token("  .loop.frames ") == "loop" and T.infer_district("canvas_energy") == "Surface"
+    assert T.infer_district("z.motion") == "Substrate" and T.infer_district("foo") == "Unknown"
+    route = T.AtlasRoute()
+    route.push_bounded(T.AtlasFrame(0.0))                       # dropped: no positive timestamp
+    for i in range(1, 6):
+        f = T.AtlasFrame(float(i), loop_support=0.1 * i, collapse_total=1.0 / i, z_signal=0.2 * i)
+        f.push_metric("trainer.loss", 2.0 - 0.3 * i)
+        f.push_metric("z.energy", 1.0)
+        f.push_metric("custom", float(i), district="Surface")
+        f.notes.append(f"n{i}")
+        f.concepts.append(("spiral", "qualia"))
+        route.push_bounded(f, capacity=4)
+    assert len(route) == 4 and route.latest().timestamp == 5.0
+    s = route.summary()
+    assert s.frames == 4 and s.loop_min == pytest.approx(0.2) and s.loop_max == pytest.approx(0.5)
+    assert s.collapse_trend == pytest.approx(1 / 5 - 1 / 2) and s.z_signal_trend == pytest.approx(0.6)
+    assert set(s.districts) == {"Concourse", "Substrate", "Surface"}
+    beacons = s.beacons()
+    assert [b["metric"] for b in beacons] == ["custom", "trainer.loss"]        # z.energy did not move
+    assert beacons[1]["trend"] == "falling" and "is easing" in beacons[1]["narrative"]
+    assert s.beacon_for("z.energy") is None and s.latest_note() == "n5"
+    assert s.concept_heatmap()["total_mentions"] == 4
+    flux = s.flux()
+    assert flux["coverage"] == 4 and flux["note_density"] == 1.0 and flux["loop_range"] == pytest.approx(0.3)
+    import json
+    json.dumps(s.to_json())
+    assert T.AtlasRoute().summary().flux() is None
