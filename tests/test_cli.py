@@ -58,3 +58,20 @@ def test_z_volume_and_xai_tools(capsys, tmp_path):
     assert cli.main(["xai", "--out", str(cam), "--size", "16", "--classes", "4", "--backend", "cpu"]) == 0
     rep = json.loads(capsys.readouterr().out)
     assert rep["cam_shape"] == [8, 8] and cam.read_bytes().startswith(b"P6 16 16 255\n")
+
+
+def test_capability_matrix():
+    from benchmarks import capability_matrix as cm
+    assert cm.parse_backend("B200") == "cuda" and cm.parse_backend(" CPU ") == "cpu"
+    import pytest
+    with pytest.raises(ValueError):
+        cm.parse_backend("wgpu")
+    row = cm.capability_by_name("tensor ops")
+    assert row.entry("cuda").state == cm.READY and "tcgen05" in row.entry("cuda").note
+    s = cm.summarize_backend("cuda")
+    assert s["tracked"] == s["ready"] + s["planned"] + s["stub"] and 0 < s["readiness_ratio"] <= 1
+    assert any(r.capability == "Sparse tensor ops" for r in cm.pending_capabilities_for_backend("cuda"))
+    assert cm.capabilities_with_note_containing("NVLink")[0].capability == "Distributed collectives"
+    md = cm.render_markdown()
+    assert md.splitlines()[0].startswith("| Capability | cpu | cuda |") and len(md.splitlines()) == len(cm.MATRIX) + 2
+    assert cm.matrix_summary()["capabilities"] == len(cm.MATRIX)
