@@ -300,3 +300,162 @@ class WarmupCosineScheduler:
         else:
             optimizer.set_fallback_learning_rate(lr)
         return lr
+
+
+_PRESSURE_MAX = 1.0e6
+
+
+class CurvatureScheduler:
+    """Keeps the (negative) curvature of the hyperbolic optimiser near a target gradient pressure.
+
+    ``observe_pressure(p)`` smooths ``p`` (EMA, ``smoothing``), and outside the tolerance band moves
+    the curvature by ``clamp(kp · (1 + boost · stability) · error, ±step)`` where stability falls from
+    1 to 0 as the relative variance of the pressure approaches ``stability_threshold``; inside the
+    band, after ``dither_period`` stable steps, it dithers by ``±dither_strength · step``.
+    Behaviour and defaults: crates/st-nn/src/trainer.rs:155-640; environment overrides
+    ``SPIRAL_CURVATURE_{STEP,TOLERANCE,ALPHA,KP,STABILITY_THRESHOLD,STABILITY_BOOST,DITHER_STRENGTH,DITHER_PERIOD}``.
+    """
+
+    def __init__(self, initial: float, min_curvature: float, max_curvature: float, target_pressure: float):
+        lo, hi = min(min_curvature, -1e-6), min(max_curvature, -1e-6)
+        if lo > hi:
+            lo, hi = hi, lo
+        self.min_curvature, self.max_curvature = lo, hi
+        self.current = min(min(max(initial, lo), hi), -1e-6)
+        self.target_pressure = min(max(target_pressure, 0.0), _PRESSURE_MAX) if math.isfinite(target_pressure) else 0.0
+        self.tolerance, self.step, self.kp, self.alpha = 0.05, 0.05, 1.0, 0.2
+        self.ema_pressure: Optional[float] = None
+        self.ema_pressure2: Optional[float] = None
+        self.stability_threshold, self.stability_boost, self.stable_steps = 1.0e-3, 0.5, 0
+        self.dither_strength, self.dither_period, self.dither_sign = 0.15, 8, 1.0
+
+    # setters ignore values outside their domain, as the reference does
+    def set_step(self, v: float):
+        if math.isfinite(v) and v > 0:
+            self.step = v
+
+    def set_proportional_gain(self, v: float):
+        if math.isfinite(v) and v >= 0:
+            self.kp = v
+
+    def set_tolerance(self, v: float):
+        if math.isfinite(v) and v >= 0:
+            self.tolerance = v
+
+    def set_smoothing(self, v: float):
+        if math.isfinite(v) and v > 0:
+            self.alpha = min(max(v, 0.01), 1.0)
+
+    def set_stability_threshold(self, v: float):
+        if math.isfinite(v) and v > 0:
+            self.stability_threshold = v
+
+    def set_stability_boost(self, v: float):
+        if math.isfinite(v) and v >= 0:
+            self.stability_boost = v
+
+    def set_dither(self, strength: float, period: int):
+        if math.isfinite(strength) and strength >= 0:
+            self.dither_strength = min(strength, 1.0)
+        if period > 0:
+            self.dither_period = int(period)
+
+    def set_target_pressure(self, v: float):
+        if math.isfinite(v):
+            self.target_pressure = min(max(v, 0.0), _PRESSURE_MAX)
+
+    def set_bounds(self, min_curvature: float, max_curvature: float):
+        lo, hi = min(min_curvature, -1e-6), min(max_curvature, -1e-6)
+        if lo > hi:
+            lo, hi = hi, lo
+        self.min_curvature, self.max_curvature = lo, hi
+        self.current = min(min(max(self.current, lo), hi), -1e-6)
+
+    def apply_env_overrides(self, env=None) -> "CurvatureScheduler":
+        import os
+        env = os.environ if env is None else env
+
+        def num(key, cast=float):
+            try:
+                return cast(env[key])
+            except (KeyError, ValueError):
+                return None
+        for key, setter in (("SPIRAL_CURVATURE_STEP", self.set_step), ("SPIRAL_CURVATURE_TOLERANCE", self.set_tolerance),
+                            ("SPIRAL_CURVATURE_ALPHA", self.set_smoothing), ("SPIRAL_CURVATURE_KP", self.set_proportional_gain),
+                            ("SPIRAL_CURVATURE_STABILITY_THRESHOLD", self.set_stability_threshold),
+                            ("SPIRAL_CURVATURE_STABILITY_BOOST", self.set_stability_boost)):
+            v = num(key)
+            if v is not None:
+                setter(v)
+        s, p = num("SPIRAL_CURVATURE_DITHER_STRENGTH"), num("SPIRAL_CURVATURE_DITHER_PERIOD", int)
+        if s is not None or p is not None:
+            self.set_dither(self.dither_strength if s is None else s, self.dither_period if p is None else p)
+        return self
+
+    def sync(self, curvature: float) -> None:
+        """Adopts an externally chosen curvature and forgets the pressure history."""
+        self.current = min(min(max(curvature, self.min_curvature), self.max_curvature), -1e-6)
+        self.ema_pressure = self.ema_pressure2 = None
+        self.stable_steps, self.dither_sign = 0, 1.0
+
+    def last_pressure_variance(self) -> Optional[float]:
+        if self.ema_pressure is None or self.ema_pressure2 is None:
+            return None
+        return max(self.ema_pressure2 - self.ema_pressure ** 2, 0.0)
+
+    def observe(self, gradient: torch.Tensor) -> dict:
+        """Pressure = mean absolute value of a gradient tensor."""
+        return self.observe_pressure(float(gradient.detach().abs().mean()) if gradient.numel() else 0.0)
+
+    def observe_pressure(self, raw_pressure: float) -> dict:
+        raw = min(max(raw_pressure, 0.0), _PRESSURE_MAX) if math.isfinite(raw_pressure) else 0.0
+        a = self.alpha
+        smoothed = raw if self.ema_pressure is None else self.ema_pressure + a * (raw - self.ema_pressure)
+        smoothed = min(max(smoothed, 0.0), _PRESSURE_MAX)
+        self.ema_pressure = smoothed
+        sq = raw * raw
+        self.ema_pressure2 = sq if self.ema_pressure2 is None else self.ema_pressure2 + a * (sq - self.ema_pressure2)
+        variance = max(self.ema_pressure2 - smoothed * smoothed, 0.0)
+        rel_var = variance / (smoothed * smoothed + 1.0e-6)
+        error = smoothed - self.target_pressure
+        within = abs(error) <= self.tolerance
+        stable = within and rel_var <= self.stability_threshold
+        self.stable_steps = self.stable_steps + 1 if stable else 0
+        delta = 0.0
+        if not within:
+            stability = max(1.0 - min(max(rel_var / self.stability_threshold, 0.0), 1.0), 0.0)
+            kp = self.kp * (1.0 + self.stability_boost * stability)
+            delta = min(max(kp * error, -self.step), self.step)
+        elif stable and self.dither_strength > 0 and self.stable_steps >= self.dither_period:
+            delta = self.dither_sign * self.dither_strength * self.step
+            self.dither_sign = -self.dither_sign
+            self.stable_steps = 0
+        changed = False
+        if abs(delta) > 1.1920929e-07:
+            nxt = min(min(max(self.current + delta, self.min_curvature), self.max_curvature), -1e-6)
+            if abs(nxt - self.current) > 1.1920929e-07:
+                self.current, changed = nxt, True
+        return {"raw_pressure": raw, "smoothed_pressure": smoothed, "curvature": self.current, "changed": changed}
+
+    _FIELDS = ("min_curvature", "max_curvature", "target_pressure", "tolerance", "step", "kp", "alpha", "current",
+               "ema_pressure", "ema_pressure2", "stability_threshold", "stability_boost", "stable_steps",
+               "dither_strength", "dither_period", "dither_sign")
+
+    def state(self) -> dict:
+        d = {k: getattr(self, k) for k in self._FIELDS}
+        d["proportional_gain"], d["smoothing"] = d.pop("kp"), d.pop("alpha")
+        return d
+
+    @classmethod
+    def from_state(cls, state: dict) -> "CurvatureScheduler":
+        s = dict(state)
+        for key in ("min_curvature", "max_curvature", "current"):
+            if not (math.isfinite(s[key]) and s[key] < 0):
+                raise ValueError(f"curvature scheduler state: {key} must be negative and finite")
+        if s["min_curvature"] > s["max_curvature"]:
+            raise ValueError("curvature scheduler state: min_curvature exceeds max_curvature")
+        sch = cls(s["current"], s["min_curvature"], s["max_curvature"], s["target_pressure"])
+        s["kp"], s["alpha"] = s.pop("proportional_gain"), s.pop("smoothing")
+        for k in cls._FIELDS:
+            setattr(sch, k, s[k])
+        return sch

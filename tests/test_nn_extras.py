@@ -169,3 +169,29 @@ def test_field_layers_match_their_definitions():
         yy = layer.forward(xx)
         gx = layer.backward(xx, st.Tensor._wrap(torch.ones_like(yy.torch())))
         assert gx.shape() == xx.shape() and any(p.accumulators() for p in layer.parameters())
+
+
+def test_curvature_scheduler_tracks_pressure():
+    from spiraltorch_b200.nn import CurvatureScheduler
+    s = CurvatureScheduler(-1.0, -2.0, -0.1, target_pressure=0.5)
+    d = s.observe_pressure(1.5)                                  # error +1 -> step limited to +0.05
+    assert d["changed"] and d["curvature"] == pytest.approx(-0.95) and d["smoothed_pressure"] == 1.5
+    for _ in range(40):
+        s.observe_pressure(1.5)
+    assert s.current == pytest.approx(-0.1)                      # saturates at the upper bound
+    s.sync(-1.0)
+    assert s.ema_pressure is None
+    for _ in range(7):
+        assert not s.observe_pressure(0.5)["changed"]            # inside the band, stable
+    d = s.observe_pressure(0.5)                                  # 8th stable step: dither +0.15 * 0.05
+    assert d["changed"] and d["curvature"] == pytest.approx(-1.0 + 0.0075)
+    assert s.dither_sign == -1.0
+    st_ = s.state()
+    s2 = CurvatureScheduler.from_state(st_)
+    assert s2.state() == st_
+    with pytest.raises(ValueError):
+        CurvatureScheduler.from_state({**st_, "current": 0.5})
+    s3 = CurvatureScheduler(-5.0, -0.5, -3.0, 0.1).apply_env_overrides({"SPIRAL_CURVATURE_STEP": "0.2", "SPIRAL_CURVATURE_DITHER_PERIOD": "3", "SPIRAL_CURVATURE_KP": "bad"})
+    assert (s3.min_curvature, s3.max_curvature, s3.current) == (-3.0, -0.5, -3.0)
+    assert s3.step == 0.2 and s3.dither_period == 3 and s3.kp == 1.0
+    assert s3.observe(torch.full((4, 4), -2.0))["raw_pressure"] == 2.0
