@@ -6,3 +6,4 @@ from .rendezvous import (BufferLengthMismatch, CollectiveTimeout, DistributedErr
                          PeerTensorFailure, RankOutOfBounds, UnknownRank, WorldSizeMismatch, join)
 from .arena import (AgentConfig, AmebaAutograd, AutogradError, CollectiveArena, CollectiveError,
                     CollectiveExecutionReport, DistributedTrainer, DistributedTrainerError)
+from . import lanes

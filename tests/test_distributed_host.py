@@ -271,3 +271,55 @@ def test_distributed_trainer_and_gossip_autograd():
     with pytest.raises(A.AutogradError, match="unknown neighbour"):
         mesh.propagate_round()
     assert mesh.weights(9) == [0.0, 0.0] and mesh.pending_messages() == 1
+
+
+def test_lane_distribution_and_consensus():
+    from spiraltorch_b200.distributed import lanes as LN
+    assert LN.canonical_lane_draw(0) == pytest.approx(0.8833108082136426, abs=1e-15)   # splitmix64(0) = 0xE220A8397B1DCDAF
+    d = LN.LaneDistribution.from_weights([(256, 2.0), (64, 1.0), (1024, 1.0)])
+    assert [l for l, _ in d.entries] == [64, 256, 1024]
+    assert d.mass() == pytest.approx(1.0) and d.entries[1][1] == pytest.approx(0.5)
+    assert d.effective_sample_size() == pytest.approx(1 / (0.25 ** 2 * 2 + 0.25))
+    s = d.sample(0)
+    assert s["params"]["lane"] == 1024 and s["seed"] == "0" and s["rng_algorithm"] == "splitmix64_u53_v1"
+    d.validate_sample(s)
+    with pytest.raises(LN.LaneProbabilityError):
+        d.validate_sample({**s, "support_index": "0"})
+    med = LN.consensus_lane_params(d, "median")
+    mean = LN.consensus_lane_params(d, "weighted_mean")
+    assert med["params"]["lane"] == 256 and mean["params"]["lane"] == 400        # (16 + 128 + 256)
+    assert med["report"]["input_sha256"] == d.sha256() and med["report"]["output_sha256"] != mean["report"]["output_sha256"]
+    for bad in ([], [(0, 1.0)], [(8, 1.0), (8, 2.0)], [(8, float("nan"))], [(8, -1.0)]):
+        with pytest.raises(LN.LaneProbabilityError):
+            LN.LaneDistribution.from_weights(bad)
+    with pytest.raises(LN.LaneProbabilityError):
+        LN.LaneDistribution.from_probabilities([(8, 0.5), (16, 0.4)])             # mass 0.9 is rejected, not repaired
+    with pytest.raises(LN.LaneProbabilityError):
+        LN.parse_policy("mode")
+    merged = LN.merge_votes([(128, 1.0), (256, 1.0), (128, 2.0)])
+    assert merged.entries[0] == (128, pytest.approx(0.75))
+    assert LN.distributed_consensus([(512, 1.0)])["params"]["lane"] == 512        # no process group: local votes
+
+
+def _lane_rank(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    from spiraltorch_b200.distributed import lanes as LN
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    out = LN.distributed_consensus([(128, 1.0)] if rank == 0 else [(512, 1.0), (128, 0.5)], policy="median")
+    q.put((rank, out["params"]["lane"], out["report"]["output_sha256"]))
+    dist.destroy_process_group()
+
+
+def test_lane_consensus_across_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_lane_rank, args=(r, 2, 29641, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert res[0][1] == res[1][1] == 128 and res[0][2] == res[1][2]
