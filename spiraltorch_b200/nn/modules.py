@@ -212,6 +212,101 @@ class Module:
             self.load_state_dict(state)
         return report
 
+    # ---- checkpoints with renamed / reshaped keys (bindings/st-py/src/nn.rs:5277-5653) ------
+    @staticmethod
+    def _transform_state(source: torch.Tensor, transform: str, target_shape) -> torch.Tensor:
+        def overlap(t):
+            out = torch.zeros(target_shape, dtype=t.dtype, device=t.device)
+            r, c = min(t.shape[0], target_shape[0]), min(t.shape[1], target_shape[1])
+            out[:r, :c] = t[:r, :c]
+            return out
+        if transform == "identity":
+            return source
+        if transform == "transpose":
+            return source.t().contiguous()
+        if transform in ("copy_overlap_zeros", "copy_overlap"):
+            return overlap(source)
+        if transform in ("transpose_copy_overlap_zeros", "transpose_copy_overlap"):
+            return overlap(source.t())
+        raise ValueError(f"unsupported state_dict transform '{transform}'")
+
+    def _mapped_report(self, checkpoint, key_map):
+        import hashlib
+        if not isinstance(key_map, dict):
+            raise TypeError("key_map must be a dict mapping source keys to target keys or rule dicts")
+        ckpt = {k: _t(v) for k, v in dict(checkpoint.items() if hasattr(checkpoint, "items") else checkpoint).items()}
+        expected = {p.name: p.value for p in self.parameters()}
+        entries, adapted, seen, mapped_sources = [], {}, set(), set()
+        matched = missing = shape_mismatched = unknown_targets = 0
+        for source_name, rule in key_map.items():
+            if isinstance(rule, str):
+                target, transform = rule, "identity"
+            elif isinstance(rule, dict):
+                if "target" not in rule:
+                    raise ValueError("key_map rule missing 'target'")
+                target, transform = rule["target"], rule.get("transform", "identity")
+            else:
+                raise TypeError("key_map values must be target strings or dicts with target/transform fields")
+            mapped_sources.add(source_name)
+            src = ckpt.get(source_name)
+            entry = {"name": target, "source_name": source_name, "transform": transform, "expected_shape": None,
+                     "source_shape": tuple(src.shape) if src is not None else None,
+                     "original_source_shape": tuple(src.shape) if src is not None else None}
+            if target not in expected:
+                unknown_targets += 1
+                entries.append({**entry, "status": "unexpected_target"})
+                continue
+            seen.add(target)
+            want = tuple(expected[target].shape)
+            entry["expected_shape"] = want
+            if src is None:
+                missing += 1
+                entries.append({**entry, "status": "missing_source"})
+                continue
+            out = self._transform_state(src, transform, want)
+            entry["source_shape"] = tuple(out.shape)
+            if tuple(out.shape) == want:
+                matched += 1
+                adapted[target] = out
+                entries.append({**entry, "status": "matched"})
+            else:
+                shape_mismatched += 1
+                entries.append({**entry, "status": "shape_mismatch"})
+        for name, value in expected.items():
+            if name not in seen:
+                missing += 1
+                entries.append({"name": name, "status": "missing_rule", "source_name": "", "transform": "identity",
+                                "expected_shape": tuple(value.shape), "source_shape": None,
+                                "original_source_shape": None})
+
+        def state_hash(state):
+            h = hashlib.sha256()
+            for k in sorted(state):
+                v = state[k].detach().to(torch.float32).cpu().contiguous()
+                h.update(k.encode())
+                h.update(str(tuple(v.shape)).encode())
+                h.update(v.numpy().tobytes())
+            return h.hexdigest()
+        report = {"compatible": missing == 0 and shape_mismatched == 0 and matched > 0, "matched": matched,
+                  "missing": missing, "shape_mismatched": shape_mismatched,
+                  "extra": sum(1 for k in ckpt if k not in mapped_sources) + unknown_targets, "entries": entries,
+                  "source_hash": state_hash(ckpt), "matched_subset_hash": state_hash(adapted)}
+        return report, adapted
+
+    def state_dict_compatibility_with_key_map(self, checkpoint, key_map) -> dict:
+        """Report of how a foreign checkpoint maps onto this module under ``key_map``:
+        ``{source: target}`` or ``{source: {"target": ..., "transform": identity | transpose |
+        copy_overlap_zeros | transpose_copy_overlap_zeros}}``."""
+        return self._mapped_report(checkpoint, key_map)[0]
+
+    def load_state_dict_subset_mapped_checked(self, checkpoint, key_map) -> dict:
+        """Loads every matched entry (and only those); parameters without a usable source keep their values."""
+        report, adapted = self._mapped_report(checkpoint, key_map)
+        for p in self.parameters():
+            if p.name in adapted:
+                p.value.copy_(adapted[p.name].to(p.value.device, torch.float32))
+        return report
+
 
 # ------------------------------------------------------------------------------------------------
 def _linear_args(args, kwargs, what: str):

@@ -339,3 +339,26 @@ def test_spiral_lightning_plans():
     loss = L.InfoNCELoss(0.1)
     with pytest.raises(st.TensorError):
         loss.forward(st.Tensor.zeros(3, 4), None)
+
+
+def test_mapped_state_dict_loading():
+    lin = st.nn.Linear(3, 2, name="fc")
+    ckpt = {"dense.kernel": torch.arange(6, dtype=torch.float32).reshape(2, 3),        # (out, in): needs a transpose
+            "dense.bias": torch.ones(1, 4), "junk": torch.zeros(1, 1)}
+    key_map = {"dense.kernel": {"target": "fc::weight", "transform": "transpose"},
+               "dense.bias": {"target": "fc::bias", "transform": "copy_overlap_zeros"},
+               "dense.gone": "fc::nothing"}
+    rep = lin.state_dict_compatibility_with_key_map(ckpt, key_map)
+    assert rep["matched"] == 2 and rep["missing"] == 0 and rep["extra"] == 2 and rep["compatible"]
+    assert {e["status"] for e in rep["entries"]} == {"matched", "unexpected_target"}
+    rep2 = lin.load_state_dict_subset_mapped_checked(ckpt, key_map)
+    assert rep2["matched_subset_hash"] == rep["matched_subset_hash"]
+    w = dict(lin.state_dict())["fc::weight"].torch()
+    assert torch.equal(w, ckpt["dense.kernel"].t()) and dict(lin.state_dict())["fc::bias"].torch().tolist() == [[1.0, 1.0]]
+    bad = lin.state_dict_compatibility_with_key_map(ckpt, {"dense.kernel": "fc::weight"})
+    assert not bad["compatible"] and bad["shape_mismatched"] == 1 and bad["missing"] == 1
+    with pytest.raises(ValueError):
+        lin.state_dict_compatibility_with_key_map(ckpt, {"dense.kernel": {"target": "fc::weight", "transform": "rot"}})
+    seq = st.nn.Sequential()
+    seq.eval()
+    assert seq.training is False

@@ -195,3 +195,75 @@ def test_curvature_scheduler_tracks_pressure():
     assert (s3.min_curvature, s3.max_curvature, s3.current) == (-3.0, -0.5, -3.0)
     assert s3.step == 0.2 and s3.dither_period == 3 and s3.kp == 1.0
     assert s3.observe(torch.full((4, 4), -2.0))["raw_pressure"] == 2.0
+
+
+def test_nd_convolutions_match_torch():
+    import torch.nn.functional as F
+    from spiraltorch_b200 import nn
+    torch.manual_seed(0)
+    c2 = nn.Conv2d("c2", 3, 5, (3, 2), (2, 1), (1, 0), (1, 2), (9, 8))
+    x = torch.randn(4, 3 * 9 * 8)
+    params = {p.name: p for p in c2.parameters()}
+    wt, bs = params["c2::weight"].value, params["c2::bias"].value
+    assert wt.shape == (5, 3 * 3 * 2)
+    bs.copy_(torch.randn(1, 5))
+    ref = F.conv2d(x.reshape(4, 3, 9, 8), wt.reshape(5, 3, 3, 2), bs.reshape(-1), (2, 1), (1, 0), (1, 2))
+    y = c2.forward(st.Tensor._wrap(x)).torch()
+    assert c2.output_shape() == tuple(ref.shape[1:])
+    assert torch.allclose(y, ref.reshape(4, -1), atol=1e-4)
+    c3 = nn.Conv3d("c3", 2, 3, (2, 3, 2), (1, 2, 1), (0, 1, 1), (1, 1, 1), (4, 6, 5))
+    x3 = torch.randn(2, 2 * 4 * 6 * 5)
+    p3 = {p.name: p for p in c3.parameters()}
+    ref3 = F.conv3d(x3.reshape(2, 2, 4, 6, 5), p3["c3::weight"].value.reshape(3, 2, 2, 3, 2), None, (1, 2, 1), (0, 1, 1))
+    assert torch.allclose(c3.forward(st.Tensor._wrap(x3)).torch(), ref3.reshape(2, -1), atol=1e-4)
+    # 4-D: a kernel of extent 1 on the first axis reduces to independent 3-D convolutions
+    c4 = nn.Conv4d("c4", 2, 3, (1, 2, 2, 2), input_dims=(3, 4, 4, 4))
+    x4 = torch.randn(2, 2 * 3 * 4 * 4 * 4)
+    w4 = {p.name: p for p in c4.parameters()}["c4::weight"].value.reshape(3, 2, 2, 2, 2)
+    y4 = c4.forward(st.Tensor._wrap(x4)).torch().reshape(2, 3, 3, 3, 3, 3)
+    for a in range(3):
+        ref4 = F.conv3d(x4.reshape(2, 2, 3, 4, 4, 4)[:, :, a], w4)
+        assert torch.allclose(y4[:, :, a], ref4, atol=1e-4)
+    # backward through the Module API: dW is averaged over the batch like Linear
+    g = c2.backward(st.Tensor._wrap(x), st.Tensor._wrap(torch.ones_like(y)))
+    assert g.shape() == (4, 3 * 9 * 8)
+    with pytest.raises(st.TensorError):
+        c2.forward(st.Tensor._wrap(torch.randn(4, 7)))
+    with pytest.raises(st.TensorError):
+        nn.Conv2d("bad", 1, 1, (5, 5), input_hw=(3, 3))
+
+
+def test_conv6da_pools_and_wave_scan():
+    from spiraltorch_b200 import nn
+    from spiraltorch_b200.nn.conv import ramanujan_pi
+    import math
+    assert abs(ramanujan_pi(2) - math.pi) < 1e-14
+    layer = nn.Conv6da("z6", 2, 3, (2, 3, 3), leech_rank=24, leech_weight=0.5)
+    assert layer.neighbor_count() == 7
+    x = torch.randn(2, 2 * 18)
+    y = layer.forward(st.Tensor._wrap(x)).torch().reshape(2, 3, 2, 3, 3)
+    params = {p.name: p for p in layer.parameters()}
+    w = params["z6::weight"].value
+    assert w[0, 0] == pytest.approx(0.01) and w[0, 1] == pytest.approx(0.0131)
+    vol = x.reshape(2, 2, 2, 3, 3)
+    # centre cell (d=0, h=1, w=1) of sample 0: neighbours in offset order, zero outside the grid
+    nb = []
+    for od, oh, ow in layer.offsets:
+        d, h, ww = 0 + od, 1 + oh, 1 + ow
+        inside = 0 <= d < 2 and 0 <= h < 3 and 0 <= ww < 3
+        nb += [float(vol[0, ic, d, h, ww]) if inside else 0.0 for ic in range(2)]
+    nb = torch.tensor(nb)
+    density = 0.5 * (math.pi ** 12 / math.factorial(12)) * float(nb.norm()) * math.sqrt(24)
+    expect = float(w[1] @ nb) + density + (ramanujan_pi(6) - math.pi)
+    assert float(y[0, 1, 0, 1, 1]) == pytest.approx(expect, abs=1e-4)
+    mp = nn.MaxPool2d(2, (2, 2), (2, 2), (0, 0), (4, 4))
+    ap = nn.AvgPool2d(2, (2, 2), (2, 2), (0, 0), (4, 4))
+    img = torch.arange(32, dtype=torch.float32).reshape(1, 32)
+    assert mp.forward(st.Tensor._wrap(img)).torch()[0, :4].tolist() == [5.0, 7.0, 13.0, 15.0]
+    assert ap.forward(st.Tensor._wrap(img)).torch()[0, :2].tolist() == [2.5, 4.5]
+    ws = nn.WaveScan("ws", 3, 4, 2, steps=6, padding=1)
+    names = sorted(p.name for p in ws.parameters())
+    assert names == ["ws::conv::bias", "ws::conv::weight", "ws::gate::bias", "ws::gate::gain"]
+    out = ws.forward(st.Tensor._wrap(torch.randn(5, 18)))
+    assert out.shape() == (5, 4)
+    assert hasattr(nn, "GoldenRetriever") and nn.ZConv6DA is nn.Conv6da
