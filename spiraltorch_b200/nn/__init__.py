@@ -18,7 +18,7 @@ from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, Dyna
 from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregation, ZSpaceGraphBatchRegressor,
                   ZSpaceGraphConvolution, ZSpaceGraphNetwork, ZSpaceGraphRegressor)
 from .lightning import (InfoNCELoss, LightningConfig, LightningReport, LightningStage, SelfSupStage, SpiralLightning)
-from .zspace import (ArdParameters, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention, ZSpaceCoherenceSequencer, ZSpaceVae,
-                     ZTensor)
+from .zspace import (ArdParameters, LanguageWaveEncoder, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention,
+                     ZSpaceCoherenceSequencer, ZSpaceTextVae, ZSpaceVae, ZTensor)
 
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)

@@ -306,3 +306,118 @@ class ZSpaceVae:
         vae.load_state_dict({k: torch.tensor(v["data"]).reshape(v["shape"]) for k, v in blob["parameters"].items()})
         vae._kind = blob.get("optimizer", "sgd")
         return vae
+
+
+class LanguageWaveEncoder:
+    """Text → complex spectrum → Poincaré-ball coordinates (crates/st-tensor/src/pure.rs:8296-8360).
+
+    Each character contributes ``(ord mod 1024)/1024 + |sin((i+1)/n)|`` scaled by the temperature;
+    the DFT of that signal gives ``n`` complex values, each mapped to the disc with radius
+    ``tanh(|z|·sqrt(-c))`` and interleaved as ``(x, y)`` pairs; the row is then projected to the ball."""
+
+    def __init__(self, curvature: float = -1.0, temperature: float = 1.0):
+        if not (math.isfinite(curvature) and curvature < 0):
+            raise TensorError(f"curvature must be negative, got {curvature}")
+        if not (math.isfinite(temperature) and temperature > 0):
+            raise TensorError(f"temperature must be positive, got {temperature}")
+        self.curvature, self.temperature = curvature, temperature
+
+    def encode_wave(self, text: str) -> torch.Tensor:
+        n = len(text)
+        if n == 0:
+            raise TensorError("text is empty")
+        idx = torch.arange(1, n + 1, dtype=torch.float32)
+        bucket = torch.tensor([(ord(ch) % 1024) / 1024.0 for ch in text], dtype=torch.float32)
+        signal = (bucket + torch.sin(idx / n).abs()) * self.temperature
+        return torch.fft.fft(signal.to(torch.complex64))
+
+    def encode_z_space(self, text: str) -> torch.Tensor:
+        wave = self.encode_wave(text)
+        radius = torch.tanh(wave.abs() * math.sqrt(-self.curvature))
+        angle = torch.angle(wave)
+        coords = torch.stack([radius * torch.cos(angle), radius * torch.sin(angle)], dim=1).reshape(1, -1)
+        from .modules import _project_rows
+        return _project_rows(coords, self.curvature)
+
+
+class ZSpaceTextVae:
+    """Z-space VAE over fixed character windows: text is cut or space-padded to ``window_chars``,
+    encoded by :class:`LanguageWaveEncoder` into ``2·window_chars`` features and fed to
+    :class:`ZSpaceVae` (crates/st-nn/src/zspace_coherence/text_vae.rs:22-330)."""
+
+    def __init__(self, window_chars: int, latent_dim: int, curvature: float = -1.0, temperature: float = 1.0,
+                 seed: int = 0):
+        if window_chars <= 0:
+            raise TensorError("zspace_text_vae_window_chars must be positive")
+        if latent_dim <= 0:
+            raise TensorError("zspace_text_vae_latent_dim must be positive")
+        self.window_chars, self.input_dim = window_chars, 2 * window_chars
+        self.encoder = LanguageWaveEncoder(curvature, temperature)
+        self.vae = ZSpaceVae(self.input_dim, latent_dim, seed)
+
+    latent_dim = property(lambda self: self.vae.latent_dim)
+    curvature = property(lambda self: self.encoder.curvature)
+    temperature = property(lambda self: self.encoder.temperature)
+
+    def optimizer_kind(self) -> str:
+        return self.vae.optimizer_kind()
+
+    def configure_optimizer_by_name(self, name: str, **hyper) -> None:
+        self.vae.configure_optimizer_by_name(name, **hyper)
+
+    def reset_optimizer(self) -> None:
+        self.vae.reset_optimizer()
+
+    def _window(self, text: str) -> str:
+        return text[: self.window_chars].ljust(self.window_chars)
+
+    def encode_text(self, text: str) -> torch.Tensor:
+        return self.encoder.encode_z_space(self._window(text)).reshape(-1)
+
+    def encode_text_with_mellin(self, text: str, basis: torch.Tensor) -> torch.Tensor:
+        """Projects the encoding onto a ``(input_dim, input_dim)`` Mellin basis matrix."""
+        enc = self.encode_text(text)
+        if basis.shape != (self.input_dim, self.input_dim):
+            raise TensorError(f"Mellin basis must be {self.input_dim}x{self.input_dim}, got {tuple(basis.shape)}")
+        return basis.to(enc.dtype) @ enc
+
+    def _batch(self, texts, basis=None) -> torch.Tensor:
+        if not texts:
+            raise TensorError("text batch is empty")
+        enc = (lambda t: self.encode_text_with_mellin(t, basis)) if basis is not None else self.encode_text
+        return torch.stack([enc(t) for t in texts])
+
+    def forward_text(self, text: str, basis=None) -> ZSpaceVaeState:
+        return self.vae.forward(self._batch([text], basis))
+
+    def forward_mean_text(self, text: str, basis=None) -> ZSpaceVaeState:
+        return self.vae.forward_mean(self._batch([text], basis))
+
+    def train_text(self, text: str, learning_rate: float = 1e-2, beta: float = 1.0, basis=None) -> ZSpaceVaeState:
+        return self.vae.train_batch(self._batch([text], basis), learning_rate, beta)
+
+    def train_text_batch(self, texts, learning_rate: float = 1e-2, beta: float = 1.0, basis=None) -> ZSpaceVaeState:
+        return self.vae.train_batch(self._batch(list(texts), basis), learning_rate, beta)
+
+    def evaluate_text_batch(self, texts, basis=None) -> dict:
+        return self.vae.evaluate_batch(self._batch(list(texts), basis))
+
+    def save(self, path) -> None:
+        import json
+        from ..config import atomic_write
+        atomic_write(path, json.dumps({"version": 1, "window_chars": self.window_chars, "curvature": self.curvature,
+                                       "temperature": self.temperature, "latent_dim": self.latent_dim,
+                                       "optimizer": self.vae.optimizer_kind(),
+                                       "vae": {k: {"shape": list(v.shape), "data": v.flatten().tolist()}
+                                               for k, v in self.vae.state_dict().items()}}))
+
+    @classmethod
+    def load(cls, path) -> "ZSpaceTextVae":
+        import json
+        blob = json.load(open(path))
+        if blob.get("version") != 1:
+            raise TensorError(f"unsupported text VAE checkpoint version {blob.get('version')}")
+        m = cls(blob["window_chars"], blob["latent_dim"], blob["curvature"], blob["temperature"])
+        m.vae.load_state_dict({k: torch.tensor(v["data"]).reshape(v["shape"]) for k, v in blob["vae"].items()})
+        m.vae._kind = blob.get("optimizer", "sgd")
+        return m

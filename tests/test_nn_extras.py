@@ -267,3 +267,31 @@ def test_conv6da_pools_and_wave_scan():
     out = ws.forward(st.Tensor._wrap(torch.randn(5, 18)))
     assert out.shape() == (5, 4)
     assert hasattr(nn, "GoldenRetriever") and nn.ZConv6DA is nn.Conv6da
+
+
+def test_text_vae_learns_and_round_trips(tmp_path):
+    from spiraltorch_b200.nn import LanguageWaveEncoder, ZSpaceTextVae
+    enc = LanguageWaveEncoder(-1.0, 0.5)
+    z = enc.encode_z_space("spiral")
+    assert z.shape == (1, 12) and float(z.norm()) < 1.0                      # inside the unit ball
+    wave = enc.encode_wave("ab")
+    sig = [((ord("a") % 1024) / 1024 + abs(math.sin(0.5))) * 0.5, ((ord("b") % 1024) / 1024 + abs(math.sin(1.0))) * 0.5]
+    assert wave[0].real == pytest.approx(sig[0] + sig[1], rel=1e-5) and wave[1].real == pytest.approx(sig[0] - sig[1], abs=1e-5)
+    vae = ZSpaceTextVae(8, 3, seed=3)
+    assert vae.input_dim == 16 and vae.encode_text("hi").shape == (16,)
+    assert torch.equal(vae.encode_text("hi"), vae.encode_text("hi      "))   # space padding
+    texts = ["spiral torch", "z-space wave", "hello world"]
+    first = vae.evaluate_text_batch(texts)["recon_loss"]
+    vae.configure_optimizer_by_name("adam")
+    for _ in range(150):
+        vae.train_text_batch(texts, learning_rate=2e-2, beta=1e-3)
+    assert vae.evaluate_text_batch(texts)["recon_loss"] < 0.5 * first
+    path = tmp_path / "tv.json"
+    vae.save(path)
+    again = ZSpaceTextVae.load(path)
+    assert again.optimizer_kind() == "adam"
+    assert again.evaluate_text_batch(texts)["recon_loss"] == pytest.approx(vae.evaluate_text_batch(texts)["recon_loss"], rel=1e-5)
+    basis = torch.eye(16).flip(0)
+    assert torch.allclose(vae.encode_text_with_mellin("hi", basis), vae.encode_text("hi").flip(0))
+    with pytest.raises(st.TensorError):
+        ZSpaceTextVae(0, 3)
