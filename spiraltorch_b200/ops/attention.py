@@ -116,10 +116,9 @@ def attention_backward(q, k, v, o, lse, do, causal: bool = True, scale: Optional
     dk = torch.empty((B, Sk, H, D), dtype=torch.bfloat16, device=dev) if dk is None else dk
     dv = torch.empty((B, Sk, H, D), dtype=torch.bfloat16, device=dev) if dv is None else dv
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
-    dq_acc = torch.zeros((B, H, Sq, D), dtype=torch.float32, device=dev)
     a = _BwdArgs()
     a.Q, a.K, a.V, a.O, a.dO = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr()
-    a.lse, a.delta, a.dQ_acc = lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr()
+    a.lse, a.delta, a.dQ_acc = lse.data_ptr(), delta.data_ptr(), None      # dQ accumulates in TMEM
     a.dQ, a.dK, a.dV = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     for pre, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", do), ("dq", dq), ("dk", dk), ("dv", dv)):
         setattr(a, pre + "_sb", t.stride(0))
