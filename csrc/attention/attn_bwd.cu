@@ -19,9 +19,10 @@
 // two (P from S, then dS from dP), S of the next tile is issued as soon as this tile's S has
 // been read, and dP of the next tile right after this tile's accumulate GEMMs, so the tensor
 // pipe works while the element-wise warps do.
-// Warp 8 is the TMA producer (two stationary tiles once; the streamed pair through a ring),
-// warp 9 issues the MMAs and owns TMEM, warps 0-7 do the element-wise work with two threads
-// per row.
+// Warp 16 is the TMA producer (two stationary tiles once; the streamed pair through a ring),
+// warp 17 issues the MMAs and owns TMEM, warps 0-15 do the element-wise work with four threads
+// per row (with two, the element-wise phase was latency-bound: 2 warps per scheduler cannot hide
+// the TMEM-load and MUFU latencies).
 //
 // The reference has no attention backward; the oracle is PyTorch autograd of the fp32 math.
 #include "../common/host.h"
@@ -36,7 +37,9 @@ namespace {
 using namespace st;
 
 constexpr int BLK = 128;
-constexpr int NUM_THREADS = 320;
+constexpr int EW_WARPS = 16;                       // element-wise warps: four threads per row, 32 key columns each
+constexpr int EW_THREADS = EW_WARPS * 32;
+constexpr int NUM_THREADS = EW_THREADS + 64;       // + TMA producer warp + MMA warp
 constexpr int MODE_KV = 0, MODE_Q = 1;
 
 struct AttnBwdParams {
@@ -62,11 +65,17 @@ template <int D, int MODE>
 struct BwdSmem {
   static constexpr int TILE = BLK * D * 2;
   static constexpr int P_TILE = BLK * BLK * 2;
-  static constexpr int NSLOT = MODE == MODE_KV ? 3 : 4;   // the dQ pass has no P buffer: one more ring slot
+  // streamed tiles: stream A is Q (dK/dV pass) or K (dQ pass), stream B is dO or V.  The dK/dV pass
+  // has room for three streamed tiles next to K, V, P and dS: two for Q, whose tile lives for a
+  // whole iteration, one for dO, which is released right after the first accumulate GEMM.  The
+  // dQ pass has no P buffer and double-buffers both streams.
+  static constexpr int NA = 2;
+  static constexpr int NB = MODE == MODE_KV ? 1 : 2;
   static constexpr int STAT0_OFF = 0;                  // K (MODE_KV) or Q (MODE_Q)
   static constexpr int STAT1_OFF = STAT0_OFF + TILE;   // V (MODE_KV) or dO (MODE_Q)
-  static constexpr int RING_OFF = STAT1_OFF + TILE;
-  static constexpr int DS_OFF = RING_OFF + NSLOT * TILE;
+  static constexpr int A_OFF = STAT1_OFF + TILE;
+  static constexpr int B_OFF = A_OFF + NA * TILE;
+  static constexpr int DS_OFF = B_OFF + NB * TILE;
   static constexpr int P_OFF = DS_OFF + P_TILE;        // MODE_KV only
   static constexpr int BAR_OFF = P_OFF + (MODE == MODE_KV ? P_TILE : 0);
   static constexpr int TOTAL = BAR_OFF + 256;
@@ -86,10 +95,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const AttnBwdParams p) {
   using L = BwdSmem<D, MODE>;
-  constexpr int DH = D / 2;
   constexpr int KB = D / 64;
-  constexpr int NSLOT = L::NSLOT;
-  // TMEM columns.  MODE_KV: S, dP, dV, dK.  MODE_Q: S, dP, dQ.
+  constexpr int NA = L::NA, NB = L::NB;
+  // TMEM columns.  MODE_KV: S, dP, dV, dK.  MODE_Q: S, dP (even tiles), dQ, dP (odd tiles).
   constexpr uint32_t S_COL = 0, DP_COL = 128, ACC0_COL = 256, ACC1_COL = 384;
   constexpr uint32_t TMEM_COLS = 512;
 
@@ -100,14 +108,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* stat_full = bars;          // 1
-  uint64_t* ring_full = bars + 1;      // NSLOT (<= 4)
-  uint64_t* ring_empty = bars + 5;     // NSLOT
+  uint64_t* a_full = bars + 1;         // 2
+  uint64_t* a_empty = bars + 3;        // 2
+  uint64_t* b_full = bars + 5;         // 2
+  uint64_t* b_empty = bars + 7;        // 2
   uint64_t* s_full = bars + 9;         // S of tile n is in TMEM
-  uint64_t* dp_full = bars + 10;       // dP of tile n is in TMEM (and tile n-1's accumulate GEMMs are done)
-  uint64_t* s_free = bars + 11;        // 256 arrivals: S of tile n has been read
-  uint64_t* pds_full = bars + 12;      // 256 arrivals: P / dS of tile n are in shared memory, dP has been read
-  uint64_t* acc_done = bars + 13;      // every GEMM of the CTA has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* dp_full = bars + 10;       // 2: dP of tile n is in TMEM (barrier n & 1)
+  uint64_t* s_free = bars + 12;        // 256 arrivals: S of tile n has been read (MODE_KV: and P is in shared memory)
+  uint64_t* pds_full = bars + 13;      // 256 arrivals: dS of tile n is in shared memory, dP has been read
+  uint64_t* ds_free = bars + 14;       // MODE_Q: the dQ GEMM of tile n has finished reading dS
+  uint64_t* acc_done = bars + 15;      // every GEMM of the CTA has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,14 +133,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(stat_full), 1);
-    for (int s = 0; s < NSLOT; ++s) {
-      mbar_init(smem_u32(&ring_full[s]), 1);
-      mbar_init(smem_u32(&ring_empty[s]), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&a_full[s]), 1);
+      mbar_init(smem_u32(&a_empty[s]), 1);
+      mbar_init(smem_u32(&b_full[s]), 1);
+      mbar_init(smem_u32(&b_empty[s]), 1);
+      mbar_init(smem_u32(&dp_full[s]), 1);
     }
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(dp_full), 1);
-    mbar_init(smem_u32(s_free), 256);
-    mbar_init(smem_u32(pds_full), 256);
+    mbar_init(smem_u32(s_free), EW_THREADS);
+    mbar_init(smem_u32(pds_full), EW_THREADS);
+    mbar_init(smem_u32(ds_free), 1);
     mbar_init(smem_u32(acc_done), 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -138,7 +152,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
   }
-  if (warp == 9) {
+  if (warp == EW_WARPS + 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -147,126 +161,153 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == EW_WARPS) {
     // ---------------------------- TMA producer -----------------------------------------
     if (lane == 0 && n_iter > 0) {
       const uint32_t sb = smem_u32(stat_full);
       mbar_arrive_expect_tx(sb, 2 * L::TILE);
       const CUtensorMap* st0 = MODE == MODE_KV ? &tmK : &tmQ;
       const CUtensorMap* st1 = MODE == MODE_KV ? &tmV : &tmdO;
+      const CUtensorMap* ma = MODE == MODE_KV ? &tmQ : &tmK;
+      const CUtensorMap* mb = MODE == MODE_KV ? &tmdO : &tmV;
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb) {
         tma_load_4d(smem_u32(smem + L::STAT0_OFF + kb * (BLK * 128)), st0, sb, kb * 64, h, own * BLK, b);
         tma_load_4d(smem_u32(smem + L::STAT1_OFF + kb * (BLK * 128)), st1, sb, kb * 64, h, own * BLK, b);
       }
-      for (int seq = 0; seq < 2 * n_iter; ++seq) {
-        const int slot = seq % NSLOT;
-        const uint32_t ph = (seq / NSLOT) & 1;
-        if (!mbar_wait(smem_u32(&ring_empty[slot]), ph ^ 1u, abort_flag)) break;
-        const uint32_t fb = smem_u32(&ring_full[slot]);
-        mbar_arrive_expect_tx(fb, L::TILE);
-        const int row0 = (t_begin + (seq >> 1)) * BLK;
-        const CUtensorMap* tm = MODE == MODE_KV ? ((seq & 1) ? &tmdO : &tmQ) : ((seq & 1) ? &tmV : &tmK);
+      for (int n = 0; n < n_iter; ++n) {
+        const int row0 = (t_begin + n) * BLK;
+        {
+          const int slot = n % NA;
+          if (!mbar_wait(smem_u32(&a_empty[slot]), ((n / NA) & 1) ^ 1u, abort_flag)) break;
+          const uint32_t fb = smem_u32(&a_full[slot]);
+          mbar_arrive_expect_tx(fb, L::TILE);
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem_u32(smem + L::RING_OFF + slot * L::TILE + kb * (BLK * 128)), tm, fb,
-                      kb * 64, h, row0, b);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem_u32(smem + L::A_OFF + slot * L::TILE + kb * (BLK * 128)), ma, fb, kb * 64, h, row0, b);
+        }
+        {
+          const int slot = n % NB;
+          if (!mbar_wait(smem_u32(&b_empty[slot]), ((n / NB) & 1) ^ 1u, abort_flag)) break;
+          const uint32_t fb = smem_u32(&b_full[slot]);
+          mbar_arrive_expect_tx(fb, L::TILE);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem_u32(smem + L::B_OFF + slot * L::TILE + kb * (BLK * 128)), mb, fb, kb * 64, h, row0, b);
+        }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == EW_WARPS + 1) {
     // ---------------------------- MMA issuer -------------------------------------------
-    if (lane == 0 && n_iter > 0) {
+    if (elect_one() && n_iter > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);   // S, dP
       constexpr uint32_t idesc_t = make_idesc_bf16(BLK, D, true, true);       // dV, dK
       constexpr uint32_t idesc_q = make_idesc_bf16(BLK, D, false, true);      // dQ
-      const uint32_t st0 = smem_u32(smem + L::STAT0_OFF);
-      const uint32_t st1 = smem_u32(smem + L::STAT1_OFF);
-      const uint32_t sp = smem_u32(smem + L::P_OFF);
-      const uint32_t sds = smem_u32(smem + L::DS_OFF);
-      auto ring = [&](int seq) { return smem_u32(smem + L::RING_OFF + (seq % NSLOT) * L::TILE); };
-      auto wait_ring = [&](int seq) {
-        return mbar_wait(smem_u32(&ring_full[seq % NSLOT]), (seq / NSLOT) & 1, abort_flag);
-      };
-      // S = Q·Kᵀ and dP = dO·Vᵀ: A is the query-side tile, B the key-side tile
-      auto issue_sdp = [&](uint32_t col, uint32_t a_tile, uint32_t b_tile) {
+      constexpr uint32_t HI = smem_desc_hi(1024);
+      // descriptor low words of every tile: K-major view (16-byte leading offset) and MN-major view
+      // (64-column blocks BLK*128 bytes apart); a K step adds a constant
+      const uint32_t st0_k = smem_desc_lo(smem_u32(smem + L::STAT0_OFF), 16);
+      const uint32_t st1_k = smem_desc_lo(smem_u32(smem + L::STAT1_OFF), 16);
+      const uint32_t ds_k = smem_desc_lo(smem_u32(smem + L::DS_OFF), 16);
+      const uint32_t ds_mn = smem_desc_lo(smem_u32(smem + L::DS_OFF), BLK * 128);
+      const uint32_t p_mn = smem_desc_lo(smem_u32(smem + L::P_OFF), BLK * 128);
+      auto a_k = [&](int n) { return smem_desc_lo(smem_u32(smem + L::A_OFF + (n % NA) * L::TILE), 16); };
+      auto a_mn = [&](int n) { return smem_desc_lo(smem_u32(smem + L::A_OFF + (n % NA) * L::TILE), BLK * 128); };
+      auto b_k = [&](int n) { return smem_desc_lo(smem_u32(smem + L::B_OFF + (n % NB) * L::TILE), 16); };
+      auto b_mn = [&](int n) { return smem_desc_lo(smem_u32(smem + L::B_OFF + (n % NB) * L::TILE), BLK * 128); };
+      auto wait_a = [&](int n) { return mbar_wait(smem_u32(&a_full[n % NA]), (n / NA) & 1, abort_flag); };
+      auto wait_b = [&](int n) { return mbar_wait(smem_u32(&b_full[n % NB]), (n / NB) & 1, abort_flag); };
+      // S = Q·Kᵀ and dP = dO·Vᵀ: both operands K-major, D/16 K steps
+      auto issue_sdp = [&](uint32_t col, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16_ss(tmem_base + col, make_smem_desc_sw128(a_tile + kb * (BLK * 128) + k * 32, 16, 1024),
-                         make_smem_desc_sw128(b_tile + kb * (BLK * 128) + k * 32, 16, 1024), idesc_s,
-                         (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t off = (kb * (BLK * 128) + k * 32) >> 4;
+            umma_bf16_ss_split(tmem_base + col, a_lo + off, HI, b_lo + off, HI, idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+      };
+      // accumulate GEMMs over the 128 rows of the streamed tile: A and B read through MN-major views
+      auto issue_acc_mn = [&](uint32_t col, uint32_t a_lo, uint32_t b_lo, bool acc_first) {
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {
+          const uint32_t off = (kk * (16 * 128)) >> 4;
+          umma_bf16_ss_split(tmem_base + col, a_lo + off, HI, b_lo + off, HI, idesc_t, (acc_first || kk != 0) ? 1u : 0u);
+        }
+      };
+      auto issue_s = [&](int n) {
+        if (MODE == MODE_KV) issue_sdp(S_COL, a_k(n), st0_k); else issue_sdp(S_COL, st0_k, a_k(n));
+        umma_commit(smem_u32(s_full));
+      };
+      auto issue_dp = [&](int n) {
+        const uint32_t col = (MODE == MODE_Q && (n & 1)) ? ACC1_COL : DP_COL;
+        if (MODE == MODE_KV) issue_sdp(col, b_k(n), st1_k); else issue_sdp(col, st1_k, b_k(n));
+        umma_commit(smem_u32(&dp_full[n & 1]));
+        if (MODE == MODE_Q) umma_commit(smem_u32(&b_empty[n % NB]));   // V is only needed by dP
       };
       bool ok = mbar_wait(smem_u32(stat_full), 0, abort_flag);
       // prologue: S(0), dP(0)
-      if (ok && (ok = wait_ring(0))) {
+      if (ok && (ok = wait_a(0))) {
         tc_fence_after();
-        if (MODE == MODE_KV) issue_sdp(S_COL, ring(0), st0); else issue_sdp(S_COL, st0, ring(0));
-        umma_commit(smem_u32(s_full));
+        issue_s(0);
       }
-      if (ok && (ok = wait_ring(1))) {
+      if (ok && (ok = wait_b(0))) {
         tc_fence_after();
-        if (MODE == MODE_KV) issue_sdp(DP_COL, ring(1), st1); else issue_sdp(DP_COL, st1, ring(1));
-        umma_commit(smem_u32(dp_full));
-        if (MODE == MODE_Q) umma_commit(smem_u32(&ring_empty[1 % NSLOT]));   // V is only needed by dP
+        issue_dp(0);
       }
       for (int n = 0; n < n_iter && ok; ++n) {
         const bool more = n + 1 < n_iter;
+        if (!(ok = mbar_wait(smem_u32(s_free), n & 1, abort_flag))) break;
+        tc_fence_after();
+        if (MODE == MODE_KV) {
+          // dV[kv, d] += sum_q P[q, kv] dO[q, d]   (P is complete once S has been read)
+          issue_acc_mn(ACC0_COL, p_mn, b_mn(n), n != 0);
+          umma_commit(smem_u32(&b_empty[n % NB]));
+        }
         if (more) {
           // S of the next tile, as soon as this tile's S has been read
-          if (!(ok = wait_ring(2 * n + 2))) break;
-          if (!(ok = mbar_wait(smem_u32(s_free), n & 1, abort_flag))) break;
+          if (!(ok = wait_a(n + 1))) break;
           tc_fence_after();
-          if (MODE == MODE_KV) issue_sdp(S_COL, ring(2 * n + 2), st0); else issue_sdp(S_COL, st0, ring(2 * n + 2));
-          umma_commit(smem_u32(s_full));
+          issue_s(n + 1);
+          if (MODE == MODE_Q) {
+            // dP of the next tile goes to the other dP buffer, read last by tile n-1
+            if (!(ok = wait_b(n + 1))) break;
+            tc_fence_after();
+            issue_dp(n + 1);
+          }
         }
         if (!(ok = mbar_wait(smem_u32(pds_full), n & 1, abort_flag))) break;
         tc_fence_after();
-        const uint32_t ta = ring(2 * n), tb = ring(2 * n + 1);
         if (MODE == MODE_KV) {
-#pragma unroll
-          for (int kk = 0; kk < BLK / 16; ++kk) {
-            // dK[kv, d] += sum_q dS[q, kv] Q[q, d]
-            umma_bf16_ss(tmem_base + ACC1_COL, make_smem_desc_sw128(sds + kk * (16 * 128), BLK * 128, 1024),
-                         make_smem_desc_sw128(ta + kk * (16 * 128), BLK * 128, 1024), idesc_t,
-                         (n | kk) != 0 ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&ring_empty[(2 * n) % NSLOT]));       // Q tile free once dK has read it
-#pragma unroll
-          for (int kk = 0; kk < BLK / 16; ++kk) {
-            // dV[kv, d] += sum_q P[q, kv] dO[q, d]
-            umma_bf16_ss(tmem_base + ACC0_COL, make_smem_desc_sw128(sp + kk * (16 * 128), BLK * 128, 1024),
-                         make_smem_desc_sw128(tb + kk * (16 * 128), BLK * 128, 1024), idesc_t,
-                         (n | kk) != 0 ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&ring_empty[(2 * n + 1) % NSLOT]));
+          // dK[kv, d] += sum_q dS[q, kv] Q[q, d]
+          issue_acc_mn(ACC1_COL, ds_mn, a_mn(n), n != 0);
+          umma_commit(smem_u32(&a_empty[n % NA]));
         } else {
+          // dQ[q, d] += sum_kv dS[q, kv] K[kv, d]: dS K-major, K through its MN-major view
+          {
+            const uint32_t k_lo = a_mn(n);
 #pragma unroll
-          for (int kk = 0; kk < BLK / 16; ++kk) {
-            // dQ[q, d] += sum_kv dS[q, kv] K[kv, d]
-            umma_bf16_ss(tmem_base + ACC0_COL,
-                         make_smem_desc_sw128(sds + (kk >> 2) * (BLK * 128) + (kk & 3) * 32, 16, 1024),
-                         make_smem_desc_sw128(ta + kk * (16 * 128), BLK * 128, 1024), idesc_q,
-                         (n | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < BLK / 16; ++kk)
+              umma_bf16_ss_split(tmem_base + ACC0_COL, ds_k + (((kk >> 2) * (BLK * 128) + (kk & 3) * 32) >> 4), HI,
+                                 k_lo + ((kk * (16 * 128)) >> 4), HI, idesc_q, (n | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&ring_empty[(2 * n) % NSLOT]));
+          umma_commit(smem_u32(&a_empty[n % NA]));
+          umma_commit(smem_u32(ds_free));
         }
         if (!more) {
           umma_commit(smem_u32(acc_done));
-        } else {
+        } else if (MODE == MODE_KV) {
           // dP of the next tile: its columns were read before pds_full(n) completed
-          if (!(ok = wait_ring(2 * n + 3))) break;
+          if (!(ok = wait_b(n + 1))) break;
           tc_fence_after();
-          if (MODE == MODE_KV) issue_sdp(DP_COL, ring(2 * n + 3), st1); else issue_sdp(DP_COL, st1, ring(2 * n + 3));
-          umma_commit(smem_u32(dp_full));
-          if (MODE == MODE_Q) umma_commit(smem_u32(&ring_empty[(2 * n + 3) % NSLOT]));
+          issue_dp(n + 1);
         }
       }
     }
   } else {
     // ---------------------------- element-wise warps -----------------------------------
     const int quad = warp & 3;
-    const int half = warp >> 2;                 // which 64 key columns of the tile this thread handles
+    const int part = warp >> 2;                 // which 32 key columns of the tile this thread handles
     const int r = quad * 32 + lane;             // query row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
@@ -294,49 +335,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // tiles that need no masking: every row and column valid and strictly below the diagonal
       const bool plain = (q_tile + 1) * BLK <= p.Sq && (kv_tile + 1) * BLK <= p.Sk &&
                          !(p.causal && kv_tile >= q_tile);
-      float pv[64];
+      float pv[32];
+      uint8_t* const p_tile = smem + L::P_OFF + (part >> 1) * (BLK * 128);    // 64-column block of the P / dS tile
+      uint8_t* const ds_tile = smem + L::DS_OFF + (part >> 1) * (BLK * 128);
+      const int c16_0 = (part & 1) * 4;                                        // first 16-byte chunk inside the 128-byte row
       // ---- phase A: P = exp2(S·c − lse) --------------------------------------------------
+      // s_full(n) was committed after the dV GEMM of tile n-1: the P buffer is free
       if (!mbar_wait_warp(smem_u32(s_full), n & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      {
         uint32_t s_r[32];
-        tmem_ld_32x32(tmem_base + lane_off + S_COL + half * 64 + ch * 32, s_r);
+        tmem_ld_32x32(tmem_base + lane_off + S_COL + part * 32, s_r);
         tmem_ld_wait();
         if (plain) {
 #pragma unroll
-          for (int q = 0; q < 32; ++q)
-            pv[ch * 32 + q] = fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
+          for (int q = 0; q < 32; ++q) pv[q] = fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
         } else {
 #pragma unroll
           for (int q = 0; q < 32; ++q) {
-            const int colg = kv0 + half * 64 + ch * 32 + q;
+            const int colg = kv0 + part * 32 + q;
             const bool dead = !row_ok || colg >= p.Sk || (p.causal && colg > row_g);
-            pv[ch * 32 + q] = dead ? 0.0f : fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
+            pv[q] = dead ? 0.0f : fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
           }
         }
+        if (MODE == MODE_KV) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) store8_bf16(p_tile, r, c16_0 + c8, &pv[c8 * 8]);
+        }
       }
+      if (MODE == MODE_KV) fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(s_free));
-      // ---- phase B: dS = P∘(dP − delta); P and dS to shared memory --------------------------
-      // dp_full(n) also says that the accumulate GEMMs of tile n-1 have finished reading the
-      // P / dS buffers
-      if (!mbar_wait_warp(smem_u32(dp_full), n & 1, abort_flag)) { ok = false; break; }
+      // ---- phase B: dS = P∘(dP − delta) → shared memory ---------------------------------------
+      if (!mbar_wait_warp(smem_u32(&dp_full[n & 1]), (n >> 1) & 1, abort_flag)) { ok = false; break; }
+      // the previous tile's GEMM that reads the dS buffer must be done: in the dK/dV pass dP(n) was
+      // issued after it; the dQ pass issues dP early and signals the buffer separately
+      if (MODE == MODE_Q && n > 0 && !mbar_wait_warp(smem_u32(ds_free), (n - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      const uint32_t dp_col = (MODE == MODE_Q && (n & 1)) ? ACC1_COL : DP_COL;
+      {
         uint32_t dp_r[32];
-        tmem_ld_32x32(tmem_base + lane_off + DP_COL + half * 64 + ch * 32, dp_r);
+        tmem_ld_32x32(tmem_base + lane_off + dp_col + part * 32, dp_r);
         tmem_ld_wait();
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
           float dsv[8];
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            dsv[q] = pv[ch * 32 + c8 * 8 + q] * (__uint_as_float(dp_r[c8 * 8 + q]) - dlt);
-          store8_bf16(smem + L::DS_OFF + half * (BLK * 128), r, ch * 4 + c8, dsv);
-          if (MODE == MODE_KV)
-            store8_bf16(smem + L::P_OFF + half * (BLK * 128), r, ch * 4 + c8, &pv[ch * 32 + c8 * 8]);
+          for (int q = 0; q < 8; ++q) dsv[q] = pv[c8 * 8 + q] * (__uint_as_float(dp_r[c8 * 8 + q]) - dlt);
+          store8_bf16(ds_tile, r, c16_0 + c8, dsv);
         }
       }
       fence_proxy_async_smem();
@@ -345,19 +391,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     if (ok && n_iter > 0 && mbar_wait_warp(smem_u32(acc_done), 0, abort_flag)) {
       tc_fence_after();
-      if (MODE == MODE_KV) {
-        const int kv_row = own * BLK + r;
-        const bool kv_ok = kv_row < p.Sk;
-        __nv_bfloat16* dvp = p.dV + (long long)b * p.dv_sb + (long long)kv_row * p.dv_ss +
-                             (long long)h * p.dv_sh + half * DH;
-        __nv_bfloat16* dkp = p.dK + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss +
-                             (long long)h * p.dk_sh + half * DH;
-#pragma unroll
-        for (int ch = 0; ch < DH / 32; ++ch) {
+      // 32 accumulator columns per thread: chunk `part` (and, for D > 128, every fourth one after it)
+      const int own_row = own * BLK + r;
+      for (int ch = part; ch < D / 32; ch += EW_WARPS / 4) {
+        if (MODE == MODE_KV) {
+          const bool kv_ok = own_row < p.Sk;
+          __nv_bfloat16* dvp = p.dV + (long long)b * p.dv_sb + (long long)own_row * p.dv_ss + (long long)h * p.dv_sh + ch * 32;
+          __nv_bfloat16* dkp = p.dK + (long long)b * p.dk_sb + (long long)own_row * p.dk_ss + (long long)h * p.dk_sh + ch * 32;
           // TMEM loads are warp-collective: every lane issues them, only the stores are predicated
           uint32_t tv[32], tk[32];
-          tmem_ld_32x32(tmem_base + lane_off + ACC0_COL + half * DH + ch * 32, tv);
-          tmem_ld_32x32(tmem_base + lane_off + ACC1_COL + half * DH + ch * 32, tk);
+          tmem_ld_32x32(tmem_base + lane_off + ACC0_COL + ch * 32, tv);
+          tmem_ld_32x32(tmem_base + lane_off + ACC1_COL + ch * 32, tk);
           tmem_ld_wait();
           if (kv_ok) {
 #pragma unroll
@@ -371,20 +415,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               uk.y = pack_bf16x2(__uint_as_float(tk[q * 8 + 2]) * p.scale, __uint_as_float(tk[q * 8 + 3]) * p.scale);
               uk.z = pack_bf16x2(__uint_as_float(tk[q * 8 + 4]) * p.scale, __uint_as_float(tk[q * 8 + 5]) * p.scale);
               uk.w = pack_bf16x2(__uint_as_float(tk[q * 8 + 6]) * p.scale, __uint_as_float(tk[q * 8 + 7]) * p.scale);
-              reinterpret_cast<uint4*>(dvp + ch * 32)[q] = uv;
-              reinterpret_cast<uint4*>(dkp + ch * 32)[q] = uk;
+              reinterpret_cast<uint4*>(dvp)[q] = uv;
+              reinterpret_cast<uint4*>(dkp)[q] = uk;
             }
           }
-        }
-      } else {
-        const int q_row = own * BLK + r;
-        const bool q_ok = q_row < p.Sq;
-        __nv_bfloat16* dqp = p.dQ + (long long)b * p.dq_sb + (long long)q_row * p.dq_ss +
-                             (long long)h * p.dq_sh + half * DH;
-#pragma unroll
-        for (int ch = 0; ch < DH / 32; ++ch) {
+        } else {
+          const bool q_ok = own_row < p.Sq;
+          __nv_bfloat16* dqp = p.dQ + (long long)b * p.dq_sb + (long long)own_row * p.dq_ss + (long long)h * p.dq_sh + ch * 32;
           uint32_t tq[32];
-          tmem_ld_32x32(tmem_base + lane_off + ACC0_COL + half * DH + ch * 32, tq);
+          tmem_ld_32x32(tmem_base + lane_off + ACC0_COL + ch * 32, tq);
           tmem_ld_wait();
           if (q_ok) {
 #pragma unroll
@@ -394,28 +433,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               u.y = pack_bf16x2(__uint_as_float(tq[q * 8 + 2]) * p.scale, __uint_as_float(tq[q * 8 + 3]) * p.scale);
               u.z = pack_bf16x2(__uint_as_float(tq[q * 8 + 4]) * p.scale, __uint_as_float(tq[q * 8 + 5]) * p.scale);
               u.w = pack_bf16x2(__uint_as_float(tq[q * 8 + 6]) * p.scale, __uint_as_float(tq[q * 8 + 7]) * p.scale);
-              reinterpret_cast<uint4*>(dqp + ch * 32)[q] = u;
+              reinterpret_cast<uint4*>(dqp)[q] = u;
             }
           }
         }
       }
     }
-    if (n_iter == 0) {
+    if (n_iter == 0 && part == 0) {
       // nothing attends to / from this tile: its gradient rows are zero
       const uint4 z = make_uint4(0, 0, 0, 0);
+      const int own_row = own * BLK + r;
       if (MODE == MODE_KV) {
-        const int kv_row = own * BLK + r;
-        if (kv_row < p.Sk) {
-          __nv_bfloat16* dvp = p.dV + (long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + half * DH;
-          __nv_bfloat16* dkp = p.dK + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + half * DH;
-          for (int q = 0; q < DH / 8; ++q) {
+        if (own_row < p.Sk) {
+          __nv_bfloat16* dvp = p.dV + (long long)b * p.dv_sb + (long long)own_row * p.dv_ss + (long long)h * p.dv_sh;
+          __nv_bfloat16* dkp = p.dK + (long long)b * p.dk_sb + (long long)own_row * p.dk_ss + (long long)h * p.dk_sh;
+          for (int q = 0; q < D / 8; ++q) {
             reinterpret_cast<uint4*>(dvp)[q] = z;
             reinterpret_cast<uint4*>(dkp)[q] = z;
           }
         }
-      } else if (row_ok) {
-        __nv_bfloat16* dqp = p.dQ + (long long)b * p.dq_sb + (long long)row_g * p.dq_ss + (long long)h * p.dq_sh + half * DH;
-        for (int q = 0; q < DH / 8; ++q) reinterpret_cast<uint4*>(dqp)[q] = z;
+      } else if (own_row < p.Sq) {
+        __nv_bfloat16* dqp = p.dQ + (long long)b * p.dq_sb + (long long)own_row * p.dq_ss + (long long)h * p.dq_sh;
+        for (int q = 0; q < D / 8; ++q) reinterpret_cast<uint4*>(dqp)[q] = z;
       }
     }
   }
@@ -426,7 +465,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (threadIdx.x == 0) report_error(p.err, ERR_MBAR_TIMEOUT, 0xA7B0u + MODE);
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
-  if (warp == 9) {
+  if (warp == EW_WARPS + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
