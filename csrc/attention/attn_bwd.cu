@@ -114,22 +114,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* b_empty = bars + 7;        // 2
   uint64_t* s_full = bars + 9;         // S of tile n is in TMEM
   uint64_t* dp_full = bars + 10;       // 2: dP of tile n is in TMEM (barrier n & 1)
-  uint64_t* s_free = bars + 12;        // 256 arrivals: S of tile n has been read (MODE_KV: and P is in shared memory)
-  uint64_t* pds_full = bars + 13;      // 256 arrivals: dS of tile n is in shared memory, dP has been read
+  uint64_t* s_free = bars + 12;        // one arrival per element-wise warp: S of tile n has been read (MODE_KV: and P is in shared memory)
+  uint64_t* pds_full = bars + 13;      // one arrival per element-wise warp: dS of tile n is in shared memory, dP has been read
   uint64_t* ds_free = bars + 14;       // MODE_Q: the dQ GEMM of tile n has finished reading dS
-  uint64_t* acc_done = bars + 15;      // every GEMM of the CTA has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* acc_done = bars + 15;      // every GEMM of the current work item has completed
+  uint64_t* stat_empty = bars + 16;    // the last S / dP GEMM of the work item has read the stationary tiles
+  uint64_t* acc_free = bars + 17;      // one arrival per warp: the accumulators of the work item have been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
   const int n_q = (p.Sq + BLK - 1) / BLK;
   const int n_kv = (p.Sk + BLK - 1) / BLK;
-  // the tile this CTA owns and the range of streamed tiles [t_begin, t_begin + n_iter)
-  const int own = MODE == MODE_KV ? blockIdx.x : n_q - 1 - blockIdx.x;   // dQ pass: longest rows first
-  const int t_begin = MODE == MODE_KV ? (p.causal ? own : 0) : 0;
-  const int t_end = MODE == MODE_KV ? n_q : (p.causal ? min(own + 1, n_kv) : n_kv);
-  const int n_iter = max(t_end - t_begin, 0);
+  // Persistent CTAs: work item w = (owned tile, head, batch), tile-major so that under a causal mask
+  // the long items come first; CTA c takes items c, c + gridDim.x, ...  Barrier phases run on over
+  // the items (g counts streamed tiles, it counts items), so TMEM, the barriers and the pipelines
+  // are set up once and the loads of the next item overlap the tail of the current one.
+  const int hb = p.H * p.B;
+  const int total_items = (MODE == MODE_KV ? n_kv : n_q) * hb;
+  struct Item { int own, h, b, t_begin, n_iter; };
+  auto item_at = [&](int w) {
+    Item I;
+    const int idx = w / hb, rem = w - idx * hb;
+    I.own = MODE == MODE_KV ? idx : n_q - 1 - idx;
+    I.h = rem % p.H;
+    I.b = rem / p.H;
+    I.t_begin = MODE == MODE_KV ? (p.causal ? I.own : 0) : 0;
+    const int t_end = MODE == MODE_KV ? n_q : (p.causal ? min(I.own + 1, n_kv) : n_kv);
+    I.n_iter = max(t_end - I.t_begin, 0);
+    return I;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(stat_full), 1);
@@ -141,10 +155,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&dp_full[s]), 1);
     }
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_free), EW_THREADS);
-    mbar_init(smem_u32(pds_full), EW_THREADS);
+    mbar_init(smem_u32(s_free), EW_WARPS);        // one arrival per warp: 512 arrivals on one word cost ~0.5 us
+    mbar_init(smem_u32(pds_full), EW_WARPS);
     mbar_init(smem_u32(ds_free), 1);
     mbar_init(smem_u32(acc_done), 1);
+    mbar_init(smem_u32(stat_empty), 1);
+    mbar_init(smem_u32(acc_free), EW_WARPS);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
@@ -163,43 +179,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp == EW_WARPS) {
     // ---------------------------- TMA producer -----------------------------------------
-    if (lane == 0 && n_iter > 0) {
-      const uint32_t sb = smem_u32(stat_full);
-      mbar_arrive_expect_tx(sb, 2 * L::TILE);
+    if (lane == 0) {
       const CUtensorMap* st0 = MODE == MODE_KV ? &tmK : &tmQ;
       const CUtensorMap* st1 = MODE == MODE_KV ? &tmV : &tmdO;
       const CUtensorMap* ma = MODE == MODE_KV ? &tmQ : &tmK;
       const CUtensorMap* mb = MODE == MODE_KV ? &tmdO : &tmV;
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const Item I = item_at(w);
+        if (I.n_iter == 0) continue;
+        if (!(ok = mbar_wait(smem_u32(stat_empty), (it & 1) ^ 1u, abort_flag))) break;
+        const uint32_t sb = smem_u32(stat_full);
+        mbar_arrive_expect_tx(sb, 2 * L::TILE);
 #pragma unroll
-      for (int kb = 0; kb < KB; ++kb) {
-        tma_load_4d(smem_u32(smem + L::STAT0_OFF + kb * (BLK * 128)), st0, sb, kb * 64, h, own * BLK, b);
-        tma_load_4d(smem_u32(smem + L::STAT1_OFF + kb * (BLK * 128)), st1, sb, kb * 64, h, own * BLK, b);
-      }
-      for (int n = 0; n < n_iter; ++n) {
-        const int row0 = (t_begin + n) * BLK;
-        {
-          const int slot = n % NA;
-          if (!mbar_wait(smem_u32(&a_empty[slot]), ((n / NA) & 1) ^ 1u, abort_flag)) break;
-          const uint32_t fb = smem_u32(&a_full[slot]);
-          mbar_arrive_expect_tx(fb, L::TILE);
-#pragma unroll
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem_u32(smem + L::A_OFF + slot * L::TILE + kb * (BLK * 128)), ma, fb, kb * 64, h, row0, b);
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_4d(smem_u32(smem + L::STAT0_OFF + kb * (BLK * 128)), st0, sb, kb * 64, I.h, I.own * BLK, I.b);
+          tma_load_4d(smem_u32(smem + L::STAT1_OFF + kb * (BLK * 128)), st1, sb, kb * 64, I.h, I.own * BLK, I.b);
         }
-        {
-          const int slot = n % NB;
-          if (!mbar_wait(smem_u32(&b_empty[slot]), ((n / NB) & 1) ^ 1u, abort_flag)) break;
-          const uint32_t fb = smem_u32(&b_full[slot]);
-          mbar_arrive_expect_tx(fb, L::TILE);
+        for (int n = 0; n < I.n_iter && ok; ++n, ++g) {
+          const int row0 = (I.t_begin + n) * BLK;
+          {
+            const int slot = g % NA;
+            if (!(ok = mbar_wait(smem_u32(&a_empty[slot]), ((g / NA) & 1) ^ 1u, abort_flag))) break;
+            const uint32_t fb = smem_u32(&a_full[slot]);
+            mbar_arrive_expect_tx(fb, L::TILE);
 #pragma unroll
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem_u32(smem + L::B_OFF + slot * L::TILE + kb * (BLK * 128)), mb, fb, kb * 64, h, row0, b);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem_u32(smem + L::A_OFF + slot * L::TILE + kb * (BLK * 128)), ma, fb, kb * 64, I.h, row0, I.b);
+          }
+          {
+            const int slot = g % NB;
+            if (!(ok = mbar_wait(smem_u32(&b_empty[slot]), ((g / NB) & 1) ^ 1u, abort_flag))) break;
+            const uint32_t fb = smem_u32(&b_full[slot]);
+            mbar_arrive_expect_tx(fb, L::TILE);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem_u32(smem + L::B_OFF + slot * L::TILE + kb * (BLK * 128)), mb, fb, kb * 64, I.h, row0, I.b);
+          }
         }
+        ++it;
       }
     }
   } else if (warp == EW_WARPS + 1) {
     // ---------------------------- MMA issuer -------------------------------------------
-    if (elect_one() && n_iter > 0) {
+    if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);   // S, dP
       constexpr uint32_t idesc_t = make_idesc_bf16(BLK, D, true, true);       // dV, dK
       constexpr uint32_t idesc_q = make_idesc_bf16(BLK, D, false, true);      // dQ
@@ -245,63 +269,73 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(smem_u32(&dp_full[n & 1]));
         if (MODE == MODE_Q) umma_commit(smem_u32(&b_empty[n % NB]));   // V is only needed by dP
       };
-      bool ok = mbar_wait(smem_u32(stat_full), 0, abort_flag);
-      // prologue: S(0), dP(0)
-      if (ok && (ok = wait_a(0))) {
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const Item I = item_at(w);
+        if (I.n_iter == 0) continue;
+        // prologue: S and dP of the item's first tile.  Their TMEM columns are free: every iteration,
+        // the previous item's last one included, waits for s_free and pds_full.
+        if (!(ok = mbar_wait(smem_u32(stat_full), it & 1, abort_flag))) break;
+        if (!(ok = wait_a(g))) break;
         tc_fence_after();
-        issue_s(0);
-      }
-      if (ok && (ok = wait_b(0))) {
+        issue_s(g);
+        if (!(ok = wait_b(g))) break;
         tc_fence_after();
-        issue_dp(0);
-      }
-      for (int n = 0; n < n_iter && ok; ++n) {
-        const bool more = n + 1 < n_iter;
-        if (!(ok = mbar_wait(smem_u32(s_free), n & 1, abort_flag))) break;
-        tc_fence_after();
-        if (MODE == MODE_KV) {
-          // dV[kv, d] += sum_q P[q, kv] dO[q, d]   (P is complete once S has been read)
-          issue_acc_mn(ACC0_COL, p_mn, b_mn(n), n != 0);
-          umma_commit(smem_u32(&b_empty[n % NB]));
-        }
-        if (more) {
-          // S of the next tile, as soon as this tile's S has been read
-          if (!(ok = wait_a(n + 1))) break;
+        issue_dp(g);
+        for (int n = 0; n < I.n_iter && ok; ++n, ++g) {
+          const bool more = n + 1 < I.n_iter;
+          // every S / dP GEMM of the item has been issued: the stationary tiles can be replaced
+          // as soon as those complete
+          if (!more) umma_commit(smem_u32(stat_empty));
+          if (!(ok = mbar_wait(smem_u32(s_free), g & 1, abort_flag))) break;
+          // the first accumulate GEMM of an item overwrites accumulators that the element-wise warps
+          // may still be reading out for the previous item
+          if (n == 0 && it > 0 && !(ok = mbar_wait(smem_u32(acc_free), (it - 1) & 1, abort_flag))) break;
           tc_fence_after();
-          issue_s(n + 1);
-          if (MODE == MODE_Q) {
-            // dP of the next tile goes to the other dP buffer, read last by tile n-1
-            if (!(ok = wait_b(n + 1))) break;
-            tc_fence_after();
-            issue_dp(n + 1);
+          if (MODE == MODE_KV) {
+            // dV[kv, d] += sum_q P[q, kv] dO[q, d]   (P is complete once S has been read)
+            issue_acc_mn(ACC0_COL, p_mn, b_mn(g), n != 0);
+            umma_commit(smem_u32(&b_empty[g % NB]));
           }
-        }
-        if (!(ok = mbar_wait(smem_u32(pds_full), n & 1, abort_flag))) break;
-        tc_fence_after();
-        if (MODE == MODE_KV) {
-          // dK[kv, d] += sum_q dS[q, kv] Q[q, d]
-          issue_acc_mn(ACC1_COL, ds_mn, a_mn(n), n != 0);
-          umma_commit(smem_u32(&a_empty[n % NA]));
-        } else {
-          // dQ[q, d] += sum_kv dS[q, kv] K[kv, d]: dS K-major, K through its MN-major view
-          {
-            const uint32_t k_lo = a_mn(n);
+          if (more) {
+            // S of the next tile, as soon as this tile's S has been read
+            if (!(ok = wait_a(g + 1))) break;
+            tc_fence_after();
+            issue_s(g + 1);
+            if (MODE == MODE_Q) {
+              // dP of the next tile goes to the other dP buffer, read last by tile g-1
+              if (!(ok = wait_b(g + 1))) break;
+              tc_fence_after();
+              issue_dp(g + 1);
+            }
+          }
+          if (!(ok = mbar_wait(smem_u32(pds_full), g & 1, abort_flag))) break;
+          tc_fence_after();
+          if (MODE == MODE_KV) {
+            // dK[kv, d] += sum_q dS[q, kv] Q[q, d]
+            issue_acc_mn(ACC1_COL, ds_mn, a_mn(g), n != 0);
+            umma_commit(smem_u32(&a_empty[g % NA]));
+          } else {
+            // dQ[q, d] += sum_kv dS[q, kv] K[kv, d]: dS K-major, K through its MN-major view
+            const uint32_t k_lo = a_mn(g);
 #pragma unroll
             for (int kk = 0; kk < BLK / 16; ++kk)
               umma_bf16_ss_split(tmem_base + ACC0_COL, ds_k + (((kk >> 2) * (BLK * 128) + (kk & 3) * 32) >> 4), HI,
                                  k_lo + ((kk * (16 * 128)) >> 4), HI, idesc_q, (n | kk) != 0 ? 1u : 0u);
+            umma_commit(smem_u32(&a_empty[g % NA]));
+            umma_commit(smem_u32(ds_free));
           }
-          umma_commit(smem_u32(&a_empty[n % NA]));
-          umma_commit(smem_u32(ds_free));
+          if (!more) {
+            umma_commit(smem_u32(acc_done));
+          } else if (MODE == MODE_KV) {
+            // dP of the next tile: its columns were read before pds_full(g) completed
+            if (!(ok = wait_b(g + 1))) break;
+            tc_fence_after();
+            issue_dp(g + 1);
+          }
         }
-        if (!more) {
-          umma_commit(smem_u32(acc_done));
-        } else if (MODE == MODE_KV) {
-          // dP of the next tile: its columns were read before pds_full(n) completed
-          if (!(ok = wait_b(n + 1))) break;
-          tc_fence_after();
-          issue_dp(n + 1);
-        }
+        ++it;
       }
     }
   } else {
@@ -312,6 +346,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
+    int g = 0, it = 0;
+    for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+    const Item I = item_at(w);
+    const int own = I.own, h = I.h, b = I.b, t_begin = I.t_begin, n_iter = I.n_iter;
     float lse2 = 0.0f, dlt = 0.0f;
     int row_g = own * BLK + r;
     bool row_ok = row_g < p.Sq;
@@ -320,7 +358,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       lse2 = p.lse[stat_idx] * LOG2E;
       dlt = p.delta[stat_idx];
     }
-    for (int n = 0; n < n_iter; ++n) {
+    for (int n = 0; n < n_iter; ++n, ++g) {
       const int t = t_begin + n;                               // streamed tile index
       const int q_tile = MODE == MODE_KV ? t : own;
       const int kv_tile = MODE == MODE_KV ? own : t;
@@ -341,7 +379,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int c16_0 = (part & 1) * 4;                                        // first 16-byte chunk inside the 128-byte row
       // ---- phase A: P = exp2(S·c − lse) --------------------------------------------------
       // s_full(n) was committed after the dV GEMM of tile n-1: the P buffer is free
-      if (!mbar_wait_warp(smem_u32(s_full), n & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(smem_u32(s_full), g & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       {
         uint32_t s_r[32];
@@ -365,14 +403,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (MODE == MODE_KV) fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(s_free));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(s_free));
       // ---- phase B: dS = P∘(dP − delta) → shared memory ---------------------------------------
-      if (!mbar_wait_warp(smem_u32(&dp_full[n & 1]), (n >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(smem_u32(&dp_full[g & 1]), (g >> 1) & 1, abort_flag)) { ok = false; break; }
       // the previous tile's GEMM that reads the dS buffer must be done: in the dK/dV pass dP(n) was
       // issued after it; the dQ pass issues dP early and signals the buffer separately
-      if (MODE == MODE_Q && n > 0 && !mbar_wait_warp(smem_u32(ds_free), (n - 1) & 1, abort_flag)) { ok = false; break; }
+      if (MODE == MODE_Q && g > 0 && !mbar_wait_warp(smem_u32(ds_free), (g - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t dp_col = (MODE == MODE_Q && (n & 1)) ? ACC1_COL : DP_COL;
+      const uint32_t dp_col = (MODE == MODE_Q && (g & 1)) ? ACC1_COL : DP_COL;
       {
         uint32_t dp_r[32];
         tmem_ld_32x32(tmem_base + lane_off + dp_col + part * 32, dp_r);
@@ -387,9 +426,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(pds_full));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(pds_full));
     }
-    if (ok && n_iter > 0 && mbar_wait_warp(smem_u32(acc_done), 0, abort_flag)) {
+    if (ok && n_iter > 0 && !mbar_wait_warp(smem_u32(acc_done), it & 1, abort_flag)) ok = false;
+    if (ok && n_iter > 0) {
       tc_fence_after();
       // 32 accumulator columns per thread: chunk `part` (and, for D > 128, every fourth one after it)
       const int own_row = own * BLK + r;
@@ -439,6 +480,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
+    if (ok && n_iter > 0) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(acc_free));
+      ++it;
+    }
     if (n_iter == 0 && part == 0) {
       // nothing attends to / from this tile: its gradient rows are zero
       const uint4 z = make_uint4(0, 0, 0, 0);
@@ -457,6 +504,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int q = 0; q < D / 8; ++q) reinterpret_cast<uint4*>(dqp)[q] = z;
       }
     }
+    }   // work items
   }
 
   tc_fence_before();
@@ -556,8 +604,16 @@ ST_API int st_attn_bwd(const StAttnBwdArgs* a, void* stream_v) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.causal = a->causal;
   p.err = st::error_word();
-  const dim3 grid_kv((a->Sk + BLK - 1) / BLK, a->H, a->B);
-  const dim3 grid_q((a->Sq + BLK - 1) / BLK, a->H, a->B);
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    ST_CUDA_CHECK(cudaGetDevice(&dev));
+    ST_CUDA_CHECK(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int items_kv = ((a->Sk + BLK - 1) / BLK) * a->H * a->B;
+  const int items_q = ((a->Sq + BLK - 1) / BLK) * a->H * a->B;
+  const dim3 grid_kv(items_kv < num_sms ? items_kv : num_sms);
+  const dim3 grid_q(items_q < num_sms ? items_q : num_sms);
   auto launch = [&](auto kernel, int smem_bytes, dim3 grid) -> int {
     ST_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     kernel<<<grid, NUM_THREADS, smem_bytes, s>>>(tq, tk, tv, tdo, p);

@@ -101,7 +101,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&k_empty[i]), 1);
       mbar_init(smem_u32(&v_empty[i]), 1);
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&p_full[i]), 256);
+      mbar_init(smem_u32(&p_full[i]), 8);     // one arrival per softmax warp
       mbar_init(smem_u32(&pv_full[i]), 1);
     }
     *abort_flag = 0;
@@ -280,7 +280,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       m = m_new;
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&p_full[buf]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));
       if (j > 0) {
         if (!accumulate(j - 1, alpha_prev)) { ok = false; break; }
       }
