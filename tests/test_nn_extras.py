@@ -295,3 +295,41 @@ def test_text_vae_learns_and_round_trips(tmp_path):
     assert torch.allclose(vae.encode_text_with_mellin("hi", basis), vae.encode_text("hi").flip(0))
     with pytest.raises(st.TensorError):
         ZSpaceTextVae(0, 3)
+
+
+def test_roundtable_node_and_conductor():
+    from spiraltorch_b200.nn import roundtable as RT
+    assert RT.outcome_band(0.5, 0.5, 0.1) == "above" and RT.outcome_band(0.1, 0.3, 0.3) == "here"
+    lo, hi = RT.wilson_bounds(0.8, 10.0, 1.0)
+    assert 0.6 < lo < 0.8 < hi < 0.95
+    assert RT.RoundtableNode().record_decision("p", "s", "topk", "above", 0.9) is None      # local mode
+    now = [0.0]
+    sent = []
+    cfg = RT.DistConfig("n0", RT.PERIODIC_META, push_interval=10.0, summary_window=3).with_aws_sqs("eu", "q").with_aws_sqs("eu", "q")
+    assert cfg.cloud_targets == [("aws_sqs", "eu", "q")]
+    node = RT.RoundtableNode(cfg, clock=lambda: now[0], sink=sent.append)
+    assert node.record_decision("plan", "wg=256", "topk", "above", 0.9, psi_total=1.0, z_signal=0.2) is None
+    assert node.record_decision("plan", "wg=256", "topk", "here", 0.7) is None
+    s = node.record_decision("plan", "wg=256", "topk", "above", 1.4)                        # window full; score clamped
+    assert s is not None and s.events == 3 and s.winner == "above" and s.mean_score == pytest.approx((0.9 + 0.7 + 1.0) / 3)
+    assert s.mean_psi == pytest.approx(1.0 / 3) and sent == [s] and len(node.pending) == 0
+    node.record_decision("plan", "wg=256", "topk", "above", 0.5)
+    now[0] = 11.0
+    assert node.record_decision("plan", "wg=256", "topk", "above", 0.5).events == 2         # interval elapsed
+    node.retune(0.0, 0)
+    assert node.config.push_interval == 0.010 and node.config.summary_window == 1
+    cond = RT.MetaConductor(threshold=0.5, participation=2)
+    a = RT.MetaSummary("n0", "plan", "wg=256", "topk", "above", 0.9, 0.7, 0.95, 0.0, 0.0, 0.4, 3, 1.0)
+    b = RT.MetaSummary("n1", "plan", "wg=256", "topk", "above", 0.8, 0.6, 0.9, 0.0, 0.5, 0.3, 3, 2.0)
+    assert cond.ingest(a) is None                                                            # one node only
+    prop = cond.ingest(b)
+    assert prop is not None and prop.ops[0].script == "wg=256" and len(prop.evidence) == 2
+    assert prop.ops[0].weight == pytest.approx((0.4 + 0.3 * 1.2) / 0.5)
+    assert cond.ingest(a) is None                                                            # evidence was cleared
+    log = RT.HeurOpLog()
+    ok, metrics = RT.simulate_proposal_locally(prop, log)
+    assert ok and metrics == {"wg=256": prop.ops[0].weight} and log.high_watermark() == 1
+    log.append(prop.ops[0]); log.append(prop.ops[0])
+    other = RT.HeurOpLog(); other.merge(log); other.merge(log)
+    assert other.high_watermark() == 2 and other.top_winners(5)[0].script == "wg=256" and RT.HeurOpLog().missing_ranges() == [(0, 0)]
+    assert RT.exchange_summaries(a) == [a] and RT.exchange_summaries(None) == []
