@@ -65,12 +65,13 @@ template <int D, int MODE>
 struct BwdSmem {
   static constexpr int TILE = BLK * D * 2;
   static constexpr int P_TILE = BLK * BLK * 2;
-  // streamed tiles: stream A is Q (dK/dV pass) or K (dQ pass), stream B is dO or V.  The dK/dV pass
-  // has room for three streamed tiles next to K, V, P and dS: two for Q, whose tile lives for a
-  // whole iteration, one for dO, which is released right after the first accumulate GEMM.  The
-  // dQ pass has no P buffer and double-buffers both streams.
-  static constexpr int NA = 2;
-  static constexpr int NB = MODE == MODE_KV ? 1 : 2;
+  // streamed tiles: stream A is Q (dK/dV pass) or K (dQ pass), stream B is dO or V.  The A tile is read by
+  // the first GEMM of an iteration (S) and by the last one (dK or dQ), so it lives for more than a whole
+  // iteration; the B tile is released early (after dV, or right after dP in the dQ pass).  The dK/dV pass
+  // has room for three streamed tiles next to K, V, P and dS: two A, one B.  The dQ pass has no P buffer:
+  // three A (with two, the issuer measured 0.47 us per iteration waiting for K), one B.
+  static constexpr int NA = MODE == MODE_KV ? 2 : 3;
+  static constexpr int NB = 1;
   static constexpr int STAT0_OFF = 0;                  // K (MODE_KV) or Q (MODE_Q)
   static constexpr int STAT1_OFF = STAT0_OFF + TILE;   // V (MODE_KV) or dO (MODE_Q)
   static constexpr int A_OFF = STAT1_OFF + TILE;
@@ -108,10 +109,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* stat_full = bars;          // 1
-  uint64_t* a_full = bars + 1;         // 2
-  uint64_t* a_empty = bars + 3;        // 2
-  uint64_t* b_full = bars + 5;         // 2
-  uint64_t* b_empty = bars + 7;        // 2
+  uint64_t* a_full = bars + 1;         // 3
+  uint64_t* a_empty = bars + 4;        // 3
+  uint64_t* b_full = bars + 7;         // 1
+  uint64_t* b_empty = bars + 8;        // 1
   uint64_t* s_full = bars + 9;         // S of tile n is in TMEM
   uint64_t* dp_full = bars + 10;       // 2: dP of tile n is in TMEM (barrier n & 1)
   uint64_t* s_free = bars + 12;        // one arrival per element-wise warp: S of tile n has been read (MODE_KV: and P is in shared memory)
@@ -119,8 +120,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* ds_free = bars + 14;       // MODE_Q: the dQ GEMM of tile n has finished reading dS
   uint64_t* acc_done = bars + 15;      // every GEMM of the current work item has completed
   uint64_t* stat_empty = bars + 16;    // the last S / dP GEMM of the work item has read the stationary tiles
-  uint64_t* acc_free = bars + 17;      // one arrival per warp: the accumulators of the work item have been read out
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* acc_free = bars + 17;
+  uint64_t* p_ready = bars + 18;       // MODE_KV, one arrival per warp: P of tile n is in shared memory
+  uint64_t* p_free = bars + 19;        // MODE_KV: the dV GEMM of tile n has finished reading P
+  // acc_free: one arrival per warp: the accumulators of the work item have been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -147,13 +151,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(stat_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(smem_u32(&a_full[s]), 1);
       mbar_init(smem_u32(&a_empty[s]), 1);
-      mbar_init(smem_u32(&b_full[s]), 1);
-      mbar_init(smem_u32(&b_empty[s]), 1);
-      mbar_init(smem_u32(&dp_full[s]), 1);
     }
+    mbar_init(smem_u32(b_full), 1);
+    mbar_init(smem_u32(b_empty), 1);
+    mbar_init(smem_u32(&dp_full[0]), 1);
+    mbar_init(smem_u32(&dp_full[1]), 1);
+    mbar_init(smem_u32(p_ready), EW_WARPS);
+    mbar_init(smem_u32(p_free), 1);
     mbar_init(smem_u32(s_full), 1);
     mbar_init(smem_u32(s_free), EW_WARPS);        // one arrival per warp: 512 arrivals on one word cost ~0.5 us
     mbar_init(smem_u32(pds_full), EW_WARPS);
@@ -293,11 +300,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // may still be reading out for the previous item
           if (n == 0 && it > 0 && !(ok = mbar_wait(smem_u32(acc_free), (it - 1) & 1, abort_flag))) break;
           tc_fence_after();
-          if (MODE == MODE_KV) {
-            // dV[kv, d] += sum_q P[q, kv] dO[q, d]   (P is complete once S has been read)
-            issue_acc_mn(ACC0_COL, p_mn, b_mn(g), n != 0);
-            umma_commit(smem_u32(&b_empty[g % NB]));
-          }
           if (more) {
             // S of the next tile, as soon as this tile's S has been read
             if (!(ok = wait_a(g + 1))) break;
@@ -309,6 +311,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               tc_fence_after();
               issue_dp(g + 1);
             }
+          }
+          if (MODE == MODE_KV) {
+            // dV[kv, d] += sum_q P[q, kv] dO[q, d], once P has been stored (S of the next tile is already
+            // running: the element-wise warps release S before they convert and store P)
+            if (!(ok = mbar_wait(smem_u32(p_ready), g & 1, abort_flag))) break;
+            tc_fence_after();
+            issue_acc_mn(ACC0_COL, p_mn, b_mn(g), n != 0);
+            umma_commit(smem_u32(&b_empty[g % NB]));
+            umma_commit(smem_u32(p_free));
           }
           if (!(ok = mbar_wait(smem_u32(pds_full), g & 1, abort_flag))) break;
           tc_fence_after();
@@ -358,16 +369,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       lse2 = p.lse[stat_idx] * LOG2E;
       dlt = p.delta[stat_idx];
     }
+    float lse_next = 0.0f, dlt_next = 0.0f;      // MODE_KV: statistics of the next query tile's row
+    if (MODE == MODE_KV && n_iter > 0 && t_begin * BLK + r < p.Sq) {
+      const long long stat_idx = ((long long)b * p.H + h) * p.Sq + t_begin * BLK + r;
+      lse_next = p.lse[stat_idx];
+      dlt_next = p.delta[stat_idx];
+    }
     for (int n = 0; n < n_iter; ++n, ++g) {
       const int t = t_begin + n;                               // streamed tile index
       const int q_tile = MODE == MODE_KV ? t : own;
       const int kv_tile = MODE == MODE_KV ? own : t;
       if (MODE == MODE_KV) {
+        // this tile's row statistics were loaded one iteration ago; start the loads for the next tile
+        // now so that their latency hides behind this iteration
         row_g = q_tile * BLK + r;
         row_ok = row_g < p.Sq;
-        const long long stat_idx = ((long long)b * p.H + h) * p.Sq + row_g;
-        lse2 = row_ok ? p.lse[stat_idx] * LOG2E : 0.0f;
-        dlt = row_ok ? p.delta[stat_idx] : 0.0f;
+        lse2 = lse_next * LOG2E;
+        dlt = dlt_next;
+        const int row_n = row_g + BLK;
+        if (n + 1 < n_iter && row_n < p.Sq) {
+          const long long stat_idx = ((long long)b * p.H + h) * p.Sq + row_n;
+          lse_next = p.lse[stat_idx];
+          dlt_next = p.delta[stat_idx];
+        } else {
+          lse_next = 0.0f;
+          dlt_next = 0.0f;
+        }
       }
       const int kv0 = kv_tile * BLK;
       // tiles that need no masking: every row and column valid and strictly below the diagonal
@@ -396,15 +423,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             pv[q] = dead ? 0.0f : fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
           }
         }
-        if (MODE == MODE_KV) {
-#pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) store8_bf16(p_tile, r, c16_0 + c8, &pv[c8 * 8]);
-        }
       }
-      if (MODE == MODE_KV) fence_proxy_async_smem();
+      // S has been read: the next S GEMM may overwrite it while P is converted and stored
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(s_free));
+      if (MODE == MODE_KV) {
+        // the dV GEMM of the previous tile must have finished reading the P buffer
+        if (g > 0 && !mbar_wait_warp(smem_u32(p_free), (g - 1) & 1, abort_flag)) { ok = false; break; }
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) store8_bf16(p_tile, r, c16_0 + c8, &pv[c8 * 8]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(p_ready));
+      }
       // ---- phase B: dS = P∘(dP − delta) → shared memory ---------------------------------------
       if (!mbar_wait_warp(smem_u32(&dp_full[g & 1]), (g >> 1) & 1, abort_flag)) { ok = false; break; }
       // the previous tile's GEMM that reads the dS buffer must be done: in the dK/dV pass dP(n) was

@@ -58,9 +58,11 @@ def _run_pair(lib, rms, rows, d, seed):
         outs.append((dx, dgamma, dbeta))
     (dx0, dg0, db0), (dx1, dg1, db1) = outs
     assert torch.equal(dx0, dx1)
-    assert torch.allclose(dg0, dg1, rtol=1e-5, atol=1e-5)
+    # the two entry points split the rows over different numbers of CTAs, so the fp32 partial sums are
+    # added in a different order
+    assert torch.allclose(dg0, dg1, rtol=2e-4, atol=2e-4)
     if not rms:
-        assert torch.allclose(db0, db1, rtol=1e-5, atol=1e-5)
+        assert torch.allclose(db0, db1, rtol=2e-4, atol=2e-4)
 
 
 def test_noalloc_matches_scratch_entry_point_twice_in_a_row():
