@@ -5,7 +5,7 @@
 ``st.describe_device()``.  CUDA work runs on hand-written sm_100a kernels (``csrc/``).
 """
 from . import (autograd, compress, config, engine, measure, distributed, hpo, kdsl, language, logic, metrics, nn, optim, plugin, rec, rl, robotics, runtime, safety,
-               selfsup, softlogic, telemetry, text)
+               selfsup, softlogic, telemetry, text, tracking)
 from .nn.io import VERSION as __version__
 from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad
 from .session import SpiralSession, build_info, describe_device

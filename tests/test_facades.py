@@ -644,3 +644,62 @@ def test_atlas_route_summary():
     import json
     json.dumps(s.to_json())
     assert T.AtlasRoute().summary().flux() is None
+
+
+def test_tracking_connectors(tmp_path):
+    import json
+    from spiraltorch_b200 import hpo, tracking as TK
+    assert TK.crc32c(b"123456789") == 0xE3069283                     # CRC-32C check value
+    tb = TK.TensorBoardTracker(str(tmp_path / "tb"))
+    jl = TK.JsonlTracker(str(tmp_path / "log" / "trials.jsonl"))
+
+    class Boom(hpo.ExperimentTracker):
+        def on_observe(self, trial):
+            raise RuntimeError("tracker down")
+
+    class FakeMlflow:
+        def __init__(self):
+            self.calls = []
+
+        def set_experiment(self, name):
+            self.calls.append(("exp", name))
+
+        def start_run(self, run_name=None, nested=False):
+            import contextlib
+            self.calls.append(("run", run_name, nested))
+            return contextlib.nullcontext()
+
+        def log_params(self, p):
+            self.calls.append(("params", dict(p)))
+
+        def log_metric(self, k, v, step=None):
+            self.calls.append(("metric", k, v, step))
+
+    fake = FakeMlflow()
+    ml = TK.MLflowTracker("exp1", client=fake)
+    comp = TK.CompositeTracker([tb, jl, Boom(), ml, TK.ConsoleTracker()])
+    space = hpo.SearchSpace([hpo.ParamSpec.Float("lr", 1e-4, 1e-1)])
+    loop = hpo.SearchLoop(space, hpo.RandomStrategy(3), trackers=[comp])
+    for i in range(3):
+        t = loop.suggest()
+        loop.observe(t.id, 1.0 / (i + 1))
+    loop.checkpoint()
+    comp.log_scalar("train/loss", 0.5, 7)
+    events = TK.read_scalar_events(tb.path)
+    assert [e["tag"] for e in events] == ["hpo/metric"] * 3 + ["train/loss"]
+    assert events[1]["value"] == pytest.approx(0.5) and events[3]["step"] == 7
+    rows = [json.loads(l) for l in open(jl.path)]
+    assert [r["event"] for r in rows] == ["trial_start", "trial_end"] * 3 + ["checkpoint", "scalar"]
+    assert ("exp", "exp1") in fake.calls and sum(1 for c in fake.calls if c[0] == "run") == 3
+    assert ("metric", "train/loss", 0.5, 7) in fake.calls
+    assert not TK.MLflowTracker().enabled or True                     # inert without the package, never raises
+    built = TK.build_trackers(["console", f"jsonl:{tmp_path / 'b.jsonl'}", f"tensorboard:{tmp_path / 'tb2'}"])
+    assert len(built.trackers) == 3
+    with pytest.raises(ValueError):
+        TK.build_trackers(["carrier-pigeon"])
+    # a corrupted byte is detected
+    blob = bytearray(open(tb.path, "rb").read())
+    blob[-6] ^= 0xFF
+    open(tb.path, "wb").write(bytes(blob))
+    with pytest.raises(ValueError):
+        TK.read_scalar_events(tb.path)
