@@ -703,3 +703,45 @@ def test_tracking_connectors(tmp_path):
     open(tb.path, "wb").write(bytes(blob))
     with pytest.raises(ValueError):
         TK.read_scalar_events(tb.path)
+
+
+def test_api_llm_runtime(tmp_path):
+    from spiraltorch_b200 import api_llm as L
+    chat = {"model": "m", "choices": [{"message": {"content": "hello spiral world"}, "finish_reason": "stop",
+                                       "logprobs": {"content": [{"logprob": -0.1, "top_logprobs": [{"logprob": -0.1}, {"logprob": -3.0}]}]}}],
+            "usage": {"prompt_tokens": 10, "completion_tokens": 30}}
+    assert L.text_from_response(chat) == "hello spiral world"
+    assert L.usage_from_response(chat) == {"prompt_tokens": 10.0, "completion_tokens": 30.0, "total_tokens": 40.0}
+    assert L.top_probability_from_response(chat) == pytest.approx(math.exp(-0.1))
+    anthropic = {"content": [{"type": "text", "text": "abc"}, {"type": "text", "text": "def"}], "stop_reason": "max_tokens",
+                 "usage": {"input_tokens": 5, "output_tokens": 2}}
+    assert L.text_from_response(anthropic) == "abcdef" and L.finish_reason_from_response(anthropic) == "max_tokens"
+    responses = {"output": [{"content": [{"text": "xy"}]}], "status": "completed"}
+    assert L.text_from_response(responses) == "xy"
+
+    class Obj:
+        output_text = "from attr"
+        usage = None
+    assert L.text_from_response(Obj()) == "from attr"
+    part = L.partial_from_response(chat, prompt="p" * 40, provider="x", latency_ms=500.0)
+    m = part.metrics
+    assert m["speed"] == pytest.approx(math.tanh(60.0 / 64.0)) and m["memory"] == pytest.approx(math.tanh(40 / 2048))
+    assert m["stability"] == pytest.approx(0.65 * 0.95 + 0.35 * math.exp(-0.1)) and m["drs"] == pytest.approx(math.tanh(0.5))
+    assert len(m["gradient"]) == 4 and part.telemetry["api_llm.finish_reason_stop"] == 1.0
+    assert L.partial_from_response(anthropic).metrics["stability"] == pytest.approx(0.65 * 0.45 + 0.35 * 0.65)
+    now = [0.0]
+
+    def clock():
+        now[0] += 0.25
+        return now[0]
+    rt = L.ApiLLMZSpaceRuntime(lambda prompt, **kw: {"choices": [{"text": prompt.upper(), "finish_reason": "stop"}]},
+                               provider="local", model="echo", trace_path=str(tmp_path / "t.jsonl"), clock=clock)
+    summary = rt.run_suite(["alpha beta", "gamma"])
+    assert summary["events"] == 2 and summary["finish_reasons"] == {"stop": 2} and summary["mean_latency_ms"] == pytest.approx(250.0)
+    assert rt.traces[0].text == "ALPHA BETA" and set(rt.fused) == set(L.METRIC_KEYS)
+    events = L.load_trace_events(str(tmp_path / "t.jsonl"))
+    assert len(events) == 2 and events[1]["model"] == "echo"
+    cmp_ = L.compare_trace_runs(events[:1], events[1:])
+    assert set(cmp_["delta"]) >= {"mean_speed", "mean_latency_ms"}
+    with pytest.raises(ValueError):
+        L.metric_gradient_projection({}, 0)
