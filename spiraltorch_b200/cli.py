@@ -25,6 +25,13 @@ ZOO = {
     "conv-classifier": ("dp", "conv-pool classifier, data-parallel, fused conv kernels + SGD momentum", "conv"),
     "contrastive": ("dp", "InfoNCE encoder, fused cross-rank similarity kernel + AdamW", "contrastive"),
     "gpt-1.3b": ("tp", "GPT 1.3B, tensor-parallel with fused all-gather→GEMM / GEMM→reduce-scatter", None),
+    "zconv_classification": ("recipe", "ZConv 3x3 → ReLU → max-pool → Linear on synthetic 8x8 images", None),
+    "llm_char_coherence_scan": ("recipe", "next-character model: Embedding → ZSpaceCoherenceScan → Linear", None),
+    "llm_char_wave_rnn_mixer": ("recipe", "next-character model: Embedding → WaveRnn → ZSpaceMixer → Linear", None),
+    "lstm_probe": ("recipe", "LSTM sequence-mean regression", None),
+    "gnn_graph_regression": ("recipe", "two graph convolutions + mean read-out on a ring graph", None),
+    "zspace_vae_reconstruction": ("recipe", "Z-space VAE on rank-3 data (own Adam optimiser)", None),
+    "zspace_text_vae": ("recipe", "Z-space VAE over wave-encoded character windows", None),
 }
 
 
@@ -48,6 +55,9 @@ def cmd_model_zoo(args) -> int:
     if kind == "cpu":
         from .models import mlp_regression
         return mlp_regression.main(["--backend", args.backend] + (["--run-dir", args.run_dir] if args.run_dir else []))
+    if kind == "recipe":
+        from .models import recipes
+        return recipes.main([args.model, "--backend", args.backend] + (["--run-dir", args.run_dir] if args.run_dir else []))
     if kind == "dp":
         cmd = _torchrun("benchmarks/dp_models.py", args.gpus, ["--model", key, "--steps", str(args.steps)])
     else:

@@ -1,0 +1,203 @@
+"""Small model-zoo recipes on the public ``st.nn`` API (CPU by default, any backend the session resolves).
+
+Each recipe builds synthetic data from a seed, trains with ``ModuleTrainer`` (or the model's own
+optimiser for the VAEs) (parameter gradients are means over the batch of a mean loss, as in the reference,
+hence the large learning rates) and, given ``run_dir``, writes the run-directory layout of
+:mod:`spiraltorch_b200.models.zoo`.  They mirror the reference's scripts in ``models/python``:
+``zconv_classification.py``, ``llm_char_coherence_scan.py``, ``llm_char_wave_rnn_mixer.py``,
+``zspace_vae_reconstruction.py``, ``zspace_text_vae.py`` and the Rust ``modelzoo_gnn_graph_regression`` /
+``modelzoo_lstm_probe`` examples — same layer stacks and artefacts, smaller data.
+
+    python -m spiraltorch_b200.models.recipes zconv_classification --run-dir runs/zconv
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+from typing import Callable, Dict
+
+import torch
+
+import spiraltorch_b200 as st
+from .zoo import RunDir
+
+_TEXT = ("spiral torch keeps its weights on a curved manifold and its rhythm in a wave; "
+         "the roundtable listens above, here and beneath before it speaks. ") * 4
+
+
+def _one_hot(ids: torch.Tensor, classes: int) -> torch.Tensor:
+    return torch.nn.functional.one_hot(ids.long(), classes).float()
+
+
+def _train(model, loss, batches, epochs: int, lr: float, backend: str, rd, quiet: bool):
+    trainer = st.nn.ModuleTrainer(backend=backend, fallback_learning_rate=lr)
+    trainer.prepare(model)
+    history = []
+    for epoch in range(1, epochs + 1):
+        stats = trainer.train_epoch(model, loss, batches)
+        history.append(stats.average_loss)
+        if rd:
+            rd.log_epoch(epoch, stats.batches, stats.average_loss)
+        if not quiet:
+            print(f"[epoch={epoch}] batches={stats.batches} avg_loss={stats.average_loss:.6f}")
+    final = trainer.evaluate_epoch(model, loss, batches).average_loss
+    return history, final
+
+
+def zconv_classification(seed: int = 0):
+    """Two classes of 8×8 one-channel images (a bright left or right half + noise): ZConv 3×3 → ReLU →
+    max-pool 2×2 → Linear → softmax cross-entropy."""
+    g = torch.Generator().manual_seed(seed)
+    n = 128
+    labels = torch.randint(0, 2, (n,), generator=g)
+    imgs = 0.3 * torch.randn(n, 1, 8, 8, generator=g)
+    imgs[labels == 0, :, :, :4] += 1.0
+    imgs[labels == 1, :, :, 4:] += 1.0
+    model = st.nn.Sequential()
+    model.add(st.nn.ZConv("conv1", 1, 4, (8, 8), (3, 3), padding=(1, 1)))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Pool2d("max", 4, 8, 8, (2, 2)))
+    model.add(st.nn.Linear(4 * 4 * 4, 2, name="head"))
+    x, y = imgs.reshape(n, -1), labels.reshape(-1, 1).float()
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, n, 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 2.0
+
+
+def _char_windows(steps: int, seed: int):
+    data = torch.tensor(list(_TEXT.encode()), dtype=torch.float32) % 64        # 64-symbol alphabet
+    g = torch.Generator().manual_seed(seed)
+    starts = torch.randint(0, data.numel() - steps - 1, (192,), generator=g)
+    x = torch.stack([data[s:s + steps] for s in starts.tolist()])
+    y = torch.stack([data[s + steps] for s in starts.tolist()]).reshape(-1, 1)
+    return x, y
+
+
+def llm_char_coherence_scan(seed: int = 0):
+    """Next-character model without attention: Embedding → ZSpaceCoherenceScan → Linear over the flattened window."""
+    steps, dim = 12, 16
+    x, y = _char_windows(steps, seed)
+    model = st.nn.Sequential()
+    model.add(st.nn.Embedding(64, dim, name="embed"))
+    model.add(st.nn.ZSpaceCoherenceScan(dim, steps, memory=4))
+    model.add(st.nn.Linear(steps * dim, 64, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, x.shape[0], 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 16.0
+
+
+def llm_char_wave_rnn_mixer(seed: int = 0):
+    """Embedding → WaveRnn (dilated gated recurrence) → ZSpaceMixer → Linear."""
+    steps, dim, hidden = 12, 16, 32
+    x, y = _char_windows(steps, seed)
+    model = st.nn.Sequential()
+    model.add(st.nn.Embedding(64, dim, name="embed"))
+    model.add(st.nn.WaveRnn("wave", dim, hidden, steps, dilation=2))
+    model.add(st.nn.ZSpaceMixer("mixer", hidden))
+    model.add(st.nn.Linear(hidden, 64, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, x.shape[0], 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 8.0
+
+
+def lstm_probe(seed: int = 0):
+    """Sequence-sum regression with an LSTM: the target is the mean of the first feature over the steps."""
+    g = torch.Generator().manual_seed(seed)
+    steps, dim = 8, 4
+    x = torch.randn(160, steps * dim, generator=g)
+    y = x.reshape(160, steps, dim)[:, :, 0].mean(dim=1, keepdim=True)
+    model = st.nn.Sequential()
+    model.add(st.nn.Lstm("lstm", dim, 16, steps))
+    model.add(st.nn.Linear(16, 1, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, 160, 32)]
+    return model, st.nn.MeanSquaredError(), batches, 8.0
+
+
+def gnn_graph_regression(seed: int = 0):
+    """One 6-node ring graph; node features → two graph convolutions → mean read-out → scalar target."""
+    from ..nn import gnn
+    g = torch.Generator().manual_seed(seed)
+    adj = torch.zeros(6, 6)
+    for i in range(6):
+        adj[i, (i + 1) % 6] = adj[(i + 1) % 6, i] = 1.0
+    ctx = gnn.GraphContext.from_adjacency(adj)
+    net = gnn.ZSpaceGraphNetwork("gnn", ctx, [3, 8, 1], learning_rate=0.3)     # the layers step on their own hypergrad tapes
+    model = gnn.ZSpaceGraphRegressor(net, gnn.GraphReadout("mean"))
+    batches = []
+    for _ in range(24):
+        feats = torch.randn(6, 3, generator=g)
+        batches.append((st.Tensor(feats), st.Tensor(feats[:, 0].mean().reshape(1, 1))))
+    return model, st.nn.MeanSquaredError(), batches, 0.05
+
+
+_TRAINER_RECIPES: Dict[str, Callable] = {
+    "zconv_classification": zconv_classification,
+    "llm_char_coherence_scan": llm_char_coherence_scan,
+    "llm_char_wave_rnn_mixer": llm_char_wave_rnn_mixer,
+    "lstm_probe": lstm_probe,
+    "gnn_graph_regression": gnn_graph_regression,
+}
+
+
+def _run_vae(name: str, epochs: int, seed: int, rd, quiet: bool):
+    g = torch.Generator().manual_seed(seed)
+    if name == "zspace_vae_reconstruction":
+        basis = torch.randn(3, 12, generator=g)
+        data = torch.randn(96, 3, generator=g) @ basis * 0.5            # rank-3 data in 12 dimensions
+        vae = st.nn.ZSpaceVae(12, 3, seed=seed)
+        vae.configure_optimizer_by_name("adam")
+        step = lambda: vae.train_batch(data, learning_rate=2e-2, beta=1e-3)  # noqa: E731
+        evaluate = lambda: vae.evaluate_batch(data)["recon_loss"]            # noqa: E731
+    else:
+        texts = [_TEXT[i:i + 16] for i in range(0, 16 * 12, 16)]
+        vae = st.nn.ZSpaceTextVae(16, 4, seed=seed)
+        vae.configure_optimizer_by_name("adam")
+        step = lambda: vae.train_text_batch(texts, learning_rate=2e-2, beta=1e-3)  # noqa: E731
+        evaluate = lambda: vae.evaluate_text_batch(texts)["recon_loss"]            # noqa: E731
+    initial = evaluate()
+    history = []
+    for epoch in range(1, epochs + 1):
+        losses = [step().recon_loss for _ in range(10)]
+        history.append(sum(losses) / len(losses))
+        if rd:
+            rd.log_epoch(epoch, 10, history[-1])
+        if not quiet:
+            print(f"[epoch={epoch}] batches=10 avg_loss={history[-1]:.6f}")
+    final = evaluate()
+    if rd:
+        vae.save(rd.path / "weights.json")
+    return {"initial_loss": initial, "final_loss": final, "history": history, "model": vae}
+
+
+RECIPES = tuple(_TRAINER_RECIPES) + ("zspace_vae_reconstruction", "zspace_text_vae")
+
+
+def run(name: str, run_dir=None, backend: str = "cpu", epochs: int = 8, seed: int = 0, quiet: bool = False) -> dict:
+    if name not in RECIPES:
+        raise KeyError(f"unknown recipe {name!r}; available: {', '.join(RECIPES)}")
+    rd = RunDir(run_dir, name, backend=backend, hyper_params={"epochs": epochs, "seed": seed}) if run_dir else None
+    if name in _TRAINER_RECIPES:
+        model, loss, batches, lr = _TRAINER_RECIPES[name](seed)
+        history, final = _train(model, loss, batches, epochs, lr, backend, rd, quiet)
+        out = {"initial_loss": history[0], "final_loss": final, "history": history, "model": model}
+        if rd:
+            rd.save_weights(model)
+    else:
+        out = _run_vae(name, epochs, seed, rd, quiet)
+    if rd:
+        rd.write_summary({"initial_loss": out["initial_loss"], "final_loss": out["final_loss"], "epochs": epochs})
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("recipe", choices=RECIPES)
+    ap.add_argument("--backend", default="cpu")
+    ap.add_argument("--run-dir", default=None)
+    ap.add_argument("--epochs", type=int, default=8)
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args(argv)
+    out = run(args.recipe, args.run_dir, args.backend, args.epochs, args.seed)
+    print(f"initial_loss={out['initial_loss']:.6f} final_loss={out['final_loss']:.6f}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -75,3 +75,20 @@ def test_capability_matrix():
     md = cm.render_markdown()
     assert md.splitlines()[0].startswith("| Capability | cpu | cuda |") and len(md.splitlines()) == len(cm.MATRIX) + 2
     assert cm.matrix_summary()["capabilities"] == len(cm.MATRIX)
+
+
+def test_zoo_recipes_learn_and_write_run_dirs(tmp_path):
+    import json
+    from spiraltorch_b200.models import recipes, zoo
+    for name in recipes.RECIPES:
+        out = recipes.run(name, tmp_path / name, epochs=4, quiet=True)
+        assert out["final_loss"] < out["initial_loss"], name
+        run = json.loads((tmp_path / name / "run.json").read_text())
+        assert run["schema"] == "st.modelzoo.run.v1" and run["arch"] == name
+        assert len(zoo.read_metrics(tmp_path / name)) == 4
+        assert (tmp_path / name / "weights.json").exists() and (tmp_path / name / "summary.json").exists()
+    from spiraltorch_b200 import cli
+    assert cli.main(["model-zoo", "lstm_probe", "--run-dir", str(tmp_path / "cli_run")]) == 0
+    import pytest
+    with pytest.raises(KeyError):
+        recipes.run("nope")
