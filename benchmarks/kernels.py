@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Per-kernel micro-benchmarks against the library op on the same GPU, with roofline fractions.
 
-    python benchmarks/kernels.py gemm attn_fwd attn_bwd conv norm adamw ce [--iters 10] [--json out.json]
+    python benchmarks/kernels.py gemm attn_fwd attn_bwd conv norm adamw ce transforms layers [--iters 10] [--json out.json]
     python benchmarks/kernels.py gemm --profile      # 2 launches of ours only: the target of an ncu capture
 
 Every timing: 3 warm-up launches, then ``iters`` launches each preceded by a write of a 256 MiB
@@ -197,6 +197,87 @@ def bench_ce(iters, profile):
     return [row("cross_entropy_stats", [T, V], timed(ours, iters), timed(lib, iters), bytes_=T * V * 2)]
 
 
+def bench_transforms(iters, profile):
+    """The rows of the reference's published transform table (docs/performance/transforms.md:48-64, RTX 4090 + WGPU,
+    times that include host<->device transfers): device-only time of the fused kernel, and the time with the upload
+    of the source image from pinned memory and the download of the result."""
+    from spiraltorch_b200 import vision as V
+    cases = [("resize_512_to_224", (3, 512, 512), dict(resize=(224, 224)), 1.7),
+             ("resize_1024_to_384", (3, 1024, 1024), dict(resize=(384, 384)), 4.8),
+             ("jitter_256_balanced", (3, 256, 256), dict(jitter=V.ColorJitter.balanced()), 0.9),
+             ("jitter_512_vivid", (3, 512, 512), dict(jitter=V.ColorJitter.vivid()), 2.3),
+             ("center_crop_256_to_224", (3, 256, 256), dict(crop=(224, 224)), 0.3),
+             ("hflip_256", (3, 256, 256), dict(flip=True), 0.2),
+             ("classification_pipeline_224", (3, 512, 512), dict(resize=(256, 256), crop=(224, 224),
+                                                                 jitter=V.ColorJitter.balanced(), flip=True), 3.1)]
+    out = []
+    for name, shape, kw, ref_ms in cases:
+        host = torch.rand(*shape).pin_memory()
+        dev = host.to(DEV)
+        if kw.get("jitter") is not None and kw["jitter"].means is None:
+            # per-channel means for the contrast term are an input of the kernel; computing them is a separate reduction
+            kw = dict(kw, jitter=V.ColorJitter(kw["jitter"].brightness, kw["jitter"].contrast, kw["jitter"].saturation,
+                                               kw["jitter"].hue, means=tuple((dev * kw["jitter"].brightness).mean(dim=(1, 2)).tolist())))
+        ours = lambda: V.preprocess(dev, **kw)  # noqa: E731
+        if profile:
+            ours(); ours(); torch.cuda.synchronize()
+            return out
+        res = ours()
+        back = torch.empty(res.shape, dtype=res.dtype).pin_memory()
+
+        def e2e():
+            d = host.to(DEV, non_blocking=True)
+            back.copy_(V.preprocess(d, **kw), non_blocking=True)
+        r = {"kernel": "transform_" + name, "shape": list(shape), "ours_ms": round(timed(ours, iters), 4),
+             "ours_with_transfers_ms": round(timed(e2e, iters), 4), "reference_published_gpu_ms": ref_ms,
+             "reference_hardware": "RTX 4090 (WGPU), includes transfers"}
+        print(json.dumps(r), flush=True)
+        out.append(r)
+    return out
+
+
+def bench_layers(iters, profile):
+    """One training step of the two small layers the reference quotes timings for (docs/learning_backend_audit.md:
+    WaveRnn one-batch step 7.1 ms CPU / 125.9 ms WGPU; GNN trainer step 16.5 ms CPU / 362.8 ms WGPU)."""
+    import spiraltorch_b200 as st
+    from spiraltorch_b200.nn import gnn
+    out = []
+    steps, dim, hidden, batch = 16, 32, 64, 32
+    wave = st.nn.Sequential()
+    wave.add(st.nn.WaveRnn("wave", dim, hidden, steps))
+    wave.add(st.nn.Linear(hidden, 8, name="head"))
+    wave.to(DEV)
+    x = st.Tensor._wrap(torch.randn(batch, steps * dim, device=DEV))
+    y = st.Tensor._wrap(torch.randn(batch, 8, device=DEV))
+    loss = st.nn.MeanSquaredError()
+
+    def wave_step():
+        pred = wave.forward(x)
+        wave.backward(x, loss.backward(pred, y))
+        wave.apply_step(1e-2)
+    adj = (torch.rand(64, 64) < 0.1).float()
+    adj = ((adj + adj.t()) > 0).float()
+    net = gnn.ZSpaceGraphNetwork("g", gnn.GraphContext.from_adjacency(adj.to(DEV)), [16, 32, 4])
+    model = gnn.ZSpaceGraphRegressor(net, gnn.GraphReadout("mean"))
+    model.to(DEV)
+    gx = st.Tensor._wrap(torch.randn(64, 16, device=DEV))
+    gy = st.Tensor._wrap(torch.randn(1, 4, device=DEV))
+
+    def gnn_step():
+        pred = model.forward(gx)
+        model.backward(gx, loss.backward(pred, gy))
+        model.apply_step(1e-2)
+    if profile:
+        wave_step(); gnn_step(); torch.cuda.synchronize()
+        return out
+    for name, fn, cpu_ms, wgpu_ms in (("wave_rnn_train_step", wave_step, 7.132, 125.897), ("gnn_train_step", gnn_step, 16.503, 362.814)):
+        r = {"kernel": name, "ours_ms": round(timed(fn, iters), 4), "reference_published_cpu_ms": cpu_ms,
+             "reference_published_wgpu_ms": wgpu_ms}
+        print(json.dumps(r), flush=True)
+        out.append(r)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernels", nargs="*", default=["gemm", "attn_fwd", "attn_bwd", "conv", "norm", "adamw", "ce"])
@@ -210,7 +291,9 @@ def main() -> int:
              "conv": lambda: bench_conv(args.iters, args.profile),
              "norm": lambda: bench_norm(args.iters, args.profile),
              "adamw": lambda: bench_adamw(args.iters, args.profile),
-             "ce": lambda: bench_ce(args.iters, args.profile)}
+             "ce": lambda: bench_ce(args.iters, args.profile),
+             "transforms": lambda: bench_transforms(args.iters, args.profile),
+             "layers": lambda: bench_layers(args.iters, args.profile)}
     rows = []
     for k in args.kernels:
         rows += table[k]()
