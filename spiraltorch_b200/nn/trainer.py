@@ -224,6 +224,20 @@ class ModuleTrainer:
         self.zero(module)
         module.train()
         stats = EpochStats(tensor_backend={"backend": self.backend, "ops_total": 0})
+        from ..observability import TensorOpStepCollector
+        collector = TensorOpStepCollector()
+        collector.__enter__()                     # tensor-op events of this thread are folded into the epoch stats
+        try:
+            self._train_batches(module, loss, batches, schedule, stats)
+        finally:
+            collector.__exit__(None, None, None)
+        stats.tensor_backend.update({k: v for k, v in collector.stats.as_dict().items() if k != "ops_total"})
+        stats.tensor_backend["tensor_ops"] = collector.stats.ops_total
+        stats.average_loss = stats.total_loss / max(1, stats.batches)
+        plugin.publish("EpochEnd", {"epoch": self.epoch, "loss": stats.average_loss})
+        return stats
+
+    def _train_batches(self, module, loss, batches, schedule, stats) -> None:
         for x, y in batches:
             t0 = time.perf_counter()
             pred = module.forward(x)
@@ -254,9 +268,6 @@ class ModuleTrainer:
                 self.monitor.observe(metrics)
             plugin.publish("TrainerStep", {"step": self.steps, "epoch": self.epoch, "loss": lv,
                                            "step_time_ms": metrics.step_time_ms})
-        stats.average_loss = stats.total_loss / max(1, stats.batches)
-        plugin.publish("EpochEnd", {"epoch": self.epoch, "loss": stats.average_loss})
-        return stats
 
     def evaluate_epoch(self, module: Module, loss, batches) -> EpochStats:
         module.eval()

@@ -53,10 +53,9 @@ def set_finite_checks(enabled: bool) -> None:
     _CHECK_FINITE[0] = bool(enabled)
 
 
-def _emit(op: str, in_shape, out_shape) -> None:
-    from . import plugin
-    if plugin.has_listeners("TensorOp"):
-        plugin.publish("TensorOp", {"op": op, "input_shape": list(in_shape), "output_shape": list(out_shape)})
+def _emit(op: str, in_shape, out_shape, **fields) -> None:
+    from . import observability
+    observability.emit_tensor_op(op, in_shape, out_shape, **fields)
 
 
 class Tensor:
@@ -221,7 +220,12 @@ class Tensor:
                 out = out + residual.to(out.device)
             out = out.to(self._t.device)
         self._check(label + "_output", out)
-        _emit(label, self.shape(), tuple(out.shape))
+        from . import observability as _obs
+        _obs.record_receipt(_obs.TensorExecutionReceipt(
+            label, backend or "auto", "cuda" if self._t.is_cuda and backend not in ("cpu", "naive", "faer", "simd", "cpu-simd") else "cpu",
+            "cuda" if use_cuda else "cpu", None,
+            {"kind": "dense_matmul", "rows": self.rows, "inner": self.cols, "cols": other.cols}))
+        _emit(label, self.shape(), tuple(out.shape), backend="cuda" if use_cuda else "cpu")
         return out
 
     def matmul(self, other: "Tensor", *, backend: Optional[str] = None, out: Optional["Tensor"] = None) -> "Tensor":
@@ -405,3 +409,32 @@ class Tensor:
         if t.dim() != 2:
             raise TensorError("from_dlpack: only 1-D and 2-D tensors are supported")
         return Tensor._wrap(t.to(torch.float32))
+
+
+def _instrument(names) -> None:
+    """Every public op publishes a tensor-op event (input shape, output shape, device) when somebody listens."""
+    import functools
+
+    def wrap(name, fn):
+        @functools.wraps(fn)
+        def inner(self, *args, **kwargs):
+            out = fn(self, *args, **kwargs)
+            from . import observability
+            if observability.has_observers() or _plugin_listening():
+                first = out[0] if isinstance(out, tuple) else out
+                shape = first.shape() if isinstance(first, Tensor) else ()
+                _emit(name, self.shape(), shape, backend="cuda" if self._t.is_cuda else "cpu")
+            return out
+        return inner
+    for n in names:
+        setattr(Tensor, n, wrap(n, getattr(Tensor, n)))
+
+
+def _plugin_listening() -> bool:
+    from . import plugin
+    return plugin.has_listeners("TensorOp")
+
+
+_instrument(["row_softmax", "row_softmax_hardmax", "scaled_dot_attention", "layer_norm_affine", "layer_norm_affine_add",
+             "gelu", "relu", "add", "sub", "scale", "hadamard", "mul_row", "transpose", "reshape", "sum_axis0_tensor",
+             "max_axis0", "cat_rows", "project_to_poincare"])

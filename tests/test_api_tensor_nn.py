@@ -362,3 +362,43 @@ def test_mapped_state_dict_loading():
     seq = st.nn.Sequential()
     seq.eval()
     assert seq.training is False
+
+
+def test_observers_receipts_and_collector():
+    from spiraltorch_b200 import observability as O
+    events = []
+    a = st.Tensor(2, 3, [1, 2, 3, 4, 5, 6])
+    b = st.Tensor(3, 2, [1, 0, 0, 1, 1, 1])
+    a.matmul(b)                                   # nobody listens: nothing is built
+    built = []
+    O.emit_tensor_op_meta("x", lambda: built.append(1) or {})
+    assert built == []
+    with O.observe(events.append):
+        a.matmul(b, backend="cpu")
+        a.add(a).row_softmax()
+        O.emit_tensor_op_meta("matmul", lambda: {"tile": 128})
+    kinds = [e["kind"] for e in events]
+    assert kinds == ["execution_receipt", "tensor_op", "tensor_op", "tensor_op", "tensor_op_meta"]
+    assert events[1]["op"] == "matmul" and events[1]["output_shape"] == [2, 2] and events[2]["op"] == "add"
+    assert events[0]["requested_backend"] == "cpu" and not events[0]["fell_back"] and events[-1]["meta"] == {"tile": 128}
+    assert O.last_receipt().workload == {"kind": "dense_matmul", "rows": 2, "inner": 3, "cols": 2}
+    a.matmul(b)
+    assert len(events) == 5                       # observer removed
+    with O.TensorOpStepCollector() as col:
+        a.matmul(b)
+        a.hadamard(a)
+    assert col.stats.ops_total == 2 and col.stats.by_op == {"matmul": 1, "hadamard": 1} and col.stats.backend_cpu == 1
+    assert O.resolve_backend("cuda", False, True) == ("cuda", "cpu", "operands are host tensors")
+    assert O.resolve_backend(None, True, False) == ("cuda", "cpu", "native library unavailable")
+    assert O.resolve_backend("faer", True, True) == ("cpu", "cpu", None)
+    with pytest.raises(RuntimeError):
+        O.resolve_backend("cuda", False, True, strict=True)
+    assert len(O.plan_commitment({"b": 1, "a": 2})) == 64 and O.plan_commitment({"a": 2, "b": 1}) == O.plan_commitment({"b": 1, "a": 2})
+    # thread-local observers do not see other threads' ops
+    import threading
+    seen = []
+    O.add_observer(seen.append, thread_local=True)
+    t = threading.Thread(target=lambda: a.matmul(b))
+    t.start(); t.join()
+    O.remove_observer(seen.append)
+    assert seen == []
