@@ -119,6 +119,10 @@ class Module:
     def to(self, device) -> "Module":
         for p in self.parameters():
             p.value = p.value.to(device)
+            if p.hypergrad is not None:
+                p.hypergrad.to(device)
+            if p.realgrad is not None:
+                p.realgrad.to(device)
             p.zero()
         return self
 

@@ -97,7 +97,26 @@ def stream_ptr(device: Optional[torch.device] = None) -> ctypes.c_void_p:
 
 
 def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+    """Device pointer of a CUDA tensor for a native launch.  A host tensor here would make the kernel
+    dereference a host address and fault the context, so it is refused."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise ValueError(f"native launch was given a host tensor of shape {tuple(t.shape)}; move it to the GPU first")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def same_device(op: str, *tensors: Optional[torch.Tensor]) -> None:
+    """Every tensor handed to one launch must live on the same CUDA device: a kernel that is given a host
+    pointer (or another GPU's) faults the context, so this is checked before the pointers are taken."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"{op}: operands live on different devices ({dev} and {t.device})")
 
 
 def use_native(t: torch.Tensor) -> bool:

@@ -145,6 +145,7 @@ def hyper_accumulate(g: torch.Tensor, v: torch.Tensor, curvature: float, tol: fl
         g.copy_(porous_mix(g + upd, saturation, porosity))
         return
     v = v.float().contiguous()
+    native.same_device("hyper_accumulate", g, v)
     st = native.lib().st_hyper_accumulate(native.ptr(g), native.ptr(v), ctypes.c_longlong(g.numel()),
                                           ctypes.c_float(curvature), ctypes.c_float(tol),
                                           ctypes.c_float(saturation), ctypes.c_float(porosity),
@@ -191,6 +192,7 @@ def hyper_apply(w: torch.Tensor, g: Optional[torch.Tensor], g_real: Optional[tor
             g_real.zero_()
         return
     assert w.dtype == torch.float32 and w.is_contiguous()
+    native.same_device("hyper_apply", w, g, g_real)
     st = native.lib().st_hyper_apply(native.ptr(w), native.ptr(g), native.ptr(g_real), ctypes.c_int(rows),
                                      ctypes.c_int(cols), ctypes.c_float(curvature), ctypes.c_float(lr),
                                      ctypes.c_float(lr_real), ctypes.c_float(tol), ctypes.c_float(saturation),

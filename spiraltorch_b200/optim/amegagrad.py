@@ -90,6 +90,9 @@ class AmegaHypergrad:
         w = _as_torch(weights)
         if tuple(w.shape) != self.shape():
             raise ValueError(f"shape mismatch: expected {self.shape()}, got {tuple(w.shape)}")
+        self.to(w.device)                     # the tape follows its weights (a module may have been moved)
+        if realgrad is not None:
+            realgrad.to(w.device)
         K.hyper_apply(w, self.gradient, None if realgrad is None else realgrad.gradient,
                       curvature=self.curvature, lr=self.learning_rate,
                       lr_real=0.0 if realgrad is None else realgrad.learning_rate,
@@ -97,6 +100,11 @@ class AmegaHypergrad:
 
     def reset(self) -> None:
         self.gradient.zero_()
+
+    def to(self, device) -> "AmegaHypergrad":
+        if self.gradient.device != torch.device(device):
+            self.gradient = self.gradient.to(device)
+        return self
 
     def gradient_norm(self) -> float:
         return float(self.gradient.norm())
@@ -128,6 +136,11 @@ class AmegaRealgrad:
         g = _as_torch(grad).to(self.gradient.device, torch.float32).reshape(self.rows, self.cols)
         self.gradient.add_(g)
 
+    def to(self, device) -> "AmegaRealgrad":
+        if self.gradient.device != torch.device(device):
+            self.gradient = self.gradient.to(device)
+        return self
+
     accumulate_wave = accumulate
 
     def accumulate_pair(self, prediction, target) -> None:
@@ -135,6 +148,7 @@ class AmegaRealgrad:
 
     def apply(self, weights: torch.Tensor) -> None:
         w = _as_torch(weights)
+        self.to(w.device)
         K.hyper_apply(w, None, self.gradient, curvature=-1.0, lr=0.0, lr_real=self.learning_rate,
                       tol=1e-6, saturation=1e6, porosity=0.2)
 

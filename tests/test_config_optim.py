@@ -195,3 +195,13 @@ def test_grad_scaler_and_warmup_cosine_schedule():
     opt2.step(layer)
     assert ad.min_scale <= ad.scale_for("w", torch.randn(4, 4)) <= ad.max_scale
     assert amp.SpectralLrAdapter.from_state(ad.state()).avg_energy == ad.avg_energy
+
+
+def test_native_pointer_guard_refuses_host_tensors():
+    import torch
+    from spiraltorch_b200.ops import native
+    assert native.ptr(None).value in (None, 0)
+    with pytest.raises(ValueError):
+        native.ptr(torch.zeros(4))
+    with pytest.raises(ValueError):
+        native.same_device("op", torch.zeros(1), torch.zeros(1, device="meta"))

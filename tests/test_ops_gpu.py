@@ -271,3 +271,39 @@ def test_recurrent_gate_kernels_match_reference():
     assert torch.equal(R.sequence_last_step(x, 5, 16), x.reshape(B, 5, 16)[:, -1])
     assert R.launch_count >= n0 + 6
     native.raise_on_device_error()
+
+
+@pytest.mark.gpu
+def test_module_moved_to_gpu_keeps_tapes_with_weights():
+    """A module built on the host with hypergrad tapes and then moved: the tapes must follow the weights
+    (a host accumulator handed to the fused step kernel would be a host pointer on the device)."""
+    import spiraltorch_b200 as st
+    from spiraltorch_b200.nn import gnn
+    adj = torch.zeros(6, 6)
+    for i in range(6):
+        adj[i, (i + 1) % 6] = adj[(i + 1) % 6, i] = 1.0
+    net = gnn.ZSpaceGraphNetwork("g", gnn.GraphContext.from_adjacency(adj), [3, 8, 1], learning_rate=0.3)
+    model = gnn.ZSpaceGraphRegressor(net, gnn.GraphReadout("mean"))
+    model.to("cuda")
+    assert all(p.hypergrad.gradient.is_cuda for p in model.parameters())
+    loss = st.nn.MeanSquaredError()
+    g = torch.Generator().manual_seed(0)
+    first = last = None
+    for _ in range(40):
+        x = torch.randn(6, 3, generator=g)
+        xt, yt = st.Tensor._wrap(x.cuda()), st.Tensor._wrap(x[:, 0].mean().reshape(1, 1).cuda())
+        pred = model.forward(xt)
+        val = float(loss.forward(pred, yt).torch())
+        first = val if first is None else first
+        last = val
+        model.backward(xt, loss.backward(pred, yt))
+        model.apply_step(1e-2)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    assert all(torch.isfinite(p.value).all() for p in model.parameters())
+    lin = st.nn.Linear(4, 4, name="l")
+    lin.attach_hypergrad(-1.0, 1e-2)
+    lin.to("cuda")
+    lin.backward(st.Tensor._wrap(torch.randn(2, 4).cuda()), st.Tensor._wrap(torch.randn(2, 4).cuda()))
+    lin.apply_step(1e-2)
+    torch.cuda.synchronize()
