@@ -402,3 +402,35 @@ def test_observers_receipts_and_collector():
     t.start(); t.join()
     O.remove_observer(seen.append)
     assert seen == []
+
+
+def test_hf_bridge_round_trip_and_lora():
+    from spiraltorch_b200 import hf_bridge as HB
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Linear(6, 4), torch.nn.ReLU(), torch.nn.Linear(4, 3))
+    model = st.nn.Sequential()
+    model.add(st.nn.Linear(6, 4, name="fc1")); model.add(st.nn.Relu()); model.add(st.nn.Linear(4, 3, name="head"))
+    rep = HB.load_torch_module(model, ref, [("0", "fc1"), ("2", "head")])
+    assert rep["compatible"] and rep["matched"] == 4
+    x = torch.randn(5, 6)
+    assert torch.allclose(model.forward(st.Tensor._wrap(x)).torch(), ref(x), atol=1e-5)
+    back = HB.export_torch_state(model, [("fc1", "0"), ("head", "2")])
+    assert all(torch.equal(back[k], v) for k, v in ref.state_dict().items())
+    # GPT-2 Conv1D layout is (in, out): inferred from the shapes
+    conv1d_state = {"c_fc.weight": torch.randn(6, 4), "c_fc.bias": torch.randn(4)}
+    lin = st.nn.Linear(6, 4, name="fc")
+    rules = HB.key_map_for_linears([("c_fc", "fc")], HB._rows(conv1d_state), lin)
+    assert rules["c_fc.weight"]["transform"] == "identity"
+    assert HB.load_torch_module(lin, conv1d_state, [("c_fc", "fc")])["matched"] == 2
+    with pytest.raises(KeyError):
+        HB.key_map_for_linears([("c_fc", "nope")], conv1d_state, lin)
+    lora = st.nn.LoraLinear(6, 4, 2, alpha=4.0, name="ad")
+    delta = torch.randn(6, 2) @ torch.randn(2, 4)
+    a, b = HB.lora_from_delta(delta, 2, alpha=4.0)
+    HB.attach_lora_factors(lora, a, b, peft_layout=False)
+    base = {p.name: p.value for p in lora.parameters()}["ad::weight"]
+    assert torch.allclose(HB.merge_lora(lora), base + delta, atol=1e-4)
+    HB.attach_lora_factors(lora, a.t().contiguous(), b.t().contiguous())       # PEFT layout: (rank, in) and (out, rank)
+    assert torch.allclose(HB.merge_lora(lora), base + delta, atol=1e-4)
+    with pytest.raises(ValueError):
+        HB.attach_lora_factors(lora, torch.zeros(3, 6), torch.zeros(4, 3))
