@@ -201,16 +201,22 @@ def main() -> int:
         barrier()
 
     fused_note = None
-    warm_up()
+    try:
+        warm_up()
+    except native.DeviceWaitTimeout as exc:
+        if not (world > 1 and tp_mode == "fused" and args.tp_mode == "auto"):
+            raise
+        fused_note = repr(exc)
+        torch.cuda.synchronize(device)
     if world > 1 and tp_mode == "fused" and args.tp_mode == "auto":
         # A bounded wait of a fused kernel that ran out (a peer that never signalled) leaves an error word on
         # the rank that saw it.  The ranks agree on the outcome; on failure every rank rebuilds the model on
         # NCCL collectives and warms up again, so that the run still yields a (slower, labelled) number.
+        ok = 0 if fused_note else 1
         try:
             native.raise_on_device_error()
-            ok = 1
         except Exception as exc:  # noqa: BLE001
-            ok, fused_note = 0, repr(exc)
+            ok, fused_note = 0, fused_note or repr(exc)
         flag = torch.tensor([ok], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:

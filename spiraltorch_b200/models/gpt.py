@@ -35,6 +35,7 @@ from ..ops import attention as attn_ops
 from ..ops import elementwise as ew
 from ..ops import gemm as gemm_ops
 from ..ops import loss as loss_ops
+from ..ops import native
 from ..ops import norm as norm_ops
 from ..parallel.tp import TPContext
 
@@ -90,6 +91,8 @@ class GPTModel(nn.Module):
         self.cfg = cfg
         self.grad_ready_hook = None   # called with a parameter-group name once its gradient is final
         self.tp = tp or TPContext()
+        # fused collectives wait (bounded) on peers: poll their error record between layers
+        self._fused_tp = type(self.tp).__name__ == "FusedTPContext" and torch.device(device).type == "cuda"
         W = self.tp.world
         assert cfg.n_heads % W == 0 and cfg.ffn % W == 0 and cfg.vocab_size % W == 0
         assert cfg.head_dim in (64, 128), "attention kernels support head_dim 64 and 128"
@@ -240,6 +243,8 @@ class GPTModel(nn.Module):
         for l in range(cfg.n_layers):
             resid, x, act = self._layer_forward(l, resid, x, B, S, keep=keep)
             acts.append(act)
+            if self._fused_tp and native.error_pending():
+                native.raise_on_device_error()     # a bounded wait ran out: stop now, not 2 s per kernel later
         yf, hf, mf, rf = self._norm_fwd(x, "norm_f", residual=resid)
         logits, yf_full = tp.ag_gemm(yf, emb, key="head")
         if targets is None:
@@ -276,6 +281,8 @@ class GPTModel(nn.Module):
         for l in reversed(range(cfg.n_layers)):
             d = self._layer_backward(l, acts[l], d, B, S)
             acts[l] = None
+            if self._fused_tp and native.error_pending():
+                native.raise_on_device_error()
             if self.grad_ready_hook is not None:
                 self.grad_ready_hook(f"h{l}")
         d_full = tp.all_gather_rows(d)

@@ -81,6 +81,11 @@ def read_error_word(clear: bool = True) -> tuple[int, int, int, int]:
     return tuple(int(x) for x in buf)  # type: ignore[return-value]
 
 
+def error_pending() -> bool:
+    """True when a kernel has left an error record (a host read of mapped memory: no synchronisation)."""
+    return read_error_word(clear=False)[0] != 0
+
+
 def raise_on_device_error() -> None:
     code, detail, block, count = read_error_word(clear=True)
     if code == 0:
