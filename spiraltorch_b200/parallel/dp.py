@@ -47,6 +47,11 @@ class FusedDataParallel:
         self.allocator = SymmetricAllocator(self.heap)
         self.kind, self.hyper, self.overlap = kind, hyper, overlap
         self.bucket_elems = int(bucket_mb * (1 << 20) / 4)
+        if self.heap.world == 1:
+            # nothing to overlap with: one launch over the whole gradient buffer on the compute stream (per-bucket
+            # launches on a side stream only add launch and stream-switch latency to a launch-bound step)
+            self.overlap = False
+            self.bucket_elems = 1 << 40
         self.comm_ctas = comm_ctas
         self.model = None
         self.dp: Optional[FusedDPStep] = None
