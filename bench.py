@@ -196,18 +196,20 @@ def main() -> int:
 
     # ---- warm-up ---------------------------------------------------------------------------
     def warm_up():
-        for i in range(args.warmup):
-            trainer.device_step(*dev_batches[i % 2])
+        """Runs the warm-up steps; every rank reaches the barrier exactly once, also when a bounded wait of a fused
+        kernel ran out on it (the collectives of the ranks must stay paired)."""
+        note = None
+        try:
+            for i in range(args.warmup):
+                trainer.device_step(*dev_batches[i % 2])
+        except native.DeviceWaitTimeout as exc:
+            if not (world > 1 and tp_mode == "fused" and args.tp_mode == "auto"):
+                raise
+            note = repr(exc)
         barrier()
+        return note
 
-    fused_note = None
-    try:
-        warm_up()
-    except native.DeviceWaitTimeout as exc:
-        if not (world > 1 and tp_mode == "fused" and args.tp_mode == "auto"):
-            raise
-        fused_note = repr(exc)
-        torch.cuda.synchronize(device)
+    fused_note = warm_up()
     if world > 1 and tp_mode == "fused" and args.tp_mode == "auto":
         # A bounded wait of a fused kernel that ran out (a peer that never signalled) leaves an error word on
         # the rank that saw it.  The ranks agree on the outcome; on failure every rank rebuilds the model on
