@@ -551,29 +551,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]; one warp per (b,s,h).
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
-                                  float* __restrict__ delta, int B, int S, int H, int D,
-                                  long long o_sb, long long o_ss, long long o_sh, long long do_sb,
-                                  long long do_ss, long long do_sh) {
-  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d].  D / 8 lanes share one (b,s,h) row, each with one
+// 16-byte load of O and of dO (a warp covers 2 rows at D = 128, 4 at D = 64): one row per warp with 4-byte
+// loads left this bandwidth-bound pass at a quarter of the copy rate.
+template <int D>
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                  float* __restrict__ delta, int B, int S, int H, long long o_sb, long long o_ss, long long o_sh,
+                  long long do_sb, long long do_ss, long long do_sh) {
+  constexpr int LPR = D / 8;                       // lanes per row
   const long long total = (long long)B * S * H;
-  if (w >= total) return;
-  const int hh = w % H;
-  const long long bs = w / H;
-  const int s = bs % S;
-  const int bb = bs / S;
-  const __nv_bfloat16* op = O + bb * o_sb + s * o_ss + hh * o_sh;
-  const __nv_bfloat16* dp = dO + bb * do_sb + s * do_ss + hh * do_sh;
-  float acc = 0.0f;
-  for (int c = lane * 2; c < D; c += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + c));
-    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + c));
-    acc += a.x * g.x + a.y * g.y;
+  const int sub = threadIdx.x % LPR;
+  const long long stride = (long long)gridDim.x * (blockDim.x / LPR);
+  for (long long w = blockIdx.x * (long long)(blockDim.x / LPR) + threadIdx.x / LPR; ; w += stride) {
+    // every lane of a warp takes the same number of trips: the shuffles below need the full warp
+    const bool live = w < total;
+    if (!__any_sync(0xffffffffu, live)) break;
+    float acc = 0.0f;
+    int hh = 0, s = 0, bb = 0;
+    if (live) {
+      hh = (int)(w % H);
+      const long long bs = w / H;
+      s = (int)(bs % S);
+      bb = (int)(bs / S);
+      const uint4 a = *reinterpret_cast<const uint4*>(O + bb * o_sb + s * o_ss + hh * o_sh + sub * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(dO + bb * do_sb + s * do_ss + hh * do_sh + sub * 8);
+      const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = unpack_bf16x2(av[i]), y = unpack_bf16x2(gv[i]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (live && sub == 0) delta[((long long)bb * H + hh) * S + s] = acc;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[((long long)bb * H + hh) * S + s] = acc;
 }
 
 }  // namespace
@@ -608,12 +621,18 @@ ST_API int st_attn_bwd(const StAttnBwdArgs* a, void* stream_v) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
 
   {
-    const long long warps = (long long)a->B * a->Sq * a->H;
-    const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
-    attn_delta_kernel<<<(unsigned)blocks, threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(a->O), static_cast<const __nv_bfloat16*>(a->dO), a->delta,
-        a->B, a->Sq, a->H, a->D, a->o_sb, a->o_ss, a->o_sh, a->do_sb, a->do_ss, a->do_sh);
+    const long long rows = (long long)a->B * a->Sq * a->H;
+    const int rows_per_block = 256 / (a->D / 8);
+    long long blocks = (rows + rows_per_block - 1) / rows_per_block;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    auto Op = static_cast<const __nv_bfloat16*>(a->O);
+    auto dOp = static_cast<const __nv_bfloat16*>(a->dO);
+    if (a->D == 128)
+      attn_delta_kernel<128><<<(unsigned)blocks, 256, 0, s>>>(Op, dOp, a->delta, a->B, a->Sq, a->H, a->o_sb, a->o_ss,
+                                                            a->o_sh, a->do_sb, a->do_ss, a->do_sh);
+    else
+      attn_delta_kernel<64><<<(unsigned)blocks, 256, 0, s>>>(Op, dOp, a->delta, a->B, a->Sq, a->H, a->o_sb, a->o_ss,
+                                                           a->o_sh, a->do_sb, a->do_ss, a->do_sh);
     ST_CUDA_CHECK(cudaGetLastError());
   }
 
