@@ -154,7 +154,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mean = RMS ? 0.0f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[MV][8], gy[MV][8];
+    float xh[MV][8], gy[MV][8], rr[MV][8];
     float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < MV; ++i) {
@@ -163,6 +163,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
         float xv[8], dv[8];
         load8(x + (size_t)row * d + vi * 8, xv);
         load8(dy + (size_t)row * d + vi * 8, dv);
+        // the residual-branch gradient is only needed after the row reduction: issue its load now so that the
+        // reduction hides the latency
+        if (dres) load8(dres + (size_t)row * d + vi * 8, rr[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mean) * rstd;
@@ -184,10 +187,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[i][j] - m2 - xh[i][j] * m1);
         if (dres) {  // gradient arriving through the residual branch
-          float r[8];
-          load8(dres + (size_t)row * d + vi * 8, r);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
+          for (int j = 0; j < 8; ++j) o[j] += rr[i][j];
         }
         store8(dx + (size_t)row * d + vi * 8, o);
       }
