@@ -333,3 +333,56 @@ def test_roundtable_node_and_conductor():
     other = RT.HeurOpLog(); other.merge(log); other.merge(log)
     assert other.high_watermark() == 2 and other.top_winners(5)[0].script == "wg=256" and RT.HeurOpLog().missing_ranges() == [(0, 0)]
     assert RT.exchange_summaries(a) == [a] and RT.exchange_summaries(None) == []
+
+
+def test_zrba_block_gate_covariance_and_metrics():
+    """Parity: crates/st-nn/src/z_rba/{mod,beta_residual,cov_head,telemetry}.rs unit tests."""
+    import math
+    from spiraltorch_b200.nn import (BetaGate, CovHead, SpectralFeatureSample, ZRBA, ZRBAConfig, ZRBAMetrics,
+                                     ZFrame, ZIndex)
+    from spiraltorch_b200.nn.zspace import ZTensor
+    from spiraltorch_b200.nn.zrba import spearman_rank_correlation
+    from spiraltorch_b200.tensor import Tensor, TensorError
+
+    stats = SpectralFeatureSample(1, 0.8, 0.1, 0.05, 0.2)
+    gate = BetaGate()
+    s = gate.forward(stats, [ZIndex(1, 2, 3)])
+    assert 0.0 <= s.sample <= 1.0 and s.alpha > 0 and s.beta > 0 and s.applied == s.sample
+    assert abs(s.expected - s.alpha / (s.alpha + s.beta)) < 1e-12
+    before = gate.ema()
+    with pytest.raises(TensorError):
+        gate.try_forward(SpectralFeatureSample(1, 0.8, math.inf, 0.05, 0.2), [ZIndex(1, 2, 3)])
+    assert gate.ema() == before                                   # a rejected draw leaves the averages alone
+    assert gate.forward(SpectralFeatureSample(1, 0.8, math.inf, 0.05, 0.2), []).expected == 0.5
+    # same seed, same stream
+    assert BetaGate().forward(stats, [ZIndex(1, 2, 3)]).sample == s.sample
+
+    g = torch.Generator().manual_seed(0)
+    mu, sig = torch.randn(12, 6, generator=g), torch.rand(12, 6, generator=g)
+    out = CovHead(2).forward(mu, sig)
+    cov = out.covariance.torch()
+    assert torch.allclose(cov, cov.T, atol=1e-6)
+    assert float(torch.linalg.eigvalsh(cov.double()).min()) >= 1e-4 - 1e-7
+    assert out.telemetry.condition_number >= 1.0
+    # full rank: covariance is exactly the sample covariance plus the mean diagonal
+    full = CovHead(6).forward(mu, sig).covariance.torch()
+    c = mu - mu.mean(0)
+    assert torch.allclose(full, c.T @ c / 12 + torch.diag(sig.mean(0)), atol=1e-5)
+
+    idx = [ZIndex(i % 3, i % 2, i % 4) for i in range(12)]
+    blk = ZRBA(ZRBAConfig(d_model=6, n_heads=2, cov_rank=3))
+    z, zc, tel = blk.forward(ZTensor(Tensor._wrap(mu), Tensor._wrap(sig), idx), ZFrame(4), stats)
+    assert z.mu.shape() == (12, 6) and zc.covariance.shape() == (6, 6) and zc.gate.applied == zc.gate.expected
+    # targets at the predicted mean: full coverage, and the NLL is the entropy term alone
+    pred, var = z.mu.torch(), z.sigma.torch()
+    m = tel.metrics(z.mu, z.sigma, pred.mean(1).tolist(), 0.9, idx)
+    assert m.picp == 1.0 and [b.band for b in m.reliability_by_band] == [0, 1, 2]
+    want = 0.5 * torch.log(2 * math.pi * var.clamp(min=1e-6).mean(1)).mean()
+    assert abs(m.nll - float(want)) < 1e-5
+    assert abs(m.pinaw - float(2 * 1.6448536 * var.mean(1).sqrt().mean())) < 1e-4
+    bundle = tel.bundle_metrics(m).to_json()
+    assert set(bundle) == {"metrics", "gate", "covariance"}
+    assert abs(spearman_rank_correlation([1, 2, 3, 4], [10, 20, 30, 40]) - 1.0) < 1e-12
+    assert abs(spearman_rank_correlation([1, 2, 3, 4], [4, 3, 2, 1]) + 1.0) < 1e-12
+    with pytest.raises(TensorError):
+        ZRBAMetrics.compute(z.mu, z.sigma, [0.0], 0.9, idx)
