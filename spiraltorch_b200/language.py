@@ -186,3 +186,158 @@ class DesireLagrangian:
         self._step += 1
         return DesireSolution(active.tolist(), probs.tolist(), adj.tolist(), phase, t, entropy(probs.double() / probs.double().sum()),
                               weights)
+
+
+# ----------------------------------------------------------------------------------------------
+# Semantic bridge + entropic Gromov-Wasserstein alignment
+# ----------------------------------------------------------------------------------------------
+class SemanticBridge:
+    """Token -> concept coupling kept as a dense ``[V, C]`` log-probability tensor.
+
+    Parity: crates/st-nn/src/language/geometry.rs:418-760 (`log_pi`, `expectation`,
+    `infer_from_window`, marginals, anchors).  The reference stores sparse rows and scans them per
+    query; dense rows turn every query into one gather + reduction on the tensor's device.
+    """
+
+    def __init__(self, log_pi: torch.Tensor, row_marginal: torch.Tensor, col_marginal: torch.Tensor,
+                 anchors=(), epsilon: float = 1e-6):
+        if log_pi.dim() != 2 or row_marginal.shape != (log_pi.shape[0],) or col_marginal.shape != (log_pi.shape[1],):
+            raise TensorError("semantic bridge marginals must match the coupling's shape")
+        if not epsilon > 0:
+            raise TensorError("semantic bridge epsilon must be positive")
+        self.log_pi_matrix, self.row_sums, self.col_sums = log_pi.float(), row_marginal.float(), col_marginal.float()
+        self._anchors = {(int(i), int(j)) for i, j in anchors}
+        self.log_epsilon = math.log(epsilon)
+
+    @classmethod
+    def from_dense(cls, pi, anchors=(), epsilon: float = 1e-6) -> "SemanticBridge":
+        pi = torch.as_tensor(pi, dtype=torch.float32)
+        if pi.dim() != 2 or pi.numel() == 0 or not bool(torch.isfinite(pi).all()) or bool((pi < 0).any()):
+            raise TensorError("coupling must be a non-empty, finite, non-negative matrix")
+        rows, cols = pi.sum(1), pi.sum(0)
+        return cls(torch.log(pi.clamp(min=epsilon)), rows / rows.sum().clamp(min=1e-30), cols / cols.sum().clamp(min=1e-30),
+                   anchors, epsilon)
+
+    def vocab_size(self) -> int:
+        return self.log_pi_matrix.shape[0]
+
+    def concept_count(self) -> int:
+        return self.log_pi_matrix.shape[1]
+
+    def log_pi(self, token: int, concept: int) -> float:
+        if 0 <= token < self.vocab_size() and 0 <= concept < self.concept_count():
+            return float(self.log_pi_matrix[token, concept])
+        return self.log_epsilon
+
+    def anchors(self) -> set:
+        return set(self._anchors)
+
+    def row_marginal(self) -> torch.Tensor:
+        return self.row_sums
+
+    def col_marginal(self) -> torch.Tensor:
+        return self.col_sums
+
+    def expectation(self, token: int, concept_dist) -> float:
+        """Concept-weighted mean log-probability of `token`, floored at log(epsilon)."""
+        w = torch.as_tensor(concept_dist, dtype=torch.float32, device=self.log_pi_matrix.device).clamp(min=0.0)
+        w = torch.where(w > 1.1920929e-07, w, torch.zeros_like(w))
+        tot = float(w.sum())
+        if tot <= 1.1920929e-07 or not 0 <= token < self.vocab_size():
+            return self.log_epsilon
+        return max(float((w * self.log_pi_matrix[token, :w.numel()]).sum()) / tot, self.log_epsilon)
+
+    def expectations(self, concept_dist) -> torch.Tensor:
+        """`expectation` for every token at once: one matrix-vector product."""
+        w = torch.as_tensor(concept_dist, dtype=torch.float32, device=self.log_pi_matrix.device).clamp(min=0.0)
+        tot = w.sum()
+        if float(tot) <= 1.1920929e-07:
+            return torch.full((self.vocab_size(),), self.log_epsilon, device=w.device)
+        return (self.log_pi_matrix @ (w / tot)).clamp(min=self.log_epsilon)
+
+    def infer_from_window(self, window, smoothing: float = 0.0) -> torch.Tensor:
+        """Concept distribution implied by weighted tokens `[(token, weight), ...]`; uniform when the
+        window carries no mass."""
+        C = self.concept_count()
+        keep = [(t, w) for t, w in window if 0 <= t < self.vocab_size() and w > 0]
+        acc = torch.full((C,), float(smoothing), device=self.log_pi_matrix.device)
+        if keep:
+            idx = torch.tensor([t for t, _ in keep], device=acc.device)
+            wts = torch.tensor([w for _, w in keep], dtype=torch.float32, device=acc.device)
+            acc = acc + wts @ torch.exp(self.log_pi_matrix[idx])
+        tot = float(acc.sum())
+        if tot <= 1.1920929e-07:
+            return torch.full((C,), 1.0 / C, device=acc.device)
+        return (acc / tot).clamp(min=1.1920929e-07)
+
+
+def _gw_marginal(label: str, w) -> torch.Tensor:
+    w = torch.as_tensor(w, dtype=torch.float32)
+    if w.numel() == 0:
+        raise TensorError("marginals cannot be empty")
+    if not bool(torch.isfinite(w).all()) or bool((w < 0).any()):
+        raise TensorError("marginals must be finite and non-negative")
+    if float(w.sum()) <= 1.1920929e-07:
+        raise TensorError("marginal sum must be positive")
+    return w / w.sum()
+
+
+class EntropicGwSolver:
+    """Entropic Gromov-Wasserstein alignment of a symbol metric space to a concept metric space.
+
+    Parity: crates/st-nn/src/language/gw.rs:96-330 (`solve`, Sinkhorn inner loop, anchor boost, the
+    cooperative `propose` / `observe` self-tuning).  The reference evaluates the quadratic cost
+    `sum_{i',j'} (Ds[i,i'] - Dz[j,j'])^2 pi[i',j']` with four nested loops; expanding the square gives
+    `(Ds^2 a)[i] + (Dz^2 b)[j] - 2 (Ds pi Dz^T)[i,j]`, i.e. two GEMMs per outer iteration, and the
+    Sinkhorn updates are matrix-vector products — everything stays on the inputs' device.
+    """
+
+    def __init__(self, epsilon: float = 0.5, anchor_strength: float = 3.0, max_iter: int = 25, sinkhorn_iter: int = 40):
+        self.epsilon, self.anchor_strength, self.max_iter, self.sinkhorn_iter = epsilon, anchor_strength, max_iter, sinkhorn_iter
+
+    def solve(self, symbol_distances, concept_distances, symbol_marginal, concept_marginal, anchors=()) -> SemanticBridge:
+        ds = torch.as_tensor(symbol_distances, dtype=torch.float32)
+        dz = torch.as_tensor(concept_distances, dtype=torch.float32).to(ds.device)
+        if ds.dim() != 2 or ds.shape[0] != ds.shape[1] or dz.dim() != 2 or dz.shape[0] != dz.shape[1]:
+            raise TensorError("distance matrices must be square")
+        n, m = ds.shape[0], dz.shape[0]
+        a, b = _gw_marginal("gw_symbol_marginal", symbol_marginal).to(ds.device), _gw_marginal("gw_concept_marginal", concept_marginal).to(ds.device)
+        if a.numel() != n:
+            raise TensorError("symbol marginal must match symbol distance matrix")
+        if b.numel() != m:
+            raise TensorError("concept marginal must match concept distance matrix")
+        boost = torch.ones(n, m, device=ds.device)
+        anchors = [(int(i), int(j)) for i, j in anchors if 0 <= i < n and 0 <= j < m]
+        if anchors:
+            ij = torch.tensor(anchors, device=ds.device)
+            boost[ij[:, 0], ij[:, 1]] = math.exp(self.anchor_strength / self.epsilon)
+        pi = a[:, None] * b[None, :]
+        ds2, dz2 = ds * ds, dz * dz
+        for _ in range(self.max_iter):
+            cost = (ds2 @ pi.sum(1))[:, None] + (dz2 @ pi.sum(0))[None, :] - 2.0 * (ds @ pi @ dz.T)
+            kern = (torch.exp(-cost / self.epsilon) * boost).clamp(min=1e-12)
+            u, v = torch.ones(n, device=ds.device), torch.ones(m, device=ds.device)
+            for _ in range(self.sinkhorn_iter):
+                kv = kern @ v
+                u = torch.where(kv > 0, a / kv, u)
+                ku = kern.T @ u
+                v = torch.where(ku > 0, b / ku, v)
+            pi = kern * u[:, None] * v[None, :]
+        return SemanticBridge.from_dense(pi.clamp(min=0.0), anchors, epsilon=1e-6) if float(pi.sum()) > 0 else \
+            SemanticBridge.from_dense(a[:, None] * b[None, :], anchors)
+
+    # cooperative self-tuning -------------------------------------------------------------------
+    def propose(self) -> tuple:
+        """(z_bias, weight) offered to a cooperative controller."""
+        return math.tanh(self.anchor_strength - self.epsilon), max(self.anchor_strength + self.epsilon, 1e-3)
+
+    def observe(self, team_reward: float, credit: float) -> None:
+        c, r = math.tanh(credit), math.tanh(team_reward)
+        cl = lambda x, lo, hi: min(max(x, lo), hi)
+        if c >= 0:
+            self.anchor_strength = cl(self.anchor_strength * (1 + 0.12 * c), 0.5, 24.0)
+            self.epsilon = cl(self.epsilon * (1 - 0.04 * c), 1e-3, 8.0)
+        else:
+            self.anchor_strength = cl(self.anchor_strength * (1 - 0.05 * -c), 0.5, 24.0)
+            self.epsilon = cl(self.epsilon * (1 + 0.1 * -c), 1e-3, 8.0)
+        self.epsilon = cl(self.epsilon * (1 - 0.03 * r), 1e-3, 8.0)

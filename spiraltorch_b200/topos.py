@@ -298,6 +298,12 @@ class TensorBiome:
             raise TensorError(f"weight must be positive and finite, got {weight}")
         self._push(label, self.monad().lift_tensor(label, tensor).torch(), weight)
 
+    def absorb_fractal_patch(self, patch: "FractalPatch") -> None:
+        """Guard the patch's depth and relation, then absorb the relation under the patch's weight."""
+        self._topos.ensure_loop_free(patch.depth)
+        self._topos.guard_tensor("tensor_biome_fractal_patch", patch.relation())
+        self.absorb_weighted("tensor_biome_fractal_patch", patch.relation(), patch.weight)
+
     def absorb_with(self, label: str, build: Callable) -> None:
         self.absorb(label, build(self.monad()))
 
@@ -329,3 +335,123 @@ class TensorBiome:
         w = torch.tensor(self._weights, dtype=torch.float32, device=self._shoots[0].device) / tot
         acc = torch.einsum("s,sij->ij", w, torch.stack(self._shoots))
         return self.monad().rewrite_tensor("tensor_biome_canopy", acc / float(w.sum()))
+
+
+# ----------------------------------------------------------------------------------------------
+# Fractal patches and their bounded scheduler
+# ----------------------------------------------------------------------------------------------
+class FractalPatch:
+    """A relation tensor with a coherence / tension pair; its weight is `coherence / (1 + tension)`.
+
+    Parity: crates/st-tensor/src/pure/fractal.rs:40-150."""
+
+    def __init__(self, relation, coherence: float, tension: float, depth: int = 0):
+        for label, v in (("coherence", coherence), ("tension", tension)):
+            if not math.isfinite(v):
+                raise TensorError(f"non-finite value for fractal_patch_{label}: {v}")
+            if v <= 0:
+                raise TensorError(f"{label} must be positive, got {v}")
+        r = _raw(relation).float()
+        if not bool(torch.isfinite(r).all()):
+            raise TensorError("non-finite value for fractal_patch_relation")
+        self._relation, self.coherence, self.tension, self.depth = r, float(coherence), float(tension), int(depth)
+        self.weight = coherence / (1.0 + tension)
+
+    def relation(self) -> Tensor:
+        return Tensor._wrap(self._relation)
+
+    def normalized_relation(self) -> Tensor:
+        n = float(self._relation.double().norm())
+        return Tensor._wrap(torch.zeros_like(self._relation) if n == 0.0 else (self._relation.double() / n).float())
+
+
+@dataclass
+class FractalSchedulerSnapshot:
+    capacity: int
+    queued: int
+    total_weight: float
+    relation_shape: Optional[tuple]
+    oldest_depth: Optional[int]
+    newest_depth: Optional[int]
+
+    def is_empty(self) -> bool:
+        return self.queued == 0
+
+
+class UringFractalScheduler:
+    """Bounded FIFO ring of same-shaped patches, safe to share between threads; a push into a full
+    ring evicts the oldest patch, and a rejected push changes nothing.
+
+    Parity: crates/st-tensor/src/pure/fractal.rs:202-400 (`push`, `pop`, `snapshot`,
+    `fold_coherence`).  Folding stacks the queued relations and reduces them with one weighted
+    sum on the relations' device."""
+
+    def __init__(self, capacity: int):
+        import threading
+        from collections import deque
+        if capacity <= 0:
+            raise TensorError("empty input: fractal scheduler capacity")
+        self._cap, self._q, self._lock = int(capacity), deque(), threading.Lock()
+
+    def capacity(self) -> int:
+        return self._cap
+
+    def __len__(self) -> int:
+        with self._lock:
+            return len(self._q)
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+    def push(self, patch: FractalPatch) -> None:
+        with self._lock:
+            evict = max(0, len(self._q) - (self._cap - 1))
+            if len(self._q) > evict and self._q[evict]._relation.shape != patch._relation.shape:
+                raise TensorError(f"shape mismatch: {tuple(self._q[evict]._relation.shape)} vs {tuple(patch._relation.shape)}")
+            for _ in range(evict):
+                self._q.popleft()
+            self._q.append(patch)
+
+    def pop(self) -> Optional[FractalPatch]:
+        with self._lock:
+            return self._q.popleft() if self._q else None
+
+    async def push_async(self, patch: FractalPatch) -> None:
+        self.push(patch)
+
+    async def pop_async(self) -> Optional[FractalPatch]:
+        return self.pop()
+
+    def total_weight(self) -> float:
+        with self._lock:
+            return float(sum(p.weight for p in self._q))
+
+    def relation_shape(self) -> Optional[tuple]:
+        with self._lock:
+            return tuple(self._q[0]._relation.shape) if self._q else None
+
+    def snapshot(self) -> FractalSchedulerSnapshot:
+        with self._lock:
+            q = list(self._q)
+        return FractalSchedulerSnapshot(self._cap, len(q), float(sum(p.weight for p in q)),
+                                        tuple(q[0]._relation.shape) if q else None,
+                                        q[0].depth if q else None, q[-1].depth if q else None)
+
+    def fold_coherence(self) -> Tensor:
+        """Weight-normalised sum of the unit-norm relations in the ring."""
+        with self._lock:
+            q = list(self._q)
+        if not q:
+            raise TensorError("empty input: fractal scheduler queue")
+        w = torch.tensor([p.weight for p in q], dtype=torch.float64, device=q[0]._relation.device)
+        stack = torch.stack([p._relation.double() for p in q])
+        norms = stack.flatten(1).norm(dim=1).clamp(min=1e-300)
+        unit = stack / norms.reshape(-1, *([1] * (stack.dim() - 1)))
+        unit[norms <= 1e-300] = 0.0
+        return Tensor._wrap(torch.tensordot(w / w.sum(), unit, dims=1).float())
+
+    def fold_coherence_into(self, target: Tensor) -> None:
+        folded = self.fold_coherence()
+        if target.shape() != folded.shape():
+            raise TensorError(f"shape mismatch: {target.shape()} vs {folded.shape()}")
+        target.torch().copy_(folded.torch())

@@ -100,3 +100,43 @@ def test_biome_canopy_is_the_weighted_mean_under_the_guard():
     assert b.canopy().data() == before
     b.clear()
     assert b.is_empty() and b.shape() is None
+
+
+def test_fractal_scheduler_ring_and_fold():
+    import asyncio
+    from spiraltorch_b200.topos import FractalPatch, UringFractalScheduler
+    for bad in ((0.0, 1.0), (1.0, 0.0), (math.nan, 1.0)):
+        with pytest.raises(TensorError):
+            FractalPatch(torch.ones(1, 2), *bad)
+    with pytest.raises(TensorError):
+        UringFractalScheduler(0)
+    s = UringFractalScheduler(2)
+    with pytest.raises(TensorError):
+        s.fold_coherence()
+    s.push(FractalPatch(torch.tensor([[3.0, 4.0]]), 1.0, 1.0, depth=0))        # weight 0.5, unit (0.6, 0.8)
+    s.push(FractalPatch(torch.tensor([[0.0, 2.0]]), 3.0, 1.0, depth=1))        # weight 1.5, unit (0, 1)
+    assert abs(s.total_weight() - 2.0) < 1e-9 and s.relation_shape() == (1, 2)
+    assert torch.allclose(s.fold_coherence().torch(), torch.tensor([[0.25 * 0.6, 0.25 * 0.8 + 0.75]]), atol=1e-6)
+    with pytest.raises(TensorError, match="shape"):
+        s.push(FractalPatch(torch.ones(2, 2), 1.0, 1.0))
+    assert len(s) == 2                                                           # the rejected push changed nothing
+    s.push(FractalPatch(torch.tensor([[1.0, 0.0]]), 1.0, 1.0, depth=2))        # evicts depth 0
+    snap = s.snapshot()
+    assert (snap.queued, snap.oldest_depth, snap.newest_depth, snap.capacity) == (2, 1, 2, 2)
+    # a full ring of capacity 1 accepts a new shape, because the only old patch is evicted
+    one = UringFractalScheduler(1)
+    one.push(FractalPatch(torch.ones(1, 2), 1.0, 1.0))
+    one.push(FractalPatch(torch.ones(2, 2), 1.0, 1.0))
+    assert one.relation_shape() == (2, 2)
+    out = Tensor._wrap(torch.zeros(1, 2))
+    s.fold_coherence_into(out)
+    assert torch.allclose(out.torch(), s.fold_coherence().torch())
+    assert asyncio.run(s.pop_async()).depth == 1 and s.pop().depth == 2 and s.pop() is None
+    zero = FractalPatch(torch.zeros(1, 2), 1.0, 1.0)
+    assert zero.normalized_relation().data() == [0.0, 0.0]
+    # biome absorbs a patch under its weight and refuses one that is too deep
+    b = TensorBiome(OpenCartesianTopos(-1.0, 1e-6, 50.0, 2, 64))
+    b.absorb_fractal_patch(FractalPatch(torch.ones(1, 2), 3.0, 1.0, depth=1))
+    assert b.weights() == [1.5]
+    with pytest.raises(TensorError, match="loop"):
+        b.absorb_fractal_patch(FractalPatch(torch.ones(1, 2), 3.0, 1.0, depth=2))
