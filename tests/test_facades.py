@@ -745,3 +745,20 @@ def test_api_llm_runtime(tmp_path):
     assert set(cmp_["delta"]) >= {"mean_speed", "mean_latency_ms"}
     with pytest.raises(ValueError):
         L.metric_gradient_projection({}, 0)
+
+
+def test_latency_advisor_and_ztiger_gain():
+    """Parity: crates/julia-ffi-poc/src/lib.rs."""
+    import math
+    from spiraltorch_b200.advisors import ZTigerOptim, latency_score
+    assert latency_score(16, 6) == 7.0
+    with pytest.raises(RuntimeError):
+        latency_score(16, 6, engine="julia")
+    z = ZTigerOptim(0.5)
+    assert z.curvature() == -1.0 and z.gain() == 1.0
+    g = z.update(0.5, [1.0, -2.0])
+    mean = (1.0 * 0.5 + 2.0 * 1.0) / 2
+    assert abs(g - (math.tanh(mean * math.tanh(1.0) / 0.5) + 1.0)) < 1e-12
+    for _ in range(40):
+        z.update(0.5, [])
+    assert z.gain() == 1.0                                    # the 32-step window has forgotten the burst
