@@ -762,3 +762,33 @@ def test_latency_advisor_and_ztiger_gain():
     for _ in range(40):
         z.update(0.5, [])
     assert z.gain() == 1.0                                    # the 32-step window has forgotten the burst
+
+
+def test_device_caps_heuristics():
+    """Parity: crates/st-core/src/backend/device_caps.rs unit tests."""
+    from spiraltorch_b200.device_caps import DeviceCaps, DeviceCapsError, parse_backend
+    c = DeviceCaps.b200()
+    assert (c.lane_width, c.max_workgroup, c.sm_count, c.shared_mem_per_workgroup) == (32, 1024, 148, 227 * 1024)
+    assert c.align_workgroup(33) == 64 and c.align_workgroup(5000) == 1024 and c.align_workgroup(1) == 32
+    assert c.occupancy_score(0) == 0.0 and c.occupancy_score(1024) > c.occupancy_score(64)
+    assert c.recommended_workgroup() == 256 and c.recommended_workgroup(40) == 64
+    assert c.preferred_tile(100_000) == 2048 and c.preferred_tile(100, hint=100) == 128
+    t, ct = c.recommended_tiles(50304)
+    assert t == 928 and ct == 512                       # 227 KB / (8 B x 32 lanes) = 908 -> 928 after warp alignment
+    assert c.with_shared_mem(None).recommended_tiles(50304) == (16384, 512)
+    small = c.with_shared_mem(16 * 1024).recommended_tiles(50304)
+    assert small[0] == 128 and small[1] <= small[0]
+    assert c.prefers_two_stage(50304, 8) and c.prefers_two_stage(1024, 256) and not c.prefers_two_stage(1024, 8)
+    assert not c.prefers_two_stage(1024, 256, rows=64) and c.prefers_two_stage(1024, 256, rows=1024)
+    assert not DeviceCaps.cpu().prefers_two_stage(50304, 8, rows=100)
+    assert c.persistent_grid(10_000) == 148 and c.persistent_grid(10) == 10 and c.persistent_grid(10_000, 2) == 296
+    assert DeviceCaps.default_lane_quota(64) == 32 and DeviceCaps.default_lane_quota(4) == 8
+    assert parse_backend("B200") == "cuda" and parse_backend("webgpu") == "wgpu"
+    assert DeviceCaps.for_backend("cpu").backend == "cpu"
+    with pytest.raises(DeviceCapsError, match="not part of this build"):
+        DeviceCaps.for_backend("hip")
+    with pytest.raises(DeviceCapsError, match="unknown"):
+        parse_backend("tpu")
+    with pytest.raises(DeviceCapsError):
+        DeviceCaps("cuda", True, 32, 16).validate()
+    assert DeviceCaps.probe().backend in ("cpu", "cuda")
