@@ -193,3 +193,128 @@ def backend_for(op: str, default: str = "auto") -> str:
     if op not in POLICY_OPS:
         raise TensorError(f"unknown policy op '{op}'")
     return getattr(current_backend_policy(), op) or default
+
+
+# ----------------------------------------------------------------------------------------------
+# Collapse drive (crates/st-core/src/engine/collapse_drive.rs:27-305)
+# ----------------------------------------------------------------------------------------------
+import math as _math
+
+
+@dataclass
+class CollapseConfig:
+    """Thresholds of the psi-driven collapse / bloom controller.  `trend_*` and `*_deviation_*`
+    triggers are off while their thresholds are infinite."""
+    enabled: bool = False
+    hi: float = 2.0
+    lo: float = 0.3
+    hysteresis: float = 0.1
+    warmup_steps: int = 50
+    cooldown_steps: int = 10
+    collapse_scale: float = 0.2
+    collapse_max_norm: Optional[float] = 1.0
+    collapse_lr_decay: Optional[float] = 0.1
+    bloom_lr_mul: float = 1.2
+    trend_alpha: float = 0.0
+    collapse_trend_threshold: float = _math.inf
+    bloom_trend_threshold: float = -_math.inf
+    baseline_alpha: float = 0.0
+    collapse_deviation_threshold: float = _math.inf
+    bloom_deviation_threshold: float = _math.inf
+
+    @classmethod
+    def automated(cls, depth: int, band_focus: float = 0.0, drift_weight: float = 0.0) -> "CollapseConfig":
+        """Thresholds derived from a model's depth and the psi meter's band focus / drift weight."""
+        d = float(max(depth, 1))
+        cl = lambda x, lo, hi: min(max(x, lo), hi)
+        return cls(True, cl(1.4 + _math.log1p(d) * 0.6, 1.8, 4.5), cl(0.18 + 0.4 / _math.sqrt(d), 0.2, 0.6),
+                   0.08 + 0.02 * _math.log1p(d), int(cl(depth * 2, 20, 240)), int(cl(round(d / 8.0), 2, 12)),
+                   cl(0.18 + 0.9 / _math.sqrt(d), 0.1, 0.4), 1.0, 0.12, cl(1.05 + band_focus / d, 1.05, 1.6),
+                   cl(0.18 + 1.2 / _math.sqrt(d), 0.2, 0.65), cl(0.08 + band_focus / (d + 4.0), 0.06, 0.25),
+                   -(0.06 + cl(drift_weight, 0.05, 0.6)), cl(0.04 + 1.5 / (d + 6.0), 0.05, 0.3),
+                   cl(0.12 + 0.35 / _math.sqrt(d) + band_focus * 0.02, 0.12, 0.35), cl(0.1 + drift_weight * 0.3, 0.1, 0.35))
+
+
+@dataclass(frozen=True)
+class DriveCmd:
+    """`kind` is "none", "collapse" (scale gradients by `grad_scale`, clip to `max_norm`, decay the
+    learning rate by `lr_decay`) or "bloom" (multiply the learning rate by `lr_mul`)."""
+    kind: str = "none"
+    grad_scale: Optional[float] = None
+    max_norm: Optional[float] = None
+    lr_decay: Optional[float] = None
+    lr_mul: Optional[float] = None
+    due_to_trend: bool = False
+    due_to_deviation: bool = False
+
+
+_DRIVE_SCALARS = {"warmup": 0.0, "stable": 1.0, "collapse": 2.0, "bloom": 3.0}
+
+
+class CollapseDrive:
+    """State machine warmup -> stable <-> collapse / bloom over the total psi reading.
+
+    From warmup / stable: psi >= hi (or a rising trend / positive deviation from the moving baseline)
+    issues a collapse, psi <= lo (or the mirrored triggers) a bloom; either starts a cool-down of
+    `cooldown_steps` silent updates.  A collapse ends once psi <= hi - hysteresis, a bloom once
+    psi >= lo + hysteresis."""
+
+    def __init__(self, cfg: Optional[CollapseConfig] = None):
+        self.cfg = cfg or CollapseConfig()
+        self.state, self.cooldown, self.last_step = "warmup", 0, 0
+        self.prev_total: Optional[float] = None
+        self.trend, self.baseline = 0.0, None
+
+    def enabled(self) -> bool:
+        return self.cfg.enabled
+
+    def diagnostics(self) -> dict:
+        return {"state": self.state, "state_scalar": _DRIVE_SCALARS[self.state], "trend": self.trend,
+                "baseline": self.baseline, "cooldown": self.cooldown}
+
+    def update(self, total: float, step: int) -> DriveCmd:
+        c = self.cfg
+        self.last_step = step
+        if not c.enabled:
+            return DriveCmd()
+        if step < c.warmup_steps:
+            self.state = "warmup"
+            return DriveCmd()
+        if self.state == "warmup":
+            self.state = "stable"
+        if self.cooldown > 0:
+            self.cooldown -= 1
+            return DriveCmd()
+        ct = cd = bt = bd = False
+        if self.prev_total is not None:
+            delta = total - self.prev_total
+            a = min(max(c.trend_alpha, 0.0), 1.0)
+            self.trend = a * delta + (1 - a) * self.trend if a > 0 else delta
+            b = min(max(c.baseline_alpha, 0.0), 1.0)
+            if b > 0:
+                base = self.prev_total if self.baseline is None else self.baseline
+                self.baseline = (1 - b) * base + b * total
+                dev = total - self.baseline
+                cd = _math.isfinite(c.collapse_deviation_threshold) and dev >= c.collapse_deviation_threshold
+                bd = _math.isfinite(c.bloom_deviation_threshold) and dev <= -c.bloom_deviation_threshold
+            else:
+                self.baseline = total
+            ct = _math.isfinite(c.collapse_trend_threshold) and self.trend >= c.collapse_trend_threshold
+            bt = _math.isfinite(c.bloom_trend_threshold) and self.trend <= c.bloom_trend_threshold
+        else:
+            self.baseline, self.trend = total, 0.0
+        self.prev_total = total
+        if self.state in ("warmup", "stable"):
+            if total >= c.hi or ct or cd:
+                self.state, self.cooldown = "collapse", c.cooldown_steps
+                return DriveCmd("collapse", c.collapse_scale, c.collapse_max_norm, c.collapse_lr_decay, None, ct, cd)
+            if total <= c.lo or bt or bd:
+                self.state, self.cooldown = "bloom", c.cooldown_steps
+                return DriveCmd("bloom", lr_mul=c.bloom_lr_mul, due_to_trend=bt, due_to_deviation=bd)
+        elif self.state == "collapse":
+            if total <= c.hi - c.hysteresis:
+                self.state = "stable"
+        elif self.state == "bloom":
+            if total >= c.lo + c.hysteresis:
+                self.state = "stable"
+        return DriveCmd()

@@ -594,3 +594,134 @@ class AtlasRouteSummary:
                 "latest_z_signal": self.latest_z_signal, "z_signal_trend": self.z_signal_trend,
                 "script_hint": self.script_hint, "total_notes": self.total_notes, "latest_notes": self.latest_notes,
                 "districts": self.districts, "beacons": self.beacons(8), "flux": self.flux()}
+
+
+# ----------------------------------------------------------------------------------------------
+# Dashboard frames (crates/st-core/src/telemetry/dashboard.rs:13-400)
+# ----------------------------------------------------------------------------------------------
+SEVERITIES = ("info", "warning", "critical")
+
+
+@dataclass
+class DashboardMetric:
+    name: str
+    value: float
+    unit: Optional[str] = None
+    trend: Optional[float] = None
+
+    def with_unit(self, unit: str) -> "DashboardMetric":
+        self.unit = unit
+        return self
+
+    def with_trend(self, trend: float) -> "DashboardMetric":
+        self.trend = float(trend)
+        return self
+
+
+@dataclass
+class DashboardEvent:
+    message: str
+    severity: str = "info"
+
+    def __post_init__(self):
+        if self.severity not in SEVERITIES:
+            raise ValueError(f"unknown severity {self.severity!r}; expected one of {SEVERITIES}")
+
+
+@dataclass
+class DashboardFrame:
+    timestamp: float
+    metrics: list = field(default_factory=list)
+    events: list = field(default_factory=list)
+
+    def push_metric(self, metric: DashboardMetric) -> None:
+        self.metrics.append(metric)
+
+    def push_event(self, event: DashboardEvent) -> None:
+        self.events.append(event)
+
+
+@dataclass
+class MetricAggregate:
+    name: str
+    mean: float
+    min: float
+    max: float
+    latest: float
+    samples: int
+
+
+@dataclass
+class DashboardSummary:
+    frame_count: int
+    span_seconds: float
+    metrics: list
+    events: dict
+
+    def is_empty(self) -> bool:
+        return self.frame_count == 0
+
+    def top_metric(self) -> Optional[MetricAggregate]:
+        """The metric with the widest range over the summarised frames (ties: the later name)."""
+        return max(self.metrics, key=lambda m: (abs(m.max - m.min), m.name), default=None)
+
+
+class DashboardRing:
+    """Bounded history of frames; `summarize(limit)` aggregates the newest `limit` frames per metric
+    name (mean / min / max / latest / samples) and counts events per severity."""
+
+    def __init__(self, capacity: int):
+        from collections import deque
+        self.capacity = max(int(capacity), 1)
+        self._frames = deque(maxlen=self.capacity)
+
+    def push(self, frame: DashboardFrame) -> None:
+        self._frames.append(frame)
+
+    def latest(self) -> Optional[DashboardFrame]:
+        return self._frames[-1] if self._frames else None
+
+    def __len__(self) -> int:
+        return len(self._frames)
+
+    def __iter__(self):
+        return iter(self._frames)
+
+    def summarize(self, limit: Optional[int] = None) -> Optional[DashboardSummary]:
+        if not self._frames:
+            return None
+        take = list(self._frames)[-max(limit or len(self._frames), 1):][::-1]          # newest first
+        acc, events = {}, {}
+        for f in take:
+            for m in f.metrics:
+                a = acc.setdefault(m.name, {"latest": m.value, "sum": 0.0, "min": m.value, "max": m.value, "n": 0})
+                a["sum"] += m.value
+                a["n"] += 1
+                a["min"], a["max"] = min(a["min"], m.value), max(a["max"], m.value)
+            for e in f.events:
+                events[e.severity] = events.get(e.severity, 0) + 1
+        metrics = [MetricAggregate(k, a["sum"] / a["n"], a["min"], a["max"], a["latest"], a["n"]) for k, a in sorted(acc.items())]
+        return DashboardSummary(len(take), abs(take[0].timestamp - take[-1].timestamp), metrics, events)
+
+
+class DashboardBuilder:
+    """Collects the metrics / events of one frame; `finish_with_latency` adds `frame_latency_ms`."""
+
+    def __init__(self, start: Optional[float] = None):
+        import time
+        self._clock = time.time
+        self._start = self._clock() if start is None else float(start)
+        self._metrics, self._events = [], []
+
+    def record_metric(self, metric: DashboardMetric) -> None:
+        self._metrics.append(metric)
+
+    def record_event(self, message: str, severity: str = "info") -> None:
+        self._events.append(DashboardEvent(message, severity))
+
+    def finish(self) -> DashboardFrame:
+        return DashboardFrame(self._start, self._metrics, self._events)
+
+    def finish_with_latency(self) -> DashboardFrame:
+        self._metrics.append(DashboardMetric("frame_latency_ms", (self._clock() - self._start) * 1e3, "ms"))
+        return self.finish()

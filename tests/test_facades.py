@@ -792,3 +792,53 @@ def test_device_caps_heuristics():
     with pytest.raises(DeviceCapsError):
         DeviceCaps("cuda", True, 32, 16).validate()
     assert DeviceCaps.probe().backend in ("cpu", "cuda")
+
+
+def test_collapse_drive_transitions_and_cooldown():
+    """Parity: crates/st-core/src/engine/collapse_drive.rs `transitions_and_cooldown` and trend tests."""
+    from spiraltorch_b200.engine import CollapseConfig, CollapseDrive
+    d = CollapseDrive(CollapseConfig(enabled=True, hi=2.0, lo=0.5, warmup_steps=0, cooldown_steps=2))
+    assert d.update(0.6, 1).kind == "none"
+    cmd = d.update(2.2, 2)
+    assert cmd.kind == "collapse" and cmd.grad_scale == 0.2 and cmd.max_norm == 1.0 and cmd.lr_decay == 0.1
+    assert [d.update(1.8, s).kind for s in (3, 4, 5)] == ["none"] * 3 and d.state == "stable"
+    cmd = d.update(0.3, 6)
+    assert cmd.kind == "bloom" and cmd.lr_mul == 1.2 and d.diagnostics()["state_scalar"] == 3.0
+    assert not CollapseDrive().enabled() and CollapseDrive().update(100.0, 1000).kind == "none"
+    w = CollapseDrive(CollapseConfig(enabled=True, warmup_steps=5))
+    assert w.update(100.0, 1).kind == "none" and w.state == "warmup"
+    # a rising trend collapses before psi reaches `hi`
+    t = CollapseDrive(CollapseConfig(enabled=True, hi=10.0, lo=-10.0, warmup_steps=0, cooldown_steps=0,
+                                     trend_alpha=1.0, collapse_trend_threshold=0.5))
+    assert t.update(1.0, 1).kind == "none"
+    cmd = t.update(1.7, 2)
+    assert cmd.kind == "collapse" and cmd.due_to_trend and not cmd.due_to_deviation
+    auto = CollapseConfig.automated(24, band_focus=0.5, drift_weight=0.1)
+    assert auto.enabled and 1.8 <= auto.hi <= 4.5 and 0.2 <= auto.lo <= 0.6 and auto.warmup_steps == 48 and auto.cooldown_steps == 3
+
+
+def test_dashboard_ring_summary():
+    """Parity: crates/st-core/src/telemetry/dashboard.rs tests."""
+    from spiraltorch_b200.telemetry import (DashboardBuilder, DashboardEvent, DashboardFrame, DashboardMetric, DashboardRing)
+    ring = DashboardRing(3)
+    assert ring.summarize() is None
+    for i in range(5):
+        f = DashboardFrame(float(i))
+        f.push_metric(DashboardMetric("loss", 10.0 - i).with_unit("nats").with_trend(-1))
+        if i % 2 == 0:
+            f.push_metric(DashboardMetric("lr", 0.1))
+            f.push_event(DashboardEvent("tick", "warning"))
+        ring.push(f)
+    assert len(ring) == 3 and ring.latest().timestamp == 4.0
+    s = ring.summarize()
+    loss = next(m for m in s.metrics if m.name == "loss")
+    assert (s.frame_count, s.span_seconds) == (3, 2.0) and s.events == {"warning": 2}
+    assert (loss.mean, loss.min, loss.max, loss.latest, loss.samples) == (7.0, 6.0, 8.0, 6.0, 3)
+    assert s.top_metric().name == "loss" and ring.summarize(1).frame_count == 1 and not s.is_empty()
+    with pytest.raises(ValueError):
+        DashboardEvent("x", "fatal")
+    b = DashboardBuilder()
+    b.record_metric(DashboardMetric("a", 1.0))
+    b.record_event("hello")
+    fr = b.finish_with_latency()
+    assert [m.name for m in fr.metrics] == ["a", "frame_latency_ms"] and fr.events[0].severity == "info"
