@@ -370,3 +370,190 @@ def score_with_free_energy(loss_before: float, loss_after: float, step_ms: float
         return r.utility - r.components["prior_band_potential"]
     except FreeEnergyError:
         return -math.inf
+
+
+# ----------------------------------------------------------------------------------------------
+# Z-space generation control (crates/st-core/src/inference/generation_control.rs:88-700)
+# ----------------------------------------------------------------------------------------------
+class ZSpaceGenerationControlError(ValueError):
+    pass
+
+
+_LOG_FLOOR, _ADJ_MIN, _ADJ_MAX = 1e-12, 0.25, 4.0
+
+
+@dataclass
+class ZSpaceSoftmaxConfig:
+    """Softmax at scale `sqrt(-curvature) / T`; with an entropy target, `T` is multiplied once by
+    `clamp(1 + gain * (target - H), 0.25, 4)` and clamped to `[min_temperature, max_temperature]`."""
+    curvature: float
+    temperature: float
+    min_temperature: Optional[float] = None
+    max_temperature: Optional[float] = None
+    entropy_target: Optional[float] = None
+    entropy_tolerance: float = 1e-4
+    entropy_gain: float = 0.5
+
+    def __post_init__(self):
+        if not math.isfinite(self.curvature) or self.curvature >= 0:
+            raise ZSpaceGenerationControlError("curvature must be finite and negative")
+        if not math.isfinite(self.temperature) or self.temperature <= 0:
+            raise ZSpaceGenerationControlError("temperature must be finite and positive")
+        if self.min_temperature is None:
+            self.min_temperature = max(self.temperature * 0.1, 1e-3)
+        if self.max_temperature is None:
+            self.max_temperature = self.temperature * 10.0
+        if not 0 < self.min_temperature <= self.max_temperature:
+            raise ZSpaceGenerationControlError("temperature bounds must satisfy 0 < min <= max")
+        if self.entropy_target is not None and (not math.isfinite(self.entropy_target) or self.entropy_target < 0):
+            raise ZSpaceGenerationControlError("entropy_target must be finite and >= 0")
+        if self.entropy_tolerance < 0 or self.entropy_gain < 0:
+            raise ZSpaceGenerationControlError("entropy tolerance and gain must be >= 0")
+
+    def fixed_temperature(self) -> float:
+        return min(max(self.temperature, self.min_temperature), self.max_temperature)
+
+    def curvature_scale(self) -> float:
+        return math.sqrt(-self.curvature)
+
+
+@dataclass
+class ZSpaceSoftmaxProjection:
+    probabilities: torch.Tensor
+    base_probabilities: torch.Tensor
+    entropy: float
+    base_entropy: float
+    effective_temperature: float
+    base_temperature: float
+    adaptive_temperature: bool
+    temperature_gradient_active: bool
+    scale: float
+    base_scale: float
+
+
+def zspace_entropy(p: torch.Tensor) -> float:
+    p = torch.as_tensor(p, dtype=torch.float64)
+    if not bool(torch.isfinite(p).all()) or bool(((p < 0) | (p > 1)).any()):
+        raise ZSpaceGenerationControlError("probability must lie in [0, 1]")
+    return float(-(p * torch.log(p.clamp(min=_LOG_FLOOR))).sum())
+
+
+def project_zspace_softmax(logits, config: ZSpaceSoftmaxConfig) -> ZSpaceSoftmaxProjection:
+    x = torch.as_tensor(logits, dtype=torch.float64)
+    if not bool(torch.isfinite(x).all()):
+        raise ZSpaceGenerationControlError("logit must be finite")
+    t0 = config.fixed_temperature()
+    s0 = config.curvature_scale() / t0
+    base = torch.softmax(x * s0, -1)
+    h0 = zspace_entropy(base) if x.numel() else 0.0
+    t, adaptive, grad_active = t0, False, False
+    if config.entropy_target is not None:
+        delta = config.entropy_target - h0
+        if abs(delta) > config.entropy_tolerance:
+            raw_adj = 1.0 + config.entropy_gain * delta
+            raw_t = t0 * min(max(raw_adj, _ADJ_MIN), _ADJ_MAX)
+            t = min(max(raw_t, config.min_temperature), config.max_temperature)
+            adaptive = True
+            grad_active = (config.entropy_gain > 0 and _ADJ_MIN < raw_adj < _ADJ_MAX
+                           and config.min_temperature < raw_t < config.max_temperature)
+    s = config.curvature_scale() / t
+    p = torch.softmax(x * s, -1) if adaptive else base.clone()
+    return ZSpaceSoftmaxProjection(p, base, zspace_entropy(p) if adaptive and x.numel() else h0, h0, t, t0, adaptive,
+                                   grad_active, s, s0)
+
+
+@dataclass
+class ZSpaceGenerationControlConfig:
+    curvature: float = -0.04
+    temperature: float = 1.0
+    entropy_target: Optional[float] = None
+    entropy_tolerance: float = 1e-4
+    entropy_gain: float = 0.5
+    min_temperature: Optional[float] = None
+    max_temperature: Optional[float] = None
+    repression_window: int = 32
+    repression_strength: float = 1.0
+    last_token_repression: float = 0.5
+    ngram_size: int = 0
+    ngram_window: int = 0
+    ngram_repression_strength: float = 0.0
+    ngram_decay: float = 1.0
+
+    def softmax_config(self) -> ZSpaceSoftmaxConfig:
+        for name in ("repression_strength", "last_token_repression", "ngram_repression_strength"):
+            v = getattr(self, name)
+            if not math.isfinite(v) or v < 0:
+                raise ZSpaceGenerationControlError(f"{name} must be finite and >= 0")
+        if not math.isfinite(self.ngram_decay) or not 0 < self.ngram_decay <= 1:
+            raise ZSpaceGenerationControlError("ngram_decay must lie in (0, 1]")
+        return ZSpaceSoftmaxConfig(self.curvature, self.temperature, self.min_temperature, self.max_temperature,
+                                   self.entropy_target, self.entropy_tolerance, self.entropy_gain)
+
+
+@dataclass
+class ZSpaceGenerationControlPayload:
+    token_ids: list
+    adjusted_logits: torch.Tensor
+    probabilities: torch.Tensor
+    log_probabilities: torch.Tensor
+    repression_penalties: torch.Tensor
+    ngram_repression_penalties: torch.Tensor
+    projection: ZSpaceSoftmaxProjection
+    before_top_token: Optional[int]
+    after_top_token: Optional[int]
+    top_changed: bool
+    repressed_token_count: int
+    ngram_repressed_token_count: int
+    max_repression: float
+    kind: str = "spiraltorch.zspace_generation_control"
+    contract_version: str = "v1"
+
+
+def _ngram_continuations(history: Sequence[int], n: int, decay: float) -> dict:
+    """token -> sum of decay^distance over earlier occurrences of the current (n-1)-prefix followed by it."""
+    if n <= 1 or len(history) < n:
+        return {}
+    k = n - 1
+    prefix, latest = list(history[-k:]), len(history) - n
+    out: dict = {}
+    for start in range(latest + 1):
+        if list(history[start:start + k]) == prefix:
+            tok = history[start + k]
+            out[tok] = out.get(tok, 0.0) + decay ** (latest - start)
+    return out
+
+
+def apply_zspace_generation_control(logits, token_ids: Sequence[int], recent_tokens: Sequence[int],
+                                    config: Optional[ZSpaceGenerationControlConfig] = None) -> ZSpaceGenerationControlPayload:
+    """Repetition / n-gram repression of candidate logits followed by the Z-space softmax.
+
+    A candidate's logit drops by `repression_strength * count(token in the last repression_window)`,
+    by `last_token_repression` if it repeats the last token, and by `ngram_repression_strength` times
+    the decayed count of times it already completed the current (n-1)-gram."""
+    cfg = config or ZSpaceGenerationControlConfig()
+    x = torch.as_tensor(logits, dtype=torch.float64)
+    ids = [int(t) for t in token_ids]
+    if x.numel() != len(ids):
+        raise ZSpaceGenerationControlError(f"candidate length mismatch: {x.numel()} logits, {len(ids)} token ids")
+    if not bool(torch.isfinite(x).all()):
+        raise ZSpaceGenerationControlError("logit must be finite")
+    soft = cfg.softmax_config()
+    recent = [int(t) for t in recent_tokens]
+    hist = recent[max(0, len(recent) - cfg.repression_window):] if cfg.repression_window > 0 else []
+    counts: dict = {}
+    for t in hist:
+        counts[t] = counts.get(t, 0) + 1
+    last = hist[-1] if hist else None
+    win = cfg.ngram_window or cfg.repression_window
+    cont = _ngram_continuations(recent[max(0, len(recent) - win):], cfg.ngram_size, cfg.ngram_decay) \
+        if cfg.ngram_repression_strength > 0 else {}
+    ngram = torch.tensor([cfg.ngram_repression_strength * cont.get(t, 0.0) for t in ids], dtype=torch.float64)
+    pen = torch.tensor([cfg.repression_strength * counts.get(t, 0) + (cfg.last_token_repression if t == last else 0.0)
+                        for t in ids], dtype=torch.float64) + ngram
+    adj = x.cpu() - pen
+    proj = project_zspace_softmax(adj, soft)
+    before = ids[int(x.argmax())] if ids else None
+    after = ids[int(adj.argmax())] if ids else None
+    return ZSpaceGenerationControlPayload(ids, adj, proj.probabilities, torch.log(proj.probabilities.clamp(min=_LOG_FLOOR)),
+                                          pen, ngram, proj, before, after, before != after, int((pen > 0).sum()),
+                                          int((ngram > 0).sum()), float(pen.max()) if ids else 0.0)

@@ -842,3 +842,20 @@ def test_dashboard_ring_summary():
     b.record_event("hello")
     fr = b.finish_with_latency()
     assert [m.name for m in fr.metrics] == ["a", "frame_latency_ms"] and fr.events[0].severity == "info"
+
+
+def test_temporal_spectral_fusion_of_a_lane_window():
+    """Parity: crates/st-core/src/backend/temporal_fusion.rs tests."""
+    import math
+    from spiraltorch_b200.advisors import LaneWindow, TemporalSpectralFusion
+    w = LaneWindow(target=64, lower=32, upper=128, stride=32)
+    assert w.lanes() == [32, 64, 96, 128] and LaneWindow(8, 8, 8).lanes() == [8]
+    f = TemporalSpectralFusion.analyse(w, rows=1024, cols=4096, k=64, lanes=32)
+    base = 0.5 * math.log1p(32) + 0.25 * math.log1p(128)
+    assert abs(float(f.temporal[0]) - (math.log1p(2.0) + base)) < 1e-5 and f.temporal.numel() == 4
+    assert f.spectral.numel() == 2 and f.fusion.shape == (2, 4)
+    assert abs(float(f.spectral[0]) - float(f.temporal.sum())) < 1e-4          # bin 0 is the plain sum
+    assert torch.allclose(f.fusion[1], f.spectral[1] * f.temporal)
+    assert f.dominant_frequency == 0.0 and 0.5 < f.tempo_hint <= 1.0 and f.spectral_energy > 0
+    big = TemporalSpectralFusion.analyse(LaneWindow(64, 1, 64), 8, 8, 4, 32)
+    assert big.temporal.numel() == 64 and big.spectral.numel() == 8

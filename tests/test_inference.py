@@ -93,3 +93,44 @@ def test_free_energy_prior_cases_and_score():
     assert good > bad
     assert abs(good - (0.5 - 0.025 - 0.1 - 0.02 + 0.1)) < 1e-12
     assert score_with_free_energy(1.0, 0.5, 10.0, 100.0, 0.0, BandEnergy(1, 0, 0), 0.2, -1.0) == -math.inf
+
+
+def test_zspace_softmax_projection_and_entropy_target():
+    from spiraltorch_b200.inference import (ZSpaceGenerationControlError, ZSpaceSoftmaxConfig, project_zspace_softmax,
+                                            zspace_entropy)
+    logits = [2.0, 1.0, 0.0]
+    p = project_zspace_softmax(logits, ZSpaceSoftmaxConfig(-4.0, 2.0))
+    assert abs(p.base_scale - 1.0) < 1e-12 and not p.adaptive_temperature
+    assert torch.allclose(p.probabilities, torch.softmax(torch.tensor(logits, dtype=torch.float64), -1))
+    hot = project_zspace_softmax(logits, ZSpaceSoftmaxConfig(-4.0, 2.0, entropy_target=1.09))
+    assert hot.adaptive_temperature and hot.effective_temperature > 2.0 and hot.entropy > p.entropy
+    assert hot.temperature_gradient_active
+    cold = project_zspace_softmax(logits, ZSpaceSoftmaxConfig(-4.0, 2.0, entropy_target=0.0, entropy_gain=10.0))
+    assert cold.effective_temperature == 0.5 and not cold.temperature_gradient_active     # adjust clamped to 0.25
+    assert abs(zspace_entropy([0.5, 0.5]) - math.log(2)) < 1e-12
+    for bad in ((0.5, 1.0), (-1.0, 0.0)):
+        with pytest.raises(ZSpaceGenerationControlError):
+            ZSpaceSoftmaxConfig(*bad)
+    with pytest.raises(ZSpaceGenerationControlError):
+        project_zspace_softmax([math.nan], ZSpaceSoftmaxConfig(-1.0, 1.0))
+
+
+def test_generation_control_represses_repeats_and_ngrams():
+    from spiraltorch_b200.inference import (ZSpaceGenerationControlConfig, ZSpaceGenerationControlError,
+                                            apply_zspace_generation_control)
+    out = apply_zspace_generation_control([3.0, 2.9, 0.0], [7, 8, 9], [1, 7, 7])
+    assert out.repression_penalties.tolist() == [2.5, 0.0, 0.0] and out.before_top_token == 7 and out.after_top_token == 8
+    assert out.top_changed and out.repressed_token_count == 1 and abs(float(out.probabilities.sum()) - 1) < 1e-12
+    assert torch.allclose(out.log_probabilities.exp(), out.probabilities)
+    # the window bounds what is counted
+    short = apply_zspace_generation_control([1.0], [7], [7, 7, 7, 1], ZSpaceGenerationControlConfig(repression_window=2))
+    assert short.repression_penalties.tolist() == [1.0]
+    # "1 2 3 ... 1 2" -> completing with 3 is an n-gram repeat; decay weights older matches less
+    cfg = ZSpaceGenerationControlConfig(repression_strength=0.0, last_token_repression=0.0, ngram_size=3,
+                                        ngram_repression_strength=2.0, ngram_decay=0.5)
+    ng = apply_zspace_generation_control([1.0, 1.0], [3, 4], [1, 2, 3, 5, 1, 2, 3, 1, 2], cfg)
+    assert ng.ngram_repression_penalties.tolist() == [2.0 * (0.5 ** 2 + 0.5 ** 6), 0.0] and ng.after_top_token == 4
+    with pytest.raises(ZSpaceGenerationControlError, match="mismatch"):
+        apply_zspace_generation_control([1.0, 2.0], [1], [])
+    with pytest.raises(ZSpaceGenerationControlError):
+        apply_zspace_generation_control([1.0], [1], [], ZSpaceGenerationControlConfig(ngram_decay=0.0))
