@@ -34,6 +34,8 @@ struct AttnFwdParams {
   float scale_log2;            // softmax scale * log2(e)
   int causal;
   unsigned* err;
+  int n_q;       // query tiles per (batch, head)
+  int n_items;   // n_q * H * B work items, heaviest (latest) query tiles first
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -82,19 +84,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 9;      // 2
   uint64_t* p_full = bars + 11;     // 2 (256 arrivals)
   uint64_t* pv_full = bars + 13;    // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* q_empty = bars + 15;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);  // [2 buffers][2 halves][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int q0 = q_tile * BLK;
-  int n_kv = (p.Sk + BLK - 1) / BLK;
-  if (p.causal) n_kv = min(n_kv, q_tile + 1);
+  // Work item w -> (query tile, head, batch); tiles with the most KV work come first so that the
+  // static round-robin over CTAs stays balanced.
+  const int hb = p.H * p.B;
+  auto item_at = [&](int w, int& q_tile, int& h, int& b, int& n_kv) {
+    q_tile = p.n_q - 1 - w / hb;
+    const int rem = w % hb;
+    h = rem % p.H;
+    b = rem / p.H;
+    n_kv = (p.Sk + BLK - 1) / BLK;
+    if (p.causal) n_kv = min(n_kv, q_tile + 1);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
+    mbar_init(smem_u32(q_empty), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&k_full[i]), 1);
       mbar_init(smem_u32(&v_full[i]), 1);
@@ -122,28 +132,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 8) {
     // ---------------------------- TMA producer -----------------------------------------
     if (lane == 0) {
-      const uint32_t qb = smem_u32(q_full);
-      mbar_arrive_expect_tx(qb, L::TILE);
-#pragma unroll
-      for (int kb = 0; kb < KB; ++kb)
-        tma_load_4d(smem_u32(smem + L::Q_OFF + kb * (BLK * 128)), &tmQ, qb, kb * 64, h, q0, b);
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&k_empty[st]), ph ^ 1u, abort_flag)) break;
-        const uint32_t kf = smem_u32(&k_full[st]);
-        mbar_arrive_expect_tx(kf, L::TILE);
-#pragma unroll
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem_u32(smem + L::K_OFF + st * L::TILE + kb * (BLK * 128)), &tmK, kf,
-                      kb * 64, h, j * BLK, b);
-        if (!mbar_wait(smem_u32(&v_empty[st]), ph ^ 1u, abort_flag)) break;
-        const uint32_t vf = smem_u32(&v_full[st]);
-        mbar_arrive_expect_tx(vf, L::TILE);
+      int g = 0;  // KV tiles loaded so far, over all work items: ring stage g & 1
+      int it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        int q_tile, h, b, n_kv;
+        item_at(w, q_tile, h, b, n_kv);
+        if (n_kv <= 0) continue;
+        // the single Q buffer is free once the previous item's last QK^T has completed
+        if (it > 0 && !mbar_wait(smem_u32(q_empty), (it - 1) & 1, abort_flag)) break;
+        const uint32_t qb = smem_u32(q_full);
+        mbar_arrive_expect_tx(qb, L::TILE);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem_u32(smem + L::V_OFF + st * L::TILE + kb * (BLK * 128)), &tmV, vf,
-                      kb * 64, h, j * BLK, b);
+          tma_load_4d(smem_u32(smem + L::Q_OFF + kb * (BLK * 128)), &tmQ, qb, kb * 64, h, q_tile * BLK, b);
+        for (int j = 0; j < n_kv; ++j, ++g) {
+          const int st = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          if (!mbar_wait(smem_u32(&k_empty[st]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t kf = smem_u32(&k_full[st]);
+          mbar_arrive_expect_tx(kf, L::TILE);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem_u32(smem + L::K_OFF + st * L::TILE + kb * (BLK * 128)), &tmK, kf,
+                        kb * 64, h, j * BLK, b);
+          if (!mbar_wait(smem_u32(&v_empty[st]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t vf = smem_u32(&v_full[st]);
+          mbar_arrive_expect_tx(vf, L::TILE);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem_u32(smem + L::V_OFF + st * L::TILE + kb * (BLK * 128)), &tmV, vf,
+                        kb * 64, h, j * BLK, b);
+        }
+        ++it;
       }
     }
   } else if (warp == 9) {
@@ -152,13 +173,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(BLK, D, false, true);
       const uint32_t sq = smem_u32(smem + L::Q_OFF);
-      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
-      auto issue_qk = [&](int jj) -> bool {
-        const int st = jj & 1;
-        if (!mbar_wait(smem_u32(&k_full[st]), (jj >> 1) & 1, abort_flag)) return false;
+      // gg: KV tile index over all work items (ring stage, S / PV buffer and barrier phase)
+      auto issue_qk = [&](int gg, bool last_of_item) -> bool {
+        const int st = gg & 1;
+        if (!mbar_wait(smem_u32(&k_full[st]), (gg >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::K_OFF + st * L::TILE);
-        const uint32_t d_tmem = tmem_base + S_COL + (jj & 1) * BLK;
+        const uint32_t d_tmem = tmem_base + S_COL + st * BLK;
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
@@ -167,33 +188,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint64_t db = make_smem_desc_sw128(sk + kb * (BLK * 128) + k * 32, 16, 1024);
             umma_bf16_ss(d_tmem, da, db, idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
-        umma_commit(smem_u32(&s_full[jj & 1]));
+        umma_commit(smem_u32(&s_full[st]));
         umma_commit(smem_u32(&k_empty[st]));
+        if (last_of_item) umma_commit(smem_u32(q_empty));
         return true;
       };
-      if (ok && n_kv > 0) ok = issue_qk(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          ok = issue_qk(j + 1);
-          if (!ok) break;
-        }
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&p_full[st]), ph, abort_flag)) break;
-        if (!mbar_wait(smem_u32(&v_full[st]), ph, abort_flag)) break;
-        tc_fence_after();
-        const uint32_t sp = smem_u32(smem + L::P_OFF + st * L::P_TILE);
-        const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
-        const uint32_t d_tmem = tmem_base + PV_COL + st * D;
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        int q_tile, h, b, n_kv;
+        item_at(w, q_tile, h, b, n_kv);
+        if (n_kv <= 0) continue;
+        ok = mbar_wait(smem_u32(q_full), it & 1, abort_flag);
+        if (ok) ok = issue_qk(g, n_kv == 1);
+        for (int j = 0; j < n_kv && ok; ++j, ++g) {
+          if (j + 1 < n_kv) {
+            ok = issue_qk(g + 1, j + 2 == n_kv);
+            if (!ok) break;
+          }
+          const int st = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          if (!mbar_wait(smem_u32(&p_full[st]), ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&v_full[st]), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sp = smem_u32(smem + L::P_OFF + st * L::P_TILE);
+          const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::TILE);
+          const uint32_t d_tmem = tmem_base + PV_COL + st * D;
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk) {
-          // A = P (K-major, two 64-column blocks); B = V (MN-major: D contiguous, KV rows = K)
-          const uint64_t da = make_smem_desc_sw128(sp + (kk >> 2) * (BLK * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sv + kk * (16 * 128), BLK * 128, 1024);
-          umma_bf16_ss(d_tmem, da, db, idesc_pv, kk != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BLK / 16; ++kk) {
+            // A = P (K-major, two 64-column blocks); B = V (MN-major: D contiguous, KV rows = K)
+            const uint64_t da = make_smem_desc_sw128(sp + (kk >> 2) * (BLK * 128) + (kk & 3) * 32, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sv + kk * (16 * 128), BLK * 128, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc_pv, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&pv_full[st]));
+          umma_commit(smem_u32(&v_empty[st]));
         }
-        umma_commit(smem_u32(&pv_full[st]));
-        umma_commit(smem_u32(&v_empty[st]));
+        ++it;
       }
     }
   } else {
@@ -201,13 +232,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int quad = warp & 3;
     const int half = warp >> 2;
     const int r = quad * 32 + lane;
-    const int row_g = q0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
-    float o[DH];
-#pragma unroll
-    for (int c = 0; c < DH; ++c) o[c] = 0.0f;
+    float2 o[DH / 2];
     bool ok = true;
+    int g0 = 0;  // KV tiles consumed by earlier work items (S / P / PV buffer index and barrier phase)
 
     auto accumulate = [&](int jj, float a) -> bool {
       const int pb = jj & 1;
@@ -218,15 +246,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t t[32];
         tmem_ld_32x32(tmem_base + lane_off + PV_COL + pb * D + half * DH + ch * 32, t);
         tmem_ld_wait();
+        const float2 a2 = make_float2(a, a);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[ch * 32 + c] = o[ch * 32 + c] * a + __uint_as_float(t[c]);
+        for (int c = 0; c < 16; ++c)
+          o[ch * 16 + c] = fma2(o[ch * 16 + c], a2,
+                                make_float2(__uint_as_float(t[2 * c]), __uint_as_float(t[2 * c + 1])));
       }
       return true;
     };
 
+    for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+    int q_tile, h, b, n_kv;
+    item_at(w, q_tile, h, b, n_kv);
+    const int q0 = q_tile * BLK;
+    const int row_g = q0 + r;
+    float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
+#pragma unroll
+    for (int c = 0; c < DH / 2; ++c) o[c] = make_float2(0.0f, 0.0f);
+
     for (int j = 0; j < n_kv; ++j) {
-      const int buf = j & 1;
-      if (!mbar_wait_warp(smem_u32(&s_full[buf]), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      const int gj = g0 + j;
+      const int buf = gj & 1;
+      if (!mbar_wait_warp(smem_u32(&s_full[buf]), (gj >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t sr[64];
       {
@@ -251,8 +292,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           mx = fmaxf(mx, s);
         }
       } else {
+        float mx1 = -INFINITY;   // two chains of three-input maxima
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+        for (int c = 0; c < 64; c += 4) {
+          mx = max3(mx, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+        }
+        mx = fmaxf(mx, mx1);
       }
       float* xb = xch + buf * (2 * BLK);
       xb[half * BLK + r] = mx;
@@ -261,21 +307,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = fast_exp2(m - m_safe);
-      float rs = 0.0f;
       uint8_t* pt = smem + L::P_OFF + buf * L::P_TILE + half * (BLK * 128);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-m_safe, -m_safe);
+      float2 rs2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
-        float e[8];
+        float2 e[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          e[q] = fast_exp2(__uint_as_float(sr[c8 * 8 + q]) * p.scale_log2 - m_safe);
-          rs += e[q];
+        for (int q = 0; q < 4; ++q) {
+          const float2 x = fma2(make_float2(__uint_as_float(sr[c8 * 8 + 2 * q]),
+                                            __uint_as_float(sr[c8 * 8 + 2 * q + 1])), sc2, nm2);
+          e[q] = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          rs2[q & 1] = add2(rs2[q & 1], e[q]);
         }
         uint4 u;
-        u.x = pack_bf16x2(e[0], e[1]); u.y = pack_bf16x2(e[2], e[3]);
-        u.z = pack_bf16x2(e[4], e[5]); u.w = pack_bf16x2(e[6], e[7]);
+        u.x = pack_bf16x2(e[0].x, e[0].y); u.y = pack_bf16x2(e[1].x, e[1].y);
+        u.z = pack_bf16x2(e[2].x, e[2].y); u.w = pack_bf16x2(e[3].x, e[3].y);
         *reinterpret_cast<uint4*>(pt + sw128_offset(r, c8)) = u;
       }
+      const float rs = (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
       l = l * alpha + rs;
       m = m_new;
       fence_proxy_async_smem();
@@ -283,11 +334,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));
       if (j > 0) {
-        if (!accumulate(j - 1, alpha_prev)) { ok = false; break; }
+        if (!accumulate(gj - 1, alpha_prev)) { ok = false; break; }
       }
       alpha_prev = alpha;
     }
-    if (ok && n_kv > 0) ok = accumulate(n_kv - 1, alpha_prev);
+    if (ok && n_kv > 0) ok = accumulate(g0 + n_kv - 1, alpha_prev);
+    g0 += n_kv > 0 ? n_kv : 0;
 
     if (ok) {
       // combine the two halves' row sums, normalise and store
@@ -296,6 +348,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       xb[half * BLK + r] = l;
       pair_sync(quad);
       const float l_tot = l + xb[(half ^ 1) * BLK + r];
+      pair_sync(quad);  // the partner has read this slot before the next item reuses it
       const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
       if (row_g < p.Sq) {
         __nv_bfloat16* op = p.O + (long long)b * p.o_sb + (long long)row_g * p.o_ss +
@@ -303,10 +356,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int c8 = 0; c8 < DH / 8; ++c8) {
           uint4 u;
-          u.x = pack_bf16x2(o[c8 * 8 + 0] * inv, o[c8 * 8 + 1] * inv);
-          u.y = pack_bf16x2(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
-          u.z = pack_bf16x2(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
-          u.w = pack_bf16x2(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+          u.x = pack_bf16x2(o[c8 * 4 + 0].x * inv, o[c8 * 4 + 0].y * inv);
+          u.y = pack_bf16x2(o[c8 * 4 + 1].x * inv, o[c8 * 4 + 1].y * inv);
+          u.z = pack_bf16x2(o[c8 * 4 + 2].x * inv, o[c8 * 4 + 2].y * inv);
+          u.w = pack_bf16x2(o[c8 * 4 + 3].x * inv, o[c8 * 4 + 3].y * inv);
           reinterpret_cast<uint4*>(op)[c8] = u;
         }
         if (half == 0)
@@ -314,6 +367,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               (l_tot > 0.0f) ? (m + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
       }
     }
+    }  // work items
   }
 
   tc_fence_before();
@@ -375,7 +429,12 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.causal = a->causal;
   p.err = st::error_word();
-  dim3 grid((a->Sq + BLK - 1) / BLK, a->H, a->B);
+  p.n_q = (a->Sq + BLK - 1) / BLK;
+  p.n_items = p.n_q * a->H * a->B;
+  if (p.n_items <= 0) return ST_OK;
+  // persistent: one CTA per SM walks the work items, so TMEM, barriers and the pipeline fill are
+  // paid once per CTA and an item's output stores overlap the next item's first loads
+  const dim3 grid(std::min(p.n_items, st::sm_count()));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
   if (a->D == 128) {
     static bool cfg = false;
