@@ -6,7 +6,9 @@ hence the large learning rates) and, given ``run_dir``, writes the run-directory
 :mod:`spiraltorch_b200.models.zoo`.  They mirror the reference's scripts in ``models/python``:
 ``zconv_classification.py``, ``llm_char_coherence_scan.py``, ``llm_char_wave_rnn_mixer.py``,
 ``zspace_vae_reconstruction.py``, ``zspace_text_vae.py`` and the Rust ``modelzoo_gnn_graph_regression`` /
-``modelzoo_lstm_probe`` examples — same layer stacks and artefacts, smaller data.
+``modelzoo_lstm_probe`` examples — same layer stacks and artefacts, smaller data — plus
+``llm_char_coherence_wave.py``, ``maxwell_simulated_z_classification.py``, ``mellin_log_grid_classification.py``,
+``modelzoo_wave_rnn_sequence``, ``modelzoo_zspace_mixer_regression`` and the forward-only ``modelzoo_zrba_telemetry``.
 
     python -m spiraltorch_b200.models.recipes zconv_classification --run-dir runs/zconv
 """
@@ -127,12 +129,101 @@ def gnn_graph_regression(seed: int = 0):
     return model, st.nn.MeanSquaredError(), batches, 0.05
 
 
+def llm_char_coherence_wave(seed: int = 0):
+    """Embedding → ZSpaceCoherenceWaveBlock (coherence scan + dilated wave gates) → Linear."""
+    steps, dim = 12, 16
+    x, y = _char_windows(steps, seed)
+    model = st.nn.Sequential()
+    model.add(st.nn.Embedding(64, dim, name="embed"))
+    model.add(st.nn.ZSpaceCoherenceWaveBlock(dim, steps, 4, dilations=[1, 2]))
+    model.add(st.nn.Linear(steps * dim, 64, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, x.shape[0], 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 16.0
+
+
+def wave_rnn_sequence(seed: int = 0):
+    """Sequence regression with a WaveRnn: the target is the last step's first feature minus the first step's."""
+    g = torch.Generator().manual_seed(seed)
+    steps, dim = 8, 4
+    x = torch.randn(160, steps * dim, generator=g)
+    seq = x.reshape(160, steps, dim)
+    y = (seq[:, -1, 0] - seq[:, 0, 0]).reshape(-1, 1)
+    model = st.nn.Sequential()
+    model.add(st.nn.WaveRnn("wave", dim, 16, steps, dilation=2))
+    model.add(st.nn.Linear(16, 1, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, 160, 32)]
+    return model, st.nn.MeanSquaredError(), batches, 4.0
+
+
+def zspace_mixer_regression(seed: int = 0):
+    """Linear → ZSpaceMixer → ReLU → Linear on a smooth scalar target."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(192, 8, generator=g)
+    y = torch.tanh(x[:, :2].sum(1, keepdim=True)) + 0.5 * x[:, 2:3]
+    model = st.nn.Sequential()
+    model.add(st.nn.Linear(8, 16, name="fc1"))
+    model.add(st.nn.ZSpaceMixer("mixer", 16))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Linear(16, 1, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, 192, 32)]
+    return model, st.nn.MeanSquaredError(), batches, 0.5
+
+
+def maxwell_simulated_z_classification(seed: int = 0):
+    """Is a Maxwell-coded signal present?  Features: the running Z statistic of 32 simulated blocks, with
+    (kappa * lambda = 0.6 sigma) or without the coded mean; model: Linear → ReLU → Linear, 2 classes."""
+    from ..theory import simulate_z_curve
+    rows, labels = [], []
+    for i in range(192):
+        present = i % 2
+        rows.append(simulate_z_curve(32, 1.0, 1.0, 0.6 if present else 0.0, seed=seed * 1000 + i).float() / 4.0)
+        labels.append(float(present))
+    x, y = torch.stack(rows), torch.tensor(labels).reshape(-1, 1)
+    x = (x - x.mean(0)) / x.std(0).clamp(min=1e-6) / 16.0      # the deterministic initial weights grow with the index
+    model = st.nn.Sequential()
+    model.add(st.nn.Linear(32, 16, name="fc1"))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Linear(16, 2, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, 192, 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 1.0
+
+
+def mellin_log_grid_classification(seed: int = 0):
+    """Power-law versus exponential decays, told apart by the magnitudes of their Mellin transforms at
+    eight points of the critical line (samples on a logarithmic grid)."""
+    from ..frac import mellin_log_grid
+    g = torch.Generator().manual_seed(seed)
+    t = torch.logspace(-2, 2, 128)
+    rows, labels = [], []
+    for i in range(160):
+        kind = i % 2
+        a = 0.5 + float(torch.rand((), generator=g))
+        f = (1 + t) ** (-1 - a) if kind else torch.exp(-a * t)
+        f = f * (1 + 0.02 * torch.randn(128, generator=g))
+        rows.append(torch.tensor([abs(mellin_log_grid(f, 1e-2, 1e2, complex(0.5, 0.5 * k))) for k in range(8)]))
+        labels.append(float(kind))
+    x = torch.stack(rows).float()
+    x = (x - x.mean(0)) / x.std(0).clamp(min=1e-6)
+    y = torch.tensor(labels).reshape(-1, 1)
+    model = st.nn.Sequential()
+    model.add(st.nn.Linear(8, 16, name="fc1"))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Linear(16, 2, name="head"))
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, 160, 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 8.0
+
+
 _TRAINER_RECIPES: Dict[str, Callable] = {
     "zconv_classification": zconv_classification,
     "llm_char_coherence_scan": llm_char_coherence_scan,
     "llm_char_wave_rnn_mixer": llm_char_wave_rnn_mixer,
     "lstm_probe": lstm_probe,
     "gnn_graph_regression": gnn_graph_regression,
+    "llm_char_coherence_wave": llm_char_coherence_wave,
+    "wave_rnn_sequence": wave_rnn_sequence,
+    "zspace_mixer_regression": zspace_mixer_regression,
+    "maxwell_simulated_z_classification": maxwell_simulated_z_classification,
+    "mellin_log_grid_classification": mellin_log_grid_classification,
 }
 
 
@@ -184,6 +275,31 @@ def run(name: str, run_dir=None, backend: str = "cpu", epochs: int = 8, seed: in
     if rd:
         rd.write_summary({"initial_loss": out["initial_loss"], "final_loss": out["final_loss"], "epochs": epochs})
     return out
+
+
+def zrba_telemetry(run_dir=None, seed: int = 0, rows: int = 24, d_model: int = 16) -> dict:
+    """Forward-only Z-RBA probe (the reference's `modelzoo_zrba_telemetry` example): run the block on a
+    synthetic indexed batch, score its predictive intervals against the noiseless signal and, given
+    `run_dir`, write `zrba_telemetry.json`."""
+    import json
+    from pathlib import Path
+    from ..nn import SpectralFeatureSample, ZFrame, ZIndex, ZRBA, ZRBAConfig
+    from ..nn.zspace import ZTensor
+    g = torch.Generator().manual_seed(seed)
+    idx = [ZIndex(i % 3, i % 2, i % 4) for i in range(rows)]
+    signal = torch.sin(torch.arange(rows, dtype=torch.float32) / 3.0)
+    mu = signal[:, None] + 0.1 * torch.randn(rows, d_model, generator=g)
+    sigma = 0.05 + 0.05 * torch.rand(rows, d_model, generator=g)
+    block = ZRBA(ZRBAConfig(d_model=d_model, n_heads=4, cov_rank=4, gate_seed=seed))
+    out, cov, tel = block.forward(ZTensor(st.Tensor(mu), st.Tensor(sigma), idx), ZFrame(4),
+                                  SpectralFeatureSample(1, 0.8, 0.1, 0.05, float(mu.abs().mean())))
+    metrics = tel.metrics(out.mu, out.sigma, (signal * cov.gate.applied).tolist(), 0.9, idx)
+    bundle = tel.bundle_metrics(metrics).to_json()
+    bundle["attention"] = {"entropy": tel.attention.entropy, "dominant_probability": tel.attention.dominant_probability}
+    if run_dir:
+        Path(run_dir).mkdir(parents=True, exist_ok=True)
+        (Path(run_dir) / "zrba_telemetry.json").write_text(json.dumps(bundle, indent=2))
+    return bundle
 
 
 def main(argv=None) -> int:

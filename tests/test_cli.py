@@ -92,3 +92,6 @@ def test_zoo_recipes_learn_and_write_run_dirs(tmp_path):
     import pytest
     with pytest.raises(KeyError):
         recipes.run("nope")
+    bundle = recipes.zrba_telemetry(tmp_path / "zrba")
+    assert 0.0 <= bundle["metrics"]["picp"] <= 1.0 and bundle["covariance"]["min_eigenvalue"] > 0
+    assert json.loads((tmp_path / "zrba" / "zrba_telemetry.json").read_text())["gate"]["mean"] == bundle["gate"]["mean"]
