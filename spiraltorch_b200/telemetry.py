@@ -725,3 +725,148 @@ class DashboardBuilder:
     def finish_with_latency(self) -> DashboardFrame:
         self._metrics.append(DashboardMetric("frame_latency_ms", (self._clock() - self._start) * 1e3, "ms"))
         return self.finish()
+
+
+# ----------------------------------------------------------------------------------------------
+# Z-space partial fusion (crates/st-core/src/telemetry/zspace_fusion.rs:160-1300)
+# ----------------------------------------------------------------------------------------------
+class ZSpaceFusionError(ValueError):
+    pass
+
+
+_METRIC_ALIASES = {"velocity": "speed", "mem": "memory", "stab": "stability", "frac_reg": "frac", "fractality": "frac",
+                   "drift": "drs", "grad": "gradient", "curvature_radius": "elliptic_curvature",
+                   "elliptic_curvature_radius": "elliptic_curvature", "geodesic_radius": "elliptic_geodesic",
+                   "normalized_radius": "elliptic_normalized", "spin_alignment": "elliptic_alignment",
+                   "normal_bias": "elliptic_bias", "sheet_position": "elliptic_sheet_position",
+                   "sheet_index": "elliptic_sheet_index", "sheet_count": "elliptic_sheet_count",
+                   "topological_sector": "elliptic_sector", "homology_index": "elliptic_homology",
+                   "resonance_heat": "elliptic_resonance", "noise_density": "elliptic_noise"}
+_METRIC_FAMILIES = ("canvas_", "hypergrad_", "realgrad_", "import_", "elliptic_", "coherence_")
+_METRIC_BASE = ("speed", "memory", "stability", "frac", "drs", "gradient")
+
+
+def canonical_metric_name(name: str) -> Optional[str]:
+    """Canonical spelling of a Z-space metric label (aliases folded, case ignored); None when unknown."""
+    if len(name) > 128:
+        return None
+    n = name.lower()
+    n = _METRIC_ALIASES.get(n, n)
+    return n if n in _METRIC_BASE or n.startswith(_METRIC_FAMILIES) else None
+
+
+@dataclass
+class ZSpaceTelemetrySummary:
+    count: int = 0
+    l1: float = 0.0
+    l2: float = 0.0
+    linf: float = 0.0
+    mean: float = 0.0
+    variance: float = 0.0
+    energy: float = 0.0
+    amplitude: float = 0.0
+    positive: float = 0.0
+    negative: float = 0.0
+    balance: float = 0.0
+    focus: float = 0.0
+
+    @classmethod
+    def from_values(cls, values: Iterable[float]) -> "ZSpaceTelemetrySummary":
+        d = [float(v) for v in values]
+        if not d:
+            return cls()
+        if not all(math.isfinite(v) for v in d):
+            raise ZSpaceFusionError("telemetry summary: non-finite value")
+        n, energy = len(d), sum(v * v for v in d)
+        mean = sum(d) / n
+        pos, neg = sum(v for v in d if v > 0), -sum(v for v in d if v < 0)
+        bal = (pos - neg) / (pos + neg + 1e-9)
+        return cls(n, sum(abs(v) for v in d), math.sqrt(energy), max(abs(v) for v in d), mean,
+                   sum((v - mean) ** 2 for v in d) / n, energy, max(d) - min(d), pos, neg, bal, math.tanh(1.5 * bal))
+
+
+def _weighted_median(pairs: list) -> float:
+    pairs = sorted(pairs)
+    half, acc = 0.5 * sum(w for _, w in pairs), 0.0
+    for i, (v, w) in enumerate(pairs):
+        acc += w
+        if acc > half + 1e-15:
+            return v
+        if abs(acc - half) <= 1e-15 and i + 1 < len(pairs):
+            return 0.5 * (v + pairs[i + 1][0])           # balanced boundary: interpolate the neighbours
+    return pairs[-1][0]
+
+
+def fuse_zspace_partials(partials: Sequence[Optional[dict]], weights: Optional[Sequence[float]] = None,
+                         strategy: str = "mean", gradient_alignment: str = "strict",
+                         metric_gradient_dimension: Optional[int] = None) -> dict:
+    """Fuse partial observations `{"metrics": {...}, "weight": w, "origin": ..., "gradient": [...]}`.
+
+    Metric labels are canonicalised; partials that are `None` or carry a non-positive weight are audited
+    and skipped.  `strategy`: mean (weighted), last, max, min, median (weighted), sum (weighted).
+    Gradients are weight-averaged; with `gradient_alignment="strict"` differing lengths are an error,
+    with "pad_zero" shorter ones are zero-padded.  A partial without a gradient contributes the projection
+    of its canonical metrics when `metric_gradient_dimension` is given."""
+    if strategy not in ("mean", "last", "max", "min", "median", "sum"):
+        raise ZSpaceFusionError(f"unknown fusion strategy {strategy!r}")
+    if gradient_alignment not in ("strict", "pad_zero"):
+        raise ZSpaceFusionError(f"unknown gradient alignment {gradient_alignment!r}")
+    if weights is not None:
+        if len(weights) != len(partials):
+            raise ZSpaceFusionError(f"weights has {len(weights)} entries, expected {len(partials)}")
+        if not all(math.isfinite(w) for w in weights):
+            raise ZSpaceFusionError("non-finite weight")
+    if metric_gradient_dimension is not None and not 1 <= metric_gradient_dimension <= 65536:
+        raise ZSpaceFusionError(f"invalid metric gradient dimension {metric_gradient_dimension}")
+    agg: Dict[str, list] = {}
+    grads, sources = [], []
+    for i, part in enumerate(partials):
+        if part is None:
+            sources.append({"index": i, "status": "null"})
+            continue
+        w = float(weights[i] if weights is not None else part.get("weight", 1.0))
+        if not math.isfinite(w):
+            raise ZSpaceFusionError(f"non-finite weight at {i}")
+        if w <= 0:
+            sources.append({"index": i, "status": "suppressed", "weight": w, "origin": part.get("origin")})
+            continue
+        canon = {}
+        for k, v in part.get("metrics", {}).items():
+            c = canonical_metric_name(k)
+            if c is None:
+                continue
+            v = float(v)
+            if not math.isfinite(v):
+                raise ZSpaceFusionError(f"non-finite metric {k!r} in partial {i}")
+            canon[c] = v
+            agg.setdefault(c, []).append((v, w))
+        g, replaced = part.get("gradient"), False
+        if g is None and metric_gradient_dimension is not None and canon:
+            from .api_llm import metric_gradient_projection
+            g, replaced = metric_gradient_projection(canon, metric_gradient_dimension)["gradient"], True
+        if g is not None:
+            g = [float(x) for x in g]
+            if not all(math.isfinite(x) for x in g):
+                raise ZSpaceFusionError(f"non-finite gradient in partial {i}")
+            grads.append((g, w))
+        sources.append({"index": i, "status": "active", "weight": w, "origin": part.get("origin"),
+                        "metric_count": len(canon), "gradient_dim": len(g) if g is not None else 0,
+                        "gradient_replaced_by_metric_projection": replaced})
+    fused = {}
+    for name, pairs in sorted(agg.items()):
+        tot = sum(w for _, w in pairs)
+        fused[name] = {"mean": sum(v * w for v, w in pairs) / tot, "last": pairs[-1][0], "max": max(v for v, _ in pairs),
+                       "min": min(v for v, _ in pairs), "median": _weighted_median(pairs),
+                       "sum": math.fsum(v * w for v, w in pairs)}[strategy]
+    gradient = None
+    if grads:
+        dims = {len(g) for g, _ in grads}
+        if len(dims) > 1 and gradient_alignment == "strict":
+            raise ZSpaceFusionError(f"gradient dimensions differ: {sorted(dims)}")
+        dim, tot = max(dims), sum(w for _, w in grads)
+        gradient = [sum((g[j] if j < len(g) else 0.0) * w for g, w in grads) / tot for j in range(dim)]
+    return {"kind": "spiraltorch.zspace_partial_fusion", "strategy": strategy, "metrics": fused, "gradient": gradient,
+            "gradient_summary": ZSpaceTelemetrySummary.from_values(gradient or []), "sources": sources,
+            "active_count": sum(s["status"] == "active" for s in sources),
+            "suppressed_count": sum(s["status"] == "suppressed" for s in sources),
+            "null_count": sum(s["status"] == "null" for s in sources)}

@@ -859,3 +859,38 @@ def test_temporal_spectral_fusion_of_a_lane_window():
     assert f.dominant_frequency == 0.0 and 0.5 < f.tempo_hint <= 1.0 and f.spectral_energy > 0
     big = TemporalSpectralFusion.analyse(LaneWindow(64, 1, 64), 8, 8, 4, 32)
     assert big.temporal.numel() == 64 and big.spectral.numel() == 8
+
+
+def test_zspace_partial_fusion():
+    """Parity: crates/st-core/src/telemetry/zspace_fusion.rs (`fuse_zspace_partials`, `canonical_metric_name`)."""
+    import math
+    from spiraltorch_b200.telemetry import (ZSpaceFusionError, ZSpaceTelemetrySummary, canonical_metric_name,
+                                            fuse_zspace_partials)
+    assert canonical_metric_name("Velocity") == "speed" and canonical_metric_name("drift") == "drs"
+    assert canonical_metric_name("canvas_energy") == "canvas_energy" and canonical_metric_name("spin_alignment") == "elliptic_alignment"
+    assert canonical_metric_name("bogus") is None
+    parts = [{"metrics": {"speed": 1.0, "mem": 4.0}, "weight": 1.0, "gradient": [1.0, 0.0]},
+             None,
+             {"metrics": {"velocity": 3.0, "bogus": 9.0}, "weight": 3.0, "origin": "b", "gradient": [0.0, 2.0]},
+             {"metrics": {"speed": 100.0}, "weight": 0.0}]
+    f = fuse_zspace_partials(parts)
+    assert f["metrics"] == {"memory": 4.0, "speed": 2.5} and f["gradient"] == [0.25, 1.5]
+    assert (f["active_count"], f["suppressed_count"], f["null_count"]) == (2, 1, 1)
+    assert fuse_zspace_partials(parts, strategy="max")["metrics"]["speed"] == 3.0
+    assert fuse_zspace_partials(parts, strategy="last")["metrics"]["speed"] == 3.0
+    assert fuse_zspace_partials(parts, strategy="sum")["metrics"]["speed"] == 10.0
+    assert fuse_zspace_partials(parts, strategy="median")["metrics"]["speed"] == 3.0
+    assert fuse_zspace_partials(parts, weights=[1.0, 1.0, 1.0, 1.0], strategy="median")["metrics"]["speed"] == 3.0
+    ragged = [{"metrics": {}, "gradient": [1.0]}, {"metrics": {}, "gradient": [1.0, 1.0]}]
+    with pytest.raises(ZSpaceFusionError, match="differ"):
+        fuse_zspace_partials(ragged)
+    assert fuse_zspace_partials(ragged, gradient_alignment="pad_zero")["gradient"] == [1.0, 0.5]
+    proj = fuse_zspace_partials([{"metrics": {"speed": 0.9, "stability": 0.2}}], metric_gradient_dimension=8)
+    assert len(proj["gradient"]) == 8 and proj["sources"][0]["gradient_replaced_by_metric_projection"]
+    with pytest.raises(ZSpaceFusionError):
+        fuse_zspace_partials(parts, weights=[1.0])
+    with pytest.raises(ZSpaceFusionError):
+        fuse_zspace_partials(parts, strategy="mode")
+    s = ZSpaceTelemetrySummary.from_values([3.0, -4.0])
+    assert (s.l1, s.l2, s.linf, s.amplitude) == (7.0, 5.0, 4.0, 7.0) and abs(s.focus - math.tanh(1.5 * s.balance)) < 1e-12
+    assert ZSpaceTelemetrySummary.from_values([]).count == 0
