@@ -4,7 +4,7 @@
 ``st.optim``, ``st.SpiralSession``, ``st.plugin``, ``st.selfsup``, ``st.build_info()`` and
 ``st.describe_device()``.  CUDA work runs on hand-written sm_100a kernels (``csrc/``).
 """
-from . import (advisors, api_llm, autograd, compress, config, device_caps, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
+from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
                selfsup, softlogic, telemetry, text, theory, topos, tracking)
 from .nn.io import VERSION as __version__
 from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad

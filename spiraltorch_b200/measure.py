@@ -8,7 +8,7 @@ optional coupling energy ``½·β·Σ_uv J_uv·symKL(p_u, p_v)``, objective ``KL
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
 import torch
@@ -19,6 +19,16 @@ _TINY = 1e-12
 
 
 @dataclass
+class BarycenterIntermediate:
+    """A point on the straight path from the weighted arithmetic mean (interpolation 0) to the barycenter (1)."""
+    interpolation: float
+    density: Tensor
+    kl_energy: float
+    entropy: float
+    objective: float
+
+
+@dataclass
 class ZSpaceBarycenter:
     objective: float
     density: Tensor
@@ -26,6 +36,7 @@ class ZSpaceBarycenter:
     entropy: float
     coupling_energy: float
     effective_weight: float
+    intermediates: list = field(default_factory=list)
 
 
 def _normalise(t: torch.Tensor) -> torch.Tensor:
@@ -79,8 +90,17 @@ def z_space_barycenter(weights: Sequence[float], densities: Sequence[Tensor], en
         coupling_energy = 0.5 * beta_j * acc
     kl_energy = sum(w * _kl(bary, p) for w, p in zip(weights, dists))
     entropy = float(-(bary * bary.log()).sum())
+    baseline = _normalise(sum(w * p for w, p in zip(weights, dists)) / effective)
+    stages = []
+    for alpha in (0.0, 0.25, 0.5, 0.75, 1.0):
+        mix = _normalise((1.0 - alpha) * baseline + alpha * bary)
+        kl_a = float(sum(w * _kl(mix, p) for w, p in zip(weights, dists)))
+        ent_a = float(-(mix * mix.clamp(min=_TINY).log()).sum())
+        stages.append(BarycenterIntermediate(alpha, Tensor._wrap(mix.float().reshape(shape)), kl_a, ent_a,
+                                             kl_a + coupling_energy - entropy_weight * ent_a))
     return ZSpaceBarycenter(kl_energy + coupling_energy - entropy_weight * entropy,
-                            Tensor._wrap(bary.float().reshape(shape)), float(kl_energy), entropy, coupling_energy, effective)
+                            Tensor._wrap(bary.float().reshape(shape)), float(kl_energy), entropy, coupling_energy, effective,
+                            stages)
 
 
 def nirt_weight_update(weights: Sequence[float], similarities: Sequence[float], coherence_rate: float, eta: float) -> list:

@@ -72,6 +72,17 @@ class AmegaHypergrad:
         K.hyper_accumulate(self.gradient, diff, self.curvature, self.topos.tolerance,
                            self.topos.saturation, self.topos.porosity, conformal=False)
 
+    def accumulate_barycenter_path(self, intermediates) -> None:
+        """Accumulate the first density of a barycenter path as a wave and every later one against its
+        predecessor (crates/st-tensor/src/pure.rs:11104-11125)."""
+        if not intermediates:
+            raise ValueError("empty input: barycenter_intermediates")
+        prev = intermediates[0].density
+        self.accumulate_wave(prev)
+        for stage in intermediates[1:]:
+            self.accumulate_pair(stage.density, prev)
+            prev = stage.density
+
     def accumulate_complex_wave(self, real, imag) -> None:
         """Interleaves real/imaginary parts into one wave of the tape's shape."""
         r, i = _as_torch(real).reshape(-1), _as_torch(imag).reshape(-1)
