@@ -90,7 +90,9 @@ def z_space_barycenter(weights: Sequence[float], densities: Sequence[Tensor], en
         coupling_energy = 0.5 * beta_j * acc
     kl_energy = sum(w * _kl(bary, p) for w, p in zip(weights, dists))
     entropy = float(-(bary * bary.log()).sum())
-    baseline = _normalise(sum(w * p for w, p in zip(weights, dists)) / effective)
+    wsum = float(sum(weights))
+    baseline = _normalise(sum(w * p for w, p in zip(weights, dists)) / wsum) if wsum > 0 else \
+        torch.full_like(dists[0], 1.0 / dists[0].numel())          # no chart carries weight: start from the uniform density
     stages = []
     for alpha in (0.0, 0.25, 0.5, 0.75, 1.0):
         mix = _normalise((1.0 - alpha) * baseline + alpha * bary)
