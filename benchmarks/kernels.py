@@ -197,6 +197,44 @@ def bench_ce(iters, profile):
     return [row("cross_entropy_stats", [T, V], timed(ours, iters), timed(lib, iters), bytes_=T * V * 2)]
 
 
+def bench_glue(iters, profile):
+    """Bandwidth-bound glue of the training steps: RoPE, GELU backward, bias-gradient column sum, embedding
+    gather / scatter-add, 2x2 max-pool.  Fractions are of the measured copy bandwidth."""
+    from spiraltorch_b200.ops import elementwise as E
+    if profile:
+        return []
+    out = []
+    T, H, Dh, S = 16384, 16, 128, 2048
+    qkv = torch.randn(T, 3 * H * Dh, device=DEV).bfloat16()
+    def rope_ref():
+        cos, sin = E.rope_tables(S, Dh, 10000.0, qkv.device)
+        v = qkv[:, : 2 * H * Dh].reshape(T, 2 * H, Dh)
+        return E.rope_reference(v, cos, sin, S, False)
+    out.append(row("rope_qk_inplace", [T, 2 * H, Dh], timed(lambda: E.rope_(qkv, 2 * H, Dh, S), iters), timed(rope_ref, iters),
+                   bytes_=T * 2 * H * Dh * 4))
+    x = torch.randn(T, 8192, device=DEV).bfloat16()
+    dy = torch.randn(T, 8192, device=DEV).bfloat16()
+    out.append(row("gelu_bwd", [T, 8192], timed(lambda: E.act_backward(x, dy, "gelu"), iters),
+                   timed(lambda: torch.ops.aten.gelu_backward(dy, x, approximate="tanh"), iters), bytes_=T * 8192 * 6))
+    out.append(row("bias_grad_colsum", [T, 8192], timed(lambda: E.colsum(dy), iters),
+                   timed(lambda: dy.float().sum(0), iters), bytes_=T * 8192 * 2))
+    V, d = 50304, 2048
+    w = torch.randn(V, d, device=DEV).bfloat16()
+    idx = torch.randint(0, V, (T,), device=DEV)
+    out.append(row("embedding_gather", [T, d], timed(lambda: E.embedding_forward(idx, w), iters),
+                   timed(lambda: torch.nn.functional.embedding(idx, w), iters), bytes_=T * d * 4))
+    dw = torch.zeros(V, d, device=DEV)
+    dyt = torch.randn(T, d, device=DEV).bfloat16()
+    dw_lib = torch.zeros(V, d, device=DEV)
+    out.append(row("embedding_scatter_add", [T, d], timed(lambda: E.embedding_backward(idx, dyt, dw), iters),
+                   timed(lambda: dw_lib.index_add_(0, idx, dyt.float()), iters), bytes_=T * d * (2 + 8)))
+    img = torch.randn(256, 64, 64, 64, device=DEV).bfloat16()
+    nchw = img.permute(0, 3, 1, 2).contiguous()
+    out.append(row("maxpool2x2_nhwc", [256, 64, 64, 64], timed(lambda: C.maxpool2(img), iters),
+                   timed(lambda: torch.nn.functional.max_pool2d(nchw, 2), iters), bytes_=img.numel() * 2 * 1.25))
+    return out
+
+
 def bench_transforms(iters, profile):
     """The rows of the reference's published transform table (docs/performance/transforms.md:48-64, RTX 4090 + WGPU,
     times that include host<->device transfers): device-only time of the fused kernel, and the time with the upload
@@ -288,6 +326,7 @@ def main() -> int:
     table = {"gemm": lambda: bench_gemm(args.iters, args.profile),
              "attn_fwd": lambda: bench_attn(args.iters, args.profile, False),
              "attn_bwd": lambda: bench_attn(args.iters, args.profile, True),
+             "glue": lambda: bench_glue(args.iters, args.profile),
              "conv": lambda: bench_conv(args.iters, args.profile),
              "norm": lambda: bench_norm(args.iters, args.profile),
              "adamw": lambda: bench_adamw(args.iters, args.profile),
