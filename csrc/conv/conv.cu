@@ -85,6 +85,49 @@ __global__ void im2col3x3_small_kernel(const __nv_bfloat16* __restrict__ x, __nv
   }
 }
 
+// Eight channels per thread (16-byte loads, one 16-byte store of y and one 8-byte store of idx); C % 8 == 0.
+__global__ void __launch_bounds__(256)
+maxpool2_fwd8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                     unsigned char* __restrict__ idx, int N, int H, int W, int C) {
+  const int OH = H / 2, OW = W / 2, C8 = C / 8;
+  const long long total = (long long)N * OH * OW * C8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c8 = i % C8;
+    const long long p = i / C8;
+    const int ow = p % OW;
+    const int oh = (p / OW) % OH;
+    const int n = p / ((long long)OW * OH);
+    uint4 v[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+      v[t] = *reinterpret_cast<const uint4*>(
+          x + ((((long long)n * H + oh * 2 + (t >> 1)) * W + ow * 2 + (t & 1)) * C + c8 * 8));
+    float best[8];
+    unsigned arg[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; arg[j] = 0; }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const uint32_t w[4] = {v[t].x, v[t].y, v[t].z, v[t].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack_bf16x2(w[q]);
+        if (f.x > best[2 * q]) { best[2 * q] = f.x; arg[2 * q] = t; }
+        if (f.y > best[2 * q + 1]) { best[2 * q + 1] = f.y; arg[2 * q + 1] = t; }
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(best[0], best[1]); o.y = pack_bf16x2(best[2], best[3]);
+    o.z = pack_bf16x2(best[4], best[5]); o.w = pack_bf16x2(best[6], best[7]);
+    *reinterpret_cast<uint4*>(y + (p * C + c8 * 8)) = o;
+    uint2 a;
+    a.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
+    a.y = arg[4] | (arg[5] << 8) | (arg[6] << 16) | (arg[7] << 24);
+    *reinterpret_cast<uint2*>(idx + (p * C + c8 * 8)) = a;
+  }
+}
+
 // y[n, h/2, w/2, c] = max over the 2x2 window; idx (uint8) records the arg-max for the backward pass
 __global__ void maxpool2_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                     unsigned char* __restrict__ idx, int N, int H, int W, int C) {
@@ -278,6 +321,14 @@ ST_API int st_im2col3x3_small(const void* x, void* col, int N, int H, int W, int
 
 ST_API int st_maxpool2_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, void* stream_v) {
   if ((H & 1) || (W & 1) || (C & 1)) return st::fail(ST_ERR_INVALID, "maxpool2: H, W and C must be even");
+  if ((C & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(idx) & 7) == 0) {
+    maxpool2_fwd8_kernel<<<grid_for((long long)N * (H / 2) * (W / 2) * (C / 8), 256), 256, 0,
+                           reinterpret_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<unsigned char*>(idx), N, H, W, C);
+    ST_CUDA_CHECK(cudaGetLastError());
+    return ST_OK;
+  }
   maxpool2_fwd_kernel<<<grid_for((long long)N * (H / 2) * (W / 2) * (C / 2), 256), 256, 0,
                         reinterpret_cast<cudaStream_t>(stream_v)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<unsigned char*>(idx), N, H, W, C);

@@ -107,6 +107,57 @@ __global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
   if (threadIdx.x == 0 && cc < cols) atomicAdd(out + cc, t);
 }
 
+// Vectorised variant: each thread owns 8 adjacent columns (one 16-byte load per row) and block.y = 8
+// row lanes; four rows are in flight per thread.  Needs cols % 8 == 0 and 16-byte aligned rows.
+__global__ void __launch_bounds__(256)
+colsum8_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows, int cols, long long ld) {
+  __shared__ float sh[8][32 * 8 + 1];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const long long rows_per = (rows + gridDim.y - 1) / gridDim.y;
+  const long long r0 = blockIdx.y * rows_per;
+  const long long r1 = min(rows, r0 + rows_per);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  if (c0 < cols) {
+    long long r = r0 + threadIdx.y;
+    for (; r + 24 < r1; r += 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + 8 * u) * ld + c0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = unpack_bf16x2(w[q]);
+          acc[2 * q] += f.x;
+          acc[2 * q + 1] += f.y;
+        }
+      }
+    }
+    for (; r < r1; r += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + r * ld + c0);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack_bf16x2(w[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sh[threadIdx.y][threadIdx.x * 8 + j] = acc[j];
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;   // 256 threads, one column each
+  float s = 0.0f;
+#pragma unroll
+  for (int y = 0; y < 8; ++y) s += sh[y][t];
+  const int c = blockIdx.x * 256 + t;
+  if (c < cols) atomicAdd(out + c, s);
+}
+
 // ------------------------------------------------------------------------------------
 // Embedding
 // ------------------------------------------------------------------------------------
@@ -345,6 +396,15 @@ ST_API int st_act_bwd(const void* x, const void* dy, void* dx, long long n, int 
 // out (fp32 [cols]) += column sums of x (bf16 [rows, cols], leading dimension ld).
 // The caller zeroes `out` first unless it wants accumulation.
 ST_API int st_colsum(const void* x, float* out, long long rows, int cols, long long ld, void* stream_v) {
+  if ((cols & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    int chunks = (int)((rows + 255) / 256);
+    if (chunks < 1) chunks = 1;
+    if (chunks > 512) chunks = 512;
+    colsum8_kernel<<<dim3((cols + 255) / 256, chunks), dim3(32, 8), 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld);
+    ST_CUDA_CHECK(cudaGetLastError());
+    return ST_OK;
+  }
   dim3 block(32, 32);
   int chunks = (int)((rows + 1023) / 1024);
   if (chunks < 1) chunks = 1;

@@ -175,6 +175,9 @@ def test_embedding_and_colsum_and_softmax():
     assert _rel(dpos, dy.float().view(-1, S, d).sum(0)) < 1e-3
     cs = E.colsum(dy)
     assert _rel(cs, dy.float().sum(0)) < 1e-3
+    for shape in ((1001, 264), (77, 100), (5, 8)):         # ragged row counts; 100 columns take the scalar kernel
+        t = torch.randn(*shape, device=DEV).bfloat16()
+        assert _rel(E.colsum(t), t.float().sum(0)) < 1e-3
     x = torch.randn(37, 1000, device=DEV)
     y, h = E.row_softmax(x, hardmax=True)
     assert _rel(y, torch.softmax(x, -1)) < 1e-4
