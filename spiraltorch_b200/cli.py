@@ -187,6 +187,12 @@ def cmd_xai(args) -> int:
     return 0
 
 
+def cmd_compare_runs(args) -> int:
+    from .models.zoo import compare_runs
+    print(json.dumps(compare_runs(args.run_dirs, args.metric), indent=2))
+    return 0
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="spiraltorch")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -232,6 +238,10 @@ def build_parser() -> argparse.ArgumentParser:
     xa.add_argument("--palette", default=None)
     xa.add_argument("--backend", default="auto")
     xa.set_defaults(fn=cmd_xai)
+    cr = sub.add_parser("compare-runs", help="rank model-zoo run directories by a logged metric")
+    cr.add_argument("run_dirs", nargs="+")
+    cr.add_argument("--metric", default="average_loss")
+    cr.set_defaults(fn=cmd_compare_runs)
     r = sub.add_parser("runtime-preflight", help="report device, build and native-library status")
     r.add_argument("--backend", default="auto")
     r.set_defaults(fn=cmd_preflight)

@@ -57,3 +57,23 @@ class RunDir:
 def read_metrics(run_dir) -> list[dict]:
     p = Path(run_dir) / "metrics.jsonl"
     return [json.loads(line) for line in p.read_text().splitlines() if line.strip()]
+
+
+def compare_runs(run_dirs, metric: str = "average_loss") -> dict:
+    """Side-by-side summary of run directories (the reference's run comparers in `tools/` and
+    `examples/zspace_experiment_compare.py`): per run the architecture, backend, epochs, first / last / best
+    value of `metric`, and the ranking by the last value (lower is better)."""
+    rows = []
+    for d in run_dirs:
+        d = Path(d)
+        run = json.loads((d / "run.json").read_text())
+        vals = [m[metric] for m in read_metrics(d) if metric in m]
+        if not vals:
+            raise ValueError(f"{d}: no {metric!r} in metrics.jsonl")
+        rows.append({"run_dir": str(d), "arch": run.get("arch"), "backend": run.get("backend"), "epochs": len(vals),
+                     "first": vals[0], "last": vals[-1], "best": min(vals),
+                     "improvement": (vals[0] - vals[-1]) / abs(vals[0]) if vals[0] else 0.0})
+    order = sorted(range(len(rows)), key=lambda i: rows[i]["last"])
+    for rank, i in enumerate(order, 1):
+        rows[i]["rank"] = rank
+    return {"schema": "st.modelzoo.compare.v1", "metric": metric, "runs": rows, "best_run": rows[order[0]]["run_dir"]}

@@ -92,6 +92,10 @@ def test_zoo_recipes_learn_and_write_run_dirs(tmp_path):
     import pytest
     with pytest.raises(KeyError):
         recipes.run("nope")
+    cmp = zoo.compare_runs([tmp_path / "lstm_probe", tmp_path / "zspace_mixer_regression"])
+    assert {r["rank"] for r in cmp["runs"]} == {1, 2} and cmp["runs"][0]["epochs"] == 4
+    assert cmp["best_run"] in (str(tmp_path / "lstm_probe"), str(tmp_path / "zspace_mixer_regression"))
+    assert cli.main(["compare-runs", str(tmp_path / "lstm_probe"), str(tmp_path / "cli_run")]) == 0
     bundle = recipes.zrba_telemetry(tmp_path / "zrba")
     assert 0.0 <= bundle["metrics"]["picp"] <= 1.0 and bundle["covariance"]["min_eigenvalue"] > 0
     assert json.loads((tmp_path / "zrba" / "zrba_telemetry.json").read_text())["gate"]["mean"] == bundle["gate"]["mean"]
