@@ -196,6 +196,31 @@ class PrometheusExporter(MetricsExporter):
         from .config import atomic_write
         atomic_write(path, self.render())
 
+    def serve(self, port: int = 9464, host: str = "127.0.0.1"):
+        """Serve `render()` at `/metrics` from a daemon thread; returns the server (`.shutdown()` stops it,
+        `.server_address[1]` is the bound port — pass `port=0` for an ephemeral one)."""
+        from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+        exporter = self
+
+        class Handler(BaseHTTPRequestHandler):
+            def do_GET(self):  # noqa: N802
+                if self.path.split("?")[0] not in ("/metrics", "/"):
+                    self.send_error(404)
+                    return
+                body = exporter.render().encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+
+            def log_message(self, *args):
+                pass
+
+        server = ThreadingHTTPServer((host, port), Handler)
+        threading.Thread(target=server.serve_forever, daemon=True).start()
+        return server
+
 
 class CallbackExporter(MetricsExporter):
     """Forwards every gauge to a callable (the hook an OpenTelemetry meter would be attached to)."""

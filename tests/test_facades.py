@@ -894,3 +894,24 @@ def test_zspace_partial_fusion():
     s = ZSpaceTelemetrySummary.from_values([3.0, -4.0])
     assert (s.l1, s.l2, s.linf, s.amplitude) == (7.0, 5.0, 4.0, 7.0) and abs(s.focus - math.tanh(1.5 * s.balance)) < 1e-12
     assert ZSpaceTelemetrySummary.from_values([]).count == 0
+
+
+def test_prometheus_exporter_serves_metrics_over_http():
+    import json
+    import urllib.request
+    from pathlib import Path
+    from spiraltorch_b200.telemetry import PrometheusExporter
+    exp = PrometheusExporter()
+    exp.record_gauge("step_time_ms", 12.5, labels=(("rank", "0"),))
+    server = exp.serve(port=0)
+    try:
+        port = server.server_address[1]
+        body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert '# TYPE spiraltorch_step_time_ms gauge' in body and 'spiraltorch_step_time_ms{rank="0"} 12.5' in body
+        with pytest.raises(Exception):
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/nope", timeout=5)
+    finally:
+        server.shutdown()
+    root = Path(__file__).resolve().parent.parent / "deploy" / "observability"
+    dash = json.loads((root / "grafana.json").read_text())
+    assert len(dash["panels"]) == 4 and "9464" in (root / "prometheus.yml").read_text()
