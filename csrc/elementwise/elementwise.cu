@@ -183,9 +183,15 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ idx, const __
   }
 }
 // dW[idx[t] - vocab_start, :] += dy[t, :]   (fp32 accumulation)
+// Four fp32 additions to 16-byte aligned global memory in one reduction instruction.
+__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__ dy,
                                      float* __restrict__ dW, float* __restrict__ dpos, long long T, int d,
-                                     int vocab_start, int vocab_local, int seq_len) {
+                                     int vocab_start, int vocab_local, int seq_len, int vec4) {
+  // vec4: both tables start on a 16-byte boundary, so the additions can go out four at a time
   const int vec = d >> 3;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < T * vec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -196,13 +202,23 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const __
     load8(dy + t * d + v * 8, g);
     if (id >= 0 && id < vocab_local) {
       float* w = dW + id * d + v * 8;
+      if (vec4) {
+        red_add4(w, g[0], g[1], g[2], g[3]);
+        red_add4(w + 4, g[4], g[5], g[6], g[7]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(w + j, g[j]);
+        for (int j = 0; j < 8; ++j) atomicAdd(w + j, g[j]);
+      }
     }
     if (dpos) {
       float* w = dpos + (t % seq_len) * d + v * 8;
+      if (vec4) {
+        red_add4(w, g[0], g[1], g[2], g[3]);
+        red_add4(w + 4, g[4], g[5], g[6], g[7]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(w + j, g[j]);
+        for (int j = 0; j < 8; ++j) atomicAdd(w + j, g[j]);
+      }
     }
   }
 }
@@ -431,7 +447,8 @@ ST_API int st_embedding_bwd(const long long* idx, const void* dy, float* dW, flo
   if (d & 7) return st::fail(ST_ERR_INVALID, "embedding: dim must be a multiple of 8");
   embedding_bwd_kernel<<<grid_for(T * (d / 8), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       idx, static_cast<const __nv_bfloat16*>(dy), dW, dpos, T, d, vocab_start, vocab_local,
-      seq_len > 0 ? seq_len : 1);
+      seq_len > 0 ? seq_len : 1,
+      ((reinterpret_cast<uintptr_t>(dW) | reinterpret_cast<uintptr_t>(dpos)) & 15) == 0 ? 1 : 0);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
