@@ -36,7 +36,7 @@ BASELINE_TOKENS_PER_S = None  # the reference publishes no tokens/s number
 
 REFERENCE_UNAVAILABLE = (
     "reference is a Rust workspace (PyO3 binding built with maturin); no cargo/rustc/maturin on this "
-    "image and 448 crates.io dependencies are not vendored, so 'pip install /root/reference' fails "
+    "image and 448 crates.io dependencies are not vendored, so pip cannot install the reference checkout "
     "(no pyproject.toml/setup.py at its root); its pure-Python stub has no nn/transformer/optimizer"
 )
 
@@ -100,6 +100,37 @@ def launch_total() -> int:
     from spiraltorch_b200.ops import attention, elementwise, gemm, loss, norm, optim
     from spiraltorch_b200.parallel import symm
     return sum(m.launch_count for m in (attention, elementwise, gemm, loss, norm, optim, symm))
+
+
+def check_fused_against_nccl(tp, device, cfg) -> dict:
+    """One all-gather->GEMM and one GEMM->reduce-scatter at a layer shape of the model, through the fused
+    context and through NCCL + the same GEMM kernel; returns the largest relative differences (the run stops
+    above 2e-2, which is far outside bf16 rounding of these sums)."""
+    import torch
+    import torch.distributed as dist
+    from spiraltorch_b200.parallel.tp import TPContext
+    W, r = tp.world, tp.rank
+    ref = TPContext(tp.group, mode="nccl")
+    g = torch.Generator(device=device).manual_seed(77 + r)
+    rows, d, n_loc = 2048 // W * 2, cfg.d_model, cfg.ffn // W
+    x = (torch.randn(rows, d, device=device, generator=g) * 0.5).bfloat16()
+    w1 = (torch.randn(n_loc, d, device=device, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(d, n_loc, device=device, generator=g) * 0.02).bfloat16()
+    y_f, xf = tp.ag_gemm(x, w1, key="bench_check")
+    y_n, xn = ref.ag_gemm(x, w1)
+    z_f = tp.gemm_rs(y_n, w2)
+    z_n = ref.gemm_rs(y_n, w2)
+    torch.cuda.synchronize(device)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6))
+    out = torch.tensor([rel(y_f, y_n), rel(z_f, z_n), 0.0 if torch.equal(xf, xn) else 1.0], device=device,
+                       dtype=torch.float64)
+    dist.all_reduce(out, op=dist.ReduceOp.MAX)
+    res = {"ag_max_rel": float(out[0]), "rs_max_rel": float(out[1]), "gathered_rows_equal": bool(out[2] == 0)}
+    if res["ag_max_rel"] > 2e-2 or res["rs_max_rel"] > 2e-2 or not res["gathered_rows_equal"]:
+        raise SystemExit(f"fused tensor-parallel kernels disagree with NCCL + GEMM: {res}")
+    return res
 
 
 def main() -> int:
@@ -209,23 +240,29 @@ def main() -> int:
         barrier()
         return note
 
+    # ---- multi-GPU numerics: fused kernels against NCCL + the same GEMM, before anything is timed ----------
+    fused_check = None
+    if world > 1 and tp_mode == "fused":
+        fused_check = check_fused_against_nccl(tp, device, cfg)
+
     fused_note = warm_up()
     if world > 1 and tp_mode == "fused" and args.tp_mode == "auto":
-        # A bounded wait of a fused kernel that ran out (a peer that never signalled) leaves an error word on
-        # the rank that saw it.  The ranks agree on the outcome; on failure every rank rebuilds the model on
-        # NCCL collectives and warms up again, so that the run still yields a (slower, labelled) number.
-        ok = 0 if fused_note else 1
+        # A bounded wait of a fused kernel that ran out (a peer that never signalled) leaves an error record on
+        # the rank that saw it.  FusedTPContext.check() makes the ranks agree; on failure every rank rebuilds
+        # the model on NCCL collectives and warms up again, so that the run still yields a (slower, labelled)
+        # number.
         try:
-            native.raise_on_device_error()
-        except Exception as exc:  # noqa: BLE001
-            ok, fused_note = 0, fused_note or repr(exc)
-        flag = torch.tensor([ok], device=device)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
+            if fused_note:
+                tp.usable = False
+                from spiraltorch_b200.parallel.symm import agree_on_status
+                agree_on_status(dist.group.WORLD, False, device)
+                raise native.DeviceWaitTimeout(fused_note)
+            tp.check(synchronize=True)
+        except native.NativeError as exc:
+            fused_note = fused_note or repr(exc)
             if rank == 0:
                 print(f"fused tensor-parallel kernels reported a device-side error ({fused_note}); "
                       "falling back to NCCL collectives", file=sys.stderr)
-            fused_note = fused_note or "a peer rank reported a device-side error"
             del trainer
             torch.cuda.empty_cache()
             tp = fused_tp.make_context(dist.group.WORLD, "nccl")
@@ -316,6 +353,7 @@ def main() -> int:
                     "h2d_bytes_per_step": trainer.h2d_bytes_last, "d2h_bytes_per_step": trainer.d2h_bytes_last,
                     "loss": loss},
             "gpu_launches": launches,
+            **({"fused_check": fused_check} if fused_check else {}),
         }
         print(json.dumps(out))
     if world > 1:

@@ -437,17 +437,17 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   const dim3 grid(std::min(p.n_items, st::sm_count()));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
   if (a->D == 128) {
-    static bool cfg = false;
-    if (!cfg) {
+    static bool cfg[st::kMaxDevices] = {false};   // the attribute is per device
+    if (!cfg[st::current_device()]) {
       ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL));
-      cfg = true;
+      cfg[st::current_device()] = true;
     }
     attn_fwd_kernel<128><<<grid, NUM_THREADS, FwdSmem<128>::TOTAL, s>>>(tq, tk, tv, p);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
+    static bool cfg[st::kMaxDevices] = {false};   // the attribute is per device
+    if (!cfg[st::current_device()]) {
       ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL));
-      cfg = true;
+      cfg[st::current_device()] = true;
     }
     attn_fwd_kernel<64><<<grid, NUM_THREADS, FwdSmem<64>::TOTAL, s>>>(tq, tk, tv, p);
   }

@@ -42,13 +42,13 @@ __device__ __forceinline__ void fence_proxy_async_global() {
 }
 
 // Bounded wait for *flag >= epoch (wrap-safe comparison).  Returns false after
-// ST_WAIT_TIMEOUT_NS; the caller reports the failure and unwinds.
+// wait_limit_ns(); the caller reports the failure and unwinds.
 __device__ __forceinline__ bool wait_flag_ge(const unsigned* flag, unsigned epoch) {
   if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
   unsigned it = 0;
   while (static_cast<int>(ld_acquire_sys(flag) - epoch) < 0) {
-    if (((++it) & 0xFF) == 0 && globaltimer_ns() - t0 > ST_WAIT_TIMEOUT_NS) return false;
+    if (((++it) & 0xFF) == 0 && globaltimer_ns() - t0 > wait_limit_ns()) return false;
   }
   return true;
 }

@@ -42,10 +42,11 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& tmC, c
   constexpr int SMEM = L::TOTAL + ((COMM == COMM_AG && ST == AG_STAGES) ? AG_EXTRA_SMEM : 0);
   static_assert(SMEM <= 232448, "dynamic shared memory above the 227 KB limit");
   auto kern = gemm_bf16_kernel<BN, ST, false, B_MN, COMM>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[st::kMaxDevices] = {false};   // the attribute is per device
+  const int dev = st::current_device();
+  if (!configured[dev]) {
     ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured = true;
+    configured[dev] = true;
   }
   kern<<<grid, COMM == COMM_AG ? NUM_THREADS_AG : NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmC, tmA_local, p, cm);
   ST_CUDA_CHECK(cudaGetLastError());

@@ -28,6 +28,11 @@ unsigned* error_word();
 
 int sm_count();
 
+// Index of the current CUDA device clamped to [0, kMaxDevices): per-device launcher state (shared-memory
+// opt-in flags, cached addresses) is keyed by it, because function attributes are set per device.
+constexpr int kMaxDevices = 16;
+int current_device();
+
 // Encodes a tiled bf16/fp32 tensor map.  dims/strides innermost first; strides in bytes for
 // dims 1..rank-1.  Returns false (after recording the error) on failure.
 bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,

@@ -3,9 +3,9 @@
 // TMEM allocation / TMEM loads, shared-memory matrix descriptors and the instruction
 // descriptor for kind::f16.
 //
-// Every wait in this file is bounded: after ST_WAIT_TIMEOUT_NS the waiter raises the
-// CTA-wide abort flag and returns false, and callers unwind to their teardown (TMEM is
-// released, the error word is written) instead of spinning for ever.
+// Every wait in this file is bounded: after wait_limit_ns() (2 s unless the host changed it with
+// st_set_wait_timeout_ns) the waiter raises the CTA-wide abort flag and returns false, and callers
+// unwind to their teardown (TMEM is released, the error word is written) instead of spinning for ever.
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -17,6 +17,28 @@
 #endif
 
 namespace st {
+
+// ---------------------------------------------------------------------------------------
+// Wait limit.  Every translation unit that includes this header owns one copy of the device
+// word (no relocatable device code is used) and registers a setter for it at load time, so
+// st_set_wait_timeout_ns() on the host reaches all of them.  Kernels read the word only on
+// the slow path of a wait (once every few hundred polls).
+// ---------------------------------------------------------------------------------------
+typedef cudaError_t (*WaitLimitSetter)(unsigned long long);
+void register_wait_limit_setter(WaitLimitSetter fn);   // defined in runtime/runtime.cu
+
+static __device__ unsigned long long g_wait_limit_ns = ST_WAIT_TIMEOUT_NS;
+static cudaError_t set_wait_limit_here(unsigned long long ns) {
+  return cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns));
+}
+struct WaitLimitRegistration {
+  WaitLimitRegistration() { register_wait_limit_setter(&set_wait_limit_here); }
+};
+static WaitLimitRegistration g_wait_limit_registration;
+
+__device__ __forceinline__ uint64_t wait_limit_ns() {
+  return *reinterpret_cast<volatile unsigned long long*>(&g_wait_limit_ns);
+}
 
 // ---------------------------------------------------------------------------------------
 // error word: [0] = code, [1] = detail, [2] = block, [3] = count.  Lives in mapped pinned
@@ -99,7 +121,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try_wait(bar, parity)) {
     if (((++it) & 0x3F) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > ST_WAIT_TIMEOUT_NS) {
+      if (globaltimer_ns() - t0 > wait_limit_ns()) {
         *abort_flag = 1;
         return false;
       }

@@ -29,10 +29,11 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& t
                 cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, COMM_NONE>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[st::kMaxDevices] = {false};   // the attribute is per device
+  const int dev = st::current_device();
+  if (!configured[dev]) {
     ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    configured = true;
+    configured[dev] = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
   const int grid = tiles < st::sm_count() ? tiles : st::sm_count();

@@ -765,7 +765,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             red_relaxed_sys_add(cm.g.signals[dest_of(sent)] + cm.slot_arrive + R * kMaxSubChunks + sent % SUBS, 1u);
         }
         if (sent >= items || (fin && sent >= *s_done_items)) break;
-        if (globaltimer_ns() - t0 > (uint64_t)(W + 2) * ST_WAIT_TIMEOUT_NS) break;   // the copy thread reports the cause
+        if (globaltimer_ns() - t0 > (uint64_t)(W + 2) * wait_limit_ns()) break;   // the copy thread reports the cause
         __nanosleep(64);
       }
     } else if (warp == 6 && lane == 0) {

@@ -30,10 +30,11 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps
                    cudaStream_t stream, int max_ctas) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, COMM_NONE>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[st::kMaxDevices] = {false};   // the attribute is per device
+  const int dev = st::current_device();
+  if (!configured[dev]) {
     ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    configured = true;
+    configured[dev] = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
   int grid = tiles < st::sm_count() ? tiles : st::sm_count();

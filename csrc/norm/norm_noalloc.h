@@ -19,6 +19,15 @@
 //     with ST_ERR_TOO_LARGE and a message in st_last_error(); nothing is launched.
 //   * The first call on each device looks up the device address of the array (the device
 //     must be current).  Make that first call before starting any stream capture.
+//   * "Allocates nothing" is true once the array exists.  The CUDA runtime loads a module's
+//     device variables lazily, so the 4.6 MiB array may only be materialised by the first norm
+//     kernel or the first call of this entry point on a device.  A process that hands out all
+//     device memory itself should therefore make one warm-up call per device (or any other norm
+//     call of this library) at start-up, BEFORE it carves up the memory; otherwise that first call
+//     can be the one that fails for lack of memory.
+//   * Host threads: the cached address is written without a lock.  Concurrent first calls from
+//     several threads on one device all store the same value, which is harmless, but the simplest
+//     rule is to make the per-device warm-up call from one thread before the others start.
 //   * Every call shares the one array.  Each call overwrites the part of it that it later
 //     reads, so no clearing is needed between calls, but two calls that overlap on the GPU
 //     (different streams) race on it: serialise them.

@@ -2,6 +2,7 @@
 // word written by bounded waits, tensor-map encoding through the driver entry point and
 // cached device properties.
 #include "../common/host.h"
+#include "../common/ptx.cuh"
 
 #include <mutex>
 #include <string>
@@ -12,7 +13,7 @@ namespace {
 std::mutex g_mu;
 std::string g_last_error;
 
-constexpr int kMaxDevices = 16;
+using st::kMaxDevices;
 unsigned* g_err_host[kMaxDevices] = {nullptr};
 unsigned* g_err_dev[kMaxDevices] = {nullptr};
 int g_sm_count[kMaxDevices] = {0};
@@ -39,7 +40,19 @@ EncodeTiledFn get_encode() {
 }
 }  // namespace
 
+namespace {
+// Setters of the per-translation-unit wait-limit words (registered by static initialisers, so the
+// list itself must not depend on another static's construction order: plain array + counter).
+constexpr int kMaxSetters = 64;
+st::WaitLimitSetter g_setters[kMaxSetters];
+int g_n_setters = 0;
+}  // namespace
+
 namespace st {
+
+void register_wait_limit_setter(WaitLimitSetter fn) {
+  if (g_n_setters < kMaxSetters) g_setters[g_n_setters++] = fn;
+}
 
 int fail(int code, const char* msg) {
   std::lock_guard<std::mutex> lk(g_mu);
@@ -69,6 +82,12 @@ unsigned* error_word() {
   g_err_host[dev] = h;
   g_err_dev[dev] = d;
   return d;
+}
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  return dev;
 }
 
 int sm_count() {
@@ -157,6 +176,17 @@ ST_API int st_read_error_word(unsigned* out, int clear) {
     for (int i = 0; i < 4; ++i) out[i] = reinterpret_cast<volatile unsigned*>(h)[i];
   if (clear) memset(h, 0, 4 * sizeof(unsigned));
   return static_cast<int>(code);
+}
+
+// Sets the limit of every bounded device-side wait (mbarrier, peer flag) on the CURRENT device, in
+// nanoseconds; 0 restores the 2 s default.  Takes effect for kernels launched afterwards.
+ST_API int st_set_wait_timeout_ns(unsigned long long ns) {
+  if (ns == 0) ns = ST_WAIT_TIMEOUT_NS;
+  for (int i = 0; i < g_n_setters; ++i) {
+    cudaError_t e = g_setters[i](ns);
+    if (e != cudaSuccess) return st::fail_cuda(e, "st_set_wait_timeout_ns");
+  }
+  return ST_OK;
 }
 
 ST_API int st_sm_count() { return st::sm_count(); }

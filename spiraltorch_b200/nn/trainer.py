@@ -26,6 +26,7 @@ from typing import Iterable, Optional, Sequence
 import torch
 
 from .. import plugin
+from ..ops import native
 from ..tensor import Tensor, TensorError
 from .modules import Module
 
@@ -208,6 +209,7 @@ class ModuleTrainer:
         self._clip(module)
         module.apply_step(self.fallback_learning_rate)
         self.steps += 1
+        native.poll()     # a kernel that gave up a bounded wait left its outputs unwritten: stop training on them
 
     def _batches(self, batches) -> list[tuple[Tensor, Tensor]]:
         out = []

@@ -63,6 +63,15 @@ def _check_layout(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be a bf16 [B,S,H,D] view with contiguous D")
 
 
+def _check_shapes(q, k, v) -> None:
+    """K and V must agree with each other and with Q's batch, heads and head dimension: the kernel sizes every
+    access from Q's B/H/D and K's length, so a smaller K or V would be read past its allocation."""
+    if k.shape != v.shape:
+        raise ValueError(f"attention: k {tuple(k.shape)} and v {tuple(v.shape)} differ")
+    if k.dim() != 4 or q.dim() != 4 or (k.shape[0], k.shape[2], k.shape[3]) != (q.shape[0], q.shape[2], q.shape[3]):
+        raise ValueError(f"attention: k/v {tuple(k.shape)} do not match q {tuple(q.shape)} in batch, heads or head_dim")
+
+
 def attention_forward(q, k, v, causal: bool = True, scale: Optional[float] = None):
     """Returns ``(o, lse)``; ``o`` is contiguous ``[B,S,H,D]`` bf16, ``lse`` fp32 ``[B,H,S]``."""
     global launch_count
@@ -72,6 +81,8 @@ def attention_forward(q, k, v, causal: bool = True, scale: Optional[float] = Non
     if not native.use_native(q):
         o, lse = attention_reference(q, k, v, causal, scale)
         return o.to(q.dtype).contiguous(), lse
+    native.require_cuda("attention_forward", q, k, v)
+    _check_shapes(q, k, v)
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_layout(t, n)
     o = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
@@ -109,6 +120,10 @@ def attention_backward(q, k, v, o, lse, do, causal: bool = True, scale: Optional
                 given.copy_(grad.to(given.dtype))
                 outs.append(given)
         return tuple(outs)
+    native.require_cuda("attention_backward", q, k, v, o, lse, do, dq, dk, dv)
+    _check_shapes(q, k, v)
+    if o.shape != q.shape or do.shape != q.shape:
+        raise ValueError(f"attention_backward: o {tuple(o.shape)} and do {tuple(do.shape)} must match q {tuple(q.shape)}")
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (do, "do")):
         _check_layout(t, n)
     dev = q.device

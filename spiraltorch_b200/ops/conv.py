@@ -71,7 +71,10 @@ def conv3x3(x: torch.Tensor, w_tap: torch.Tensor, bias: Optional[torch.Tensor] =
     act = 4 if relu_mask_of is not None else (1 if relu else 0)
     if not native.use_native(x):
         return _conv_ref(x, w_tap, bias, act, relu_mask_of)
+    native.require_cuda("conv3x3", x, w_tap, bias, relu_mask_of)
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and w_tap.dtype == torch.bfloat16 and w_tap.is_contiguous()
+    assert w_tap.shape[1] == 9 * C, "weights must be [OC, 9*C] (tap-major)"
+    assert relu_mask_of is None or relu_mask_of.shape == (N, H, W, OC)
     if C % 64 != 0:
         # few input channels (the RGB stem): explicit im2col with K padded to a multiple of 32
         kpad = (9 * C + 31) // 32 * 32
@@ -106,7 +109,9 @@ def conv3x3_wgrad(dy: torch.Tensor, x: torch.Tensor, dw_tap: torch.Tensor) -> No
         cols = F.unfold(xf, 3, padding=1).reshape(N, C, 9, H * W).permute(0, 3, 2, 1).reshape(N * H * W, 9 * C)
         dw_tap += dy.float().reshape(-1, OC).t() @ cols
         return
-    assert dw_tap.dtype == torch.float32 and dw_tap.is_contiguous()
+    native.require_cuda("conv3x3_wgrad", dy, x, dw_tap)
+    assert dw_tap.dtype == torch.float32 and dw_tap.is_contiguous() and dw_tap.numel() == OC * 9 * C
+    assert dy.shape[:3] == x.shape[:3] and dy.is_contiguous() and x.is_contiguous()
     if C % 64 != 0:
         kpad = (9 * C + 31) // 32 * 32
         col = torch.empty((N * H * W, kpad), dtype=torch.bfloat16, device=x.device)

@@ -131,6 +131,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         return _reference(a, b, a_mn, b_mn, out, out_dtype, bias, act_id, residual, aux_out, aux_in,
                           alpha, accumulate)
 
+    native.require_cuda("gemm", a, b, out, bias, residual, aux_out, aux_in)
     batched = a.dim() == 3
     if batched:
         assert b.dim() == 3 and a.shape[0] == b.shape[0]

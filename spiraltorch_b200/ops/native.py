@@ -97,6 +97,26 @@ def raise_on_device_error() -> None:
     raise NativeError(f"device error code={code} detail=0x{detail:x} block={block} count={count}")
 
 
+def poll() -> None:
+    """Step-boundary check: raise if any kernel launched so far left an error record.
+
+    A bounded wait that runs out (or a bounds check that refused an access) makes the kernel return early with
+    its outputs unwritten while the launcher still reports success, so trainers and the host-transfer points of
+    ``Tensor`` call this.  It is a host read of mapped pinned memory: no device synchronisation, and a no-op
+    until the library has been loaded."""
+    if _lib is None:
+        return
+    if error_pending():
+        raise_on_device_error()
+
+
+def set_wait_timeout(seconds: Optional[float]) -> None:
+    """Limit of every bounded device-side wait on the current device (``None`` or 0 restores the 2 s default).
+    Applies to kernels launched after the call."""
+    ns = 0 if not seconds else max(1, int(seconds * 1e9))
+    check(lib().st_set_wait_timeout_ns(ctypes.c_ulonglong(ns)), "st_set_wait_timeout_ns")
+
+
 def stream_ptr(device: Optional[torch.device] = None) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -118,6 +138,22 @@ def same_device(op: str, *tensors: Optional[torch.Tensor]) -> None:
     for t in tensors:
         if t is None:
             continue
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"{op}: operands live on different devices ({dev} and {t.device})")
+
+
+def require_cuda(op: str, *tensors: Optional[torch.Tensor]) -> None:
+    """Refuse a launch unless every operand is a CUDA tensor on one device.  Launchers receive raw addresses:
+    a host tensor's address would be encoded into a TMA tensor map or dereferenced by the kernel and fault the
+    context, so the check comes before any pointer is taken."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError(f"{op}: operand of shape {tuple(t.shape)} is a host tensor; move it to the GPU first")
         if dev is None:
             dev = t.device
         elif t.device != dev:

@@ -78,6 +78,7 @@ class FusedInfoNCE:
         return row_loss, row_lse
 
     def apply(self, anchors: torch.Tensor, positives: torch.Tensor) -> torch.Tensor:
+        native.poll()   # an earlier launch that gave up a bounded wait leaves the arrival counters out of step
         return _InfoNceFn.apply(anchors, positives, self)
 
 

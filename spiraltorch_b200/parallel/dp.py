@@ -21,6 +21,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..ops import native
 from .symm import FusedDPStep, PeerSignals, SymmetricHeap
 
 
@@ -119,6 +120,7 @@ class FusedDataParallel:
         self._armed = False
         self._launched.clear()
         self._done.clear()
+        native.poll()
 
 
 class NcclDataParallel:

@@ -78,6 +78,29 @@ class _DpStepArgs(ctypes.Structure):
                 ("cta_counter", ctypes.c_ulonglong), ("max_ctas", ctypes.c_int)]
 
 
+def agree_on_status(group: Optional[dist.ProcessGroup], local_ok: bool,
+                    device: Optional[torch.device] = None) -> bool:
+    """Every rank says whether its own device error record is clean; the answer is True only when all are.
+
+    A bounded wait that ran out on ONE rank (a peer that never signalled) must stop EVERY rank before anybody
+    commits a partial result, and every rank has to make the same decision or their next collectives no longer
+    pair up.  One MIN all-reduce of a status word does both (on the group's backend: CPU tensor for gloo,
+    device tensor for NCCL).  Plays the role of the rendezvous' "a participant failed: everyone leaves with an
+    error" rule (crates/spiral-selfsup/src/trainer/distributed.rs:407-423)."""
+    if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return bool(local_ok)
+    on_cpu = dist.get_backend(group) == "gloo"
+    dev = torch.device("cpu") if on_cpu else (device or torch.device("cuda", torch.cuda.current_device()))
+    flag = torch.tensor([1 if local_ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(int(flag.item()) == 1)
+
+
+class FusedContextBroken(native.NativeError):
+    """A fused launch of this context gave up a bounded wait: its cumulative arrival counters no longer match
+    what the peers will send, so every later launch would time out too.  Build a new context."""
+
+
 class SymmetricBuffer:
     """A tensor plus the addresses under which every rank (and the switch) can reach it."""
 
@@ -181,6 +204,33 @@ class FusedTPContext(TPContext):
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
         self._stage: dict = {}
+        self.usable = True
+
+    # -- failure handling ------------------------------------------------------------------
+    def _require_usable(self) -> None:
+        if not self.usable:
+            raise FusedContextBroken("this fused tensor-parallel context reported a device-side timeout; "
+                                     "rebuild it (FusedTPContext(group)) before launching again")
+
+    def check(self, synchronize: bool = False) -> None:
+        """Step-boundary health check, to be called by every rank at the same point.
+
+        Reads this rank's error record (after an optional device synchronisation), agrees on the outcome with
+        the other ranks and, if any rank saw a failure, marks the context unusable and raises
+        :class:`native.DeviceWaitTimeout` on every rank, the ones that saw nothing included."""
+        if synchronize:
+            torch.cuda.synchronize(self.device)
+        local: Optional[BaseException] = None
+        try:
+            native.raise_on_device_error()
+        except native.NativeError as exc:
+            local = exc
+        if agree_on_status(self.group, local is None, self.device):
+            return
+        self.usable = False
+        if local is not None:
+            raise local
+        raise native.DeviceWaitTimeout("a peer rank reported a device-side wait timeout in a fused kernel")
 
     # -- buffers ---------------------------------------------------------------------------
     def _gather_buffer(self, key, T: int, K: int) -> SymmetricBuffer:
@@ -205,6 +255,8 @@ class FusedTPContext(TPContext):
         """``y = epilogue(all_gather_rows(x_shard) @ op(w))``; returns ``(y, x_full)`` where
         ``x_full`` is the gathered activation (a view of the symmetric buffer keyed by ``key``)."""
         global launch_count
+        self._require_usable()
+        native.require_cuda("ag_gemm", x_shard, w, aux_out, aux_in, bias)
         rows, K = x_shard.shape
         T = rows * self.world
         N = w.shape[1] if b_mn else w.shape[0]
@@ -243,9 +295,15 @@ class FusedTPContext(TPContext):
         return y, gbuf.tensor.view(T, K)
 
     def gemm_rs(self, a_full: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
-                residual: Optional[torch.Tensor] = None, alpha: float = 1.0) -> torch.Tensor:
-        """``reduce_scatter_rows(a_full @ op(w)) (+ residual)`` → ``[T/world, N]``."""
+                residual: Optional[torch.Tensor] = None, alpha: float = 1.0, _withhold: int = 0) -> torch.Tensor:
+        """``reduce_scatter_rows(a_full @ op(w)) (+ residual)`` → ``[T/world, N]``.
+
+        ``_withhold`` (tests of the failure path only) raises this one launch's arrival target above what the
+        peers will deliver, so that the bounded wait of the local tiles runs out; the context's own counters are
+        not changed by it."""
         global launch_count
+        self._require_usable()
+        native.require_cuda("gemm_rs", a_full, w, residual)
         T, K = a_full.shape
         N = w.shape[1] if b_mn else w.shape[0]
         rows = T // self.world
@@ -269,7 +327,7 @@ class FusedTPContext(TPContext):
         r.b_mn = int(b_mn)
         r.alpha = alpha
         r.slot_enter, r.slot_done = self.slot_enter, slot
-        r.done_target = cum & 0xFFFFFFFF
+        r.done_target = (cum + _withhold) & 0xFFFFFFFF
         r.stage_mc = 0
         r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")

@@ -21,6 +21,7 @@ import torch
 from .ops import attention as _attn
 from .ops import elementwise as _ew
 from .ops import gemm as _gemm
+from .ops import native as _native
 from .ops import optim as _optim
 
 _DEFAULT_DEVICE = [torch.device("cpu")]
@@ -151,18 +152,30 @@ class Tensor:
     def shape(self) -> tuple[int, int]:
         return (self._t.shape[0], self._t.shape[1])
 
+    def _host(self) -> torch.Tensor:
+        """Host copy of the data.  The copy synchronises with the device, so this is also where a kernel
+        that gave up (bounded wait, refused access) is reported instead of handing back unwritten memory."""
+        if not self._t.is_cuda:
+            return self._t.detach()
+        out = self._t.detach().cpu()
+        _native.poll()
+        return out
+
     def tolist(self) -> list[list[float]]:
-        return self._t.detach().cpu().tolist()
+        return self._host().tolist()
 
     def data(self) -> list[float]:
-        return self._t.detach().cpu().reshape(-1).tolist()
+        return self._host().reshape(-1).tolist()
 
     def torch(self) -> torch.Tensor:
         """The underlying ``torch.Tensor`` (shares storage)."""
         return self._t
 
     def to(self, device) -> "Tensor":
-        return Tensor._wrap(self._t.to(device))
+        out = Tensor._wrap(self._t.to(device))
+        if self._t.is_cuda and not out._t.is_cuda:
+            _native.poll()
+        return out
 
     def cuda(self) -> "Tensor":
         return self.to("cuda")

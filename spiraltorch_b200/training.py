@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from .models.gpt import GPTModel
+from .ops import native
 from .optim.flat import FlatAdamW
 
 
@@ -58,6 +59,8 @@ class LMTrainer:
             self._loss_acc += loss
         self.optimizer.step()
         self.steps += 1
+        if self.device.type == "cuda":
+            native.poll()     # a kernel that gave up a bounded wait left its outputs unwritten: stop here
         return self._loss_acc
 
     def train_step(self, tokens_host: torch.Tensor, targets_host: torch.Tensor) -> float:
@@ -74,6 +77,7 @@ class LMTrainer:
             self._loss_host.copy_(loss_dev, non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()
             loss = float(self._loss_host[0])
+            native.poll()
         else:
             loss = float(loss_dev[0])
         self.d2h_bytes_last = 4

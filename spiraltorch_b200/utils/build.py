@@ -88,10 +88,40 @@ def _compile_one(nvcc: str, src: Path, hdr_hash: str, verbose: bool) -> tuple[Pa
     return obj, log
 
 
+class _BuildLock:
+    """Exclusive inter-process lock around check / compile / link / replace.  Under a multi-rank launcher every
+    rank loads the library at the same moment; without the lock they would compile into the same object files
+    and could link or load a half-written one."""
+
+    def __init__(self, name: str):
+        NATIVE_DIR.mkdir(parents=True, exist_ok=True)
+        self.path = NATIVE_DIR / name
+        self.fh = None
+
+    def __enter__(self):
+        import fcntl
+        self.fh = open(self.path, "w")
+        fcntl.flock(self.fh, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self.fh, fcntl.LOCK_UN)
+        self.fh.close()
+        return False
+
+
 def build_native(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
     """Compile and link the native library if it is missing or stale; return its path."""
     if not force and is_current():
         return LIB_PATH
+    with _BuildLock(".build.lock"):
+        if not force and is_current():      # another process built it while this one waited
+            return LIB_PATH
+        return _build_native_locked(force, verbose, jobs)
+
+
+def _build_native_locked(force: bool, verbose: bool, jobs: int | None) -> Path:
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build the sm_100a native library")
@@ -108,7 +138,7 @@ def build_native(force: bool = False, verbose: bool = False, jobs: int | None = 
         results = list(ex.map(lambda s: _compile_one(nvcc, s, hdr_hash, verbose), srcs))
     objs = [str(o) for o, _ in results]
     logs = [l for _, l in results if l]
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
     cmd = [nvcc, "-shared", "-o", str(tmp), *objs, "-lcudart"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
@@ -146,14 +176,17 @@ def build_host(force: bool = False) -> Path:
     cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
     if cxx is None:
         raise RuntimeError("no C++ compiler found: cannot build the host runtime")
-    NATIVE_DIR.mkdir(parents=True, exist_ok=True)
-    tmp = HOST_LIB_PATH.with_suffix(".so.tmp")
-    cmd = [cxx, *HOST_FLAGS, *[str(s) for s in host_sources()], "-o", str(tmp)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"host runtime build failed:\n{proc.stdout}\n{proc.stderr}")
-    os.replace(tmp, HOST_LIB_PATH)
-    HOST_STAMP_PATH.write_text(_host_hash())
+    with _BuildLock(".build_host.lock"):
+        if not force and HOST_LIB_PATH.exists() and HOST_STAMP_PATH.exists() and \
+                HOST_STAMP_PATH.read_text().strip() == _host_hash():
+            return HOST_LIB_PATH
+        tmp = HOST_LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
+        cmd = [cxx, *HOST_FLAGS, *[str(s) for s in host_sources()], "-o", str(tmp)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"host runtime build failed:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(tmp, HOST_LIB_PATH)
+        HOST_STAMP_PATH.write_text(_host_hash())
     return HOST_LIB_PATH
 
 

@@ -96,9 +96,13 @@ def test_gpt_fused_context_matches_plain_world1():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_kernels_two_ranks():
     script = os.path.join(os.path.dirname(__file__), "multi_gpu", "run_fused_tp.py")
+    import socket
+    with socket.socket() as sock:           # a free port: the machine is shared with other jobs
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                           "--master-addr", "127.0.0.1", "--master-port", "29533", script],
+                           "--master-addr", "127.0.0.1", "--master-port", str(port), script],
                           capture_output=True, text=True, timeout=600, env=env)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "FUSED_TP_OK" in proc.stdout

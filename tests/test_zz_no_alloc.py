@@ -5,8 +5,9 @@ loop that pre-carved all device memory, a host application with its own allocato
 library offers a variant whose scratch lives in a fixed array inside the ``.so``.  The test
 calls the exported C symbol directly through ctypes, twice in a row (the array keeps the
 previous call's contents, so the second call checks that stale data does no harm), and
-compares with the regular entry point that takes a caller-provided scratch buffer.  It also
-checks that an over-sized problem is refused with a clear message and nothing is written.
+compares with the regular entry point that takes a caller-provided scratch buffer and, since
+that one runs the same kernels, also with the fp32 PyTorch statement of the backward pass.  It
+also checks that an over-sized problem is refused with a clear message and nothing is written.
 This file sorts last so that a run that stops at the first failure has already run
 everything else.
 """
@@ -63,6 +64,19 @@ def _run_pair(lib, rms, rows, d, seed):
     assert torch.allclose(dg0, dg1, rtol=2e-4, atol=2e-4)
     if not rms:
         assert torch.allclose(db0, db1, rtol=2e-4, atol=2e-4)
+    # independent oracle: the backward pass written out in fp32 PyTorch (accumulate=1 on top of the 0.5 / -0.25 fills)
+    dyf, gf = dy.float(), gamma.float()
+    xh = (xf - (0 if rms else mean[:, None])) * rstd[:, None]
+    gy = dyf * gf
+    m1 = (gy * xh).mean(-1, keepdim=True)
+    m2 = 0 if rms else gy.mean(-1, keepdim=True)
+    dx_ref = rstd[:, None] * (gy - m2 - xh * m1) + dres.float()
+    dg_ref = 0.5 + (dyf * xh).sum(0)
+    assert (dx1.float() - dx_ref).abs().max().item() <= 2e-2 * dx_ref.abs().max().item()
+    assert (dg1 - dg_ref).abs().max().item() <= 2e-3 * dg_ref.abs().max().item() + 1e-3
+    if not rms:
+        db_ref = -0.25 + dyf.sum(0)
+        assert (db1 - db_ref).abs().max().item() <= 2e-3 * db_ref.abs().max().item() + 1e-3
 
 
 def test_noalloc_matches_scratch_entry_point_twice_in_a_row():
