@@ -53,6 +53,11 @@ struct AttnBwdParams {
   float scale, scale_log2;
   int causal;
   unsigned* err;
+  // optional additive biases and valid lengths, as in the forward kernel (null = absent)
+  const float* key_bias;
+  const float* attn_bias;
+  const int* lengths;
+  long long kb_sb, kb_sh, ab_sb, ab_sh, ab_sq;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -90,7 +95,7 @@ __device__ __forceinline__ void store8_bf16(uint8_t* tile, int r, int c16, const
   *reinterpret_cast<uint4*>(tile + sw128_offset(r, c16)) = u;
 }
 
-template <int D, int MODE>
+template <int D, int MODE, bool BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -398,8 +403,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const int kv0 = kv_tile * BLK;
       // tiles that need no masking: every row and column valid and strictly below the diagonal
+      constexpr bool biased = BIAS;   // additive biases / valid lengths: a separate instantiation, the plain one is unchanged
       const bool plain = (q_tile + 1) * BLK <= p.Sq && (kv_tile + 1) * BLK <= p.Sk &&
-                         !(p.causal && kv_tile >= q_tile);
+                         !(p.causal && kv_tile >= q_tile) && !biased;
       float pv[32];
       uint8_t* const p_tile = smem + L::P_OFF + (part >> 1) * (BLK * 128);    // 64-column block of the P / dS tile
       uint8_t* const ds_tile = smem + L::DS_OFF + (part >> 1) * (BLK * 128);
@@ -415,12 +421,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (plain) {
 #pragma unroll
           for (int q = 0; q < 32; ++q) pv[q] = fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
-        } else {
+        } else if constexpr (!biased) {
 #pragma unroll
           for (int q = 0; q < 32; ++q) {
             const int colg = kv0 + part * 32 + q;
             const bool dead = !row_ok || colg >= p.Sk || (p.causal && colg > row_g);
             pv[q] = dead ? 0.0f : fast_exp2(__uint_as_float(s_r[q]) * p.scale_log2 - lse2);
+          }
+        } else {
+          // the forward's logits were scale * q·k + key_bias + attn_bias with keys (and queries) beyond the
+          // valid length masked; a fully masked row has lse = -inf and contributes nothing
+          int kv_len = p.Sk;
+          if (p.lengths) kv_len = max(0, min(p.Sk, p.lengths[b]));
+          const bool row_live = row_ok && (!p.lengths || row_g < kv_len) && lse2 > -INFINITY;
+          const float* kb = p.key_bias ? p.key_bias + (long long)b * p.kb_sb + (long long)h * p.kb_sh : nullptr;
+          const float* ab = (p.attn_bias && row_ok)
+                                ? p.attn_bias + (long long)b * p.ab_sb + (long long)h * p.ab_sh + (long long)row_g * p.ab_sq
+                                : nullptr;
+#pragma unroll
+          for (int q = 0; q < 32; ++q) {
+            const int colg = kv0 + part * 32 + q;
+            const bool dead = !row_live || colg >= kv_len || (p.causal && colg > row_g);
+            float e = 0.0f;
+            if (!dead) {
+              float bias = kb ? kb[colg] : 0.0f;
+              if (ab) bias += ab[colg];
+              e = fast_exp2(fmaf(__uint_as_float(s_r[q]), p.scale_log2, bias * LOG2E) - lse2);
+            }
+            pv[q] = e;
           }
         }
       }
@@ -600,6 +628,10 @@ struct StAttnBwdArgs {
   int B, H, Sq, Sk, D;
   float scale;
   int causal;
+  // optional additive biases (fp32) and valid lengths (int32 [B]) of the forward pass; null = absent
+  const float* key_bias;  long long kb_sb, kb_sh;
+  const float* attn_bias; long long ab_sb, ab_sh, ab_sq;
+  const int* lengths;
 };
 
 // delta: fp32 [B,H,Sq] workspace.  dQ_acc is unused (kept in the argument block for ABI stability).
@@ -655,6 +687,10 @@ ST_API int st_attn_bwd(const StAttnBwdArgs* a, void* stream_v) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.causal = a->causal;
   p.err = st::error_word();
+  p.key_bias = a->key_bias; p.kb_sb = a->kb_sb; p.kb_sh = a->kb_sh;
+  p.attn_bias = a->attn_bias; p.ab_sb = a->ab_sb; p.ab_sh = a->ab_sh; p.ab_sq = a->ab_sq;
+  p.lengths = a->lengths;
+  const bool biased = a->key_bias || a->attn_bias || a->lengths;
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -673,11 +709,21 @@ ST_API int st_attn_bwd(const StAttnBwdArgs* a, void* stream_v) {
   };
   int rc;
   if (a->D == 128) {
-    if ((rc = launch(attn_bwd_kernel<128, MODE_KV>, BwdSmem<128, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
-    if ((rc = launch(attn_bwd_kernel<128, MODE_Q>, BwdSmem<128, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    if (biased) {
+      if ((rc = launch(attn_bwd_kernel<128, MODE_KV, true>, BwdSmem<128, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
+      if ((rc = launch(attn_bwd_kernel<128, MODE_Q, true>, BwdSmem<128, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    } else {
+      if ((rc = launch(attn_bwd_kernel<128, MODE_KV, false>, BwdSmem<128, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
+      if ((rc = launch(attn_bwd_kernel<128, MODE_Q, false>, BwdSmem<128, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    }
   } else {
-    if ((rc = launch(attn_bwd_kernel<64, MODE_KV>, BwdSmem<64, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
-    if ((rc = launch(attn_bwd_kernel<64, MODE_Q>, BwdSmem<64, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    if (biased) {
+      if ((rc = launch(attn_bwd_kernel<64, MODE_KV, true>, BwdSmem<64, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
+      if ((rc = launch(attn_bwd_kernel<64, MODE_Q, true>, BwdSmem<64, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    } else {
+      if ((rc = launch(attn_bwd_kernel<64, MODE_KV, false>, BwdSmem<64, MODE_KV>::TOTAL, grid_kv)) != ST_OK) return rc;
+      if ((rc = launch(attn_bwd_kernel<64, MODE_Q, false>, BwdSmem<64, MODE_Q>::TOTAL, grid_q)) != ST_OK) return rc;
+    }
   }
   return ST_OK;
 }

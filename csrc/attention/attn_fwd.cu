@@ -14,6 +14,12 @@
 //
 // Outputs O (bf16, [B,S,H,D] strided) and the log-sum-exp per row (fp32 [B,H,S]).
 //
+// The BIAS instantiation adds, before the softmax, a per-key bias key_bias[b, (h,) key] and / or a
+// per-(query, key) bias attn_bias[b, (h,) query, key] (both fp32, added to scale * q·k), and honours a
+// valid length per batch entry: keys at or beyond lengths[b] are masked and queries at or beyond it
+// produce zeros (the semantics of the reference's z_bias / attn_bias / context_lengths arguments,
+// crates/st-core/src/backend/cuda_attention.cu:85-96,117-202).  The plain instantiation is unchanged.
+//
 // Reference parity: fused_attention_online.wgsl (crates/st-backend-wgpu/src/shaders),
 // scaled_dot_attention_kernel (crates/st-core/src/backend/cuda_attention.cu:80-258),
 // fused_attention_cpu (crates/st-tensor/src/pure.rs:11845-11919).
@@ -36,6 +42,11 @@ struct AttnFwdParams {
   unsigned* err;
   int n_q;       // query tiles per (batch, head)
   int n_items;   // n_q * H * B work items, heaviest (latest) query tiles first
+  // ---- BIAS instantiation only ----
+  const float* key_bias;       // [B, (H,) Sk] or null; element strides kb_sb, kb_sh (0 = shared by the heads)
+  const float* attn_bias;      // [B, (H,) Sq, Sk] or null; element strides ab_sb, ab_sh, ab_sq (keys contiguous)
+  const int* lengths;          // [B] valid keys (and queries) per batch entry, or null
+  long long kb_sb, kb_sh, ab_sb, ab_sh, ab_sq;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -60,7 +71,7 @@ struct FwdSmem {
   static constexpr int TOTAL = XCH_OFF + 2 * 2 * BLK * 4;
 };
 
-template <int D>
+template <int D, bool BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -98,8 +109,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int rem = w % hb;
     h = rem % p.H;
     b = rem / p.H;
-    n_kv = (p.Sk + BLK - 1) / BLK;
+    int kv_len = p.Sk;
+    if (BIAS && p.lengths) kv_len = max(0, min(p.Sk, p.lengths[b]));
+    n_kv = (kv_len + BLK - 1) / BLK;
     if (p.causal) n_kv = min(n_kv, q_tile + 1);
+    if (BIAS && p.lengths && q_tile * BLK >= kv_len) n_kv = 0;   // every query of the tile is beyond the valid length
   };
 
   if (threadIdx.x == 0) {
@@ -263,6 +277,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
 #pragma unroll
     for (int c = 0; c < DH / 2; ++c) o[c] = make_float2(0.0f, 0.0f);
+    // BIAS: logits are moved to the log2 domain (scale and biases applied) before the maximum, so the
+    // factor used afterwards is 1
+    const float sc = BIAS ? 1.0f : p.scale_log2;
+    int kv_len = p.Sk;
+    if (BIAS && p.lengths) kv_len = max(0, min(p.Sk, p.lengths[b]));
+    const bool row_live = !BIAS || row_g < kv_len || !p.lengths;
 
     for (int j = 0; j < n_kv; ++j) {
       const int gj = g0 + j;
@@ -282,7 +302,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int col0 = j * BLK + half * 64;
       const bool need_mask = (p.causal && (j == q_tile)) || (col0 + 64 > p.Sk);
       float mx = -INFINITY;
-      if (need_mask) {
+      if constexpr (BIAS) {
+        constexpr float LOG2E = 1.4426950408889634f;
+        const float* kb = p.key_bias ? p.key_bias + (long long)b * p.kb_sb + (long long)h * p.kb_sh : nullptr;
+        const float* ab = (p.attn_bias && row_g < p.Sq)
+                              ? p.attn_bias + (long long)b * p.ab_sb + (long long)h * p.ab_sh + (long long)row_g * p.ab_sq
+                              : nullptr;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int col = col0 + c;
+          const bool dead = !row_live || col >= kv_len || (p.causal && col > row_g);
+          float s = -INFINITY;
+          if (!dead) {
+            float bias = kb ? kb[col] : 0.0f;
+            if (ab) bias += ab[col];
+            s = fmaf(__uint_as_float(sr[c]), p.scale_log2, bias * LOG2E);
+          }
+          sr[c] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+      } else if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const int col = col0 + c;
@@ -304,11 +343,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       xb[half * BLK + r] = mx;
       pair_sync(quad);
       mx = fmaxf(mx, xb[(half ^ 1) * BLK + r]);
-      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float m_new = fmaxf(m, mx * sc);
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = fast_exp2(m - m_safe);
       uint8_t* pt = smem + L::P_OFF + buf * L::P_TILE + half * (BLK * 128);
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 sc2 = make_float2(sc, sc);
       const float2 nm2 = make_float2(-m_safe, -m_safe);
       float2 rs2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
@@ -403,6 +442,10 @@ struct StAttnFwdArgs {
   int B, H, Sq, Sk, D;
   float scale;
   int causal;
+  // optional additive biases (fp32) and valid lengths (int32 [B]); all null = the plain kernel
+  const float* key_bias;  long long kb_sb, kb_sh;            // [B, (H,) Sk]
+  const float* attn_bias; long long ab_sb, ab_sh, ab_sq;     // [B, (H,) Sq, Sk], keys contiguous
+  const int* lengths;
 };
 
 ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
@@ -431,26 +474,33 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   p.err = st::error_word();
   p.n_q = (a->Sq + BLK - 1) / BLK;
   p.n_items = p.n_q * a->H * a->B;
+  p.key_bias = a->key_bias; p.kb_sb = a->kb_sb; p.kb_sh = a->kb_sh;
+  p.attn_bias = a->attn_bias; p.ab_sb = a->ab_sb; p.ab_sh = a->ab_sh; p.ab_sq = a->ab_sq;
+  p.lengths = a->lengths;
+  const bool biased = a->key_bias || a->attn_bias || a->lengths;
   if (p.n_items <= 0) return ST_OK;
   // persistent: one CTA per SM walks the work items, so TMEM, barriers and the pipeline fill are
   // paid once per CTA and an item's output stores overlap the next item's first loads
   const dim3 grid(std::min(p.n_items, st::sm_count()));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
+  auto launch = [&](auto kern, int smem_bytes, bool* cfg) -> int {
+    if (!cfg[st::current_device()]) {     // the attribute is per device
+      ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      cfg[st::current_device()] = true;
+    }
+    kern<<<grid, NUM_THREADS, smem_bytes, s>>>(tq, tk, tv, p);
+    return ST_OK;
+  };
+  static bool cfg[4][st::kMaxDevices] = {{false}};
+  int rc;
   if (a->D == 128) {
-    static bool cfg[st::kMaxDevices] = {false};   // the attribute is per device
-    if (!cfg[st::current_device()]) {
-      ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL));
-      cfg[st::current_device()] = true;
-    }
-    attn_fwd_kernel<128><<<grid, NUM_THREADS, FwdSmem<128>::TOTAL, s>>>(tq, tk, tv, p);
+    rc = biased ? launch(attn_fwd_kernel<128, true>, FwdSmem<128>::TOTAL, cfg[0])
+                : launch(attn_fwd_kernel<128, false>, FwdSmem<128>::TOTAL, cfg[1]);
   } else {
-    static bool cfg[st::kMaxDevices] = {false};   // the attribute is per device
-    if (!cfg[st::current_device()]) {
-      ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL));
-      cfg[st::current_device()] = true;
-    }
-    attn_fwd_kernel<64><<<grid, NUM_THREADS, FwdSmem<64>::TOTAL, s>>>(tq, tk, tv, p);
+    rc = biased ? launch(attn_fwd_kernel<64, true>, FwdSmem<64>::TOTAL, cfg[2])
+                : launch(attn_fwd_kernel<64, false>, FwdSmem<64>::TOTAL, cfg[3]);
   }
+  if (rc != ST_OK) return rc;
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }

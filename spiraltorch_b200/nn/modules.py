@@ -9,8 +9,9 @@ Each layer states its math once as a pure PyTorch function ``_fwd(x, params)``; 
 differentiates that function with ``torch.autograd`` and applies the reference's gradient
 convention: parameter gradients are divided by the batch size (rows of the input) before they
 are accumulated (crates/st-nn/src/layers/linear.rs:109-170, conv.rs:567, embedding.rs:449,
-normalization.rs:116).  On CUDA tensors the linear algebra runs on the sm_100a kernels through
-:mod:`spiraltorch_b200.ops`.
+normalization.rs:116).  On CUDA tensors the heavy math of ``Linear``, ``LayerNorm``, ``Embedding``, ``ZConv``
+and 2x2 max ``Pool2d`` - forward, data gradient and parameter gradients - runs on the sm_100a kernels through
+:mod:`spiraltorch_b200.nn.functional`, so neither call reaches a library GEMM or convolution.
 
 Parameter naming and layouts follow the reference: ``Linear`` has ``{name}::weight`` of shape
 ``(in, out)`` and ``{name}::bias`` ``(1, out)``; convolutions keep ``(out_channels,
@@ -29,6 +30,7 @@ from ..tensor import Tensor, TensorError
 
 
 from ..ops import recurrent as _rec  # noqa: E402
+from . import functional as _fn  # noqa: E402
 
 
 def _t(x) -> torch.Tensor:
@@ -137,9 +139,11 @@ class Module:
     __call__ = forward
 
     def backward(self, x: Tensor, grad_output: Tensor) -> Tensor:
-        xt = _t(x).detach().clone().requires_grad_(True)
+        xt = _t(x).detach().requires_grad_(True)
         plist = [p for p in self.parameters() if p.trainable]
-        leaves = {p.name: p.value.detach().clone().requires_grad_(True) for p in plist}
+        # leaves alias the parameter storage (no copy): the values are only read here, and the bf16 copies
+        # cached per storage stay valid from the forward to the backward call
+        leaves = {p.name: p.value.detach().requires_grad_(True) for p in plist}
         pmap = dict(self._param_map())
         pmap.update(leaves)
         with torch.enable_grad():
@@ -327,11 +331,8 @@ def _linear_args(args, kwargs, what: str):
 
 
 def _mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """x @ w with w stored (in, out); tcgen05 GEMM for CUDA tensors outside autograd."""
-    if x.is_cuda and not torch.is_grad_enabled():
-        from ..ops.gemm import gemm
-        return gemm(x.to(torch.bfloat16), w.to(torch.bfloat16), b_mn=True, out_dtype=torch.float32)
-    return x @ w
+    """x @ w with w stored (in, out); on CUDA the tcgen05 GEMM, forward and both gradients."""
+    return _fn.linear(x, w, None)
 
 
 class Identity(Module):
@@ -356,7 +357,7 @@ class Linear(Module):
     def _fwd(self, x, params):
         if x.shape[1] != self.input_dim:
             raise TensorError(f"Linear {self.name}: expected {self.input_dim} input columns, got {x.shape[1]}")
-        return _mm(x, params[f"{self.name}::weight"]) + params[f"{self.name}::bias"]
+        return _fn.linear(x, params[f"{self.name}::weight"], params[f"{self.name}::bias"])
 
 
 class LoraLinear(Module):
@@ -378,7 +379,8 @@ class LoraLinear(Module):
 
     def _fwd(self, x, p):
         n = self.name
-        return x @ p[f"{n}::weight"] + p[f"{n}::bias"] + self.scale * ((x @ p[f"{n}::lora_a"]) @ p[f"{n}::lora_b"])
+        base = _fn.linear(x, p[f"{n}::weight"], p[f"{n}::bias"])
+        return base + self.scale * _mm(_mm(x, p[f"{n}::lora_a"]), p[f"{n}::lora_b"])
 
     def state_dict(self):
         return sorted(((p.name, Tensor._wrap(p.value.clone())) for p in self.parameters() if p.trainable),
@@ -400,7 +402,7 @@ class Embedding(Module):
 
     def _fwd(self, x, p):
         ids = x.detach().round().long().clamp(0, self.vocab - 1)
-        return p[f"{self.name}::weight"][ids].reshape(x.shape[0], -1)
+        return _fn.embedding(ids, p[f"{self.name}::weight"]).reshape(x.shape[0], -1)
 
 
 class Relu(Module):
@@ -477,8 +479,7 @@ class LayerNorm(Module):
         self._register(f"{name}::beta", torch.zeros(1, features))
 
     def _fwd(self, x, p):
-        return F.layer_norm(x, (self.features,), p[f"{self.name}::gamma"].reshape(-1),
-                            p[f"{self.name}::beta"].reshape(-1), self.epsilon)
+        return _fn.layer_norm(x, p[f"{self.name}::gamma"], p[f"{self.name}::beta"], self.epsilon)
 
 
 class ZSpaceLayerNorm(LayerNorm):
@@ -708,8 +709,8 @@ class ZConv(Module):
     def _fwd(self, x, p):
         b = x.shape[0]
         img = x.reshape(b, self.ic, *self.input_hw)
-        w = p[f"{self.name}::weight"].reshape(self.oc, self.ic, *self.kernel)
-        y = F.conv2d(img, w, p[f"{self.name}::bias"].reshape(-1), self.stride, self.padding, self.dilation)
+        y = _fn.conv2d(img, p[f"{self.name}::weight"], p[f"{self.name}::bias"], self.kernel, self.stride,
+                       self.padding, self.dilation)
         return y.reshape(b, -1)
 
 
@@ -726,6 +727,8 @@ class Pool2d(Module):
 
     def _fwd(self, x, p):
         img = x.reshape(x.shape[0], self.c, self.h, self.w)
+        if self.mode == "max" and self.kernel == (2, 2) and self.stride == (2, 2) and self.padding == (0, 0):
+            return _fn.max_pool2x2(img).reshape(x.shape[0], -1)
         f = F.max_pool2d if self.mode == "max" else F.avg_pool2d
         return f(img, self.kernel, self.stride, self.padding).reshape(x.shape[0], -1)
 

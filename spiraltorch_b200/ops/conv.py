@@ -47,6 +47,20 @@ def dgrad_weights(w_tap: torch.Tensor, ic: int) -> torch.Tensor:
     return w_tap.reshape(oc, 3, 3, ic).flip(1, 2).permute(3, 1, 2, 0).reshape(ic, 9 * oc).contiguous()
 
 
+def implicit_ok(N: int, H: int, W: int, C: int, OC: int, pixels: int = 128) -> bool:
+    """Whether the implicit-GEMM kernels take this geometry: channels in 64-blocks, and a pixel block of
+    ``pixels`` output positions (128 forward / data gradient, 64 weight gradient) must be W columns x whole rows
+    x whole images.  Other shapes go through the explicit im2col + GEMM path."""
+    if C % 64 != 0 or OC % 8 != 0 or W <= 0 or W > pixels or pixels % W != 0:
+        return False
+    hb, nb = pixels // W, 1
+    if hb > H:
+        if hb % H != 0:
+            return False
+        nb, hb = hb // H, H
+    return H % hb == 0 and N % nb == 0
+
+
 def _conv_ref(x, w_tap, bias, act, aux_in):
     N, H, W, C = x.shape
     oc = w_tap.shape[0]
@@ -75,8 +89,9 @@ def conv3x3(x: torch.Tensor, w_tap: torch.Tensor, bias: Optional[torch.Tensor] =
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and w_tap.dtype == torch.bfloat16 and w_tap.is_contiguous()
     assert w_tap.shape[1] == 9 * C, "weights must be [OC, 9*C] (tap-major)"
     assert relu_mask_of is None or relu_mask_of.shape == (N, H, W, OC)
-    if C % 64 != 0:
-        # few input channels (the RGB stem): explicit im2col with K padded to a multiple of 32
+    if not implicit_ok(N, H, W, C, OC, 128):
+        # few input channels (the RGB stem) or a geometry the 4-D TMA boxes cannot tile: explicit im2col
+        # with K padded to a multiple of 32, then the plain GEMM
         kpad = (9 * C + 31) // 32 * 32
         col = torch.empty((N * H * W, kpad), dtype=torch.bfloat16, device=x.device)
         st = native.lib().st_im2col3x3_small(native.ptr(x), native.ptr(col), ctypes.c_int(N), ctypes.c_int(H),
@@ -86,7 +101,10 @@ def conv3x3(x: torch.Tensor, w_tap: torch.Tensor, bias: Optional[torch.Tensor] =
         launch_count += 1
         wp = torch.zeros((OC, kpad), dtype=torch.bfloat16, device=x.device)
         wp[:, : 9 * C] = w_tap
-        y = gemm(col, wp, bias=bias, act="relu" if relu else None)
+        if relu_mask_of is not None:
+            y = gemm(col, wp, bias=bias, act="relu_bwd", aux_in=relu_mask_of.reshape(N * H * W, OC))
+        else:
+            y = gemm(col, wp, bias=bias, act="relu" if relu else None)
         return y.view(N, H, W, OC)
     y = torch.empty((N, H, W, OC), dtype=torch.bfloat16, device=x.device)
     a = _ConvArgs()
@@ -112,7 +130,7 @@ def conv3x3_wgrad(dy: torch.Tensor, x: torch.Tensor, dw_tap: torch.Tensor) -> No
     native.require_cuda("conv3x3_wgrad", dy, x, dw_tap)
     assert dw_tap.dtype == torch.float32 and dw_tap.is_contiguous() and dw_tap.numel() == OC * 9 * C
     assert dy.shape[:3] == x.shape[:3] and dy.is_contiguous() and x.is_contiguous()
-    if C % 64 != 0:
+    if not implicit_ok(N, H, W, C, OC, 64):
         kpad = (9 * C + 31) // 32 * 32
         col = torch.empty((N * H * W, kpad), dtype=torch.bfloat16, device=x.device)
         st = native.lib().st_im2col3x3_small(native.ptr(x), native.ptr(col), ctypes.c_int(N), ctypes.c_int(H),

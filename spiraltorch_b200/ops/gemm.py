@@ -100,6 +100,27 @@ def _reference(a, b, a_mn, b_mn, out, out_dtype, bias, act, residual, aux_out, a
     return out
 
 
+# bf16 copies of fp32 parameters, keyed by storage address and invalidated by the tensor's version counter: a
+# weight is rounded once per optimizer step instead of once per forward.
+_bf16_cache: dict = {}
+_BF16_CACHE_MAX = 512
+
+
+def cached_bf16(t: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of ``t`` (itself when it already is bf16), reused until ``t`` is modified in place."""
+    if t.dtype == torch.bfloat16:
+        return t
+    key = (t.data_ptr(), tuple(t.shape), t.device)
+    hit = _bf16_cache.get(key)
+    if hit is not None and hit[0] == t._version:
+        return hit[1]
+    if len(_bf16_cache) >= _BF16_CACHE_MAX:
+        _bf16_cache.clear()
+    out = t.detach().to(torch.bfloat16).contiguous()
+    _bf16_cache[key] = (t._version, out)
+    return out
+
+
 def _pad_to(t: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
     if t.shape[-2] == rows and t.shape[-1] == cols and t.stride(-1) == 1 and t.stride(-2) % 8 == 0 \
             and t.data_ptr() % 16 == 0:

@@ -22,6 +22,7 @@ from .ops import attention as _attn
 from .ops import elementwise as _ew
 from .ops import gemm as _gemm
 from .ops import native as _native
+from .ops import norm as _norm
 from .ops import optim as _optim
 
 _DEFAULT_DEVICE = [torch.device("cpu")]
@@ -214,7 +215,7 @@ class Tensor:
         use_cuda = self._t.is_cuda and backend not in ("cpu", "naive", "faer", "simd", "cpu-simd")
         if use_cuda:
             a = self._t.to(torch.bfloat16)
-            b = other._t.to(torch.bfloat16)
+            b = _gemm.cached_bf16(other._t)      # weights are rounded once, not on every call
             out = _gemm.gemm(a, b, b_mn=True, out_dtype=torch.float32 if (act is None and bias is None and residual is None) else torch.bfloat16,
                              bias=None if bias is None else bias.to(torch.bfloat16).reshape(-1),
                              act=act, residual=None if residual is None else residual.to(torch.bfloat16))
@@ -292,11 +293,18 @@ class Tensor:
         q = self._t.view(contexts, sequence, d)
         k = keys._t.view(contexts, sequence, d)
         v = values._t.view(contexts, sequence, values.cols)
-        fast = (self._t.is_cuda and z_bias is None and attn_bias is None and d in (64, 128) and values.cols == d)
+        fast = self._t.is_cuda and d in (64, 128) and values.cols == d
         if fast:
-            o, _ = _attn.attention_forward(q.to(torch.bfloat16).unsqueeze(2), k.to(torch.bfloat16).unsqueeze(2),
-                                           v.to(torch.bfloat16).unsqueeze(2), causal=False, scale=scale)
-            return Tensor._wrap(o.float().reshape(contexts * sequence, d))
+            # contexts map onto the batch axis of the kernel (one head); z_bias is its per-key bias and
+            # attn_bias its per-(query, key) bias, both added to scale * q·k before the softmax
+            o, _ = _attn.attention_forward(
+                q.to(torch.bfloat16).unsqueeze(2), k.to(torch.bfloat16).unsqueeze(2),
+                v.to(torch.bfloat16).unsqueeze(2), causal=False, scale=scale,
+                key_bias=None if z_bias is None else z_bias._t.reshape(contexts, sequence),
+                attn_bias=None if attn_bias is None else attn_bias._t.reshape(contexts, sequence, sequence))
+            out = o.float().reshape(contexts * sequence, d)
+            self._check("scaled_dot_attention_output", out)
+            return Tensor._wrap(out)
         s = torch.matmul(q, k.transpose(1, 2)) * scale
         if z_bias is not None:
             s = s + z_bias._t.view(contexts, 1, sequence)
@@ -310,13 +318,26 @@ class Tensor:
     def layer_norm_affine(self, gamma: "Tensor", beta: "Tensor", *, epsilon: float = 1e-5, backend=None) -> "Tensor":
         if gamma.cols != self.cols or beta.cols != self.cols:
             raise TensorError("layer_norm_affine: gamma/beta must be (1, cols)")
-        y = torch.nn.functional.layer_norm(self._t, (self.cols,), gamma._t.reshape(-1), beta._t.reshape(-1), epsilon)
-        return Tensor._wrap(y)
+        return Tensor._wrap(self._layer_norm(None, gamma, beta, epsilon))
+
+    def _layer_norm(self, residual, gamma, beta, epsilon) -> torch.Tensor:
+        x = self._t
+        if x.is_cuda and self.cols % 8 == 0:
+            # LayerNorm kernel (bf16 in / out, fp32 statistics); the residual add is fused into it
+            y, _, _, _ = _norm.norm_forward(
+                x.to(torch.bfloat16).contiguous(), _gemm.cached_bf16(gamma._t).reshape(-1),
+                _gemm.cached_bf16(beta._t).reshape(-1), float(epsilon), False,
+                None if residual is None else residual._t.to(torch.bfloat16).contiguous())
+            return y.float()
+        v = x if residual is None else x + residual._t
+        return torch.nn.functional.layer_norm(v, (self.cols,), gamma._t.reshape(-1), beta._t.reshape(-1), epsilon)
 
     def layer_norm_affine_add(self, residual: "Tensor", gamma: "Tensor", beta: "Tensor", *,
                               epsilon: float = 1e-5, backend=None) -> "Tensor":
         self._same_shape(residual, "layer_norm_affine_add")
-        return Tensor._wrap(self._t + residual._t).layer_norm_affine(gamma, beta, epsilon=epsilon)
+        if gamma.cols != self.cols or beta.cols != self.cols:
+            raise TensorError("layer_norm_affine_add: gamma/beta must be (1, cols)")
+        return Tensor._wrap(self._layer_norm(residual, gamma, beta, epsilon))
 
     def gelu(self) -> "Tensor":
         return Tensor._wrap(torch.nn.functional.gelu(self._t, approximate="tanh"))
