@@ -91,8 +91,9 @@ struct StAgGemmArgs {
   int slot_enter, slot_arrive;   // slot_arrive: counter area of THIS sub_per_chunk value (world * 16 words)
   unsigned arrive_target;  // cumulative arrivals per counter: launches with this sub_per_chunk so far
                            // times st_ag_arrivals_per_launch()
-  unsigned long long trace;  // optional device buffer of [2 * grid][4] 64-bit time stamps, or 0
+  unsigned long long trace;  // optional device buffer of [3 * grid][4] 64-bit time stamps, or 0
   int stages;                // 0: choose by world size; 3 or 4: force that operand-pipeline depth
+  int local_in_place;        // x_shard IS this rank's slot of its own gather buffer: nothing is copied locally
 };
 
 // Arrivals every (source, sub-chunk) counter receives per launch: one per CTA of the grid.
@@ -136,6 +137,10 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   cm.arrive_target = a->arrive_target;
   cm.trace = reinterpret_cast<unsigned long long*>(a->trace);
   cm.sub_major = 0;
+  cm.local_in_place = a->local_in_place;
+  if (a->local_in_place &&
+      a->x_shard != a->gather_peers[a->g.rank] + (unsigned long long)a->g.rank * rows * a->K * 2)
+    return st::fail(ST_ERR_INVALID, "ag_gemm: local_in_place needs x_shard to be this rank's slot of the gather buffer");
   cm.src_shard = reinterpret_cast<const __nv_bfloat16*>(a->x_shard);
   for (int i = 0; i < st::kMaxRanks; ++i) cm.gather_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->gather_peers[i]);
   cm.gather_mc = reinterpret_cast<__nv_bfloat16*>(a->gather_mc);
@@ -188,6 +193,8 @@ struct StGemmRsArgs {
   unsigned done_target;                          // cumulative warp arrivals expected per row block
   unsigned long long stage_mc;                   // unused
   unsigned long long trace;                      // optional [grid][4] 64-bit time stamps, or 0
+  int groups;                                    // row-block groups per chunk for the remote / local interleave;
+                                                 // 0 = choose (up to 8), 1 = all remote tiles first, local last
 };
 
 ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
@@ -216,6 +223,18 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
   cm.slot_done = a->slot_done;
   cm.done_target = a->done_target;
   for (int i = 0; i < st::kMaxRanks; ++i) cm.stage_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->stage_peers[i]);
+  {
+    const int tiles_m_chunk = a->T / W / BM;
+    int G = a->groups;
+    if (G <= 0) {
+      // a group should hold at least one full wave of remote tiles, or the interleave only adds waiting
+      G = 8;
+      const int tiles_n = (a->N + BN - 1) / BN;
+      while (G > 1 && (tiles_m_chunk % G != 0 || (long long)(W - 1) * (tiles_m_chunk / G) * tiles_n < st::sm_count())) G >>= 1;
+    }
+    if (G < 1 || tiles_m_chunk % G != 0) return st::fail(ST_ERR_INVALID, "gemm_rs: groups must divide the row blocks per rank");
+    cm.rs_groups = W == 1 ? 1 : G;
+  }
   cm.rs_out = reinterpret_cast<__nv_bfloat16*>(a->out);
   cm.rs_residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
   const int tiles = (a->T / BM) * ((a->N + BN - 1) / BN);

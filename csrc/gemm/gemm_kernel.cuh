@@ -10,7 +10,9 @@
 //              while its other warps run GEMM tiles.  The TMA producer waits (bounded) for the
 //              counter of the rows it is about to load; the local rows are read from the shard
 //              itself; tiles are ordered local chunk first, then in ring order.
-//   COMM_RS    GEMM → reduce-scatter.  Tiles are ordered so that the chunk this rank owns comes last.
+//   COMM_RS    GEMM → reduce-scatter.  Tiles are ordered so that the chunk this rank owns comes last (or, with
+//              row-block groups, so that each group of the own chunk comes one group after the remote tiles of
+//              the same group: see map_tile).
 //              For the other chunks the epilogue TMA-stores each partial tile straight into the
 //              owner's staging slot (peer writes over NVLink) and counts the tile on the owner's
 //              per-row-block counter.  For its own chunk the epilogue waits (bounded) until every
@@ -52,6 +54,8 @@ struct GemmComm {
                            // writer per word) or a cumulative count (multicast path, n_comm writers)
   unsigned long long* trace;  // optional [gridDim.x][4] globaltimer stamps (start, entry, tiles/push done, end)
   int sub_major;        // tile order of the remote chunks: 0 chunk by chunk (ring), 1 sub-chunk by sub-chunk
+  int local_in_place;   // AG: the shard already lives in this rank's slot of its own gather buffer (no local copy)
+  int rs_groups;        // RS: row-block groups per chunk; remote and local tiles are interleaved group by group
   // ---- RS ----
   __nv_bfloat16* stage_peers[kMaxRanks];   // on each owner: [world][rows_per_chunk, N]
   int slot_done;        // counters: slot_done + row block within the chunk
@@ -147,6 +151,42 @@ __device__ __forceinline__ void map_tile(int t, int tiles_m, int tiles_n, int ti
       const int rr = r - blk * per_sub;
       tn = rr / msub;
       tm = ((c.g.rank + ci) % c.g.world) * tiles_m_chunk + s * msub + rr % msub;
+      return;
+    }
+    if (COMM == COMM_RS && c.rs_groups > 1) {
+      // Row blocks of every chunk are split into G groups.  Order: R(0), R(1), L(0), R(2), L(1), ..., R(G-1),
+      // L(G-2), L(G-1), where R(g) are the tiles of group g of the W-1 remote chunks (ring order) and L(g)
+      // the tiles of group g of this rank's own chunk.  A local tile needs every peer's partial of its row
+      // block; peers deliver those in their R(g), so running L(g) one group late lets the final reduction of
+      // group g ride behind the transfers of group g+1 instead of after all of them.
+      const int W = c.g.world, G = c.rs_groups;
+      const int msub = tiles_m_chunk / G;
+      const int per_l = msub * tiles_n;
+      const int per_r = (W - 1) * per_l;
+      int g, r;
+      bool local;
+      if (t < per_r) {
+        g = 0; local = false; r = t;
+      } else {
+        const int u = t - per_r;
+        const int pair = u / (per_r + per_l);
+        if (pair < G - 1) {
+          const int v = u - pair * (per_r + per_l);
+          if (v < per_r) { g = pair + 1; local = false; r = v; }
+          else { g = pair; local = true; r = v - per_r; }
+        } else {
+          g = G - 1; local = true; r = u - (G - 1) * (per_r + per_l);
+        }
+      }
+      int lm;
+      if (local) {
+        tile_coords(r, msub, tiles_n, lm, tn);
+        tm = c.g.rank * tiles_m_chunk + g * msub + lm;
+      } else {
+        const int ci = r / per_l;
+        tile_coords(r - ci * per_l, msub, tiles_n, lm, tn);
+        tm = ((c.g.rank + 1 + ci) % W) * tiles_m_chunk + g * msub + lm;
+      }
       return;
     }
     const int ci = t / per_chunk;
@@ -745,7 +785,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     volatile int* s_finished = reinterpret_cast<volatile int*>(tmem_slot + 3);
     const int W = cm.g.world, R = cm.g.rank;
     const int SUBS = cm.sub_per_chunk;
-    const int items = W * SUBS;
+    // the copy into this rank's own gather buffer comes last and is skipped when the shard already lives there
+    const int items = (cm.local_in_place ? W - 1 : W) * SUBS;
     auto dest_of = [&](int item) {
       const int q = item / SUBS;
       return q < W - 1 ? (R - 1 - q + W) % W : R;
@@ -793,7 +834,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const long long lo = min(sub_bytes, (long long)blockIdx.x * slice);
         const long long hi = min(sub_bytes, lo + slice);
         const int n_ch = (int)((hi - lo + CH - 1) / CH);     // chunks per item for this CTA (may be 0)
-        if (n_ch == 0) {
+        if (n_ch == 0 || items == 0) {
           *s_done_items = items;                              // nothing to copy: the arrivals still count
         } else {
           volatile int local_abort = 0;
@@ -841,6 +882,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 fence_proxy_async_global();
                 __threadfence_block();
                 *s_done_items = cc / n_ch + 1;
+                if (cm.trace && cc / n_ch + 1 == (W - 1) * SUBS)     // every remote store of this CTA has completed
+                  cm.trace[(2 * gridDim.x + blockIdx.x) * 4 + 0] = globaltimer_ns();
               }
             }
           }

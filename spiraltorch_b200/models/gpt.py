@@ -163,17 +163,21 @@ class GPTModel(nn.Module):
             o, n, shp = self._offsets[name]
             yield name, o, n, shp
 
-    def _norm_fwd(self, x, name, residual=None):
+    def _norm_fwd(self, x, name, residual=None, gather_key=None):
+        """``gather_key``: the all-gather this output feeds; the context may offer the shard's place inside its
+        gather buffer, which saves the fused all-gather the local copy."""
         rms = self.cfg.norm == "rms"
         beta = None if rms else self.p[name + ".beta"]
-        return norm_ops.norm_forward(x, self.p[name + ".gamma"], beta, self.cfg.norm_eps, rms, residual)
+        out = None if gather_key is None else self.tp.shard_slot(gather_key, x.shape[0], x.shape[1])
+        return norm_ops.norm_forward(x, self.p[name + ".gamma"], beta, self.cfg.norm_eps, rms, residual, out=out)
 
-    def _norm_bwd(self, dy, x, stat, name, dres=None):
+    def _norm_bwd(self, dy, x, stat, name, dres=None, gather_key=None):
         rms = self.cfg.norm == "rms"
         mean, rstd = stat
         beta_g = None if rms else self.p[name + ".beta"].main_grad
+        out = None if gather_key is None else self.tp.shard_slot(gather_key, x.shape[0], x.shape[1])
         return norm_ops.norm_backward(dy, x, self.p[name + ".gamma"], mean, rstd, rms,
-                                      self.p[name + ".gamma"].main_grad, beta_g, True, dres)
+                                      self.p[name + ".gamma"].main_grad, beta_g, True, dres, out=out)
 
     # ------------------------------------------------------------------------------------------
     def _layer_forward(self, l: int, resid, x, B: int, S: int, keep: bool):
@@ -181,17 +185,17 @@ class GPTModel(nn.Module):
         P = self.p
         act = _Act()
         if x is None:
-            y1, _, m1, r1 = self._norm_fwd(resid, f"h{l}.norm1")
+            y1, _, m1, r1 = self._norm_fwd(resid, f"h{l}.norm1", gather_key=(l, "y1"))
             h1 = resid
         else:
-            y1, h1, m1, r1 = self._norm_fwd(x, f"h{l}.norm1", residual=resid)
+            y1, h1, m1, r1 = self._norm_fwd(x, f"h{l}.norm1", residual=resid, gather_key=(l, "y1"))
         qkv, y1_full = tp.ag_gemm(y1, P[f"h{l}.qkv.weight"], key=(l, "y1"))
         if cfg.positional == "rope":
             ew.rope_(qkv, 2 * hl, D, S, cfg.rope_base)
         qkv5 = qkv.view(B, S, 3, hl, D)
         o, lse = attn_ops.attention_forward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], True)
         attn_out = tp.gemm_rs(o.view(B * S, hl * D), P[f"h{l}.proj.weight"])
-        y2, h2, m2, r2 = self._norm_fwd(attn_out, f"h{l}.norm2", residual=h1)
+        y2, h2, m2, r2 = self._norm_fwd(attn_out, f"h{l}.norm2", residual=h1, gather_key=(l, "y2"))
         u = torch.empty((y2.shape[0] * tp.world, self.ffn_local), dtype=y2.dtype, device=y2.device)
         a, y2_full = tp.ag_gemm(y2, P[f"h{l}.fc1.weight"], key=(l, "y2"), act="gelu", aux_out=u)
         mlp_out = tp.gemm_rs(a, P[f"h{l}.fc2.weight"])
@@ -211,7 +215,7 @@ class GPTModel(nn.Module):
         g(dmlp_full, act.a, a_mn=True, b_mn=True, out=w2.main_grad, accumulate=True)
         g(du, act.y2_full, a_mn=True, b_mn=True, out=w1.main_grad, accumulate=True)
         dy2 = tp.gemm_rs(du, w1, b_mn=True)
-        d_h2 = self._norm_bwd(dy2, act.h2, act.stat2, f"h{l}.norm2", dres=d_out)
+        d_h2 = self._norm_bwd(dy2, act.h2, act.stat2, f"h{l}.norm2", dres=d_out, gather_key="bwd_attn")
         o2 = act.o.view(B * S, hl * D)
         do, dh2_full = tp.ag_gemm(d_h2, wo, b_mn=True, key="bwd_attn")
         g(dh2_full, o2, a_mn=True, b_mn=True, out=wo.main_grad, accumulate=True)
@@ -224,7 +228,9 @@ class GPTModel(nn.Module):
             ew.rope_(dqkv, 2 * hl, D, S, cfg.rope_base, backward=True)
         g(dqkv, act.y1_full, a_mn=True, b_mn=True, out=wqkv.main_grad, accumulate=True)
         dy1 = tp.gemm_rs(dqkv, wqkv, b_mn=True)
-        return self._norm_bwd(dy1, act.h1, act.stat1, f"h{l}.norm1", dres=d_h2)
+        # the result is the next layer's `d_out`, which its first all-gather (key "bwd_mlp") pushes
+        return self._norm_bwd(dy1, act.h1, act.stat1, f"h{l}.norm1", dres=d_h2,
+                              gather_key="bwd_mlp" if l > 0 else None)
 
     # ------------------------------------------------------------------------------------------
     def _forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor], loss_scale: float,
@@ -245,7 +251,7 @@ class GPTModel(nn.Module):
             acts.append(act)
             if self._fused_tp and native.error_pending():
                 native.raise_on_device_error()     # a bounded wait ran out: stop now, not 2 s per kernel later
-        yf, hf, mf, rf = self._norm_fwd(x, "norm_f", residual=resid)
+        yf, hf, mf, rf = self._norm_fwd(x, "norm_f", residual=resid, gather_key="head")
         logits, yf_full = tp.ag_gemm(yf, emb, key="head")
         if targets is None:
             return logits, None
@@ -277,7 +283,7 @@ class GPTModel(nn.Module):
         g = gemm_ops.gemm
         g(dlogits, yf_full, a_mn=True, b_mn=True, out=emb.main_grad, accumulate=True)
         dyf = tp.gemm_rs(dlogits, emb, b_mn=True)
-        d = self._norm_bwd(dyf, hf, statf, "norm_f")
+        d = self._norm_bwd(dyf, hf, statf, "norm_f", gather_key="bwd_mlp")
         for l in reversed(range(cfg.n_layers)):
             d = self._layer_backward(l, acts[l], d, B, S)
             acts[l] = None

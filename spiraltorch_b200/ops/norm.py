@@ -47,14 +47,20 @@ def norm_reference(x, gamma, beta, eps, rms, residual=None):
     return y, xf, mean.squeeze(-1), rstd.squeeze(-1)
 
 
-def norm_forward(x2: torch.Tensor, gamma, beta, eps: float, rms: bool, residual=None):
-    """x2: [rows, d] bf16.  Returns (y, summed_input_or_None, mean, rstd)."""
+def norm_forward(x2: torch.Tensor, gamma, beta, eps: float, rms: bool, residual=None, out=None):
+    """x2: [rows, d] bf16.  Returns (y, summed_input_or_None, mean, rstd); ``out`` (contiguous, same shape and
+    dtype) receives y when given."""
     global launch_count
     rows, d = x2.shape
+    if out is not None:
+        assert out.shape == x2.shape and out.dtype == x2.dtype and out.is_contiguous() and out.device == x2.device
     if not native.use_native(x2):
         y, xs, mean, rstd = norm_reference(x2, gamma, beta, eps, rms, residual)
-        return y.to(x2.dtype), (xs.to(x2.dtype) if residual is not None else None), mean, rstd
-    y = torch.empty_like(x2)
+        y = y.to(x2.dtype)
+        if out is not None:
+            y = out.copy_(y)
+        return y, (xs.to(x2.dtype) if residual is not None else None), mean, rstd
+    y = torch.empty_like(x2) if out is None else out
     s = torch.empty_like(x2) if residual is not None else None
     mean = torch.empty(rows, dtype=torch.float32, device=x2.device)
     rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
@@ -68,10 +74,12 @@ def norm_forward(x2: torch.Tensor, gamma, beta, eps: float, rms: bool, residual=
 
 
 def norm_backward(dy2, x2, gamma, mean, rstd, rms: bool, dgamma: torch.Tensor,
-                  dbeta: Optional[torch.Tensor], accumulate: bool, dres=None):
-    """Writes dx (returned) and fp32 dgamma/dbeta (in place, ``+=`` when ``accumulate``)."""
+                  dbeta: Optional[torch.Tensor], accumulate: bool, dres=None, out=None):
+    """Writes dx (returned; into ``out`` when given) and fp32 dgamma/dbeta (in place, ``+=`` when ``accumulate``)."""
     global launch_count
     rows, d = x2.shape
+    if out is not None:
+        assert out.shape == x2.shape and out.dtype == x2.dtype and out.is_contiguous() and out.device == x2.device
     if not native.use_native(x2):
         xf, dyf, g = x2.float(), dy2.float(), gamma.float()
         xh = (xf - (0 if rms else mean.unsqueeze(-1))) * rstd.unsqueeze(-1)
@@ -86,8 +94,9 @@ def norm_backward(dy2, x2, gamma, mean, rstd, rms: bool, dgamma: torch.Tensor,
         if dbeta is not None:
             db = dyf.sum(0)
             dbeta.copy_(dbeta + db if accumulate else db)
-        return dx.to(x2.dtype)
-    dx = torch.empty_like(x2)
+        dx = dx.to(x2.dtype)
+        return dx if out is None else out.copy_(dx)
+    dx = torch.empty_like(x2) if out is None else out
     lib = native.lib()
     lib.st_norm_bwd_scratch_elems.restype = ctypes.c_longlong
     need = lib.st_norm_bwd_scratch_elems(ctypes.c_int(rows), ctypes.c_int(d))

@@ -50,7 +50,7 @@ class _AgGemmArgs(ctypes.Structure):
                 ("b_mn", ctypes.c_int), ("act", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("sub_per_chunk", ctypes.c_int), ("comm_ctas", ctypes.c_int),
                 ("slot_enter", ctypes.c_int), ("slot_arrive", ctypes.c_int), ("arrive_target", ctypes.c_uint),
-                ("trace", ctypes.c_ulonglong), ("stages", ctypes.c_int)]
+                ("trace", ctypes.c_ulonglong), ("stages", ctypes.c_int), ("local_in_place", ctypes.c_int)]
 
 
 class _GemmRsArgs(ctypes.Structure):
@@ -60,7 +60,7 @@ class _GemmRsArgs(ctypes.Structure):
                 ("T", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn", ctypes.c_int),
                 ("alpha", ctypes.c_float), ("slot_enter", ctypes.c_int), ("slot_done", ctypes.c_int),
                 ("done_target", ctypes.c_uint), ("stage_mc", ctypes.c_ulonglong),
-                ("trace", ctypes.c_ulonglong)]
+                ("trace", ctypes.c_ulonglong), ("groups", ctypes.c_int)]
 
 
 class _DpStepArgs(ctypes.Structure):
@@ -200,6 +200,7 @@ class FusedTPContext(TPContext):
         self.slot_arrive = {s: self.signals.alloc(MAX_RANKS * 16) for s in (1, 2, 4, 8, 16)}
         self._ag_arrivals = {s: 0 for s in (1, 2, 4, 8, 16)}
         self.ag_stages = int(os.environ.get("ST_TP_AG_STAGES", "0"))   # 0 = by world size
+        self.rs_groups = int(os.environ.get("ST_TP_RS_GROUPS", "0"))   # 0 = chosen by the launcher, 1 = no interleave
         self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
@@ -249,6 +250,13 @@ class FusedTPContext(TPContext):
             self._stage[k] = buf
         return buf
 
+    def shard_slot(self, key, rows: int, K: int) -> torch.Tensor:
+        """This rank's ``[rows, K]`` slot inside its own gather buffer for ``key``.  A producer that writes the
+        shard there (instead of into a fresh tensor) saves the all-gather its local copy: ``ag_gemm`` recognises
+        the address and pushes to the peers only."""
+        gbuf = self._gather_buffer(key, rows * self.world, K)
+        return gbuf.tensor.view(self.world, rows, K)[self.rank]
+
     # -- fused linears ---------------------------------------------------------------------
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, key="shared",
                 act=None, aux_out=None, aux_in=None, bias=None, alpha: float = 1.0):
@@ -262,6 +270,7 @@ class FusedTPContext(TPContext):
         N = w.shape[1] if b_mn else w.shape[0]
         x_shard = x_shard.contiguous()
         gbuf = self._gather_buffer(key, T, K)
+        in_place = x_shard.data_ptr() == gbuf.tensor.data_ptr() + self.rank * rows * K * 2
         y = torch.empty((T, N), dtype=torch.bfloat16, device=x_shard.device)
         sub = self.sub_per_chunk
         while sub > 1 and rows % (sub * 128) != 0:
@@ -287,6 +296,7 @@ class FusedTPContext(TPContext):
         a.slot_enter = self.slot_enter
         a.trace = 0 if self.trace is None else self.trace.data_ptr()
         a.stages = self.ag_stages
+        a.local_in_place = int(in_place)
         self._ag_arrivals[sub] += native.lib().st_ag_arrivals_per_launch()
         a.slot_arrive, a.arrive_target = self.slot_arrive[sub], self._ag_arrivals[sub] & 0xFFFFFFFF
         native.check(native.lib().st_ag_gemm(ctypes.byref(a), native.stream_ptr(x_shard.device)), "st_ag_gemm")
@@ -329,6 +339,7 @@ class FusedTPContext(TPContext):
         r.slot_enter, r.slot_done = self.slot_enter, slot
         r.done_target = (cum + _withhold) & 0xFFFFFFFF
         r.stage_mc = 0
+        r.groups = self.rs_groups
         r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")
         launch_count += 1

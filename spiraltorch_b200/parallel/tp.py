@@ -70,6 +70,11 @@ class TPContext:
         self.collective_calls += 1
         return out
 
+    def shard_slot(self, key, rows: int, K: int) -> Optional[torch.Tensor]:
+        """Where a producer may write the row shard that ``ag_gemm(..., key=key)`` will gather, or ``None`` when
+        the context has no preferred place (the fused context returns a view of its symmetric gather buffer)."""
+        return None
+
     # -- parallel linears (collective + GEMM); the fused context overrides these ------------
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, key=None, **epilogue):
         """Column-parallel product ``all_gather_rows(x_shard) @ op(w)``; returns ``(y, x_full)``."""

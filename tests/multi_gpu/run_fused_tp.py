@@ -203,7 +203,7 @@ def main():
         start, in us) the slowest CTA finished each phase."""
         if os.environ.get("ST_FUSED_TRACE", "0") != "1":
             return
-        fused.trace = torch.zeros(320, 4, dtype=torch.int64, device=dev)
+        fused.trace = torch.zeros(480, 4, dtype=torch.int64, device=dev)
         dist.barrier()
         torch.cuda.synchronize()
         fn()
@@ -211,11 +211,15 @@ def main():
         tr = fused.trace.cpu()
         fused.trace = None
         if rank == 0:
-            used = tr[tr[:, 0] > 0]
-            t0 = used[:, 0].min().item()
-            comm = used[used[:, 3] == 0]
-            gem = used[used[:, 3] > 0]
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            rows_g, rows_c, rows_r = tr[:sms], tr[sms:2 * sms], tr[2 * sms:3 * sms]
+            gem = rows_g[rows_g[:, 0] > 0]
+            comm = rows_c[rows_c[:, 0] > 0]
+            remote = rows_r[rows_r[:, 0] > 0][:, 0]
+            t0 = min(gem[:, 0].min().item(), comm[:, 0].min().item() if len(comm) else 1 << 62)
             msg = f"TRACE {label}: "
+            if len(remote):
+                msg += f"remote stores done {(remote.min().item() - t0) / 1e3:.1f}..{(remote.max().item() - t0) / 1e3:.1f}; "
             if len(comm) and label.startswith("gemm_rs"):
                 msg += (f"first local tile reached {(comm[:, 0].min().item() - t0) / 1e3:.1f}..{(comm[:, 0].max().item() - t0) / 1e3:.1f} "
                         f"peers' partials ready {(comm[:, 1].min().item() - t0) / 1e3:.1f}..{(comm[:, 1].max().item() - t0) / 1e3:.1f}; ")
