@@ -223,6 +223,30 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const __
   }
 }
 
+// Deterministic variant: the token positions have been sorted by id (stably) on the host side, so one CTA owns
+// one distinct id and adds its occurrences in position order into registers; nothing is added atomically and
+// the result does not depend on scheduling.
+__global__ void embedding_bwd_sorted_kernel(const long long* __restrict__ uniq_ids, const long long* __restrict__ seg_start,
+                                            const long long* __restrict__ seg_count, const long long* __restrict__ perm,
+                                            const __nv_bfloat16* __restrict__ dy, float* __restrict__ dW, int d,
+                                            int vocab_start, int vocab_local) {
+  const long long id = uniq_ids[blockIdx.x] - vocab_start;
+  if (id < 0 || id >= vocab_local) return;
+  const long long start = seg_start[blockIdx.x], count = seg_count[blockIdx.x];
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long j = 0; j < count; ++j) {
+      float g[8];
+      load8(dy + perm[start + j] * d + c, g);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += g[k];
+    }
+    float* w = dW + id * d + c;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w[k] += acc[k];
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // Row softmax (fp32 in/out, any width) with optional hardmax mask — Tensor API parity.
 // ------------------------------------------------------------------------------------
@@ -449,6 +473,20 @@ ST_API int st_embedding_bwd(const long long* idx, const void* dy, float* dW, flo
       idx, static_cast<const __nv_bfloat16*>(dy), dW, dpos, T, d, vocab_start, vocab_local,
       seq_len > 0 ? seq_len : 1,
       ((reinterpret_cast<uintptr_t>(dW) | reinterpret_cast<uintptr_t>(dpos)) & 15) == 0 ? 1 : 0);
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}
+
+// Scatter-add with a fixed summation order: `uniq_ids` / `seg_start` / `seg_count` describe the runs of equal ids in
+// the stably sorted id list and `perm` maps sorted positions back to rows of dy.
+ST_API int st_embedding_bwd_sorted(const long long* uniq_ids, const long long* seg_start, const long long* seg_count,
+                                   const long long* perm, const void* dy, float* dW, long long n_unique, int d,
+                                   int vocab_start, int vocab_local, void* stream_v) {
+  if (d & 7) return st::fail(ST_ERR_INVALID, "embedding: dim must be a multiple of 8");
+  if (n_unique <= 0) return ST_OK;
+  const int threads = d >= 2048 ? 256 : (d >= 512 ? 64 : 32);
+  embedding_bwd_sorted_kernel<<<(unsigned)n_unique, threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      uniq_ids, seg_start, seg_count, perm, static_cast<const __nv_bfloat16*>(dy), dW, d, vocab_start, vocab_local);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }

@@ -143,7 +143,8 @@ def conv3x3_wgrad(dy: torch.Tensor, x: torch.Tensor, dw_tap: torch.Tensor) -> No
         return
     a = _WgradArgs()
     a.dy, a.x, a.dw = dy.data_ptr(), x.data_ptr(), dw_tap.data_ptr()
-    a.N, a.H, a.W, a.C, a.OC, a.splits = N, H, W, C, OC, 0
+    # one CTA per (tap, tile) when the summation order must be fixed; 0 lets the launcher split the pixel loop
+    a.N, a.H, a.W, a.C, a.OC, a.splits = N, H, W, C, OC, (1 if native.deterministic_reduction() else 0)
     native.check(native.lib().st_conv3x3_wgrad(ctypes.byref(a), native.stream_ptr(x.device)), "st_conv3x3_wgrad")
     launch_count += 1
 

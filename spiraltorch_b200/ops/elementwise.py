@@ -169,6 +169,21 @@ def embedding_backward(idx: torch.Tensor, dy2: torch.Tensor, dweight: torch.Tens
         return
     assert dweight.dtype == torch.float32 and dy2.dtype == torch.bfloat16 and dy2.is_contiguous()
     flat = flat.to(torch.int64).contiguous()
+    if native.deterministic_reduction():
+        # fixed summation order: sort the positions by id (stable), one CTA per distinct id adds its rows in
+        # position order; positions are summed over the batch with a plain (deterministic) reduction
+        sorted_ids, perm = torch.sort(flat, stable=True)
+        uniq, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
+        starts = torch.cumsum(counts, 0) - counts
+        st = native.lib().st_embedding_bwd_sorted(
+            native.ptr(uniq), native.ptr(starts), native.ptr(counts), native.ptr(perm), native.ptr(dy2),
+            native.ptr(dweight), ctypes.c_longlong(uniq.numel()), ctypes.c_int(d), ctypes.c_int(vocab_start),
+            ctypes.c_int(dweight.shape[0]), native.stream_ptr(dy2.device))
+        native.check(st, "st_embedding_bwd_sorted")
+        launch_count += 1
+        if dpos is not None:
+            dpos += dy2.view(-1, seq_len, d).float().sum(0)
+        return
     st = native.lib().st_embedding_bwd(native.ptr(flat), native.ptr(dy2), native.ptr(dweight), native.ptr(dpos),
                                        ctypes.c_longlong(T), ctypes.c_int(d), ctypes.c_int(vocab_start),
                                        ctypes.c_int(dweight.shape[0]), ctypes.c_int(seq_len),

@@ -42,10 +42,9 @@ class _GemmArgs(ctypes.Structure):
 
 
 #: split the K loop of weight-gradient GEMMs whose tile count fills the SMs badly (the partial
-#: sums meet in fp32 atomics, so the summation order is not fixed); SPIRAL_DETERMINISTIC_REDUCTION
-#: turns it off
-import os as _os
-SPLIT_K = _os.environ.get("SPIRAL_DETERMINISTIC_REDUCTION", "0") in ("0", "", "false")
+#: sums meet in fp32 atomics, so the summation order is not fixed); native.deterministic_reduction()
+#: (SPIRAL_DETERMINISTIC_REDUCTION / SPIRAL_DETERMINISTIC) turns it off per call
+SPLIT_K = True
 _NUM_SMS = 148
 
 
@@ -203,7 +202,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.a_mn_major, args.b_mn_major = int(a_mn), int(b_mn)
     args.out_fp32 = int(out.dtype == torch.float32)
     args.accumulate = int(accumulate)
-    split = _split_k(M, N, K) if (SPLIT_K and accumulate and a_mn and b_mn and not batched and
+    split = _split_k(M, N, K) if (SPLIT_K and not native.deterministic_reduction() and accumulate and a_mn and b_mn and not batched and
                                   out.dtype == torch.float32 and N % 32 == 0 and out.stride(0) % 4 == 0
                                   and bias is None and residual is None and act_id == 0) else 1
     if split > 1:

@@ -160,6 +160,15 @@ def require_cuda(op: str, *tensors: Optional[torch.Tensor]) -> None:
             raise ValueError(f"{op}: operands live on different devices ({dev} and {t.device})")
 
 
+def deterministic_reduction() -> bool:
+    """``SPIRAL_DETERMINISTIC_REDUCTION`` (or the master switch ``SPIRAL_DETERMINISTIC``): reductions whose order
+    would depend on scheduling - split-K weight gradients that meet in fp32 atomics, the embedding scatter-add -
+    take their fixed-order form, so two runs give bit-identical gradients."""
+    def on(name: str) -> bool:
+        return os.environ.get(name, "0").strip().lower() not in ("0", "", "false", "off", "no")
+    return on("SPIRAL_DETERMINISTIC_REDUCTION") or on("SPIRAL_DETERMINISTIC")
+
+
 def use_native(t: torch.Tensor) -> bool:
     """CUDA tensors always take the native path; CPU tensors take the PyTorch CPU path."""
     return t.is_cuda

@@ -452,3 +452,188 @@ class VideoPipeline:
 
     def temporal_digest_window(self, window: int) -> dict:
         return _digest(self._samples[-window:] if window > 0 else [], self.config.quiescence_threshold)
+
+
+# ------------------------------------------------------------------------------------------------------
+# Transform pipeline (torchvision-like operations with a seeded RNG) and the multi-view dataset adapter.
+# Reference: TransformOperation / TransformPipeline / standard_classification_pipeline
+# (crates/st-vision/src/lib.rs:3404-3540,4170-4197), MultiViewFrame / MultiViewDatasetAdapter
+# (crates/st-vision/src/datasets/mod.rs:12-135).  Every operation runs through `preprocess`, i.e. on the
+# fused CUDA kernel for device tensors.
+# ------------------------------------------------------------------------------------------------------
+class Normalize:
+    name = "Normalize"
+
+    def __init__(self, mean: Sequence[float], std: Sequence[float]):
+        if len(mean) != len(std) or not mean or any(s == 0 for s in std):
+            raise ValueError("Normalize: mean/std must be non-empty, of equal length, with non-zero std")
+        self.mean, self.std = list(map(float, mean)), list(map(float, std))
+
+    def apply(self, img: torch.Tensor, gen: torch.Generator) -> torch.Tensor:
+        if img.shape[-3] != len(self.mean):
+            raise ValueError(f"Normalize: expected {len(self.mean)} channels, got {img.shape[-3]}")
+        m = torch.tensor(self.mean, device=img.device).view(-1, 1, 1)
+        s = torch.tensor(self.std, device=img.device).view(-1, 1, 1)
+        return (img - m) / s
+
+
+class Resize:
+    name = "Resize"
+
+    def __init__(self, height: int, width: int):
+        if height <= 0 or width <= 0:
+            raise ValueError("Resize: dimensions must be > 0")
+        self.height, self.width = height, width
+
+    def apply(self, img, gen):
+        return resize(img, self.height, self.width)
+
+
+class CenterCrop:
+    name = "CenterCrop"
+
+    def __init__(self, height: int, width: int):
+        if height <= 0 or width <= 0:
+            raise ValueError("CenterCrop: dimensions must be > 0")
+        self.height, self.width = height, width
+
+    def apply(self, img, gen):
+        return center_crop(img, self.height, self.width)
+
+
+class RandomHorizontalFlip:
+    name = "RandomHorizontalFlip"
+
+    def __init__(self, probability: float = 0.5):
+        if not 0.0 <= probability <= 1.0:
+            raise ValueError("horizontal_flip_probability must be in [0, 1]")
+        self.probability = probability
+
+    def apply(self, img, gen):
+        return horizontal_flip(img) if float(torch.rand((), generator=gen)) < self.probability else img
+
+
+class RandomColorJitter:
+    """Random factors ``1 ± amount`` for brightness / contrast / saturation and a hue rotation of up to
+    ``hue * pi``, applied in a random order (crates/st-vision/src/lib.rs:4011-4165)."""
+    name = "ColorJitter"
+
+    def __init__(self, brightness: float = 0.0, contrast: float = 0.0, saturation: float = 0.0, hue: float = 0.0):
+        if brightness < 0 or contrast < 0 or saturation < 0 or not 0.0 <= hue <= 0.5:
+            raise ValueError("color jitter amounts must be >= 0 and hue in [0, 0.5]")
+        self.brightness, self.contrast, self.saturation, self.hue = brightness, contrast, saturation, hue
+
+    def apply(self, img, gen):
+        def draw(amount):
+            return float((torch.rand((), generator=gen) * 2 - 1) * amount)
+        ops = []
+        if self.brightness > 0:
+            ops.append(ColorJitter(brightness=1.0 + draw(self.brightness)))
+        if self.contrast > 0:
+            ops.append(ColorJitter(contrast=1.0 + draw(self.contrast)))
+        if self.saturation > 0 and img.shape[-3] >= 3:
+            ops.append(ColorJitter(saturation=1.0 + draw(self.saturation)))
+        if self.hue > 0 and img.shape[-3] >= 3:
+            ops.append(ColorJitter(hue=draw(self.hue) * math.pi))
+        for i in torch.randperm(len(ops), generator=gen).tolist():
+            img = color_jitter(img, ops[i])
+        return img
+
+
+class TransformPipeline:
+    """Ordered list of transform operations sharing one seeded generator."""
+
+    def __init__(self, seed: Optional[int] = None):
+        self._ops: list = []
+        self._gen = torch.Generator()
+        self._gen.manual_seed(0 if seed is None else int(seed) & 0x7FFFFFFFFFFFFFFF)
+
+    @classmethod
+    def with_seed(cls, seed: int) -> "TransformPipeline":
+        return cls(seed)
+
+    def add(self, op) -> "TransformPipeline":
+        if not hasattr(op, "apply") or not hasattr(op, "name"):
+            raise TypeError("a transform operation needs .name and .apply(image, generator)")
+        self._ops.append(op)
+        return self
+
+    def operations(self) -> list:
+        return list(self._ops)
+
+    def __len__(self) -> int:
+        return len(self._ops)
+
+    def is_empty(self) -> bool:
+        return not self._ops
+
+    def apply(self, img: torch.Tensor) -> torch.Tensor:
+        for op in self._ops:
+            img = op.apply(img, self._gen)
+        return img
+
+
+def standard_classification_pipeline(image_size: int, seed: Optional[int] = None) -> TransformPipeline:
+    """Resize(size+32) → CenterCrop(size) → RandomHorizontalFlip(0.5) → ImageNet Normalize."""
+    return (TransformPipeline(seed)
+            .add(Resize(image_size + 32, image_size + 32)).add(CenterCrop(image_size, image_size))
+            .add(RandomHorizontalFlip(0.5)).add(Normalize([0.485, 0.456, 0.406], [0.229, 0.224, 0.225])))
+
+
+class MultiViewFrame:
+    """Rays of one camera view: origins / directions ``[rays, dims]``, colours ``[rays, 3]``, bounds ``[rays, 2]``."""
+
+    def __init__(self, origins, directions, colors, bounds):
+        o, d, c, b = (torch.as_tensor(t, dtype=torch.float32) for t in (origins, directions, colors, bounds))
+        if o.dim() != 2 or o.shape[0] == 0:
+            raise ValueError("multiview_rays: empty input")
+        if not (d.shape[0] == c.shape[0] == b.shape[0] == o.shape[0]):
+            raise ValueError("multiview frame: row counts differ")
+        if d.shape[1] != o.shape[1] or c.shape[1] != 3 or b.shape[1] != 2:
+            raise ValueError("multiview frame: directions must match origins, colours need 3 and bounds 2 columns")
+        self.origins, self.directions, self.colors, self.bounds = o, d, c, b
+
+    def __len__(self) -> int:
+        return self.origins.shape[0]
+
+
+class MultiViewDatasetAdapter:
+    def __init__(self, frames: Sequence[MultiViewFrame]):
+        frames = list(frames)
+        if not frames:
+            raise ValueError("multiview_frames: empty input")
+        self.origin_dims = frames[0].origins.shape[1]
+        if any(f.origins.shape[1] != self.origin_dims for f in frames):
+            raise ValueError("multiview frames disagree on the origin dimension")
+        self._frames = frames
+        self.set_frame_weights([1.0] * len(frames))
+
+    def num_frames(self) -> int:
+        return len(self._frames)
+
+    def frames(self) -> list:
+        return self._frames
+
+    def frame_weights(self) -> list:
+        return list(self._weights)
+
+    def set_frame_weights(self, weights: Sequence[float]) -> None:
+        w = [float(x) for x in weights]
+        if len(w) != len(self._frames):
+            raise ValueError(f"frame_weights: expected {len(self._frames)} values, got {len(w)}")
+        if any((not math.isfinite(x)) or x < 0 for x in w) or sum(w) <= 0:
+            raise ValueError("frame_weights must be finite, non-negative and not all zero")
+        self._weights = w
+
+    def sample_batch(self, gen: torch.Generator, batch_size: int) -> dict:
+        """``batch_size`` rays drawn frame-by-weight, then uniformly inside the frame."""
+        if batch_size <= 0:
+            raise ValueError("batch_size must be > 0")
+        fidx = torch.multinomial(torch.tensor(self._weights), batch_size, replacement=True, generator=gen)
+        cols = {"origins": [], "directions": [], "colors": [], "bounds": []}
+        for f in fidx.tolist():
+            fr = self._frames[f]
+            r = int(torch.randint(0, len(fr), (), generator=gen))
+            for k in cols:
+                cols[k].append(getattr(fr, k)[r])
+        return {k: torch.stack(v) for k, v in cols.items()}

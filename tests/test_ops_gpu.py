@@ -310,3 +310,26 @@ def test_module_moved_to_gpu_keeps_tapes_with_weights():
     lin.backward(st.Tensor._wrap(torch.randn(2, 4).cuda()), st.Tensor._wrap(torch.randn(2, 4).cuda()))
     lin.apply_step(1e-2)
     torch.cuda.synchronize()
+
+
+def test_deterministic_reduction_gives_bit_identical_gradients(monkeypatch):
+    """With SPIRAL_DETERMINISTIC_REDUCTION the split-K weight gradients and the embedding scatter-add take their
+    fixed-order forms: two runs of the same step give bit-identical flat gradients (and agree with the default,
+    atomics-based path to rounding)."""
+    from spiraltorch_b200.models.gpt import GPTConfig, GPTModel
+    cfg = GPTConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=2, ffn=1024, seq_len=1024, init_std=0.05)
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (8, 1024), device="cuda")       # few distinct ids: many collisions in the scatter-add
+    targets = torch.randint(0, 512, (8, 1024), device="cuda")
+
+    def run():
+        m = GPTModel(cfg, device="cuda", seed=9)
+        m.forward_backward(tokens, targets)
+        torch.cuda.synchronize()
+        return m.flat_grad.clone()
+    monkeypatch.setenv("SPIRAL_DETERMINISTIC_REDUCTION", "1")
+    a, b = run(), run()
+    assert torch.equal(a, b)
+    monkeypatch.setenv("SPIRAL_DETERMINISTIC_REDUCTION", "0")
+    c = run()
+    assert ((a - c).norm() / a.norm()).item() < 1e-3
