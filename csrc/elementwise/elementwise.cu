@@ -303,6 +303,121 @@ __global__ void row_softmax_kernel(const float* __restrict__ x, float* __restric
   }
 }
 
+// Row softmax + arg-max mask + "spiral consensus" blend and the Z-space projection of the row, in one pass over
+// the row (the reference runs three shaders: softmax, softmax_spiral_consensus.wgsl, softmax_zspace_projection.wgsl):
+//   spiral[c]  = (1 + enrichment) * (phi_conj * p[c] + phi_bias * mask[c]),
+//                enrichment = leech_scale * (entropy * ramanujan_ratio + hardmass * phi)
+//   metrics    = (entropy, hardmass, enrichment, coherence)           per row
+//   zmetrics   = (focus = sum p^2, above, here, swirl = sum p sin(c * golden_angle))  with golden-ratio bands
+struct SpiralConsts {
+  float phi, phi_conj, phi_bias, leech_scale, ramanujan_ratio, golden_angle;
+};
+
+__global__ void row_softmax_spiral_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ hard,
+                                          float* __restrict__ spiral, float* __restrict__ metrics,
+                                          float* __restrict__ zmetrics, int rows, int cols, SpiralConsts k) {
+  __shared__ float sh[32];
+  __shared__ int shi[32];
+  __shared__ float red[5][32];
+  const int row = blockIdx.x;
+  const float* xr = x + (size_t)row * cols;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float m = -INFINITY;
+  int mi = 0x7fffffff;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = xr[c];
+    if (v > m || (v == m && c < mi)) { m = v; mi = c; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+    if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+  }
+  if (l == 0) { sh[w] = m; shi[w] = mi; }
+  __syncthreads();
+  if (w == 0) {
+    m = l < nw ? sh[l] : -INFINITY;
+    mi = l < nw ? shi[l] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+      if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+    }
+    if (l == 0) { sh[0] = m; shi[0] = mi; }
+  }
+  __syncthreads();
+  m = sh[0];
+  mi = shi[0];
+  __syncthreads();
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s += __expf(xr[c] - m);
+  s = warp_sum(s);
+  if (l == 0) sh[w] = s;
+  __syncthreads();
+  if (w == 0) {
+    s = l < nw ? sh[l] : 0.0f;
+    s = warp_sum(s);
+    if (l == 0) sh[0] = s;
+  }
+  __syncthreads();
+  const float inv = 1.0f / sh[0];
+  // golden-ratio bands of the Z-space projection
+  int band_above = max(1, (int)floorf((float)cols / k.phi));
+  int band_here = max(1, (int)floorf((float)cols / (k.phi * k.phi)));
+  if (band_above >= cols) { band_above = cols; band_here = 0; }
+  else if (band_above + band_here >= cols) band_here = cols - band_above;
+  const int band_split = band_above + band_here;
+  float acc[5] = {0, 0, 0, 0, 0};   // entropy, focus, above, here, swirl
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float p = __expf(xr[c] - m) * inv;
+    y[(size_t)row * cols + c] = p;
+    if (hard) hard[(size_t)row * cols + c] = (c == mi) ? 1.0f : 0.0f;
+    if (p > 0.0f) acc[0] -= p * __logf(p);
+    acc[1] += p * p;
+    if (c < band_above) acc[2] += p;
+    else if (c < band_split) acc[3] += p;
+    acc[4] += p * __sinf((float)c * k.golden_angle);
+  }
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    const float v = warp_sum(acc[i]);
+    if (l == 0) red[i][w] = v;
+  }
+  __syncthreads();
+  if (w == 0) {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      float v = l < nw ? red[i][l] : 0.0f;
+      v = warp_sum(v);
+      if (l == 0) red[i][0] = v;
+    }
+  }
+  __syncthreads();
+  const float entropy = red[0][0], hardmass = 1.0f;
+  const float geodesic = entropy * k.ramanujan_ratio + hardmass * k.phi;
+  const float enrichment = geodesic > 1e-12f ? k.leech_scale * geodesic : 0.0f;
+  const float scale = 1.0f + enrichment;
+  if (spiral) {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float p = y[(size_t)row * cols + c];
+      spiral[(size_t)row * cols + c] = scale * (k.phi_conj * p + ((c == mi) ? k.phi_bias : 0.0f));
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (metrics) {
+      const float en = entropy > 0.0f ? fminf(1.0f, entropy / (entropy + 1.0f)) : 0.0f;
+      const float hn = fminf(1.0f, hardmass / (float)cols);
+      const float rn = enrichment != 0.0f ? fminf(1.0f, fmaxf(0.0f, enrichment / (1.0f + fabsf(enrichment)))) : 0.0f;
+      float* mr = metrics + (size_t)row * 4;
+      mr[0] = entropy; mr[1] = hardmass; mr[2] = enrichment; mr[3] = (en + hn + rn) / 3.0f;
+    }
+    if (zmetrics) {
+      float* zr = zmetrics + (size_t)row * 4;
+      zr[0] = red[1][0]; zr[1] = red[2][0]; zr[2] = red[3][0]; zr[3] = red[4][0];   // the row sums to one: no rescale
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // Cross-entropy over (a shard of) the vocabulary.
 // stats pass: per row max, sum exp(l - max), target logit (0 when the target is elsewhere).
@@ -495,6 +610,19 @@ ST_API int st_row_softmax_f32(const float* x, float* y, float* hard, int rows, i
   if (rows <= 0 || cols <= 0) return st::fail(ST_ERR_INVALID, "softmax: empty input");
   int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
   row_softmax_kernel<<<rows, threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(x, y, hard, rows, cols);
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}
+
+ST_API int st_row_softmax_spiral_f32(const float* x, float* y, float* hard, float* spiral, float* metrics,
+                                     float* zmetrics, int rows, int cols, float phi, float phi_conj, float phi_bias,
+                                     float leech_scale, float ramanujan_ratio, float golden_angle, void* stream_v) {
+  if (rows <= 0 || cols <= 0) return st::fail(ST_ERR_INVALID, "softmax: empty input");
+  if (!x || !y) return st::fail(ST_ERR_INVALID, "softmax: null pointer");
+  int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
+  SpiralConsts k{phi, phi_conj, phi_bias, leech_scale, ramanujan_ratio, golden_angle};
+  row_softmax_spiral_kernel<<<rows, threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(x, y, hard, spiral, metrics,
+                                                                                           zmetrics, rows, cols, k);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }

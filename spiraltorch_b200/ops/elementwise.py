@@ -8,6 +8,7 @@ RoPE cache util (crates/st-core/src/util/rope_lru.rs).
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import Optional
 
 import torch
@@ -119,7 +120,8 @@ def colsum(x2: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: boo
         out = torch.zeros(cols, dtype=torch.float32, device=x2.device)
     elif not accumulate:
         out.zero_()
-    if not native.use_native(x2) or x2.dtype != torch.bfloat16 or x2.stride(-1) != 1:
+    if not native.use_native(x2) or x2.dtype != torch.bfloat16 or x2.stride(-1) != 1 or \
+            native.deterministic_reduction():      # the kernel joins its row chunks with fp32 atomics
         out += x2.float().sum(0)
         return out
     st = native.lib().st_colsum(native.ptr(x2), native.ptr(out), ctypes.c_longlong(rows), ctypes.c_int(cols),
@@ -210,3 +212,73 @@ def row_softmax(x: torch.Tensor, hardmax: bool = False):
     native.check(st, "st_row_softmax_f32")
     launch_count += 1
     return (y, h) if hardmax else y
+
+
+# ---- softmax + hardmax + spiral consensus + Z-space projection -------------------------------------------
+def _ramanujan_pi(iterations: int) -> float:
+    pref, base, factor, total, approx = (2.0 * math.sqrt(2.0)) / 9801.0, 396.0 ** 4, 1.0, 0.0, math.pi
+    for k in range(max(1, iterations)):
+        total += factor * (1103.0 + 26390.0 * k)
+        approx = 1.0 / (pref * total)
+        n = k + 1.0
+        factor *= ((4 * n - 3) * (4 * n - 2) * (4 * n - 1) * (4 * n)) / (n ** 4 * base)
+    return approx
+
+
+GOLDEN_RATIO = (1.0 + math.sqrt(5.0)) / 2.0
+GOLDEN_RATIO_CONJUGATE = 1.0 / GOLDEN_RATIO
+GOLDEN_RATIO_BIAS = 1.0 - GOLDEN_RATIO_CONJUGATE
+GOLDEN_ANGLE = math.pi * (3.0 - math.sqrt(5.0))
+RAMANUJAN_PI = _ramanujan_pi(6)
+RAMANUJAN_RATIO = math.pi / RAMANUJAN_PI
+RAMANUJAN_DELTA = abs(RAMANUJAN_PI - math.pi)
+LEECH_SCALE = 0.75 * 0.0019295743094039225 * math.sqrt(24.0) * RAMANUJAN_RATIO     # projector weight, packing density, rank
+
+
+def row_softmax_spiral(x: torch.Tensor):
+    """Row softmax, arg-max mask, spiral-consensus blend and per-row metrics in one kernel launch.
+
+    Returns ``(soft, hard, spiral, metrics[rows, 4], zmetrics[rows, 4])`` with ``metrics`` columns
+    (entropy, hardmass, enrichment, coherence) and ``zmetrics`` columns (focus, above, here, swirl).
+    ``spiral = (1 + enrichment) * (phi_conj * soft + phi_bias * hard)`` with
+    ``enrichment = leech_scale * (entropy * ramanujan_ratio + hardmass * phi)`` (the stub's
+    ``_spiral_softmax_hardmax_consensus_python`` and softmax_spiral_consensus.wgsl /
+    softmax_zspace_projection.wgsl of crates/st-backend-wgpu/src/shaders)."""
+    global launch_count
+    xf = x.float().contiguous()
+    rows, cols = xf.shape
+    if not native.use_native(x):
+        soft = torch.softmax(xf, dim=-1)
+        idx = xf.argmax(dim=-1, keepdim=True)
+        hard = torch.zeros_like(soft).scatter_(1, idx, 1.0)
+        entropy = -(torch.where(soft > 0, soft * torch.log(soft.clamp(min=1e-45)), torch.zeros_like(soft))).sum(-1)
+        hardmass = hard.sum(-1)
+        geodesic = entropy * RAMANUJAN_RATIO + hardmass * GOLDEN_RATIO
+        enrichment = torch.where(geodesic > 1e-12, LEECH_SCALE * geodesic, torch.zeros_like(geodesic))
+        spiral = (1.0 + enrichment)[:, None] * (GOLDEN_RATIO_CONJUGATE * soft + GOLDEN_RATIO_BIAS * hard)
+        en = torch.where(entropy > 0, entropy / (entropy + 1.0), torch.zeros_like(entropy)).clamp(0, 1)
+        hn = (hardmass / cols).clamp(0, 1)
+        rn = torch.where(enrichment != 0, enrichment / (1.0 + enrichment.abs()), torch.zeros_like(enrichment)).clamp(0, 1)
+        metrics = torch.stack([entropy, hardmass, enrichment, (en + hn + rn) / 3.0], dim=1)
+        above_n = max(1, int(cols / GOLDEN_RATIO))
+        here_n = max(1, int(cols / (GOLDEN_RATIO * GOLDEN_RATIO)))
+        if above_n >= cols:
+            above_n, here_n = cols, 0
+        elif above_n + here_n >= cols:
+            here_n = cols - above_n
+        cidx = torch.arange(cols, device=xf.device, dtype=torch.float32)
+        zmetrics = torch.stack([(soft * soft).sum(-1), soft[:, :above_n].sum(-1),
+                                soft[:, above_n:above_n + here_n].sum(-1),
+                                (soft * torch.sin(cidx * GOLDEN_ANGLE)).sum(-1)], dim=1)
+        return soft, hard, spiral, metrics, zmetrics
+    soft, hard, spiral = torch.empty_like(xf), torch.empty_like(xf), torch.empty_like(xf)
+    metrics = torch.empty((rows, 4), dtype=torch.float32, device=xf.device)
+    zmetrics = torch.empty((rows, 4), dtype=torch.float32, device=xf.device)
+    st = native.lib().st_row_softmax_spiral_f32(
+        native.ptr(xf), native.ptr(soft), native.ptr(hard), native.ptr(spiral), native.ptr(metrics),
+        native.ptr(zmetrics), ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_float(GOLDEN_RATIO),
+        ctypes.c_float(GOLDEN_RATIO_CONJUGATE), ctypes.c_float(GOLDEN_RATIO_BIAS), ctypes.c_float(LEECH_SCALE),
+        ctypes.c_float(RAMANUJAN_RATIO), ctypes.c_float(GOLDEN_ANGLE), native.stream_ptr(xf.device))
+    native.check(st, "st_row_softmax_spiral_f32")
+    launch_count += 1
+    return soft, hard, spiral, metrics, zmetrics

@@ -53,6 +53,10 @@ def plan_rank(kind: str, rows: int, cols: int, k: int, backend: str = "auto") ->
     padded = 2
     while padded < cols:
         padded <<= 1
+    if backend == "cuda" and cols > 8192 and MODES[kind] != 2:
+        chunks = -(-cols // 8192)
+        return RankPlan(kind, rows, cols, k, "cuda", f"two_stage_smem_bitonic(chunks={chunks})", 1024,
+                        shared_bytes=8192 * 8)
     if backend == "cuda" and cols <= 8192:
         if k == 1 and MODES[kind] != 2:
             return RankPlan(kind, rows, cols, k, "cuda", "block_argmax", 256 if cols >= 1024 else 64)
@@ -88,8 +92,12 @@ def rank_select(x: torch.Tensor, k: int, kind: str = "topk"):
     rows, cols = x.shape
     if k < 0 or k > max(cols, 0) and cols > 0 and k > cols:
         raise ValueError(f"k={k} exceeds cols={cols}")
-    if not native.use_native(x) or cols > 8192:
+    if not native.use_native(x):
         return rank_select_reference(x, k, mode)
+    if cols > MAX_KERNEL_COLS:
+        if mode == 2 or k == 0:
+            return rank_select_reference(x, k, mode)     # mid-k needs the global order statistics
+        return _rank_select_two_stage(x, k, kind)
     xf = x.float().contiguous()
     out_v = torch.empty((rows, k), dtype=torch.float32, device=x.device)
     out_i = torch.empty((rows, k), dtype=torch.int32, device=x.device)
@@ -99,6 +107,33 @@ def rank_select(x: torch.Tensor, k: int, kind: str = "topk"):
     native.check(st, "st_rank_select")
     launch_count += 1
     return out_v, out_i
+
+
+MAX_KERNEL_COLS = 8192      # one CTA sorts a row of at most this many (value, index) keys in shared memory
+
+
+def _rank_select_two_stage(x: torch.Tensor, k: int, kind: str):
+    """Rows wider than one CTA's shared-memory sort: select per column chunk, then select among the candidates
+    (the reference's two-stage path: rankk_exact_2ce.wgsl, crates/st-core/src/distributed/topk3_stage.rs:56).
+    Exact, including the tie rule: candidates keep chunk order and, inside a chunk, the kernel's own order, so
+    equal values still resolve to the lower column."""
+    rows, cols = x.shape
+    n_chunks = -(-cols // MAX_KERNEL_COLS)
+    width = -(-cols // n_chunks)
+    pad = n_chunks * width - cols
+    xf = x.float()
+    if pad:
+        xf = torch.cat([xf, torch.full((rows, pad), float("nan"), dtype=torch.float32, device=x.device)], dim=1)
+    kc = min(k, width)
+    cv, ci = rank_select(xf.reshape(rows * n_chunks, width), kc, kind)            # stage 1: per chunk
+    cv = cv.reshape(rows, n_chunks * kc)
+    offs = (torch.arange(n_chunks, device=x.device, dtype=torch.int32) * width).repeat_interleave(kc)[None, :]
+    ci = ci.reshape(rows, n_chunks * kc)
+    gidx = torch.where(ci >= 0, ci + offs, ci)
+    v, pos = rank_select(cv, k, kind)                                              # stage 2 (recurses if still too wide)
+    out_i = torch.gather(gidx, 1, pos.clamp(min=0).long())
+    out_i = torch.where(pos >= 0, out_i, torch.full_like(out_i, -1))
+    return v, out_i.to(torch.int32)
 
 
 def topk(x, k):

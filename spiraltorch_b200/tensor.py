@@ -280,6 +280,22 @@ class Tensor:
     def row_hardmax(self, *, backend=None) -> "Tensor":
         return self.row_softmax_hardmax()[1]
 
+    def row_softmax_hardmax_spiral(self, *, backend=None) -> tuple["Tensor", "Tensor", "Tensor", dict]:
+        """Softmax, arg-max mask, their spiral-consensus blend and the consensus metrics (one kernel on CUDA)."""
+        self._check("row_softmax_input", self._t)
+        soft, hard, spiral, metrics, _ = _ew.row_softmax_spiral(self._t)
+        means = metrics.mean(dim=0).tolist() if metrics.shape[0] else [0.0, 0.0, 0.0, 0.0]
+        report = {"phi": _ew.GOLDEN_RATIO, "phi_conjugate": _ew.GOLDEN_RATIO_CONJUGATE, "phi_bias": _ew.GOLDEN_RATIO_BIAS,
+                  "ramanujan_ratio": _ew.RAMANUJAN_RATIO, "ramanujan_delta": _ew.RAMANUJAN_DELTA,
+                  "average_enrichment": means[2], "mean_entropy": means[0], "mean_hardmass": means[1],
+                  "spiral_coherence": means[3]}
+        return Tensor._wrap(soft), Tensor._wrap(hard), Tensor._wrap(spiral), report
+
+    def row_softmax_zspace_projection(self, *, backend=None) -> "Tensor":
+        """Per-row Z-space summary of the softmax: columns (focus, above, here, swirl) over golden-ratio bands
+        (crates/st-backend-wgpu/src/shaders/softmax_zspace_projection.wgsl)."""
+        return Tensor._wrap(_ew.row_softmax_spiral(self._t)[4])
+
     def scaled_dot_attention(self, keys: "Tensor", values: "Tensor", *, contexts: int, sequence: int,
                              scale: Optional[float] = None, z_bias: Optional["Tensor"] = None,
                              attn_bias: Optional["Tensor"] = None, backend=None) -> "Tensor":

@@ -49,6 +49,25 @@ def test_rank_kernels_match_cpu(rows, cols, k):
         assert torch.equal(torch.nan_to_num(cv, nan=-7.0), torch.nan_to_num(gv.cpu(), nan=-7.0))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,k", [(5, 50304, 40), (3, 20000, 1), (2, 9000, 2500), (2, 70000, 5000)])
+def test_rank_two_stage_for_wide_rows_matches_cpu(rows, cols, k):
+    """Rows wider than one CTA's shared-memory sort (a 50,304-wide vocabulary row) stay on the kernel: select per
+    column chunk, then among the candidates; values, indices and the lower-column tie rule must match the CPU path."""
+    torch.manual_seed(1)
+    x = torch.randn(rows, cols)
+    x[0, 100:110] = float("nan")
+    x[:, 8191] = x[:, 8193] = x[:, 17] = 9.0          # ties across chunk boundaries, all in the top
+    before = R.launch_count
+    for kind in ("topk", "bottomk"):
+        cv, ci = R.rank_select(x, k, kind)
+        gv, gi = R.rank_select(x.cuda(), k, kind)
+        assert torch.equal(ci, gi.cpu()), kind
+        assert torch.equal(torch.nan_to_num(cv, nan=-7.0), torch.nan_to_num(gv.cpu(), nan=-7.0))
+    assert R.launch_count - before >= 4               # two stages per call, on the kernel
+    assert R.plan_rank("topk", rows, cols, k, backend="cuda").kernel.startswith("two_stage")
+
+
 @pytest.mark.parametrize("dev", _dev_params())
 def test_compaction(dev):
     x = torch.tensor([[0.1, 5.0, 0.3, NAN, 0.2, -1.0], [9.0, 9.0, 9.0, 9.0, 9.0, 9.0]], device=dev)
