@@ -125,6 +125,8 @@ def _rank_select_two_stage(x: torch.Tensor, k: int, kind: str):
     if pad:
         xf = torch.cat([xf, torch.full((rows, pad), float("nan"), dtype=torch.float32, device=x.device)], dim=1)
     kc = min(k, width)
+    if n_chunks * kc >= cols:      # k is so large that a chunk pass would not shrink the row: sort it once
+        return rank_select_reference(x, k, MODES[kind])
     cv, ci = rank_select(xf.reshape(rows * n_chunks, width), kc, kind)            # stage 1: per chunk
     cv = cv.reshape(rows, n_chunks * kc)
     offs = (torch.arange(n_chunks, device=x.device, dtype=torch.int32) * width).repeat_interleave(kc)[None, :]
