@@ -579,11 +579,9 @@ class SpiralRnn(_Recurrent):
         super().__init__(name, input_dim, hidden_dim, steps, 1)
 
     def _fwd(self, x, p):
-        xs = self._split(x)
-        h = torch.zeros(x.shape[0], self.hidden_dim, dtype=x.dtype, device=x.device)
-        for t in range(self.steps):
-            h = torch.tanh(xs[:, t] @ p[f"{self.name}::w_ih"] + h @ p[f"{self.name}::w_hh"] + p[f"{self.name}::bias"])
-        return h
+        # one launch for the whole sequence on CUDA (csrc/recurrent/scan.cu); the step loop on CPU
+        return _rec.rnn_sequence(self._split(x), p[f"{self.name}::w_ih"], p[f"{self.name}::w_hh"],
+                                 p[f"{self.name}::bias"], "tanh")
 
 
 class Lstm(_Recurrent):
@@ -593,14 +591,8 @@ class Lstm(_Recurrent):
         super().__init__(name, input_dim, hidden_dim, steps, 4)
 
     def _fwd(self, x, p):
-        xs = self._split(x)
-        H = self.hidden_dim
-        h = torch.zeros(x.shape[0], H, dtype=x.dtype, device=x.device)
-        c = torch.zeros_like(h)
-        for t in range(self.steps):
-            z = xs[:, t] @ p[f"{self.name}::w_ih"] + h @ p[f"{self.name}::w_hh"] + p[f"{self.name}::bias"]
-            h, c = _rec.lstm_gate(z, c)           # fused gate kernel (and its BPTT step) on CUDA
-        return h
+        return _rec.rnn_sequence(self._split(x), p[f"{self.name}::w_ih"], p[f"{self.name}::w_hh"],
+                                 p[f"{self.name}::bias"], "lstm")
 
 
 class WaveRnn(_Recurrent):
@@ -611,16 +603,8 @@ class WaveRnn(_Recurrent):
         self.dilation = max(1, dilation)
 
     def _fwd(self, x, p):
-        xs = self._split(x)
-        H = self.hidden_dim
-        hs = []
-        h = torch.zeros(x.shape[0], H, dtype=x.dtype, device=x.device)
-        for t in range(self.steps):
-            skip = hs[t - self.dilation] if t >= self.dilation else torch.zeros_like(h)
-            z = xs[:, t] @ p[f"{self.name}::w_ih"] + (h + skip) @ p[f"{self.name}::w_hh"] + p[f"{self.name}::bias"]
-            h = _rec.wave_gate(z)
-            hs.append(h)
-        return h
+        return _rec.rnn_sequence(self._split(x), p[f"{self.name}::w_ih"], p[f"{self.name}::w_hh"],
+                                 p[f"{self.name}::bias"], "wave", self.dilation)
 
 
 class ZSpaceCoherenceScan(Module):

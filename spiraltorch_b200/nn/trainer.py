@@ -239,9 +239,31 @@ class ModuleTrainer:
         plugin.publish("EpochEnd", {"epoch": self.epoch, "loss": stats.average_loss})
         return stats
 
+    def enable_autopilot(self, autopilot, apply_picks=None, device_load=None) -> None:
+        """Couples an :class:`spiraltorch_b200.runtime.autopilot.Autopilot` to the step loop: before every
+        batch the trainer builds the context (batch rows, feature columns, parameter count, device load), asks
+        for a suggestion and hands the picks to ``apply_picks(dict)``; after the step it reports the step's
+        :class:`StepMetrics` so that the bandit is credited and the device profile committed
+        (the per-step hooks of crates/st-nn/src/trainer.rs:8100-8500)."""
+        self.autopilot, self._apply_picks, self._device_load = autopilot, apply_picks, device_load
+        self.last_autopilot_picks: dict = {}
+
+    def _autopilot_before(self, module, x) -> None:
+        ap = getattr(self, "autopilot", None)
+        if ap is None:
+            return
+        rows, cols = x.shape()
+        load = float(self._device_load()) if self._device_load is not None else 0.0
+        extras = [(n, 0.0) for n in ap.extra_features]
+        ctx = ap.build_context(max(1, rows), max(1, cols), max(1, len(module.parameters())), load, extras)
+        self.last_autopilot_picks = dict(ap.suggest(ctx)) if ctx else {}
+        if self._apply_picks is not None and self.last_autopilot_picks:
+            self._apply_picks(self.last_autopilot_picks)
+
     def _train_batches(self, module, loss, batches, schedule, stats) -> None:
         for x, y in batches:
             t0 = time.perf_counter()
+            self._autopilot_before(module, x)
             pred = module.forward(x)
             value = loss.forward(pred, y)
             grad = loss.backward(pred, y)
@@ -268,6 +290,8 @@ class ModuleTrainer:
                                   extra={"loss": lv, **({f"band_{k}": v for k, v in (self.last_band_energy or {}).items()})})
             if self.monitor is not None:
                 self.monitor.observe(metrics)
+            if getattr(self, "autopilot", None) is not None and self.autopilot.suggestion_ready:
+                self.autopilot.report(metrics)
             plugin.publish("TrainerStep", {"step": self.steps, "epoch": self.epoch, "loss": lv,
                                            "step_time_ms": metrics.step_time_ms})
 

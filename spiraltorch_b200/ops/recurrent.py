@@ -140,3 +140,118 @@ def sequence_last_step(x: torch.Tensor, steps: int, dim: int) -> torch.Tensor:
                                                     native.stream_ptr(x.device)), "st_sequence_last_step")
     launch_count += 1
     return y
+
+
+# ---- whole-sequence scans (csrc/recurrent/scan.cu) -----------------------------------------------------------
+CELLS = {"tanh": 0, "wave": 1, "lstm": 2}
+_GATES = {"tanh": 1, "wave": 2, "lstm": 4}
+
+
+class _ScanArgs(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("zx", "w_hh", "h_all", "hin_all", "z_all", "c_all", "dh_last", "dz_all",
+                                               "dhin_all")] + \
+               [(n, ctypes.c_int) for n in ("B", "T", "H", "cell", "dilation", "backward")]
+
+
+def scan_supported(hidden: int, cell: str) -> bool:
+    return bool(native.lib().st_rnn_scan_supported(ctypes.c_int(hidden), ctypes.c_int(CELLS[cell])))
+
+
+def rnn_sequence_reference(x, w_ih, w_hh, bias, cell: str, dilation: int = 1):
+    """Step-by-step PyTorch statement: ``x`` [B, T, in] → last hidden state [B, H]."""
+    B, T, _ = x.shape
+    H = w_hh.shape[0]
+    h = torch.zeros(B, H, dtype=x.dtype, device=x.device)
+    c = torch.zeros_like(h)
+    hs = []
+    for t in range(T):
+        hin = h
+        if cell == "wave" and t >= dilation:
+            hin = h + hs[t - dilation]
+        z = x[:, t] @ w_ih + hin @ w_hh + bias
+        if cell == "tanh":
+            h = torch.tanh(z)
+        elif cell == "wave":
+            h = torch.tanh(z[:, :H]) * torch.sigmoid(z[:, H:])
+        else:
+            i, f, g, o = torch.sigmoid(z[:, :H]), torch.sigmoid(z[:, H:2 * H]), torch.tanh(z[:, 2 * H:3 * H]), \
+                torch.sigmoid(z[:, 3 * H:])
+            c = f * c + i * g
+            h = o * torch.tanh(c)
+        hs.append(h)
+    return h
+
+
+class _RnnSequenceFn(torch.autograd.Function):
+    """Input projection for all steps as one GEMM, the recurrence over all steps as one kernel launch; the backward
+    is one BPTT launch followed by three GEMMs (dW_hh, dW_ih, dx) and a column sum (db)."""
+
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, bias, cell, dilation):
+        global launch_count
+        from . import gemm as G
+        B, T, I = x.shape
+        H = w_hh.shape[0]
+        GH = _GATES[cell] * H
+        dev = x.device
+        xb = x.detach().reshape(B * T, I).to(torch.bfloat16).contiguous()
+        wib = G.cached_bf16(w_ih)
+        zx = G.gemm(xb, wib, b_mn=True, bias=G.cached_bf16(bias).reshape(-1), out_dtype=torch.float32)   # [B*T, GH]
+        whh = w_hh.detach().float().contiguous()
+        h_all = torch.empty((B, T, H), dtype=torch.float32, device=dev)
+        hin_all = torch.empty_like(h_all)
+        z_all = torch.empty((B, T, GH), dtype=torch.float32, device=dev)
+        c_all = torch.empty_like(h_all) if cell == "lstm" else None
+        a = _ScanArgs()
+        a.zx, a.w_hh, a.h_all, a.hin_all, a.z_all = zx.data_ptr(), whh.data_ptr(), h_all.data_ptr(), \
+            hin_all.data_ptr(), z_all.data_ptr()
+        a.c_all = None if c_all is None else c_all.data_ptr()
+        a.B, a.T, a.H, a.cell, a.dilation, a.backward = B, T, H, CELLS[cell], int(dilation), 0
+        native.check(native.lib().st_rnn_scan(ctypes.byref(a), native.stream_ptr(dev)), "st_rnn_scan")
+        launch_count += 1
+        ctx.save_for_backward(xb, wib, whh, h_all, hin_all, z_all, c_all)
+        ctx.meta = (B, T, I, H, GH, cell, int(dilation))
+        return h_all[:, -1].clone()
+
+    @staticmethod
+    def backward(ctx, dh_last):
+        global launch_count
+        from . import elementwise as E
+        from . import gemm as G
+        xb, wib, whh, h_all, hin_all, z_all, c_all = ctx.saved_tensors
+        B, T, I, H, GH, cell, dilation = ctx.meta
+        dev = xb.device
+        dz_all = torch.empty((B, T, GH), dtype=torch.float32, device=dev)
+        dhin_all = torch.empty((B, T, H), dtype=torch.float32, device=dev)
+        dh = dh_last.detach().float().contiguous()
+        a = _ScanArgs()
+        a.zx, a.w_hh, a.h_all, a.hin_all, a.z_all = z_all.data_ptr(), whh.data_ptr(), h_all.data_ptr(), \
+            hin_all.data_ptr(), z_all.data_ptr()
+        a.c_all = None if c_all is None else c_all.data_ptr()
+        a.dh_last, a.dz_all, a.dhin_all = dh.data_ptr(), dz_all.data_ptr(), dhin_all.data_ptr()
+        a.B, a.T, a.H, a.cell, a.dilation, a.backward = B, T, H, CELLS[cell], dilation, 1
+        native.check(native.lib().st_rnn_scan(ctypes.byref(a), native.stream_ptr(dev)), "st_rnn_scan")
+        launch_count += 1
+        dzb = dz_all.reshape(B * T, GH).to(torch.bfloat16)
+        dx = dw_ih = dw_hh = db = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(dzb, wib, out_dtype=torch.float32).reshape(B, T, I)                  # dz · W_ihᵀ
+        if ctx.needs_input_grad[1]:
+            dw_ih = G.gemm(xb, dzb, a_mn=True, b_mn=True, out_dtype=torch.float32)           # xᵀ · dz
+        if ctx.needs_input_grad[2]:
+            hinb = hin_all.reshape(B * T, H).to(torch.bfloat16)
+            dw_hh = G.gemm(hinb, dzb, a_mn=True, b_mn=True, out_dtype=torch.float32)         # hinᵀ · dz
+        if ctx.needs_input_grad[3]:
+            db = E.colsum(dzb).reshape(1, GH)
+        return dx, dw_ih, dw_hh, db, None, None
+
+
+def rnn_sequence(x: torch.Tensor, w_ih: torch.Tensor, w_hh: torch.Tensor, bias: torch.Tensor, cell: str,
+                 dilation: int = 1) -> torch.Tensor:
+    """Last hidden state of an Elman (``"tanh"``), wave-gated (``"wave"``, dilated skip) or LSTM (``"lstm"``) layer
+    over ``x`` [B, T, in]; ``w_ih`` [in, G·H], ``w_hh`` [H, G·H], ``bias`` [1, G·H].  Differentiable."""
+    if cell not in CELLS:
+        raise ValueError(f"unknown recurrent cell '{cell}'")
+    if x.is_cuda and w_ih.is_cuda and w_hh.is_cuda and bias.is_cuda and scan_supported(w_hh.shape[0], cell):
+        return _RnnSequenceFn.apply(x, w_ih, w_hh, bias, cell, dilation)
+    return rnn_sequence_reference(x, w_ih, w_hh, bias, cell, dilation)

@@ -86,14 +86,46 @@ class BlackCat:
         return x
 
     def try_choose(self, context) -> dict:
+        return self.try_choose_with_hints(context, {})
+
+    def choice_domains(self) -> dict:
+        """Knob → the complete list of values the runtime may emit for it."""
+        return {g: list(vals) for g, vals in self.groups.items()}
+
+    def try_choose_with_hints(self, context, hints: dict) -> dict:
+        """As ``try_choose``; a hinted value wins only among candidates whose upper confidence bounds are
+        equivalent (within 1e-9), otherwise the bandit's own decision stands
+        (crates/st-core/src/runtime/autopilot.rs:61-71 ``AutoMode::Hint``)."""
+        if self._pending is not None:
+            raise BlackCatError("a selection is pending: report or abandon it first")
         x = self._context(context)
-        picks = {}
+        picks, witness = {}, {}
         for g, vals in self.groups.items():
             scores = [(self._bandits[g][v].ucb_score(x, self.exploration), -i, v) for i, v in enumerate(vals)]
-            picks[g] = max(scores)[2]          # ties go to the earlier candidate
-        self._pending = (x, dict(picks))
+            best = max(scores)
+            pick = best[2]                     # ties go to the earlier candidate
+            hinted = hints.get(g)
+            if hinted is not None and hinted in vals:
+                hs = next(sc for sc in scores if sc[2] == hinted)
+                if abs(hs[0] - best[0]) <= 1e-9:
+                    pick = hinted
+            picks[g] = pick
+            witness[g] = {"pick": pick, "score": best[0], "hinted": hinted if hinted in vals else None}
         self.selections += 1
+        self._pending = (x, dict(picks))
+        self._selection_id = self.selections
+        self._witness = {"selection_id": self.selections, "groups": witness, "exploration": self.exploration}
         return picks
+
+    def abandon_pending_selection(self) -> Optional[int]:
+        """Drop the pending selection without crediting it; returns its id (None when nothing was pending)."""
+        if self._pending is None:
+            return None
+        self._pending = None
+        return getattr(self, "_selection_id", None)
+
+    def last_selection_witness(self) -> Optional[dict]:
+        return getattr(self, "_witness", None)
 
     def choose(self, context) -> dict:
         try:

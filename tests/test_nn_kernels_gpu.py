@@ -225,3 +225,45 @@ def test_zconv_recipe_trains_on_the_kernels_and_matches_cpu():
         assert abs(a - b) < 5e-2 * max(1.0, abs(b)), (gpu_losses, cpu_losses)
     torch.cuda.synchronize()
     assert native.read_error_word()[0] == 0
+
+
+# ---- whole-sequence recurrent scans ---------------------------------------------------------------------
+@pytest.mark.parametrize("cell,hidden,dilation", [("tanh", 32, 1), ("wave", 64, 2), ("wave", 32, 1), ("wave", 16, 3),
+                                                  ("lstm", 64, 1), ("lstm", 40, 1)])
+def test_rnn_sequence_kernel_matches_step_loop(cell, hidden, dilation):
+    from spiraltorch_b200.ops import recurrent as R
+    torch.manual_seed(8)
+    B, T, I = 9, 7, 24
+    G_ = {"tanh": 1, "wave": 2, "lstm": 4}[cell]
+    x, w_ih, w_hh, b, dh = _bf(torch.randn(B, T, I), torch.randn(I, G_ * hidden) * 0.3,
+                               torch.randn(hidden, G_ * hidden) * 0.3, torch.randn(1, G_ * hidden) * 0.1,
+                               torch.randn(B, hidden))
+    f = lambda *a: R.rnn_sequence(*a, cell, dilation)       # noqa: E731
+    before = R.launch_count
+    y_g, g_g = _grads(f, [t.to(DEV) for t in (x, w_ih, w_hh, b)], dh)
+    assert R.launch_count - before == 2                     # one forward scan, one backward scan
+    y_c, g_c = _grads(f, [x, w_ih, w_hh, b], dh)
+    assert _rel(y_g, y_c) < 2e-2
+    for a, c in zip(g_g, g_c):
+        assert _rel(a, c) < 4e-2
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
+
+
+def test_wave_rnn_module_training_step_runs_on_the_scan_kernel():
+    from spiraltorch_b200.ops import recurrent as R
+    torch.manual_seed(9)
+    layer = st.nn.WaveRnn("wave", 32, 64, 16, dilation=2)
+    cpu_x, cpu_g = torch.randn(32, 16 * 32), torch.randn(32, 64)
+    ref_dx = layer.backward(st.Tensor(cpu_x), st.Tensor(cpu_g)).torch()
+    ref_acc = {p.name: p.gradient.clone() for p in layer.parameters()}
+    layer.zero_accumulators()
+    layer.to("cuda")
+    before = R.launch_count
+    y = layer.forward(st.Tensor(cpu_x).cuda())
+    dx = layer.backward(st.Tensor(cpu_x).cuda(), st.Tensor(cpu_g).cuda()).torch()
+    assert R.launch_count - before == 3                     # forward scan; forward + backward scan of backward()
+    assert y.shape() == (32, 64)
+    assert _rel(dx, ref_dx) < 5e-2
+    for p in layer.parameters():
+        assert _rel(p.gradient, ref_acc[p.name]) < 5e-2, p.name
