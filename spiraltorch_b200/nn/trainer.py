@@ -248,6 +248,28 @@ class ModuleTrainer:
         self.autopilot, self._apply_picks, self._device_load = autopilot, apply_picks, device_load
         self.last_autopilot_picks: dict = {}
 
+    def enable_psi(self, meter) -> None:
+        """Feeds a :class:`spiraltorch_b200.psi.PsiMeter` after every step (loss, global gradient norm, band
+        energy when a roundtable schedule is active) and publishes ``PsiReading`` / ``PsiThresholdCross`` events;
+        the latest reading is kept in ``last_psi``."""
+        self.psi_meter, self.last_psi = meter, None
+
+    def _psi_after(self, module, loss_value: float, grad_norm: float) -> None:
+        meter = getattr(self, "psi_meter", None)
+        if meter is None:
+            return
+        from ..psi import PsiInput
+        band = sum(abs(v) for v in (self.last_band_energy or {}).values()) if getattr(self, "last_band_energy", None) else 0.0
+        reading, events = meter.update(PsiInput(loss=loss_value, grad_l2=grad_norm, band_energy=band,
+                                                update_ratio=self.fallback_learning_rate * grad_norm))
+        self.last_psi = reading
+        if plugin.has_listeners("PsiReading"):
+            plugin.publish("PsiReading", {"step": reading.step, "total": reading.total,
+                                          "breakdown": {c.label: v for c, v in reading.breakdown.items()}})
+        for ev in events:
+            plugin.publish("PsiThresholdCross", {"component": ev.component.label, "value": ev.value,
+                                                 "threshold": ev.threshold, "up": ev.up, "step": ev.step})
+
     def _autopilot_before(self, module, x) -> None:
         ap = getattr(self, "autopilot", None)
         if ap is None:
@@ -280,8 +302,12 @@ class ModuleTrainer:
                     if not torch.isfinite(a).all():
                         module.zero_accumulators()
                         raise TensorError(f"non-finite gradient in '{p.name}'; accumulators were cleared")
+            gnorm = 0.0
+            if getattr(self, "psi_meter", None) is not None:
+                gnorm = math.sqrt(sum(float(a.pow(2).sum()) for p in module.parameters() for a in p.accumulators()))
             self.step(module)
             lv = float(value.torch().reshape(-1)[0])
+            self._psi_after(module, lv, gnorm)
             stats.batches += 1
             stats.total_loss += lv
             stats.tensor_backend["ops_total"] += 1
