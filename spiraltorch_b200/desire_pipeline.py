@@ -1,0 +1,459 @@
+"""Desire automation and pipeline: drives a :class:`DesireLagrangian` step by step, watches the integration
+phase for sustained repression pressure and fans every step (and every rewrite trigger) out to sinks - a JSONL
+logbook that can be replayed, an in-process channel, the telemetry bus, trigger and trainer bridges.
+
+Restated from crates/st-nn/src/language: ``DesireAutomation`` (automation.rs:122-330: phase-dependent mixing of
+avoidance heat / desire bias into the desire vector with weights 0.35 / 0.65, the trigger rule - integration
+phase, at least ``min_samples`` penalties, mean penalty at or above ``score_thresh``, cool-down elapsed),
+``SelfRewriteCfg`` (crates/st-core/src/config/self_rewrite.rs:11-25), ``DesireLogbook`` / ``DesireLogReplay``
+(logbook.rs:17-120), ``DesirePipelineSink`` / ``DesireChannelSink`` / ``DesireTelemetrySink`` /
+``DesireTriggerBuffer`` / ``DesireTrainerBridge`` / ``DesirePipelineBuilder`` / ``DesirePipeline``
+(pipeline.rs:40-1060,1122-1300).
+"""
+from __future__ import annotations
+
+import json
+import queue
+import threading
+import time
+from collections import deque
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from . import plugin
+from .language import INTEGRATION, OBSERVATION, DesireLagrangian, DesireSolution, DesireWeights
+
+OBSERVATION_MIX, INTEGRATION_MIX = 0.35, 0.65
+HISTORY_LIMIT, TRIGGER_EXPORT = 256, 12
+
+
+@dataclass
+class SelfRewriteCfg:
+    score_thresh: float = 0.02
+    min_samples: int = 30
+    cooldown_sec: float = 300.0
+
+
+@dataclass
+class DesireAvoidanceReport:
+    tokens: list              # token ids with the highest avoidance heat, hottest first
+    scores: list
+    observation_steps: int = 0
+
+
+@dataclass
+class DesireRewriteTrigger:
+    report: DesireAvoidanceReport
+    mean_penalty: float
+    mean_entropy: float
+    temperature: float
+    samples: int
+
+
+@dataclass
+class DesireAutomatedStep:
+    solution: DesireSolution
+    trigger: Optional[DesireRewriteTrigger] = None
+
+
+class DesireAutomation:
+    def __init__(self, desire: DesireLagrangian, cfg: Optional[SelfRewriteCfg] = None):
+        self.desire, self.cfg = desire, cfg or SelfRewriteCfg()
+        self.penalties: deque = deque()
+        self.entropies: deque = deque()
+        self.last_trigger: Optional[float] = None
+        self.vector = torch.zeros(desire.vocab_size())
+        self.trigger_count = 0
+        self._observation_steps = 0
+
+    def desire_vector(self) -> list:
+        return self.vector.tolist()
+
+    def mean_penalty(self) -> float:
+        return sum(self.penalties) / len(self.penalties) if self.penalties else 0.0
+
+    def mean_entropy(self) -> float:
+        return sum(self.entropies) / len(self.entropies) if self.entropies else 0.0
+
+    def penalty_samples(self) -> int:
+        return len(self.penalties)
+
+    def report(self, limit: int) -> DesireAvoidanceReport:
+        heat = self.desire.avoidance_heat
+        k = max(0, min(limit, int((heat > 0).sum())))
+        top = torch.topk(heat, k) if k else None
+        return DesireAvoidanceReport([] if top is None else top.indices.tolist(),
+                                     [] if top is None else top.values.tolist(), self._observation_steps)
+
+    def step(self, lm_logits, previous_token: int, concept_hint, now: Optional[float] = None) -> DesireAutomatedStep:
+        return self._drive(self.desire.step_with_scheduler(lm_logits, previous_token, concept_hint), now)
+
+    def step_with_weights(self, lm_logits, previous_token: int, concept_hint, weights: DesireWeights,
+                          now: Optional[float] = None) -> DesireAutomatedStep:
+        return self._drive(self.desire.step(lm_logits, previous_token, concept_hint, weights), now)
+
+    def _drive(self, solution: DesireSolution, now: Optional[float]) -> DesireAutomatedStep:
+        now = time.monotonic() if now is None else now
+        if solution.phase == OBSERVATION:
+            self._observation_steps += 1
+            self._mix(self.desire.avoidance_heat, OBSERVATION_MIX)
+        else:
+            self._mix(self.desire.desire_bias, INTEGRATION_MIX)
+        return DesireAutomatedStep(solution, self._evaluate(now, solution))
+
+    def _mix(self, source: torch.Tensor, mix: float) -> None:
+        total = float(source.sum())
+        if total <= 1e-6:
+            self.vector.mul_(1.0 - mix)
+            return
+        self.vector = self.vector * (1.0 - mix) + mix * (source / total).clamp(min=0.0)
+        norm = float(self.vector.sum())
+        if norm > 1e-6:
+            self.vector /= norm
+
+    def _evaluate(self, now: float, solution: DesireSolution) -> Optional[DesireRewriteTrigger]:
+        if solution.phase != INTEGRATION:
+            return None
+        limit = max(self.cfg.min_samples, HISTORY_LIMIT)
+        for store, v in ((self.penalties, solution.hypergrad_penalty), (self.entropies, solution.entropy)):
+            if v == v and abs(v) != float("inf"):
+                store.append(max(0.0, float(v)))
+                while len(store) > limit:
+                    store.popleft()
+        if len(self.penalties) < max(1, self.cfg.min_samples) or self.mean_penalty() < self.cfg.score_thresh:
+            return None
+        if self.last_trigger is not None and now < self.last_trigger + self.cfg.cooldown_sec:
+            return None
+        trig = DesireRewriteTrigger(self.report(TRIGGER_EXPORT), self.mean_penalty(), self.mean_entropy(),
+                                    solution.temperature, len(self.penalties))
+        self.last_trigger = now
+        self.trigger_count += 1
+        self.penalties.clear()
+        self.entropies.clear()
+        return trig
+
+
+# ---- logbook ---------------------------------------------------------------------------------------------------
+def _step_to_doc(step: DesireAutomatedStep) -> dict:
+    return {"solution": asdict(step.solution), "trigger": None if step.trigger is None else asdict(step.trigger)}
+
+
+def _step_from_doc(doc: dict) -> DesireAutomatedStep:
+    sol = dict(doc["solution"])
+    sol["weights"] = DesireWeights(**sol["weights"])
+    trig = doc.get("trigger")
+    if trig is not None:
+        trig = dict(trig)
+        trig["report"] = DesireAvoidanceReport(**trig["report"])
+        trig = DesireRewriteTrigger(**trig)
+    return DesireAutomatedStep(DesireSolution(**sol), trig)
+
+
+@dataclass
+class DesireLogRecord:
+    ordinal: int
+    timestamp_ms: int
+    step: DesireAutomatedStep
+
+
+class DesireLogbook:
+    """Append-only JSON-lines log of automated steps; ordinals continue across re-opens of the same file."""
+
+    def __init__(self, path, flush_every: int = 1):
+        self.path = Path(path)
+        self.flush_every = max(1, flush_every)
+        self._ordinal = 0
+        if self.path.exists():
+            with open(self.path, "r", encoding="utf-8") as f:
+                self._ordinal = sum(1 for line in f if line.strip())
+        self._fh = open(self.path, "a", encoding="utf-8")
+        self._pending = 0
+
+    def ordinal(self) -> int:
+        return self._ordinal
+
+    def record(self, step: DesireAutomatedStep, timestamp: Optional[float] = None) -> None:
+        ts = time.time() if timestamp is None else timestamp
+        self._fh.write(json.dumps({"ordinal": self._ordinal, "timestamp_ms": int(ts * 1e3), **_step_to_doc(step)}) + "\n")
+        self._ordinal += 1
+        self._pending += 1
+        if self._pending >= self.flush_every:
+            self.flush()
+
+    record_now = record
+
+    def flush(self) -> None:
+        self._fh.flush()
+        self._pending = 0
+
+    def close(self) -> None:
+        self.flush()
+        self._fh.close()
+
+
+class DesireLogReplay:
+    def __init__(self, path):
+        self.path = Path(path)
+        if not self.path.exists():
+            raise FileNotFoundError(f"desire logbook {self.path} does not exist")
+
+    @classmethod
+    def open(cls, path) -> "DesireLogReplay":
+        return cls(path)
+
+    def __iter__(self):
+        with open(self.path, "r", encoding="utf-8") as f:
+            for n, line in enumerate(f):
+                if not line.strip():
+                    continue
+                try:
+                    doc = json.loads(line)
+                    yield DesireLogRecord(int(doc["ordinal"]), int(doc["timestamp_ms"]), _step_from_doc(doc))
+                except (ValueError, KeyError, TypeError) as exc:
+                    raise ValueError(f"desire logbook {self.path} line {n + 1} is malformed: {exc}") from exc
+
+
+# ---- sinks -----------------------------------------------------------------------------------------------------
+class DesirePipelineSink:
+    def on_step(self, step: DesireAutomatedStep, timestamp: float) -> None: ...
+    def on_trigger(self, trigger: DesireRewriteTrigger, timestamp: float) -> None: ...
+    def flush(self) -> None: ...
+
+
+class _LogbookSink(DesirePipelineSink):
+    def __init__(self, logbook: DesireLogbook):
+        self.logbook = logbook
+
+    def on_step(self, step, timestamp):
+        self.logbook.record(step, timestamp)
+
+    def flush(self):
+        self.logbook.flush()
+
+
+class DesireChannelSink(DesirePipelineSink):
+    """Events as ``("step" | "trigger", payload, timestamp)`` tuples on a thread-safe queue."""
+
+    def __init__(self, sender: Optional[queue.Queue] = None):
+        self.queue = sender if sender is not None else queue.Queue()
+
+    def on_step(self, step, timestamp):
+        self.queue.put(("step", step, timestamp))
+
+    def on_trigger(self, trigger, timestamp):
+        self.queue.put(("trigger", trigger, timestamp))
+
+
+class DesireTelemetrySink(DesirePipelineSink):
+    """Publishes ``DesireStep`` / ``DesireTrigger`` on the plugin event bus."""
+
+    def on_step(self, step, timestamp):
+        s = step.solution
+        plugin.publish("DesireStep", {"phase": s.phase, "temperature": s.temperature, "entropy": s.entropy,
+                                      "hypergrad_penalty": s.hypergrad_penalty, "alpha": s.weights.alpha,
+                                      "beta": s.weights.beta, "gamma": s.weights.gamma, "lambda": s.weights.lam,
+                                      "triggered": step.trigger is not None})
+
+    def on_trigger(self, trigger, timestamp):
+        plugin.publish("DesireTrigger", {"mean_penalty": trigger.mean_penalty, "mean_entropy": trigger.mean_entropy,
+                                         "temperature": trigger.temperature, "samples": trigger.samples,
+                                         "tokens": list(trigger.report.tokens)})
+
+
+@dataclass
+class DesireTriggerEvent:
+    trigger: DesireRewriteTrigger
+    timestamp: float
+
+
+class DesireTriggerBuffer(DesirePipelineSink):
+    def __init__(self):
+        self._events: list = []
+        self._lock = threading.Lock()
+
+    def on_trigger(self, trigger, timestamp):
+        with self._lock:
+            self._events.append(DesireTriggerEvent(trigger, timestamp))
+
+    def __len__(self):
+        with self._lock:
+            return len(self._events)
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+    def drain(self) -> list:
+        with self._lock:
+            out, self._events = self._events, []
+        return out
+
+
+@dataclass
+class DesireTrainerEvent:
+    timestamp: float
+    phase: str
+    temperature: float
+    entropy: float
+    hypergrad_penalty: float
+    weights: DesireWeights
+    trigger: Optional[DesireRewriteTrigger]
+
+
+@dataclass
+class DesireTrainerSummary:
+    total: int = 0
+    observation: int = 0
+    injection: int = 0
+    integration: int = 0
+    triggers: int = 0
+    mean_entropy: float = 0.0
+    mean_temperature: float = 0.0
+    mean_penalty: float = 0.0
+    mean_alpha: float = 0.0
+    mean_beta: float = 0.0
+    mean_gamma: float = 0.0
+    mean_lambda: float = 0.0
+    trigger_mean_penalty: float = 0.0
+
+    @classmethod
+    def from_events(cls, events: list) -> Optional["DesireTrainerSummary"]:
+        if not events:
+            return None
+        n = len(events)
+        trig = [e.trigger for e in events if e.trigger is not None]
+        mean = lambda f: sum(f(e) for e in events) / n       # noqa: E731
+        return cls(n, sum(e.phase == "observation" for e in events), sum(e.phase == "injection" for e in events),
+                   sum(e.phase == "integration" for e in events), len(trig), mean(lambda e: e.entropy),
+                   mean(lambda e: e.temperature), mean(lambda e: e.hypergrad_penalty), mean(lambda e: e.weights.alpha),
+                   mean(lambda e: e.weights.beta), mean(lambda e: e.weights.gamma), mean(lambda e: e.weights.lam),
+                   sum(t.mean_penalty for t in trig) / len(trig) if trig else 0.0)
+
+
+class DesireTrainerBridge(DesirePipelineSink):
+    """Queue between the pipeline and a trainer: the trainer drains the events (or their summary) once per step."""
+
+    def __init__(self):
+        self._events: list = []
+        self._lock = threading.Lock()
+
+    def on_step(self, step, timestamp):
+        s = step.solution
+        with self._lock:
+            self._events.append(DesireTrainerEvent(timestamp, s.phase, s.temperature, s.entropy, s.hypergrad_penalty,
+                                                   s.weights, step.trigger))
+
+    def __len__(self):
+        with self._lock:
+            return len(self._events)
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+    def drain(self) -> list:
+        with self._lock:
+            out, self._events = self._events, []
+        return out
+
+    def drain_summary(self) -> Optional[DesireTrainerSummary]:
+        return DesireTrainerSummary.from_events(self.drain())
+
+    def checkpoint(self) -> list:
+        with self._lock:
+            return [asdict(e) for e in self._events]
+
+    def restore_checkpoint(self, doc: list) -> None:
+        events = []
+        for d in doc:
+            d = dict(d)
+            d["weights"] = DesireWeights(**d["weights"])
+            if d.get("trigger") is not None:
+                t = dict(d["trigger"])
+                t["report"] = DesireAvoidanceReport(**t["report"])
+                d["trigger"] = DesireRewriteTrigger(**t)
+            events.append(DesireTrainerEvent(**d))
+        with self._lock:
+            self._events = events
+
+
+# ---- pipeline --------------------------------------------------------------------------------------------------
+class DesirePipelineBuilder:
+    def __init__(self, automation: DesireAutomation):
+        self.automation, self.sinks = automation, []
+
+    def with_sink(self, sink: DesirePipelineSink) -> "DesirePipelineBuilder":
+        self.sinks.append(sink)
+        return self
+
+    def with_logbook(self, logbook: DesireLogbook): return self.with_sink(_LogbookSink(logbook))                 # noqa: E704
+    def with_channel(self, sender: queue.Queue): return self.with_sink(DesireChannelSink(sender))                # noqa: E704
+    def with_telemetry(self): return self.with_sink(DesireTelemetrySink())                                        # noqa: E704
+    def with_trainer_bridge(self, bridge: DesireTrainerBridge): return self.with_sink(bridge)                    # noqa: E704
+    def with_trigger_buffer(self, buffer: DesireTriggerBuffer): return self.with_sink(buffer)                    # noqa: E704
+
+    def build(self) -> "DesirePipeline":
+        pipe = DesirePipeline(self.automation)
+        pipe.sinks = list(self.sinks)
+        return pipe
+
+
+class DesirePipeline:
+    def __init__(self, automation: DesireAutomation):
+        self.automation = automation
+        self.sinks: list = []
+
+    @staticmethod
+    def builder(automation: DesireAutomation) -> DesirePipelineBuilder:
+        return DesirePipelineBuilder(automation)
+
+    def attach_sink(self, sink: DesirePipelineSink) -> None:
+        self.sinks.append(sink)
+
+    def attach_logbook(self, logbook): self.attach_sink(_LogbookSink(logbook))            # noqa: E704
+    def attach_channel(self, sender): self.attach_sink(DesireChannelSink(sender))         # noqa: E704
+    def attach_telemetry(self): self.attach_sink(DesireTelemetrySink())                   # noqa: E704
+    def attach_trainer_bridge(self, bridge): self.attach_sink(bridge)                     # noqa: E704
+
+    def sink_count(self) -> int:
+        return len(self.sinks)
+
+    def _dispatch(self, step: DesireAutomatedStep, timestamp: float) -> DesireAutomatedStep:
+        first = None
+        for sink in self.sinks:
+            try:
+                sink.on_step(step, timestamp)
+                if step.trigger is not None:
+                    sink.on_trigger(step.trigger, timestamp)
+            except Exception as exc:  # noqa: BLE001 - every sink sees the step; the first failure is reported after
+                first = first or exc
+        if first is not None:
+            raise first
+        return step
+
+    def step_at(self, lm_logits, previous_token: int, concept_hint, now: float, timestamp: float) -> DesireAutomatedStep:
+        return self._dispatch(self.automation.step(lm_logits, previous_token, concept_hint, now), timestamp)
+
+    def step_with_weights_at(self, lm_logits, previous_token: int, concept_hint, weights: DesireWeights, now: float,
+                             timestamp: float) -> DesireAutomatedStep:
+        return self._dispatch(self.automation.step_with_weights(lm_logits, previous_token, concept_hint, weights, now),
+                              timestamp)
+
+    def step_realtime(self, lm_logits, previous_token: int, concept_hint) -> DesireAutomatedStep:
+        return self.step_at(lm_logits, previous_token, concept_hint, time.monotonic(), time.time())
+
+    def step_with_weights_realtime(self, lm_logits, previous_token, concept_hint, weights) -> DesireAutomatedStep:
+        return self.step_with_weights_at(lm_logits, previous_token, concept_hint, weights, time.monotonic(), time.time())
+
+    def replay(self, replay: DesireLogReplay) -> int:
+        """Feeds recorded steps to the sinks again (the automation itself is not re-run); returns their count."""
+        n = 0
+        for rec in replay:
+            self._dispatch(rec.step, rec.timestamp_ms / 1e3)
+            n += 1
+        return n
+
+    def flush(self) -> None:
+        for sink in self.sinks:
+            sink.flush()

@@ -105,6 +105,7 @@ class DesireSolution:
     temperature: float
     entropy: float
     weights: DesireWeights
+    hypergrad_penalty: float = 0.0      # lambda-weighted probability mass that stayed on repressed tokens
 
 
 class DesireLagrangian:
@@ -184,8 +185,9 @@ class DesireLagrangian:
         self.avoidance_heat[active] = 0.9 * self.avoidance_heat[active] + 0.1 * probs * self.repression[active]
         self.desire_bias[active] = 0.95 * self.desire_bias[active] + 0.05 * (probs - 1.0 / k)
         self._step += 1
+        penalty = float(weights.lam * (probs * self.repression[active].clamp(min=0)).sum())
         return DesireSolution(active.tolist(), probs.tolist(), adj.tolist(), phase, t, entropy(probs.double() / probs.double().sum()),
-                              weights)
+                              weights, penalty)
 
 
 # ----------------------------------------------------------------------------------------------
