@@ -96,9 +96,7 @@ class BlackCat:
         """As ``try_choose``; a hinted value wins only among candidates whose upper confidence bounds are
         equivalent (within 1e-9), otherwise the bandit's own decision stands
         (crates/st-core/src/runtime/autopilot.rs:61-71 ``AutoMode::Hint``)."""
-        if self._pending is not None:
-            raise BlackCatError("a selection is pending: report or abandon it first")
-        x = self._context(context)
+        x = self._context(context)          # a selection still pending is replaced: only the latest one is credited
         picks, witness = {}, {}
         for g, vals in self.groups.items():
             scores = [(self._bandits[g][v].ucb_score(x, self.exploration), -i, v) for i, v in enumerate(vals)]
