@@ -195,6 +195,7 @@ struct StGemmRsArgs {
   unsigned long long trace;                      // optional [grid][4] 64-bit time stamps, or 0
   int groups;                                    // row-block groups per chunk for the remote / local interleave;
                                                  // 0 = choose (up to 8), 1 = all remote tiles first, local last
+  int lag;                                       // groups by which a local group trails its remote group (0 = 1)
 };
 
 ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
@@ -234,6 +235,7 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
     }
     if (G < 1 || tiles_m_chunk % G != 0) return st::fail(ST_ERR_INVALID, "gemm_rs: groups must divide the row blocks per rank");
     cm.rs_groups = W == 1 ? 1 : G;
+    cm.rs_lag = a->lag > 0 ? a->lag : 1;
   }
   cm.rs_out = reinterpret_cast<__nv_bfloat16*>(a->out);
   cm.rs_residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);

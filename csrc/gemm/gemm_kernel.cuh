@@ -56,6 +56,7 @@ struct GemmComm {
   int sub_major;        // tile order of the remote chunks: 0 chunk by chunk (ring), 1 sub-chunk by sub-chunk
   int local_in_place;   // AG: the shard already lives in this rank's slot of its own gather buffer (no local copy)
   int rs_groups;        // RS: row-block groups per chunk; remote and local tiles are interleaved group by group
+  int rs_lag;           // RS: groups a local group trails the remote group of the same index (>= 1)
   // ---- RS ----
   __nv_bfloat16* stage_peers[kMaxRanks];   // on each owner: [world][rows_per_chunk, N]
   int slot_done;        // counters: slot_done + row block within the chunk
@@ -154,28 +155,31 @@ __device__ __forceinline__ void map_tile(int t, int tiles_m, int tiles_n, int ti
       return;
     }
     if (COMM == COMM_RS && c.rs_groups > 1) {
-      // Row blocks of every chunk are split into G groups.  Order: R(0), R(1), L(0), R(2), L(1), ..., R(G-1),
-      // L(G-2), L(G-1), where R(g) are the tiles of group g of the W-1 remote chunks (ring order) and L(g)
-      // the tiles of group g of this rank's own chunk.  A local tile needs every peer's partial of its row
-      // block; peers deliver those in their R(g), so running L(g) one group late lets the final reduction of
-      // group g ride behind the transfers of group g+1 instead of after all of them.
+      // Row blocks of every chunk are split into G groups.  Order (lag 1): R(0), R(1), L(0), R(2), L(1), ...,
+      // R(G-1), L(G-2), L(G-1), where R(g) are the tiles of group g of the W-1 remote chunks (ring order) and
+      // L(g) the tiles of group g of this rank's own chunk.  A local tile needs every peer's partial of its row
+      // block; peers deliver those in their R(g), so running L(g) `lag` groups late lets the final reduction of
+      // group g ride behind later transfers instead of after all of them.  lag >= G is "all remote, then local".
       const int W = c.g.world, G = c.rs_groups;
+      const int lag = min(max(c.rs_lag, 1), G);          // local group g runs after remote group g + lag
       const int msub = tiles_m_chunk / G;
       const int per_l = msub * tiles_n;
       const int per_r = (W - 1) * per_l;
       int g, r;
       bool local;
-      if (t < per_r) {
-        g = 0; local = false; r = t;
+      if (t < lag * per_r) {                             // R(0) .. R(lag-1)
+        g = per_r > 0 ? t / per_r : 0; local = false; r = t - g * per_r;
       } else {
-        const int u = t - per_r;
-        const int pair = u / (per_r + per_l);
-        if (pair < G - 1) {
+        const int u = t - lag * per_r;
+        const int pairs = G - lag;                       // (R(lag + i), L(i)) for i < pairs
+        if (u < pairs * (per_r + per_l)) {
+          const int pair = u / (per_r + per_l);
           const int v = u - pair * (per_r + per_l);
-          if (v < per_r) { g = pair + 1; local = false; r = v; }
+          if (v < per_r) { g = lag + pair; local = false; r = v; }
           else { g = pair; local = true; r = v - per_r; }
-        } else {
-          g = G - 1; local = true; r = u - (G - 1) * (per_r + per_l);
+        } else {                                         // L(pairs) .. L(G-1)
+          const int w = u - pairs * (per_r + per_l);
+          g = pairs + w / per_l; local = true; r = w - (w / per_l) * per_l;
         }
       }
       int lm;

@@ -60,7 +60,7 @@ class _GemmRsArgs(ctypes.Structure):
                 ("T", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn", ctypes.c_int),
                 ("alpha", ctypes.c_float), ("slot_enter", ctypes.c_int), ("slot_done", ctypes.c_int),
                 ("done_target", ctypes.c_uint), ("stage_mc", ctypes.c_ulonglong),
-                ("trace", ctypes.c_ulonglong), ("groups", ctypes.c_int)]
+                ("trace", ctypes.c_ulonglong), ("groups", ctypes.c_int), ("lag", ctypes.c_int)]
 
 
 class _DpStepArgs(ctypes.Structure):
@@ -201,6 +201,7 @@ class FusedTPContext(TPContext):
         self._ag_arrivals = {s: 0 for s in (1, 2, 4, 8, 16)}
         self.ag_stages = int(os.environ.get("ST_TP_AG_STAGES", "0"))   # 0 = by world size
         self.rs_groups = int(os.environ.get("ST_TP_RS_GROUPS", "0"))   # 0 = chosen by the launcher, 1 = no interleave
+        self.rs_lag = int(os.environ.get("ST_TP_RS_LAG", "0"))         # 0 = one group
         self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
@@ -339,7 +340,7 @@ class FusedTPContext(TPContext):
         r.slot_enter, r.slot_done = self.slot_enter, slot
         r.done_target = (cum + _withhold) & 0xFFFFFFFF
         r.stage_mc = 0
-        r.groups = self.rs_groups
+        r.groups, r.lag = self.rs_groups, self.rs_lag
         r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")
         launch_count += 1
