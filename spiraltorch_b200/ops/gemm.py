@@ -99,24 +99,40 @@ def _reference(a, b, a_mn, b_mn, out, out_dtype, bias, act, residual, aux_out, a
     return out
 
 
-# bf16 copies of fp32 parameters, keyed by storage address and invalidated by the tensor's version counter: a
-# weight is rounded once per optimizer step instead of once per forward.
-_bf16_cache: dict = {}
-_BF16_CACHE_MAX = 512
+# bf16 copies of fp32 parameters: a weight is rounded once per optimizer step instead of once per forward.
+# Entries are keyed by storage address and invalidated by the tensor's version counter; each entry also HOLDS its
+# source tensor, so the address cannot be freed and handed to another tensor while the entry lives (a recycled
+# address with an equal version would otherwise return another tensor's values).  Least-recently-used entries are
+# dropped once the cache holds more than _BF16_CACHE_BYTES of sources and copies.
+from collections import OrderedDict as _OrderedDict
+
+_bf16_cache: "_OrderedDict" = _OrderedDict()
+_bf16_cache_bytes = 0
+_BF16_CACHE_BYTES = 1 << 30
 
 
 def cached_bf16(t: torch.Tensor) -> torch.Tensor:
     """bf16 copy of ``t`` (itself when it already is bf16), reused until ``t`` is modified in place."""
+    global _bf16_cache_bytes
     if t.dtype == torch.bfloat16:
         return t
-    key = (t.data_ptr(), tuple(t.shape), t.device)
+    key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.device)
     hit = _bf16_cache.get(key)
     if hit is not None and hit[0] == t._version:
+        _bf16_cache.move_to_end(key)
         return hit[1]
-    if len(_bf16_cache) >= _BF16_CACHE_MAX:
-        _bf16_cache.clear()
     out = t.detach().to(torch.bfloat16).contiguous()
-    _bf16_cache[key] = (t._version, out)
+    cost = t.numel() * (t.element_size() + 2)
+    if cost > _BF16_CACHE_BYTES // 4:
+        return out                                   # too large to be worth pinning
+    if hit is not None:
+        _bf16_cache_bytes -= hit[3]
+    _bf16_cache[key] = (t._version, out, t.detach(), cost)      # the detached alias keeps the storage alive
+    _bf16_cache.move_to_end(key)
+    _bf16_cache_bytes += cost
+    while _bf16_cache_bytes > _BF16_CACHE_BYTES and len(_bf16_cache) > 1:
+        _, old = _bf16_cache.popitem(last=False)
+        _bf16_cache_bytes -= old[3]
     return out
 
 
