@@ -35,6 +35,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--clip", type=float, default=0.0,
+                    help="global-norm clipping threshold applied in BOTH arms (0 = off): the fused step then runs its "
+                         "two-phase form, the NCCL arm clips in the flat optimizer")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -49,7 +52,8 @@ def main() -> int:
     fused = args.mode == "fused"
     hyper = dict(lr=3e-4, weight_decay=0.0) if args.model != "conv" else dict(lr=0.005, momentum=0.9, weight_decay=0.0)
     kind = "sgd" if args.model == "conv" else "adamw"
-    dp = FusedDataParallel(group, dev, kind=kind, overlap=not args.no_overlap, **hyper) if fused else None
+    dp = FusedDataParallel(group, dev, kind=kind, overlap=not args.no_overlap, max_grad_norm=args.clip, **hyper) \
+        if fused else None
     alloc = dp.allocator if fused else None
 
     if args.model == "charlm":
@@ -111,8 +115,8 @@ def main() -> int:
         if fused:
             dp.attach(model)
         else:
-            opt = (FlatSGD(model, lr=0.005, momentum=0.9) if kind == "sgd" else
-                   FlatAdamW(model, lr=3e-4, weight_decay=0.0, max_grad_norm=0.0))
+            opt = (FlatSGD(model, lr=0.005, momentum=0.9, max_grad_norm=args.clip) if kind == "sgd" else
+                   FlatAdamW(model, lr=3e-4, weight_decay=0.0, max_grad_norm=args.clip))
             nccl = NcclDataParallel(model, opt, group)
 
     def step(i):
@@ -149,7 +153,7 @@ def main() -> int:
         print(json.dumps({"model": args.model, "mode": args.mode, "n_gpus": world, "unit": unit,
                           "value": per_step * world * args.steps / (ms.item() / 1e3),
                           "ms_per_step": ms.item() / args.steps, "loss": float(loss), "scaling": "weak",
-                          "overlap": not args.no_overlap}))
+                          "overlap": not args.no_overlap, "clip": args.clip}))
     if world > 1:
         dist.destroy_process_group()
     return 0

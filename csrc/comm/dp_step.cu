@@ -12,6 +12,12 @@
 // writes the error word and returns without touching the remaining data.
 // The grid never exceeds the SM count, so every CTA is resident while it waits.
 //
+// Global-norm clipping needs the norm of the whole reduced gradient before any weight moves, so the step can also
+// run in two phases per bucket: phase 1 (overlapped with the backward pass) reduces the owned shard, keeps the
+// reduced gradient in a shard-sized fp32 buffer and adds its squared norm to a device word; phase 2 (after the
+// backward pass) exchanges the ranks' partial norms through a small symmetric array behind its entry rendezvous,
+// derives the clip coefficient min(1, max_norm / ||g||) in the kernel and then updates and broadcasts as above.
+//
 // Reference parity: replaces the per-parameter all-reduce-mean followed by apply_step of
 // ModuleTrainer::step (crates/st-nn/src/trainer.rs:7259-7268, :9035-9062) and the thread
 // rendezvous all-reduce (crates/spiral-selfsup/src/trainer/distributed.rs:299-430).
@@ -40,15 +46,28 @@ struct DpStepArgs {
   int slot_enter, slot_exit;         // signal slots (each `world` words wide)
   unsigned* cta_counter;             // local counter for "last CTA done"
   unsigned* err;
+  // ---- two-phase mode (global-norm clipping) ----
+  int phase;                         // 0 one pass; 1 reduce + squared norm; 2 clip + update + broadcast
+  float* gred;                       // shard-local reduced gradient (n / world floats), phases 1 and 2
+  float* sumsq_local;                // this rank's sum of squares over its shards of every bucket
+  float* norm_peers[kMaxRanks];      // symmetric [world] floats: slot r = rank r's sum of squares
+  float max_norm;                    // clip threshold (phase 2)
 };
 
 __global__ void __launch_bounds__(512)
 dp_step_kernel(const DpStepArgs a) {
   __shared__ int s_ok;
+  __shared__ float s_clip;
+  __shared__ float s_red[16];
   const int W = a.g.world, R = a.g.rank;
   // ---- entry rendezvous -------------------------------------------------------------------
   if (threadIdx.x == 0) {
     bool ok = true;
+    if (a.phase == 2 && blockIdx.x == 0) {
+      // this rank's partial norm is final (stream order): hand it to every rank before the entry signal
+      const float mine = *a.sumsq_local;
+      for (int p = 0; p < W; ++p) a.norm_peers[p][R] = mine;
+    }
     if (W > 1) {
       if (blockIdx.x == 0) {
         fence_sys();
@@ -57,6 +76,14 @@ dp_step_kernel(const DpStepArgs a) {
       for (int p = 0; p < W && ok; ++p) ok = wait_flag_ge(a.g.signals[R] + a.slot_enter + p, a.g.epoch);
     }
     s_ok = ok ? 1 : 0;
+    if (a.phase == 2 && ok) {
+      // W == 1: the slot was written by CTA 0 of this launch, which other CTAs cannot wait for - read the word itself
+      float total = 0.0f;
+      if (W == 1) total = *a.sumsq_local;
+      else for (int p = 0; p < W; ++p) total += reinterpret_cast<volatile float*>(a.norm_peers[R])[p];
+      const float norm = sqrtf(fmaxf(total, 0.0f));
+      s_clip = (a.max_norm > 0.0f && norm > a.max_norm) ? a.max_norm / (norm + 1e-6f) : 1.0f;
+    }
   }
   __syncthreads();
   if (!s_ok) {
@@ -67,11 +94,16 @@ dp_step_kernel(const DpStepArgs a) {
   // ---- owned shard: reduce, update, broadcast ------------------------------------------------
   const long long shard = a.n / W;
   const long long base = shard * R;
-  const float gs = a.grad_scale * (a.scale_ptr ? *a.scale_ptr : 1.0f);
+  // phase 2 reads gradients that phase 1 already scaled: only the clip coefficient is left to apply
+  const float gs = a.phase == 2 ? s_clip : a.grad_scale * (a.scale_ptr ? *a.scale_ptr : 1.0f);
+  float sq = 0.0f;
   for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < shard;
        i += (long long)gridDim.x * blockDim.x * 8) {
     float g[8];
-    if (a.grad_mc) {
+    if (a.phase == 2) {
+      const float4 x0 = reinterpret_cast<const float4*>(a.gred + i)[0], x1 = reinterpret_cast<const float4*>(a.gred + i)[1];
+      g[0] = x0.x; g[1] = x0.y; g[2] = x0.z; g[3] = x0.w; g[4] = x1.x; g[5] = x1.y; g[6] = x1.z; g[7] = x1.w;
+    } else if (a.grad_mc) {
       float4 x0 = multimem_ld_reduce_f32x4(a.grad_mc + base + i);
       float4 x1 = multimem_ld_reduce_f32x4(a.grad_mc + base + i + 4);
       g[0] = x0.x; g[1] = x0.y; g[2] = x0.z; g[3] = x0.w; g[4] = x1.x; g[5] = x1.y; g[6] = x1.z; g[7] = x1.w;
@@ -84,6 +116,14 @@ dp_step_kernel(const DpStepArgs a) {
         float4 x0 = src[0], x1 = src[1];
         g[0] += x0.x; g[1] += x0.y; g[2] += x0.z; g[3] += x0.w; g[4] += x1.x; g[5] += x1.y; g[6] += x1.z; g[7] += x1.w;
       }
+    }
+    if (a.phase == 1) {
+      // keep the reduced (scaled, not yet clipped) gradient and its squared norm; weights move in phase 2
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] *= gs; sq = fmaf(g[j], g[j], sq); }
+      reinterpret_cast<float4*>(a.gred + i)[0] = make_float4(g[0], g[1], g[2], g[3]);
+      reinterpret_cast<float4*>(a.gred + i)[1] = make_float4(g[4], g[5], g[6], g[7]);
+      continue;
     }
     float w[8];
     {
@@ -132,6 +172,18 @@ dp_step_kernel(const DpStepArgs a) {
     }
   }
 
+  if (a.phase == 1) {
+    // block sum of the squared norm, one atomic per CTA
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v = threadIdx.x < (blockDim.x >> 5) ? s_red[threadIdx.x] : 0.0f;
+      v = warp_sum(v);
+      if (threadIdx.x == 0) atomicAdd(a.sumsq_local, v);
+    }
+  }
+
   // ---- exit rendezvous ---------------------------------------------------------------------
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -153,6 +205,7 @@ dp_step_kernel(const DpStepArgs a) {
     if (threadIdx.x == 0) report_error(a.err, ERR_FLAG_TIMEOUT, 0xD901u);
     return;
   }
+  if (a.phase == 2) return;          // the gradients were consumed and cleared in phase 1
   // every peer has finished reading my gradients: clear the whole local bucket
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
   for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < a.n;
@@ -183,6 +236,12 @@ struct StDpStepArgs {
   int slot_enter, slot_exit;
   unsigned long long cta_counter;
   int max_ctas;
+  // two-phase mode for global-norm clipping (phase 0 = the single fused pass, all fields below unused)
+  int phase;                              // 1: reduce + squared norm into gred / sumsq_local; 2: clip + update + broadcast
+  unsigned long long gred;                // fp32 [n / world] reduced gradient of this bucket's owned shard
+  unsigned long long sumsq_local;         // fp32 word, zeroed by the caller at the start of the step
+  unsigned long long norm_peers[st::kMaxRanks];   // symmetric fp32 [world] on every rank
+  float max_norm;
 };
 
 namespace st {
@@ -227,6 +286,14 @@ ST_API int st_dp_step(const StDpStepArgs* s, void* stream_v) {
   a.slot_enter = s->slot_enter; a.slot_exit = s->slot_exit;
   a.cta_counter = reinterpret_cast<unsigned*>(s->cta_counter);
   a.err = st::error_word();
+  a.phase = s->phase;
+  a.gred = reinterpret_cast<float*>(s->gred);
+  a.sumsq_local = reinterpret_cast<float*>(s->sumsq_local);
+  for (int i = 0; i < st::kMaxRanks; ++i) a.norm_peers[i] = reinterpret_cast<float*>(s->norm_peers[i]);
+  a.max_norm = s->max_norm;
+  if (s->phase < 0 || s->phase > 2) return st::fail(ST_ERR_INVALID, "dp_step: phase must be 0, 1 or 2");
+  if (s->phase != 0 && (!s->gred || !s->sumsq_local || !s->norm_peers[s->g.rank]))
+    return st::fail(ST_ERR_INVALID, "dp_step: the two-phase mode needs gred, sumsq_local and norm_peers");
   const int threads = 512;
   long long want = (s->n / s->g.world / 8 + threads - 1) / threads;
   int cap = st::sm_count();

@@ -42,7 +42,11 @@ class SymmetricAllocator:
 
 class FusedDataParallel:
     def __init__(self, group, device, kind: str = "adamw", bucket_mb: float = 32.0, overlap: bool = True,
-                 comm_ctas: int = 32, **hyper):
+                 comm_ctas: int = 32, max_grad_norm: float = 0.0, **hyper):
+        """``max_grad_norm > 0``: clip by the global norm of the averaged gradient.  The reductions still overlap
+        the backward pass bucket by bucket; the clipped update and the weight broadcast of every bucket follow
+        once the backward pass has ended (same optimizer as the single-GPU and NCCL paths)."""
+        self.max_grad_norm = float(max_grad_norm)
         self.heap = SymmetricHeap(group, device)
         self.signals = PeerSignals(self.heap)
         self.allocator = SymmetricAllocator(self.heap)
@@ -64,7 +68,7 @@ class FusedDataParallel:
         self.model = model
         grad, w = self.allocator.buffers[torch.float32], self.allocator.buffers[model.flat_w.dtype]
         self.dp = FusedDPStep(self.heap, self.signals, grad, w, kind=self.kind, bucket_elems=self.bucket_elems,
-                              max_ctas=self.comm_ctas if self.overlap else 0)
+                              max_ctas=self.comm_ctas if self.overlap else 0, max_grad_norm=self.max_grad_norm)
         # which parameter groups does each bucket need?
         spans = {}
         for name, (o, n, _) in model._offsets.items():
@@ -90,10 +94,16 @@ class FusedDataParallel:
         if self.stream is not None and self.overlap:
             self.stream.wait_stream(torch.cuda.current_stream(self.heap.device))
             with torch.cuda.stream(self.stream):
-                self.dp.step_bucket(i, **self.hyper)
+                self._bucket_kernel(i)
+        else:
+            self._bucket_kernel(i)
+        self._launched.add(i)
+
+    def _bucket_kernel(self, i: int) -> None:
+        if self.max_grad_norm > 0:
+            self.dp.reduce_bucket(i, **self.hyper)
         else:
             self.dp.step_bucket(i, **self.hyper)
-        self._launched.add(i)
 
     def _on_ready(self, group: str) -> None:
         if not self._armed or not self.overlap:
@@ -115,6 +125,15 @@ class FusedDataParallel:
         for i in reversed(range(len(self.dp.buckets))):
             if i not in self._launched:
                 self._launch(i)
+        if self.max_grad_norm > 0:
+            # every reduction is queued: now the clipped update + weight broadcast, bucket by bucket
+            if self.stream is not None and self.overlap:
+                with torch.cuda.stream(self.stream):
+                    for i in reversed(range(len(self.dp.buckets))):
+                        self.dp.update_bucket(i, **self.hyper)
+            else:
+                for i in reversed(range(len(self.dp.buckets))):
+                    self.dp.update_bucket(i, **self.hyper)
         if self.stream is not None and self.overlap:
             torch.cuda.current_stream(self.heap.device).wait_stream(self.stream)
         self._armed = False

@@ -75,7 +75,9 @@ class _DpStepArgs(ctypes.Structure):
                 ("eps", ctypes.c_float), ("weight_decay", ctypes.c_float), ("momentum", ctypes.c_float),
                 ("step", ctypes.c_int), ("grad_scale", ctypes.c_float), ("scale_ptr", ctypes.c_ulonglong),
                 ("kind", ctypes.c_int), ("slot_enter", ctypes.c_int), ("slot_exit", ctypes.c_int),
-                ("cta_counter", ctypes.c_ulonglong), ("max_ctas", ctypes.c_int)]
+                ("cta_counter", ctypes.c_ulonglong), ("max_ctas", ctypes.c_int),
+                ("phase", ctypes.c_int), ("gred", ctypes.c_ulonglong), ("sumsq_local", ctypes.c_ulonglong),
+                ("norm_peers", ctypes.c_ulonglong * MAX_RANKS), ("max_norm", ctypes.c_float)]
 
 
 def agree_on_status(group: Optional[dist.ProcessGroup], local_ok: bool,
@@ -352,9 +354,13 @@ class FusedDPStep:
     """Data-parallel optimizer step over symmetric flat buffers (one launch per bucket)."""
 
     def __init__(self, heap: SymmetricHeap, signals: PeerSignals, grad: SymmetricBuffer, weight: SymmetricBuffer,
-                 kind: str = "adamw", bucket_elems: int = 1 << 24, max_ctas: int = 0):
+                 kind: str = "adamw", bucket_elems: int = 1 << 24, max_ctas: int = 0, max_grad_norm: float = 0.0):
+        """``max_grad_norm > 0`` selects the two-phase form: :meth:`reduce_bucket` for every bucket (these may
+        overlap the backward pass), then :meth:`update_bucket` for every bucket once all reductions are queued -
+        the update clips by the global norm of the averaged gradient, which the kernels exchange themselves."""
         self.heap, self.signals, self.grad, self.weight = heap, signals, grad, weight
         self.kind = kind
+        self.max_grad_norm = float(max_grad_norm)
         n = grad.tensor.numel()
         W = heap.world
         assert n % (8 * W) == 0, "flat length must be a multiple of 8*world"
@@ -377,14 +383,33 @@ class FusedDPStep:
         self.slot_enter = signals.alloc(MAX_RANKS)
         self.slot_exit = signals.alloc(MAX_RANKS)
         self.step_count = 0
+        self.gred, self.sumsq, self.norm_buf = None, None, None
+        if self.max_grad_norm > 0:
+            self.gred = [torch.empty(ln // W, dtype=torch.float32, device=dev) for (_, ln, *_r) in self.buckets]
+            self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            self.norm_buf = heap.empty(MAX_RANKS, torch.float32, zero=True)
 
     def begin_step(self) -> None:
         self.step_count += 1
+        if self.sumsq is not None:
+            self.sumsq.zero_()          # stream-ordered before this step's first reduction
+
+    def reduce_bucket(self, index: int, **kw) -> None:
+        self.step_bucket(index, _phase=1, **kw)
+
+    def update_bucket(self, index: int, **kw) -> None:
+        self.step_bucket(index, _phase=2, **kw)
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global norm of the averaged gradient of the last two-phase step (device scalar)."""
+        return self.norm_buf.tensor[: self.heap.world].sum().sqrt()
 
     def step_bucket(self, index: int, *, lr: float, beta1: float = 0.9, beta2: float = 0.95, eps: float = 1e-8,
                     weight_decay: float = 0.0, momentum: float = 0.9, grad_scale: float = 1.0,
-                    scale_tensor: Optional[torch.Tensor] = None) -> None:
+                    scale_tensor: Optional[torch.Tensor] = None, _phase: int = 0) -> None:
         global launch_count
+        if _phase and self.gred is None:
+            raise ValueError("the two-phase step needs max_grad_norm > 0 at construction")
         off, ln, master, m, v = self.buckets[index]
         a = _DpStepArgs()
         a.g = self.signals.next_group()
@@ -406,10 +431,21 @@ class FusedDPStep:
         a.slot_enter, a.slot_exit = self.slot_enter, self.slot_exit
         a.cta_counter = self.signals.local_counter.data_ptr()
         a.max_ctas = self.max_ctas
+        a.phase = _phase
+        if _phase:
+            a.gred, a.sumsq_local = self.gred[index].data_ptr(), self.sumsq.data_ptr()
+            a.norm_peers = self.norm_buf.peers_array()
+            a.max_norm = self.max_grad_norm
         native.check(native.lib().st_dp_step(ctypes.byref(a), native.stream_ptr(self.heap.device)), "st_dp_step")
         launch_count += 1
 
     def step(self, **kw) -> None:
         self.begin_step()
+        if self.max_grad_norm > 0:
+            for i in range(len(self.buckets)):
+                self.reduce_bucket(i, **kw)
+            for i in range(len(self.buckets)):
+                self.update_bucket(i, **kw)
+            return
         for i in range(len(self.buckets)):
             self.step_bucket(i, **kw)

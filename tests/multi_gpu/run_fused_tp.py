@@ -134,6 +134,95 @@ def main():
 
     if not only_bench:
         sec.run("dp_step", sec_dp_step)
+
+    def sec_ag_in_place():
+        # the shard written straight into this rank's slot of the gather buffer: no local copy, same result
+        torch.manual_seed(400 + rank)
+        rows, K, N = 1024, 512, 384
+        x = torch.randn(rows, K, device=dev).bfloat16()
+        w = torch.randn(N, K, device=dev).bfloat16()
+        y_ref, xf_ref = nccl.ag_gemm(x, w)
+        outs = []
+        for rep in range(2):
+            slot = fused.shard_slot("inplace", rows, K)
+            slot.copy_(x)
+            y, xf = fused.ag_gemm(slot, w, key="inplace")
+            outs.append((y, xf.clone()))
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        for y, xf in outs:
+            assert torch.equal(xf, xf_ref)
+            assert rel(y, y_ref) <= 1e-2, rel(y, y_ref)
+
+    def sec_dp_two_phase():
+        # global-norm clipping inside the fused step against all-reduce-mean + clip + AdamW
+        n = 8 * world * 4096
+        grad = fused.heap.empty(n, torch.float32)
+        wbuf = fused.heap.empty(n, torch.bfloat16)
+        torch.manual_seed(500 + rank)
+        grad.tensor.copy_(torch.randn(n, device=dev))
+        torch.manual_seed(9)
+        wbuf.tensor.copy_(torch.randn(n, device=dev).bfloat16())
+        g_ref = grad.tensor.clone()
+        dist.all_reduce(g_ref)
+        g_ref /= world
+        max_norm = 0.25 * g_ref.norm().item()
+        master = wbuf.tensor.float().clone()
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        dp = FusedDPStep(fused.heap, fused.signals, grad, wbuf, kind="adamw", bucket_elems=n // 4, max_grad_norm=max_norm)
+        dist.barrier()
+        dp.step(lr=1e-2, weight_decay=0.1)
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        norm = g_ref.norm()
+        assert abs(dp.grad_norm().item() - norm.item()) < 1e-3 * norm.item(), (dp.grad_norm().item(), norm.item())
+        O.adamw_reference(g_ref * (max_norm / (norm + 1e-6)), master, m, v, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, False)
+        assert rel(wbuf.tensor, master) < 1e-2, rel(wbuf.tensor, master)
+        assert grad.tensor.abs().max().item() == 0
+
+    def sec_distributed_topk():
+        # candidates read straight from the peers' memory (st_gather_candidates) against the all-gather path
+        from spiraltorch_b200.ops import rank as RK
+        torch.manual_seed(600)
+        full = torch.randn(6, 512 * world, device=dev)
+        full[:, 5] = full[:, 5 + 512 * (world - 1)]            # a tie across shards
+        shard = full[:, rank * 512:(rank + 1) * 512].contiguous()
+        before = RK.launch_count
+        v_p, i_p = RK.distributed_topk(shard, 37, group=dist.group.WORLD, heap=fused.heap)
+        assert RK.launch_count > before
+        v_a, i_a = RK.distributed_topk(shard, 37, group=dist.group.WORLD)
+        v_r, i_r = RK.rank_select(full, 37, "topk")
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        assert torch.equal(i_p, i_a) and torch.equal(i_p, i_r) and torch.equal(v_p, v_r)
+
+    def sec_info_nce_plain():
+        # FusedInfoNCE without a tensor-parallel context (the data-parallel benchmark's configuration)
+        from spiraltorch_b200.parallel.contrastive import FusedInfoNCE
+        torch.manual_seed(700 + rank)
+        op = FusedInfoNCE(fused.heap, fused.signals, rows=1024, dim=256, temperature=0.1)
+        base = torch.randn(1024, 256, device=dev)
+        a = torch.nn.functional.normalize(base + 0.3 * torch.randn_like(base), dim=-1).requires_grad_(True)
+        p_ = torch.nn.functional.normalize(base + 0.3 * torch.randn_like(base), dim=-1).requires_grad_(True)
+        loss = op.apply(a, p_)
+        loss.backward()
+        a2 = a.detach().bfloat16().float().requires_grad_(True)
+        parts = [torch.empty_like(a2) for _ in range(world)]
+        dist.all_gather(parts, p_.detach().bfloat16().float())
+        logits = a2 @ torch.cat(parts, 0).t() / 0.1
+        idx = torch.arange(1024, device=dev) + rank * 1024
+        ref = (torch.logsumexp(logits, -1) - logits[torch.arange(1024, device=dev), idx]).mean()
+        ref.backward()
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
+        assert rel(a.grad, a2.grad) < 5e-2, rel(a.grad, a2.grad)
+
+    if not only_bench:
+        sec.run("ag_in_place", sec_ag_in_place)
+        sec.run("dp_two_phase", sec_dp_two_phase)
+        sec.run("distributed_topk", sec_distributed_topk)
+        sec.run("info_nce_plain", sec_info_nce_plain)
     def sec_gpt():
         # small GPT step: fused vs NCCL context
         cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=8, ffn=1024, seq_len=512, init_std=0.05)

@@ -143,3 +143,35 @@ def test_contrastive_encoder_learns():
         losses.append(contrastive_step(enc, base, seed=i).item())
         opt.step()
     assert losses[-1] < losses[0] and losses[-1] < 1.0, losses
+
+
+def test_dp_step_two_phase_clips_by_global_norm_world1():
+    """Global-norm clipping inside the fused data-parallel step: reduce + squared norm per bucket, then the clipped
+    update; the result must equal clipping the whole gradient first and running the plain fused optimizer."""
+    from spiraltorch_b200.parallel.symm import FusedDPStep, PeerSignals, SymmetricHeap
+    torch.manual_seed(2)
+    heap = SymmetricHeap(None, torch.device(DEV))
+    sig = PeerSignals(heap)
+    n = 8 * 3000
+    for kind, max_norm in (("adamw", 0.5), ("sgd", 1e9)):        # one case that clips, one that does not
+        grad, w = heap.empty(n, torch.float32), heap.empty(n, torch.bfloat16)
+        grad.tensor.copy_(torch.randn(n, device=DEV) * 0.1)
+        w.tensor.copy_(torch.randn(n, device=DEV).bfloat16())
+        g0, master = grad.tensor.clone(), w.tensor.float().clone()
+        m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        dp = FusedDPStep(heap, sig, grad, w, kind=kind, bucket_elems=8192, max_grad_norm=max_norm)
+        assert len(dp.buckets) > 1
+        dp.step(lr=1e-2, weight_decay=0.1, momentum=0.9)
+        norm = g0.norm()
+        assert abs(dp.grad_norm().item() - norm.item()) < 1e-3 * norm.item()
+        gc = g0 * (max_norm / (norm + 1e-6)) if norm > max_norm else g0
+        if kind == "adamw":
+            O.adamw_reference(gc, master, m, v, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, False)
+        else:
+            m.mul_(0.9).add_(gc + 0.1 * master)
+            master.sub_(1e-2 * m)
+        assert _rel(w.tensor, master) < 1e-2
+        assert _rel(torch.cat([b[2] for b in dp.buckets]), master) < 1e-5
+        assert grad.tensor.abs().max().item() == 0
+    torch.cuda.synchronize()
+    assert native.read_error_word()[0] == 0
