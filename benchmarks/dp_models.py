@@ -35,6 +35,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the forward/backward pass from a CUDA graph (the step is launch-bound otherwise); the "
+                         "data-parallel step stays outside the graph and is not overlapped with the backward pass")
     ap.add_argument("--clip", type=float, default=0.0,
                     help="global-norm clipping threshold applied in BOTH arms (0 = off): the fused step then runs its "
                          "two-phase form, the NCCL arm clips in the flat optimizer")
@@ -50,6 +53,8 @@ def main() -> int:
     torch.manual_seed(1000 + rank)
 
     fused = args.mode == "fused"
+    if args.graph:
+        args.no_overlap = True        # hooks fire at capture time only
     hyper = dict(lr=3e-4, weight_decay=0.0) if args.model != "conv" else dict(lr=0.005, momentum=0.9, weight_decay=0.0)
     kind = "sgd" if args.model == "conv" else "adamw"
     dp = FusedDataParallel(group, dev, kind=kind, overlap=not args.no_overlap, max_grad_norm=args.clip, **hyper) \
@@ -119,6 +124,19 @@ def main() -> int:
                    FlatAdamW(model, lr=3e-4, weight_decay=0.0, max_grad_norm=args.clip))
             nccl = NcclDataParallel(model, opt, group)
 
+    if args.graph and model is not None:
+        from spiraltorch_b200.training import GraphedForwardBackward
+        if args.model == "charlm":
+            graphed = GraphedForwardBackward(model, (toks[0, :, :-1].contiguous(), toks[0, :, 1:].contiguous()))
+
+            def fwd_bwd(i):   # noqa: F811
+                return graphed(toks[i % 2, :, :-1], toks[i % 2, :, 1:])
+        else:
+            graphed = GraphedForwardBackward(model, (imgs[0], labels[0]))
+
+            def fwd_bwd(i):   # noqa: F811
+                return graphed(imgs[i % 2], labels[i % 2])
+
     def step(i):
         if model is None:
             return fwd_bwd(i)
@@ -153,7 +171,7 @@ def main() -> int:
         print(json.dumps({"model": args.model, "mode": args.mode, "n_gpus": world, "unit": unit,
                           "value": per_step * world * args.steps / (ms.item() / 1e3),
                           "ms_per_step": ms.item() / args.steps, "loss": float(loss), "scaling": "weak",
-                          "overlap": not args.no_overlap, "clip": args.clip}))
+                          "overlap": not args.no_overlap, "clip": args.clip, "cuda_graph": bool(args.graph)}))
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -86,3 +86,50 @@ class LMTrainer:
             plugin.publish("TrainerStep", {"step": self.steps, "loss": loss,
                                            "step_time_ms": (time.perf_counter() - t0) * 1e3})
         return loss
+
+
+class GraphedForwardBackward:
+    """``model.forward_backward`` captured once in a CUDA graph and replayed per micro-batch.
+
+    The small models (85 M char-LM, conv classifier) launch about a thousand kernels of a few microseconds per
+    step, so the step time is the host's launch rate; a replay issues them from the device side instead.  Inputs
+    live in static buffers (``tokens`` / ``targets`` are copied in before each replay), the loss comes back as a
+    static device scalar, and gradients accumulate into the model's ``flat_grad`` exactly as in the eager call.
+
+    Only single-rank tensor-parallel contexts can be captured: the fused collectives take their epoch and arrival
+    targets by value, which a captured graph would freeze.  Gradient hooks (``grad_ready_hook``) run at capture
+    time only, so bucket overlap of the data-parallel step is not available under a graph; the data-parallel step
+    itself stays outside the graph.
+    """
+
+    def __init__(self, model, example_inputs: tuple, warmup: int = 2, **kwargs):
+        if getattr(getattr(model, "tp", None), "world", 1) != 1:
+            raise ValueError("CUDA-graph capture needs a single-rank tensor-parallel context")
+        dev = model.flat_w.device
+        if dev.type != "cuda":
+            raise ValueError("CUDA-graph capture needs a CUDA model")
+        self.model, self.kwargs = model, kwargs
+        self.static_in = tuple(t.to(dev).clone() for t in example_inputs)
+        hook, model.grad_ready_hook = getattr(model, "grad_ready_hook", None), None
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        grads = model.flat_grad.clone()
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):             # first calls allocate scratch, tables and opt into shared memory
+                model.forward_backward(*self.static_in, **kwargs)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        native.poll()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_loss = model.forward_backward(*self.static_in, **kwargs)
+        model.flat_grad.copy_(grads)                    # the warm-up and capture passes must not count as gradients
+        model.grad_ready_hook = hook
+        self.replays = 0
+
+    def __call__(self, *inputs) -> torch.Tensor:
+        for dst, src in zip(self.static_in, inputs):
+            dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        self.replays += 1
+        return self.static_loss
