@@ -8,7 +8,8 @@ hence the large learning rates) and, given ``run_dir``, writes the run-directory
 ``zspace_vae_reconstruction.py``, ``zspace_text_vae.py`` and the Rust ``modelzoo_gnn_graph_regression`` /
 ``modelzoo_lstm_probe`` examples — same layer stacks and artefacts, smaller data — plus
 ``llm_char_coherence_wave.py``, ``maxwell_simulated_z_classification.py``, ``mellin_log_grid_classification.py``,
-``modelzoo_wave_rnn_sequence``, ``modelzoo_zspace_mixer_regression`` and the forward-only ``modelzoo_zrba_telemetry``.
+``modelzoo_wave_rnn_sequence``, ``modelzoo_zspace_mixer_regression``, the forward-only ``modelzoo_zrba_telemetry``,
+``vision_conv_pool_classification.py`` and the two-stage ``llm_char_finetune.py``.
 
     python -m spiraltorch_b200.models.recipes zconv_classification --run-dir runs/zconv
 """
@@ -32,6 +33,10 @@ def _one_hot(ids: torch.Tensor, classes: int) -> torch.Tensor:
 
 
 def _train(model, loss, batches, epochs: int, lr: float, backend: str, rd, quiet: bool):
+    if backend == "cuda":
+        # parameters and batches live on the device: every layer then runs on the sm_100a kernels
+        model.to("cuda")
+        batches = [(x.cuda(), y.cuda()) for x, y in batches]
     trainer = st.nn.ModuleTrainer(backend=backend, fallback_learning_rate=lr)
     trainer.prepare(model)
     history = []
@@ -60,6 +65,30 @@ def zconv_classification(seed: int = 0):
     model.add(st.nn.Relu())
     model.add(st.nn.Pool2d("max", 4, 8, 8, (2, 2)))
     model.add(st.nn.Linear(4 * 4 * 4, 2, name="head"))
+    x, y = imgs.reshape(n, -1), labels.reshape(-1, 1).float()
+    batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, n, 32)]
+    return model, st.nn.SoftmaxCrossEntropy(), batches, 2.0
+
+
+def vision_conv_pool_classification(seed: int = 0):
+    """Four classes of 16x16 one-channel images (a bright quadrant + noise): ZConv 3x3 -> ReLU -> max-pool 2x2 ->
+    ZConv 3x3 -> ReLU -> max-pool 2x2 -> Linear -> softmax cross-entropy (the layer stack of the reference's
+    ``models/python/vision_conv_pool_classification.py``)."""
+    g = torch.Generator().manual_seed(seed)
+    n = 192
+    labels = torch.randint(0, 4, (n,), generator=g)
+    imgs = 0.3 * torch.randn(n, 1, 16, 16, generator=g)
+    for c, (ys, xs) in enumerate(((slice(0, 8), slice(0, 8)), (slice(0, 8), slice(8, 16)), (slice(8, 16), slice(0, 8)),
+                                  (slice(8, 16), slice(8, 16)))):
+        imgs[labels == c, :, ys, xs] += 1.0
+    model = st.nn.Sequential()
+    model.add(st.nn.ZConv("conv1", 1, 8, (16, 16), (3, 3), padding=(1, 1)))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Pool2d("max", 8, 16, 16, (2, 2)))
+    model.add(st.nn.ZConv("conv2", 8, 16, (8, 8), (3, 3), padding=(1, 1)))
+    model.add(st.nn.Relu())
+    model.add(st.nn.Pool2d("max", 16, 8, 8, (2, 2)))
+    model.add(st.nn.Linear(16 * 4 * 4, 4, name="head"))
     x, y = imgs.reshape(n, -1), labels.reshape(-1, 1).float()
     batches = [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, n, 32)]
     return model, st.nn.SoftmaxCrossEntropy(), batches, 2.0
@@ -213,7 +242,58 @@ def mellin_log_grid_classification(seed: int = 0):
     return model, st.nn.SoftmaxCrossEntropy(), batches, 8.0
 
 
+def _char_lm(steps: int = 12, dim: int = 16, hidden: int = 32):
+    model = st.nn.Sequential()
+    model.add(st.nn.Embedding(64, dim, name="embed"))
+    model.add(st.nn.SpiralRnn("rnn", dim, hidden, steps))
+    model.add(st.nn.Linear(hidden, 64, name="head"))
+    return model
+
+
+def llm_char_finetune(run_dir=None, backend: str = "cpu", epochs: int = 8, seed: int = 0, quiet: bool = False) -> dict:
+    """Character LM (Embedding -> SpiralRnn -> Linear) trained on one text, saved, reloaded into a fresh model and
+    fine-tuned on a second text: the two-stage flow of the reference's ``models/python/llm_char_finetune.py``
+    (:1193-1210 save / ``--load-weights`` resume).  Returns both stages' losses and the loss of the base model on
+    the second text before fine-tuning."""
+    import tempfile
+    from pathlib import Path
+    steps = 12
+
+    def windows(text: str, n: int, s: int):
+        data = torch.tensor(list(text.encode()), dtype=torch.float32) % 64
+        g = torch.Generator().manual_seed(s)
+        starts = torch.randint(0, data.numel() - steps - 1, (n,), generator=g)
+        x = torch.stack([data[i:i + steps] for i in starts.tolist()])
+        y = torch.stack([data[i + steps] for i in starts.tolist()]).reshape(-1, 1)
+        return [(st.Tensor(x[i:i + 32]), st.Tensor(y[i:i + 32])) for i in range(0, n, 32)]
+    text_b = ("the trainer hands its gradient to the bandit, the bandit hands a knob back; "
+              "every step is measured, every measure is kept. ") * 4
+    base_batches, tune_batches = windows(_TEXT, 192, seed), windows(text_b, 128, seed + 1)
+    loss = st.nn.SoftmaxCrossEntropy()
+    rd = RunDir(run_dir, "llm_char_finetune", backend=backend, hyper_params={"epochs": epochs, "seed": seed}) if run_dir else None
+    base = _char_lm(steps)
+    base_hist, base_final = _train(base, loss, base_batches, epochs, 8.0, backend, rd, quiet)
+    work = Path(run_dir) if run_dir else Path(tempfile.mkdtemp(prefix="st_finetune_"))
+    work.mkdir(parents=True, exist_ok=True)
+    st.nn.save(str(work / "base_weights.json"), base)
+    tuned = _char_lm(steps)
+    st.nn.load(str(work / "base_weights.json"), tuned)                  # the second stage starts from the saved weights
+    probe = st.nn.ModuleTrainer(backend=backend)
+    if backend == "cuda":
+        tuned.to("cuda")
+    before = probe.evaluate_epoch(tuned, loss, [(x.cuda(), y.cuda()) for x, y in tune_batches] if backend == "cuda"
+                                  else tune_batches).average_loss
+    tune_hist, tune_final = _train(tuned, loss, tune_batches, max(2, epochs // 2), 4.0, backend, None, quiet)
+    out = {"initial_loss": base_hist[0], "final_loss": tune_final, "base_final_loss": base_final,
+           "finetune_loss_before": before, "history": base_hist + tune_hist, "model": tuned}
+    if rd:
+        rd.save_weights(tuned)
+        rd.write_summary({k: v for k, v in out.items() if k not in ("model", "history")} | {"epochs": epochs})
+    return out
+
+
 _TRAINER_RECIPES: Dict[str, Callable] = {
+    "vision_conv_pool_classification": vision_conv_pool_classification,
     "zconv_classification": zconv_classification,
     "llm_char_coherence_scan": llm_char_coherence_scan,
     "llm_char_wave_rnn_mixer": llm_char_wave_rnn_mixer,
@@ -257,12 +337,14 @@ def _run_vae(name: str, epochs: int, seed: int, rd, quiet: bool):
     return {"initial_loss": initial, "final_loss": final, "history": history, "model": vae}
 
 
-RECIPES = tuple(_TRAINER_RECIPES) + ("zspace_vae_reconstruction", "zspace_text_vae")
+RECIPES = tuple(_TRAINER_RECIPES) + ("zspace_vae_reconstruction", "zspace_text_vae", "llm_char_finetune")
 
 
 def run(name: str, run_dir=None, backend: str = "cpu", epochs: int = 8, seed: int = 0, quiet: bool = False) -> dict:
     if name not in RECIPES:
         raise KeyError(f"unknown recipe {name!r}; available: {', '.join(RECIPES)}")
+    if name == "llm_char_finetune":
+        return llm_char_finetune(run_dir, backend, epochs, seed, quiet)
     rd = RunDir(run_dir, name, backend=backend, hyper_params={"epochs": epochs, "seed": seed}) if run_dir else None
     if name in _TRAINER_RECIPES:
         model, loss, batches, lr = _TRAINER_RECIPES[name](seed)
