@@ -12,6 +12,7 @@ exposition format; nothing here needs a network.
 from __future__ import annotations
 
 import math
+import json
 import re
 import threading
 import time
@@ -230,6 +231,64 @@ class CallbackExporter(MetricsExporter):
 
     def record_gauge(self, name, value, labels=()):
         self._fn(name, float(value), tuple(labels))
+
+
+class OtelExporter(MetricsExporter):
+    """OpenTelemetry metrics without the SDK: gauges keep their latest value, counters accumulate, and
+    ``payload()`` renders both as an OTLP/JSON ``ExportMetricsServiceRequest`` (``resourceMetrics`` →
+    ``scopeMetrics`` → ``metrics`` with ``gauge`` / monotonic cumulative ``sum`` data points) that ``write(path)``
+    stores durably and ``post(endpoint)`` sends to an OTLP/HTTP collector (``/v1/metrics``) with the standard
+    library.  Plays the role of the reference's ``OtelExporter`` over an ``opentelemetry`` meter
+    (crates/st-core/src/telemetry/monitoring.rs:526-575)."""
+
+    def __init__(self, service_name: str = "spiraltorch", scope: str = "spiraltorch_b200.telemetry"):
+        self.service_name, self.scope = service_name, scope
+        self._gauges: dict = {}
+        self._counters: dict = {}
+        self._lock = threading.Lock()
+        self._start_ns = time.time_ns()
+
+    def record_gauge(self, name, value, labels=()):
+        with self._lock:
+            self._gauges[(name, tuple(sorted(labels)))] = (float(value), time.time_ns())
+
+    def record_counter(self, name, value, labels=()):
+        key = (name, tuple(sorted(labels)))
+        with self._lock:
+            total = self._counters.get(key, (0.0, 0))[0] + max(float(value), 0.0)
+            self._counters[key] = (total, time.time_ns())
+
+    @staticmethod
+    def _attrs(labels) -> list:
+        return [{"key": k, "value": {"stringValue": str(v)}} for k, v in labels]
+
+    def payload(self) -> dict:
+        metrics: dict = {}
+        with self._lock:
+            for (name, labels), (v, ts) in sorted(self._gauges.items()):
+                m = metrics.setdefault(("g", name), {"name": name, "description": f"Gauge for {name}", "gauge": {"dataPoints": []}})
+                m["gauge"]["dataPoints"].append({"asDouble": v, "timeUnixNano": str(ts), "attributes": self._attrs(labels)})
+            for (name, labels), (v, ts) in sorted(self._counters.items()):
+                m = metrics.setdefault(("c", name), {"name": name, "description": f"Counter for {name}",
+                                                     "sum": {"dataPoints": [], "isMonotonic": True,
+                                                             "aggregationTemporality": 2}})
+                m["sum"]["dataPoints"].append({"asDouble": v, "startTimeUnixNano": str(self._start_ns),
+                                               "timeUnixNano": str(ts), "attributes": self._attrs(labels)})
+        return {"resourceMetrics": [{
+            "resource": {"attributes": [{"key": "service.name", "value": {"stringValue": self.service_name}}]},
+            "scopeMetrics": [{"scope": {"name": self.scope}, "metrics": list(metrics.values())}]}]}
+
+    def write(self, path) -> None:
+        from .config import atomic_write
+        atomic_write(path, json.dumps(self.payload(), sort_keys=True))
+
+    def post(self, endpoint: str, timeout: float = 5.0) -> int:
+        """POST the payload to ``endpoint`` (e.g. ``http://127.0.0.1:4318/v1/metrics``); returns the HTTP status."""
+        import urllib.request
+        req = urllib.request.Request(endpoint, data=json.dumps(self.payload()).encode(),
+                                     headers={"Content-Type": "application/json"}, method="POST")
+        with urllib.request.urlopen(req, timeout=timeout) as resp:      # noqa: S310 - caller-provided collector URL
+            return resp.status
 
 
 def _sanitize(name: str) -> str:
