@@ -270,6 +270,41 @@ class ModuleTrainer:
             plugin.publish("PsiThresholdCross", {"component": ev.component.label, "value": ev.value,
                                                  "threshold": ev.threshold, "up": ev.up, "step": ev.step})
 
+    def attach_desire_bridge(self, bridge) -> None:
+        """A :class:`spiraltorch_b200.desire_pipeline.DesireTrainerBridge` whose queued events belong to this
+        trainer's resumable state."""
+        self.desire_bridge = bridge
+
+    def external_state_checkpoint(self):
+        """State kept beside the module and its accumulators - psi meter, desire trainer queue, the Autopilot's
+        pending selection - as one validated document (see :mod:`spiraltorch_b200.runtime.trainer_external`)."""
+        from ..runtime.trainer_external import TrainerExternalCheckpointComponents
+        b = TrainerExternalCheckpointComponents()
+        meter = getattr(self, "psi_meter", None)
+        if meter is not None:
+            b.require("psi_meter").with_psi_meter(meter.checkpoint())
+        bridge = getattr(self, "desire_bridge", None)
+        if bridge is not None:
+            b.require("desire_trainer").with_desire_trainer(bridge.checkpoint())
+        ap = getattr(self, "autopilot", None)
+        if ap is not None:
+            b.require("autopilot").with_autopilot({"picks": dict(ap.picks), "suggestion_ready": bool(ap.suggestion_ready),
+                                                   "profile_key": ap.profile_key})
+        return b.build()
+
+    def restore_external_state(self, checkpoint) -> None:
+        """Inverse of :meth:`external_state_checkpoint` for the components attached to this trainer; a pending
+        Autopilot suggestion cannot be revived (its bandit selection is gone) and is dropped."""
+        checkpoint.validate()
+        if checkpoint.psi_meter is not None and getattr(self, "psi_meter", None) is not None:
+            from ..psi import PsiMeter
+            self.psi_meter = PsiMeter.from_checkpoint(checkpoint.psi_meter)
+        if checkpoint.desire_trainer is not None and getattr(self, "desire_bridge", None) is not None:
+            self.desire_bridge.restore_checkpoint(checkpoint.desire_trainer)
+        ap = getattr(self, "autopilot", None)
+        if ap is not None and ap.suggestion_ready:
+            ap.abandon_suggestion()
+
     def _autopilot_before(self, module, x) -> None:
         ap = getattr(self, "autopilot", None)
         if ap is None:
