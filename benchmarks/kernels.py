@@ -333,6 +333,58 @@ def bench_layers(iters, profile):
     return out
 
 
+def bench_fused(iters, profile):
+    """The fused all-gather->GEMM and GEMM->reduce-scatter kernels in their world-1 form (the peer is this GPU: the
+    same code path, rendezvous flags, arrival counters and epilogues, without NVLink), against the plain GEMM."""
+    from spiraltorch_b200.ops.gemm import gemm
+    from spiraltorch_b200.parallel.symm import FusedTPContext
+    tp = FusedTPContext(None, device=DEV)
+    T, K, N = 16384, 2048, 3072
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    w2 = torch.randn(K, N, device=DEV).bfloat16()
+    a = torch.randn(T, N, device=DEV).bfloat16()
+    if profile:
+        for _ in range(2):
+            tp.ag_gemm(x, w, key="prof")
+            tp.gemm_rs(a, w2)
+        torch.cuda.synchronize()
+        return []
+    out = []
+    for name, fn, ref, flops in (("ag_gemm_world1", lambda: tp.ag_gemm(x, w, key="bench"), lambda: gemm(x, w), 2.0 * T * N * K),
+                                 ("gemm_rs_world1", lambda: tp.gemm_rs(a, w2), lambda: gemm(a, w2), 2.0 * T * N * K)):
+        r = row(name, f"{T}x{N}x{K}", timed(fn, iters), timed(ref, iters), flops=flops)
+        out.append(r)
+    return out
+
+
+def bench_scan(iters, profile):
+    """Whole-sequence recurrent kernels: forward + backward of the LSTM / wave / Elman layers in one launch each,
+    against the per-step PyTorch loop on the same device."""
+    from spiraltorch_b200.ops import recurrent as R
+    out = []
+    for cell, B, T_, I, H, dil in (("wave", 32, 16, 32, 64, 2), ("lstm", 64, 32, 64, 64, 1), ("tanh", 64, 32, 64, 128, 1)):
+        G_ = {"tanh": 1, "wave": 2, "lstm": 4}[cell]
+        xs = torch.randn(B, T_, I, device=DEV, requires_grad=True)
+        w_ih = (torch.randn(I, G_ * H, device=DEV) * 0.2).requires_grad_(True)
+        w_hh = (torch.randn(H, G_ * H, device=DEV) * 0.2).requires_grad_(True)
+        b = torch.zeros(1, G_ * H, device=DEV, requires_grad=True)
+
+        def ours():
+            R.rnn_sequence(xs, w_ih, w_hh, b, cell, dil).sum().backward()
+
+        def loop():
+            R.rnn_sequence_reference(xs, w_ih, w_hh, b, cell, dil).sum().backward()
+        if profile:
+            ours(); ours(); torch.cuda.synchronize()
+            continue
+        r = {"kernel": f"rnn_scan_{cell}_fwd_bwd", "shape": f"B{B} T{T_} in{I} H{H}", "ours_ms": round(timed(ours, iters), 4),
+             "torch_step_loop_ms": round(timed(loop, iters), 4)}
+        print(json.dumps(r), flush=True)
+        out.append(r)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernels", nargs="*", default=["gemm", "attn_fwd", "attn_bwd", "conv", "norm", "adamw", "ce"])
@@ -349,7 +401,9 @@ def main() -> int:
              "adamw": lambda: bench_adamw(args.iters, args.profile),
              "ce": lambda: bench_ce(args.iters, args.profile),
              "transforms": lambda: bench_transforms(args.iters, args.profile),
-             "layers": lambda: bench_layers(args.iters, args.profile)}
+             "layers": lambda: bench_layers(args.iters, args.profile),
+             "fused": lambda: bench_fused(args.iters, args.profile),
+             "scan": lambda: bench_scan(args.iters, args.profile)}
     rows = []
     for k in args.kernels:
         rows += table[k]()
