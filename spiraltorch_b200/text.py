@@ -48,6 +48,12 @@ class TextResonator:
         s = timeline.summarise(window)
         return None if s is None else self.describe_summary(s)
 
+    def describe_frame(self, frame) -> ResonanceNarrative:
+        return _frame_narrative(frame)
+
+    def describe_atlas(self, atlas, chrono_summary=None, maintainer_status: Optional[str] = None) -> ResonanceNarrative:
+        return _atlas_narrative(atlas, chrono_summary, maintainer_status)
+
     def synthesize_wave(self, timeline: ChronoTimeline, sample_rate: int = 8000, seconds_per_frame: float = 0.05,
                         base_frequency: float = 220.0) -> WaveSynthesis:
         samples, phase = [], 0.0
@@ -59,3 +65,91 @@ class TextResonator:
                 phase += 2 * math.pi * freq / sample_rate
                 samples.append(amp * math.sin(phase))
         return WaveSynthesis(samples, sample_rate, base_frequency)
+
+
+# ---- frame / atlas narratives, realtime narrator, token semantics ------------------------------------------------
+def _frame_narrative(frame) -> ResonanceNarrative:
+    """One temporal frame in words (crates/st-text/src/lib.rs:122-146)."""
+    if frame.total_energy <= 1.1920929e-07:
+        summary = (f"At t={frame.timestamp:.3f} the resonance settled; curvature drift {frame.curvature_drift:+.3f} "
+                   "with negligible energy.")
+    else:
+        summary = (f"At t={frame.timestamp:.3f} the resonance carried {frame.total_energy:.3f} energy with curvature "
+                   f"drift {frame.curvature_drift:+.3f}.")
+    hl = [f"homotopy {frame.homotopy_ratio() * 100:.1f}%", f"functor {frame.functor_ratio() * 100:.1f}%",
+          f"recursive {frame.recursive_ratio() * 100:.1f}%", f"projection {frame.projection_ratio() * 100:.1f}%",
+          f"infinity {frame.infinity_ratio() * 100:.1f}%", f"energy decay {frame.energy_decay:+.3f}"]
+    return ResonanceNarrative(summary, hl)
+
+
+def _atlas_narrative(atlas, chrono_summary=None, maintainer_status: Optional[str] = None) -> ResonanceNarrative:
+    """An atlas snapshot in words: span / energy / drift when a chrono summary is known, then loop support, collapse
+    total, Z bias, every metric, the notes and the script hint as highlights (crates/st-text/src/lib.rs:475-537)."""
+    if chrono_summary is not None:
+        summary = (f"Atlas at t={atlas.timestamp:.3f} spans {chrono_summary.duration:.3f}s with energy "
+                   f"{chrono_summary.mean_energy:.3f} and drift {chrono_summary.mean_drift:+.3f}.")
+    else:
+        summary = f"Atlas snapshot at t={atlas.timestamp:.3f}."
+    if maintainer_status:
+        summary += f" Maintainer {maintainer_status}."
+    hl = []
+    if atlas.loop_support > 0.0:
+        hl.append(f"loop support {atlas.loop_support:.3f}")
+    if atlas.collapse_total is not None:
+        hl.append(f"collapse total {atlas.collapse_total:.3f}")
+    if atlas.z_signal is not None:
+        hl.append(f"z bias {atlas.z_signal:+.3f}")
+    hl += [f"{name} {value:.3f}" for name, value in atlas.metrics.items()]
+    hl += list(atlas.notes)
+    if atlas.script_hint:
+        hl.append(f"script {atlas.script_hint}")
+    return ResonanceNarrative(summary, hl)
+
+
+class RealtimeNarrator:
+    """Timeline → audio samples at a fixed rate (crates/st-text/src/lib.rs:595-627)."""
+
+    def __init__(self, curvature: float = -1.0, temperature: float = 0.6, sample_rate: int = 8000):
+        self.inner, self.sample_rate = TextResonator(curvature, temperature), max(1, sample_rate)
+
+    @classmethod
+    def from_resonator(cls, resonator: TextResonator, sample_rate: int) -> "RealtimeNarrator":
+        n = cls.__new__(cls)
+        n.inner, n.sample_rate = resonator, max(1, sample_rate)
+        return n
+
+    def narrate_timeline(self, timeline: ChronoTimeline) -> list:
+        return self.inner.synthesize_wave(timeline, self.sample_rate).samples
+
+
+def describe_frame(frame) -> str:
+    return TextResonator(-1.0, 0.6).describe_frame(frame).summary
+
+
+def describe_timeline(timeline: ChronoTimeline) -> Optional[str]:
+    n = TextResonator(-1.0, 0.6).describe_timeline(timeline)
+    return None if n is None else n.summary
+
+
+def describe_atlas(atlas) -> str:
+    return TextResonator(-1.0, 0.6).describe_atlas(atlas).summary
+
+
+def token_scale_stack(embeddings, scales, threshold: float, metric: str = "euclidean"):
+    """Scale stack of a token sequence: tokens are samples along the sequence, the embedding dimension is the
+    semantic feature axis (crates/st-text/src/semantics.rs:16-31).  Returns the same :class:`ScaleStack` the
+    fractal module builds for vector-valued fields, so persistence, boundary dimension and coherence breaks apply."""
+    import torch
+    from .frac import ScaleStack
+    e = embeddings.torch() if hasattr(embeddings, "torch") else torch.as_tensor(embeddings, dtype=torch.float32)
+    if e.dim() != 2:
+        raise ValueError(f"token_scale_stack needs a [tokens, dims] matrix, got shape {tuple(e.shape)}")
+    if metric not in ("euclidean", "cosine"):
+        raise ValueError(f"unknown semantic metric '{metric}'")
+    return ScaleStack.from_semantic_field(e, list(scales), float(threshold), 1, metric)
+
+
+def token_coherence_levels(embeddings, scales, threshold: float, metric: str = "euclidean", levels=(0.25, 0.5, 0.75)):
+    """Per level, the smallest scale whose gate fraction reaches it, else ``None``
+    (crates/st-text/src/semantics.rs:34-43)."""
+    return token_scale_stack(embeddings, scales, threshold, metric).coherence_profile(list(levels))
