@@ -343,3 +343,225 @@ class EntropicGwSolver:
             self.anchor_strength = cl(self.anchor_strength * (1 - 0.05 * -c), 0.5, 24.0)
             self.epsilon = cl(self.epsilon * (1 + 0.1 * -c), 1e-3, 8.0)
         self.epsilon = cl(self.epsilon * (1 - 0.03 * r), 1e-3, 8.0)
+
+
+# ---- concept hints, narrative hints and the Maxwell -> desire bridge --------------------------------------------------
+class ConceptHint:
+    """Either a concept distribution or a weighted token window (crates/st-nn/src/language/geometry.rs:752-870).
+    ``as_distribution`` resolves both against a semantic bridge: a distribution is padded with 1e-6 to the concept
+    count, clipped at zero and normalised (floor: float32 epsilon; uniform when it carries no mass); a window is
+    pushed through the bridge's window inference."""
+
+    def __init__(self, distribution=None, window=None):
+        if (distribution is None) == (window is None):
+            raise TensorError("a concept hint is either a distribution or a window")
+        self.distribution = None if distribution is None else [float(v) for v in distribution]
+        self.window = None if window is None else [(int(t), float(w)) for t, w in window]
+
+    @classmethod
+    def from_distribution(cls, dist) -> "ConceptHint":
+        return cls(distribution=dist)
+
+    @classmethod
+    def from_window(cls, window) -> "ConceptHint":
+        return cls(window=window)
+
+    def as_distribution(self, bridge: SemanticBridge) -> list:
+        c = bridge.concept_count()
+        if self.window is not None:
+            return [float(v) for v in bridge.infer_from_window(self.window, 1e-6).tolist()]
+        if not self.distribution:
+            return [1.0 / c] * c
+        buf = [1e-6] * c
+        for i, v in enumerate(self.distribution[:c]):
+            buf[i] = v
+        buf = [max(v, 0.0) if math.isfinite(v) else 0.0 for v in buf]
+        s = sum(buf)
+        if s <= 1.1920929e-07:
+            return [1.0 / c] * c
+        return [max(v / s, 1.1920929e-07) for v in buf]
+
+    def snapshot(self, max_len: int = 256) -> dict:
+        n = max(int(max_len), 1)
+        if self.window is not None:
+            return {"window": [[t, w] for t, w in self.window[:n]]}
+        return {"distribution": self.distribution[:n]}
+
+
+@dataclass
+class NarrativeSummary:
+    channel: str
+    dominant_tag: Optional[str]
+    tags: list
+    intensity: float
+    amplitude: float
+    phase: float
+    coherence: float
+    decoherence: float
+    emphasis: float
+
+    def describe(self) -> str:
+        what = f"tag `{self.dominant_tag}`" if self.dominant_tag is not None else "neutral"
+        return (f"[{self.channel}] {what} emphasis {self.emphasis:.3f} (amp {self.amplitude:.3f}, coh {self.coherence:.2f}, "
+                f"deco {self.decoherence:.2f})")
+
+    __str__ = describe
+
+    def as_dict(self) -> dict:
+        return dict(self.__dict__)
+
+
+class NarrativeHint:
+    """Tags attached to a Maxwell channel with a small "quantum" state (crates/st-nn/src/language/maxwell.rs:15-170):
+    the collapsed tag is the one maximising ``|amplitude| * coherence * (1 - decoherence) * max(|sin(phase + i * phi)|
+    + 0.5, 1e-3)`` over tag positions ``i`` (phi = 1.618034); emphasis is the first three factors."""
+
+    def __init__(self, channel: str, tags, intensity: float):
+        self.channel, self.tags, self.intensity = str(channel), list(tags), float(intensity)
+        self.amplitude, self.phase, self.coherence, self.decoherence = float(intensity), 0.0, 1.0, 0.0
+        self.collapsed_tag: Optional[str] = None
+        self._recompute()
+
+    def _recompute(self) -> None:
+        if not self.tags:
+            self.collapsed_tag = None
+            return
+        base = max(1.0 - self.decoherence, 0.0)
+        best, best_w = self.tags[0], -math.inf
+        for i, tag in enumerate(self.tags):
+            w = abs(self.amplitude) * self.coherence * base * max(abs(math.sin(self.phase + i * 1.618034)) + 0.5, 1e-3)
+            if w > best_w:
+                best, best_w = tag, w
+        self.collapsed_tag = best
+
+    def with_quantum_state(self, amplitude: float, phase: float, coherence: float, decoherence: float) -> "NarrativeHint":
+        self.amplitude, self.phase = float(amplitude), float(phase)
+        self.coherence, self.decoherence = min(max(coherence, 0.0), 1.0), min(max(decoherence, 0.0), 1.0)
+        self._recompute()
+        return self
+
+    def collapse(self) -> "NarrativeHint":
+        self._recompute()
+        return self
+
+    def dominant_tag(self) -> Optional[str]:
+        return self.collapsed_tag if self.collapsed_tag is not None else (self.tags[0] if self.tags else None)
+
+    def quantum_emphasis(self) -> float:
+        a = abs(self.amplitude)
+        return 0.0 if a <= 1.1920929e-07 else a * self.coherence * (1.0 - self.decoherence)
+
+    def summary(self) -> NarrativeSummary:
+        return NarrativeSummary(self.channel, self.dominant_tag(), list(self.tags), self.intensity, self.amplitude, self.phase,
+                                self.coherence, self.decoherence, self.quantum_emphasis())
+
+
+def _clean_tags(tags) -> list:
+    out = []
+    for t in tags or ():
+        t = str(t).strip()
+        if not t:
+            raise TensorError("invalid value: narrative tag cannot be empty")
+        out.append(t)
+    return sorted(set(out))
+
+
+class MaxwellDesireBridge:
+    """Maps a Maxwell Z pulse on a named channel to a concept window (each registered ``(token, weight)`` becomes
+    ``(weight + smoothing) * max(|z|, magnitude_floor)``) and, when the channel has tags, a narrative hint of
+    intensity ``magnitude * gain`` (crates/st-nn/src/language/maxwell.rs:196-460)."""
+
+    def __init__(self, smoothing: float = 1e-4, magnitude_floor: float = 0.0):
+        self.smoothing, self.magnitude_floor = max(float(smoothing), 0.0), max(float(magnitude_floor), 0.0)
+        self._channels: dict = {}
+
+    def with_smoothing(self, s: float) -> "MaxwellDesireBridge":
+        self.smoothing = max(float(s), 0.0)
+        return self
+
+    def with_magnitude_floor(self, f: float) -> "MaxwellDesireBridge":
+        self.magnitude_floor = max(float(f), 0.0)
+        return self
+
+    def __len__(self) -> int:
+        return len(self._channels)
+
+    def is_empty(self) -> bool:
+        return not self._channels
+
+    def contains(self, channel: str) -> bool:
+        return channel in self._channels
+
+    def channel_names(self) -> list:
+        return list(self._channels)
+
+    def register_channel(self, channel: str, window, tags=(), gain: float = 1.0) -> None:
+        if not str(channel).strip():
+            raise TensorError("invalid value: channel name cannot be empty")
+        window = list(window)
+        if not window:
+            raise TensorError("invalid value: Maxwell concept window cannot be empty")
+        clean = []
+        for tok, w in window:
+            if not math.isfinite(w):
+                raise TensorError("invalid value: window weight must be finite")
+            if w < 0:
+                raise TensorError("invalid value: window weight must be non-negative")
+            clean.append((int(tok), float(w)))
+        self._channels[str(channel)] = {"window": clean, "tags": _clean_tags(tags), "gain": max(float(gain), 0.0)}
+
+    register_channel_with_narrative = register_channel
+
+    def with_channel(self, channel: str, window, tags=()) -> "MaxwellDesireBridge":
+        self.register_channel(channel, window, tags)
+        return self
+
+    with_channel_and_narrative = with_channel
+
+    def _program(self, channel: str) -> dict:
+        if channel not in self._channels:
+            raise TensorError("invalid value: channel is not registered")
+        return self._channels[channel]
+
+    def set_narrative_tags(self, channel: str, tags) -> None:
+        self._program(channel)["tags"] = _clean_tags(tags)
+
+    def set_narrative_gain(self, channel: str, gain: float) -> None:
+        self._program(channel)["gain"] = max(float(gain), 0.0)
+
+    def narrative_tags(self, channel: str) -> Optional[list]:
+        p = self._channels.get(channel)
+        return None if p is None else list(p["tags"])
+
+    def narrative_gain(self, channel: str) -> Optional[float]:
+        p = self._channels.get(channel)
+        return None if p is None else p["gain"]
+
+    def hint_for(self, channel: str, pulse) -> Optional[ConceptHint]:
+        p = self._channels.get(channel)
+        if p is None or not p["window"]:
+            return None
+        mag = max(float(pulse.magnitude()), self.magnitude_floor)
+        if mag <= 1.1920929e-07 and self.smoothing <= 1.1920929e-07:
+            return None
+        scaled = [(t, (max(w, 0.0) + self.smoothing) * mag) for t, w in p["window"]]
+        scaled = [(t, v) for t, v in scaled if v > 1.1920929e-07]
+        return ConceptHint.from_window(scaled) if scaled else None
+
+    def narrative_for(self, channel: str, pulse) -> Optional[NarrativeHint]:
+        p = self._channels.get(channel)
+        if p is None or not p["tags"]:
+            return None
+        mag = max(float(pulse.magnitude()), self.magnitude_floor)
+        intensity = mag * p["gain"]
+        if mag <= 1.1920929e-07 or intensity <= 1.1920929e-07:
+            return None
+        above, here, beneath = pulse.band_energy
+        coherence = min(max((above + beneath) / (above + here + beneath + 1e-6), 0.0), 1.0)
+        se = abs(pulse.standard_error)
+        phase = math.atan(pulse.z_score) * max(len(p["tags"]), 1)
+        return NarrativeHint(channel, p["tags"], intensity).with_quantum_state(intensity, phase, coherence, min(se / (se + 1.0), 1.0)).collapse()
+
+    def emit(self, channel: str, pulse):
+        hint = self.hint_for(channel, pulse)
+        return None if hint is None else (hint, self.narrative_for(channel, pulse))

@@ -11,7 +11,7 @@ from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, I
                       ZSpaceCoherenceWaveBlock, ZSpaceLayerNorm, ZSpaceMixer, ZSpaceSoftmax, conv_output_shape,
                       pool_output_shape)
 from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
-from . import amp, conv, fields, gnn, lightning, roundtable, zrba, zspace
+from . import amp, coherence, conv, fields, gnn, lightning, roundtable, zrba, zspace
 from .roundtable import DistConfig, MetaConductor, MetaSummary, RoundtableNode
 from .conv import AvgPool2d, Conv2d, Conv3d, Conv4d, Conv6da, MaxPool2d, WaveScan, ZConv6DA
 from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,
@@ -21,7 +21,14 @@ from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregatio
 from .lightning import (InfoNCELoss, LightningConfig, LightningReport, LightningStage, SelfSupStage, SpiralLightning)
 from .zrba import (BetaGate, BetaGateConfig, BetaGateSample, CovHead, CovHeadTelemetry, ReliabilityBin,
                    SpectralFeatureSample, ZCov, ZRBA, ZRBAConfig, ZRBAMetrics, ZRBATelemetry, ZTelemetryBundle)
-from .zspace import (ArdParameters, LanguageWaveEncoder, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention,
-                     ZSpaceCoherenceSequencer, ZSpaceTextVae, ZSpaceVae, ZTensor)
+from .zspace import (ArdParameters, LanguageWaveEncoder, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention, ZSpaceTextVae,
+                     ZSpaceVae, ZSpaceVaeState, ZTensor)
+from .coherence import (CoherenceBackend, CoherenceChannelReport, CoherenceDiagnostics, CoherenceEngine, CoherenceObservation,
+                        CoherenceSignature, DomainLinguisticProfile, LinguisticChannelReport, LinguisticContour,
+                        PreDiscardPolicy, PreDiscardRegulator, PreDiscardSnapshot, PreDiscardTelemetry,
+                        ZSpaceCoherenceSequencer, ZSpaceTraceConfig, ZSpaceTraceRecorder, coherence_relation_tensor,
+                        is_swap_invariant)
+from ..language import ConceptHint, MaxwellDesireBridge, NarrativeHint, NarrativeSummary
+from ..desire_pipeline import DesirePipeline, DesireTrainerBridge
 
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)

@@ -149,32 +149,6 @@ class ZRBFAttention:
         return ZRBFAttentionOutput(Tensor._wrap(mean), Tensor._wrap(var), tel)
 
 
-class ZSpaceCoherenceSequencer:
-    """Attention-free sequence mixing: each step is a convex blend of the running coherent state and
-    the new token, the blend weight coming from their cosine coherence under curvature ``c``."""
-
-    def __init__(self, dim: int, curvature: float = -1.0, memory: float = 0.9):
-        if dim <= 0 or not curvature < 0 or not 0.0 <= memory < 1.0:
-            raise TensorError("sequencer needs dim > 0, curvature < 0 and memory in [0, 1)")
-        self.dim, self.curvature, self.memory = dim, curvature, memory
-
-    def forward(self, x: Tensor) -> tuple:
-        """``x``: ``(steps, dim)`` → ``(mixed (steps, dim), coherence weights (steps, 1))``."""
-        t = _t(x).float()
-        if t.shape[1] != self.dim:
-            raise TensorError(f"input has {t.shape[1]} columns, expected {self.dim}")
-        state = torch.zeros(self.dim, device=t.device)
-        out, coh = [], []
-        scale = math.sqrt(-self.curvature)
-        for row in t:
-            c = torch.nn.functional.cosine_similarity(state, row, dim=0, eps=1e-12) if bool(state.any()) else torch.tensor(0.0)
-            gate = torch.sigmoid(scale * c) * self.memory
-            state = gate * state + (1.0 - gate) * row
-            out.append(state)
-            coh.append(gate)
-        return Tensor._wrap(torch.stack(out)), Tensor._wrap(torch.stack(coh).reshape(-1, 1))
-
-
 @dataclass
 class ZSpaceVaeState:
     mu: torch.Tensor

@@ -83,14 +83,7 @@ def test_zrba_attention_kernel_and_variance():
         zspace.ZTensor(mu, sigma, idx[:2])
 
 
-def test_coherence_sequencer_and_vae(tmp_path):
-    seq = zspace.ZSpaceCoherenceSequencer(4, curvature=-1.0, memory=0.8)
-    x = st.Tensor._wrap(torch.tensor([[1.0, 0, 0, 0], [1.0, 0, 0, 0], [0, 1.0, 0, 0]]))
-    mixed, coh = seq.forward(x)
-    assert mixed.shape() == (3, 4) and coh.shape() == (3, 1)
-    c = coh.torch().flatten()
-    assert c[0] == pytest.approx(0.4) and c[1] > c[2]          # aligned token keeps more of the state
-
+def test_zspace_vae_optimizers(tmp_path):
     torch.manual_seed(0)
     basis = torch.randn(2, 6)
     data = torch.randn(64, 2) @ basis
