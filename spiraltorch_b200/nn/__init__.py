@@ -1,5 +1,6 @@
 """``spiraltorch.nn``: modules, losses, trainer, data and weight files of the public API."""
-from .amp import (AutocastGuard, CurvatureScheduler, GradScaler, OptimizerMode, SpectralLrAdapter, WarmupCosineScheduler,
+from .amp import (AutocastGuard, CoherenceSignal, CurvatureDecision, CurvatureScheduler, GradScaler, OptimizerMode,
+                  SpectralAdjustment, SpectralLearningRatePolicy, SpectralLrAdapter, WarmupCosineScheduler,
                   ZSpaceParameterOptimizer, autocast_enabled)
 from .data import DataLoader, Dataset, from_samples
 from .io import load, load_bincode, load_json, save, save_bincode, save_json

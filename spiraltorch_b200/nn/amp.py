@@ -305,6 +305,22 @@ class WarmupCosineScheduler:
 _PRESSURE_MAX = 1.0e6
 
 
+@dataclass(frozen=True)
+class CurvatureDecision:
+    """What one scheduler observation decided (crates/st-nn/src/trainer.rs:641-648); also readable by key."""
+    raw_pressure: float
+    smoothed_pressure: float
+    curvature: float
+    changed: bool
+
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+    def as_dict(self) -> dict:
+        return {"raw_pressure": self.raw_pressure, "smoothed_pressure": self.smoothed_pressure, "curvature": self.curvature,
+                "changed": self.changed}
+
+
 class CurvatureScheduler:
     """Keeps the (negative) curvature of the hyperbolic optimiser near a target gradient pressure.
 
@@ -403,11 +419,11 @@ class CurvatureScheduler:
             return None
         return max(self.ema_pressure2 - self.ema_pressure ** 2, 0.0)
 
-    def observe(self, gradient: torch.Tensor) -> dict:
+    def observe(self, gradient: torch.Tensor) -> "CurvatureDecision":
         """Pressure = mean absolute value of a gradient tensor."""
         return self.observe_pressure(float(gradient.detach().abs().mean()) if gradient.numel() else 0.0)
 
-    def observe_pressure(self, raw_pressure: float) -> dict:
+    def observe_pressure(self, raw_pressure: float) -> "CurvatureDecision":
         raw = min(max(raw_pressure, 0.0), _PRESSURE_MAX) if math.isfinite(raw_pressure) else 0.0
         a = self.alpha
         smoothed = raw if self.ema_pressure is None else self.ema_pressure + a * (raw - self.ema_pressure)
@@ -435,7 +451,7 @@ class CurvatureScheduler:
             nxt = min(min(max(self.current + delta, self.min_curvature), self.max_curvature), -1e-6)
             if abs(nxt - self.current) > 1.1920929e-07:
                 self.current, changed = nxt, True
-        return {"raw_pressure": raw, "smoothed_pressure": smoothed, "curvature": self.current, "changed": changed}
+        return CurvatureDecision(raw, smoothed, self.current, changed)
 
     _FIELDS = ("min_curvature", "max_curvature", "target_pressure", "tolerance", "step", "kp", "alpha", "current",
                "ema_pressure", "ema_pressure2", "stability_threshold", "stability_boost", "stable_steps",
@@ -459,3 +475,255 @@ class CurvatureScheduler:
         for k in cls._FIELDS:
             setattr(sch, k, s[k])
         return sch
+
+
+# ---- coherence-driven learning-rate policy ------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class CoherenceSignal:
+    """The part of a sequencer's diagnostics the spectral policy consumes, re-derived through the coherence contract
+    so every number agrees with the normalized weights (crates/st-nn/src/trainer.rs:668-985)."""
+    dominant_channel: Optional[int]
+    preserved_channels: int
+    z_bias: float
+    control: object                  # zspace_coherence.ControlPayload
+    classification: object           # zspace_coherence.ClassificationPayload
+    repaired_weights_total: int = 0
+    pre_discard_repairs_total: int = 0
+
+    @classmethod
+    def from_diagnostics(cls, diagnostics) -> Optional["CoherenceSignal"]:
+        from .. import zspace_coherence as zc
+        try:
+            proj = diagnostics.project_to_zspace_partial()
+        except zc.CoherenceProjectionError:
+            return None
+        if proj.control is None or proj.classification is None:
+            return None
+        pre = diagnostics.pre_discard
+        return cls(diagnostics.dominant_channel, diagnostics.preserved_channels(), diagnostics.z_bias, proj.control,
+                   proj.classification, diagnostics.repaired_weights_total, 0 if pre is None else pre.repairs_total)
+
+    @property
+    def label(self) -> str:
+        return self.classification.label
+
+    @property
+    def repairs_total(self) -> int:
+        return self.repaired_weights_total + self.pre_discard_repairs_total
+
+
+@dataclass
+class SpectralAdjustment:
+    band_scale: tuple          # smoothed (above, here, beneath) gradient-band multipliers
+    lr_multiplier: float       # factor to apply to the current learning rate this step
+    lr_scale: float            # resulting absolute scale against the base learning rate
+    local_lr: tuple            # band scales divided by their mean, smoothed
+    metrics: dict
+
+
+class SpectralLearningRatePolicy:
+    """Turns coherence diagnostics + the roundtable band energy into per-band gradient scales and a learning-rate
+    multiplier (crates/st-nn/src/trainer.rs:4612-5216).
+
+    Per observation: the dominant channel's position biases Above or Beneath (``sheet_gain``), the Z bias does the same
+    (``spin_gain``), curvature and a flat spectrum (``1 - spectral_radius``) lift all bands; band energy shares tilt the
+    bands by ``energy_gain``; the dominant channel's index mod 3 picks the band that gets the phase gain (larger while
+    the dominant channel has not changed for a while — "stuck"); the coherence label scales the learning rate (cascade
+    0.7, symmetric 0.9, diffuse 1.15) and flattens the side bands.  Everything is smoothed (faster when the label
+    changed), clamped to the band / lr bounds, and the lr multiplier is limited to ``max_lr_step`` per observation."""
+
+    _STATE = ("smoothing", "event_smoothing", "turnover_smoothing", "coherence_gain", "curvature_gain", "sheet_gain", "spin_gain",
+              "radius_gain", "energy_gain", "phase_gain", "stuck_phase_gain", "max_phase_gain", "stuck_turnover_threshold",
+              "dominant_turnover", "last_dominant", "last_label", "min_lr_scale", "max_lr_scale", "max_lr_step", "min_band_scale",
+              "max_band_scale", "band_state", "lr_state", "applied_lr_scale", "local_lr_state")
+
+    def __init__(self):
+        self.smoothing, self.event_smoothing, self.turnover_smoothing = 0.2, 0.75, 0.15
+        self.coherence_gain, self.curvature_gain, self.sheet_gain, self.spin_gain = 0.5, 0.15, 0.6, 0.4
+        self.radius_gain, self.energy_gain = 0.35, 0.25
+        self.phase_gain, self.stuck_phase_gain, self.max_phase_gain, self.stuck_turnover_threshold = 0.25, 0.35, 0.65, 0.12
+        self.dominant_turnover, self.last_dominant, self.last_label = 0.0, None, None
+        self.min_lr_scale, self.max_lr_scale, self.max_lr_step = 0.1, 6.0, 1.4
+        self.min_band_scale, self.max_band_scale = 0.5, 2.75
+        self.band_state, self.lr_state, self.applied_lr_scale, self.local_lr_state = [1.0, 1.0, 1.0], 1.0, 1.0, [1.0, 1.0, 1.0]
+
+    # builders: values outside the domain are ignored
+    def _set_smooth(self, name, v):
+        if math.isfinite(v) and v > 0:
+            setattr(self, name, min(max(v, 1.0e-3), 1.0))
+        return self
+
+    def _set_nonneg(self, name, v, clamp_low=False):
+        if math.isfinite(v) and (clamp_low or v >= 0):
+            setattr(self, name, max(v, 0.0))
+        return self
+
+    def with_smoothing(self, v): return self._set_smooth("smoothing", v)                       # noqa: E704
+    def with_event_smoothing(self, v): return self._set_smooth("event_smoothing", v)           # noqa: E704
+    def with_turnover_smoothing(self, v): return self._set_smooth("turnover_smoothing", v)     # noqa: E704
+    def with_phase_gain(self, v): return self._set_nonneg("phase_gain", v)                     # noqa: E704
+    def with_stuck_phase_gain(self, v): return self._set_nonneg("stuck_phase_gain", v)         # noqa: E704
+    def with_stuck_turnover_threshold(self, v): return self._set_nonneg("stuck_turnover_threshold", v)   # noqa: E704
+    def with_coherence_gain(self, v): return self._set_nonneg("coherence_gain", v, True)       # noqa: E704
+    def with_sheet_gain(self, v): return self._set_nonneg("sheet_gain", v, True)               # noqa: E704
+    def with_spin_gain(self, v): return self._set_nonneg("spin_gain", v, True)                 # noqa: E704
+    def with_radius_gain(self, v): return self._set_nonneg("radius_gain", v, True)             # noqa: E704
+    def with_energy_gain(self, v): return self._set_nonneg("energy_gain", v, True)             # noqa: E704
+
+    def _clamp_state(self) -> None:
+        cl = lambda v, lo, hi: min(max(v, lo), hi)                                             # noqa: E731
+        self.band_state = [cl(v, self.min_band_scale, self.max_band_scale) for v in self.band_state]
+        self.local_lr_state = [cl(v, self.min_band_scale, self.max_band_scale) for v in self.local_lr_state]
+        self.lr_state = cl(self.lr_state, self.min_lr_scale, self.max_lr_scale)
+        self.applied_lr_scale = cl(self.applied_lr_scale, self.min_lr_scale, self.max_lr_scale)
+
+    def with_lr_bounds(self, lo, hi):
+        if math.isfinite(lo) and math.isfinite(hi) and lo > 0 and hi > lo:
+            self.min_lr_scale, self.max_lr_scale = lo, hi
+            self._clamp_state()
+        return self
+
+    def with_band_bounds(self, lo, hi):
+        if math.isfinite(lo) and math.isfinite(hi) and lo > 0 and hi > lo:
+            self.min_band_scale, self.max_band_scale = lo, hi
+            self._clamp_state()
+        return self
+
+    def with_max_lr_step(self, v):
+        if math.isfinite(v) and v > 0:
+            self.max_lr_step = max(v, 1.0)
+        return self
+
+    def apply_env_overrides(self, env=None) -> "SpectralLearningRatePolicy":
+        """``SPIRAL_SPECTRAL_POLICY_{SMOOTHING,EVENT_SMOOTHING,TURNOVER_SMOOTHING,PHASE_GAIN,STUCK_PHASE_GAIN,MAX_PHASE_GAIN,
+        STUCK_TURNOVER_THRESHOLD,LR_MIN,LR_MAX,BAND_MIN,BAND_MAX}``; unparsable or out-of-domain values are ignored."""
+        import os
+        env = os.environ if env is None else env
+
+        def num(key):
+            try:
+                v = float(env["SPIRAL_SPECTRAL_POLICY_" + key])
+                return v if math.isfinite(v) else None
+            except (KeyError, ValueError):
+                return None
+        for key, fn in (("SMOOTHING", self.with_smoothing), ("EVENT_SMOOTHING", self.with_event_smoothing),
+                        ("TURNOVER_SMOOTHING", self.with_turnover_smoothing), ("PHASE_GAIN", self.with_phase_gain),
+                        ("STUCK_PHASE_GAIN", self.with_stuck_phase_gain)):
+            v = num(key)
+            if v is not None:
+                fn(v)
+        v = num("MAX_PHASE_GAIN")
+        if v is not None and v >= 0:
+            self.max_phase_gain = v
+        v = num("STUCK_TURNOVER_THRESHOLD")
+        if v is not None and v >= 0:
+            self.stuck_turnover_threshold = min(v, 1.0)
+        lo, hi = num("LR_MIN"), num("LR_MAX")
+        if lo is not None and hi is not None:
+            self.with_lr_bounds(lo, hi)
+        lo, hi = num("BAND_MIN"), num("BAND_MAX")
+        if lo is not None and hi is not None:
+            self.with_band_bounds(lo, hi)
+        self._clamp_state()
+        return self
+
+    with_env_overrides = apply_env_overrides
+
+    def state(self) -> dict:
+        return {k: (list(getattr(self, k)) if isinstance(getattr(self, k), list) else getattr(self, k)) for k in self._STATE}
+
+    @classmethod
+    def from_state(cls, state: dict) -> "SpectralLearningRatePolicy":
+        p = cls()
+        for k in cls._STATE:
+            if k not in state:
+                raise ValueError(f"spectral policy state is missing '{k}'")
+            v = state[k]
+            if k in ("band_state", "local_lr_state"):
+                v = [float(x) for x in v]
+                if len(v) != 3 or not all(math.isfinite(x) and x > 0 for x in v):
+                    raise ValueError(f"spectral policy state '{k}' must hold three positive finite values")
+            elif k not in ("last_dominant", "last_label") and not math.isfinite(float(v)):
+                raise ValueError(f"spectral policy state '{k}' must be finite")
+            setattr(p, k, v)
+        if not (0 < p.min_lr_scale < p.max_lr_scale and 0 < p.min_band_scale < p.max_band_scale):
+            raise ValueError("spectral policy bounds must satisfy 0 < min < max")
+        if p.max_lr_step < 1.0:
+            raise ValueError("spectral policy max_lr_step must be at least 1")
+        inside = all(p.min_band_scale <= v <= p.max_band_scale for v in p.band_state + p.local_lr_state) and \
+            all(p.min_lr_scale <= v <= p.max_lr_scale for v in (p.lr_state, p.applied_lr_scale))
+        if not inside:
+            raise ValueError("spectral policy state lies outside its own bounds")
+        return p
+
+    def last_coherence_label(self) -> Optional[str]:
+        return self.last_label
+
+    @staticmethod
+    def _smooth(prev: float, target: float, alpha: float) -> float:
+        return target if not math.isfinite(prev) else prev + (target - prev) * alpha
+
+    def observe(self, diagnostics, curvature: float, band_energy) -> Optional[SpectralAdjustment]:
+        signal = diagnostics if isinstance(diagnostics, CoherenceSignal) or diagnostics is None else CoherenceSignal.from_diagnostics(diagnostics)
+        return self.observe_signal(signal, curvature, band_energy)
+
+    def observe_signal(self, signal: Optional[CoherenceSignal], curvature: float, band_energy) -> Optional[SpectralAdjustment]:
+        if signal is None:
+            return None
+        cl = lambda v, lo, hi: min(max(v, lo), hi)                                             # noqa: E731
+        label, ctl = signal.label, signal.control
+        sheets = max(ctl.channels, 1)
+        dominant = min(signal.dominant_channel or 0, sheets - 1)
+        changed = self.last_dominant is not None and self.last_dominant != dominant
+        self.dominant_turnover = cl(self._smooth(self.dominant_turnover, 1.0 if changed else 0.0, self.turnover_smoothing), 0.0, 1.0)
+        self.last_dominant = dominant
+        label_changed = self.last_label is not None and self.last_label != label
+        self.last_label = label
+        smoothing = max(self.event_smoothing, self.smoothing) if label_changed else self.smoothing
+        sheet_bias = ((dominant + 0.5) / sheets - 0.5) * self.sheet_gain
+        spin = cl(signal.z_bias, -1.0, 1.0)
+        spin_bias = spin * self.spin_gain
+        curv = math.sqrt(-curvature) * self.curvature_gain if curvature < 0 else 0.0
+        radius_bias = cl(1.0 - ctl.spectral_radius, 0.0, 1.0) * self.radius_gain
+        base = (1.0 + max(sheet_bias, 0.0) + max(spin_bias, 0.0) + curv * 0.25 + radius_bias * 0.5,
+                1.0 + max(1.0 - abs(sheet_bias), 0.0) * 0.5 * self.sheet_gain + curv * 0.5 + (1.0 - radius_bias) * 0.25,
+                1.0 + max(-sheet_bias, 0.0) + max(-spin_bias, 0.0) + curv * 0.25 + radius_bias * 0.5)
+        be = (band_energy.above, band_energy.here, band_energy.beneath)
+        tot = max(sum(abs(v) for v in be), 1e-5)
+        stuck = self.dominant_turnover < self.stuck_turnover_threshold
+        lr_label = {"background": 1.05 if stuck else 1.0, "symmetric_pulse": 0.9, "cascade_imbalance": 0.7, "diffuse_drift": 1.15}[label]
+        band_label = {"cascade_imbalance": (0.92, 1.15, 0.92), "symmetric_pulse": (0.96, 1.06, 0.96)}.get(label, (1.0, 1.0, 1.0))
+        pg = {"diffuse_drift": self.phase_gain * 1.15, "cascade_imbalance": 0.0, "symmetric_pulse": self.phase_gain * 0.35,
+              "background": self.phase_gain}[label]
+        if stuck and label != "cascade_imbalance":
+            pg += self.stuck_phase_gain
+        pg = cl(pg, 0.0, self.max_phase_gain)
+        phase_mul = [1.0 - 0.5 * pg] * 3
+        phase_mul[dominant % 3] = 1.0 + pg
+        lo, hi = self.min_band_scale, self.max_band_scale
+        for i in range(3):
+            t = cl(base[i] * (1.0 + cl(be[i] / tot, -1.0, 1.0) * self.energy_gain), lo, hi)
+            t = cl(t * phase_mul[i] * band_label[i], lo, hi)
+            self.band_state[i] = self._smooth(self.band_state[i], t, smoothing)
+        band = tuple(self.band_state)
+        mean_band = sum(band) / 3.0
+        target_lr = cl(mean_band * (1.0 + ctl.spectral_pressure * self.coherence_gain) * lr_label, self.min_lr_scale, self.max_lr_scale)
+        self.lr_state = self._smooth(self.lr_state, target_lr, smoothing)
+        target_lr = cl(self.lr_state, self.min_lr_scale, self.max_lr_scale)
+        for i in range(3):
+            self.local_lr_state[i] = self._smooth(self.local_lr_state[i], cl(band[i] / mean_band, lo, hi), smoothing)
+        local = tuple(self.local_lr_state)
+        mult = 1.0
+        if math.isfinite(self.applied_lr_scale) and self.applied_lr_scale > 0:
+            step = self.max_lr_step * 1.25 if label_changed else self.max_lr_step
+            mult = cl(target_lr / self.applied_lr_scale, 1.0 / step, step)
+        self.applied_lr_scale = cl(self.applied_lr_scale * mult, self.min_lr_scale, self.max_lr_scale)
+        metrics = {"absolute_lr_scale": self.applied_lr_scale, "sheet_index": signal.dominant_channel, "sheet_count": sheets,
+                   "spin_alignment": spin, "raw_mean_coherence": ctl.raw_mean_coherence, "raw_coherence_entropy": ctl.raw_coherence_entropy,
+                   "spectral_radius": ctl.spectral_radius, "spectral_entropy": ctl.spectral_entropy,
+                   "spectral_pressure": ctl.spectral_pressure, "effective_channels": ctl.effective_channels,
+                   "distribution_channels": ctl.channels, "energy_ratio": ctl.energy_ratio, "control_kind": ctl.kind,
+                   "control_contract_version": ctl.contract_version, "classification_reason": signal.classification.reason,
+                   "classification_contract_version": signal.classification.contract_version, "label": label,
+                   "band_scale": band, "local_lr": local}
+        return SpectralAdjustment(band, mult, self.applied_lr_scale, local, metrics)

@@ -111,6 +111,34 @@ class StepMetrics:
     extra: dict = field(default_factory=dict)
 
 
+def _signal_from_trace_record(record):
+    """A coherence signal from a stable ``Aggregated`` trace record; ``None`` unless the record carries a complete
+    distribution witness whose re-derived summary agrees with the numbers written beside it."""
+    from .. import zspace_coherence as zc
+    from .amp import CoherenceSignal
+    if not isinstance(record, dict) or record.get("kind") != "Aggregated":
+        return None
+    d = (record.get("payload") or {}).get("diagnostics") or {}
+    wit = d.get("distribution_witness")
+    try:
+        witness = zc.DistributionWitness(**wit)
+        dist = zc.validate_distribution_witness(witness)
+        close = lambda a, b: a is not None and abs(a - b) <= 8 * 1.1920929e-07 * max(abs(b), 1.0)      # noqa: E731
+        if d.get("distribution_channels") != dist.channels or not close(d.get("entropy"), dist.weight_entropy) \
+                or not close(d.get("normalized_entropy"), dist.normalized_entropy) or not close(d.get("concentration"), dist.concentration):
+            return None
+        proj = zc.project(zc.DiagnosticsInput(d["mean_coherence"], d["entropy"], d["energy_ratio"], d["z_bias"], d["fractional_order"],
+                                              list(witness.normalized_weights), d["preserved_channels"], d["discarded_channels"],
+                                              d.get("dominant_channel")))
+    except (TypeError, KeyError, zc.CoherenceProjectionError):
+        return None
+    if proj.control is None or proj.classification is None or proj.classification.label != d.get("classification_kind"):
+        return None
+    pre = d.get("pre_discard") or {}
+    return CoherenceSignal(d.get("dominant_channel"), d["preserved_channels"], d["z_bias"], proj.control, proj.classification,
+                           int(d.get("repaired_weights_total", 0)), int(pre.get("repairs_total", 0)))
+
+
 class ModuleTrainer:
     def __init__(self, *, backend: str = "cpu", curvature: float = -1.0, hyper_learning_rate: float = 1e-2,
                  fallback_learning_rate: float = 1e-2, lane_width: Optional[int] = None,
@@ -239,6 +267,73 @@ class ModuleTrainer:
         plugin.publish("EpochEnd", {"epoch": self.epoch, "loss": stats.average_loss})
         return stats
 
+    # ---- coherence-driven learning rate (crates/st-nn/src/trainer.rs:5667-5700, 7488-7545) ----------------------------
+    def enable_spectral_learning_rate(self, policy=None) -> None:
+        """Per step, a pending coherence signal (pushed diagnostics, or the latest ``Aggregated`` record a sequencer's
+        trace recorder published on the plugin bus) is turned into roundtable band weights and a learning-rate
+        multiplier; needs a roundtable schedule in ``train_epoch``."""
+        from .amp import SpectralLearningRatePolicy
+        self.spectral_policy = (policy or SpectralLearningRatePolicy()).apply_env_overrides()
+        self.last_spectral_metrics = None
+        self.enable_zspace_trace_coherence_bridge()
+
+    def disable_spectral_learning_rate(self) -> None:
+        self.spectral_policy = None
+        self.last_spectral_metrics = None
+
+    def push_coherence_diagnostics(self, diagnostics) -> bool:
+        from .amp import CoherenceSignal
+        self.pending_coherence = CoherenceSignal.from_diagnostics(diagnostics)
+        return self.pending_coherence is not None
+
+    def enable_zspace_trace_coherence_bridge(self) -> None:
+        if getattr(self, "_coherence_bridge", None) is None:
+            self._bridge_latest = None
+
+            def on_trace(event: dict) -> None:
+                sig = _signal_from_trace_record(event.get("record"))
+                if sig is not None:
+                    self._bridge_latest = sig
+            self._coherence_bridge = plugin.subscribe("ZSpaceTrace", on_trace)
+
+    def disable_zspace_trace_coherence_bridge(self) -> None:
+        sid = getattr(self, "_coherence_bridge", None)
+        if sid is not None:
+            plugin.unsubscribe("ZSpaceTrace", sid)
+            self._coherence_bridge = None
+            self._bridge_latest = None
+
+    def scale_learning_rates(self, module: Module, factor: float) -> None:
+        if not (math.isfinite(factor) and factor > 0):
+            raise TensorError(f"learning-rate factor must be positive and finite, got {factor}")
+        self.fallback_learning_rate *= factor
+        self.hyper_learning_rate *= factor
+        if self.realgrad_lr is not None:
+            self.realgrad_lr *= factor
+        for p in module.parameters():
+            for tape in (p.hypergrad, p.realgrad):
+                if tape is not None:
+                    tape.learning_rate *= factor
+
+    def _spectral_band_weights(self, module: Module):
+        policy = getattr(self, "spectral_policy", None)
+        if policy is None:
+            return None
+        if getattr(self, "pending_coherence", None) is None and getattr(self, "_bridge_latest", None) is not None:
+            self.pending_coherence, self._bridge_latest = self._bridge_latest, None
+        signal, self.pending_coherence = getattr(self, "pending_coherence", None), None
+        from ..inference import BandEnergy
+        adj = policy.observe_signal(signal, self.curvature, BandEnergy(**self.last_band_energy))
+        if adj is None:
+            return None
+        if math.isfinite(adj.lr_multiplier) and abs(adj.lr_multiplier - 1.0) > 1.0e-3:
+            self.scale_learning_rates(module, adj.lr_multiplier)
+        self.last_spectral_metrics = adj.metrics
+        for w in adj.band_scale:
+            if not (math.isfinite(w) and w >= 0):
+                raise TensorError(f"band weight must be finite and non-negative, got {w}")
+        return adj.band_scale
+
     def enable_autopilot(self, autopilot, apply_picks=None, device_load=None) -> None:
         """Couples an :class:`spiraltorch_b200.runtime.autopilot.Autopilot` to the step loop: before every
         batch the trainer builds the context (batch rows, feature columns, parameter count, device load), asks
@@ -326,10 +421,17 @@ class ModuleTrainer:
             grad = loss.backward(pred, y)
             if schedule is not None:
                 self.last_band_energy = schedule.band_energy(grad)
-            if schedule is not None and self.band_backward:
-                for band in schedule.split(grad):
-                    if float(band.torch().abs().max()) > 0.0:
-                        module.backward(x, band)
+            weights = self._spectral_band_weights(module) if schedule is not None else None
+            if schedule is not None and (self.band_backward or weights is not None):
+                bands = schedule.split(grad)
+                if weights is not None:
+                    bands = tuple(Tensor._wrap(b.torch() * w) for b, w in zip(bands, weights))
+                if self.band_backward:
+                    for band in bands:
+                        if float(band.torch().abs().max()) > 0.0:
+                            module.backward(x, band)
+                else:                                   # backward is linear in the gradient: one pass over the weighted sum
+                    module.backward(x, Tensor._wrap(bands[0].torch() + bands[1].torch() + bands[2].torch()))
             else:
                 module.backward(x, grad)
             for p in module.parameters():
