@@ -22,8 +22,8 @@ from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregatio
 from .lightning import (InfoNCELoss, LightningConfig, LightningReport, LightningStage, SelfSupStage, SpiralLightning)
 from .zrba import (BetaGate, BetaGateConfig, BetaGateSample, CovHead, CovHeadTelemetry, ReliabilityBin,
                    SpectralFeatureSample, ZCov, ZRBA, ZRBAConfig, ZRBAMetrics, ZRBATelemetry, ZTelemetryBundle)
-from .zspace import (ArdParameters, LanguageWaveEncoder, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention, ZSpaceTextVae,
-                     ZSpaceVae, ZSpaceVaeState, ZTensor)
+from .zspace import (ArdParameters, LanguageWaveEncoder, MellinBasis, ZFrame, ZIndex, ZMetricWeights, ZRBFAttention,
+                     ZSpaceTextVae, ZSpaceVae, ZSpaceVaeBatchStats, ZSpaceVaeState, ZSpaceVaeStats, ZTensor)
 from .coherence import (CoherenceBackend, CoherenceChannelReport, CoherenceDiagnostics, CoherenceEngine, CoherenceObservation,
                         CoherenceSignature, DomainLinguisticProfile, LinguisticChannelReport, LinguisticContour,
                         PreDiscardPolicy, PreDiscardRegulator, PreDiscardSnapshot, PreDiscardTelemetry,

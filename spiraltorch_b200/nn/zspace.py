@@ -149,17 +149,90 @@ class ZRBFAttention:
         return ZRBFAttentionOutput(Tensor._wrap(mean), Tensor._wrap(var), tel)
 
 
+class MellinBasis:
+    """Per-coordinate exponents: ``project(x) = sign(x) |x|^s / ||.||`` with ``|x|`` floored at 1e-9 and exponent 1
+    for coordinates past the table (crates/st-nn/src/zspace_coherence/vae.rs:15-74)."""
+
+    def __init__(self, exponents):
+        self.exponents = torch.as_tensor(list(exponents), dtype=torch.float64)
+
+    @classmethod
+    def constant(cls, dimension: int, exponent: float) -> "MellinBasis":
+        return cls([exponent] * dimension)
+
+    @classmethod
+    def ramp(cls, dimension: int, start: float, end: float) -> "MellinBasis":
+        if dimension <= 1:
+            return cls([start])
+        return cls([start + (end - start) * i / (dimension - 1) for i in range(dimension)])
+
+    def dimension(self) -> int:
+        return int(self.exponents.numel())
+
+    def project(self, x) -> torch.Tensor:
+        t = _t(x).double()
+        flat = t.reshape(-1, t.shape[-1])
+        e = torch.ones(flat.shape[-1], dtype=torch.float64, device=t.device)
+        n = min(self.dimension(), flat.shape[-1])
+        e[:n] = self.exponents[:n].to(t.device)
+        warped = torch.sign(flat) * flat.abs().clamp(min=1e-9) ** e
+        warped = torch.where(flat == 0, flat.abs().clamp(min=1e-9) ** e, warped)          # +0 keeps the positive branch
+        norm = warped.norm(dim=-1, keepdim=True)
+        return (warped / torch.where(norm > 0, norm, torch.ones_like(norm))).reshape(t.shape).to(_t(x).dtype if _t(x).is_floating_point() else torch.float32)
+
+
+@dataclass
+class ZSpaceVaeStats:
+    """Per-call losses: mean squared reconstruction error over the input dimensions, KL summed over the latent
+    dimensions, ELBO = -(recon + kl); batch calls report the mean over rows."""
+    recon_loss: float
+    kl_loss: float
+    evidence_lower_bound: float
+    target: torch.Tensor
+
+
 @dataclass
 class ZSpaceVaeState:
     mu: torch.Tensor
     logvar: torch.Tensor
     latent: torch.Tensor
     reconstruction: torch.Tensor
+    stats: ZSpaceVaeStats
+
+    recon_loss = property(lambda self: self.stats.recon_loss)
+    kl_loss = property(lambda self: self.stats.kl_loss)
+    evidence_lower_bound = property(lambda self: self.stats.evidence_lower_bound)
+
+
+@dataclass
+class ZSpaceVaeBatchStats:
+    batch_size: int
     recon_loss: float
     kl_loss: float
+    evidence_lower_bound: float
+    weighted_loss: float
+    kl_weight: float
+    learning_rate: float
+    gradient_l2: float
+    clipped_gradient_l2: float
+    update_l2: float
+    optimizer_step: int
+    optimizer: str
+
+    def __getitem__(self, key: str):
+        return self.batch_size if key == "samples" else getattr(self, key)
 
 
 class ZSpaceVae:
+    """Linear-Gaussian VAE over Z-space coordinates with its own SGD / Adam / RMSprop state
+    (crates/st-nn/src/zspace_coherence/vae.rs:296-1044).
+
+    Training uses the latent mean (no sampling noise in the gradient) and closed-form gradients:
+    ``d_rec = 2 (rec - x) / input_dim``, ``dW_dec = d_rec^T z``, ``d_mu = d_rec W_dec + beta mu``,
+    ``d_logvar = beta (exp(logvar) - 1) / 2``, encoder gradients are the outer products with the input, all averaged
+    over the batch — five GEMMs per step on the parameters' device instead of a per-sample loop.  The summed gradient
+    is clipped to ``grad_clip`` (L2 over all six tensors) before the optimizer step."""
+
     OPTIMIZERS = ("sgd", "adam", "rmsprop")
 
     def __init__(self, input_dim: int, latent_dim: int, seed: int = 0, device="cpu"):
@@ -177,7 +250,7 @@ class ZSpaceVae:
         self._kind, self._step = "sgd", 0
         self._m = {k: torch.zeros_like(v) for k, v in self.p.items()}
         self._v = {k: torch.zeros_like(v) for k, v in self.p.items()}
-        self._hyper = {"beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "decay": 0.99}
+        self._hyper = {"beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "decay": 0.99, "grad_clip": None}
 
     def optimizer_kind(self) -> str:
         return self._kind
@@ -186,12 +259,25 @@ class ZSpaceVae:
         return self._step
 
     def configure_optimizer_by_name(self, name: str, **hyper) -> None:
+        """``beta1`` / ``beta2`` in [0, 1), ``eps`` > 0, ``decay`` in [0, 1), ``grad_clip`` positive or ``None``."""
         name = name.lower()
         if name not in self.OPTIMIZERS:
             raise TensorError(f"unknown optimiser '{name}'")
+        aliases = {"epsilon": "eps", "rms_decay": "decay"}
+        hyper = {aliases.get(k, k): v for k, v in hyper.items()}
+        for k, v in hyper.items():
+            if k not in self._hyper:
+                raise TensorError(f"unknown optimiser setting '{k}'")
+            if k == "grad_clip":
+                if v is not None and not (math.isfinite(v) and v > 0):
+                    raise TensorError("invalid value: zspace_vae_grad_clip")
+            elif not math.isfinite(v) or (k == "eps" and v <= 0) or (k != "eps" and not 0.0 <= v < 1.0):
+                raise TensorError(f"invalid value: zspace_vae_{k}")
         self._kind = name
         self._hyper.update(hyper)
         self.reset_optimizer()
+
+    configure_optimizer = configure_optimizer_by_name
 
     def reset_optimizer(self) -> None:
         self._step = 0
@@ -199,62 +285,130 @@ class ZSpaceVae:
             for t in d.values():
                 t.zero_()
 
+    def _rows(self, x, label: str = "zspace_vae_input") -> torch.Tensor:
+        x = _t(x).float().reshape(-1, self.input_dim).to(self.p["dec"].device)
+        if x.shape[0] == 0:
+            raise TensorError(f"empty input: {label}")
+        if not bool(torch.isfinite(x).all()):
+            raise TensorError(f"non-finite value for {label}")
+        return x
+
     def encode(self, x: torch.Tensor):
         return x @ self.p["enc_mu"] + self.p["b_mu"], x @ self.p["enc_logvar"] + self.p["b_logvar"]
+
+    def encode_with_mellin(self, x, basis: MellinBasis):
+        return self.encode(basis.project(x).float())
 
     def decode(self, z: torch.Tensor) -> torch.Tensor:
         return z @ self.p["dec"] + self.p["b_dec"]
 
-    def _losses(self, x, p, eps):
-        mu = x @ p["enc_mu"] + p["b_mu"]
-        logvar = (x @ p["enc_logvar"] + p["b_logvar"]).clamp(-10.0, 10.0)
-        z = mu + torch.exp(0.5 * logvar) * eps
-        rec = z @ p["dec"] + p["b_dec"]
-        recon = ((rec - x) ** 2).sum(-1).mean()
-        kl = (-0.5 * (1 + logvar - mu ** 2 - logvar.exp()).sum(-1)).mean()
-        return mu, logvar, z, rec, recon, kl
+    def decode_with_mellin(self, z, basis: MellinBasis) -> torch.Tensor:
+        return basis.project(self.decode(z)).float()
+
+    def _state(self, x, mu, logvar, z) -> ZSpaceVaeState:
+        rec = self.decode(z)
+        recon = ((rec - x) ** 2).mean(-1)
+        kl = -0.5 * (1 + logvar - mu ** 2 - logvar.exp()).sum(-1)
+        r, k = float(recon.mean()), float(kl.mean())
+        return ZSpaceVaeState(mu, logvar, z, rec, ZSpaceVaeStats(r, k, -(r + k), x))
 
     def forward(self, x, sample: bool = True) -> ZSpaceVaeState:
-        x = _t(x).float().reshape(-1, self.input_dim)
-        eps = torch.randn(x.shape[0], self.latent_dim, generator=self._gen).to(x.device) if sample else \
-            torch.zeros(x.shape[0], self.latent_dim, device=x.device)
-        with torch.no_grad():
-            mu, logvar, z, rec, recon, kl = self._losses(x, self.p, eps)
-        return ZSpaceVaeState(mu, logvar, z, rec, float(recon), float(kl))
+        x = self._rows(x)
+        mu, logvar = self.encode(x)
+        z = mu
+        if sample:
+            z = mu + torch.exp(0.5 * logvar) * torch.randn(x.shape[0], self.latent_dim, generator=self._gen).to(x.device)
+        return self._state(x, mu, logvar, z)
 
     def forward_mean(self, x) -> ZSpaceVaeState:
         return self.forward(x, sample=False)
 
-    def train_batch(self, x, learning_rate: float = 1e-2, beta: float = 1.0) -> ZSpaceVaeState:
-        x = _t(x).float().reshape(-1, self.input_dim)
-        if not bool(torch.isfinite(x).all()):
-            raise TensorError("non-finite VAE input")
-        eps = torch.randn(x.shape[0], self.latent_dim, generator=self._gen).to(x.device)
-        leaves = {k: v.detach().clone().requires_grad_(True) for k, v in self.p.items()}
-        with torch.enable_grad():
-            mu, logvar, z, rec, recon, kl = self._losses(x, leaves, eps)
-            grads = torch.autograd.grad(recon + beta * kl, list(leaves.values()))
+    @staticmethod
+    def _hyperparams(learning_rate: float, kl_weight: float):
+        if not math.isfinite(learning_rate):
+            raise TensorError("non-finite value for zspace_vae_learning_rate")
+        if learning_rate <= 0:
+            raise TensorError(f"non-positive learning rate {learning_rate}")
+        if not math.isfinite(kl_weight):
+            raise TensorError("non-finite value for zspace_vae_kl_weight")
+        if kl_weight < 0:
+            raise TensorError("invalid value: zspace_vae_kl_weight")
+        return float(learning_rate), float(kl_weight)
+
+    def _gradients(self, x, beta: float):
+        mu, logvar = self.encode(x)
+        st = self._state(x, mu, logvar, mu)
+        n = x.shape[0]
+        d_rec = (st.reconstruction - x) * (2.0 / self.input_dim)
+        d_mu = d_rec @ self.p["dec"].T
+        d_lv = torch.zeros_like(logvar)
+        if beta > 0:
+            d_mu = d_mu + beta * mu
+            d_lv = beta * 0.5 * (logvar.exp() - 1.0)
+        g = {"enc_mu": x.T @ d_mu / n, "enc_logvar": x.T @ d_lv / n, "dec": mu.T @ d_rec / n,
+             "b_mu": d_mu.mean(0), "b_logvar": d_lv.mean(0), "b_dec": d_rec.mean(0)}
+        return st, g
+
+    def _apply(self, grads: dict, lr: float) -> float:
         self._step += 1
-        h = self._hyper
-        for (k, w), g in zip(self.p.items(), grads):
+        h, sq = self._hyper, 0.0
+        for k, w in self.p.items():
+            g = grads[k]
             if self._kind == "sgd":
-                upd = g
+                upd = lr * g
             elif self._kind == "adam":
                 self._m[k].mul_(h["beta1"]).add_(g, alpha=1 - h["beta1"])
                 self._v[k].mul_(h["beta2"]).addcmul_(g, g, value=1 - h["beta2"])
-                upd = (self._m[k] / (1 - h["beta1"] ** self._step)) / \
-                      ((self._v[k] / (1 - h["beta2"] ** self._step)).sqrt() + h["eps"])
+                upd = lr * (self._m[k] / (1 - h["beta1"] ** self._step)) / \
+                    ((self._v[k] / (1 - h["beta2"] ** self._step)).sqrt() + h["eps"])
             else:
                 self._v[k].mul_(h["decay"]).addcmul_(g, g, value=1 - h["decay"])
-                upd = g / (self._v[k].sqrt() + h["eps"])
-            w.sub_(learning_rate * upd)
-        return ZSpaceVaeState(mu.detach(), logvar.detach(), z.detach(), rec.detach(), float(recon.detach()), float(kl.detach()))
+                upd = lr * g / (self._v[k].sqrt() + h["eps"])
+            w.sub_(upd)
+            sq += float(upd.pow(2).sum())
+        return math.sqrt(sq)
 
-    train_step = train_batch
+    def _clip(self, grads: dict):
+        norm = math.sqrt(sum(float(g.pow(2).sum()) for g in grads.values()))
+        limit = self._hyper["grad_clip"]
+        if limit is not None and norm > limit and norm > 0:
+            for g in grads.values():
+                g.mul_(limit / norm)
+            return norm, limit
+        return norm, norm
 
-    def evaluate_batch(self, x) -> dict:
-        st = self.forward_mean(x)
-        return {"recon_loss": st.recon_loss, "kl_loss": st.kl_loss, "samples": st.mu.shape[0]}
+    def train_batch(self, x, learning_rate: float = 1e-2, beta: float = 1.0) -> ZSpaceVaeBatchStats:
+        x = self._rows(x, "zspace_vae_train_batch")
+        lr, beta = self._hyperparams(learning_rate, beta)
+        st, grads = self._gradients(x, beta)
+        norm, clipped = self._clip(grads)
+        upd = self._apply(grads, lr)
+        s = st.stats
+        return ZSpaceVaeBatchStats(x.shape[0], s.recon_loss, s.kl_loss, s.evidence_lower_bound, s.recon_loss + beta * s.kl_loss, beta, lr,
+                                   norm, clipped, upd, self._step, self._kind)
+
+    def train_step(self, x, learning_rate: float = 1e-2, beta: float = 1.0) -> ZSpaceVaeState:
+        """One update from a single input (or a batch treated as one averaged sample); returns the pre-update state."""
+        x = self._rows(x)
+        lr, beta = self._hyperparams(learning_rate, beta)
+        st, grads = self._gradients(x, beta)
+        self._clip(grads)
+        self._apply(grads, lr)
+        return st
+
+    def evaluate_batch(self, x, beta: float = 1.0) -> ZSpaceVaeBatchStats:
+        x = self._rows(x, "zspace_vae_evaluate_batch")
+        _, beta = self._hyperparams(1.0, beta)
+        s = self.forward_mean(x).stats
+        return ZSpaceVaeBatchStats(x.shape[0], s.recon_loss, s.kl_loss, s.evidence_lower_bound, s.recon_loss + beta * s.kl_loss, beta, 0.0,
+                                   0.0, 0.0, 0.0, self._step, self._kind)
+
+    def refine_decoder(self, state: ZSpaceVaeState, learning_rate: float) -> None:
+        """One plain gradient step of the decoder alone towards the state's target, rate clamped to [1e-6, 0.1]."""
+        lr = min(max(learning_rate, 1e-6), 1e-1)
+        err = state.reconstruction - state.stats.target
+        self.p["dec"].sub_(lr * (state.latent.T @ err) / err.shape[0])
+        self.p["b_dec"].sub_(lr * err.mean(0))
 
     def state_dict(self) -> dict:
         return {k: v.detach().cpu().clone() for k, v in self.p.items()}
@@ -268,7 +422,8 @@ class ZSpaceVae:
     def save(self, path) -> None:
         import json
         from ..config import atomic_write
-        atomic_write(path, json.dumps({"input_dim": self.input_dim, "latent_dim": self.latent_dim, "optimizer": self._kind,
+        atomic_write(path, json.dumps({"version": 1, "input_dim": self.input_dim, "latent_dim": self.latent_dim, "optimizer": self._kind,
+                                       "optimizer_step": self._step, "hyper": self._hyper,
                                        "parameters": {k: {"shape": list(v.shape), "data": v.flatten().tolist()}
                                                       for k, v in self.state_dict().items()}}))
 
@@ -276,9 +431,13 @@ class ZSpaceVae:
     def load(cls, path) -> "ZSpaceVae":
         import json
         blob = json.load(open(path))
+        if blob.get("version", 1) != 1:
+            raise TensorError(f"unsupported VAE checkpoint version {blob.get('version')}")
         vae = cls(blob["input_dim"], blob["latent_dim"])
         vae.load_state_dict({k: torch.tensor(v["data"]).reshape(v["shape"]) for k, v in blob["parameters"].items()})
         vae._kind = blob.get("optimizer", "sgd")
+        vae._step = int(blob.get("optimizer_step", 0))
+        vae._hyper.update(blob.get("hyper", {}))
         return vae
 
 
@@ -348,9 +507,11 @@ class ZSpaceTextVae:
     def encode_text(self, text: str) -> torch.Tensor:
         return self.encoder.encode_z_space(self._window(text)).reshape(-1)
 
-    def encode_text_with_mellin(self, text: str, basis: torch.Tensor) -> torch.Tensor:
-        """Projects the encoding onto a ``(input_dim, input_dim)`` Mellin basis matrix."""
+    def encode_text_with_mellin(self, text: str, basis) -> torch.Tensor:
+        """Warps the encoding by a :class:`MellinBasis`, or projects it onto an ``(input_dim, input_dim)`` matrix."""
         enc = self.encode_text(text)
+        if isinstance(basis, MellinBasis):
+            return basis.project(enc).float()
         if basis.shape != (self.input_dim, self.input_dim):
             raise TensorError(f"Mellin basis must be {self.input_dim}x{self.input_dim}, got {tuple(basis.shape)}")
         return basis.to(enc.dtype) @ enc
@@ -368,13 +529,13 @@ class ZSpaceTextVae:
         return self.vae.forward_mean(self._batch([text], basis))
 
     def train_text(self, text: str, learning_rate: float = 1e-2, beta: float = 1.0, basis=None) -> ZSpaceVaeState:
-        return self.vae.train_batch(self._batch([text], basis), learning_rate, beta)
+        return self.vae.train_step(self._batch([text], basis), learning_rate, beta)
 
-    def train_text_batch(self, texts, learning_rate: float = 1e-2, beta: float = 1.0, basis=None) -> ZSpaceVaeState:
+    def train_text_batch(self, texts, learning_rate: float = 1e-2, beta: float = 1.0, basis=None) -> ZSpaceVaeBatchStats:
         return self.vae.train_batch(self._batch(list(texts), basis), learning_rate, beta)
 
-    def evaluate_text_batch(self, texts, basis=None) -> dict:
-        return self.vae.evaluate_batch(self._batch(list(texts), basis))
+    def evaluate_text_batch(self, texts, basis=None, beta: float = 1.0) -> ZSpaceVaeBatchStats:
+        return self.vae.evaluate_batch(self._batch(list(texts), basis), beta)
 
     def save(self, path) -> None:
         import json

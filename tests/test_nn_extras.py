@@ -379,3 +379,61 @@ def test_zrba_block_gate_covariance_and_metrics():
     assert abs(spearman_rank_correlation([1, 2, 3, 4], [4, 3, 2, 1]) + 1.0) < 1e-12
     with pytest.raises(TensorError):
         ZRBAMetrics.compute(z.mu, z.sigma, [0.0], 0.9, idx)
+
+
+def test_zspace_vae_closed_form_gradients_match_autograd_and_stats():
+    torch.manual_seed(4)
+    vae = zspace.ZSpaceVae(6, 3, seed=1)
+    x = torch.randn(5, 6)
+    leaves = {k: v.clone().requires_grad_(True) for k, v in vae.p.items()}
+    mu = x @ leaves["enc_mu"] + leaves["b_mu"]
+    lv = x @ leaves["enc_logvar"] + leaves["b_logvar"]
+    rec = mu @ leaves["dec"] + leaves["b_dec"]
+    loss = (((rec - x) ** 2).mean(-1) + 0.3 * (-0.5 * (1 + lv - mu ** 2 - lv.exp()).sum(-1))).mean()
+    want = torch.autograd.grad(loss, list(leaves.values()))
+    _, got = vae._gradients(x, 0.3)
+    for (k, _), w in zip(leaves.items(), want):
+        assert torch.allclose(got[k], w, atol=1e-6), k
+    vae.configure_optimizer_by_name("adam", grad_clip=1e-3)
+    before = {k: v.clone() for k, v in vae.p.items()}
+    st_ = vae.train_batch(x, learning_rate=1e-2, beta=0.3)
+    assert st_.batch_size == 5 and st_["samples"] == 5 and st_.optimizer == "adam" and st_.optimizer_step == 1
+    assert st_.gradient_l2 > 1e-3 and st_.clipped_gradient_l2 == pytest.approx(1e-3) and st_.update_l2 > 0
+    assert st_.weighted_loss == pytest.approx(st_.recon_loss + 0.3 * st_.kl_loss)
+    assert st_.evidence_lower_bound == pytest.approx(-(st_.recon_loss + st_.kl_loss))
+    assert any(not torch.equal(before[k], vae.p[k]) for k in before)
+    ev = vae.evaluate_batch(x, beta=0.0)
+    assert ev.learning_rate == 0.0 and ev.gradient_l2 == 0.0 and ev.kl_weight == 0.0
+    state = vae.forward_mean(x)
+    assert torch.equal(state.latent, state.mu) and state.recon_loss == state.stats.recon_loss
+    r0 = state.recon_loss
+    for _ in range(20):
+        vae.refine_decoder(vae.forward_mean(x), 0.05)
+    assert vae.forward_mean(x).recon_loss < r0
+    for bad in (dict(learning_rate=0.0), dict(learning_rate=float("nan")), dict(beta=-1.0)):
+        with pytest.raises(st.TensorError):
+            vae.train_batch(x, **{"learning_rate": 1e-2, "beta": 1.0, **bad})
+    with pytest.raises(st.TensorError):
+        vae.configure_optimizer_by_name("adam", grad_clip=-1.0)
+    with pytest.raises(st.TensorError):
+        vae.train_batch(torch.full((2, 6), float("inf")))
+
+
+def test_mellin_basis_projection():
+    b = zspace.MellinBasis([1.0, 2.0, 0.5])
+    p = b.project(torch.tensor([1.0, -2.0, 3.0]))
+    assert float(p.norm()) == pytest.approx(1.0, abs=1e-6) and p[1] < 0
+    raw = torch.tensor([1.0, -4.0, 3.0 ** 0.5])
+    assert torch.allclose(p, raw / raw.norm(), atol=1e-6)
+    ramp = zspace.MellinBasis.ramp(4, 0.5, 2.0)
+    assert ramp.exponents.tolist() == pytest.approx([0.5, 1.0, 1.5, 2.0]) and ramp.dimension() == 4
+    assert zspace.MellinBasis.ramp(1, 0.7, 9.0).exponents.tolist() == [0.7]
+    assert zspace.MellinBasis.constant(3, 2.0).exponents.tolist() == [2.0] * 3
+    short = zspace.MellinBasis([2.0]).project(torch.tensor([[2.0, 3.0]]))          # missing exponents default to 1
+    assert torch.allclose(short, torch.tensor([[4.0, 3.0]]) / 5.0, atol=1e-6)
+    vae = zspace.ZSpaceVae(3, 2, seed=0)
+    mu, _ = vae.encode_with_mellin(torch.tensor([[1.0, -2.0, 3.0]]), b)
+    assert torch.allclose(mu, vae.encode(p.reshape(1, 3))[0], atol=1e-6)
+    assert float(vae.decode_with_mellin(mu, b).norm()) == pytest.approx(1.0, abs=1e-5)
+    tv = zspace.ZSpaceTextVae(4, 2)
+    assert float(tv.encode_text_with_mellin("abcd", zspace.MellinBasis.constant(8, 1.5)).norm()) == pytest.approx(1.0, abs=1e-5)
