@@ -325,7 +325,13 @@ def bench_layers(iters, profile):
     if profile:
         wave_step(); gnn_step(); torch.cuda.synchronize()
         return out
-    for name, fn, cpu_ms, wgpu_ms in (("wave_rnn_train_step", wave_step, 7.132, 125.897), ("gnn_train_step", gnn_step, 16.503, 362.814)):
+    # the same two steps captured once in a CUDA graph and replayed (st.nn.GraphedTrainStep): the launches are issued
+    # from the device, so what is left is the kernels' own time
+    wave_g = st.nn.GraphedTrainStep(wave, loss, x, y, learning_rate=1e-2)
+    gnn_g = st.nn.GraphedTrainStep(model, loss, gx, gy, learning_rate=1e-2)
+    for name, fn, cpu_ms, wgpu_ms in (("wave_rnn_train_step", wave_step, 7.132, 125.897), ("gnn_train_step", gnn_step, 16.503, 362.814),
+                                      ("wave_rnn_train_step_graphed", lambda: wave_g(x, y), 7.132, 125.897),
+                                      ("gnn_train_step_graphed", lambda: gnn_g(gx, gy), 16.503, 362.814)):
         r = {"kernel": name, "ours_ms": round(timed(fn, iters), 4), "reference_published_cpu_ms": cpu_ms,
              "reference_published_wgpu_ms": wgpu_ms}
         print(json.dumps(r), flush=True)

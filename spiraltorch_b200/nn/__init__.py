@@ -12,7 +12,8 @@ from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, I
                       ZSpaceCoherenceWaveBlock, ZSpaceLayerNorm, ZSpaceMixer, ZSpaceSoftmax, conv_output_shape,
                       pool_output_shape)
 from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
-from . import amp, coherence, conv, fields, gnn, lightning, roundtable, zrba, zspace
+from . import amp, coherence, conv, fields, gnn, graph, lightning, roundtable, zrba, zspace
+from .graph import GraphedTrainStep
 from .roundtable import DistConfig, MetaConductor, MetaSummary, RoundtableNode
 from .conv import AvgPool2d, Conv2d, Conv3d, Conv4d, Conv6da, MaxPool2d, WaveScan, ZConv6DA
 from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,

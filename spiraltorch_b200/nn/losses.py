@@ -19,6 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from ..tensor import Tensor, TensorError
+from .modules import assert_finite
 
 
 class Loss:
@@ -29,8 +30,7 @@ class Loss:
         if pred.shape() != target.shape():
             raise TensorError(f"loss: shape mismatch {pred.shape()} vs {target.shape()}")
         p, t = pred.torch(), target.torch()
-        if not (torch.isfinite(p).all() and torch.isfinite(t).all()):
-            raise TensorError("loss: non-finite input")
+        assert_finite([p, t], lambda i: "loss: non-finite input")
         return p, t
 
     def forward(self, pred: Tensor, target: Tensor) -> Tensor:

@@ -37,6 +37,28 @@ def _t(x) -> torch.Tensor:
     return x.torch() if isinstance(x, Tensor) else torch.as_tensor(x, dtype=torch.float32)
 
 
+_capture_flag: Optional[torch.Tensor] = None      # device flag that collects finite-checks while a CUDA graph is captured
+
+
+def assert_finite(tensors, describe) -> None:
+    """Raises ``TensorError(describe(i))`` for the first non-finite tensor ``i``.  All tensors are reduced to one
+    device flag first, so the check costs one host read however many tensors it covers; under CUDA-graph capture
+    (no host read possible) the flag is OR-ed into the capturing step's error word instead, which its owner polls."""
+    tensors = [t for t in tensors if t is not None]
+    if not tensors:
+        return
+    oks = [torch.isfinite(t).all() for t in tensors]
+    ok = oks[0] if len(oks) == 1 else torch.stack(oks).all()
+    if ok.is_cuda and torch.cuda.is_current_stream_capturing():
+        if _capture_flag is None:
+            raise TensorError("finite-check reached under CUDA-graph capture without a capture flag")
+        _capture_flag.logical_or_(~ok)
+        return
+    if not bool(ok):
+        bad = next(i for i, o in enumerate(oks) if not bool(o))
+        raise TensorError(describe(bad))
+
+
 class Parameter:
     """Named 2-D parameter with Euclidean, hypergrad and realgrad accumulators
     (crates/st-nn/src/module.rs:44-52)."""
@@ -153,11 +175,10 @@ class Module:
                 raise TensorError(f"backward: grad_output shape {tuple(g.shape)} != output shape {tuple(y.shape)}")
             grads = torch.autograd.grad(y, [xt] + [leaves[p.name] for p in plist], g, allow_unused=True)
         batch = max(1, xt.shape[0])
-        for p, gp in zip(plist, grads[1:]):
-            if gp is not None:
-                if not torch.isfinite(gp).all():
-                    raise TensorError(f"non-finite gradient for parameter {p.name}")
-                p.accumulate(gp / batch)
+        live = [(p, gp) for p, gp in zip(plist, grads[1:]) if gp is not None]
+        assert_finite([gp for _, gp in live], lambda i: f"non-finite gradient for parameter {live[i][0].name}")
+        for p, gp in live:
+            p.accumulate(gp / batch)
         gx = grads[0] if grads[0] is not None else torch.zeros_like(xt)
         return Tensor._wrap(gx.detach())
 

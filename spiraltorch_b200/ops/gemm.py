@@ -136,6 +136,13 @@ def cached_bf16(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def clear_bf16_cache() -> None:
+    """Drops every cached bf16 copy (CUDA-graph capture calls this so that the casts it needs are captured too)."""
+    global _bf16_cache_bytes
+    _bf16_cache.clear()
+    _bf16_cache_bytes = 0
+
+
 def _pad_to(t: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
     if t.shape[-2] == rows and t.shape[-1] == cols and t.stride(-1) == 1 and t.stride(-2) % 8 == 0 \
             and t.data_ptr() % 16 == 0:

@@ -387,7 +387,7 @@ def test_language_bridges_and_trace_recorder(tmp_path):
 def test_sequencer_on_gpu_matches_cpu():
     torch.manual_seed(2)
     x = torch.randn(64, 256) * 0.4
-    seq = _seq(256, 8, -1.0)
+    seq = C.ZSpaceCoherenceSequencer(256, 8, -1.0, OpenCartesianTopos(-1.0, 1e-5, 10.0, 256, 1 << 20))
     out_c, coh_c, d_c = seq.forward_with_diagnostics(st.Tensor._wrap(x))
     out_g, coh_g, d_g = seq.forward_with_diagnostics(st.Tensor._wrap(x.cuda()))
     assert out_g.torch().is_cuda

@@ -267,3 +267,42 @@ def test_wave_rnn_module_training_step_runs_on_the_scan_kernel():
     assert _rel(dx, ref_dx) < 5e-2
     for p in layer.parameters():
         assert _rel(p.gradient, ref_acc[p.name]) < 5e-2, p.name
+
+
+def _wave_model(seed):
+    torch.manual_seed(seed)
+    m = st.nn.Sequential()
+    m.add(st.nn.WaveRnn("wave", 32, 64, 16))
+    m.add(st.nn.Linear(64, 8, name="head"))
+    m.to("cuda")
+    return m
+
+
+def test_graphed_train_step_matches_eager_steps_and_reports_non_finite_inputs():
+    loss = st.nn.MeanSquaredError()
+    torch.manual_seed(11)
+    batches = [(torch.randn(32, 16 * 32, device="cuda"), torch.randn(32, 8, device="cuda")) for _ in range(4)]
+    eager, graphed = _wave_model(5), _wave_model(5)
+    step = st.nn.GraphedTrainStep(graphed, loss, st.Tensor._wrap(batches[0][0]), st.Tensor._wrap(batches[0][1]), learning_rate=1e-2)
+    for p, q in zip(eager.parameters(), graphed.parameters()):
+        assert torch.equal(p.value, q.value)                      # warm-up and capture left the parameters untouched
+    for x, y in batches:
+        xe, ye = st.Tensor._wrap(x), st.Tensor._wrap(y)
+        pred = eager.forward(xe)
+        want = float(loss.forward(pred, ye).torch())
+        eager.backward(xe, loss.backward(pred, ye))
+        eager.apply_step(1e-2)
+        got = float(step(xe, ye))
+        assert got == pytest.approx(want, rel=2e-3)
+    step.check()
+    assert step.replays == 4
+    for p, q in zip(eager.parameters(), graphed.parameters()):
+        assert _rel(q.value, p.value) < 2e-3, p.name
+    # an eager forward after graphed training must see the trained weights, not a stale low-precision copy
+    xe = st.Tensor._wrap(batches[0][0])
+    assert _rel(graphed.forward(xe).torch(), eager.forward(xe).torch()) < 2e-2
+    bad = batches[0][1].clone()
+    bad[0, 0] = float("nan")
+    step(xe, st.Tensor._wrap(bad))
+    with pytest.raises(st.TensorError):
+        step.check()
