@@ -329,6 +329,7 @@ def bench_layers(iters, profile):
     # from the device, so what is left is the kernels' own time
     wave_g = st.nn.GraphedTrainStep(wave, loss, x, y, learning_rate=1e-2)
     gnn_g = st.nn.GraphedTrainStep(model, loss, gx, gy, learning_rate=1e-2)
+    wave_g.check(); gnn_g.check()
     for name, fn, cpu_ms, wgpu_ms in (("wave_rnn_train_step", wave_step, 7.132, 125.897), ("gnn_train_step", gnn_step, 16.503, 362.814),
                                       ("wave_rnn_train_step_graphed", lambda: wave_g(x, y), 7.132, 125.897),
                                       ("gnn_train_step_graphed", lambda: gnn_g(gx, gy), 16.503, 362.814)):
