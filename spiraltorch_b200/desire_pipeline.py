@@ -13,6 +13,7 @@ phase, at least ``min_samples`` penalties, mean penalty at or above ``score_thre
 from __future__ import annotations
 
 import json
+import math
 import queue
 import threading
 import time
@@ -378,6 +379,217 @@ class DesireTrainerBridge(DesirePipelineSink):
             self._events = events
 
 
+# ---- roundtable bridge --------------------------------------------------------------------------------------------
+@dataclass
+class DesireRoundtableImpulse:
+    multipliers: tuple      # (above, here, beneath) band multipliers, each in [0.35, 1.65]
+    drift: float            # tanh(lambda) * drift_gain, in [-1, 1]
+    timestamp: float
+
+
+@dataclass
+class DesireRoundtableEvent:
+    timestamp: float
+    solution: DesireSolution
+    trigger: Optional[DesireRewriteTrigger]
+    multipliers: tuple
+    drift: float
+
+
+_RT_SUMS = ("entropy", "temperature", "alpha", "beta", "gamma", "lambda", "above", "here", "beneath", "drift")
+
+
+@dataclass
+class DesireRoundtableSummary:
+    steps: int = 0
+    triggers: int = 0
+    mean_entropy: float = 0.0
+    mean_temperature: float = 0.0
+    mean_alpha: float = 0.0
+    mean_beta: float = 0.0
+    mean_gamma: float = 0.0
+    mean_lambda: float = 0.0
+    mean_above: float = 0.0
+    mean_here: float = 0.0
+    mean_beneath: float = 0.0
+    mean_drift: float = 0.0
+    last_timestamp: float = 0.0
+
+    @classmethod
+    def from_events(cls, events: list) -> "DesireRoundtableSummary":
+        return _summary_from_pending(_absorb(None, events))
+
+
+def _absorb(pending: Optional[dict], events: list) -> dict:
+    p = dict(pending) if pending else {"steps": 0, "triggers": 0, "last_timestamp": 0.0, **{f"sum_{k}": 0.0 for k in _RT_SUMS}}
+    for e in events:
+        w = e.solution.weights
+        p["steps"] += 1
+        p["triggers"] += int(e.trigger is not None)
+        for k, v in zip(_RT_SUMS, (e.solution.entropy, e.solution.temperature, w.alpha, w.beta, w.gamma, w.lam, *e.multipliers, e.drift)):
+            p[f"sum_{k}"] += v
+        p["last_timestamp"] = max(p["last_timestamp"], e.timestamp)
+    return p
+
+
+def _summary_from_pending(p: dict) -> DesireRoundtableSummary:
+    n = max(p["steps"], 1)
+    return DesireRoundtableSummary(p["steps"], p["triggers"], *[p[f"sum_{k}"] / n for k in _RT_SUMS], p["last_timestamp"])
+
+
+class DesireRoundtableBridge(DesirePipelineSink):
+    """Projects each desire step onto the roundtable: the (alpha, gamma, beta) weights become barycentric band
+    multipliers ``1 + blend * (share - 1/3)`` for (above, here, beneath), the lambda weight becomes a drift
+    (crates/st-nn/src/language/pipeline.rs:1583-1890, 2057-2124).  The trainer reads the latest impulse per step and
+    drains the event queue (or its summary) when it reports; ``propose`` / ``observe`` make it a cooperative agent
+    whose blend and drift gain react to team reward and credit."""
+
+    def __init__(self, blend: float = 0.35, drift_gain: float = 0.35):
+        self._lock = threading.Lock()
+        self._blend = self._drift_gain = 0.35
+        self._latest: Optional[DesireRoundtableImpulse] = None
+        self._pending: Optional[dict] = None
+        self._events: list = []
+        self.set_blend(blend)
+        self.set_drift_gain(drift_gain)
+
+    def blend(self) -> float:
+        return self._blend
+
+    def drift_gain(self) -> float:
+        return self._drift_gain
+
+    def set_blend(self, v: float) -> None:
+        if math.isfinite(v):
+            self._blend = min(max(float(v), 0.0), 1.0)
+
+    def set_drift_gain(self, v: float) -> None:
+        if math.isfinite(v):
+            self._drift_gain = min(max(float(v), 0.0), 1.0)
+
+    def with_blend(self, v: float) -> "DesireRoundtableBridge":
+        self.set_blend(v)
+        return self
+
+    def with_drift_gain(self, v: float) -> "DesireRoundtableBridge":
+        self.set_drift_gain(v)
+        return self
+
+    @staticmethod
+    def project(weights: DesireWeights, blend: float, drift_gain: float, timestamp: float) -> DesireRoundtableImpulse:
+        above, here, beneath = max(weights.alpha, 0.0), max(weights.gamma, 0.0), max(weights.beta, 0.0)
+        total = max(above + here + beneath, 1e-6)
+        mult = tuple(min(max(1.0 + blend * (v / total - 1.0 / 3.0), 0.35), 1.65) for v in (above, here, beneath))
+        return DesireRoundtableImpulse(mult, min(max(math.tanh(weights.lam) * drift_gain, -1.0), 1.0), timestamp)
+
+    def on_step(self, step, timestamp):
+        with self._lock:
+            imp = self.project(step.solution.weights, self._blend, self._drift_gain, timestamp)
+            self._events.append(DesireRoundtableEvent(timestamp, step.solution, step.trigger, imp.multipliers, imp.drift))
+            self._latest = imp
+
+    def impulse(self) -> Optional[DesireRoundtableImpulse]:
+        return self._latest
+
+    def __len__(self):
+        with self._lock:
+            return len(self._events) + (self._pending["steps"] if self._pending else 0)
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+    def drain(self) -> list:
+        with self._lock:
+            out, self._events = self._events, []
+        return out
+
+    def drain_summary(self) -> Optional[DesireRoundtableSummary]:
+        with self._lock:
+            p = _absorb(self._pending, self._events)
+            self._pending, self._events = None, []
+        return None if p["steps"] == 0 else _summary_from_pending(p)
+
+    def checkpoint(self) -> dict:
+        """Blend, drift gain, latest impulse and the queue folded into running sums (events themselves are not kept)."""
+        with self._lock:
+            p = _absorb(self._pending, self._events)
+            latest = None if self._latest is None else {"multipliers": list(self._latest.multipliers), "drift": self._latest.drift,
+                                                        "timestamp": self._latest.timestamp}
+            return {"blend": self._blend, "drift_gain": self._drift_gain, "latest": latest,
+                    "pending_summary": p if p["steps"] else None}
+
+    def restore_checkpoint(self, doc: dict) -> None:
+        """Validates everything first; a rejected document leaves the bridge unchanged."""
+        def finite(name, v, lo=None, hi=None):
+            if not isinstance(v, (int, float)) or not math.isfinite(v) or (lo is not None and v < lo) or (hi is not None and v > hi):
+                raise ValueError(f"desire roundtable checkpoint: '{name}' is out of its domain ({v})")
+            return float(v)
+        blend, gain = finite("blend", doc.get("blend"), 0.0, 1.0), finite("drift_gain", doc.get("drift_gain"), 0.0, 1.2)
+        latest = None
+        if doc.get("latest") is not None:
+            lt = doc["latest"]
+            if len(lt.get("multipliers", ())) != 3:
+                raise ValueError("desire roundtable checkpoint: 'latest.multipliers' needs three values")
+            latest = DesireRoundtableImpulse(tuple(finite("latest.multipliers", m, 0.35, 1.65) for m in lt["multipliers"]),
+                                             finite("latest.drift", lt.get("drift"), -1.0, 1.0), finite("latest.timestamp", lt.get("timestamp"), 0.0))
+        pending = None
+        if doc.get("pending_summary") is not None:
+            ps = doc["pending_summary"]
+            pending = {"steps": int(ps["steps"]), "triggers": int(ps["triggers"]), "last_timestamp": finite("pending.last_timestamp", ps["last_timestamp"], 0.0),
+                       **{f"sum_{k}": finite(f"pending.sum_{k}", ps[f"sum_{k}"]) for k in _RT_SUMS}}
+            if pending["steps"] <= 0 or not 0 <= pending["triggers"] <= pending["steps"]:
+                raise ValueError("desire roundtable checkpoint: pending step / trigger counts are inconsistent")
+        with self._lock:
+            self._blend, self._drift_gain, self._latest, self._pending, self._events = blend, gain, latest, pending, []
+
+    # cooperative agent ---------------------------------------------------------------------------------------------
+    def propose(self) -> tuple:
+        """``(z_bias, weight)``: the latest drift, weighted by the mean multiplier in [0.05, 2]; neutral ``(0, 1)`` before any step."""
+        imp = self._latest
+        if imp is None:
+            return 0.0, 1.0
+        return imp.drift, min(max(sum(imp.multipliers) / 3.0, 0.05), 2.0)
+
+    def observe(self, team_reward: float, credit: float) -> None:
+        r, c = math.tanh(team_reward), math.tanh(credit)
+        with self._lock:
+            b = self._blend + (-r * 0.05 if r < 0 else -r * 0.03) + (-c * 0.04 if c < 0 else -c * 0.02)
+            self._blend = min(max(b, 0.05), 0.95)
+            g = self._drift_gain * ((1.0 - 0.08 * c) if c > 0 else (1.0 + 0.05 * -c))
+            self._drift_gain = min(max(g * (1.0 - 0.03 * abs(r)), 0.1), 1.2)
+
+
+class DesireTelemetryBundle:
+    """The bridges a pipeline should feed, handed around as one object."""
+
+    def __init__(self, trainer: Optional[DesireTrainerBridge] = None, roundtable: Optional[DesireRoundtableBridge] = None, psi=None):
+        self.trainer, self.roundtable, self.psi = trainer, roundtable, psi
+
+    def with_trainer_bridge(self, bridge) -> "DesireTelemetryBundle":
+        self.trainer = bridge
+        return self
+
+    def with_roundtable_bridge(self, bridge) -> "DesireTelemetryBundle":
+        self.roundtable = bridge
+        return self
+
+    def with_psi_bridge(self, bridge) -> "DesireTelemetryBundle":
+        self.psi = bridge
+        return self
+
+    def trainer_bridge(self):
+        return self.trainer
+
+    def roundtable_bridge(self):
+        return self.roundtable
+
+    def psi_bridge(self):
+        return self.psi
+
+    def sinks(self) -> list:
+        return [b for b in (self.trainer, self.roundtable, self.psi) if b is not None]
+
+
 # ---- pipeline --------------------------------------------------------------------------------------------------
 class DesirePipelineBuilder:
     def __init__(self, automation: DesireAutomation):
@@ -392,6 +604,12 @@ class DesirePipelineBuilder:
     def with_telemetry(self): return self.with_sink(DesireTelemetrySink())                                        # noqa: E704
     def with_trainer_bridge(self, bridge: DesireTrainerBridge): return self.with_sink(bridge)                    # noqa: E704
     def with_trigger_buffer(self, buffer: DesireTriggerBuffer): return self.with_sink(buffer)                    # noqa: E704
+    def with_roundtable_bridge(self, bridge: "DesireRoundtableBridge"): return self.with_sink(bridge)            # noqa: E704
+
+    def with_telemetry_bundle(self, bundle: "DesireTelemetryBundle") -> "DesirePipelineBuilder":
+        for sink in bundle.sinks():
+            self.with_sink(sink)
+        return self
 
     def build(self) -> "DesirePipeline":
         pipe = DesirePipeline(self.automation)
@@ -415,6 +633,7 @@ class DesirePipeline:
     def attach_channel(self, sender): self.attach_sink(DesireChannelSink(sender))         # noqa: E704
     def attach_telemetry(self): self.attach_sink(DesireTelemetrySink())                   # noqa: E704
     def attach_trainer_bridge(self, bridge): self.attach_sink(bridge)                     # noqa: E704
+    def attach_roundtable_bridge(self, bridge): self.attach_sink(bridge)                  # noqa: E704
 
     def sink_count(self) -> int:
         return len(self.sinks)

@@ -31,6 +31,6 @@ from .coherence import (CoherenceBackend, CoherenceChannelReport, CoherenceDiagn
                         ZSpaceCoherenceSequencer, ZSpaceTraceConfig, ZSpaceTraceRecorder, coherence_relation_tensor,
                         is_swap_invariant)
 from ..language import ConceptHint, MaxwellDesireBridge, NarrativeHint, NarrativeSummary
-from ..desire_pipeline import DesirePipeline, DesireTrainerBridge
+from ..desire_pipeline import DesirePipeline, DesireRoundtableBridge, DesireTelemetryBundle, DesireTrainerBridge
 
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)

@@ -96,3 +96,50 @@ def test_trainer_bridge_checkpoint():
     restored.restore_checkpoint(doc)
     a, b = bridge.drain_summary(), restored.drain_summary()
     assert a == b and a.total == 6
+
+
+def test_roundtable_bridge_projection_summary_checkpoint_and_cooperation():
+    import copy
+    import math
+    from spiraltorch_b200.desire_pipeline import DesireRoundtableBridge, DesireRoundtableSummary, DesireTelemetryBundle
+    imp = DesireRoundtableBridge.project(DesireWeights(alpha=0.6, beta=0.1, gamma=0.3, lam=0.5), 0.6, 0.4, 7.0)
+    assert imp.multipliers == pytest.approx((1 + 0.6 * (0.6 - 1 / 3), 1 + 0.6 * (0.3 - 1 / 3), 1 + 0.6 * (0.1 - 1 / 3)))
+    assert imp.drift == pytest.approx(math.tanh(0.5) * 0.4) and imp.timestamp == 7.0
+    flat = DesireRoundtableBridge.project(DesireWeights(alpha=-1.0, beta=0.0, gamma=0.0, lam=-50.0), 1.0, 1.0, 0.0)
+    assert flat.multipliers == pytest.approx((2 / 3, 2 / 3, 2 / 3)) and flat.drift == pytest.approx(-1.0)
+
+    rt, tr = DesireRoundtableBridge(blend=0.5, drift_gain=0.3), DesireTrainerBridge()
+    assert rt.propose() == (0.0, 1.0)
+    bundle = DesireTelemetryBundle().with_trainer_bridge(tr).with_roundtable_bridge(rt)
+    pipe = DesirePipeline.builder(_automation()).with_telemetry_bundle(bundle).build()
+    assert pipe.sink_count() == 2
+    for i in range(5):
+        pipe.step_at(LOGITS, 0, [0.5, 0.5], now=float(i), timestamp=10.0 + i)
+    assert len(rt) == 5 and len(tr) == 5 and rt.impulse().timestamp == 14.0
+    drift, weight = rt.propose()
+    assert -1.0 <= drift <= 1.0 and 0.05 <= weight <= 2.0
+    doc = copy.deepcopy(rt.checkpoint())
+    assert doc["pending_summary"]["steps"] == 5 and doc["latest"]["timestamp"] == 14.0
+    events = rt.drain()
+    want = DesireRoundtableSummary.from_events(events)
+    assert want.steps == 5 and want.last_timestamp == 14.0 and want.mean_above == pytest.approx(sum(e.multipliers[0] for e in events) / 5)
+    other = DesireRoundtableBridge()
+    other.restore_checkpoint(doc)
+    assert other.blend() == 0.5 and other.drift_gain() == 0.3 and len(other) == 5
+    got = other.drain_summary()
+    assert (got.steps, got.triggers) == (want.steps, want.triggers)
+    assert got.mean_entropy == pytest.approx(want.mean_entropy) and got.mean_drift == pytest.approx(want.mean_drift)
+    assert other.drain_summary() is None and rt.drain_summary() is None
+    before = other.checkpoint()
+    for bad in ({**doc, "blend": float("nan")}, {**doc, "latest": {"multipliers": [1.0, 9.0, 1.0], "drift": 0.0, "timestamp": 1.0}},
+                {**doc, "pending_summary": {**doc["pending_summary"], "triggers": 99}}):
+        with pytest.raises(ValueError):
+            other.restore_checkpoint(bad)
+    assert other.checkpoint() == before                                   # a rejected document changes nothing
+    b0, g0 = other.blend(), other.drift_gain()
+    other.observe(-0.2, -0.6)
+    assert other.blend() > b0 and other.drift_gain() > g0
+    other.observe(2.0, 2.0)
+    assert other.blend() < 0.5 + 0.1 and 0.1 <= other.drift_gain() <= 1.2
+    other.set_blend(float("nan"))
+    assert math.isfinite(other.blend())
