@@ -10,7 +10,7 @@ from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, I
                       LoraLinear, Lstm, Module, NonLiner, Parameter, Pool2d, Relu, Scaler, Sequential, SpiralRnn,
                       WaveGate, WaveRnn, ZConv, ZPooling, ZSpaceBatchNorm1d, ZSpaceCoherenceScan,
                       ZSpaceCoherenceWaveBlock, ZSpaceLayerNorm, ZSpaceMixer, ZSpaceSoftmax, conv_output_shape,
-                      pool_output_shape)
+                      pool_output_shape, reorder_feature_tensor, reorder_feature_tensor_3d)
 from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
 from . import amp, coherence, conv, fields, gnn, graph, lightning, roundtable, zrba, zspace
 from .graph import GraphedTrainStep
@@ -33,4 +33,5 @@ from .coherence import (CoherenceBackend, CoherenceChannelReport, CoherenceDiagn
 from ..language import ConceptHint, MaxwellDesireBridge, NarrativeHint, NarrativeSummary
 from ..desire_pipeline import DesirePipeline, DesireRoundtableBridge, DesireTelemetryBundle, DesireTrainerBridge
 
+NnModuleTrainer = ModuleTrainer          # the binding registers the trainer under both names
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)

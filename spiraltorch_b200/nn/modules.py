@@ -667,18 +667,49 @@ class ZSpaceCoherenceWaveBlock(ZSpaceCoherenceScan):
         return (out / (1 + len(self.dilations))).reshape(x.shape[0], -1)
 
 
+_DIRECTIONS = {"to_canonical": True, "to": True, "from_canonical": False, "from": False}
+
+
+def _reorder_rows(x: torch.Tensor, channels: int, spatial: tuple, layout: str, direction: str) -> torch.Tensor:
+    """Rows of flattened feature maps between channel-last and the canonical channel-first order: one strided copy."""
+    layout = layout.upper()
+    first, last = ("NCHW", "NHWC") if len(spatial) == 2 else ("NCDHW", "NDHWC")
+    if layout not in (first, last):
+        raise ValueError(f"unsupported layout '{layout}', expected '{first}' or '{last}'")
+    if direction.lower() not in _DIRECTIONS:
+        raise ValueError(f"unknown direction '{direction}', expected 'to_canonical' or 'from_canonical'")
+    size = channels * math.prod(spatial)
+    if x.dim() != 2 or x.shape[1] != size:
+        raise TensorError(f"feature tensor has {tuple(x.shape)} values per row, expected (*, {size})")
+    if layout == first:
+        return x * 1.0
+    b, nd = x.shape[0], len(spatial)
+    if _DIRECTIONS[direction.lower()]:                 # channel-last rows -> channel-first rows
+        return x.reshape(b, *spatial, channels).permute(0, nd + 1, *range(1, nd + 1)).reshape(b, -1)
+    return x.reshape(b, channels, *spatial).permute(0, *range(2, nd + 2), 1).reshape(b, -1)
+
+
+def reorder_feature_tensor(tensor: Tensor, channels: int, height: int, width: int, layout: str = "NHWC",
+                           direction: str = "to_canonical") -> Tensor:
+    """``(batch, C*H*W)`` rows between ``NHWC`` and the canonical ``NCHW`` order (``NCHW`` is the identity);
+    ``direction`` is ``to_canonical`` / ``to`` or ``from_canonical`` / ``from`` (bindings/st-py/src/nn.rs:900-931, 1250-1264)."""
+    return Tensor._wrap(_reorder_rows(_t(tensor), channels, (height, width), layout, direction).contiguous())
+
+
+def reorder_feature_tensor_3d(tensor: Tensor, channels: int, depth: int, height: int, width: int, layout: str = "NDHWC",
+                              direction: str = "to_canonical") -> Tensor:
+    """The same for volumes: ``NDHWC`` rows against the canonical ``NCDHW`` order (bindings/st-py/src/nn.rs:977-1010)."""
+    return Tensor._wrap(_reorder_rows(_t(tensor), channels, (depth, height, width), layout, direction).contiguous())
+
+
 class FeatureReorder2d(Module):
     def __init__(self, channels: int, height: int, width: int, *, layout: str = "NCHW", direction: str = "to_canonical"):
         super().__init__()
         self.c, self.h, self.w, self.layout, self.direction = channels, height, width, layout.upper(), direction
+        _reorder_rows(torch.zeros(1, channels * height * width), channels, (height, width), layout, direction)   # validates the labels
 
     def _fwd(self, x, p):
-        b = x.shape[0]
-        if self.layout == "NCHW":
-            return x * 1.0
-        if self.direction == "to_canonical":      # NHWC → NCHW
-            return x.reshape(b, self.h, self.w, self.c).permute(0, 3, 1, 2).reshape(b, -1)
-        return x.reshape(b, self.c, self.h, self.w).permute(0, 2, 3, 1).reshape(b, -1)
+        return _reorder_rows(x, self.c, (self.h, self.w), self.layout, self.direction)
 
 
 def conv_output_shape(input_hw, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1)) -> tuple[int, int]:

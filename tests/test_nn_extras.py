@@ -437,3 +437,24 @@ def test_mellin_basis_projection():
     assert float(vae.decode_with_mellin(mu, b).norm()) == pytest.approx(1.0, abs=1e-5)
     tv = zspace.ZSpaceTextVae(4, 2)
     assert float(tv.encode_text_with_mellin("abcd", zspace.MellinBasis.constant(8, 1.5)).norm()) == pytest.approx(1.0, abs=1e-5)
+
+
+def test_reorder_feature_tensor_layouts():
+    x = torch.arange(2 * 2 * 3 * 4, dtype=torch.float32).reshape(2, -1)          # C=4, H=2, W=3 stored NHWC
+    t = st.nn.reorder_feature_tensor(st.Tensor._wrap(x), 4, 2, 3, "nhwc", "to")
+    assert torch.equal(st.nn.reorder_feature_tensor(t, 4, 2, 3, "NHWC", "from_canonical").torch(), x)
+    row, can = x[0], t.torch()[0]
+    assert all(can[c * 6 + h * 3 + w] == row[(h * 3 + w) * 4 + c] for c in range(4) for h in range(2) for w in range(3))
+    assert torch.equal(st.nn.reorder_feature_tensor(st.Tensor._wrap(x), 4, 2, 3, "NCHW").torch(), x)
+    v = torch.arange(2 * 3 * 2 * 2 * 2, dtype=torch.float32).reshape(2, -1)       # C=3, D=H=W=2 stored NDHWC
+    t3 = st.nn.reorder_feature_tensor_3d(st.Tensor._wrap(v), 3, 2, 2, 2)
+    assert torch.equal(st.nn.reorder_feature_tensor_3d(t3, 3, 2, 2, 2, direction="from").torch(), v)
+    assert t3.torch()[0][1 * 8 + 1 * 4 + 0 * 2 + 1] == v[0][((1 * 2 + 0) * 2 + 1) * 3 + 1]
+    with pytest.raises(ValueError):
+        st.nn.reorder_feature_tensor(t, 4, 2, 3, "CHWN")
+    with pytest.raises(ValueError):
+        st.nn.reorder_feature_tensor(t, 4, 2, 3, "NHWC", "sideways")
+    with pytest.raises(st.TensorError):
+        st.nn.reorder_feature_tensor(t, 5, 2, 3)
+    with pytest.raises(ValueError):
+        st.nn.FeatureReorder2d(4, 2, 3, layout="HWCN")
