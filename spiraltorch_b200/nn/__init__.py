@@ -18,7 +18,8 @@ from .roundtable import DistConfig, MetaConductor, MetaSummary, RoundtableNode
 from .conv import AvgPool2d, Conv2d, Conv3d, Conv4d, Conv6da, MaxPool2d, WaveScan, ZConv6DA
 from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,
                      DynamicSchrodingerField, ToposResonator, ZRelativity, ZSpaceProjector)
-from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregation, ZSpaceGraphBatchRegressor,
+from .gnn import (GraphBatch, GraphContext, GraphReadout, NeighborhoodAggregation, RoundtableBandInfluence, RoundtableBandSignal,
+                  RoundtableGnnBridge, ZSpaceGraphBatchRegressor,
                   ZSpaceGraphConvolution, ZSpaceGraphNetwork, ZSpaceGraphRegressor)
 from .lightning import (InfoNCELoss, LightningConfig, LightningReport, LightningStage, SelfSupStage, SpiralLightning)
 from .zrba import (BetaGate, BetaGateConfig, BetaGateSample, CovHead, CovHeadTelemetry, ReliabilityBin,

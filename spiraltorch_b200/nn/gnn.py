@@ -9,6 +9,7 @@ regressors (readout.rs:20-700).  Propagation and the kernel product run on the G
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -105,6 +106,218 @@ class NeighborhoodAggregation:
         return w
 
 
+# ---- roundtable influence on message passing -------------------------------------------------------------------------
+GNN_ROUNDTABLE_MAX_HISTORY_SIGNALS = 4096
+_F32_MAX = 3.4028234663852886e38
+
+
+class RoundtableBandSignal:
+    """One roundtable observation for graph modules: band energies (+ drift and an optional spectral sample of the
+    gradient) and the schedule's band sizes (crates/st-nn/src/gnn/mod.rs:44-230)."""
+
+    def __init__(self, above: float, here: float, beneath: float, band_sizes, drift: float = 0.0, spectral=None,
+                 issued_at: Optional[float] = None):
+        import time
+        from .zrba import SpectralFeatureSample
+        self.above, self.here, self.beneath, self.drift = float(above), float(here), float(beneath), float(drift)
+        self.band_sizes = tuple(int(v) for v in band_sizes)
+        self.spectral = spectral or SpectralFeatureSample()
+        self.issued_at = time.time() if issued_at is None else float(issued_at)
+        self.validate()
+
+    @classmethod
+    def from_schedule(cls, schedule, energy, drift: float = 0.0, spectral=None) -> "RoundtableBandSignal":
+        """``schedule``: a ``RoundtableSchedule``; ``energy``: its ``band_energy`` dict or an object with the three fields."""
+        get = (lambda k: energy[k]) if isinstance(energy, dict) else (lambda k: getattr(energy, k))
+        n = schedule.rows * schedule.cols
+        sizes = (schedule.top_k, n - schedule.top_k - schedule.bottom_k, schedule.bottom_k)
+        return cls(get("above"), get("here"), get("beneath"), sizes, drift, spectral)
+
+    def validate(self) -> None:
+        sp = self.spectral
+        for name, v in (("band_energy.above", self.above), ("band_energy.here", self.here), ("band_energy.beneath", self.beneath),
+                        ("spectral.energy", sp.energy)):
+            if not math.isfinite(v):
+                raise TensorError(f"GNN roundtable field '{name}' must be finite")
+            if v < 0:
+                raise TensorError(f"GNN roundtable field '{name}' must be non-negative")
+            if v > _F32_MAX:
+                raise TensorError(f"GNN roundtable field '{name}' must be in [-f32::MAX, f32::MAX]")
+        if not math.isfinite(self.drift) or abs(self.drift) > _F32_MAX:
+            raise TensorError("GNN roundtable field 'band_energy.drift' must be finite")
+        for name, v, lo, hi in (("spectral.sheet_confidence", sp.sheet_confidence, 0.0, 1.0), ("spectral.curvature", sp.curvature, 0.0, 4.0),
+                                ("spectral.spin", sp.spin, -1.0, 1.0)):
+            if not math.isfinite(v) or not lo <= v <= hi:
+                raise TensorError(f"GNN roundtable field '{name}' must be in [{lo}, {hi}]")
+        if len(self.band_sizes) != 3 or any(v <= 0 for v in self.band_sizes):
+            raise TensorError("GNN roundtable field 'band_sizes' must hold three positive sizes")
+        if not math.isfinite(self.issued_at) or self.issued_at < 0:
+            raise TensorError("GNN roundtable signal timestamp must be a finite, non-negative epoch time")
+
+    def depth(self) -> int:
+        return sum(self.band_sizes)
+
+    def as_dict(self) -> dict:
+        sp = self.spectral
+        return {"band_energy": {"above": self.above, "here": self.here, "beneath": self.beneath, "drift": self.drift},
+                "band_sizes": {"above": self.band_sizes[0], "here": self.band_sizes[1], "beneath": self.band_sizes[2]},
+                "spectral": {"sheet_index": sp.sheet_index, "sheet_confidence": sp.sheet_confidence, "curvature": sp.curvature,
+                             "spin": sp.spin, "energy": sp.energy}, "issued_at": self.issued_at}
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "RoundtableBandSignal":
+        from .zrba import SpectralFeatureSample
+        e, z = d["band_energy"], d["band_sizes"]
+        return cls(e["above"], e["here"], e["beneath"], (z["above"], z["here"], z["beneath"]), e.get("drift", 0.0),
+                   SpectralFeatureSample(**d.get("spectral", {})), d.get("issued_at"))
+
+
+def _cl(v, lo, hi):
+    return min(max(v, lo), hi)
+
+
+class RoundtableBandInfluence:
+    """Band multipliers and a drift bias derived from a signal, and from them one scale per message-passing hop
+    (crates/st-core/src/inference/gnn_roundtable.rs:70-255): hop 0 follows the Here multiplier, hop 1 the Above
+    multiplier times the drift bias, deeper hops the Beneath multiplier over the drift bias with a 5 %-per-hop decay.
+
+    The occupancy of each band mixes its energy share with its share of the schedule (more weight on energy when the
+    spectral sample is confident or the energy is lopsided); the direction combines the occupancy asymmetry with the
+    spectral spin; curvature pulls weight to the Here band; lopsided energy lifts both edge bands."""
+
+    def __init__(self, signal: RoundtableBandSignal):
+        signal.validate()
+        self.signal = signal
+        sp = signal.spectral
+        total = max(signal.above + signal.here + signal.beneath, 1.0e-6)
+        bary = [_cl(v / total, 0.0, 1.0) for v in (signal.above, signal.here, signal.beneath)]
+        share = [v / signal.depth() for v in signal.band_sizes]
+        focus = sp.sheet_confidence
+        curv = _cl(sp.curvature / 4.0, 0.0, 1.0)
+        stability = _cl(abs(sp.spin) * (1.0 - curv), 0.0, 1.0)
+        e_rel = _cl(0.5 + 0.35 * focus + 0.25 * _cl(abs(bary[0] - bary[2]), 0.0, 1.0), 0.55, 0.9)
+        occ = [e_rel * b + (1.0 - e_rel) * s_ for b, s_ in zip(bary, share)]
+        direction = _cl(0.6 * _cl(occ[0] - occ[2], -1.0, 1.0) + 0.4 * focus * sp.spin, -1.0, 1.0)
+        pull = _cl(focus * curv, 0.0, 1.0)
+        edge_bias = max(max(bary[0], bary[2]) - bary[1], 0.0)
+        edge = _cl(0.5 * edge_bias + 0.5 * abs(direction) * focus, 0.0, 1.0)
+        edge_lift, center = _cl(1.0 + 0.18 * edge, 1.0, 1.35), _cl(1.0 - 0.24 * edge, 0.72, 1.0)
+        lift = _cl(0.92 + 0.16 * stability + 0.10 * edge_bias, 0.85, 1.2)
+        neutrality = _cl((occ[1] + stability + pull) / 3.0, 0.0, 1.0)
+        relax = _cl(1.0 - pull, 0.65, 1.0)
+        m = [(0.72 + 0.62 * occ[0]) * (1.0 + 0.26 * max(direction, 0.0) + 0.12 * edge_bias) * relax * edge_lift,
+             (0.78 + 0.52 * occ[1]) * (1.0 + 0.18 * pull + 0.12 * neutrality) * (1.0 + 0.07 * (1.0 - focus)) * center,
+             (0.72 + 0.62 * occ[2]) * (1.0 + 0.26 * max(-direction, 0.0) + 0.12 * edge_bias) * relax * edge_lift]
+        m[0 if direction > 0 else 2 if direction < 0 else 1] *= lift
+        self._multipliers = tuple(_cl(v, 0.35, 1.75) for v in m)
+        dbias = _cl(0.55 * math.tanh(signal.drift) + 0.45 * direction, -1.0, 1.0)
+        self._drift_bias = _cl((1.0 + 0.22 * dbias) * (1.0 + 0.08 * edge) * (1.0 - 0.12 * pull) * (1.0 - 0.06 * neutrality * stability),
+                               0.55, 1.45)
+
+    from_signal = classmethod(lambda cls, signal: cls(signal))
+
+    def multipliers(self) -> tuple:
+        return self._multipliers
+
+    def drift_bias(self) -> float:
+        return self._drift_bias
+
+    def scale_for_step(self, step: int) -> float:
+        a, h, b = self._multipliers
+        if step == 0:
+            s = h
+        elif step == 1:
+            s = a * self._drift_bias
+        else:
+            s = b / max(self._drift_bias, 0.5)
+            if step > 2:
+                s *= max(1.0 - min(step - 2, 8) * 0.05, 0.6)
+        return _cl(s, 0.25, 2.0)
+
+    def band_pass_scale_for_step(self, band: str, step: int, intensity: float) -> float:
+        """Extra scale while the trainer back-propagates one band (``above`` / ``here`` / ``beneath``) at a time: the hop
+        that matches the band (1 / 0 / >= 2) is lifted, the others damped, in proportion to ``intensity`` in [0, 1]."""
+        if not (math.isfinite(intensity) and 0.0 <= intensity <= 1.0):
+            raise TensorError("GNN roundtable field 'band_pass.intensity' must be in [0, 1]")
+        band = band.lower()
+        if band not in ("above", "here", "beneath"):
+            raise TensorError(f"unknown roundtable band '{band}'")
+        avg = max(sum(self._multipliers) / 3.0, 0.35)
+        focus = intensity * _cl(self._multipliers[("above", "here", "beneath").index(band)] / avg, 0.8, 1.35)
+        k = min(step, 2)
+        if band == "above":
+            s = 1.0 + (-0.10, 0.24, -0.14)[k] * focus
+        elif band == "here":
+            s = 1.0 + (0.20, -0.07, -0.10)[k] * focus
+        elif k < 2:
+            s = 1.0 + (-0.12, -0.08)[k] * focus
+        else:
+            s = 1.0 + 0.24 * focus * _cl(1.0 - min(max(step - 2, 0), 3) * 0.06, 0.82, 1.0)
+        return _cl(s, 0.7, 1.35)
+
+
+class RoundtableGnnBridge:
+    """Shares roundtable band signals with graph modules: the trainer publishes one per step, graph networks read
+    the latest; a bounded history keeps the last ``history_limit`` (crates/st-nn/src/roundtable.rs:165-290)."""
+
+    def __init__(self, history_limit: int = 64):
+        import threading
+        self._lock = threading.Lock()
+        self._latest: Optional[RoundtableBandSignal] = None
+        self._history: list = []
+        self._limit = 64
+        self.set_history_limit(history_limit)
+
+    def set_history_limit(self, limit: int) -> None:
+        if not 1 <= limit <= GNN_ROUNDTABLE_MAX_HISTORY_SIGNALS:
+            raise TensorError("invalid value: roundtable GNN history limit")
+        with self._lock:
+            self._limit = int(limit)
+            del self._history[:max(len(self._history) - self._limit, 0)]
+
+    def history_limit(self) -> int:
+        return self._limit
+
+    def publish(self, signal: RoundtableBandSignal) -> RoundtableBandSignal:
+        signal.validate()
+        with self._lock:
+            self._latest = signal
+            self._history.append(signal)
+            del self._history[:max(len(self._history) - self._limit, 0)]
+        return signal
+
+    def record(self, schedule, energy, drift: float = 0.0, spectral=None) -> RoundtableBandSignal:
+        return self.publish(RoundtableBandSignal.from_schedule(schedule, energy, drift, spectral))
+
+    def latest(self) -> Optional[RoundtableBandSignal]:
+        return self._latest
+
+    def drain(self) -> list:
+        with self._lock:
+            out, self._history = self._history, []
+        return out
+
+    def __len__(self) -> int:
+        return len(self._history)
+
+    def is_empty(self) -> bool:
+        return not self._history
+
+    def snapshot_state(self) -> dict:
+        with self._lock:
+            return {"latest": None if self._latest is None else self._latest.as_dict(), "history": [s.as_dict() for s in self._history],
+                    "history_limit": self._limit}
+
+    def restore_state(self, state: dict) -> None:
+        latest = None if state.get("latest") is None else RoundtableBandSignal.from_dict(state["latest"])
+        history = [RoundtableBandSignal.from_dict(d) for d in state.get("history", ())]
+        limit = int(state.get("history_limit", 64))
+        if not 1 <= limit <= GNN_ROUNDTABLE_MAX_HISTORY_SIGNALS or len(history) > limit:
+            raise TensorError("invalid value: roundtable GNN bridge state")
+        with self._lock:
+            self._latest, self._history, self._limit = latest, history, limit
+
+
 class ZSpaceGraphConvolution(Module):
     def __init__(self, name: str, context: GraphContext, input_dim: int, output_dim: int, curvature: float = -1.0,
                  learning_rate: float = 1e-2):
@@ -119,6 +332,15 @@ class ZSpaceGraphConvolution(Module):
         self.attach_hypergrad(curvature, learning_rate)
         self.aggregation = NeighborhoodAggregation()
         self.last_flows: Optional[list] = None
+        self.roundtable: Optional[RoundtableBandInfluence] = None
+        self.active_band_pass: Optional[tuple] = None       # (band, intensity) while one band is back-propagated
+        self.last_step_scales: list = []
+
+    def set_roundtable_influence(self, influence: Optional["RoundtableBandInfluence"]) -> None:
+        self.roundtable = influence
+
+    def set_active_band_pass(self, band: Optional[str], intensity: float = 1.0) -> None:
+        self.active_band_pass = None if band is None else (band, float(intensity))
 
     def set_aggregation(self, aggregation: NeighborhoodAggregation) -> None:
         aggregation.validate()
@@ -130,11 +352,19 @@ class ZSpaceGraphConvolution(Module):
 
     def _support(self, x: torch.Tensor) -> torch.Tensor:
         cur, support = x, torch.zeros_like(x)
+        scales = []
         for h, w in enumerate(self.aggregation.weights()):
             if h > 0:
                 cur = self.context.propagate_t(cur)
-            if abs(w) > 1.1920929e-07:
-                support = support + w * cur
+            scale = 1.0
+            if self.roundtable is not None:
+                scale = self.roundtable.scale_for_step(h)
+                if self.active_band_pass is not None:
+                    scale *= self.roundtable.band_pass_scale_for_step(self.active_band_pass[0], h, self.active_band_pass[1])
+            scales.append(scale)
+            if abs(w * scale) > 1.1920929e-07:
+                support = support + (w * scale) * cur
+        self.last_step_scales = scales
         return support
 
     def _fwd(self, x, params):
@@ -162,6 +392,28 @@ class ZSpaceGraphNetwork(Module):
             if i + 1 < len(self.layers):
                 x = torch.relu(x)
         return x
+
+    def apply_roundtable_band(self, signal: RoundtableBandSignal) -> RoundtableBandInfluence:
+        influence = RoundtableBandInfluence(signal)
+        for layer in self.layers:
+            layer.set_roundtable_influence(influence)
+        return influence
+
+    def clear_roundtable_band(self) -> None:
+        for layer in self.layers:
+            layer.set_roundtable_influence(None)
+
+    def attach_roundtable_bridge(self, bridge: RoundtableGnnBridge) -> None:
+        """Every ``refresh_roundtable()`` (the trainer calls it before a step) adopts the bridge's latest signal."""
+        self._roundtable_bridge = bridge
+
+    def refresh_roundtable(self) -> bool:
+        bridge = getattr(self, "_roundtable_bridge", None)
+        signal = None if bridge is None else bridge.latest()
+        if signal is None:
+            return False
+        self.apply_roundtable_band(signal)
+        return True
 
 
 class GraphReadout:
