@@ -49,17 +49,23 @@ def fracdiff_gl(x: torch.Tensor, alpha: float, h: float = 1.0, m: int | None = N
 
 
 def fracdiff_spectral(x: torch.Tensor, alpha: float, h: float = 1.0) -> torch.Tensor:
-    """Spectral fractional derivative: multiply the spectrum by ``(i·omega)^alpha``."""
-    n = x.shape[-1]
-    omega = 2 * math.pi * torch.fft.fftfreq(n, d=h, device=x.device)
-    mult = torch.pow(torch.complex(torch.zeros_like(omega), omega), alpha)
-    mult[0] = 0 if alpha > 0 else mult[0]
-    return torch.fft.ifft(torch.fft.fft(x.to(torch.complex64)) * mult).real
+    """Spectral fractional derivative: FFT, multiply the spectrum by ``(i·omega)^alpha``, inverse FFT.  On CUDA all
+    three steps are this library's kernels (shared-memory FFT and the spectral multiplier)."""
+    from .ops import spectral
+    spec = spectral.specmul_frac_derivative(spectral.fft(x), alpha, h)
+    return spectral.fft(spec, inverse=True).real
 
 
 def fft(x: torch.Tensor, inverse: bool = False) -> torch.Tensor:
-    z = x if torch.is_complex(x) else x.to(torch.complex64)
-    return torch.fft.ifft(z) if inverse else torch.fft.fft(z)
+    from .ops import spectral
+    return spectral.fft(x, inverse=inverse)
+
+
+def specmul_frac_laplace(spectrum: torch.Tensor, power: float) -> torch.Tensor:
+    """Fractional-Laplacian frequency envelope ``min(col, cols - 1 - col)^power`` on an FFT's coefficients
+    (crates/st-core/src/backend/wgpu_frac.rs:491-500)."""
+    from .ops import spectral
+    return spectral.specmul_frac_laplace(spectrum, power)
 
 
 def mellin_log_grid(f: torch.Tensor, t_min: float, t_max: float, s: complex) -> complex:

@@ -296,14 +296,104 @@ def canvas_paint(x: torch.Tensor, palette: str = "spiral", lo: Optional[float] =
     return out
 
 
-def canvas_fft(field: torch.Tensor, axis: str = "2d") -> torch.Tensor:
-    """Row / column / 2-D FFT of a (complex or real) vector field (library FFT: not a named hot path)."""
-    f = field if torch.is_complex(field) else field.to(torch.complex64)
-    if axis == "row":
-        return torch.fft.fft(f, dim=-1)
-    if axis == "col":
-        return torch.fft.fft(f, dim=-2)
-    return torch.fft.fft2(f)
+def canvas_fft(field: torch.Tensor, axis: str = "2d", inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+    """Row / column / 2-D FFT of a (complex or real) field on the shared-memory FFT kernel; ``window`` names a taper
+    (``hann`` / ``hamming`` / ``blackman``) applied along each transformed axis."""
+    from .ops import spectral
+    if axis not in ("row", "col", "2d"):
+        raise ValueError("axis is 'row', 'col' or '2d'")
+    out = field
+    if axis in ("row", "2d"):
+        w = None if window is None else spectral.window_coefficients(window, field.shape[-1], field.device)
+        out = spectral.fft(out, dim=-1, inverse=inverse, window=w)
+    if axis in ("col", "2d"):
+        w = None if window is None else spectral.window_coefficients(window, field.shape[-2], field.device)
+        out = spectral.fft(out, dim=-2, inverse=inverse, window=w)
+    return out
+
+
+class ColorVectorField:
+    """Canvas vector field ``[H, W, 4]``: normalised energy plus three chroma channels per pixel, with the spectral
+    views of the canvas projector (crates/st-tensor/src/pure/wasm_canvas.rs:267-1100): per-channel row / column FFTs
+    in the interleaved ``[H, W, 8]`` layout and their magnitude, power, dB and phase maps."""
+
+    FFT_INTERLEAVED_STRIDE = 8
+    POWER_DB_EPSILON = 1e-12
+    POWER_DB_FLOOR = -160.0
+
+    def __init__(self, vectors: torch.Tensor):
+        if vectors.dim() != 3 or vectors.shape[-1] != 4:
+            raise ValueError(f"vector field must be [H, W, 4], got {tuple(vectors.shape)}")
+        if vectors.shape[0] == 0 or vectors.shape[1] == 0:
+            raise ValueError("empty input: canvas_fft")
+        self.vectors = vectors.float()
+
+    height = property(lambda self: self.vectors.shape[0])
+    width = property(lambda self: self.vectors.shape[1])
+
+    @classmethod
+    def from_energy(cls, energy: torch.Tensor, palette: str = "spiral") -> "ColorVectorField":
+        """Energy normalised to [0, 1] with the palette's colour (scaled to [0, 1]) as chroma."""
+        e = energy.float()
+        lo, hi = float(e.min()), float(e.max())
+        norm = (e - lo) / max(hi - lo, 1e-12)
+        rgb = canvas_paint(e, palette)[..., :3].float() / 255.0
+        return cls(torch.cat([norm[..., None], rgb.to(norm.device)], dim=-1))
+
+    def energy_tensor(self) -> torch.Tensor:
+        return self.vectors[..., 0]
+
+    def as_tensor(self) -> torch.Tensor:
+        return self.vectors.reshape(self.height, self.width * 4)
+
+    def _spectrum(self, axis: str, inverse: bool, window: Optional[str]) -> torch.Tensor:
+        from .ops import spectral
+        return spectral.fft_field_interleaved(self.vectors, axis, inverse, window)
+
+    def fft_rows_tensor(self, inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._spectrum("row", inverse, window).reshape(self.height, self.width * 8)
+
+    def fft_cols_tensor(self, inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._spectrum("col", inverse, window).reshape(self.height, self.width * 8)
+
+    def fft_2d_tensor(self, inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        """Rows then columns, per channel; ``[H, W * 8]`` interleaved."""
+        from .ops import spectral
+        rows = torch.view_as_complex(self._spectrum("row", inverse, window).reshape(self.height, self.width, 4, 2).contiguous())
+        w = None if window is None else spectral.window_coefficients(window, self.height, rows.device)
+        both = spectral.fft(rows, dim=0, inverse=inverse, window=w)
+        return torch.view_as_real(both).reshape(self.height, self.width * 8)
+
+    @staticmethod
+    def _views(spectrum: torch.Tensor, height: int, width: int):
+        z = spectrum.reshape(height, width, 4, 2)
+        return z[..., 0], z[..., 1]
+
+    def _derived(self, which: str, axis: str, inverse: bool, window: Optional[str]) -> torch.Tensor:
+        spec = {"row": self.fft_rows_tensor, "col": self.fft_cols_tensor, "2d": self.fft_2d_tensor}[axis](inverse, window)
+        re, im = self._views(spec, self.height, self.width)
+        power = re * re + im * im
+        if which == "magnitude":
+            out = power.sqrt()
+        elif which == "power":
+            out = power
+        elif which == "power_db":
+            out = (10.0 * torch.log10(power.clamp(min=self.POWER_DB_EPSILON))).clamp(min=self.POWER_DB_FLOOR)
+        else:
+            out = torch.atan2(im, re)
+        return out.reshape(self.height, self.width * 4)
+
+    def fft_magnitude_tensor(self, axis: str = "row", inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._derived("magnitude", axis, inverse, window)
+
+    def fft_power_tensor(self, axis: str = "row", inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._derived("power", axis, inverse, window)
+
+    def fft_power_db_tensor(self, axis: str = "row", inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._derived("power_db", axis, inverse, window)
+
+    def fft_phase_tensor(self, axis: str = "row", inverse: bool = False, window: Optional[str] = None) -> torch.Tensor:
+        return self._derived("phase", axis, inverse, window)
 
 
 def temporal_volume_render(volume: torch.Tensor, density_scale: float = 1.0) -> torch.Tensor:
@@ -315,6 +405,36 @@ def temporal_volume_render(volume: torch.Tensor, density_scale: float = 1.0) -> 
     sigma = rad.mean(-1) * density_scale
     deltas = torch.ones_like(sigma)
     return nerf_composite(sigma, rad, deltas).reshape(H, W, 4)
+
+
+@dataclass
+class TemporalRenderOutput:
+    frames: int
+    depth: int
+    height: int
+    width: int
+    times: list                 # seconds of each frame
+    data: torch.Tensor          # [frames, depth, height, width]
+
+    def frame(self, index: int) -> Optional[torch.Tensor]:
+        return self.data[index] if 0 <= index < self.frames else None
+
+
+class TemporalRenderer:
+    """Plays a Z-space volume forward in time: every voxel is its base value plus its temporal harmonics
+    ``sum_c a_c sin(2 pi (c + 1) t)``, damped by ``exp(-decay t)``, sampled at ``frames`` instants ``sample_rate_hz``
+    apart (crates/st-backend-wgpu/src/render/temporal.rs:196-360).  One kernel launch renders all frames."""
+
+    def __init__(self, frames: int = 16, sample_rate_hz: float = 24.0):
+        self.frames, self.sample_rate_hz = int(frames), float(sample_rate_hz)
+
+    def render(self, voxels: torch.Tensor, resonance_decay: torch.Tensor, temporal_harmonics: Optional[torch.Tensor] = None) -> TemporalRenderOutput:
+        from .ops import spectral
+        if voxels.dim() != 3:
+            raise ValueError(f"volume must be [depth, height, width], got {tuple(voxels.shape)}")
+        data = spectral.temporal_render(voxels, temporal_harmonics, resonance_decay, self.frames, self.sample_rate_hz)
+        D, H, W = voxels.shape
+        return TemporalRenderOutput(self.frames, D, H, W, [f / self.sample_rate_hz for f in range(self.frames)], data)
 
 
 # ----------------------------------------------------------------------------------------------
