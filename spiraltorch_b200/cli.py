@@ -160,11 +160,21 @@ def cmd_z_volume(args) -> int:
     z = torch.linspace(0, 1, d, device=dev)[:, None, None]
     y = torch.linspace(-1, 1, h, device=dev)[None, :, None]
     x = torch.linspace(-1, 1, w, device=dev)[None, None, :]
-    volume = torch.sin(6.0 * (x * x + y * y).sqrt() - 6.0 * z).mul(0.5).add(0.5) * torch.exp(-2.0 * z)
-    image = vision.temporal_volume_render(volume, density_scale=args.density)[..., :3].mean(-1)      # composited luminance
+    radius = (x * x + y * y).sqrt()
+    volume = torch.sin(6.0 * radius - 6.0 * z).mul(0.5).add(0.5) * torch.exp(-2.0 * z)
+    # temporal playback: two harmonics per voxel and a depth-dependent decay, rendered for `frames` instants by the
+    # temporal renderer kernel; the chosen frame is then composited front to back and painted
+    harmonics = torch.stack([0.25 * torch.cos(3.0 * radius).expand(d, h, w), 0.1 * torch.sin(5.0 * radius + z).expand(d, h, w)], dim=-1)
+    decay = (0.5 + 2.0 * z).expand(d, h, w).contiguous()
+    frames = max(int(getattr(args, "frames", 8)), 1)
+    played = vision.TemporalRenderer(frames, getattr(args, "rate", 24.0)).render(volume.contiguous(), decay, harmonics.contiguous())
+    pick = min(max(int(getattr(args, "frame", frames // 2)), 0), frames - 1)
+    frame = played.frame(pick).clamp(min=0.0)
+    image = vision.temporal_volume_render(frame, density_scale=args.density)[..., :3].mean(-1)       # composited luminance
     rgba = vision.canvas_paint(image, palette=args.palette)
     _write_ppm(args.out, rgba[..., :3])
-    print(json.dumps({"out": args.out, "shape": [h, w], "device": dev, "mean": float(image.mean())}))
+    print(json.dumps({"out": args.out, "shape": [h, w], "device": dev, "mean": float(image.mean()), "frames": frames,
+                      "frame": pick, "time_s": played.times[pick]}))
     return 0
 
 
@@ -229,6 +239,9 @@ def build_parser() -> argparse.ArgumentParser:
     zv.add_argument("--density", type=float, default=1.0)
     zv.add_argument("--palette", default="spiral")
     zv.add_argument("--backend", default="auto")
+    zv.add_argument("--frames", type=int, default=8, help="instants rendered by the temporal renderer")
+    zv.add_argument("--rate", type=float, default=24.0, help="frames per second of the playback")
+    zv.add_argument("--frame", type=int, default=4, help="which rendered instant becomes the image")
     zv.set_defaults(fn=cmd_z_volume)
     xa = sub.add_parser("xai", help="Grad-CAM heat map of a ResNet backbone")
     xa.add_argument("--out", default="gradcam.ppm")
