@@ -352,3 +352,48 @@ ST_API int st_info_nce_fwd(const StInfoNceArgs* a, void* stream_v) {
     default: return launch(info_nce_fwd_kernel<4>);
   }
 }
+
+// ---- backward helper: d_logits = (exp(logit - lse) - onehot) * coef, bf16, in both orientations ---------------------
+// The two gradient GEMMs want d_logits as [R, C] (for d_anchor = d_logits @ P) and as [C, R] (rows = the gathered
+// positives, for the GEMM -> reduce-scatter of d_positives).  One pass over the fp32 logits writes both: a 32 x 32
+// tile goes through shared memory so that both stores are coalesced.
+namespace {
+
+__global__ void info_nce_grad_kernel(const float* __restrict__ logits, const float* __restrict__ row_lse,
+                                     const float* __restrict__ coef, __nv_bfloat16* __restrict__ dl,
+                                     __nv_bfloat16* __restrict__ dl_t, int R, int C, int target_offset) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const float k = coef[0];
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    float v = 0.0f;
+    if (r < R && c < C) {
+      v = __expf(logits[(long long)r * C + c] - row_lse[r]);
+      if (c == r + target_offset) v -= 1.0f;
+      v *= k;
+      dl[(long long)r * C + c] = __float2bfloat16(v);
+    }
+    tile[i][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < R && c < C) dl_t[(long long)c * R + r] = __float2bfloat16(tile[threadIdx.x][i]);
+  }
+}
+
+}  // namespace
+
+// logits [R, C] fp32 (already divided by the temperature), row_lse [R], coef: one device float (upstream gradient / R);
+// the positive of row r is column r + target_offset.  Writes dl [R, C] and dl_t [C, R] in bf16.
+ST_API int st_info_nce_grad(const float* logits, const float* row_lse, const float* coef, void* dl, void* dl_t, int R,
+                            int C, int target_offset, void* stream_v) {
+  if (R <= 0 || C <= 0) return st::fail(ST_ERR_INVALID, "info_nce_grad: empty problem");
+  if (target_offset < 0 || target_offset + R > C) return st::fail(ST_ERR_INVALID, "info_nce_grad: positives fall outside the columns");
+  dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+  info_nce_grad_kernel<<<grid, block, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      logits, row_lse, coef, reinterpret_cast<__nv_bfloat16*>(dl), reinterpret_cast<__nv_bfloat16*>(dl_t), R, C, target_offset);
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}

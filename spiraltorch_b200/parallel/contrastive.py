@@ -82,6 +82,28 @@ class FusedInfoNCE:
         return _InfoNceFn.apply(anchors, positives, self)
 
 
+def info_nce_grad(logits: torch.Tensor, row_lse: torch.Tensor, coef: torch.Tensor, target_offset: int):
+    """``(exp(logits - lse) - onehot) * coef`` in bf16 as ``[R, C]`` and as ``[C, R]``; the positive of row ``r`` is
+    column ``r + target_offset``.  One kernel pass over the fp32 logits on CUDA, plain tensor ops on CPU."""
+    global launch_count
+    R, C = logits.shape
+    if not (logits.is_cuda and native.available()):
+        prob = torch.exp(logits.float() - row_lse[:, None])
+        idx = torch.arange(R, device=logits.device)
+        prob[idx, idx + target_offset] -= 1.0
+        dl = (prob * coef.float()).to(torch.bfloat16)
+        return dl, dl.t().contiguous()
+    lg = logits.float().contiguous()
+    dl = torch.empty(R, C, dtype=torch.bfloat16, device=lg.device)
+    dl_t = torch.empty(C, R, dtype=torch.bfloat16, device=lg.device)
+    st = native.lib().st_info_nce_grad(native.ptr(lg), native.ptr(row_lse.float().contiguous()), native.ptr(coef.float().contiguous()),
+                                       native.ptr(dl), native.ptr(dl_t), ctypes.c_int(R), ctypes.c_int(C),
+                                       ctypes.c_int(target_offset), native.stream_ptr(lg.device))
+    native.check(st, "st_info_nce_grad")
+    launch_count += 1
+    return dl, dl_t
+
+
 class _InfoNceFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, anchors, positives, op: FusedInfoNCE):
@@ -102,17 +124,13 @@ class _InfoNceFn(torch.autograd.Function):
         # fp32 logits: for a confident positive, softmax - 1 is a difference of nearly equal numbers
         # and bf16 logits (spacing 0.06 near 10) would lose most of its digits
         logits = gemm_ops.gemm(a_, p_all, alpha=inv_t, out_dtype=torch.float32)      # [R, W*R]
-        target = torch.arange(R, device=a_.device, dtype=torch.int64) + rank * R
-        coef = dloss.float() / R
-        prob = torch.exp(logits - row_lse[:, None])
-        prob[torch.arange(R, device=a_.device), target] -= 1.0
-        dl = (prob * coef).to(torch.bfloat16)                                       # softmax - onehot, scaled
+        coef = (dloss.float() / R).reshape(1).contiguous()
+        dl, dl_t = info_nce_grad(logits, row_lse, coef, rank * R)                    # softmax - onehot, scaled; and its transpose
         d_anchor = gemm_ops.gemm(dl, p_all, b_mn=True, alpha=inv_t)
-        dl_t = dl.t().contiguous()                                          # [W*R, R]
         if W == 1:
             d_pos = gemm_ops.gemm(dl_t, a_, b_mn=True, alpha=inv_t)
         elif op.tp is not None:
-            d_pos = op.tp.gemm_rs(dl_t, a_, b_mn=True) * inv_t
+            d_pos = op.tp.gemm_rs(dl_t, a_, b_mn=True, alpha=inv_t)
         else:
             partial = gemm_ops.gemm(dl_t, a_, b_mn=True, alpha=inv_t)
             d_pos = torch.empty((R, op.D), dtype=partial.dtype, device=partial.device)

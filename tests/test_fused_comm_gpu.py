@@ -175,3 +175,23 @@ def test_dp_step_two_phase_clips_by_global_norm_world1():
         assert grad.tensor.abs().max().item() == 0
     torch.cuda.synchronize()
     assert native.read_error_word()[0] == 0
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 128), (50, 70, 11)])
+def test_info_nce_grad_kernel_matches_formula_in_both_orientations(shape):
+    from spiraltorch_b200.parallel import contrastive as C
+    R, cols, off = shape
+    torch.manual_seed(R)
+    logits = torch.randn(R, cols, device=DEV) * 3
+    lse = torch.logsumexp(logits, dim=1)
+    coef = torch.tensor([0.37 / R], device=DEV)
+    before = C.launch_count
+    dl, dl_t = C.info_nce_grad(logits, lse, coef, off)
+    assert C.launch_count == before + 1 and dl.dtype == torch.bfloat16 and dl_t.shape == (cols, R)
+    want = torch.softmax(logits, dim=1)
+    want[torch.arange(R), torch.arange(R) + off] -= 1.0
+    want = want * coef
+    assert float((dl.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    assert torch.equal(dl_t, dl.t().contiguous())
+    cpu = C.info_nce_grad(logits.cpu(), lse.cpu(), coef.cpu(), off)[0]
+    assert float((cpu.float() - dl.float().cpu()).abs().max()) <= 1e-2 * float(want.abs().max())
