@@ -650,3 +650,46 @@ ST_API int st_ce_grad(const void* logits, const long long* target, const float* 
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
+
+// ---- N-d indexer: logical element id -> strided address and segment id ------------------------------------------------
+// Each logical id is decoded against `dims` (innermost last; a zero dimension is skipped and leaves coordinate 0),
+// dotted with `strides`, and the address is bucketed into `segments` segments of `segment_stride` elements.
+namespace {
+struct NdIndexerParams {
+  unsigned dims[4];
+  unsigned strides[4];
+  unsigned segments, segment_stride;
+};
+
+__global__ void nd_indexer_kernel(const unsigned* __restrict__ positions, unsigned* __restrict__ out_index,
+                                  unsigned* __restrict__ out_segment, long long n, NdIndexerParams p) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    unsigned remaining = positions[i], flat = 0;
+#pragma unroll
+    for (int d = 3; d >= 0; --d) {
+      const unsigned dim = p.dims[d];
+      if (dim == 0) continue;
+      flat += (remaining % dim) * p.strides[d];
+      remaining /= dim;
+    }
+    out_index[i] = flat;
+    out_segment[i] = (flat / p.segment_stride) % p.segments;
+  }
+}
+}  // namespace
+
+ST_API int st_nd_indexer(const unsigned* positions, unsigned* out_index, unsigned* out_segment, long long n,
+                         const unsigned* dims4, const unsigned* strides4, unsigned segments, unsigned segment_stride,
+                         void* stream_v) {
+  if (n <= 0) return ST_OK;
+  if (!dims4 || !strides4) return st::fail(ST_ERR_INVALID, "nd_indexer: null dims / strides");
+  if (segments == 0 || segment_stride == 0) return st::fail(ST_ERR_INVALID, "nd_indexer: segments and segment_stride must be positive");
+  NdIndexerParams p;
+  for (int i = 0; i < 4; ++i) { p.dims[i] = dims4[i]; p.strides[i] = strides4[i]; }
+  p.segments = segments; p.segment_stride = segment_stride;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  nd_indexer_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(positions, out_index, out_segment, n, p);
+  ST_CUDA_CHECK(cudaGetLastError());
+  return ST_OK;
+}

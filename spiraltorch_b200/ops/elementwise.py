@@ -282,3 +282,43 @@ def row_softmax_spiral(x: torch.Tensor):
     native.check(st, "st_row_softmax_spiral_f32")
     launch_count += 1
     return soft, hard, spiral, metrics, zmetrics
+
+
+def nd_indexer(positions: torch.Tensor, dims, strides, segments: int, segment_stride: int):
+    """Strided address and segment id of each logical element id (crates/st-backend-wgpu/src/shaders/nd_indexer.wgsl).
+
+    ``dims`` / ``strides``: up to four entries, innermost last; a zero dimension is skipped.  The id is decoded
+    against ``dims``, the coordinates are dotted with ``strides`` and the address falls into segment
+    ``(address // segment_stride) % segments``.  Returns ``(addresses, segments)`` as int64 tensors (32-bit unsigned
+    arithmetic inside, as the shader's)."""
+    global launch_count
+    dims, strides = list(dims), list(strides)
+    if not 1 <= len(dims) <= 4 or len(dims) != len(strides):
+        raise ValueError("nd_indexer takes between one and four dimensions with as many strides")
+    if segments <= 0 or segment_stride <= 0:
+        raise ValueError("segments and segment_stride must be positive")
+    if any(d < 0 or d >= 1 << 32 for d in dims + strides):
+        raise ValueError("dimensions and strides must fit an unsigned 32-bit integer")
+    dims = [0] * (4 - len(dims)) + dims
+    strides = [0] * (4 - len(strides)) + strides
+    pos = positions.reshape(-1).to(torch.int64)
+    if pos.numel() and (int(pos.min()) < 0 or int(pos.max()) >= 1 << 32):
+        raise ValueError("logical ids must fit an unsigned 32-bit integer")
+    if not (pos.is_cuda and native.available()):
+        remaining, flat = pos.clone(), torch.zeros_like(pos)
+        for d in range(3, -1, -1):
+            if dims[d] == 0:
+                continue
+            flat = (flat + (remaining % dims[d]) * strides[d]) & 0xFFFFFFFF
+            remaining = remaining // dims[d]
+        return flat.reshape(positions.shape), ((flat // segment_stride) % segments).reshape(positions.shape)
+    p32 = pos.to(torch.int32) if int(pos.max() if pos.numel() else 0) < 1 << 31 else (pos - (1 << 32) * (pos >= 1 << 31)).to(torch.int32)
+    out_i, out_s = torch.empty_like(p32), torch.empty_like(p32)
+    arr = ctypes.c_uint * 4
+    st = native.lib().st_nd_indexer(native.ptr(p32), native.ptr(out_i), native.ptr(out_s), ctypes.c_longlong(p32.numel()),
+                                    arr(*dims), arr(*strides), ctypes.c_uint(segments), ctypes.c_uint(segment_stride),
+                                    native.stream_ptr(p32.device))
+    native.check(st, "st_nd_indexer")
+    launch_count += 1
+    unsigned = lambda t: t.to(torch.int64) & 0xFFFFFFFF                       # noqa: E731
+    return unsigned(out_i).reshape(positions.shape), unsigned(out_s).reshape(positions.shape)

@@ -58,3 +58,30 @@ def test_kernel_matches_cpu_statement(shape):
     assert E.launch_count == before + 1
     for a, b, tol in zip(gpu, cpu, (1e-5, 0, 1e-5, 2e-4, 2e-4)):
         assert (a.cpu() - b).abs().max().item() <= tol + 1e-5 * b.abs().max().item()
+
+
+def test_nd_indexer_cpu_semantics():
+    from spiraltorch_b200.ops import elementwise as E
+    pos = torch.arange(24)
+    addr, seg = E.nd_indexer(pos, [2, 3, 4], [100, 10, 1], 4, 50)
+    want = torch.tensor([100 * (p // 12) + 10 * ((p // 4) % 3) + (p % 4) for p in range(24)])
+    assert torch.equal(addr, want) and torch.equal(seg, (want // 50) % 4)
+    assert E.nd_indexer(pos[:6], [0, 3, 2], [7, 2, 1], 1, 1)[0].tolist() == [0, 1, 2, 3, 4, 5]          # a zero dimension is skipped
+    assert E.nd_indexer(pos.reshape(4, 6), [24], [3], 2, 9)[0].shape == (4, 6)
+    for bad in (lambda: E.nd_indexer(pos, [1] * 5, [1] * 5, 1, 1), lambda: E.nd_indexer(pos, [2, 3], [1], 1, 1),
+                lambda: E.nd_indexer(pos, [24], [1], 0, 1), lambda: E.nd_indexer(-pos - 1, [24], [1], 1, 1)):
+        with pytest.raises(ValueError):
+            bad()
+
+
+@pytest.mark.gpu
+def test_nd_indexer_kernel_matches_cpu():
+    from spiraltorch_b200.ops import elementwise as E
+    torch.manual_seed(0)
+    pos = torch.randint(0, 5 * 7 * 11 * 13, (10000,))
+    args = ([5, 7, 11, 13], [2002, 143, 13, 1], 8, 640)
+    before = E.launch_count
+    a_g, s_g = E.nd_indexer(pos.cuda(), *args)
+    assert E.launch_count == before + 1
+    a_c, s_c = E.nd_indexer(pos, *args)
+    assert torch.equal(a_g.cpu(), a_c) and torch.equal(s_g.cpu(), s_c)
