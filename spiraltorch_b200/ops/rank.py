@@ -85,11 +85,16 @@ def rank_select_reference(x: torch.Tensor, k: int, mode: int):
     return out_v, out_i
 
 
-def rank_select(x: torch.Tensor, k: int, kind: str = "topk"):
-    """Returns ``(values [rows,k] fp32, indices [rows,k] int32)``."""
+def rank_select(x: torch.Tensor, k: int, kind: str = "topk", choice=None):
+    """Returns ``(values [rows,k] fp32, indices [rows,k] int32)``.  ``choice`` (a ``unison.RankChoice``) may ask for the
+    two-stage path with its sweep tile as chunk width on rows that one CTA could also sort directly; top / bottom only,
+    and only when a chunk pass actually shrinks the row."""
     global launch_count
     mode = MODES[kind]
     rows, cols = x.shape
+    if choice is not None and choice.use_2ce and mode != 2 and 0 < k and native.use_native(x) and cols <= MAX_KERNEL_COLS \
+            and 0 < choice.tile < cols and -(-cols // choice.tile) * min(k, choice.tile) < cols:
+        return _rank_select_two_stage(x, k, kind, chunk=choice.tile)
     if k < 0 or k > max(cols, 0) and cols > 0 and k > cols:
         raise ValueError(f"k={k} exceeds cols={cols}")
     if not native.use_native(x):
@@ -112,13 +117,13 @@ def rank_select(x: torch.Tensor, k: int, kind: str = "topk"):
 MAX_KERNEL_COLS = 8192      # one CTA sorts a row of at most this many (value, index) keys in shared memory
 
 
-def _rank_select_two_stage(x: torch.Tensor, k: int, kind: str):
+def _rank_select_two_stage(x: torch.Tensor, k: int, kind: str, chunk: int = 0):
     """Rows wider than one CTA's shared-memory sort: select per column chunk, then select among the candidates
     (the reference's two-stage path: rankk_exact_2ce.wgsl, crates/st-core/src/distributed/topk3_stage.rs:56).
     Exact, including the tie rule: candidates keep chunk order and, inside a chunk, the kernel's own order, so
     equal values still resolve to the lower column."""
     rows, cols = x.shape
-    n_chunks = -(-cols // MAX_KERNEL_COLS)
+    n_chunks = -(-cols // (min(chunk, MAX_KERNEL_COLS) if chunk > 0 else MAX_KERNEL_COLS))
     width = -(-cols // n_chunks)
     pad = n_chunks * width - cols
     xf = x.float()
