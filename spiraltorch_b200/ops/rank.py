@@ -92,6 +92,8 @@ def rank_select(x: torch.Tensor, k: int, kind: str = "topk", choice=None):
     global launch_count
     mode = MODES[kind]
     rows, cols = x.shape
+    if choice is None and mode != 2 and k > 1 and 1024 <= cols <= MAX_KERNEL_COLS and native.use_native(x):
+        choice = _tuned_choice(rows, cols, k, kind)
     if choice is not None and choice.use_2ce and mode != 2 and 0 < k and native.use_native(x) and cols <= MAX_KERNEL_COLS \
             and 0 < choice.tile < cols and -(-cols // choice.tile) * min(k, choice.tile) < cols:
         return _rank_select_two_stage(x, k, kind, chunk=choice.tile)
@@ -112,6 +114,24 @@ def rank_select(x: torch.Tensor, k: int, kind: str = "topk", choice=None):
     native.check(st, "st_rank_select")
     launch_count += 1
     return out_v, out_i
+
+
+_choice_cache: dict = {}
+
+
+def _tuned_choice(rows: int, cols: int, k: int, kind: str):
+    """The three-voice chooser's pick for this shape (cached per power-of-two row bucket): on rows of 1024 to 8192
+    columns the tuned table often prefers per-chunk candidates + merge over one full-width sort."""
+    key = (1 << max(rows - 1, 0).bit_length(), cols, k, MODES[kind])
+    hit = _choice_cache.get(key)
+    if hit is None:
+        from .. import unison
+        from ..device_caps import DeviceCaps
+        hit = unison.choose_unified_rank(rows, cols, k, DeviceCaps.cuda(), "topk" if MODES[kind] == 0 else "bottomk").choice
+        if len(_choice_cache) > 4096:
+            _choice_cache.clear()
+        _choice_cache[key] = hit
+    return hit
 
 
 MAX_KERNEL_COLS = 8192      # one CTA sorts a row of at most this many (value, index) keys in shared memory

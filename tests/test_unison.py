@@ -87,7 +87,11 @@ def test_two_stage_by_choice_matches_direct_selection():
     x = torch.randn(64, 4096, device="cuda")
     x[:, 100] = x[:, 7]                                                                  # a tie: the lower column must win
     for kind in ("topk", "bottomk"):
-        dv, di = rank.rank_select(x, 16, kind)
+        dv, di = rank.rank_select(x, 16, kind, choice=unison.RankChoice(False, 256, 16, 4096, 256))      # one full-width sort
+        ref_v, ref_i = rank.rank_select_reference(x, 16, rank.MODES[kind])
+        assert torch.equal(dv, ref_v) and torch.equal(di, ref_i)
+        tv, ti = rank.rank_select(x, 16, kind)                                               # the tuned default
+        assert torch.equal(tv, ref_v) and torch.equal(ti, ref_i)
         before = rank.launch_count
         cv, ci = rank.rank_select(x, 16, kind, choice=unison.RankChoice(True, 256, 16, 512, 256))
         assert rank.launch_count - before == 2                                           # per-chunk pass + merge pass
