@@ -14,6 +14,7 @@ from .modules import (BatchNorm1d, Dropout, Embedding, FeatureReorder2d, Gelu, I
 from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSchedule, SoftLogicConfig, StepMetrics
 from . import amp, coherence, conv, fields, gnn, graph, lightning, roundtable, zrba, zspace
 from .graph import GraphedTrainStep
+from .zrelativity import ZRelativityModule
 from .roundtable import DistConfig, MetaConductor, MetaSummary, RoundtableNode
 from .conv import AvgPool2d, Conv2d, Conv3d, Conv4d, Conv6da, MaxPool2d, WaveScan, ZConv6DA
 from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,
