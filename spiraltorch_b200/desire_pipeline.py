@@ -559,6 +559,108 @@ class DesireRoundtableBridge(DesirePipelineSink):
             self._drift_gain = min(max(g * (1.0 - 0.03 * abs(r)), 0.1), 1.2)
 
 
+# ---- psi bridge ---------------------------------------------------------------------------------------------------
+def record_step_with_psi(step: DesireAutomatedStep, timestamp: float):
+    """Builds the step's telemetry sample with the psi reading, psi events and soft-logic Z feedback that the
+    telemetry hub holds at this moment, stores it as the hub's latest desire step, and returns
+    ``(sample, reading, z_feedback)``.  Parity: crates/st-nn/src/language/pipeline.rs:150-231."""
+    from . import hub
+    s = step.solution
+    with hub.telemetry_guard():
+        reading, events, z = hub.get_last_psi(), hub.get_last_psi_events(), hub.get_softlogic_z()
+    avoid = getattr(s, "avoidance", None)
+    offsets = getattr(s, "logit_offsets", None)
+    sample = hub.DesireStepTelemetry(
+        timestamp=timestamp, entropy=s.entropy, temperature=s.temperature, hypergrad_penalty=s.hypergrad_penalty,
+        avoidance_energy=float(sum(abs(float(v)) for v in avoid.scores)) if avoid is not None else 0.0,
+        logit_energy=float(torch.as_tensor(offsets).abs().sum()) if offsets is not None else 0.0, phase=s.phase,
+        alpha=s.weights.alpha, beta=s.weights.beta, gamma=s.weights.gamma, lam=s.weights.lam,
+        avoidance={"tokens": list(avoid.tokens), "scores": [float(v) for v in avoid.scores]} if avoid is not None else None,
+        trigger=None if step.trigger is None else {"mean_penalty": step.trigger.mean_penalty, "mean_entropy": step.trigger.mean_entropy,
+                                                   "temperature": step.trigger.temperature, "samples": step.trigger.samples},
+        trigger_emitted=step.trigger is not None, psi_total=None if reading is None else reading.total,
+        psi_breakdown={} if reading is None else dict(reading.breakdown), psi_events=list(events), z_feedback=z)
+    hub.set_last_desire_step(sample)
+    return sample, reading, z
+
+
+@dataclass
+class DesirePsiEvent:
+    timestamp: float
+    solution: DesireSolution
+    trigger: Optional[DesireRewriteTrigger]
+    telemetry: object
+    reading: object
+    z_feedback: object
+    events: list
+
+
+@dataclass
+class DesirePsiSummary:
+    steps: int = 0
+    triggers: int = 0
+    psi_samples: int = 0
+    mean_psi_total: float = 0.0
+    component_means: dict = field(default_factory=dict)
+    threshold_crossings: dict = field(default_factory=dict)          # component -> (ups, downs)
+    mean_entropy: float = 0.0
+    mean_temperature: float = 0.0
+    mean_hypergrad_penalty: float = 0.0
+    mean_z_signal: float = 0.0
+    last_timestamp: float = 0.0
+
+    @classmethod
+    def from_events(cls, events: list) -> "DesirePsiSummary":
+        n = len(events)
+        comp_sum, comp_n, crossings = {}, {}, {}
+        psi_samples = psi_total = z_n = z_sum = 0.0
+        for e in events:
+            t = e.telemetry
+            if t.psi_total is not None:
+                psi_samples, psi_total = psi_samples + 1, psi_total + t.psi_total
+                for c, v in t.psi_breakdown.items():
+                    comp_sum[c], comp_n[c] = comp_sum.get(c, 0.0) + v, comp_n.get(c, 0) + 1
+            if e.z_feedback is not None:
+                z_n, z_sum = z_n + 1, z_sum + e.z_feedback.z_signal
+            for ev in t.psi_events:
+                up, down = crossings.get(ev.component, (0, 0))
+                crossings[ev.component] = (up + 1, down) if ev.up else (up, down + 1)
+        mean = lambda f: sum(f(e.telemetry) for e in events) / n if n else 0.0       # noqa: E731
+        return cls(n, sum(e.trigger is not None for e in events), int(psi_samples), psi_total / psi_samples if psi_samples else 0.0,
+                   {c: comp_sum[c] / comp_n[c] for c in comp_sum}, crossings, mean(lambda t: t.entropy), mean(lambda t: t.temperature),
+                   mean(lambda t: max(t.hypergrad_penalty, 0.0)), z_sum / z_n if z_n else 0.0, max((e.timestamp for e in events), default=0.0))
+
+
+class DesirePsiBridge(DesirePipelineSink):
+    """Pairs every desire step with the psi reading and Z feedback current at that moment; a trainer drains the events
+    (or their summary) once per step.  Parity: crates/st-nn/src/language/pipeline.rs:2288-2470."""
+
+    def __init__(self):
+        self._events: list = []
+        self._lock = threading.Lock()
+
+    def on_step(self, step, timestamp):
+        sample, reading, z = record_step_with_psi(step, timestamp)
+        with self._lock:
+            self._events.append(DesirePsiEvent(timestamp, step.solution, step.trigger, sample, reading, z, list(sample.psi_events)))
+
+    def __len__(self):
+        with self._lock:
+            return len(self._events)
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+    def drain(self) -> list:
+        with self._lock:
+            out, self._events = self._events, []
+        return out
+
+    def drain_summary(self) -> Optional[DesirePsiSummary]:
+        events = self.drain()
+        return DesirePsiSummary.from_events(events) if events else None
+
+
 class DesireTelemetryBundle:
     """The bridges a pipeline should feed, handed around as one object."""
 
@@ -605,6 +707,7 @@ class DesirePipelineBuilder:
     def with_trainer_bridge(self, bridge: DesireTrainerBridge): return self.with_sink(bridge)                    # noqa: E704
     def with_trigger_buffer(self, buffer: DesireTriggerBuffer): return self.with_sink(buffer)                    # noqa: E704
     def with_roundtable_bridge(self, bridge: "DesireRoundtableBridge"): return self.with_sink(bridge)            # noqa: E704
+    def with_psi_bridge(self, bridge: "DesirePsiBridge"): return self.with_sink(bridge)                          # noqa: E704
 
     def with_telemetry_bundle(self, bundle: "DesireTelemetryBundle") -> "DesirePipelineBuilder":
         for sink in bundle.sinks():
@@ -634,6 +737,7 @@ class DesirePipeline:
     def attach_telemetry(self): self.attach_sink(DesireTelemetrySink())                   # noqa: E704
     def attach_trainer_bridge(self, bridge): self.attach_sink(bridge)                     # noqa: E704
     def attach_roundtable_bridge(self, bridge): self.attach_sink(bridge)                  # noqa: E704
+    def attach_psi_bridge(self, bridge): self.attach_sink(bridge)                         # noqa: E704
 
     def sink_count(self) -> int:
         return len(self.sinks)

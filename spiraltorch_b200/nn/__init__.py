@@ -33,7 +33,8 @@ from .coherence import (CoherenceBackend, CoherenceChannelReport, CoherenceDiagn
                         ZSpaceCoherenceSequencer, ZSpaceTraceConfig, ZSpaceTraceRecorder, coherence_relation_tensor,
                         is_swap_invariant)
 from ..language import ConceptHint, MaxwellDesireBridge, NarrativeHint, NarrativeSummary
-from ..desire_pipeline import DesirePipeline, DesireRoundtableBridge, DesireTelemetryBundle, DesireTrainerBridge
+from ..desire_pipeline import (DesirePipeline, DesirePsiBridge, DesirePsiEvent, DesirePsiSummary, DesireRoundtableBridge,
+                               DesireTelemetryBundle, DesireTrainerBridge)
 
 NnModuleTrainer = ModuleTrainer          # the binding registers the trainer under both names
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)

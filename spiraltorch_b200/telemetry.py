@@ -462,6 +462,309 @@ class ChronoTimeline:
         return k
 
 
+# ---- chrono harmonics, loop signal, time warps, maintainer ------------------------------------------------
+@dataclass
+class ChronoPeak:
+    frequency: float = 0.0
+    magnitude: float = 0.0
+    phase: float = 0.0
+
+
+@dataclass
+class ChronoHarmonics:
+    """Magnitude spectra ``|DFT| / n`` of the drift and energy series of a window of frames (the first ``bins``
+    bins), with the strongest non-DC bin of each.  Parity: crates/st-core/src/telemetry/chrono.rs:55-151,258-300."""
+    frames: int
+    duration: float
+    sample_rate: float
+    nyquist: float
+    drift_power: List[float]
+    energy_power: List[float]
+    dominant_drift: Optional[ChronoPeak]
+    dominant_energy: Optional[ChronoPeak]
+
+    @staticmethod
+    def _spectrum(series: List[float], bins: int) -> List[float]:
+        import torch
+        x = torch.tensor(series, dtype=torch.float64)
+        return (torch.fft.rfft(x).abs()[:bins] / len(series)).tolist()
+
+    @staticmethod
+    def _peak(power: List[float], sample_rate: float, samples: int) -> Optional[ChronoPeak]:
+        best, best_v = None, 0.0
+        for k, v in enumerate(power):
+            if k and math.isfinite(v) and v > best_v:
+                best, best_v = k, v
+        return None if best is None else ChronoPeak(sample_rate * best / samples, best_v, 0.0)
+
+    @classmethod
+    def from_frames(cls, frames: Sequence[ChronoFrame], bins: int) -> Optional["ChronoHarmonics"]:
+        n = len(frames)
+        if n < 2 or bins <= 0:
+            return None
+        duration = sum(max(f.dt, 1.1920929e-07) for f in frames)
+        if not math.isfinite(duration) or duration <= 1.1920929e-07:
+            return None
+        rate = n / duration
+        bins = min(bins, n // 2 + 1)
+        dp = cls._spectrum([f.curvature_drift for f in frames], bins)
+        ep = cls._spectrum([f.total_energy for f in frames], bins)
+        out = cls(n, duration, rate, 0.5 * rate, dp, ep, cls._peak(dp, rate, n), cls._peak(ep, rate, n))
+        from . import observability
+        observability.emit_tensor_op("chrono_harmonics_summary", (n, bins), (2, bins))
+        observability.emit_tensor_op_meta("chrono_harmonics_summary", lambda: {
+            "backend": "torch", "kind": "chrono_harmonics_summary", "frames": n, "bins": bins, "duration": duration,
+            "sample_rate": rate, "nyquist": 0.5 * rate, "drift_power_total": sum(dp), "energy_power_total": sum(ep),
+            "has_dominant_drift": out.dominant_drift is not None, "has_dominant_energy": out.dominant_energy is not None,
+            "dominant_drift_frequency": out.dominant_drift.frequency if out.dominant_drift else 0.0,
+            "dominant_energy_frequency": out.dominant_energy.frequency if out.dominant_energy else 0.0})
+        return out
+
+
+def _clampf(v: float, lo: float, hi: float) -> float:
+    return min(max(v, lo), hi)
+
+
+@dataclass
+class ChronoLoopSignal:
+    """A summary with its harmonics and the SpiralK hints derived from them (radix / segments / tile_cols from the
+    drift and energy statistics, kl / wg from the dominant peaks).  Parity: chrono.rs:157-256."""
+    summary: ChronoSummary
+    harmonics: Optional[ChronoHarmonics] = None
+    spiralk_script: Optional[str] = None
+    spiralk_hints: list = field(default_factory=list)
+
+    def __post_init__(self):
+        from .kdsl_rewrite import HeuristicHint, synthesize_program
+        s, hints = self.summary, []
+        drift = _clampf(s.mean_abs_drift, 0.0, 4.0)
+        band = max(s.max_energy - s.min_energy, 0.0)
+        hints.append(HeuristicHint("radix", f"{_clampf(2.0 + drift * 4.0, 2.0, 16.0):.3f}", _clampf(0.25 + drift, 0.25, 0.9), "true"))
+        hints.append(HeuristicHint("segments", f"{_clampf(1.0 + band ** 0.25 * 2.0, 1.0, 8.0):.3f}", 0.3 + min(drift, 1.0) * 0.2, "true"))
+        hints.append(HeuristicHint("tile_cols", f"{_clampf(64.0 + s.mean_energy * 8.0, 32.0, 512.0):.3f}",
+                                   _clampf(0.3 + math.sqrt(band) * 0.1, 0.3, 1.1), "true"))
+        h = self.harmonics
+        if h is not None and h.dominant_drift is not None:
+            hints.append(HeuristicHint("kl", f"{_clampf(1.0 + h.dominant_drift.frequency * max(h.duration, 1e-3), 1.0, 9.0):.3f}",
+                                       _clampf(h.dominant_drift.magnitude, 0.05, 1.2), "true"))
+        if h is not None and h.dominant_energy is not None:
+            hints.append(HeuristicHint("wg", f"{_clampf(128.0 + h.dominant_energy.frequency * 48.0, 64.0, 2048.0):.3f}",
+                                       _clampf(h.dominant_energy.magnitude, 0.05, 1.5), "true"))
+        self.spiralk_hints = hints
+        self.spiralk_script = synthesize_program("", hints) if hints else None
+
+
+class TemporalWarpError(ValueError):
+    def __init__(self, kind: str, message: str):
+        super().__init__(message)
+        self.kind = kind
+
+
+@dataclass(frozen=True)
+class TemporalWarp:
+    """``t -> pivot + (t - pivot) * scale + offset`` with a positive finite scale.  Parity: crates/st-core/src/util/timewarp.rs."""
+    scale: float = 1.0
+    offset: float = 0.0
+    pivot: float = 0.0
+
+    def validate(self) -> None:
+        if not all(math.isfinite(v) for v in (self.scale, self.offset, self.pivot)):
+            raise TemporalWarpError("non_finite", "warp components must be finite")
+        if self.scale <= 0.0:
+            raise TemporalWarpError("invalid_scale", f"warp scale must be positive, got {self.scale}")
+
+    @classmethod
+    def dilation(cls, factor: float) -> "TemporalWarp":
+        return cls(factor, 0.0, 0.0)
+
+    @classmethod
+    def translation(cls, offset: float) -> "TemporalWarp":
+        return cls(1.0, offset, 0.0)
+
+    @classmethod
+    def fit_span(cls, source_start: float, source_end: float, target_start: float, target_end: float) -> "TemporalWarp":
+        if not all(math.isfinite(v) for v in (source_start, source_end, target_start, target_end)):
+            raise TemporalWarpError("non_finite", "spans must be finite")
+        src, dst = source_end - source_start, target_end - target_start
+        if abs(src) <= 1.1920929e-07:
+            if abs(dst) <= 1.1920929e-07:
+                return cls(1.0, target_start - source_start, 0.0)
+            raise TemporalWarpError("degenerate", "cannot stretch an empty span")
+        scale = dst / src
+        if scale <= 0.0:
+            raise TemporalWarpError("invalid_scale", f"warp scale must be positive, got {scale}")
+        return cls(scale, target_start - source_start * scale, 0.0)
+
+    def apply(self, t: float) -> float:
+        return self.pivot + (t - self.pivot) * self.scale + self.offset
+
+
+def _timeline_harmonics(self, window: int, bins: int) -> Optional[ChronoHarmonics]:
+    fr = list(self._frames)[-max(1, window):]
+    return ChronoHarmonics.from_frames(fr, bins) if fr else None
+
+
+def _timeline_loop_signal(self, window: int, bins: int) -> Optional[ChronoLoopSignal]:
+    if not self._frames:
+        return None
+    window = min(max(1, window), len(self._frames))
+    summary = self.summarise(window)
+    return ChronoLoopSignal(summary, None if window < 2 else self.harmonics(window, max(bins, 1)))
+
+
+def _timeline_warp(self, warp: TemporalWarp) -> None:
+    """Re-times every frame; ``dt`` follows the warped axis and the energy decay rate is divided by the scale."""
+    if not self._frames:
+        raise TemporalWarpError("empty", "the timeline has no frames")
+    warp.validate()
+    frames = list(self._frames)
+    axis = [frames[0].timestamp - frames[0].dt] + [f.timestamp for f in frames]
+    if not all(math.isfinite(t) for t in axis):
+        raise TemporalWarpError("non_finite", "timestamps must be finite")
+    if any(b < a for a, b in zip(axis, axis[1:])):
+        raise TemporalWarpError("non_monotonic", "timestamps must not decrease")
+    warped = [warp.apply(t) for t in axis]
+    if not all(math.isfinite(t) for t in warped):
+        raise TemporalWarpError("non_finite", "the warp leaves the representable range")
+    prev = warped[0]
+    for f, t in zip(frames, warped[1:]):
+        f.dt, f.timestamp = max(t - prev, 1.1920929e-07), t
+        f.energy_decay /= warp.scale
+        prev = t
+    self._time = prev
+
+
+def _timeline_dilate(self, factor: float) -> None:
+    self.warp_time_axis(TemporalWarp.dilation(factor))
+
+
+def _timeline_shift(self, offset: float) -> None:
+    if not math.isfinite(offset):
+        raise TemporalWarpError("non_finite", "offset must be finite")
+    self.warp_time_axis(TemporalWarp.translation(offset))
+
+
+def _timeline_align(self, progress: float, window: float) -> None:
+    """Stretches the recorded span onto ``[0, window * progress]``."""
+    if not self._frames:
+        raise TemporalWarpError("empty", "the timeline has no frames")
+    if not (math.isfinite(progress) and math.isfinite(window)):
+        raise TemporalWarpError("non_finite", "progress and window must be finite")
+    first, last = self._frames[0], self._frames[-1]
+    target = max(max(window, 1.1920929e-07) * max(progress, 0.0), 1.1920929e-07)
+    self.warp_time_axis(TemporalWarp.fit_span(first.timestamp - first.dt, last.timestamp, 0.0, target))
+
+
+ChronoTimeline.harmonics = _timeline_harmonics
+ChronoTimeline.loop_signal = _timeline_loop_signal
+ChronoTimeline.warp_time_axis = _timeline_warp
+ChronoTimeline.dilate = _timeline_dilate
+ChronoTimeline.shift = _timeline_shift
+ChronoTimeline.align_to_progress = _timeline_align
+
+
+def chrono_summary_from_frames(frames: Sequence[ChronoFrame]) -> Optional[ChronoSummary]:
+    t = ChronoTimeline(max(len(frames), 1))
+    t._frames.extend(frames)
+    return t.summarise(len(frames)) if frames else None
+
+
+MAINTAINER_STATUSES = ("stable", "dormant", "clamp", "rewrite")
+
+
+@dataclass
+class MaintainerConfig:
+    jitter_threshold: float = 0.35
+    growth_threshold: float = 0.05
+    energy_floor: float = 1e-3
+    clamp_min: float = 2.0
+    clamp_max: float = 3.0
+    pressure_step: float = 0.12
+    window: int = 32
+
+    def sanitise(self) -> "MaintainerConfig":
+        def pos(v, d, strict=True):
+            return v if math.isfinite(v) and (v > 0.0 if strict else v >= 0.0) else d
+        lo = self.clamp_min if math.isfinite(self.clamp_min) else 2.0
+        hi = self.clamp_max if math.isfinite(self.clamp_max) else 3.0
+        return MaintainerConfig(pos(self.jitter_threshold, 0.35), pos(self.growth_threshold, 0.05), pos(self.energy_floor, 1e-3, False),
+                                min(lo, hi), max(lo, hi), pos(self.pressure_step, 0.12), max(int(self.window), 1))
+
+
+@dataclass
+class MaintainerReport:
+    status: str
+    average_drift: float = 0.0
+    mean_energy: float = 0.0
+    mean_decay: float = 0.0
+    drift_peak: Optional[ChronoPeak] = None
+    energy_peak: Optional[ChronoPeak] = None
+    suggested_max_scale: Optional[float] = None
+    suggested_pressure: Optional[float] = None
+    diagnostic: str = ""
+    spiralk_script: Optional[str] = None
+
+    def should_rewrite(self) -> bool:
+        return self.status == "rewrite"
+
+
+class Maintainer:
+    """Reads the tail of a chrono timeline and decides whether the temporal dynamics are stable, dormant (no energy),
+    need a clamp (curvature jitter or a strong drift harmonic) or a rewrite (energy growth or a strong energy harmonic),
+    with a suggested scale clamp and pressure.  Parity: crates/st-core/src/telemetry/maintainer.rs:108-265."""
+
+    def __init__(self, config: Optional[MaintainerConfig] = None):
+        self.config = (config or MaintainerConfig()).sanitise()
+
+    def assess(self, frames: Sequence[ChronoFrame]) -> MaintainerReport:
+        frames = list(frames)
+        c = self.config
+        if not frames:
+            return self._emit(0, 0, MaintainerReport("dormant", diagnostic="No temporal frames recorded; timeline is dormant."))
+        tail = frames[-max(min(c.window, len(frames)), 1):]
+        s = chrono_summary_from_frames(tail)
+        h = ChronoHarmonics.from_frames(tail, 16)
+        dpk, epk = (h.dominant_drift if h else None), (h.dominant_energy if h else None)
+        growth = max(-s.mean_decay, 0.0)
+        status = "dormant" if s.mean_energy <= c.energy_floor else "stable"
+        reasons, scale, pressure = [], None, None
+        if s.mean_abs_drift > c.jitter_threshold:
+            status = "clamp"
+            scale = _clampf(c.clamp_min + s.mean_abs_drift / (c.jitter_threshold + 1.1920929e-07), c.clamp_min, c.clamp_max)
+            reasons.append(f"curvature jitter {s.mean_abs_drift:.3f} exceeds threshold {c.jitter_threshold:.3f}")
+        if growth > c.growth_threshold:
+            status = "rewrite"
+            pressure = min(c.pressure_step * (1.0 + growth / c.growth_threshold), 1.0)
+            reasons.append(f"energy growth {growth:.3f} exceeds threshold {c.growth_threshold:.3f}")
+        elif status == "clamp":
+            pressure = min(c.pressure_step * (1.0 + s.mean_abs_drift / c.jitter_threshold), 1.0)
+        if dpk is not None and dpk.magnitude > c.jitter_threshold:
+            status = "clamp"
+            reasons.append(f"drift harmonic {dpk.frequency:.2f}Hz magnitude {dpk.magnitude:.3f}")
+            scale = scale if scale is not None else c.clamp_max
+        if epk is not None and epk.magnitude > c.growth_threshold:
+            status = "rewrite"
+            reasons.append(f"energy harmonic {epk.frequency:.2f}Hz magnitude {epk.magnitude:.3f}")
+            pressure = min(c.pressure_step * (1.0 + epk.magnitude / c.growth_threshold), 1.0)
+        if not reasons:
+            reasons.append(f"timeline energy below floor; drift {s.mean_abs_drift:.3f}±{s.drift_std:.3f}" if status == "dormant" else
+                           f"temporal dynamics within expected range (drift {s.mean_abs_drift:.3f}±{s.drift_std:.3f}, "
+                           f"energy {s.mean_energy:.3f}±{s.energy_std:.3f})")
+        return self._emit(len(frames), len(tail), MaintainerReport(status, s.mean_abs_drift, s.mean_energy, s.mean_decay, dpk, epk, scale, pressure,
+                                                                   "; ".join(reasons), ChronoLoopSignal(s, h).spiralk_script))
+
+    @staticmethod
+    def _emit(frames: int, window: int, report: MaintainerReport) -> MaintainerReport:
+        from . import observability
+        observability.emit_tensor_op("timeline_maintainer_assessment", (frames, window), (1, 8))
+        observability.emit_tensor_op_meta("timeline_maintainer_assessment", lambda: {
+            "backend": "host", "kind": "timeline_maintainer_assessment", "frames": frames, "window": window, "status": report.status,
+            "average_drift": report.average_drift, "mean_energy": report.mean_energy, "mean_decay": report.mean_decay,
+            "should_rewrite": report.should_rewrite(), "has_suggested_max_scale": report.suggested_max_scale is not None,
+            "has_suggested_pressure": report.suggested_pressure is not None})
+        return report
+
+
 # ---- device-timed step metrics ----------------------------------------------------------------------
 class StepTimer:
     """Measures a training step with CUDA events on the current stream (wall clock on CPU) and
@@ -539,10 +842,60 @@ class AtlasFrame:
     districts: Dict[str, str] = field(default_factory=dict)      # explicit district per metric
     notes: List[str] = field(default_factory=list)
     concepts: List[tuple] = field(default_factory=list)          # (term, sense)
+    chrono_summary: Optional["ChronoSummary"] = None
+    harmonics: Optional[object] = None
+    maintainer_status: Optional[str] = None
+    maintainer_diagnostic: Optional[str] = None
+    suggested_max_scale: Optional[float] = None
+    suggested_pressure: Optional[float] = None
 
     def __post_init__(self):
         if not math.isfinite(self.timestamp):
             self.timestamp = 0.0
+
+    @classmethod
+    def from_fragment(cls, fragment: "AtlasFragment") -> Optional["AtlasFrame"]:
+        if fragment.is_empty():
+            return None
+        frame = cls(0.0)
+        frame.merge_fragment(fragment)
+        return frame if frame.timestamp > 0.0 else None
+
+    def merge_fragment(self, fragment: "AtlasFragment") -> None:
+        """Folds a producer's partial view in: the timestamp only moves forward, loop support accumulates, scalars and
+        texts are replaced when the fragment carries a usable value, metrics replace by name, notes and concepts are
+        appended once.  Parity: crates/st-core/src/telemetry/atlas.rs:337-409."""
+        if fragment.is_empty():
+            return
+        ts = fragment.timestamp if fragment.timestamp is not None else (fragment.summary.latest_timestamp if fragment.summary else None)
+        if ts is not None and math.isfinite(ts):
+            self.timestamp = max(ts, 1.1920929e-07) if self.timestamp <= 0.0 else max(self.timestamp, ts)
+        if fragment.summary is not None:
+            self.chrono_summary = fragment.summary
+        if fragment.harmonics is not None:
+            self.harmonics = fragment.harmonics
+        if fragment.loop_support is not None and math.isfinite(fragment.loop_support):
+            self.loop_support += max(fragment.loop_support, 0.0)
+        for name in ("collapse_total", "z_signal", "suggested_max_scale", "suggested_pressure"):
+            v = getattr(fragment, name)
+            if v is not None and math.isfinite(v):
+                setattr(self, name, float(v))
+        for name in ("script_hint", "maintainer_diagnostic"):
+            v = getattr(fragment, name)
+            if v is not None and v.strip():
+                setattr(self, name, v.strip())
+        if fragment.maintainer_status is not None:
+            self.maintainer_status = fragment.maintainer_status
+        for name, value, district in fragment.metrics:
+            self.push_metric(name, value, district)
+        for note in fragment.notes:
+            if note not in self.notes:
+                self.notes.append(note)
+        for concept in fragment.concepts:
+            if concept not in self.concepts:
+                self.concepts.append(concept)
+        if self.timestamp <= 0.0:
+            self.timestamp = 1.1920929e-07
 
     def push_metric(self, name: str, value: float, district: Optional[str] = None) -> None:
         if math.isfinite(value):
@@ -558,6 +911,43 @@ class AtlasFrame:
 
     def district_of(self, name: str) -> str:
         return self.districts.get(name) or infer_district(name)
+
+
+@dataclass
+class AtlasFragment:
+    """What one producer knows about the current atlas frame."""
+    timestamp: Optional[float] = None
+    summary: Optional["ChronoSummary"] = None
+    harmonics: Optional[object] = None
+    loop_support: Optional[float] = None
+    collapse_total: Optional[float] = None
+    z_signal: Optional[float] = None
+    script_hint: Optional[str] = None
+    maintainer_status: Optional[str] = None
+    maintainer_diagnostic: Optional[str] = None
+    suggested_max_scale: Optional[float] = None
+    suggested_pressure: Optional[float] = None
+    metrics: List[tuple] = field(default_factory=list)          # (name, value, district or None)
+    notes: List[str] = field(default_factory=list)
+    concepts: List[tuple] = field(default_factory=list)
+
+    def is_empty(self) -> bool:
+        scalars = (self.timestamp, self.summary, self.harmonics, self.loop_support, self.collapse_total, self.z_signal, self.script_hint,
+                   self.maintainer_status, self.maintainer_diagnostic, self.suggested_max_scale, self.suggested_pressure)
+        return all(v is None for v in scalars) and not self.metrics and not self.notes and not self.concepts
+
+    def push_metric(self, name: str, value: float, district: Optional[str] = None) -> None:
+        name = str(name).strip()
+        if name and isinstance(value, (int, float)) and math.isfinite(value):
+            self.metrics.append((name, float(value), district))
+
+    def push_note(self, note: str) -> None:
+        note = str(note).strip()
+        if note:
+            self.notes.append(note)
+
+    def push_concept(self, term: str, sense: str) -> None:
+        self.concepts.append((term, sense))
 
 
 class AtlasRoute:
