@@ -94,12 +94,20 @@ struct StAgGemmArgs {
   unsigned long long trace;  // optional device buffer of [3 * grid][4] 64-bit time stamps, or 0
   int stages;                // 0: choose by world size; 3 or 4: force that operand-pipeline depth
   int local_in_place;        // x_shard IS this rank's slot of its own gather buffer: nothing is copied locally
+  int max_ctas;              // 0: one CTA per SM; > 0: a smaller grid, which leaves SMs to a concurrent kernel.  Every
+                             // rank must pass the same value: the grid is also the arrival count per counter.
 };
 
 // Arrivals every (source, sub-chunk) counter receives per launch: one per CTA of the grid.
 ST_API int st_ag_arrivals_per_launch() {
   const int sms = st::sm_count();
   return sms > 0 ? sms : 148;
+}
+
+// The same for a launch whose grid is limited to `max_ctas` (0 = no limit).
+ST_API int st_ag_arrivals_for(int max_ctas) {
+  const int full = st_ag_arrivals_per_launch();
+  return max_ctas > 0 && max_ctas < full ? max_ctas : full;
 }
 
 ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
@@ -144,7 +152,7 @@ ST_API int st_ag_gemm(const StAgGemmArgs* a, void* stream_v) {
   cm.src_shard = reinterpret_cast<const __nv_bfloat16*>(a->x_shard);
   for (int i = 0; i < st::kMaxRanks; ++i) cm.gather_peers[i] = reinterpret_cast<__nv_bfloat16*>(a->gather_peers[i]);
   cm.gather_mc = reinterpret_cast<__nv_bfloat16*>(a->gather_mc);
-  const int grid = st_ag_arrivals_per_launch();   // every SM pushes, whether or not it has tiles
+  const int grid = st_ag_arrivals_for(a->max_ctas);   // every CTA pushes, whether or not it has tiles
   cm.gemm_ctas = grid;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   OutMaps tmC;
@@ -196,6 +204,7 @@ struct StGemmRsArgs {
   int groups;                                    // row-block groups per chunk for the remote / local interleave;
                                                  // 0 = choose (up to 8), 1 = all remote tiles first, local last
   int lag;                                       // groups by which a local group trails its remote group (0 = 1)
+  int max_ctas;                                  // 0: one CTA per SM; > 0: a smaller grid (SMs left to a concurrent kernel)
 };
 
 ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
@@ -241,6 +250,7 @@ ST_API int st_gemm_rs(const StGemmRsArgs* a, void* stream_v) {
   cm.rs_residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
   const int tiles = (a->T / BM) * ((a->N + BN - 1) / BN);
   int grid = st::sm_count();
+  if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
   if (grid > tiles) grid = tiles;
   cm.gemm_ctas = grid;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);

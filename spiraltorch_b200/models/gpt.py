@@ -24,6 +24,7 @@ description: d_model 2048, 24 layers, 16 heads, FFN 8192, vocab 50304, sequence 
 from __future__ import annotations
 
 import math
+import os
 import zlib
 from dataclasses import dataclass, asdict
 from typing import Optional
@@ -95,6 +96,16 @@ class GPTModel(nn.Module):
         self._fused_tp = type(self.tp).__name__ == "FusedTPContext" and torch.device(device).type == "cuda"
         W = self.tp.world
         assert cfg.n_heads % W == 0 and cfg.ffn % W == 0 and cfg.vocab_size % W == 0
+        # Weight-gradient GEMMs need no communication.  When the fused linears are link-bound (many ranks, thin
+        # per-rank GEMMs) they can run beside them: the backward pass launches its fused kernels on a grid that
+        # leaves `_wgrad_ctas` SMs free and queues the weight gradients on a second stream, limited to those SMs.
+        # ST_TP_WGRAD_OVERLAP=0/1 forces it off / on; ST_TP_WGRAD_CTAS sets the share (default 40 of 148).
+        self._wgrad_ctas, self._wgrad_stream, self._wgrad_guard = 0, None, {}
+        if self._fused_tp:
+            env = os.environ.get("ST_TP_WGRAD_OVERLAP")
+            if (W >= 6) if env is None else env == "1":
+                self._wgrad_ctas = int(os.environ.get("ST_TP_WGRAD_CTAS", "40"))
+                self._wgrad_stream = torch.cuda.Stream(torch.device(device))
         assert cfg.head_dim in (64, 128), "attention kernels support head_dim 64 and 128"
         self.heads_local = cfg.n_heads // W
         self.ffn_local = cfg.ffn // W
@@ -204,21 +215,56 @@ class GPTModel(nn.Module):
             act.h2, act.stat2, act.y2_full, act.u, act.a = h2, (m2, r2), y2_full, u, a
         return h2, mlp_out, act
 
+    def _wgrads(self, jobs, gather_keys=()):
+        """``out += a^T b`` for every ``(a, b, out)``.  With the overlap on, the products are queued on the side stream
+        (after everything the main stream has launched so far) and `gather_keys` names the gather buffers they read:
+        the next all-gather into one of those waits for them."""
+        g = gemm_ops.gemm
+        if not self._wgrad_ctas:
+            for a, b, out in jobs:
+                g(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
+            return
+        side, main = self._wgrad_stream, torch.cuda.current_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for a, b, out in jobs:
+                g(a, b, a_mn=True, b_mn=True, out=out, accumulate=True, max_ctas=self._wgrad_ctas)
+                a.record_stream(side)
+                b.record_stream(side)
+            done = torch.cuda.Event()
+            done.record(side)
+        for k in gather_keys:
+            self._wgrad_guard[k] = done
+
+    def _wgrad_wait(self, key) -> None:
+        """Before the gather buffer `key` is written again: the weight gradients that still read it must be done."""
+        ev = self._wgrad_guard.pop(key, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _wgrad_join(self) -> None:
+        if self._wgrad_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._wgrad_stream)
+            self._wgrad_guard.clear()
+
     def _layer_backward(self, l: int, act: _Act, d_out, B: int, S: int):
-        """``d_out`` is the gradient w.r.t. both outputs (h2 and mlp_out) of the layer."""
+        """``d_out`` is the gradient w.r.t. both outputs (h2 and mlp_out) of the layer.  Its gather buffers alternate
+        with the layer's parity, so that the weight gradients of one layer may still read theirs while the next
+        layer's all-gathers already fill the other pair."""
         cfg, tp, hl, D = self.cfg, self.tp, self.heads_local, self.cfg.head_dim
         P = self.p
-        g = gemm_ops.gemm
         w1, w2 = P[f"h{l}.fc1.weight"], P[f"h{l}.fc2.weight"]
         wqkv, wo = P[f"h{l}.qkv.weight"], P[f"h{l}.proj.weight"]
-        du, dmlp_full = tp.ag_gemm(d_out, w2, b_mn=True, key="bwd_mlp", act="gelu_bwd", aux_in=act.u)
-        g(dmlp_full, act.a, a_mn=True, b_mn=True, out=w2.main_grad, accumulate=True)
-        g(du, act.y2_full, a_mn=True, b_mn=True, out=w1.main_grad, accumulate=True)
+        k_mlp, k_attn = ("bwd_mlp", l & 1), ("bwd_attn", l & 1)
+        self._wgrad_wait(k_mlp)
+        du, dmlp_full = tp.ag_gemm(d_out, w2, b_mn=True, key=k_mlp, act="gelu_bwd", aux_in=act.u)
+        self._wgrads([(dmlp_full, act.a, w2.main_grad), (du, act.y2_full, w1.main_grad)], (k_mlp,))
         dy2 = tp.gemm_rs(du, w1, b_mn=True)
-        d_h2 = self._norm_bwd(dy2, act.h2, act.stat2, f"h{l}.norm2", dres=d_out, gather_key="bwd_attn")
+        self._wgrad_wait(k_attn)
+        d_h2 = self._norm_bwd(dy2, act.h2, act.stat2, f"h{l}.norm2", dres=d_out, gather_key=k_attn)
         o2 = act.o.view(B * S, hl * D)
-        do, dh2_full = tp.ag_gemm(d_h2, wo, b_mn=True, key="bwd_attn")
-        g(dh2_full, o2, a_mn=True, b_mn=True, out=wo.main_grad, accumulate=True)
+        do, dh2_full = tp.ag_gemm(d_h2, wo, b_mn=True, key=k_attn)
+        self._wgrads([(dh2_full, o2, wo.main_grad)], (k_attn,))
         dqkv = torch.empty_like(act.qkv)
         qkv5, dqkv5 = act.qkv.view(B, S, 3, hl, D), dqkv.view(B, S, 3, hl, D)
         attn_ops.attention_backward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], act.o, act.lse,
@@ -226,11 +272,13 @@ class GPTModel(nn.Module):
                                     dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
         if cfg.positional == "rope":
             ew.rope_(dqkv, 2 * hl, D, S, cfg.rope_base, backward=True)
-        g(dqkv, act.y1_full, a_mn=True, b_mn=True, out=wqkv.main_grad, accumulate=True)
+        self._wgrads([(dqkv, act.y1_full, wqkv.main_grad)])
         dy1 = tp.gemm_rs(dqkv, wqkv, b_mn=True)
-        # the result is the next layer's `d_out`, which its first all-gather (key "bwd_mlp") pushes
-        return self._norm_bwd(dy1, act.h1, act.stat1, f"h{l}.norm1", dres=d_h2,
-                              gather_key="bwd_mlp" if l > 0 else None)
+        # the result is the next layer's `d_out`, which its first all-gather pushes
+        nxt = ("bwd_mlp", (l - 1) & 1)
+        if l > 0:
+            self._wgrad_wait(nxt)
+        return self._norm_bwd(dy1, act.h1, act.stat1, f"h{l}.norm1", dres=d_h2, gather_key=nxt if l > 0 else None)
 
     # ------------------------------------------------------------------------------------------
     def _forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor], loss_scale: float,
@@ -280,17 +328,25 @@ class GPTModel(nn.Module):
         if dloss is not None:
             coef = coef * dloss.to(torch.float32).reshape(1)
         dlogits = loss_ops._grad_(logits, tgt, lse, coef.contiguous(), 1.0, self.vocab_start)
-        g = gemm_ops.gemm
-        g(dlogits, yf_full, a_mn=True, b_mn=True, out=emb.main_grad, accumulate=True)
-        dyf = tp.gemm_rs(dlogits, emb, b_mn=True)
-        d = self._norm_bwd(dyf, hf, statf, "norm_f", gather_key="bwd_mlp")
-        for l in reversed(range(cfg.n_layers)):
-            d = self._layer_backward(l, acts[l], d, B, S)
-            acts[l] = None
-            if self._fused_tp and native.error_pending():
-                native.raise_on_device_error()
-            if self.grad_ready_hook is not None:
-                self.grad_ready_hook(f"h{l}")
+        overlap = self._wgrad_ctas > 0
+        if overlap:
+            tp.max_ctas = max(torch.cuda.get_device_properties(dlogits.device).multi_processor_count - self._wgrad_ctas, 1)
+        try:
+            self._wgrads([(dlogits, yf_full, emb.main_grad)])
+            dyf = tp.gemm_rs(dlogits, emb, b_mn=True)
+            d = self._norm_bwd(dyf, hf, statf, "norm_f", gather_key=("bwd_mlp", (cfg.n_layers - 1) & 1))
+            for l in reversed(range(cfg.n_layers)):
+                d = self._layer_backward(l, acts[l], d, B, S)
+                acts[l] = None
+                if self._fused_tp and native.error_pending():
+                    native.raise_on_device_error()
+                if self.grad_ready_hook is not None:
+                    self._wgrad_join()
+                    self.grad_ready_hook(f"h{l}")
+        finally:
+            if overlap:
+                tp.max_ctas = 0
+        self._wgrad_join()              # the embedding gradient below and the optimizer read what the side stream wrote
         d_full = tp.all_gather_rows(d)
         dpos = pos.main_grad if pos is not None else None
         ew.embedding_backward(tokens, d_full.contiguous(), emb.main_grad, dpos, S, self.vocab_start)

@@ -50,7 +50,8 @@ class _AgGemmArgs(ctypes.Structure):
                 ("b_mn", ctypes.c_int), ("act", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("sub_per_chunk", ctypes.c_int), ("comm_ctas", ctypes.c_int),
                 ("slot_enter", ctypes.c_int), ("slot_arrive", ctypes.c_int), ("arrive_target", ctypes.c_uint),
-                ("trace", ctypes.c_ulonglong), ("stages", ctypes.c_int), ("local_in_place", ctypes.c_int)]
+                ("trace", ctypes.c_ulonglong), ("stages", ctypes.c_int), ("local_in_place", ctypes.c_int),
+                ("max_ctas", ctypes.c_int)]
 
 
 class _GemmRsArgs(ctypes.Structure):
@@ -60,7 +61,7 @@ class _GemmRsArgs(ctypes.Structure):
                 ("T", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn", ctypes.c_int),
                 ("alpha", ctypes.c_float), ("slot_enter", ctypes.c_int), ("slot_done", ctypes.c_int),
                 ("done_target", ctypes.c_uint), ("stage_mc", ctypes.c_ulonglong),
-                ("trace", ctypes.c_ulonglong), ("groups", ctypes.c_int), ("lag", ctypes.c_int)]
+                ("trace", ctypes.c_ulonglong), ("groups", ctypes.c_int), ("lag", ctypes.c_int), ("max_ctas", ctypes.c_int)]
 
 
 class _DpStepArgs(ctypes.Structure):
@@ -204,6 +205,7 @@ class FusedTPContext(TPContext):
         self.ag_stages = int(os.environ.get("ST_TP_AG_STAGES", "0"))   # 0 = by world size
         self.rs_groups = int(os.environ.get("ST_TP_RS_GROUPS", "0"))   # 0 = chosen by the launcher, 1 = no interleave
         self.rs_lag = int(os.environ.get("ST_TP_RS_LAG", "0"))         # 0 = one group
+        self.max_ctas = 0       # grid limit of the next fused launches (0 = one CTA per SM); the same on every rank
         self.trace: Optional[torch.Tensor] = None     # int64 [>= SMs, 4]: per-CTA phase time stamps (debug)
         self._done_slots: dict[int, tuple[int, int]] = {}   # row blocks → (slot, cumulative target)
         self._gather: dict = {}
@@ -300,7 +302,8 @@ class FusedTPContext(TPContext):
         a.trace = 0 if self.trace is None else self.trace.data_ptr()
         a.stages = self.ag_stages
         a.local_in_place = int(in_place)
-        self._ag_arrivals[sub] += native.lib().st_ag_arrivals_per_launch()
+        a.max_ctas = int(self.max_ctas)
+        self._ag_arrivals[sub] += native.lib().st_ag_arrivals_for(ctypes.c_int(a.max_ctas))
         a.slot_arrive, a.arrive_target = self.slot_arrive[sub], self._ag_arrivals[sub] & 0xFFFFFFFF
         native.check(native.lib().st_ag_gemm(ctypes.byref(a), native.stream_ptr(x_shard.device)), "st_ag_gemm")
         launch_count += 1
@@ -343,6 +346,7 @@ class FusedTPContext(TPContext):
         r.done_target = (cum + _withhold) & 0xFFFFFFFF
         r.stage_mc = 0
         r.groups, r.lag = self.rs_groups, self.rs_lag
+        r.max_ctas = int(self.max_ctas)
         r.trace = 0 if self.trace is None else self.trace.data_ptr()
         native.check(lib.st_gemm_rs(ctypes.byref(r), native.stream_ptr(a_full.device)), "st_gemm_rs")
         launch_count += 1

@@ -240,8 +240,37 @@ def main():
         r = ((ma.flat_grad - mb.flat_grad).norm() / ma.flat_grad.norm()).item()
         assert r < 3e-2, r
 
+    def sec_gpt_wgrad_overlap():
+        # the same comparison with the weight gradients on the side stream beside grid-limited fused kernels
+        # (forced on: by default only link-bound world sizes use it); four layers exercise both buffer parities
+        cfg = GPTConfig(vocab_size=1024, d_model=512, n_layers=4, n_heads=8, ffn=1024, seq_len=512, init_std=0.05)
+        ma = GPTModel(cfg, device=dev, seed=7, tp=nccl)
+        prev = os.environ.get("ST_TP_WGRAD_OVERLAP")
+        os.environ["ST_TP_WGRAD_OVERLAP"] = "1"
+        try:
+            mb = GPTModel(cfg, device=dev, seed=7, tp=fused)
+        finally:
+            if prev is None:
+                del os.environ["ST_TP_WGRAD_OVERLAP"]
+            else:
+                os.environ["ST_TP_WGRAD_OVERLAP"] = prev
+        assert mb._wgrad_ctas > 0 and ma._wgrad_ctas == 0
+        gen = torch.Generator().manual_seed(13)
+        tokens = torch.randint(0, 1024, (2 * world, 512), generator=gen).to(dev)
+        targets = torch.randint(0, 1024, (2 * world, 512), generator=gen).to(dev)
+        for _ in range(3):
+            la = ma.forward_backward(tokens, targets)
+            lb = mb.forward_backward(tokens, targets)
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        assert fused.max_ctas == 0
+        assert abs(la.item() - lb.item()) < 2e-2, (la.item(), lb.item())
+        r = ((ma.flat_grad - mb.flat_grad).norm() / ma.flat_grad.norm()).item()
+        assert r < 3e-2, r
+
     if not only_bench:
         sec.run("gpt", sec_gpt)
+        sec.run("gpt_wgrad_overlap", sec_gpt_wgrad_overlap)
 
     def sec_info_nce():
         from spiraltorch_b200.parallel.contrastive import FusedInfoNCE
