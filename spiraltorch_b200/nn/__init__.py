@@ -2,7 +2,7 @@
 from .amp import (AutocastGuard, CoherenceSignal, CurvatureDecision, CurvatureScheduler, GradScaler, OptimizerMode,
                   SpectralAdjustment, SpectralLearningRatePolicy, SpectralLrAdapter, WarmupCosineScheduler,
                   ZSpaceParameterOptimizer, autocast_enabled)
-from .data import DataLoader, Dataset, from_samples
+from .data import DataLoader, DataLoaderIter, Dataset, from_samples
 from .io import load, load_bincode, load_json, save, save_bincode, save_json
 from .losses import (CategoricalCrossEntropy, ContrastiveLoss, CrossEntropy, FocalLoss, HyperbolicCrossEntropy,
                      Loss, MeanSquaredError, SoftmaxCrossEntropy, TripletLoss)
@@ -15,6 +15,7 @@ from .trainer import EpochStats, ModuleTrainer, RoundtableConfig, RoundtableSche
 from . import amp, coherence, conv, fields, gnn, graph, lightning, roundtable, zrba, zspace
 from .graph import GraphedTrainStep
 from .zrelativity import ZRelativityModule
+py_is_swap_invariant = None  # bound below, once the coherence names are imported
 from .roundtable import DistConfig, MetaConductor, MetaSummary, RoundtableNode
 from .conv import AvgPool2d, Conv2d, Conv3d, Conv4d, Conv6da, MaxPool2d, WaveScan, ZConv6DA
 from .fields import (ContinuousWavelet, Conv1d, DynamicHamiltonJacobiField, DynamicKleinGordonField,
@@ -38,3 +39,5 @@ from ..desire_pipeline import (DesirePipeline, DesirePsiBridge, DesirePsiEvent, 
 
 NnModuleTrainer = ModuleTrainer          # the binding registers the trainer under both names
 from ..runtime.golden import GoldenRetriever  # noqa: E402  (multi-trainer lives with the host runtime)
+
+py_is_swap_invariant = is_swap_invariant          # the name the reference's binding registers (bindings/st-py/src/nn.rs:80)

@@ -108,7 +108,12 @@ class DataLoader:
                 xs, ys = xs.to(dev), ys.to(dev)
         return xs, ys
 
-    def __iter__(self) -> Iterator[tuple[Tensor, Tensor]]:
+    def __iter__(self) -> "DataLoaderIter":
+        return DataLoaderIter(self._batches())
+
+    iter = __iter__
+
+    def _batches(self) -> Iterator[tuple[Tensor, Tensor]]:
         if self._prefetch <= 0:
             for g in self._groups():
                 yield self._make(g)
@@ -132,3 +137,17 @@ class DataLoader:
             if isinstance(item, BaseException):
                 raise item
             yield item
+
+
+class DataLoaderIter:
+    """One pass over a loader's batches (bindings/st-py/src/nn.rs:8915-8940: ``iter(loader)`` returns this object; it is its
+    own iterator and raises `StopIteration` when the pass is over)."""
+
+    def __init__(self, batches: Iterator[tuple[Tensor, Tensor]]):
+        self._batches = batches
+
+    def __iter__(self) -> "DataLoaderIter":
+        return self
+
+    def __next__(self) -> tuple[Tensor, Tensor]:
+        return next(self._batches)

@@ -434,3 +434,17 @@ def test_hf_bridge_round_trip_and_lora():
     assert torch.allclose(HB.merge_lora(lora), base + delta, atol=1e-4)
     with pytest.raises(ValueError):
         HB.attach_lora_factors(lora, torch.zeros(3, 6), torch.zeros(4, 3))
+
+
+def test_loader_iteration_object_and_binding_alias():
+    import spiraltorch_b200 as st
+    samples = [(st.Tensor(1, 1, [float(i)]), st.Tensor(1, 1, [float(2 * i)])) for i in range(5)]
+    loader = st.nn.from_samples(samples).loader().batched(2)
+    it = iter(loader)
+    assert isinstance(it, st.nn.DataLoaderIter) and iter(it) is it and isinstance(loader.iter(), st.nn.DataLoaderIter)
+    x, y = next(it)
+    assert x.shape() == (2, 1) and y.tolist() == [[0.0], [2.0]]
+    assert len(list(it)) == 2 and len(list(loader)) == 3                # a new pass per iter(); the old one is exhausted
+    with __import__("pytest").raises(StopIteration):
+        next(it)
+    assert st.nn.py_is_swap_invariant is st.nn.is_swap_invariant
