@@ -392,6 +392,42 @@ def bench_scan(iters, profile):
     return out
 
 
+def bench_spectral(iters, profile):
+    """Spectral kernels: batched shared-memory FFT against cuFFT (`torch.fft.fft`), the fractional multiplier against
+    its elementwise torch statement, and the temporal volume renderer against an einsum statement."""
+    from spiraltorch_b200.ops import spectral as S
+    out = []
+    rows, n = (8192, 4096) if profile else (16384, 4096)                 # complex64 [rows, n]: 0.5 GiB in + 0.5 GiB out at full size
+    x = torch.randn(rows, n, dtype=torch.complex64, device=DEV)
+    xr = torch.randn(rows, n, device=DEV)
+    V, C, F = 1 << 22, 4, 16                                             # 100 MB in, 268 MB out
+    vox, harm, decay = torch.rand(V, device=DEV), torch.rand(V, C, device=DEV) * 0.1, torch.rand(V, device=DEV)
+    if profile:
+        for _ in range(2):
+            S.fft(x)
+            S.specmul_frac_derivative(x, 0.5)
+            S.temporal_render(vox, harm, decay, F)
+        torch.cuda.synchronize()
+        return []
+    bytes_fft = 2.0 * rows * n * 8
+    out.append(row("fft_c2c_4096", f"{rows}x{n}", timed(lambda: S.fft(x), iters), timed(lambda: torch.fft.fft(x), iters), bytes_=bytes_fft))
+    out.append(row("fft_r2c_full_4096", f"{rows}x{n}", timed(lambda: S.fft(xr), iters), timed(lambda: torch.fft.fft(xr), iters),
+                   bytes_=rows * n * 4.0 + rows * n * 8.0))
+    omega = 2 * math.pi * torch.fft.fftfreq(n, device=DEV)
+    mult = torch.where(omega == 0, torch.zeros_like(omega, dtype=torch.complex64), (1j * omega.to(torch.complex64)) ** 0.5)
+    out.append(row("specmul_frac_derivative", f"{rows}x{n}", timed(lambda: S.specmul_frac_derivative(x, 0.5), iters),
+                   timed(lambda: x * mult, iters), bytes_=bytes_fft))
+    t = torch.arange(F, device=DEV, dtype=torch.float32) / 24.0
+    k = torch.arange(1, C + 1, device=DEV, dtype=torch.float32)
+
+    def torch_render():
+        s = torch.sin(2 * math.pi * t[:, None, None] * k[None, None, :])               # [F, 1, C]
+        return (vox[None] + (harm[None] * s).sum(-1)) * torch.exp(-decay[None] * t[:, None])
+    out.append(row("temporal_render", f"V{V} C{C} F{F}", timed(lambda: S.temporal_render(vox, harm, decay, F), iters), timed(torch_render, iters),
+                   bytes_=V * (C + 2) * 4.0 + V * F * 4.0))
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernels", nargs="*", default=["gemm", "attn_fwd", "attn_bwd", "conv", "norm", "adamw", "ce"])
@@ -410,7 +446,8 @@ def main() -> int:
              "transforms": lambda: bench_transforms(args.iters, args.profile),
              "layers": lambda: bench_layers(args.iters, args.profile),
              "fused": lambda: bench_fused(args.iters, args.profile),
-             "scan": lambda: bench_scan(args.iters, args.profile)}
+             "scan": lambda: bench_scan(args.iters, args.profile),
+             "spectral": lambda: bench_spectral(args.iters, args.profile)}
     rows = []
     for k in args.kernels:
         rows += table[k]()

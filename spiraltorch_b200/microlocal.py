@@ -4,14 +4,13 @@ fuse the pulses of several gauges through the Z conductor.
 Parity: crates/st-core/src/theory/microlocal.rs — `InterfaceGauge::analyze*` (:58-240: per cell the largest one-sided
 difference, the interface flag against the threshold, the second-difference vector, the boundary-aware Laplacian, the
 bounded mean curvature, the label-signed curvature and the unit orientation), `MicrolocalGaugeBank` (:242-345),
-`InterfaceZLift::project` (:399-575, the branch without an elliptic warp), `InterfaceZPulse::{aggregate, lerp, scaled,
+`InterfaceZLift::project` (:399-575), `InterfaceZPulse::{aggregate, lerp, scaled,
 into_softlogic_feedback}` (:577-757), `MicrolocalFeedback` (:806-900), quality policies `Default / Fixed / Composite /
 Band / Budget` (:900-1082), `InterfaceZConductor::{apply_feedback, step}` (:1119-1440).
 
 The gauge is a stencil over the whole mask: here it is a handful of shifted tensor differences on whichever device holds
-the mask (any number of dimensions), not a loop over cells.  The elliptic-warp refinement of the lift (a curved
-chart of the orientation with sheet / spin telemetry) is not built; `reinforce_positive_curvature` installs its band
-policy only.
+the mask (any number of dimensions), not a loop over cells.  With an `EllipticWarp` on the lift the mean orientation is
+read on a curved chart (`elliptic.py`) and its sheet / spin / heat telemetry shapes the bands and the bias.
 """
 from __future__ import annotations
 
@@ -23,6 +22,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from . import observability
+from .elliptic import EllipticAccumulator, EllipticTelemetry, EllipticWarp
 from .hub import SoftlogicZFeedback
 from .theory import LeechProjector
 from .zpulse import ZConductor, ZEmitter, ZPulse, ZRegistry, ZScale, ZSupport, source_label
@@ -175,6 +175,7 @@ class InterfaceZPulse:
     z_bias: float = 0.0
     quality_hint: Optional[float] = None
     standard_error: Optional[float] = None
+    elliptic: Optional[EllipticTelemetry] = None
 
     def total_energy(self) -> float:
         return sum(self.band_energy)
@@ -197,9 +198,14 @@ class InterfaceZPulse:
         total = sum(w)
         scale = ZScale.weighted_average((p.scale, wi) for p, wi in zip(pulses, w) if p.scale is not None) \
             or next((p.scale for p in reversed(pulses) if p.scale is not None), None) or ZScale.ONE
+        acc = EllipticAccumulator()
+        for p, wi in zip(pulses, w):
+            if p.elliptic is not None:
+                acc.accumulate(p.elliptic, wi)
         return InterfaceZPulse("microlocal", sum(p.support for p in pulses), sum(p.interface_cells for p in pulses),
                                tuple(sum(p.band_energy[i] for p in pulses) for i in range(3)), scale,
-                               sum(p.drift * wi for p, wi in zip(pulses, w)) / total, sum(p.z_bias * wi for p, wi in zip(pulses, w)) / total)
+                               sum(p.drift * wi for p, wi in zip(pulses, w)) / total, sum(p.z_bias * wi for p, wi in zip(pulses, w)) / total,
+                               elliptic=acc.finish())
 
     @staticmethod
     def lerp(current: "InterfaceZPulse", nxt: "InterfaceZPulse", alpha: float) -> "InterfaceZPulse":
@@ -209,7 +215,8 @@ class InterfaceZPulse:
         return InterfaceZPulse(nxt.source, mix(current.support, nxt.support), mix(current.interface_cells, nxt.interface_cells),
                                tuple(mix(a, b) for a, b in zip(current.band_energy, nxt.band_energy)), scale, mix(current.drift, nxt.drift),
                                mix(current.z_bias, nxt.z_bias), nxt.quality_hint if nxt.quality_hint is not None else current.quality_hint,
-                               nxt.standard_error if nxt.standard_error is not None else current.standard_error)
+                               nxt.standard_error if nxt.standard_error is not None else current.standard_error,
+                               current.elliptic.lerp(nxt.elliptic, t) if current.elliptic and nxt.elliptic else (current.elliptic or nxt.elliptic))
 
     def scaled(self, gain: float) -> "InterfaceZPulse":
         g = max(gain, 0.0)
@@ -217,18 +224,30 @@ class InterfaceZPulse:
                        band_energy=tuple(b * g for b in self.band_energy), drift=self.drift * g, z_bias=self.z_bias * g)
 
     def into_softlogic_feedback(self, psi_total: float = 0.0, weighted_loss: float = 0.0) -> SoftlogicZFeedback:
-        return SoftlogicZFeedback(psi_total, weighted_loss, tuple(self.band_energy), self.drift, self.z_bias, self.scale)
+        return SoftlogicZFeedback(psi_total, weighted_loss, tuple(self.band_energy), self.drift, self.z_bias, self.scale,
+                                  elliptic=None if self.elliptic is None else self.elliptic.as_dict())
 
 
 class InterfaceZLift:
     """Turns a signature into a pulse: the mean variation is the "here" band, the support-weighted mean orientation along
     the first axis splits it into above / beneath, and its Leech-enriched magnitude (times the bias gain) is the bias."""
 
-    def __init__(self, weights: Sequence[float], projector: LeechProjector, bias_gain: float = 1.0):
+    def __init__(self, weights: Sequence[float], projector: LeechProjector, bias_gain: float = 1.0, elliptic: Optional[EllipticWarp] = None):
         if not len(weights):
             raise ValueError("at least one weight expected")
         norm = max(sum(weights), EPS)
         self.weights, self.projector, self._bias_gain = [w / norm for w in weights], projector, max(bias_gain, 0.0)
+        self.elliptic = elliptic
+
+    def with_elliptic_warp(self, warp: EllipticWarp) -> "InterfaceZLift":
+        self.elliptic = warp
+        return self
+
+    def set_elliptic_warp(self, warp: Optional[EllipticWarp]) -> None:
+        self.elliptic = warp
+
+    def elliptic_warp(self) -> Optional[EllipticWarp]:
+        return self.elliptic
 
     def with_bias_gain(self, gain: float) -> "InterfaceZLift":
         self._bias_gain = max(gain, 0.0)
@@ -242,7 +261,7 @@ class InterfaceZLift:
         return self._bias_gain
 
     def clone(self) -> "InterfaceZLift":
-        out = InterfaceZLift([1.0], self.projector, self._bias_gain)
+        out = InterfaceZLift([1.0], self.projector, self._bias_gain, None if self.elliptic is None else self.elliptic.clone())
         out.weights = list(self.weights)
         return out
 
@@ -251,13 +270,47 @@ class InterfaceZLift:
         support = float(r.sum())
         here = max(float(signature.raw_density.mean()) if signature.raw_density.numel() else 0.0, 0.0)
         above = beneath = bias = 0.0
+        sample = None
         if signature.orientation is not None:
-            primary = (float((signature.orientation[0] * r).sum()) / support if support > 0.0 else 0.0) * self.weights[0]
-            bias = self.projector.enrich(abs(primary)) * math.copysign(1.0, primary) * self._bias_gain if primary != 0.0 else 0.0
-            above, beneath = max(primary, 0.0) * here, max(-primary, 0.0) * here
+            o = signature.orientation
+            mean = [(float((o[a] * r).sum()) / support if support > 0.0 else 0.0) for a in range(o.shape[0])]
+            sample = self.elliptic.map_orientation(mean) if self.elliptic is not None else None
+            if sample is not None:
+                above, beneath, bias = self._elliptic_split(sample, here)
+            else:
+                primary = mean[0] * self.weights[0]
+                bias = self.projector.enrich(abs(primary)) * math.copysign(1.0, primary) * self._bias_gain if primary != 0.0 else 0.0
+                above, beneath = max(primary, 0.0) * here, max(-primary, 0.0) * here
         band = (max(above, 0.0), here, max(beneath, 0.0))
         drift = (band[0] - band[2]) / max(support, 1e-6) if support > 0.0 else 0.0
-        return InterfaceZPulse("microlocal", support, float((r > 0.5).sum()), band, ZScale.new(signature.physical_radius), drift, bias)
+        return InterfaceZPulse("microlocal", support, float((r > 0.5).sum()), band, ZScale.new(signature.physical_radius), drift, bias,
+                               elliptic=sample)
+
+    def _elliptic_split(self, s: EllipticTelemetry, here: float):
+        """Leading / trailing shares of the "here" energy and the bias on a curved chart: the distance from the pole sets
+        the base split, the sheet position, homology phase, spin, rotor focus against lateral flux, noise and resonance
+        heat tilt it, and the sector parity picks which side the heat favours (microlocal.rs:487-545)."""
+        normalized, spin = s.clamped_radius(), min(max(s.spin_alignment, -1.0), 1.0)
+        leading, trailing = max(1.0 - normalized, 0.0), max(normalized, 0.0)
+        rotor_focus = math.sqrt(abs(s.rotor_field[2]) + 1e-3)
+        lateral = (abs(s.rotor_field[0]) + abs(s.rotor_field[1])) * 0.5
+        gate = min(max(1.0 - s.noise_density, 0.05), 1.0)
+        sector_bias = 1.0 + (s.topological_sector & 0x7) * 0.05
+        phase = (s.homology_index & 0xFF) / 255.0
+        leading *= max(0.55 + 0.45 * s.sheet_position + phase * 0.2, 1e-3)
+        trailing *= max(0.55 + 0.45 * (1.0 - s.sheet_position) + (1.0 - phase) * 0.2, 1e-3)
+        leading *= max(0.5 * (1.0 + spin), 1e-3) * (1.0 + rotor_focus * 0.5) * gate
+        trailing *= max(0.5 * (1.0 - spin), 1e-3) * (1.0 + lateral * 0.5) * (1.0 - gate * 0.35)
+        even = s.topological_sector & 1 == 0
+        leading *= 1.0 + s.resonance_heat * (1.0 if even else 0.25)
+        trailing *= 1.0 + s.resonance_heat * (0.25 if even else 1.0)
+        leading *= sector_bias
+        trailing *= max(2.0 - sector_bias, 0.25)
+        total = max(leading + trailing, 1e-5)
+        bias = self.projector.enrich(abs(s.normal_bias)) * (math.copysign(1.0, s.normal_bias) if s.normal_bias != 0.0 else 0.0) * self._bias_gain
+        bias *= (1.0 + spin * 0.25) * (1.0 + min(max(s.flow_vector[2], -1.0), 1.0) * 0.5) * (1.0 - s.noise_density * 0.5)
+        bias += (1.0 if even else -1.0) * s.resonance_heat * 0.1
+        return here * leading / total, here * trailing / total, bias
 
 
 @dataclass
@@ -267,13 +320,18 @@ class MicrolocalFeedback:
     smoothing: Optional[float] = None
     tempo_hint: Optional[float] = None
     stderr_hint: Optional[float] = None
+    elliptic_radius: Optional[float] = None
+    elliptic_sheet_count: Optional[int] = None
+    elliptic_spin_harmonics: Optional[int] = None
 
     def merge(self, other: "MicrolocalFeedback") -> "MicrolocalFeedback":
         """Threshold scales multiply; for everything else the other side wins when it has a value."""
         a, b = self.threshold_scale, other.threshold_scale
         pick = lambda x, y: y if y is not None else x                      # noqa: E731
         return MicrolocalFeedback(max(a * b, 0.0) if a is not None and b is not None else pick(a, b), pick(self.bias_gain, other.bias_gain),
-                                  pick(self.smoothing, other.smoothing), pick(self.tempo_hint, other.tempo_hint), pick(self.stderr_hint, other.stderr_hint))
+                                  pick(self.smoothing, other.smoothing), pick(self.tempo_hint, other.tempo_hint), pick(self.stderr_hint, other.stderr_hint),
+                                  pick(self.elliptic_radius, other.elliptic_radius), pick(self.elliptic_sheet_count, other.elliptic_sheet_count),
+                                  pick(self.elliptic_spin_harmonics, other.elliptic_spin_harmonics))
 
     def with_threshold_scale(self, scale: float) -> "MicrolocalFeedback":
         return replace(self, threshold_scale=(self.threshold_scale or 1.0) * scale) if scale > 0.0 else self
@@ -289,6 +347,15 @@ class MicrolocalFeedback:
 
     def with_stderr_hint(self, stderr: float) -> "MicrolocalFeedback":
         return replace(self, stderr_hint=stderr) if stderr >= 0.0 else self
+
+    def with_elliptic_radius(self, radius: float) -> "MicrolocalFeedback":
+        return replace(self, elliptic_radius=radius) if math.isfinite(radius) and radius > 0.0 else self
+
+    def with_elliptic_sheet_count(self, sheets: int) -> "MicrolocalFeedback":
+        return replace(self, elliptic_sheet_count=sheets) if sheets > 0 else self
+
+    def with_elliptic_spin_harmonics(self, harmonics: int) -> "MicrolocalFeedback":
+        return replace(self, elliptic_spin_harmonics=harmonics) if harmonics > 0 else self
 
 
 # ---- quality policies -------------------------------------------------------------------------------------------------------
@@ -457,6 +524,7 @@ class InterfaceZConductor:
         return self
 
     def reinforce_positive_curvature(self, radius: float) -> "InterfaceZConductor":
+        self._lift.set_elliptic_warp(EllipticWarp(radius))
         self.band_policy = BandPolicy.positive_curvature(radius).with_hysteresis(0.05)
         return self
 
@@ -478,6 +546,16 @@ class InterfaceZConductor:
             self.default_tempo_hint = max(feedback.tempo_hint, 0.0)
         if feedback.stderr_hint is not None:
             self.default_stderr_hint = max(feedback.stderr_hint, 0.0)
+        if feedback.elliptic_radius is not None or feedback.elliptic_sheet_count is not None or feedback.elliptic_spin_harmonics is not None:
+            cur = self._lift.elliptic_warp()
+            r = feedback.elliptic_radius
+            if r is not None and math.isfinite(r) and r > 0.0:
+                warp = EllipticWarp(r, cur.sheet_count() if cur else 2, cur.spin_harmonics() if cur else 1)
+            else:
+                warp = cur.clone() if cur else None
+            if warp is not None:
+                warp.configure(feedback.elliptic_sheet_count, feedback.elliptic_spin_harmonics)
+                self._lift.set_elliptic_warp(warp)
 
     def last_fused_pulse(self) -> InterfaceZPulse:
         return replace(self.previous) if self.previous is not None else InterfaceZPulse()
@@ -502,6 +580,8 @@ class InterfaceZConductor:
         if self.previous is not None and self.smoothing > 0.0:
             fused = InterfaceZPulse.lerp(self.previous, fused, self.smoothing)
             events.append("smoothing.applied")
+        if fused.elliptic is not None:
+            events.extend(fused.elliptic.event_tags())
         budget_scale = self.budget_policy.apply(fused) if self.budget_policy is not None else 1.0
         self.policy.late_fuse(fused, pulses, qualities)
         now, self.clock = self.clock, self.clock + 1
