@@ -1,6 +1,7 @@
 // Spectral kernels: batched 1-D FFT in shared memory (any stride, real or complex input, optional window,
-// power-of-two lengths by Stockham radix-2 passes and other lengths by a direct DFT against a shared twiddle
-// table), spectral multipliers for the fractional operators, and the temporal volume renderer.
+// power-of-two lengths by Stockham radix-8 passes with the butterflies in registers and other lengths by a direct
+// DFT against a shared twiddle table), spectral multipliers for the fractional operators, and the temporal volume
+// renderer.
 //
 // All of them are bandwidth-bound elementwise / small-transform work: one pass over the data, fp32 math,
 // no tensor cores.  A transform lives entirely in one CTA's shared memory (two ping-pong buffers), so a batch
@@ -15,6 +16,8 @@ namespace {
 constexpr int kMaxFftLen = 8192;        // 2 x 8192 complex fp32 = 128 KB of shared memory
 constexpr int kMaxDftLen = 4096;        // direct DFT: input + twiddle table
 constexpr float kTau = 6.283185307179586f;
+constexpr int kMaxRenderTableFrames = 4096;   // 32 KB of (sin, cos) per CTA
+constexpr int kRenderRegChannels = 8;         // harmonic amplitudes kept in registers across the frame loop
 
 struct FftLayout {
   // element (b0, b1, i) of the input lives at in[b0 * in_b0 + b1 * in_b1 + i * in_i] (in floats; complex input
@@ -28,52 +31,143 @@ __device__ __forceinline__ float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
 
-// One transform per CTA.  Stockham autosort: pass s (half = 1, 2, 4, ...) reads x[j + k*half] style pairs from
-// `src` and writes in natural order to `dst`, so no bit-reversal pass is needed.
-__global__ void fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ window,
-                                FftLayout L, int n, int log2n, int complex_in, int inverse) {
+// ---- in-register DFTs of 2, 4 and 8 points (forward sign, natural output order) -------------------------------
+__device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ float2 mul_neg_i(float2 a) { return make_float2(a.y, -a.x); }          // a * (-i)
+
+__device__ __forceinline__ void dft4(float2& x0, float2& x1, float2& x2, float2& x3) {
+  const float2 a = cadd(x0, x2), b = csub(x0, x2), c = cadd(x1, x3), d = mul_neg_i(csub(x1, x3));
+  x0 = cadd(a, c); x1 = cadd(b, d); x2 = csub(a, c); x3 = csub(b, d);
+}
+
+template <int R>
+__device__ __forceinline__ void dft_regs(float2 (&v)[8]) {
+  if constexpr (R == 2) {
+    const float2 a = v[0];
+    v[0] = cadd(a, v[1]); v[1] = csub(a, v[1]);
+  } else if constexpr (R == 4) {
+    dft4(v[0], v[1], v[2], v[3]);
+  } else {
+    float2 e0 = v[0], e1 = v[2], e2 = v[4], e3 = v[6], o0 = v[1], o1 = v[3], o2 = v[5], o3 = v[7];
+    dft4(e0, e1, e2, e3);
+    dft4(o0, o1, o2, o3);
+    constexpr float h = 0.70710678118654752f;
+    o1 = make_float2(h * (o1.x + o1.y), h * (o1.y - o1.x));            // * exp(-i pi / 4)
+    o2 = mul_neg_i(o2);                                                 // * exp(-i pi / 2)
+    o3 = make_float2(h * (o3.y - o3.x), -h * (o3.x + o3.y));           // * exp(-3 i pi / 4)
+    v[0] = cadd(e0, o0); v[4] = csub(e0, o0);
+    v[1] = cadd(e1, o1); v[5] = csub(e1, o1);
+    v[2] = cadd(e2, o2); v[6] = csub(e2, o2);
+    v[3] = cadd(e3, o3); v[7] = csub(e3, o3);
+  }
+}
+
+// Shared-memory index with 8 elements of padding per 64: the second pass writes groups of 8 consecutive points that
+// are 64 points apart, which would land on the same banks four times over.
+__device__ __forceinline__ int pad_idx(int i) { return i + ((i >> 6) << 3); }
+
+// One Stockham pass of radix R over a transform of n points whose sub-transforms already have length ns:
+//   v[r] = src[j + r n/R] * w^r (w = exp(-2 pi i (j mod ns) / (ns R))), DFT_R(v), dst[(j / ns) ns R + (j mod ns) + r ns] = v[r]
+// FIRST reads the (strided, possibly real, windowed) input from global memory, LAST writes the output there, so a
+// transform of three passes crosses shared memory twice.  The inverse transform is conj(FFT(conj(x))) / n.
+template <int R, bool FIRST, bool LAST>
+__device__ __forceinline__ void stockham_pass(const float2* __restrict__ src, float2* __restrict__ dst, const float* __restrict__ gin,
+                                              float* __restrict__ gout, const float* __restrict__ window, long long in_i,
+                                              long long out_i, int n, int ns, int complex_in, int inverse, float scale) {
+  const int m = n / R;
+  for (int j = threadIdx.x; j < m; j += blockDim.x) {
+    float2 v[8];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = j + r * m;
+      if constexpr (FIRST) {
+        const float w = window ? window[i] : 1.0f;
+        const float re = gin[i * in_i];
+        const float im = complex_in ? gin[i * in_i + 1] : 0.0f;
+        v[r] = make_float2(re * w, inverse ? -im * w : im * w);
+      } else {
+        v[r] = src[pad_idx(i)];
+      }
+    }
+    const int k = j & (ns - 1);
+    if (!FIRST && k != 0) {
+      float sn, cs;
+      sincospif(-2.0f * (float)k / (float)(ns * R), &sn, &cs);
+      const float2 w1 = make_float2(cs, sn);
+      v[1] = cmul(v[1], w1);
+      if constexpr (R >= 4) {
+        const float2 w2 = cmul(w1, w1), w3 = cmul(w2, w1);
+        v[2] = cmul(v[2], w2); v[3] = cmul(v[3], w3);
+        if constexpr (R == 8) {
+          const float2 w4 = cmul(w2, w2);
+          v[4] = cmul(v[4], w4); v[5] = cmul(v[5], cmul(w4, w1)); v[6] = cmul(v[6], cmul(w4, w2)); v[7] = cmul(v[7], cmul(w4, w3));
+        }
+      }
+    }
+    dft_regs<R>(v);
+    const int j0 = (j - k) * R + k;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int o = j0 + r * ns;
+      if constexpr (LAST) {
+        gout[o * out_i] = v[r].x * scale;
+        gout[o * out_i + 1] = (inverse ? -v[r].y : v[r].y) * scale;
+      } else {
+        dst[pad_idx(o)] = v[r];
+      }
+    }
+  }
+}
+
+// One transform per CTA: n = 8^a * tail with tail in {1, 2, 4}; `a` radix-8 passes, then the tail pass.
+__global__ void __launch_bounds__(512, 2)
+fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ window,
+                FftLayout L, int n, int log2n, int complex_in, int inverse) {
   extern __shared__ float2 smem[];
+  const int padded = pad_idx(n - 1) + 1;
   float2* a = smem;
-  float2* b = smem + n;
+  float2* b = smem + padded;
   const int batch = blockIdx.x;
   const int b0 = batch / L.batch1, b1 = batch % L.batch1;
-  const float* src_ptr = in + b0 * L.in_b0 + b1 * L.in_b1;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float w = window ? window[i] : 1.0f;
-    const float re = src_ptr[i * L.in_i];
-    const float im = complex_in ? src_ptr[i * L.in_i + 1] : 0.0f;
-    a[i] = make_float2(re * w, im * w);
+  const float* gin = in + b0 * L.in_b0 + b1 * L.in_b1;
+  float* gout = out + b0 * L.out_b0 + b1 * L.out_b1;
+  const float scale = inverse ? 1.0f / (float)n : 1.0f;
+  const int eights = log2n / 3, tail = 1 << (log2n - 3 * eights);
+  if (n == 1) {
+    if (threadIdx.x == 0) {
+      const float w = window ? window[0] : 1.0f;
+      gout[0] = gin[0] * w;
+      gout[1] = complex_in ? gin[1] * w : 0.0f;
+    }
+    return;
   }
+  if (eights == 0) {               // n = 2 or 4: a single pass from global to global
+    if (tail == 2) stockham_pass<2, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+    else stockham_pass<4, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+    return;
+  }
+  if (eights == 1 && tail == 1) {  // n = 8
+    stockham_pass<8, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+    return;
+  }
+  stockham_pass<8, true, false>(nullptr, a, gin, nullptr, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
   __syncthreads();
-  const float sign = inverse ? 1.0f : -1.0f;
-  const int half_n = n >> 1;
-  // Stockham: at stage with `l` = number of already-combined points per group (1, 2, 4, ...) and m = n / (2l)
-  // groups: y[j*2l + k] = x[j*l + k] + w * x[j*l + k + n/2], y[j*2l + k + l] = x[...] - w * x[...]
   float2* src = a;
   float2* dst = b;
-  for (int l = 1; l < n; l <<= 1) {
-    for (int t = threadIdx.x; t < half_n; t += blockDim.x) {
-      const int k = t & (l - 1);          // position inside the group
-      const int j = t / l;                // group index
-      float sn, cs;
-      sincospif(sign * (float)k / (float)l, &sn, &cs);          // exp(sign * 2 pi i k / 2l)
-      const float2 w = make_float2(cs, sn);
-      const float2 u = src[j * l + k];
-      const float2 v = cmul(w, src[j * l + k + half_n]);
-      dst[j * 2 * l + k] = make_float2(u.x + v.x, u.y + v.y);
-      dst[j * 2 * l + k + l] = make_float2(u.x - v.x, u.y - v.y);
+  int ns = 8;
+  for (int p = 1; p < eights; ++p) {
+    if (p == eights - 1 && tail == 1) {
+      stockham_pass<8, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
+      return;
     }
+    stockham_pass<8, false, false>(src, dst, nullptr, nullptr, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
     __syncthreads();
-    float2* tmp = src; src = dst; dst = tmp;
+    float2* t = src; src = dst; dst = t;
+    ns *= 8;
   }
-  const float scale = inverse ? 1.0f / (float)n : 1.0f;
-  float* dst_ptr = out + b0 * L.out_b0 + b1 * L.out_b1;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float2 v = src[i];
-    dst_ptr[i * L.out_i] = v.x * scale;
-    dst_ptr[i * L.out_i + 1] = v.y * scale;
-  }
-  (void)log2n;
+  if (tail == 2) stockham_pass<2, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
+  else stockham_pass<4, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
 }
 
 // Direct DFT for lengths that are not powers of two: out[k] = sum_i x[i] * w^(k*i mod n), twiddles from a table.
@@ -113,32 +207,40 @@ __global__ void dft_kernel(const float* __restrict__ in, float* __restrict__ out
 // mode 0: fractional-Laplacian envelope, scale = min(col, cols - 1 - col)^power (real multiplier)
 // mode 1: fractional derivative, multiplier = (i * omega_col)^alpha with omega = 2 pi * fftfreq(cols, h);
 //         the zero frequency is set to 0 for alpha > 0
+// One thread owns a column: the multiplier (a pow and, for the derivative, a sincos) is computed once and applied to
+// that column of `rows_per_block` consecutive rows, so the kernel is a streaming multiply.
 __global__ void specmul_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int cols, float power,
-                               float inv_h, int mode) {
-  const long long total = rows * cols;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const int col = (int)(idx % cols);
-    const float2 v = reinterpret_cast<const float2*>(x)[idx];
-    float2 r;
-    if (mode == 0) {
-      const int mirror = cols - 1 - col;
-      const float s = powf(fmaxf((float)(col < mirror ? col : mirror), 0.0f), power);
-      r = make_float2(v.x * s, v.y * s);
+                               float inv_h, int mode, int rows_per_block) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  float2 mult;
+  bool passthrough = false, infinite = false;
+  if (mode == 0) {
+    const int mirror = cols - 1 - col;
+    mult = make_float2(powf(fmaxf((float)(col < mirror ? col : mirror), 0.0f), power), 0.0f);
+  } else {
+    const int k = col < (cols + 1) / 2 ? col : col - cols;      // fftfreq ordering
+    const float omega = kTau * (float)k * inv_h / (float)cols;
+    if (k == 0) {
+      mult = make_float2(0.0f, 0.0f);
+      passthrough = power == 0.0f;
+      infinite = power < 0.0f;
     } else {
-      const int k = col < (cols + 1) / 2 ? col : col - cols;      // fftfreq ordering
-      const float omega = kTau * (float)k * inv_h / (float)cols;
-      if (k == 0) {
-        r = power > 0.0f ? make_float2(0.0f, 0.0f) : (power == 0.0f ? v : make_float2(CUDART_INF_F, CUDART_INF_F));
-      } else {
-        // (i omega)^a = |omega|^a * exp(i * a * sign(omega) * pi / 2)
-        const float mag = powf(fabsf(omega), power);
-        float sn, cs;
-        sincosf(power * (omega > 0.0f ? 1.0f : -1.0f) * 1.5707963267948966f, &sn, &cs);
-        r = cmul(v, make_float2(mag * cs, mag * sn));
-      }
+      // (i omega)^a = |omega|^a * exp(i * a * sign(omega) * pi / 2)
+      const float mag = powf(fabsf(omega), power);
+      float sn, cs;
+      sincosf(power * (omega > 0.0f ? 1.0f : -1.0f) * 1.5707963267948966f, &sn, &cs);
+      mult = make_float2(mag * cs, mag * sn);
     }
-    reinterpret_cast<float2*>(y)[idx] = r;
+  }
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  const long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+  const float2* xp = reinterpret_cast<const float2*>(x);
+  float2* yp = reinterpret_cast<float2*>(y);
+#pragma unroll 4
+  for (long long r = r0; r < r1; ++r) {
+    const float2 v = xp[r * cols + col];
+    yp[r * cols + col] = passthrough ? v : (infinite ? make_float2(CUDART_INF_F, CUDART_INF_F) : cmul(v, mult));
   }
 }
 
@@ -148,25 +250,51 @@ __global__ void specmul_kernel(const float* __restrict__ x, float* __restrict__ 
 __global__ void temporal_render_kernel(const float* __restrict__ voxels, const float* __restrict__ harmonics,
                                        const float* __restrict__ decay, float* __restrict__ out, long long n_voxels,
                                        int channels, int frames, float dt) {
+  // sin / cos of the base angle of every frame are the same for all voxels: one table per CTA
+  extern __shared__ float2 frame_sc[];
+  const bool table = channels > 0 && frames <= kMaxRenderTableFrames;
+  if (table) {
+    for (int f = threadIdx.x; f < frames; f += blockDim.x) {
+      float sn, cs;
+      sincosf(kTau * ((float)f * dt), &sn, &cs);
+      frame_sc[f] = make_float2(sn, cs);
+    }
+    __syncthreads();
+  }
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < n_voxels;
        v += (long long)gridDim.x * blockDim.x) {
     const float base0 = voxels[v];
     float d = decay[v];
     d = isfinite(d) ? fmaxf(d, 0.0f) : 1.0f;
     const float* h = harmonics + v * channels;
+    float amp[kRenderRegChannels];
+    const bool in_regs = channels <= kRenderRegChannels;
+    if (in_regs) {
+#pragma unroll
+      for (int c = 0; c < kRenderRegChannels; ++c) amp[c] = c < channels ? h[c] : 0.0f;
+    }
     for (int f = 0; f < frames; ++f) {
       const float t = (float)f * dt;
       float base = base0;
       if (channels > 0) {
         float sn, cs;
-        sincosf(kTau * t, &sn, &cs);
+        if (table) { sn = frame_sc[f].x; cs = frame_sc[f].y; } else { sincosf(kTau * t, &sn, &cs); }
         float s_prev = 0.0f, s_cur = sn;                 // sin(0 * theta), sin(1 * theta)
         const float two_c = 2.0f * cs;
-        for (int c = 0; c < channels; ++c) {
-          const float amp = h[c];
-          if (fabsf(amp) > 1.1920929e-07f) base += amp * s_cur;
-          const float s_next = two_c * s_cur - s_prev;
-          s_prev = s_cur; s_cur = s_next;
+        if (in_regs) {
+#pragma unroll
+          for (int c = 0; c < kRenderRegChannels; ++c) {
+            if (fabsf(amp[c]) > 1.1920929e-07f) base += amp[c] * s_cur;
+            const float s_next = two_c * s_cur - s_prev;
+            s_prev = s_cur; s_cur = s_next;
+          }
+        } else {
+          for (int c = 0; c < channels; ++c) {
+            const float a = h[c];
+            if (fabsf(a) > 1.1920929e-07f) base += a * s_cur;
+            const float s_next = two_c * s_cur - s_prev;
+            s_prev = s_cur; s_cur = s_next;
+          }
         }
       }
       out[(long long)f * n_voxels + v] = d <= 1.1920929e-07f ? 0.0f : base * __expf(-d * t);
@@ -197,17 +325,20 @@ ST_API int st_fft_1d(const StFftArgs* a, void* stream_v) {
   FftLayout L{a->in_b0, a->in_b1, a->in_i, a->out_b0, a->out_b1, a->out_i, a->batch1};
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const int grid = a->batch0 * a->batch1;
-  const size_t smem = 2 * (size_t)a->n * sizeof(float2);
+  const size_t padded = (size_t)a->n + (((size_t)a->n - 1) >> 6 << 3);          // the kernel's pad_idx(n - 1) + 1
+  const size_t smem = pow2 ? 2 * padded * sizeof(float2) : 2 * (size_t)a->n * sizeof(float2);
   static bool configured[st::kMaxDevices][2] = {};
   const int dev = st::current_device();
   if (pow2) {
     if (smem > 48 * 1024 && !configured[dev][0]) {
-      ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kMaxFftLen * (int)sizeof(float2)));
+      ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         2 * (kMaxFftLen + kMaxFftLen / 8) * (int)sizeof(float2)));
       configured[dev][0] = true;
     }
     int log2n = 0;
     while ((1 << log2n) < a->n) ++log2n;
-    const int threads = a->n >= 2048 ? 512 : (a->n >= 256 ? 128 : 32);
+    int threads = a->n / 8;                    // one radix-8 butterfly per thread and pass
+    threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
     fft_pow2_kernel<<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
   } else {
     if (smem > 48 * 1024 && !configured[dev][1]) {
@@ -227,12 +358,18 @@ ST_API int st_specmul(const float* x_reim, float* y_reim, long long rows, int co
   if (mode != 0 && mode != 1) return st::fail(ST_ERR_INVALID, "specmul: mode is 0 (Laplace envelope) or 1 (derivative)");
   if (!isfinite(power)) return st::fail(ST_ERR_INVALID, "specmul: power must be finite");
   if (mode == 1 && !(h > 0.0f)) return st::fail(ST_ERR_INVALID, "specmul: sample spacing must be positive");
-  const long long total = rows * cols;
-  long long blocks = (total + 255) / 256;
-  const long long cap = (long long)st::sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  specmul_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(x_reim, y_reim, rows, cols, power,
-                                                                                   mode == 1 ? 1.0f / h : 0.0f, mode);
+  const int threads = cols >= 128 ? 128 : 32;
+  const int col_blocks = (cols + threads - 1) / threads;
+  // enough row chunks to fill the machine a few times over, each long enough to amortise the multiplier
+  long long chunks = ((long long)st::sm_count() * 16 + col_blocks - 1) / col_blocks;
+  if (chunks > rows) chunks = rows;
+  if (chunks > 65535) chunks = 65535;
+  if (chunks < 1) chunks = 1;
+  const long long rows_per_block = (rows + chunks - 1) / chunks;
+  if (rows_per_block > 2147483647LL) return st::fail(ST_ERR_TOO_LARGE, "specmul: too many rows");
+  chunks = (rows + rows_per_block - 1) / rows_per_block;
+  specmul_kernel<<<dim3(col_blocks, (unsigned)chunks), threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      x_reim, y_reim, rows, cols, power, mode == 1 ? 1.0f / h : 0.0f, mode, (int)rows_per_block);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
 }
@@ -246,7 +383,8 @@ ST_API int st_temporal_render(const float* voxels, const float* harmonics, const
   long long blocks = (n_voxels + 255) / 256;
   const long long cap = (long long)st::sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  temporal_render_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+  const size_t table = (channels > 0 && frames <= kMaxRenderTableFrames) ? (size_t)frames * sizeof(float2) : 0;
+  temporal_render_kernel<<<(int)blocks, 256, table, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       voxels, harmonics, decay, out, n_voxels, channels, frames, 1.0f / sample_rate_hz);
   ST_CUDA_CHECK(cudaGetLastError());
   return ST_OK;
