@@ -6,7 +6,7 @@
 """
 from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
                selfsup, softlogic, telemetry, text, theory, topos, tracking, vision, zspace_coherence, zvolume)
-from . import elliptic, hub, kdsl_ir, kv, mellin, meta_narrative, microlocal, psi_sync, psychoid, qr_studio, sot, relativity, rg_flow, spiral_dynamics, unison, zpulse  # noqa: E402  (network key/value client imports logic)
+from . import elliptic, hub, introspect, kdsl_ir, kv, mellin, meta_narrative, microlocal, psi_sync, psychoid, qr_studio, sot, relativity, rg_flow, spiral_dynamics, unison, zpulse  # noqa: E402  (network key/value client imports logic)
 from .nn.io import VERSION as __version__
 from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad
 from .session import SpiralSession, build_info, describe_device
@@ -27,3 +27,4 @@ def init_backend(name: str = "auto") -> str:
     return SpiralSession(name).effective_backend
 
 from .elliptic import EllipticTelemetry, EllipticWarp  # noqa: E402  (top-level names of the reference's Python surface)
+from .introspect import clear_zspace_feedback, describe_zspace, softlogic_feedback, softlogic_signal, zspace_snapshot  # noqa: E402
