@@ -421,6 +421,371 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Pair kernel (no bias / lengths): one CTA owns TWO adjacent 128-row query tiles of one (batch, head), so every K and
+// V tile that TMA brings in feeds two products, and the probabilities never touch shared memory:
+//   S_t = Q_t·Kᵀ          tcgen05.mma (both operands from shared memory), fp32 in TMEM, one S buffer per query tile
+//   P_t = exp2(S_t·c − m)  one softmax warpgroup per query tile, one thread per row; P is written back as bf16 over
+//                          the first 64 columns of S_t with tcgen05.st
+//   O_t += P_t·V           tcgen05.mma with the A operand read from TMEM; O_t stays in TMEM for the whole item
+// The running maximum is only raised when it grew by more than 8 (in the log2 domain): P then stays below 2^8, the
+// row sum and O keep one common reference, and the rescale of O_t in TMEM (load, multiply, store) is rare.  The MMA
+// warp alternates the two tiles (PV_0, QK_0, PV_1, QK_1, ...), so the tensor pipe works on one tile while the other
+// tile's warpgroup is in its softmax.  Shared-memory traffic per query tile and KV tile drops from 224 KB (two
+// operand reads per product, K and V written per tile, P written and read) to 128 KB.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int PAIR_THREADS = 384;   // two softmax warpgroups + one warpgroup holding the producer and MMA warps
+// Registers are a per-scheduler pool of 512 per lane shared by three warps here (launch allocation 168 each): the
+// producer / MMA warpgroup hands its share back and each softmax warp, which keeps a 128-column row of S live, grows.
+constexpr int PAIR_REGS_AUX = 88, PAIR_REGS_SOFTMAX = 208;
+constexpr int PAIR_STAGES = 4;      // ring of K / V tiles in the order K_j, V_j, K_j+1, V_j+1
+
+template <int D>
+struct PairSmem {
+  static constexpr int TILE = BLK * D * 2;
+  static constexpr int Q_OFF = 0;                          // two query tiles
+  static constexpr int KV_OFF = 2 * TILE;
+  static constexpr int BAR_OFF = KV_OFF + PAIR_STAGES * TILE;
+  static constexpr int TOTAL = BAR_OFF + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using L = PairSmem<D>;
+  constexpr int KB = D / 64;
+  constexpr uint32_t S_COL = 0;       // S_t at S_COL + 128 t; P_t (bf16 pairs) over its first 64 columns
+  constexpr uint32_t O_COL = 256;     // O_t at O_COL + D t
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr float RESCALE_STEP = 8.0f;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) report_error(p.err, ERR_BOUNDS, 0xA7F3u);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;             // 2
+  uint64_t* q_empty = bars + 2;        // 2
+  uint64_t* kv_full = bars + 4;        // PAIR_STAGES
+  uint64_t* kv_empty = bars + 8;       // PAIR_STAGES
+  uint64_t* s_full = bars + 12;        // 2
+  uint64_t* p_full = bars + 14;        // 2 (one arrival per softmax warp of the tile)
+  uint64_t* o_full = bars + 16;        // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hb = p.H * p.B;
+  const int n_pairs = (p.n_q + 1) / 2;
+  const int n_kv_all = (p.Sk + BLK - 1) / BLK;
+  // Work item w -> (query pair, head, batch) and the KV tiles each of its two query tiles visits
+  auto item_at = [&](int w, int& qp, int& h, int& b, int& n0, int& n1) {
+    qp = n_pairs - 1 - w / hb;
+    const int rem = w % hb;
+    h = rem % p.H;
+    b = rem / p.H;
+    n0 = p.causal ? min(n_kv_all, 2 * qp + 1) : n_kv_all;
+    n1 = (2 * qp + 1 < p.n_q) ? (p.causal ? min(n_kv_all, 2 * qp + 2) : n_kv_all) : 0;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&q_full[i]), 1);
+      mbar_init(smem_u32(&q_empty[i]), 1);
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&p_full[i]), 4);
+      mbar_init(smem_u32(&o_full[i]), 1);
+    }
+    for (int i = 0; i < PAIR_STAGES; ++i) {
+      mbar_init(smem_u32(&kv_full[i]), 1);
+      mbar_init(smem_u32(&kv_empty[i]), 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PAIR_REGS_AUX));
+  if (warp == 8) {
+    // ---------------------------- TMA producer ---------------------------------------------------
+    if (lane == 0) {
+      int g = 0;                 // KV tiles loaded so far over all items: K at ring index 2g, V at 2g + 1
+      int items_t[2] = {0, 0};   // items in which query tile t took part (phase of q_full / q_empty)
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        int qp, h, b, n_t[2];
+        item_at(w, qp, h, b, n_t[0], n_t[1]);
+        const int n_kv = max(n_t[0], n_t[1]);
+        if (n_kv <= 0) continue;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (n_t[t] <= 0) continue;
+          // the tile's Q buffer is free once its last QK^T of the previous item has completed
+          if (items_t[t] > 0 && !mbar_wait(smem_u32(&q_empty[t]), (items_t[t] - 1) & 1, abort_flag)) { ok = false; break; }
+          const uint32_t qb = smem_u32(&q_full[t]);
+          mbar_arrive_expect_tx(qb, L::TILE);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem_u32(smem + L::Q_OFF + t * L::TILE + kb * (BLK * 128)), &tmQ, qb, kb * 64, h,
+                        (2 * qp + t) * BLK, b);
+          ++items_t[t];
+        }
+        for (int j = 0; j < n_kv && ok; ++j, ++g) {
+#pragma unroll
+          for (int kv = 0; kv < 2; ++kv) {
+            const int idx = 2 * g + kv;
+            const int st = idx % PAIR_STAGES;
+            const uint32_t ph = (idx / PAIR_STAGES) & 1;
+            if (!mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t fb = smem_u32(&kv_full[st]);
+            mbar_arrive_expect_tx(fb, L::TILE);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem_u32(smem + L::KV_OFF + st * L::TILE + kb * (BLK * 128)), kv == 0 ? &tmK : &tmV, fb,
+                          kb * 64, h, j * BLK, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------------------- MMA issuer -----------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BLK, D, false, true);
+      int g = 0;
+      uint32_t steps_t[2] = {0, 0};   // softmax steps of tile t consumed so far (phase of p_full)
+      int items_t[2] = {0, 0};
+      int n_t[2] = {0, 0};
+      // The K (V) tile of step j is released by the last product that reads it: tile 1's when tile 1 visits step j.
+      auto issue_qk = [&](int t, int j) -> bool {
+        if (j == 0 && !mbar_wait(smem_u32(&q_full[t]), items_t[t] & 1, abort_flag)) return false;
+        const int idx = 2 * (g + j);
+        const int st = idx % PAIR_STAGES;
+        if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::Q_OFF + t * L::TILE);
+        const uint32_t sk = smem_u32(smem + L::KV_OFF + st * L::TILE);
+        const uint32_t d_tmem = tmem_base + S_COL + t * BLK;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_smem_desc_sw128(sq + kb * (BLK * 128) + k * 32, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sk + kb * (BLK * 128) + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+        umma_commit(smem_u32(&s_full[t]));
+        if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
+        if (j == n_t[t] - 1) umma_commit(smem_u32(&q_empty[t]));
+        return true;
+      };
+      auto issue_pv = [&](int t, int j) -> bool {
+        if (!mbar_wait(smem_u32(&p_full[t]), steps_t[t] & 1u, abort_flag)) return false;
+        ++steps_t[t];
+        const int idx = 2 * (g + j) + 1;
+        const int st = idx % PAIR_STAGES;
+        if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sv = smem_u32(smem + L::KV_OFF + st * L::TILE);
+        const uint32_t a_tmem = tmem_base + S_COL + t * BLK;
+        const uint32_t d_tmem = tmem_base + O_COL + t * D;
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {
+          // A = P from TMEM (8 columns per K = 16 step); B = V (MN-major: D contiguous, KV rows = K)
+          const uint64_t db = make_smem_desc_sw128(sv + kk * (16 * 128), BLK * 128, 1024);
+          umma_bf16_ts(d_tmem, a_tmem + kk * 8, db, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+        }
+        if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
+        if (j == n_t[t] - 1) umma_commit(smem_u32(&o_full[t]));
+        return true;
+      };
+      bool ok = true;
+      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        int qp, h, b;
+        item_at(w, qp, h, b, n_t[0], n_t[1]);
+        const int n_kv = max(n_t[0], n_t[1]);
+        if (n_kv <= 0) continue;
+        if (n_t[0] > 0) ok = issue_qk(0, 0);
+        if (ok && n_t[1] > 0) ok = issue_qk(1, 0);
+        for (int j = 0; j < n_kv && ok; ++j) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!ok || j >= n_t[t]) continue;
+            ok = issue_pv(t, j);
+            if (ok && j + 1 < n_t[t]) ok = issue_qk(t, j + 1);
+          }
+        }
+        g += n_kv;
+        if (n_t[0] > 0) ++items_t[0];
+        if (n_t[1] > 0) ++items_t[1];
+      }
+    }
+  }
+  } else {
+    // ---------------------------- softmax / output warpgroups ------------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PAIR_REGS_SOFTMAX));
+    const int t = warp >> 2;              // query tile of the pair
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may access
+    const int r = quad * 32 + lane;       // row of the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + S_COL + t * BLK;
+    const uint32_t o_addr = tmem_base + lane_off + O_COL + t * D;
+    const float sc = p.scale_log2;
+    uint32_t steps = 0;   // softmax steps done (phase of s_full)
+    int items = 0;        // items this tile took part in (phase of o_full)
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+      int qp, h, b, n0, n1;
+      item_at(w, qp, h, b, n0, n1);
+      const int n_kv = t == 0 ? n0 : n1;
+      if (n_kv <= 0) continue;
+      const int q_tile = 2 * qp + t;
+      const int row_g = q_tile * BLK + r;
+      float m = -INFINITY, l = 0.0f;
+      for (int j = 0; j < n_kv; ++j) {
+        if (!mbar_wait_warp(smem_u32(&s_full[t]), steps & 1u, abort_flag)) { ok = false; break; }
+        ++steps;
+        tc_fence_after();
+        uint32_t sr[BLK];
+        {
+          uint32_t t0[32], t1[32], t2[32], t3[32];
+          tmem_ld_32x32(s_addr, t0);
+          tmem_ld_32x32(s_addr + 32, t1);
+          tmem_ld_32x32(s_addr + 64, t2);
+          tmem_ld_32x32(s_addr + 96, t3);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) { sr[c] = t0[c]; sr[32 + c] = t1[c]; sr[64 + c] = t2[c]; sr[96 + c] = t3[c]; }
+        }
+        const int col0 = j * BLK;
+        float mx = -INFINITY;
+        if ((p.causal && j == q_tile) || col0 + BLK > p.Sk) {
+#pragma unroll
+          for (int c = 0; c < BLK; ++c) {
+            const int col = col0 + c;
+            const bool dead = (col >= p.Sk) || (p.causal && col > row_g);
+            const float s = dead ? -INFINITY : __uint_as_float(sr[c]);
+            sr[c] = __float_as_uint(s);
+            mx = fmaxf(mx, s);
+          }
+        } else {
+          float mx1 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < BLK; c += 4) {
+            mx = max3(mx, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+            mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          }
+          mx = fmaxf(mx, mx1);
+        }
+        const float m_new = fmaxf(m, mx * sc);
+        bool raise = false;
+        float alpha = 1.0f;
+        if (j == 0) {
+          m = m_new;                                   // O_t is overwritten by the first PV: nothing to rescale
+        } else if (m_new - m > RESCALE_STEP) {
+          raise = true;
+          alpha = fast_exp2(m - m_new);                // m = -inf gives 0
+          m = m_new;
+          l *= alpha;
+        }
+        if (__any_sync(0xffffffffu, raise)) {
+          // S_t of this step was committed after PV_t of the previous step, so O_t is complete here
+          const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+          for (int ch = 0; ch < D / 32; ++ch) {
+            uint32_t v[32];
+            tmem_ld_32x32(o_addr + ch * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const float2 y = mul2(make_float2(__uint_as_float(v[2 * c]), __uint_as_float(v[2 * c + 1])), a2);
+              v[2 * c] = __float_as_uint(y.x);
+              v[2 * c + 1] = __float_as_uint(y.y);
+            }
+            tmem_st_32x32(o_addr + ch * 32, v);
+          }
+        }
+        const float m_ref = (m == -INFINITY) ? 0.0f : m;
+        const float2 sc2 = make_float2(sc, sc);
+        const float2 nm2 = make_float2(-m_ref, -m_ref);
+        float2 rs2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t pr[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int cc = hlf * 64 + 2 * c;
+            const float2 x = fma2(make_float2(__uint_as_float(sr[cc]), __uint_as_float(sr[cc + 1])), sc2, nm2);
+            const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            rs2[c & 1] = add2(rs2[c & 1], e);
+            pr[c] = pack_bf16x2(e.x, e.y);
+          }
+          tmem_st_32x32(s_addr + hlf * 32, pr);
+        }
+        l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_full[t]));
+      }
+      if (!ok) break;
+      // ---- output: O_t / l as bf16, one row per thread; log-sum-exp in natural units ----
+      if (!mbar_wait_warp(smem_u32(&o_full[t]), items & 1, abort_flag)) { ok = false; break; }
+      ++items;
+      tc_fence_after();
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      __nv_bfloat16* op = p.O + (long long)b * p.o_sb + (long long)row_g * p.o_ss + (long long)h * p.o_sh;
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(o_addr + ch * 32, v);
+        tmem_ld_wait();
+        if (row_g < p.Sq) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(v[c8 * 8 + 0]) * inv, __uint_as_float(v[c8 * 8 + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(v[c8 * 8 + 2]) * inv, __uint_as_float(v[c8 * 8 + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(v[c8 * 8 + 4]) * inv, __uint_as_float(v[c8 * 8 + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(v[c8 * 8 + 6]) * inv, __uint_as_float(v[c8 * 8 + 7]) * inv);
+            reinterpret_cast<uint4*>(op)[ch * 4 + c8] = u;
+          }
+        }
+      }
+      if (row_g < p.Sq)
+        p.lse[((long long)b * p.H + h) * p.Sq + row_g] =
+            (l > 0.0f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      // the next item's first PV_t overwrites O_t only after this warpgroup's next p_full arrival, which follows
+      // these loads in program order
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) report_error(p.err, ERR_MBAR_TIMEOUT, 0xA7F2u);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 }  // namespace
 
 namespace st {
@@ -447,6 +812,12 @@ struct StAttnFwdArgs {
   const float* attn_bias; long long ab_sb, ab_sh, ab_sq;     // [B, (H,) Sq, Sk], keys contiguous
   const int* lengths;
 };
+
+// 1 (default): plain attention runs the pair kernel (two query tiles per CTA, P and O in TMEM); 0: the single-tile
+// kernel for every case.  The biased / variable-length instantiation always uses the single-tile kernel.
+static int g_pair_kernel = 1;
+ST_API void st_attn_fwd_set_pair_kernel(int on) { g_pair_kernel = on ? 1 : 0; }
+ST_API int st_attn_fwd_get_pair_kernel() { return g_pair_kernel; }
 
 ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   if (!a || !a->Q || !a->K || !a->V || !a->O || !a->lse) return st::fail(ST_ERR_INVALID, "attn_fwd: null pointer");
@@ -479,10 +850,32 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   p.lengths = a->lengths;
   const bool biased = a->key_bias || a->attn_bias || a->lengths;
   if (p.n_items <= 0) return ST_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
+  if (!biased && g_pair_kernel) {
+    // two query tiles per CTA: the items are (query pair, head, batch)
+    p.n_items = ((p.n_q + 1) / 2) * a->H * a->B;
+    const dim3 pgrid(std::min(p.n_items, st::sm_count()));
+    static bool pcfg[2][st::kMaxDevices] = {{false}};
+    const int dev = st::current_device();
+    if (a->D == 128) {
+      if (!pcfg[0][dev]) {
+        ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_pair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<128>::TOTAL));
+        pcfg[0][dev] = true;
+      }
+      attn_fwd_pair_kernel<128><<<pgrid, PAIR_THREADS, PairSmem<128>::TOTAL, s>>>(tq, tk, tv, p);
+    } else {
+      if (!pcfg[1][dev]) {
+        ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_pair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<64>::TOTAL));
+        pcfg[1][dev] = true;
+      }
+      attn_fwd_pair_kernel<64><<<pgrid, PAIR_THREADS, PairSmem<64>::TOTAL, s>>>(tq, tk, tv, p);
+    }
+    ST_CUDA_CHECK(cudaGetLastError());
+    return ST_OK;
+  }
   // persistent: one CTA per SM walks the work items, so TMEM, barriers and the pipeline fill are
   // paid once per CTA and an item's output stores overlap the next item's first loads
   const dim3 grid(std::min(p.n_items, st::sm_count()));
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
   auto launch = [&](auto kern, int smem_bytes, bool* cfg) -> int {
     if (!cfg[st::current_device()]) {     // the attribute is per device
       ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));

@@ -7,6 +7,7 @@
 // no tensor cores.  A transform lives entirely in one CTA's shared memory (two ping-pong buffers), so a batch
 // of transforms costs one read and one write of the data whatever the length.
 #include <cuda_runtime.h>
+#include <cstdint>
 #include <math_constants.h>
 
 #include "../common/host.h"
@@ -63,37 +64,54 @@ __device__ __forceinline__ void dft_regs(float2 (&v)[8]) {
   }
 }
 
-// Shared-memory index with 8 elements of padding per 64: the second pass writes groups of 8 consecutive points that
-// are 64 points apart, which would land on the same banks four times over.
-__device__ __forceinline__ int pad_idx(int i) { return i + ((i >> 6) << 3); }
+// Shared-memory slot of point i: 8 slots of padding per 64 points (the second pass writes groups of 8 consecutive
+// points that are 64 points apart) and the low three bits XOR-ed with bits 4..6 of i (the first pass writes 8
+// consecutive points per thread, so 16 threads of a half-warp would land on two bank pairs without it).  With both,
+// every 64-bit shared-memory access of every pass touches 16 distinct bank pairs per half-warp.
+__device__ __forceinline__ int slot(int i) { return (i + ((i >> 6) << 3)) ^ ((i >> 4) & 7); }
 
 // One Stockham pass of radix R over a transform of n points whose sub-transforms already have length ns:
 //   v[r] = src[j + r n/R] * w^r (w = exp(-2 pi i (j mod ns) / (ns R))), DFT_R(v), dst[(j / ns) ns R + (j mod ns) + r ns] = v[r]
 // FIRST reads the (strided, possibly real, windowed) input from global memory, LAST writes the output there, so a
 // transform of three passes crosses shared memory twice.  The inverse transform is conj(FFT(conj(x))) / n.
-template <int R, bool FIRST, bool LAST>
+// NSC is ns when it is 1, 8 or 64 and 0 for a run-time ns that is a multiple of 512: each case has a closed form of
+// slot() for its eight outputs (one XOR and one add per output instead of the shifts of the general formula).
+// VEC: input and output are interleaved complex with unit stride, moved as float2.
+template <int R, bool FIRST, bool LAST, int NSC, bool VEC>
 __device__ __forceinline__ void stockham_pass(const float2* __restrict__ src, float2* __restrict__ dst, const float* __restrict__ gin,
                                               float* __restrict__ gout, const float* __restrict__ window, long long in_i,
-                                              long long out_i, int n, int ns, int complex_in, int inverse, float scale) {
+                                              long long out_i, int n, int ns_rt, int complex_in, int inverse, float scale) {
+  const int ns = NSC ? NSC : ns_rt;
   const int m = n / R;
+  const bool stride_reads = (m & 127) == 0;          // slot(j + r m) = slot(j) + r (m + m / 8)
+  const int m_slots = m + (m >> 3);
+  const float angle_scale = -2.0f / (float)(ns * R);  // a power of two: exact
   for (int j = threadIdx.x; j < m; j += blockDim.x) {
     float2 v[8];
+    if constexpr (FIRST) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int i = j + r * m;
-      if constexpr (FIRST) {
+      for (int r = 0; r < R; ++r) {
+        const int i = j + r * m;
         const float w = window ? window[i] : 1.0f;
-        const float re = gin[i * in_i];
-        const float im = complex_in ? gin[i * in_i + 1] : 0.0f;
+        float re, im;
+        if constexpr (VEC) {
+          const float2 x = reinterpret_cast<const float2*>(gin)[i];
+          re = x.x; im = x.y;
+        } else {
+          re = gin[i * in_i];
+          im = complex_in ? gin[i * in_i + 1] : 0.0f;
+        }
         v[r] = make_float2(re * w, inverse ? -im * w : im * w);
-      } else {
-        v[r] = src[pad_idx(i)];
       }
+    } else {
+      const int s0 = slot(j);
+#pragma unroll
+      for (int r = 0; r < R; ++r) v[r] = src[stride_reads ? s0 + r * m_slots : slot(j + r * m)];
     }
     const int k = j & (ns - 1);
-    if (!FIRST && k != 0) {
+    if constexpr (!FIRST) {
       float sn, cs;
-      sincospif(-2.0f * (float)k / (float)(ns * R), &sn, &cs);
+      sincospif((float)k * angle_scale, &sn, &cs);
       const float2 w1 = make_float2(cs, sn);
       v[1] = cmul(v[1], w1);
       if constexpr (R >= 4) {
@@ -106,26 +124,50 @@ __device__ __forceinline__ void stockham_pass(const float2* __restrict__ src, fl
       }
     }
     dft_regs<R>(v);
-    const int j0 = (j - k) * R + k;
+    if constexpr (LAST) {
+      const int j0 = (j - k) * R + k;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int o = j0 + r * ns;
-      if constexpr (LAST) {
-        gout[o * out_i] = v[r].x * scale;
-        gout[o * out_i + 1] = (inverse ? -v[r].y : v[r].y) * scale;
+      for (int r = 0; r < R; ++r) {
+        const int o = j0 + r * ns;
+        const float2 y = make_float2(v[r].x * scale, (inverse ? -v[r].y : v[r].y) * scale);
+        if constexpr (VEC) {
+          reinterpret_cast<float2*>(gout)[o] = y;
+        } else {
+          gout[o * out_i] = y.x;
+          gout[o * out_i + 1] = y.y;
+        }
+      }
+    } else {
+      static_assert(LAST || R == 8, "only radix-8 passes write shared memory");
+      if constexpr (NSC == 1) {
+        const int base = j * 8 + ((j >> 3) << 3), x = (j >> 1) & 7;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dst[base + (r ^ x)] = v[r];
+      } else if constexpr (NSC == 8) {
+        const int g = j >> 3, base = g * 72, x = k ^ ((g & 1) << 2);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dst[base + r * 8 + (x ^ (r >> 1))] = v[r];
+      } else if constexpr (NSC == 64) {
+        const int base = (j >> 6) * 576, x = k ^ (k >> 4);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dst[base + r * 72 + (x ^ ((r & 1) << 2))] = v[r];
       } else {
-        dst[pad_idx(o)] = v[r];
+        const int ns_slots = ns + (ns >> 3);
+        const int base = ((j - k) / ns) * 8 * ns_slots + slot(k);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dst[base + r * ns_slots] = v[r];
       }
     }
   }
 }
 
 // One transform per CTA: n = 8^a * tail with tail in {1, 2, 4}; `a` radix-8 passes, then the tail pass.
+template <bool VEC>
 __global__ void __launch_bounds__(512, 2)
 fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ window,
                 FftLayout L, int n, int log2n, int complex_in, int inverse) {
   extern __shared__ float2 smem[];
-  const int padded = pad_idx(n - 1) + 1;
+  const int padded = n + (((n - 1) >> 6) << 3);
   float2* a = smem;
   float2* b = smem + padded;
   const int batch = blockIdx.x;
@@ -134,6 +176,8 @@ fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const flo
   float* gout = out + b0 * L.out_b0 + b1 * L.out_b1;
   const float scale = inverse ? 1.0f / (float)n : 1.0f;
   const int eights = log2n / 3, tail = 1 << (log2n - 3 * eights);
+#define ST_FFT_PASS(R, FIRST, LAST, NSC, SRC, DST, NS) \
+  stockham_pass<R, FIRST, LAST, NSC, VEC>(SRC, DST, gin, gout, window, L.in_i, L.out_i, n, NS, complex_in, inverse, scale)
   if (n == 1) {
     if (threadIdx.x == 0) {
       const float w = window ? window[0] : 1.0f;
@@ -143,31 +187,36 @@ fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const flo
     return;
   }
   if (eights == 0) {               // n = 2 or 4: a single pass from global to global
-    if (tail == 2) stockham_pass<2, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
-    else stockham_pass<4, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+    if (tail == 2) ST_FFT_PASS(2, true, true, 1, nullptr, nullptr, 1);
+    else ST_FFT_PASS(4, true, true, 1, nullptr, nullptr, 1);
     return;
   }
   if (eights == 1 && tail == 1) {  // n = 8
-    stockham_pass<8, true, true>(nullptr, nullptr, gin, gout, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+    ST_FFT_PASS(8, true, true, 1, nullptr, nullptr, 1);
     return;
   }
-  stockham_pass<8, true, false>(nullptr, a, gin, nullptr, window, L.in_i, L.out_i, n, 1, complex_in, inverse, scale);
+  ST_FFT_PASS(8, true, false, 1, nullptr, a, 1);
   __syncthreads();
   float2* src = a;
   float2* dst = b;
   int ns = 8;
   for (int p = 1; p < eights; ++p) {
     if (p == eights - 1 && tail == 1) {
-      stockham_pass<8, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
+      if (p == 1) ST_FFT_PASS(8, false, true, 8, src, nullptr, 8);
+      else if (p == 2) ST_FFT_PASS(8, false, true, 64, src, nullptr, 64);
+      else ST_FFT_PASS(8, false, true, 0, src, nullptr, ns);
       return;
     }
-    stockham_pass<8, false, false>(src, dst, nullptr, nullptr, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
+    if (p == 1) ST_FFT_PASS(8, false, false, 8, src, dst, 8);
+    else if (p == 2) ST_FFT_PASS(8, false, false, 64, src, dst, 64);
+    else ST_FFT_PASS(8, false, false, 0, src, dst, ns);
     __syncthreads();
     float2* t = src; src = dst; dst = t;
     ns *= 8;
   }
-  if (tail == 2) stockham_pass<2, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
-  else stockham_pass<4, false, true>(src, nullptr, nullptr, gout, window, L.in_i, L.out_i, n, ns, complex_in, inverse, scale);
+  if (tail == 2) ST_FFT_PASS(2, false, true, 0, src, nullptr, ns);
+  else ST_FFT_PASS(4, false, true, 0, src, nullptr, ns);
+#undef ST_FFT_PASS
 }
 
 // Direct DFT for lengths that are not powers of two: out[k] = sum_i x[i] * w^(k*i mod n), twiddles from a table.
@@ -325,21 +374,27 @@ ST_API int st_fft_1d(const StFftArgs* a, void* stream_v) {
   FftLayout L{a->in_b0, a->in_b1, a->in_i, a->out_b0, a->out_b1, a->out_i, a->batch1};
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const int grid = a->batch0 * a->batch1;
-  const size_t padded = (size_t)a->n + (((size_t)a->n - 1) >> 6 << 3);          // the kernel's pad_idx(n - 1) + 1
+  const size_t padded = (size_t)a->n + (((size_t)a->n - 1) >> 6 << 3);          // 8 slots of padding per 64 points, as slot() in the kernel
   const size_t smem = pow2 ? 2 * padded * sizeof(float2) : 2 * (size_t)a->n * sizeof(float2);
   static bool configured[st::kMaxDevices][2] = {};
   const int dev = st::current_device();
   if (pow2) {
     if (smem > 48 * 1024 && !configured[dev][0]) {
-      ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         2 * (kMaxFftLen + kMaxFftLen / 8) * (int)sizeof(float2)));
+      const int max_smem = 2 * (kMaxFftLen + kMaxFftLen / 8) * (int)sizeof(float2);
+      ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
       configured[dev][0] = true;
     }
     int log2n = 0;
     while ((1 << log2n) < a->n) ++log2n;
     int threads = a->n / 8;                    // one radix-8 butterfly per thread and pass
     threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
-    fft_pow2_kernel<<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
+    // interleaved complex on both sides with unit stride and 8-byte aligned transforms: float2 loads and stores
+    const bool vec = a->complex_in && a->in_i == 2 && a->out_i == 2 && a->n > 1 &&
+                     ((a->in_b0 | a->in_b1 | a->out_b0 | a->out_b1) & 1) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a->in) | reinterpret_cast<uintptr_t>(a->out)) & 7) == 0;
+    if (vec) fft_pow2_kernel<true><<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
+    else fft_pow2_kernel<false><<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
   } else {
     if (smem > 48 * 1024 && !configured[dev][1]) {
       ST_CUDA_CHECK(cudaFuncSetAttribute(dft_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kMaxDftLen * (int)sizeof(float2)));

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -110,6 +111,30 @@ def _bias_args(a, q, k, key_bias, attn_bias, lengths, keep: list) -> None:
         a.lengths = ln.data_ptr()
 
 
+def set_pair_kernel(on: bool) -> None:
+    """Plain (no bias, no lengths) forward attention runs the pair kernel by default: two 128-row query tiles per
+    CTA share every K / V tile, with the probabilities and the output accumulator in tensor memory.  ``False``
+    selects the single-tile kernel, which the biased / variable-length cases always use."""
+    native.lib().st_attn_fwd_set_pair_kernel(1 if on else 0)
+
+
+def pair_kernel_enabled() -> bool:
+    return bool(native.lib().st_attn_fwd_get_pair_kernel())
+
+
+_env_applied = False
+
+
+def _apply_env_once() -> None:
+    """``ST_ATTN_FWD_PAIR=0`` in the environment selects the single-tile forward kernel for the whole process."""
+    global _env_applied
+    if not _env_applied:
+        _env_applied = True
+        v = os.environ.get("ST_ATTN_FWD_PAIR")
+        if v is not None:
+            set_pair_kernel(v.strip() not in ("0", "false", "off", ""))
+
+
 def _check_layout(t: torch.Tensor, name: str) -> None:
     if t.dim() != 4 or t.stride(-1) != 1 or t.dtype != torch.bfloat16:
         raise ValueError(f"{name} must be a bf16 [B,S,H,D] view with contiguous D")
@@ -137,6 +162,7 @@ def attention_forward(q, k, v, causal: bool = True, scale: Optional[float] = Non
         o, lse = attention_reference(q, k, v, causal, scale, key_bias=key_bias, attn_bias=attn_bias, lengths=lengths)
         return o.to(q.dtype).contiguous(), lse
     native.require_cuda("attention_forward", q, k, v, key_bias, attn_bias, lengths)
+    _apply_env_once()
     _check_shapes(q, k, v)
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_layout(t, n)

@@ -94,6 +94,35 @@ def test_attention_fwd_bwd(D, B, S, H, causal):
     _no_device_error()
 
 
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("B,Sq,Sk,H,D,causal", [(4, 2048, 2048, 8, 128, True), (1, 200, 333, 2, 128, False),
+                                                  (3, 640, 640, 5, 64, True), (1, 129, 129, 1, 64, True),
+                                                  (2, 384, 1000, 2, 64, False)])
+def test_attention_fwd_pair_and_single_tile_kernels(pair, B, Sq, Sk, H, D, causal):
+    """Both forward kernels (two query tiles per CTA with P and O in tensor memory; one tile per CTA) against the fp32
+    statement: more work items than SMs, ragged tails in queries and keys, an odd number of query tiles, and logits
+    whose running maximum grows by more than the lazy-rescale step."""
+    from spiraltorch_b200.ops import attention as A
+    torch.manual_seed(7)
+    q = torch.randn(B, Sq, H, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, Sk, H, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, Sk, H, D, device="cuda", dtype=torch.bfloat16)
+    # later keys get larger logits, so the running maximum keeps rising across KV tiles
+    ramp = torch.linspace(0.5, 4.0, Sk, device="cuda").view(1, Sk, 1, 1)
+    k = (k * ramp).to(torch.bfloat16)
+    was = A.pair_kernel_enabled()
+    try:
+        A.set_pair_kernel(pair)
+        o, lse = A.attention_forward(q, k, v, causal=causal)
+        torch.cuda.synchronize()
+    finally:
+        A.set_pair_kernel(was)
+    o_ref, lse_ref = A.attention_reference(q.float(), k.float(), v.float(), causal, 1.0 / D ** 0.5)
+    assert torch.isfinite(o.float()).all()
+    assert (o.float() - o_ref).abs().max().item() < 3e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
 @pytest.mark.parametrize("rms", [True, False])
 @pytest.mark.parametrize("rows,d", [(64, 768), (1000, 2048), (33, 8192), (7, 264)])
 def test_norm_fwd_bwd(rms, rows, d):
