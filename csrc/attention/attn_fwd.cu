@@ -47,12 +47,19 @@ struct AttnFwdParams {
   const float* attn_bias;      // [B, (H,) Sq, Sk] or null; element strides ab_sb, ab_sh, ab_sq (keys contiguous)
   const int* lengths;          // [B] valid keys (and queries) per batch entry, or null
   long long kb_sb, kb_sh, ab_sb, ab_sh, ab_sq;
+  // ---- pair kernel only: optional phase clock sums of CTA 0 (null = off) ----
+  unsigned long long* trace;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// bf16 pair of two positive finite floats by integer arithmetic (round half up, then the two upper halves): the
+// conversion instruction shares the 16-lane pipe with ex2, which is the softmax warps' bottleneck.
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 __device__ __forceinline__ void pair_sync(int quad) {
   asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
@@ -434,6 +441,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // tile's warpgroup is in its softmax.  Shared-memory traffic per query tile and KV tile drops from 224 KB (two
 // operand reads per product, K and V written per tile, P written and read) to 128 KB.
 // ------------------------------------------------------------------------------------------------------------------
+// Phase clocks of CTA 0 (SM cycles summed over the launch), written when tracing is switched on:
+//   softmax warp 0:  0 steps, 1 wait for S, 2 S load, 3 maximum / rescale, 4 first half of P, 5 second half of P,
+//                    6 output, 7 items
+//   MMA thread:      8 PV calls, 9 wait first half of P, 10 wait V, 11 first four PV steps, 12 wait second half,
+//                    13 last four PV steps and commits, 14 QK waits (Q, K), 15 QK issue and commits
+constexpr int PAIR_TRACE_SLOTS = 16;
+__device__ unsigned long long g_pair_trace[PAIR_TRACE_SLOTS];
 constexpr int PAIR_THREADS = 384;   // two softmax warpgroups + one warpgroup holding the producer and MMA warps
 // Registers are a per-scheduler pool of 512 per lane shared by three warps here (launch allocation 168 each): the
 // producer / MMA warpgroup hands its share back and each softmax warp, which keeps a 128-column row of S live, grows.
@@ -473,13 +487,21 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* s_full = bars + 12;        // 2
   uint64_t* p_full = bars + 14;        // 2 (one arrival per softmax warp of the tile)
   uint64_t* o_full = bars + 16;        // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* p_half = bars + 18;        // 2: the first 64 columns of P_t are in TMEM (PV starts on them)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hb = p.H * p.B;
   const int n_pairs = (p.n_q + 1) / 2;
   const int n_kv_all = (p.Sk + BLK - 1) / BLK;
+  // Items are sorted by decreasing work; round k hands items [k G, (k + 1) G) to the G CTAs in alternating direction
+  // (CTA i takes k G + i in even rounds and k G + G - 1 - i in odd ones), which keeps the per-CTA sums within a few
+  // percent of each other where a plain stride would leave the first CTAs with the heavy end of every round.
+  auto item_of_round = [&](int round) {
+    const int G = gridDim.x, i = blockIdx.x;
+    return round * G + ((round & 1) ? G - 1 - i : i);
+  };
   // Work item w -> (query pair, head, batch) and the KV tiles each of its two query tiles visits
   auto item_at = [&](int w, int& qp, int& h, int& b, int& n0, int& n1) {
     qp = n_pairs - 1 - w / hb;
@@ -496,6 +518,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(smem_u32(&q_empty[i]), 1);
       mbar_init(smem_u32(&s_full[i]), 1);
       mbar_init(smem_u32(&p_full[i]), 4);
+      mbar_init(smem_u32(&p_half[i]), 4);
       mbar_init(smem_u32(&o_full[i]), 1);
     }
     for (int i = 0; i < PAIR_STAGES; ++i) {
@@ -525,7 +548,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       int g = 0;                 // KV tiles loaded so far over all items: K at ring index 2g, V at 2g + 1
       int items_t[2] = {0, 0};   // items in which query tile t took part (phase of q_full / q_empty)
       bool ok = true;
-      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+      for (int round = 0; ok; ++round) {
+        const int w = item_of_round(round);
+        if (w >= p.n_items) break;
         int qp, h, b, n_t[2];
         item_at(w, qp, h, b, n_t[0], n_t[1]);
         const int n_kv = max(n_t[0], n_t[1]);
@@ -569,51 +594,75 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       uint32_t steps_t[2] = {0, 0};   // softmax steps of tile t consumed so far (phase of p_full)
       int items_t[2] = {0, 0};
       int n_t[2] = {0, 0};
+      // Descriptor words are formed once: the high word is common to every tile, the low word of a K step is the
+      // tile's low word plus a compile-time offset, so an MMA costs a handful of instructions in this single
+      // issuing thread (which otherwise, not the tensor pipe, sets the pace).
+      constexpr uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(smem + L::Q_OFF), 16);
+      const uint32_t k_lo0 = smem_desc_lo(smem_u32(smem + L::KV_OFF), 16);           // K tiles: K-major
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(smem + L::KV_OFF), BLK * 128);    // V tiles: MN-major
       // The K (V) tile of step j is released by the last product that reads it: tile 1's when tile 1 visits step j.
+      const bool tr = p.trace != nullptr && blockIdx.x == 0;
+      uint32_t c0 = 0, c1 = 0;
+      uint32_t tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       auto issue_qk = [&](int t, int j) -> bool {
+        if (tr) c0 = static_cast<uint32_t>(clock());
         if (j == 0 && !mbar_wait(smem_u32(&q_full[t]), items_t[t] & 1, abort_flag)) return false;
         const int idx = 2 * (g + j);
         const int st = idx % PAIR_STAGES;
         if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + L::Q_OFF + t * L::TILE);
-        const uint32_t sk = smem_u32(smem + L::KV_OFF + st * L::TILE);
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[6] += c1 - c0; }
+        const uint32_t a_lo = q_lo0 + t * (L::TILE >> 4);
+        const uint32_t b_lo = k_lo0 + st * (L::TILE >> 4);
         const uint32_t d_tmem = tmem_base + S_COL + t * BLK;
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_smem_desc_sw128(sq + kb * (BLK * 128) + k * 32, 16, 1024);
-            const uint64_t db = make_smem_desc_sw128(sk + kb * (BLK * 128) + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc_s, (kb | k) != 0 ? 1u : 0u);
+            const uint32_t off = (kb * (BLK * 128) + k * 32) >> 4;
+            umma_bf16_ss_split(d_tmem, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
         umma_commit(smem_u32(&s_full[t]));
         if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
         if (j == n_t[t] - 1) umma_commit(smem_u32(&q_empty[t]));
+        if (tr) tacc[7] += static_cast<uint32_t>(clock()) - c1;
         return true;
       };
       auto issue_pv = [&](int t, int j) -> bool {
-        if (!mbar_wait(smem_u32(&p_full[t]), steps_t[t] & 1u, abort_flag)) return false;
-        ++steps_t[t];
+        if (tr) c0 = static_cast<uint32_t>(clock());
+        if (!mbar_wait(smem_u32(&p_half[t]), steps_t[t] & 1u, abort_flag)) return false;
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[1] += c1 - c0; tacc[0] += 1; c0 = c1; }
         const int idx = 2 * (g + j) + 1;
         const int st = idx % PAIR_STAGES;
         if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sv = smem_u32(smem + L::KV_OFF + st * L::TILE);
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[2] += c1 - c0; c0 = c1; }
+        const uint32_t b_lo = v_lo0 + st * (L::TILE >> 4);
         const uint32_t a_tmem = tmem_base + S_COL + t * BLK;
         const uint32_t d_tmem = tmem_base + O_COL + t * D;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk) {
+          if (kk == BLK / 32) {    // the second half of P_t
+            if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[3] += c1 - c0; c0 = c1; }
+            if (!mbar_wait(smem_u32(&p_full[t]), steps_t[t] & 1u, abort_flag)) return false;
+            tc_fence_after();
+            if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[4] += c1 - c0; c0 = c1; }
+          }
           // A = P from TMEM (8 columns per K = 16 step); B = V (MN-major: D contiguous, KV rows = K)
-          const uint64_t db = make_smem_desc_sw128(sv + kk * (16 * 128), BLK * 128, 1024);
-          umma_bf16_ts(d_tmem, a_tmem + kk * 8, db, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+          umma_bf16_ts_split(d_tmem, a_tmem + kk * 8, b_lo + ((kk * (16 * 128)) >> 4), desc_hi, idesc_pv,
+                             (j | kk) != 0 ? 1u : 0u);
         }
+        ++steps_t[t];
         if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
         if (j == n_t[t] - 1) umma_commit(smem_u32(&o_full[t]));
+        if (tr) tacc[5] += static_cast<uint32_t>(clock()) - c0;
         return true;
       };
       bool ok = true;
-      for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+      for (int round = 0; ok; ++round) {
+        const int w = item_of_round(round);
+        if (w >= p.n_items) break;
         int qp, h, b;
         item_at(w, qp, h, b, n_t[0], n_t[1]);
         const int n_kv = max(n_t[0], n_t[1]);
@@ -632,6 +681,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (n_t[0] > 0) ++items_t[0];
         if (n_t[1] > 0) ++items_t[1];
       }
+      if (tr)
+        for (int i = 0; i < 8; ++i) p.trace[8 + i] += tacc[i];
     }
   }
   } else {
@@ -647,7 +698,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t steps = 0;   // softmax steps done (phase of s_full)
     int items = 0;        // items this tile took part in (phase of o_full)
     bool ok = true;
-    for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+    const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+    uint32_t c0 = 0, c1 = 0;
+    uint32_t tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int round = 0; ok; ++round) {
+        const int w = item_of_round(round);
+        if (w >= p.n_items) break;
       int qp, h, b, n0, n1;
       item_at(w, qp, h, b, n0, n1);
       const int n_kv = t == 0 ? n0 : n1;
@@ -656,9 +712,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int row_g = q_tile * BLK + r;
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j < n_kv; ++j) {
+        if (tr) c0 = static_cast<uint32_t>(clock());
         if (!mbar_wait_warp(smem_u32(&s_full[t]), steps & 1u, abort_flag)) { ok = false; break; }
         ++steps;
         tc_fence_after();
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[1] += c1 - c0; tacc[0] += 1; c0 = c1; }
         uint32_t sr[BLK];
         {
           uint32_t t0[32], t1[32], t2[32], t3[32];
@@ -670,6 +728,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int c = 0; c < 32; ++c) { sr[c] = t0[c]; sr[32 + c] = t1[c]; sr[64 + c] = t2[c]; sr[96 + c] = t3[c]; }
         }
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[2] += c1 - c0; c0 = c1; }
         const int col0 = j * BLK;
         float mx = -INFINITY;
         if ((p.causal && j == q_tile) || col0 + BLK > p.Sk) {
@@ -718,6 +777,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tmem_st_32x32(o_addr + ch * 32, v);
           }
         }
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[3] += c1 - c0; c0 = c1; }
         const float m_ref = (m == -INFINITY) ? 0.0f : m;
         const float2 sc2 = make_float2(sc, sc);
         const float2 nm2 = make_float2(-m_ref, -m_ref);
@@ -731,17 +791,26 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const float2 x = fma2(make_float2(__uint_as_float(sr[cc]), __uint_as_float(sr[cc + 1])), sc2, nm2);
             const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
             rs2[c & 1] = add2(rs2[c & 1], e);
-            pr[c] = pack_bf16x2(e.x, e.y);
+            pr[c] = pack_bf16x2_alu(e.x, e.y);
           }
           tmem_st_32x32(s_addr + hlf * 32, pr);
+          if (hlf == 0) {          // PV_t may start on the first 64 keys while the rest is computed
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_half[t]));
+            if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[4] += c1 - c0; c0 = c1; }
+          }
         }
         l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&p_full[t]));
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[5] += c1 - c0; }
       }
       if (!ok) break;
+      if (tr) c0 = static_cast<uint32_t>(clock());
       // ---- output: O_t / l as bf16, one row per thread; log-sum-exp in natural units ----
       if (!mbar_wait_warp(smem_u32(&o_full[t]), items & 1, abort_flag)) { ok = false; break; }
       ++items;
@@ -768,10 +837,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (row_g < p.Sq)
         p.lse[((long long)b * p.H + h) * p.Sq + row_g] =
             (l > 0.0f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (tr) { tacc[6] += static_cast<uint32_t>(clock()) - c0; tacc[7] += 1; }
       // the next item's first PV_t overwrites O_t only after this warpgroup's next p_full arrival, which follows
       // these loads in program order
       tc_fence_before();
     }
+    if (tr)
+      for (int i = 0; i < 8; ++i) p.trace[i] += tacc[i];
   }
 
   tc_fence_before();
@@ -816,6 +888,23 @@ struct StAttnFwdArgs {
 // 1 (default): plain attention runs the pair kernel (two query tiles per CTA, P and O in TMEM); 0: the single-tile
 // kernel for every case.  The biased / variable-length instantiation always uses the single-tile kernel.
 static int g_pair_kernel = 1;
+static int g_pair_trace_on = 0;
+// Phase tracing of the pair kernel (CTA 0 only; slots listed at g_pair_trace): on = 1 zeroes the sums and makes
+// later launches add to them, st_attn_fwd_read_trace copies the 16 sums out after a synchronisation.
+ST_API int st_attn_fwd_set_trace(int on) {
+  g_pair_trace_on = on ? 1 : 0;
+  if (on) {
+    unsigned long long zeros[PAIR_TRACE_SLOTS] = {};
+    ST_CUDA_CHECK(cudaMemcpyToSymbol(g_pair_trace, zeros, sizeof(zeros)));
+  }
+  return ST_OK;
+}
+ST_API int st_attn_fwd_read_trace(unsigned long long* out, int n) {
+  if (!out || n < PAIR_TRACE_SLOTS) return st::fail(ST_ERR_INVALID, "attn_fwd_read_trace: need room for 16 values");
+  ST_CUDA_CHECK(cudaDeviceSynchronize());
+  ST_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(unsigned long long) * PAIR_TRACE_SLOTS));
+  return ST_OK;
+}
 ST_API void st_attn_fwd_set_pair_kernel(int on) { g_pair_kernel = on ? 1 : 0; }
 ST_API int st_attn_fwd_get_pair_kernel() { return g_pair_kernel; }
 
@@ -848,11 +937,13 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
   p.key_bias = a->key_bias; p.kb_sb = a->kb_sb; p.kb_sh = a->kb_sh;
   p.attn_bias = a->attn_bias; p.ab_sb = a->ab_sb; p.ab_sh = a->ab_sh; p.ab_sq = a->ab_sq;
   p.lengths = a->lengths;
+  p.trace = nullptr;
   const bool biased = a->key_bias || a->attn_bias || a->lengths;
   if (p.n_items <= 0) return ST_OK;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_v);
   if (!biased && g_pair_kernel) {
     // two query tiles per CTA: the items are (query pair, head, batch)
+    if (g_pair_trace_on) ST_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.trace), g_pair_trace));
     p.n_items = ((p.n_q + 1) / 2) * a->H * a->B;
     const dim3 pgrid(std::min(p.n_items, st::sm_count()));
     static bool pcfg[2][st::kMaxDevices] = {{false}};
