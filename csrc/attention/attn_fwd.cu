@@ -61,6 +61,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
   return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
+// exp2 of two values on the FMA pipe (the 16-lane ex2 unit is what the softmax warps queue on): round to the nearest
+// integer n with the 1.5 * 2^23 trick, a cubic in f = x - n on [-0.5, 0.5] (relative error 7.5e-5, far below the
+// bf16 rounding of P) and n added into the exponent field.  Inputs at or below -125 (masked logits) give ~2^-125.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float2 big = make_float2(12582912.0f, 12582912.0f);
+  x.x = fmaxf(x.x, -125.0f);
+  x.y = fmaxf(x.y, -125.0f);
+  const float2 t = add2(x, big);
+  const float2 n = add2(t, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = fma2(n, make_float2(-1.0f, -1.0f), x);
+  float2 q = fma2(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
+  q = fma2(q, f, make_float2(0.6932609677f, 0.6932609677f));
+  q = fma2(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
+}
 __device__ __forceinline__ void pair_sync(int quad) {
   asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
 }
@@ -448,6 +464,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //                    13 last four PV steps and commits, 14 QK waits (Q, K), 15 QK issue and commits
 constexpr int PAIR_TRACE_SLOTS = 16;
 __device__ unsigned long long g_pair_trace[PAIR_TRACE_SLOTS];
+constexpr int PAIR_POLY_OF_4 = 2;   // share of the exponentials computed on the FMA pipe instead of the ex2 unit
 constexpr int PAIR_THREADS = 384;   // two softmax warpgroups + one warpgroup holding the producer and MMA warps
 // Registers are a per-scheduler pool of 512 per lane shared by three warps here (launch allocation 168 each): the
 // producer / MMA warpgroup hands its share back and each softmax warp, which keeps a 128-column row of S live, grows.
@@ -587,7 +604,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (warp == 9) {
     // ---------------------------- MMA issuer -----------------------------------------------------
-    if (lane == 0) {
+    // The whole warp walks the schedule in step (every value below is warp-uniform, so the compiler can keep the
+    // descriptors in uniform registers, which is where tcgen05.mma reads them) and one elected lane issues.
+    {
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(BLK, D, false, true);
       int g = 0;
@@ -605,57 +625,67 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool tr = p.trace != nullptr && blockIdx.x == 0;
       uint32_t c0 = 0, c1 = 0;
       uint32_t tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      const bool leader = elect_one();
       auto issue_qk = [&](int t, int j) -> bool {
         if (tr) c0 = static_cast<uint32_t>(clock());
-        if (j == 0 && !mbar_wait(smem_u32(&q_full[t]), items_t[t] & 1, abort_flag)) return false;
+        if (j == 0 && !mbar_wait_warp(smem_u32(&q_full[t]), items_t[t] & 1, abort_flag)) return false;
         const int idx = 2 * (g + j);
         const int st = idx % PAIR_STAGES;
-        if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait_warp(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
         if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[6] += c1 - c0; }
         const uint32_t a_lo = q_lo0 + t * (L::TILE >> 4);
         const uint32_t b_lo = k_lo0 + st * (L::TILE >> 4);
-        const uint32_t d_tmem = tmem_base + S_COL + t * BLK;
+        const uint32_t d_tmem = tmem_u + S_COL + t * BLK;
+        if (leader) {
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb)
+          for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t off = (kb * (BLK * 128) + k * 32) >> 4;
-            umma_bf16_ss_split(d_tmem, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc_s, (kb | k) != 0 ? 1u : 0u);
-          }
-        umma_commit(smem_u32(&s_full[t]));
-        if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
-        if (j == n_t[t] - 1) umma_commit(smem_u32(&q_empty[t]));
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t off = (kb * (BLK * 128) + k * 32) >> 4;
+              umma_bf16_ss_split(d_tmem, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc_s, (kb | k) != 0 ? 1u : 0u);
+            }
+          umma_commit(smem_u32(&s_full[t]));
+          if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
+          if (j == n_t[t] - 1) umma_commit(smem_u32(&q_empty[t]));
+        }
+        __syncwarp();
         if (tr) tacc[7] += static_cast<uint32_t>(clock()) - c1;
         return true;
       };
       auto issue_pv = [&](int t, int j) -> bool {
         if (tr) c0 = static_cast<uint32_t>(clock());
-        if (!mbar_wait(smem_u32(&p_half[t]), steps_t[t] & 1u, abort_flag)) return false;
+        if (!mbar_wait_warp(smem_u32(&p_half[t]), steps_t[t] & 1u, abort_flag)) return false;
         if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[1] += c1 - c0; tacc[0] += 1; c0 = c1; }
         const int idx = 2 * (g + j) + 1;
         const int st = idx % PAIR_STAGES;
-        if (!mbar_wait(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait_warp(smem_u32(&kv_full[st]), (idx / PAIR_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
         if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[2] += c1 - c0; c0 = c1; }
         const uint32_t b_lo = v_lo0 + st * (L::TILE >> 4);
-        const uint32_t a_tmem = tmem_base + S_COL + t * BLK;
-        const uint32_t d_tmem = tmem_base + O_COL + t * D;
+        const uint32_t a_tmem = tmem_u + S_COL + t * BLK;
+        const uint32_t d_tmem = tmem_u + O_COL + t * D;
+        // A = P from TMEM (8 columns per K = 16 step); B = V (MN-major: D contiguous, KV rows = K)
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk) {
-          if (kk == BLK / 32) {    // the second half of P_t
-            if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[3] += c1 - c0; c0 = c1; }
-            if (!mbar_wait(smem_u32(&p_full[t]), steps_t[t] & 1u, abort_flag)) return false;
-            tc_fence_after();
-            if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[4] += c1 - c0; c0 = c1; }
-          }
-          // A = P from TMEM (8 columns per K = 16 step); B = V (MN-major: D contiguous, KV rows = K)
-          umma_bf16_ts_split(d_tmem, a_tmem + kk * 8, b_lo + ((kk * (16 * 128)) >> 4), desc_hi, idesc_pv,
-                             (j | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BLK / 32; ++kk)
+            umma_bf16_ts_split(d_tmem, a_tmem + kk * 8, b_lo + ((kk * (16 * 128)) >> 4), desc_hi, idesc_pv,
+                               (j | kk) != 0 ? 1u : 0u);
         }
+        __syncwarp();
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[3] += c1 - c0; c0 = c1; }
+        if (!mbar_wait_warp(smem_u32(&p_full[t]), steps_t[t] & 1u, abort_flag)) return false;   // second half of P_t
+        tc_fence_after();
+        if (tr) { c1 = static_cast<uint32_t>(clock()); tacc[4] += c1 - c0; c0 = c1; }
+        if (leader) {
+#pragma unroll
+          for (int kk = BLK / 32; kk < BLK / 16; ++kk)
+            umma_bf16_ts_split(d_tmem, a_tmem + kk * 8, b_lo + ((kk * (16 * 128)) >> 4), desc_hi, idesc_pv, 1u);
+          if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
+          if (j == n_t[t] - 1) umma_commit(smem_u32(&o_full[t]));
+        }
+        __syncwarp();
         ++steps_t[t];
-        if (t == 1 || j >= n_t[1]) umma_commit(smem_u32(&kv_empty[st]));
-        if (j == n_t[t] - 1) umma_commit(smem_u32(&o_full[t]));
         if (tr) tacc[5] += static_cast<uint32_t>(clock()) - c0;
         return true;
       };
@@ -681,7 +711,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (n_t[0] > 0) ++items_t[0];
         if (n_t[1] > 0) ++items_t[1];
       }
-      if (tr)
+      if (tr && lane == 0)
         for (int i = 0; i < 8; ++i) p.trace[8 + i] += tacc[i];
     }
   }
@@ -741,13 +771,16 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             mx = fmaxf(mx, s);
           }
         } else {
-          float mx1 = -INFINITY;
+          float mc[8];                                 // eight independent chains
 #pragma unroll
-          for (int c = 0; c < BLK; c += 4) {
-            mx = max3(mx, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-            mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          for (int q = 0; q < 8; ++q) mc[q] = fmaxf(__uint_as_float(sr[2 * q]), __uint_as_float(sr[2 * q + 1]));
+#pragma unroll
+          for (int c = 16; c < BLK; c += 16) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              mc[q] = max3(mc[q], __uint_as_float(sr[c + 2 * q]), __uint_as_float(sr[c + 2 * q + 1]));
           }
-          mx = fmaxf(mx, mx1);
+          mx = fmaxf(fmaxf(max3(mc[0], mc[1], mc[2]), max3(mc[3], mc[4], mc[5])), fmaxf(mc[6], mc[7]));
         }
         const float m_new = fmaxf(m, mx * sc);
         bool raise = false;
@@ -789,7 +822,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int c = 0; c < 32; ++c) {
             const int cc = hlf * 64 + 2 * c;
             const float2 x = fma2(make_float2(__uint_as_float(sr[cc]), __uint_as_float(sr[cc + 1])), sc2, nm2);
-            const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            // PAIR_POLY_OF_4 of every four pairs take the polynomial, the rest the ex2 unit
+            const float2 e = (c & 3) < PAIR_POLY_OF_4 ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
             rs2[c & 1] = add2(rs2[c & 1], e);
             pr[c] = pack_bf16x2_alu(e.x, e.y);
           }
