@@ -56,27 +56,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// bf16 pair of two positive finite floats by integer arithmetic (round half up, then the two upper halves): the
-// conversion instruction shares the 16-lane pipe with ex2, which is the softmax warps' bottleneck.
-__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
-  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
-}
-// exp2 of two values on the FMA pipe (the 16-lane ex2 unit is what the softmax warps queue on): round to the nearest
-// integer n with the 1.5 * 2^23 trick, a cubic in f = x - n on [-0.5, 0.5] (relative error 7.5e-5, far below the
-// bf16 rounding of P) and n added into the exponent field.  Inputs at or below -125 (masked logits) give ~2^-125.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  const float2 big = make_float2(12582912.0f, 12582912.0f);
-  x.x = fmaxf(x.x, -125.0f);
-  x.y = fmaxf(x.y, -125.0f);
-  const float2 t = add2(x, big);
-  const float2 n = add2(t, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = fma2(n, make_float2(-1.0f, -1.0f), x);
-  float2 q = fma2(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
-  q = fma2(q, f, make_float2(0.6932609677f, 0.6932609677f));
-  q = fma2(q, f, make_float2(0.9999280572f, 0.9999280572f));
-  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
-}
 __device__ __forceinline__ void pair_sync(int quad) {
   asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
 }
@@ -464,7 +443,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //                    13 last four PV steps and commits, 14 QK waits (Q, K), 15 QK issue and commits
 constexpr int PAIR_TRACE_SLOTS = 16;
 __device__ unsigned long long g_pair_trace[PAIR_TRACE_SLOTS];
-constexpr int PAIR_POLY_OF_4 = 2;   // share of the exponentials computed on the FMA pipe instead of the ex2 unit
 constexpr int PAIR_THREADS = 384;   // two softmax warpgroups + one warpgroup holding the producer and MMA warps
 // Registers are a per-scheduler pool of 512 per lane shared by three warps here (launch allocation 168 each): the
 // producer / MMA warpgroup hands its share back and each softmax warp, which keeps a 128-column row of S live, grows.
@@ -822,10 +800,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int c = 0; c < 32; ++c) {
             const int cc = hlf * 64 + 2 * c;
             const float2 x = fma2(make_float2(__uint_as_float(sr[cc]), __uint_as_float(sr[cc + 1])), sc2, nm2);
-            // PAIR_POLY_OF_4 of every four pairs take the polynomial, the rest the ex2 unit
-            const float2 e = (c & 3) < PAIR_POLY_OF_4 ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
             rs2[c & 1] = add2(rs2[c & 1], e);
-            pr[c] = pack_bf16x2_alu(e.x, e.y);
+            pr[c] = pack_bf16x2(e.x, e.y);
           }
           tmem_st_32x32(s_addr + hlf * 32, pr);
           if (hlf == 0) {          // PV_t may start on the first 64 keys while the rest is computed
@@ -980,21 +957,19 @@ ST_API int st_attn_fwd(const StAttnFwdArgs* a, void* stream_v) {
     if (g_pair_trace_on) ST_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.trace), g_pair_trace));
     p.n_items = ((p.n_q + 1) / 2) * a->H * a->B;
     const dim3 pgrid(std::min(p.n_items, st::sm_count()));
-    static bool pcfg[2][st::kMaxDevices] = {{false}};
     const int dev = st::current_device();
-    if (a->D == 128) {
-      if (!pcfg[0][dev]) {
-        ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_pair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<128>::TOTAL));
-        pcfg[0][dev] = true;
+    auto plaunch = [&](auto kern, int smem_bytes, bool* cfg) -> int {
+      if (!cfg[dev]) {
+        ST_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        cfg[dev] = true;
       }
-      attn_fwd_pair_kernel<128><<<pgrid, PAIR_THREADS, PairSmem<128>::TOTAL, s>>>(tq, tk, tv, p);
-    } else {
-      if (!pcfg[1][dev]) {
-        ST_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_pair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<64>::TOTAL));
-        pcfg[1][dev] = true;
-      }
-      attn_fwd_pair_kernel<64><<<pgrid, PAIR_THREADS, PairSmem<64>::TOTAL, s>>>(tq, tk, tv, p);
-    }
+      kern<<<pgrid, PAIR_THREADS, smem_bytes, s>>>(tq, tk, tv, p);
+      return ST_OK;
+    };
+    static bool pcfg[2][st::kMaxDevices] = {{false}};
+    const int prc = a->D == 128 ? plaunch(attn_fwd_pair_kernel<128>, PairSmem<128>::TOTAL, pcfg[0])
+                                : plaunch(attn_fwd_pair_kernel<64>, PairSmem<64>::TOTAL, pcfg[1]);
+    if (prc != ST_OK) return prc;
     ST_CUDA_CHECK(cudaGetLastError());
     return ST_OK;
   }

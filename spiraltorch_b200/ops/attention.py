@@ -132,7 +132,7 @@ def _apply_env_once() -> None:
         _env_applied = True
         v = os.environ.get("ST_ATTN_FWD_PAIR")
         if v is not None:
-            set_pair_kernel(v.strip() not in ("0", "false", "off", ""))
+            set_pair_kernel(v.strip().lower() not in ("0", "false", "off", ""))
 
 
 def _check_layout(t: torch.Tensor, name: str) -> None:
