@@ -6,7 +6,7 @@
 """
 from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
                selfsup, softlogic, telemetry, text, theory, topos, tracking, vision, zspace_coherence, zvolume)
-from . import (elliptic, hub, inflaton, introspect, kdsl_ir, kv, macro_model, mellin, meta_narrative, microlocal, observation, psi_sync, psychoid, qr_studio, sot, relativity,
+from . import (elliptic, hub, inflaton, introspect, kdsl_ir, kv, macro_model, mellin, meta_narrative, microlocal, observation, psi_sync, psychoid, qr_studio, quantum_overlay, quantum_reality, sot, relativity,
                rg_flow, spiral_dynamics, stv, sync_bridge, unison, zpulse)  # noqa: E402  (network key/value client imports logic)
 from .nn.io import VERSION as __version__
 from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad
