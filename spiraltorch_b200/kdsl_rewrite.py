@@ -188,6 +188,8 @@ class SelfRewriteEngine:
         self.trace_limit = 0
         self.trace_log: deque = deque()
         self.generator_calls = 0
+        from .kdsl_policy import HintPolicyStack
+        self.policy = HintPolicyStack()
 
     # ---- configuration (builder style, like the reference) ----
     def with_eta_floor(self, v: float): self.eta_floor = v if v > 0 and math.isfinite(v) else self.eta_floor; return self   # noqa: E702
@@ -198,6 +200,36 @@ class SelfRewriteEngine:
     def with_max_staleness(self, n: int): self.max_staleness = max(1, n); return self              # noqa: E702
     def with_anomaly_patience(self, n: int): self.anomaly_patience = max(1, n); return self        # noqa: E702
     def enable_trace_mode(self, limit: int): self.trace_limit = max(1, limit); return self         # noqa: E702
+    # the learning layers (bandit, chain policy, transition / saga graphs, diversity governor): crates/st-kdsl/src/self_mod.rs:1461-1612
+    def with_diversity_window(self, n: int): self.policy.diversity.window = max(1, n); return self                      # noqa: E702
+    def with_diversity_threshold(self, v: float): self.policy.diversity.threshold = v if v >= 0 and math.isfinite(v) else self.policy.diversity.threshold; return self   # noqa: E702
+    def with_diversity_cooldown(self, n: int): self.policy.diversity.cooldown = max(1, n); return self                  # noqa: E702
+    def with_transition_decay(self, v: float): self.policy.transitions.decay_rate = min(v, 0.999) if v > 0 and math.isfinite(v) else self.policy.transitions.decay_rate; return self   # noqa: E702
+    def with_transition_fanout(self, n: int): self.policy.transitions.fanout = max(1, n); return self                   # noqa: E702
+    def with_saga_depth(self, n: int): self.policy.saga.set_depth(max(0, n)); return self                               # noqa: E702
+    def with_saga_decay(self, v: float): self.policy.saga.decay_rate = min(v, 0.999) if v > 0 and math.isfinite(v) else self.policy.saga.decay_rate; return self   # noqa: E702
+    def with_saga_fanout(self, n: int): self.policy.saga.fanout = max(1, n); return self                                # noqa: E702
+    def with_feedback_gamma(self, v: float): self.policy.feedback_gamma = max(0.01, min(1.0, v)); return self           # noqa: E702
+    def with_chain_learning_rate(self, v: float): self.policy.chain_policy.lr = max(0.05, min(1.0, v)); return self     # noqa: E702
+    def with_chain_discount(self, v: float): self.policy.chain_policy.discount = max(0.0, min(0.99, v)); return self    # noqa: E702
+    def with_chain_explore_bonus(self, v: float): self.policy.chain_policy.explore_bonus = max(0.0, v); return self     # noqa: E702
+    def with_chain_horizon(self, n: int): self.policy.chain_policy.horizon = max(1, n); return self                     # noqa: E702
+    def with_bandit_explore(self, v: float): self.policy.bandit.explore = max(0.0, v); return self                      # noqa: E702
+    def with_bandit_temperature(self, v: float): self.policy.bandit.temperature = max(0.1, v); return self              # noqa: E702
+    def with_bandit_learning_rate(self, v: float): self.policy.bandit.learning_rate = max(0.05, min(1.0, v)); return self   # noqa: E702
+    def with_bandit_decay(self, v: float): self.policy.bandit.decay_rate = min(v, 0.999) if v > 0 else self.policy.bandit.decay_rate; return self   # noqa: E702
+    def with_bandit_min_pulls(self, n: int): self.policy.bandit.min_pulls = max(1, n); return self                      # noqa: E702
+    def with_relation_decay(self, v: float): self.policy.relations.decay_rate = v; return self                          # noqa: E702
+    def with_relation_fanout(self, n: int): self.policy.relations.max_neighbors = max(1, n); return self                # noqa: E702
+
+    def transition_snapshots(self) -> list: return self.policy.transitions.snapshots()              # noqa: E704
+    def saga_snapshots(self) -> list: return self.policy.saga.snapshots()                           # noqa: E704
+    def chain_policy_snapshots(self) -> list: return self.policy.chain_policy.snapshots()           # noqa: E704
+    def bandit_snapshots(self) -> list: return self.policy.bandit.snapshots()                       # noqa: E704
+    def chain_feedback(self) -> list: return self.policy.snapshot()["chain_feedback"]              # noqa: E704
+    def relation_graph(self) -> list: return self.policy.relations.snapshots()                      # noqa: E704
+    def diversity_snapshot(self) -> dict: return self.policy.diversity.snapshot()                   # noqa: E704
+    def quality_model(self) -> dict: return self.policy.quality.snapshot()                          # noqa: E704
 
     # ---- introspection ----
     def smoothed_eta(self) -> Optional[float]:
@@ -256,22 +288,25 @@ class SelfRewriteEngine:
         decay = 0.5 ** (c.staleness / self.staleness_half_life)
         st = self.stats.get(c.key)
         record = 1.0 + (st.mean_gain() if st else 0.0) - 0.25 * (st.failures if st else 0)
-        return c.eta * decay * context_affinity(c.ctx_signature, sig) * max(record, 0.05)
+        quality = self.policy.quality_score(st.last_gain, st.mean_gain(), st.best_gain, st.last_affinity, c.staleness) if st else 0.0
+        return (c.eta + quality) * decay * context_affinity(c.ctx_signature, sig) * max(record, 0.05) * self.policy.priority_multiplier(c.key)
 
     def _penalize(self, key: str) -> None:
         st = self.stats.setdefault(key, HintStat(key))
         st.failures += 1
+        self.policy.record_failure(key, st.mean_gain(), st.best_gain, st.last_affinity)
         if st.failures >= self.anomaly_patience and key not in self.frozen:
             self.frozen[key] = self.freeze_cooldown
             self._trace("Frozen", f"key={key} failures={st.failures}")
 
-    def _success(self, key: str, observed: float, eta: float, affinity: float) -> float:
+    def _success(self, key: str, observed: float, eta: float, affinity: float, fresh: bool = False) -> float:
         gain = max(0.0, eta - observed)
         st = self.stats.setdefault(key, HintStat(key))
         st.uses += 1
         st.total_gain += gain
         st.best_gain = max(st.best_gain, gain)
         st.last_eta, st.last_affinity, st.last_gain = eta, affinity, gain
+        self.policy.record_success(key, gain, affinity, affinity, fresh, st.mean_gain(), st.best_gain)
         return gain
 
     def _push_cache(self, eta: float, hints, sig: int) -> None:
@@ -282,11 +317,15 @@ class SelfRewriteEngine:
 
     def tick(self, base_src: str, ctx: Ctx, metrics: Optional[WilsonMetrics], observed_eta: float) -> Optional[SelfRewriteEvent]:
         self._age()
+        self.policy.advance()
         smoothed = self.smoothed_eta()
         if observed_eta >= self.eta_floor and (observed_eta if smoothed is None else smoothed) >= self.eta_floor:
             return None
         sig = ctx_signature(ctx)
-        for c in sorted(self.cache, key=lambda c: -self._priority(c, sig)):
+        force_fresh = self.policy.should_force_fresh()          # stalled gains: skip the cache and ask the generator
+        if force_fresh:
+            self._trace("DiversityForce", f"debt={self.policy.diversity.debt}")
+        for c in ([] if force_fresh else sorted(self.cache, key=lambda c: -self._priority(c, sig))):
             if c.key in self.frozen:
                 self._trace("CachePenalty", f"skip frozen key={c.key}")
                 continue
@@ -310,6 +349,6 @@ class SelfRewriteEngine:
         event = self._eval(base_src, ctx, hints)
         self._record_eta(event.eta_bar)
         self._push_cache(event.eta_bar, event.hints, sig)
-        gain = self._success(hint_key(event.hints), observed_eta, event.eta_bar, 1.0)
+        gain = self._success(hint_key(event.hints), observed_eta, event.eta_bar, 1.0, fresh=True)
         self._trace("GeneratorSuccess", f"key={hint_key(event.hints)} gain={gain:.3f} eta={event.eta_bar:.3f}")
         return event
