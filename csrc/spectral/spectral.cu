@@ -11,6 +11,7 @@
 #include <math_constants.h>
 
 #include "../common/host.h"
+#include "../common/ptx.cuh"
 
 namespace {
 
@@ -219,6 +220,80 @@ fft_pow2_kernel(const float* __restrict__ in, float* __restrict__ out, const flo
 #undef ST_FFT_PASS
 }
 
+// Streaming form for long batches of contiguous complex rows: a persistent CTA walks rows blockIdx.x, + gridDim.x, ...
+// and, while it works through the passes of one row, a bulk asynchronous copy brings the next row into a staging
+// buffer, so the only exposed global-memory latency is that of the CTA's first row.  The first pass reads the staging
+// buffer; everything else is the kernel above.  n = 8^a * tail with a >= 2.
+__global__ void __launch_bounds__(512, 2)
+fft_pow2_stream_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ window,
+                       FftLayout L, int n, int log2n, int inverse, int batches, unsigned* err) {
+  extern __shared__ __align__(16) float2 smem[];
+  constexpr bool VEC = true;
+  constexpr int complex_in = 1;
+  const int padded = n + (((n - 1) >> 6) << 3);
+  float2* a = smem;
+  float2* b = smem + padded;
+  float2* stage = smem + 2 * padded;                                  // n complex values, 16-byte aligned (padded is a multiple of 8)
+  uint64_t* bar = reinterpret_cast<uint64_t*>(stage + n);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar + 1);
+  const uint32_t row_bytes = static_cast<uint32_t>(n) * 8u;
+  auto row_in = [&](int batch) { return in + (batch / L.batch1) * L.in_b0 + (batch % L.batch1) * L.in_b1; };
+  if (threadIdx.x == 0) {
+    st::mbar_init(st::smem_u32(bar), 1);
+    *abort_flag = 0;
+    st::fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < batches) {
+    st::mbar_arrive_expect_tx(st::smem_u32(bar), row_bytes);
+    st::bulk_load_g2s(st::smem_u32(stage), row_in(blockIdx.x), row_bytes, st::smem_u32(bar));
+  }
+  const float scale = inverse ? 1.0f / (float)n : 1.0f;
+  const int eights = log2n / 3, tail = 1 << (log2n - 3 * eights);
+  uint32_t phase = 0;
+  for (int batch = blockIdx.x; batch < batches; batch += gridDim.x) {
+    float* gout = out + (batch / L.batch1) * L.out_b0 + (batch % L.batch1) * L.out_b1;
+    const float* gin = reinterpret_cast<const float*>(stage);
+    // bounded wait; the CTA decides together, so nobody is left at a barrier by a thread that gave up
+    if (!__syncthreads_and(st::mbar_wait(st::smem_u32(bar), phase, abort_flag) ? 1 : 0)) break;
+    phase ^= 1u;
+#define ST_FFT_PASS(R, FIRST, LAST, NSC, SRC, DST, NS) \
+  stockham_pass<R, FIRST, LAST, NSC, VEC>(SRC, DST, gin, gout, window, L.in_i, L.out_i, n, NS, complex_in, inverse, scale)
+    ST_FFT_PASS(8, true, false, 1, nullptr, a, 1);
+    __syncthreads();                       // the staging buffer has been read by everyone: refill it with the next row
+    if (threadIdx.x == 0 && batch + static_cast<int>(gridDim.x) < batches) {
+      st::mbar_arrive_expect_tx(st::smem_u32(bar), row_bytes);
+      st::bulk_load_g2s(st::smem_u32(stage), row_in(batch + gridDim.x), row_bytes, st::smem_u32(bar));
+    }
+    float2* src = a;
+    float2* dst = b;
+    int ns = 8;
+    bool done = false;
+    for (int p = 1; p < eights && !done; ++p) {
+      if (p == eights - 1 && tail == 1) {
+        if (p == 1) ST_FFT_PASS(8, false, true, 8, src, nullptr, 8);
+        else if (p == 2) ST_FFT_PASS(8, false, true, 64, src, nullptr, 64);
+        else ST_FFT_PASS(8, false, true, 0, src, nullptr, ns);
+        done = true;
+        break;
+      }
+      if (p == 1) ST_FFT_PASS(8, false, false, 8, src, dst, 8);
+      else if (p == 2) ST_FFT_PASS(8, false, false, 64, src, dst, 64);
+      else ST_FFT_PASS(8, false, false, 0, src, dst, ns);
+      __syncthreads();
+      float2* t = src; src = dst; dst = t;
+      ns *= 8;
+    }
+    if (!done) {
+      if (tail == 2) ST_FFT_PASS(2, false, true, 0, src, nullptr, ns);
+      else ST_FFT_PASS(4, false, true, 0, src, nullptr, ns);
+    }
+#undef ST_FFT_PASS
+    __syncthreads();                       // the last pass has read its source before the next row's first pass writes `a`
+  }
+  if (*abort_flag && threadIdx.x == 0) st::report_error(err, st::ERR_MBAR_TIMEOUT, 0xF7F1u);
+}
+
 // Direct DFT for lengths that are not powers of two: out[k] = sum_i x[i] * w^(k*i mod n), twiddles from a table.
 __global__ void dft_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ window,
                            FftLayout L, int n, int complex_in, int inverse) {
@@ -393,7 +468,20 @@ ST_API int st_fft_1d(const StFftArgs* a, void* stream_v) {
     const bool vec = a->complex_in && a->in_i == 2 && a->out_i == 2 && a->n > 1 &&
                      ((a->in_b0 | a->in_b1 | a->out_b0 | a->out_b1) & 1) == 0 &&
                      ((reinterpret_cast<uintptr_t>(a->in) | reinterpret_cast<uintptr_t>(a->out)) & 7) == 0;
-    if (vec) fft_pow2_kernel<true><<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
+    // long batches of contiguous, 16-byte aligned rows: persistent CTAs with the next row prefetched asynchronously
+    const size_t stream_smem = smem + (size_t)a->n * sizeof(float2) + 16;
+    const bool streamed = vec && log2n >= 6 && a->n <= 4096 && grid > 4 * st::sm_count() &&
+                          ((a->in_b0 | a->in_b1) & 3) == 0 && (reinterpret_cast<uintptr_t>(a->in) & 15) == 0;
+    if (streamed) {
+      static bool stream_cfg[st::kMaxDevices] = {};
+      if (!stream_cfg[dev]) {
+        ST_CUDA_CHECK(cudaFuncSetAttribute(fft_pow2_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (2 * (4096 + 4096 / 8) + 4096) * (int)sizeof(float2) + 16));
+        stream_cfg[dev] = true;
+      }
+      fft_pow2_stream_kernel<<<2 * st::sm_count(), threads, stream_smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->inverse,
+                                                                                    grid, st::error_word());
+    } else if (vec) fft_pow2_kernel<true><<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
     else fft_pow2_kernel<false><<<grid, threads, smem, stream>>>(a->in, a->out, a->window, L, a->n, log2n, a->complex_in, a->inverse);
   } else {
     if (smem > 48 * 1024 && !configured[dev][1]) {

@@ -130,6 +130,22 @@ def test_fft_kernel_matches_torch(n):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("rows,n", [(2048, 4096), (1500, 512), (4001, 64), (700, 2048)])
+def test_streamed_fft_of_long_batches_matches_torch(rows, n):
+    """Batches longer than four rows per SM take the persistent kernel that prefetches the next row with a bulk
+    asynchronous copy; forward and inverse against torch, including a row count that leaves some CTAs one row short."""
+    torch.manual_seed(rows + n)
+    x = torch.randn(rows, n, device="cuda", dtype=torch.complex64)
+    ref = torch.fft.fft(x)
+    z = spectral.fft(x)
+    assert float((z - ref).abs().max()) <= 2e-5 * float(ref.abs().max()) * math.log2(n)
+    back = spectral.fft(z, inverse=True)
+    assert float((back - x).abs().max()) <= 5e-5 * math.log2(n) * float(x.abs().max())
+    from spiraltorch_b200.ops import native
+    native.raise_on_device_error()
+
+
+@pytest.mark.gpu
 def test_field_spectra_multipliers_and_renderer_on_gpu():
     torch.manual_seed(3)
     v = torch.rand(16, 32, 4)
