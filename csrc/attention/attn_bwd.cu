@@ -235,13 +235,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == EW_WARPS + 1) {
     // ---------------------------- MMA issuer -------------------------------------------
-    // The whole warp walks the schedule in step, so every descriptor word and TMEM address below is warp-uniform and
-    // can live in uniform registers (where tcgen05.mma reads its operands); one elected lane issues the MMAs and
-    // commits.  With the loop inside a single-lane branch each MMA cost the issuing thread ~85 cycles of register
-    // moves, more than the 64 cycles the tensor pipe needs for it.
-    {
-      const bool leader = elect_one();
-      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);   // S, dP
       constexpr uint32_t idesc_t = make_idesc_bf16(BLK, D, true, true);       // dV, dK
       constexpr uint32_t idesc_q = make_idesc_bf16(BLK, D, false, true);      // dQ
@@ -257,38 +251,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto a_mn = [&](int n) { return smem_desc_lo(smem_u32(smem + L::A_OFF + (n % NA) * L::TILE), BLK * 128); };
       auto b_k = [&](int n) { return smem_desc_lo(smem_u32(smem + L::B_OFF + (n % NB) * L::TILE), 16); };
       auto b_mn = [&](int n) { return smem_desc_lo(smem_u32(smem + L::B_OFF + (n % NB) * L::TILE), BLK * 128); };
-      auto wait_a = [&](int n) { return mbar_wait_warp(smem_u32(&a_full[n % NA]), (n / NA) & 1, abort_flag); };
-      auto wait_b = [&](int n) { return mbar_wait_warp(smem_u32(&b_full[n % NB]), (n / NB) & 1, abort_flag); };
+      auto wait_a = [&](int n) { return mbar_wait(smem_u32(&a_full[n % NA]), (n / NA) & 1, abort_flag); };
+      auto wait_b = [&](int n) { return mbar_wait(smem_u32(&b_full[n % NB]), (n / NB) & 1, abort_flag); };
       // S = Q·Kᵀ and dP = dO·Vᵀ: both operands K-major, D/16 K steps
       auto issue_sdp = [&](uint32_t col, uint32_t a_lo, uint32_t b_lo) {
-        if (!leader) return;
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t off = (kb * (BLK * 128) + k * 32) >> 4;
-            umma_bf16_ss_split(tmem_u + col, a_lo + off, HI, b_lo + off, HI, idesc_s, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss_split(tmem_base + col, a_lo + off, HI, b_lo + off, HI, idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
       };
       // accumulate GEMMs over the 128 rows of the streamed tile: A and B read through MN-major views
       auto issue_acc_mn = [&](uint32_t col, uint32_t a_lo, uint32_t b_lo, bool acc_first) {
-        if (!leader) return;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk) {
           const uint32_t off = (kk * (16 * 128)) >> 4;
-          umma_bf16_ss_split(tmem_u + col, a_lo + off, HI, b_lo + off, HI, idesc_t, (acc_first || kk != 0) ? 1u : 0u);
+          umma_bf16_ss_split(tmem_base + col, a_lo + off, HI, b_lo + off, HI, idesc_t, (acc_first || kk != 0) ? 1u : 0u);
         }
       };
-      auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
       auto issue_s = [&](int n) {
         if (MODE == MODE_KV) issue_sdp(S_COL, a_k(n), st0_k); else issue_sdp(S_COL, st0_k, a_k(n));
-        commit(smem_u32(s_full));
+        umma_commit(smem_u32(s_full));
       };
       auto issue_dp = [&](int n) {
         const uint32_t col = (MODE == MODE_Q && (n & 1)) ? ACC1_COL : DP_COL;
         if (MODE == MODE_KV) issue_sdp(col, b_k(n), st1_k); else issue_sdp(col, st1_k, b_k(n));
-        commit(smem_u32(&dp_full[n & 1]));
-        if (MODE == MODE_Q) commit(smem_u32(&b_empty[n % NB]));   // V is only needed by dP
+        umma_commit(smem_u32(&dp_full[n & 1]));
+        if (MODE == MODE_Q) umma_commit(smem_u32(&b_empty[n % NB]));   // V is only needed by dP
       };
       int g = 0, it = 0;
       bool ok = true;
@@ -297,7 +288,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (I.n_iter == 0) continue;
         // prologue: S and dP of the item's first tile.  Their TMEM columns are free: every iteration,
         // the previous item's last one included, waits for s_free and pds_full.
-        if (!(ok = mbar_wait_warp(smem_u32(stat_full), it & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(smem_u32(stat_full), it & 1, abort_flag))) break;
         if (!(ok = wait_a(g))) break;
         tc_fence_after();
         issue_s(g);
@@ -308,11 +299,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const bool more = n + 1 < I.n_iter;
           // every S / dP GEMM of the item has been issued: the stationary tiles can be replaced
           // as soon as those complete
-          if (!more) commit(smem_u32(stat_empty));
-          if (!(ok = mbar_wait_warp(smem_u32(s_free), g & 1, abort_flag))) break;
+          if (!more) umma_commit(smem_u32(stat_empty));
+          if (!(ok = mbar_wait(smem_u32(s_free), g & 1, abort_flag))) break;
           // the first accumulate GEMM of an item overwrites accumulators that the element-wise warps
           // may still be reading out for the previous item
-          if (n == 0 && it > 0 && !(ok = mbar_wait_warp(smem_u32(acc_free), (it - 1) & 1, abort_flag))) break;
+          if (n == 0 && it > 0 && !(ok = mbar_wait(smem_u32(acc_free), (it - 1) & 1, abort_flag))) break;
           tc_fence_after();
           if (more) {
             // S of the next tile, as soon as this tile's S has been read
@@ -329,31 +320,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (MODE == MODE_KV) {
             // dV[kv, d] += sum_q P[q, kv] dO[q, d], once P has been stored (S of the next tile is already
             // running: the element-wise warps release S before they convert and store P)
-            if (!(ok = mbar_wait_warp(smem_u32(p_ready), g & 1, abort_flag))) break;
+            if (!(ok = mbar_wait(smem_u32(p_ready), g & 1, abort_flag))) break;
             tc_fence_after();
             issue_acc_mn(ACC0_COL, p_mn, b_mn(g), n != 0);
-            commit(smem_u32(&b_empty[g % NB]));
-            commit(smem_u32(p_free));
+            umma_commit(smem_u32(&b_empty[g % NB]));
+            umma_commit(smem_u32(p_free));
           }
-          if (!(ok = mbar_wait_warp(smem_u32(pds_full), g & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(smem_u32(pds_full), g & 1, abort_flag))) break;
           tc_fence_after();
           if (MODE == MODE_KV) {
             // dK[kv, d] += sum_q dS[q, kv] Q[q, d]
             issue_acc_mn(ACC1_COL, ds_mn, a_mn(g), n != 0);
-            commit(smem_u32(&a_empty[g % NA]));
+            umma_commit(smem_u32(&a_empty[g % NA]));
           } else {
             // dQ[q, d] += sum_kv dS[q, kv] K[kv, d]: dS K-major, K through its MN-major view
             const uint32_t k_lo = a_mn(g);
-            if (leader)
 #pragma unroll
             for (int kk = 0; kk < BLK / 16; ++kk)
-              umma_bf16_ss_split(tmem_u + ACC0_COL, ds_k + (((kk >> 2) * (BLK * 128) + (kk & 3) * 32) >> 4), HI,
+              umma_bf16_ss_split(tmem_base + ACC0_COL, ds_k + (((kk >> 2) * (BLK * 128) + (kk & 3) * 32) >> 4), HI,
                                  k_lo + ((kk * (16 * 128)) >> 4), HI, idesc_q, (n | kk) != 0 ? 1u : 0u);
-            commit(smem_u32(&a_empty[g % NA]));
-            commit(smem_u32(ds_free));
+            umma_commit(smem_u32(&a_empty[g % NA]));
+            umma_commit(smem_u32(ds_free));
           }
           if (!more) {
-            commit(smem_u32(acc_done));
+            umma_commit(smem_u32(acc_done));
           } else if (MODE == MODE_KV) {
             // dP of the next tile: its columns were read before pds_full(g) completed
             if (!(ok = wait_b(g + 1))) break;
