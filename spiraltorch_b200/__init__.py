@@ -6,8 +6,8 @@
 """
 from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
                selfsup, softlogic, telemetry, text, theory, topos, tracking, vision, zspace_coherence, zvolume)
-from . import (elliptic, hub, inflaton, introspect, kdsl_ir, kv, macro_model, mellin, meta_narrative, microlocal, observation, psi_sync, psychoid, qr_studio, quantum_overlay, quantum_reality, sot, relativity,
-               rg_flow, spiral_dynamics, stv, sync_bridge, unison, zpulse)  # noqa: E402  (network key/value client imports logic)
+from . import (ecosystem, elliptic, hub, inflaton, introspect, kdsl_ir, kv, macro_model, mellin, meta_narrative, microlocal, observation, psi_sync, psychoid, qr_studio, quantum_overlay, quantum_reality, sot, relativity,
+               rg_flow, schrodinger, soft_learning, spiral_dynamics, stv, sync_bridge, unison, zpulse, zspace_posterior)  # noqa: E402  (network key/value client imports logic)
 from .nn.io import VERSION as __version__
 from .optim.amegagrad import AmegaHypergrad as Hypergrad, AmegaRealgrad as Realgrad
 from .session import SpiralSession, build_info, describe_device
