@@ -32,6 +32,11 @@ class TextResonator:
             raise ValueError("curvature must be negative and temperature positive")
         self.curvature, self.temperature = curvature, temperature
 
+    def describe_resonance(self, resonance) -> ResonanceNarrative:
+        """Narrative of a differential resonance (its five channels' squared norms): which band dominates, its share,
+        the total energy and the observed curvature -sqrt(homotopy energy).  crates/st-text/src/lib.rs:115-120, 656-760."""
+        return resonance_narrative(resonance)
+
     def describe_summary(self, s: ChronoSummary) -> ResonanceNarrative:
         level = "quiet" if s.mean_energy < 0.1 else "steady" if s.mean_energy < 1.0 else "energetic"
         drift = "flat" if abs(s.mean_drift) < 1e-3 else "rising" if s.mean_drift > 0 else "falling"
@@ -68,6 +73,55 @@ class TextResonator:
 
 
 # ---- frame / atlas narratives, realtime narrator, token semantics ------------------------------------------------
+_BAND_LABELS = ("Above band accelerating curvature", "Here band weaving functor linearisation",
+                "Beneath band anchoring recursive objective", "∞ projection tightening geodesics", "∞ hierarchy storing latent energy")
+_EPS32 = 1.1920929e-07
+
+
+def _sq_norm(t) -> float:
+    data = t.torch() if hasattr(t, "torch") else t
+    import torch
+    return float((torch.as_tensor(data, dtype=torch.float32) ** 2).sum())
+
+
+def resonance_narrative(resonance) -> ResonanceNarrative:
+    """``resonance`` has the channels homotopy_flow, functor_linearisation, recursive_objective, infinity_projection,
+    infinity_energy (tensors or anything array-like)."""
+    e = [_sq_norm(getattr(resonance, n)) for n in ("homotopy_flow", "functor_linearisation", "recursive_objective", "infinity_projection",
+                                                    "infinity_energy")]
+    e = [v if math.isfinite(v) and v > 0.0 else 0.0 for v in e]
+    total = sum(e)
+    if total <= _EPS32:
+        return ResonanceNarrative("Resonance geometry is quiescent; no meaningful curvature pulses detected.", ["all bands below activation threshold"])
+    curvature = -math.sqrt(e[0]) if e[0] > 0.0 else -1.0
+    lead = max(range(5), key=lambda i: (e[i], -i))                      # the first of equal bands leads
+    pct = [v / total for v in e]
+    summary = (f"{_BAND_LABELS[lead]} commanding {min(max(pct[lead], 0.0), 1.0) * 100.0:.1f}% of the field while total energy sits at "
+               f"{total:.3f} with curvature {curvature:+.3f}.")
+    highlights = [f"Above {pct[0] * 100:.1f}%", f"Here {pct[1] * 100:.1f}%", f"Beneath {pct[2] * 100:.1f}%", f"∞ proj {pct[3] * 100:.1f}%",
+                  f"∞ tower {pct[4] * 100:.1f}%", f"curvature {curvature:+.3f}"]
+    entropy = -sum(p * math.log(p) for p in pct if p > 0.0)
+    if entropy > 0.0:
+        highlights.append(f"band entropy {entropy:.2f}")
+    ordered = sorted(pct, reverse=True)
+    if ordered[0] - ordered[1] > 0.0:
+        highlights.append(f"dominant contrast {(ordered[0] - ordered[1]) * 100:.1f}%")
+    mean = sum(pct) / 5.0
+    spread = math.sqrt(sum((p - mean) ** 2 for p in pct) / 5.0)
+    if spread > 0.0:
+        highlights.append(f"band spread σ {spread * 100:.1f}%")
+    if entropy > 0.0:
+        highlights.append(f"band evenness {entropy / math.log(5.0) * 100:.1f}%")
+    active = sum(1 for p in pct if p > 0.05)
+    if active:
+        highlights.append(f"active bands {active}")
+    return ResonanceNarrative(summary, highlights)
+
+
+def describe_resonance(resonance) -> str:
+    return TextResonator(-1.0, 0.6).describe_resonance(resonance).summary
+
+
 def _frame_narrative(frame) -> ResonanceNarrative:
     """One temporal frame in words (crates/st-text/src/lib.rs:122-146)."""
     if frame.total_energy <= 1.1920929e-07:
