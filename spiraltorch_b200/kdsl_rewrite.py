@@ -190,6 +190,9 @@ class SelfRewriteEngine:
         self.generator_calls = 0
         from .kdsl_policy import HintPolicyStack
         self.policy = HintPolicyStack()
+        self.recombination_trials = 2
+        self.clusters: list = []                 # ContextCluster records of the contexts where hints paid off
+        self.cluster_limit, self.cluster_decay = 6, 0.9
 
     # ---- configuration (builder style, like the reference) ----
     def with_eta_floor(self, v: float): self.eta_floor = v if v > 0 and math.isfinite(v) else self.eta_floor; return self   # noqa: E702
@@ -200,6 +203,9 @@ class SelfRewriteEngine:
     def with_max_staleness(self, n: int): self.max_staleness = max(1, n); return self              # noqa: E702
     def with_anomaly_patience(self, n: int): self.anomaly_patience = max(1, n); return self        # noqa: E702
     def enable_trace_mode(self, limit: int): self.trace_limit = max(1, limit); return self         # noqa: E702
+    def with_recombination_trials(self, n: int): self.recombination_trials = max(1, n); return self   # noqa: E702
+    def with_cluster_limit(self, n: int): self.cluster_limit = max(1, n); return self              # noqa: E702
+    def with_cluster_decay(self, v: float): self.cluster_decay = min(v, 0.999) if v > 0 and math.isfinite(v) else self.cluster_decay; return self   # noqa: E702
     # the learning layers (bandit, chain policy, transition / saga graphs, diversity governor): crates/st-kdsl/src/self_mod.rs:1461-1612
     def with_diversity_window(self, n: int): self.policy.diversity.window = max(1, n); return self                      # noqa: E702
     def with_diversity_threshold(self, v: float): self.policy.diversity.threshold = v if v >= 0 and math.isfinite(v) else self.policy.diversity.threshold; return self   # noqa: E702
@@ -230,6 +236,10 @@ class SelfRewriteEngine:
     def relation_graph(self) -> list: return self.policy.relations.snapshots()                      # noqa: E704
     def diversity_snapshot(self) -> dict: return self.policy.diversity.snapshot()                   # noqa: E704
     def quality_model(self) -> dict: return self.policy.quality.snapshot()                          # noqa: E704
+
+    def context_clusters(self) -> list:
+        return [{"signature": c.signature, "mean_gain": c.mean_gain(), "best_gain": c.best_gain, "momentum": c.momentum, "hits": c.hits}
+                for c in sorted(self.clusters, key=lambda c: -c.best_gain)]
 
     # ---- introspection ----
     def smoothed_eta(self) -> Optional[float]:
@@ -299,7 +309,7 @@ class SelfRewriteEngine:
             self.frozen[key] = self.freeze_cooldown
             self._trace("Frozen", f"key={key} failures={st.failures}")
 
-    def _success(self, key: str, observed: float, eta: float, affinity: float, fresh: bool = False) -> float:
+    def _success(self, key: str, observed: float, eta: float, affinity: float, fresh: bool = False, sig: Optional[int] = None) -> float:
         gain = max(0.0, eta - observed)
         st = self.stats.setdefault(key, HintStat(key))
         st.uses += 1
@@ -307,7 +317,92 @@ class SelfRewriteEngine:
         st.best_gain = max(st.best_gain, gain)
         st.last_eta, st.last_affinity, st.last_gain = eta, affinity, gain
         self.policy.record_success(key, gain, affinity, affinity, fresh, st.mean_gain(), st.best_gain)
+        if sig is not None:
+            self._promote_cluster(sig, gain, affinity)
         return gain
+
+    # ---- context clusters (crates/st-kdsl/src/self_mod.rs:2419-2497) ----
+    def _promote_cluster(self, sig: int, gain: float, affinity: float) -> None:
+        """Fold a success into the nearest cluster of context signatures, or open a new one (the weakest goes when full)."""
+        if not math.isfinite(gain):
+            return
+        from .kdsl_policy import ContextCluster
+        near = max(self.clusters, key=lambda c: context_affinity(c.signature, sig), default=None)
+        closeness = context_affinity(near.signature, sig) if near is not None else 0.0
+        if closeness > 0.0:
+            near.update(sig, gain, affinity * closeness, self.cluster_decay)
+            return
+        if len(self.clusters) >= self.cluster_limit:
+            self.clusters.remove(min(self.clusters, key=lambda c: c.best_gain))
+        self.clusters.append(ContextCluster.new(sig, gain, affinity))
+
+    def _decay_clusters(self) -> None:
+        for c in self.clusters:
+            c.total_gain *= self.cluster_decay
+            c.momentum *= self.cluster_decay
+        self.clusters = [c for c in self.clusters if c.total_gain > 1e-4 or c.momentum > 1e-4]
+
+    def cluster_bridge_affinity(self, cached: int, current: int) -> float:
+        """Affinity of two contexts through a cluster close to both: sqrt(a_cached · a_current) times the cluster's
+        energy min(1 + best gain + momentum/2, 1.6), capped at 1; clusters under 0.4 to the cached side or 0.2 to the
+        current side do not bridge."""
+        best = 0.0
+        for c in self.clusters:
+            to_cached, to_current = context_affinity(c.signature, cached), context_affinity(c.signature, current)
+            if to_cached < 0.4 or to_current < 0.2:
+                continue
+            energy = min(1.0 + c.best_gain + c.momentum * 0.5, 1.6)
+            best = max(best, min(min(math.sqrt(to_cached * to_current), 1.0) * energy, 1.0))
+        return best
+
+    def _effective_affinity(self, cached: int, current: int) -> float:
+        """Direct affinity, lifted to the bridged one when the direct one is at least half the sensitivity."""
+        aff = context_affinity(cached, current)
+        return max(aff, self.cluster_bridge_affinity(cached, current)) if aff >= self.ctx_sensitivity * 0.5 else aff
+
+    # ---- recombination (crates/st-kdsl/src/self_mod.rs:1902-1995, 2136-2152) ----
+    @staticmethod
+    def recombine_hints(a: list, b: list) -> list:
+        """First half of `a` (rounded up) followed by the second half of `b`; an empty side yields the other."""
+        if not a or not b:
+            return list(a or b)
+        return list(a[:(len(a) + 1) // 2]) + list(b[len(b) // 2:])
+
+    def _try_recombined(self, base_src: str, ctx: Ctx, observed_eta: float, sig: int) -> Optional[SelfRewriteEvent]:
+        """Cross the four best cached hint sets pairwise, at most `recombination_trials` evaluations per tick."""
+        if len(self.cache) < 2 or self.recombination_trials == 0:
+            return None
+        pool = sorted(self.cache, key=lambda c: -self._priority(c, sig))[:4]
+        attempts = 0
+        for i, a in enumerate(pool):
+            for b in pool[i + 1:]:
+                if attempts >= self.recombination_trials:
+                    return None
+                if a.key == b.key:
+                    continue
+                combined = self.recombine_hints(a.hints, b.hints)
+                key = hint_key(combined)
+                if not combined or key in self.frozen or key in (a.key, b.key):
+                    continue
+                attempts += 1
+                event = self._eval(base_src, ctx, combined)
+                if event.eta_bar <= observed_eta:
+                    self._trace("RecombineFailure", f"key={key} eta={event.eta_bar:.3f}")
+                    st = self.stats.setdefault(key, HintStat(key))
+                    st.uses += 1
+                    st.last_eta = event.eta_bar
+                    st.last_gain *= 0.5
+                    st.last_affinity *= 0.5
+                    st.total_gain *= 0.5
+                    self._penalize(key)
+                    continue
+                aff = min(max((context_affinity(a.ctx_signature, sig) + context_affinity(b.ctx_signature, sig)) * 0.5, 0.1), 1.0)
+                gain = self._success(key, observed_eta, event.eta_bar, aff, sig=sig)
+                self._record_eta(event.eta_bar)
+                self._push_cache(event.eta_bar, combined, sig)
+                self._trace("RecombineSuccess", f"key={key} from=({a.key}, {b.key}) gain={gain:.3f} affinity={aff:.3f}")
+                return event
+        return None
 
     def _push_cache(self, eta: float, hints, sig: int) -> None:
         key = hint_key(hints)
@@ -318,6 +413,7 @@ class SelfRewriteEngine:
     def tick(self, base_src: str, ctx: Ctx, metrics: Optional[WilsonMetrics], observed_eta: float) -> Optional[SelfRewriteEvent]:
         self._age()
         self.policy.advance()
+        self._decay_clusters()
         smoothed = self.smoothed_eta()
         if observed_eta >= self.eta_floor and (observed_eta if smoothed is None else smoothed) >= self.eta_floor:
             return None
@@ -329,7 +425,7 @@ class SelfRewriteEngine:
             if c.key in self.frozen:
                 self._trace("CachePenalty", f"skip frozen key={c.key}")
                 continue
-            aff = context_affinity(c.ctx_signature, sig)
+            aff = self._effective_affinity(c.ctx_signature, sig)
             if aff < self.ctx_sensitivity or c.eta <= observed_eta:
                 self._penalize(c.key)
                 continue
@@ -338,17 +434,21 @@ class SelfRewriteEngine:
                 self._penalize(c.key)
                 self._trace("CachePenalty", f"failed reuse key={c.key} eta={event.eta_bar:.3f}")
                 continue
-            gain = self._success(c.key, observed_eta, event.eta_bar, aff)
+            gain = self._success(c.key, observed_eta, event.eta_bar, aff, sig=sig)
             c.eta, c.staleness, c.ctx_signature = event.eta_bar, 0, sig
             self._record_eta(event.eta_bar)
             self._trace("CacheReuse", f"key={c.key} gain={gain:.3f} affinity={aff:.3f}")
             return event
+        if not force_fresh:
+            event = self._try_recombined(base_src, ctx, observed_eta, sig)
+            if event is not None:
+                return event
         prompt = AiRewritePrompt(base_src, ctx, metrics, observed_eta if observed_eta > 0 and math.isfinite(observed_eta) else 0.5)
         self.generator_calls += 1
         hints = _checked_hints(self.generator, self.config, prompt)
         event = self._eval(base_src, ctx, hints)
         self._record_eta(event.eta_bar)
         self._push_cache(event.eta_bar, event.hints, sig)
-        gain = self._success(hint_key(event.hints), observed_eta, event.eta_bar, 1.0, fresh=True)
+        gain = self._success(hint_key(event.hints), observed_eta, event.eta_bar, 1.0, fresh=True, sig=sig)
         self._trace("GeneratorSuccess", f"key={hint_key(event.hints)} gain={gain:.3f} eta={event.eta_bar:.3f}")
         return event

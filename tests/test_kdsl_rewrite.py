@@ -1,5 +1,7 @@
 """SpiralK rewrite helpers and the self-rewrite engine (reference behaviour: crates/st-kdsl/src/auto.rs and
 src/self_mod.rs with their tests)."""
+import math
+
 import pytest
 
 from spiraltorch_b200.kdsl import Ctx, WilsonMetrics
@@ -70,6 +72,12 @@ def test_engine_rewrites_below_floor_and_reuses_cache():
     # a very different context falls below the affinity threshold: the generator is asked again
     far = Ctx(r=3, c=7, k=1, sg=False, sgc=5, kc=9, tile_cols=11, radix=13, segments=17)
     eng.with_context_sensitivity(0.99)
+    # the cluster opened by the two successes sits on CTX itself and bridges to any context at least half as close
+    # as the sensitivity asks, so the cached hints would still be reused ...
+    assert context_affinity(ctx_signature(CTX), ctx_signature(far)) < 0.99
+    assert eng.cluster_bridge_affinity(ctx_signature(CTX), ctx_signature(far)) == 1.0
+    # ... without it the direct affinity decides and the generator is asked again
+    eng.clusters.clear()
     eng.tick("wg: 128;", far, None, 0.1)
     assert len(calls) == 2
 
@@ -87,3 +95,45 @@ def test_engine_freezes_hints_that_keep_failing_and_ages_the_cache():
     for _ in range(4):
         eng.tick("wg: 64;", CTX, None, 0.95)                                    # healthy ticks still age the cache
     assert eng.cached_keys() == []
+
+
+def test_recombination_crosses_cached_hint_sets_before_asking_the_generator():
+    assert SelfRewriteEngine.recombine_hints([], []) == [] and SelfRewriteEngine.recombine_hints([1], []) == [1]
+    assert SelfRewriteEngine.recombine_hints([1, 2, 3], [4, 5, 6, 7]) == [1, 2, 6, 7]
+    calls = []
+
+    def gen(cfg, prompt):
+        calls.append(1)
+        return [HeuristicHint.new("radix", 8, 0.0, "true")]
+    eng = SelfRewriteEngine(gen, AiRewriteConfig("t", eta_floor=0.97)).enable_trace_mode(32).with_recombination_trials(3)
+    sig = ctx_signature(CTX)
+    a = [HeuristicHint.new("radix", 4, 2.0, "true"), HeuristicHint.new("wg", 64, 0.0, "true")]
+    b = [HeuristicHint.new("radix", 2, 0.0, "true"), HeuristicHint.new("wg", 256, 2.0, "true")]
+    eng._push_cache(0.6, a, sig)                    # the higher stored eta ranks `a` first, so the cross tried is head(a) + tail(b)
+    eng._push_cache(0.1, b, sig)
+    # alone each set scores tanh(0.97 + 1.0) = 0.9618, under the observed 0.965; their cross keeps the two heavy rules
+    # and scores tanh(0.97 + 2.0) = 0.9947, and is found without a generator call
+    ev = eng.tick("wg: 128;", CTX, None, 0.965)
+    kinds = [k for k, _ in eng.take_trace()]
+    assert ev is not None and not calls and "RecombineSuccess" in kinds
+    assert ev.eta_bar == pytest.approx(math.tanh(2.97), abs=1e-6)
+    assert hint_key(ev.hints) in eng.cached_keys() and len(eng.cached_keys()) == 3
+    assert eng.context_clusters()[0]["signature"] == sig
+
+
+def test_context_clusters_follow_successes_and_fade():
+    eng = SelfRewriteEngine(lambda c, p: [HeuristicHint.new("radix", 4, 0.9, "true")], AiRewriteConfig("t", eta_floor=0.4)).with_cluster_limit(2)
+    sig = ctx_signature(CTX)
+    eng.tick("wg: 128;", CTX, None, 0.1)
+    (c,) = eng.context_clusters()
+    assert c["signature"] == sig and c["hits"] == 1 and c["best_gain"] > 0.6
+    assert eng.cluster_bridge_affinity(sig, sig) == 1.0
+    assert eng.cluster_bridge_affinity(sig ^ ((1 << 40) - 1), sig) == 0.0          # 40 bits away from the cluster: under 0.4
+    m0 = c["momentum"]
+    for _ in range(3):
+        eng.tick("wg: 128;", CTX, None, 0.95)                                       # healthy ticks: clusters only fade
+    assert eng.context_clusters()[0]["momentum"] == pytest.approx(m0 * 0.9 ** 3)
+    eng.with_cluster_decay(0.001)
+    for _ in range(3):
+        eng.tick("wg: 128;", CTX, None, 0.95)
+    assert eng.context_clusters() == []
