@@ -4,7 +4,7 @@
 ``st.optim``, ``st.SpiralSession``, ``st.plugin``, ``st.selfsup``, ``st.build_info()`` and
 ``st.describe_device()``.  CUDA work runs on hand-written sm_100a kernels (``csrc/``).
 """
-from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
+from . import (advisors, api_llm, autograd, compress, config, device_caps, differential, drift_response, engine, inference, measure, distributed, hf_bridge, hf_study, hpo, kdsl, language, logic, metrics, nn, observability, optim, plugin, rec, rl, robotics, runtime, safety,
                selfsup, softlogic, telemetry, text, theory, topos, tracking, vision, zspace_coherence, zvolume)
 from . import (ecosystem, elliptic, hub, inflaton, introspect, kdsl_ir, kv, macro_model, mellin, meta_narrative, microlocal, observation, psi_sync, psychoid, qr_studio, quantum_overlay, quantum_reality, sot, relativity,
                rg_flow, schrodinger, soft_learning, spiral_dynamics, stv, sync_bridge, unison, zpulse, zspace_posterior)  # noqa: E402  (network key/value client imports logic)
