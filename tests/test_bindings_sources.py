@@ -34,3 +34,21 @@ def test_julia_binding_names_only_declared_symbols():
     for name, types in re.findall(r"ccall\(_sym\(:(spiraltorch_\w+)\),\s*[\w{}.]+,\s*\(([^)]*)\)", src):
         n = 0 if not types.strip() else len([t for t in types.split(",") if t.strip()])
         assert n == _argc(DECLS[name]), (name, n, DECLS[name])
+
+
+def test_wasm_binding_names_only_declared_symbols():
+    src = (ROOT / "bindings" / "wasm" / "spiraltorch.mjs").read_text()
+    used = set(re.findall(r"M\._(spiraltorch_\w+)\(", src))
+    exported = set(re.findall(r'"(spiraltorch_\w+)"', src[src.index("export const EXPORTED"):]))
+    assert len(used) >= 25 and used <= set(DECLS), sorted(used - set(DECLS))
+    assert used == exported, sorted(used ^ exported)                       # the build exports what the wrapper calls, no more
+    for name, args in re.findall(r"M\._(spiraltorch_\w+)\(((?:[^()]|\((?:[^()]|\([^()]*\))*\))*)\)", src):
+        depth, count = 0, 1 if args.strip() else 0
+        for ch in args:
+            depth += ch == "("
+            depth -= ch == ")"
+            count += ch == "," and depth == 0
+        assert count == _argc(DECLS[name]), (name, count, DECLS[name])
+    # only tensor_abi.cpp is compiled for the browser: nothing the wrapper calls may live in another source file
+    for name in used:
+        assert re.search(rf"\b{name}\([^)]*\);\s*/\* csrc/host/tensor_abi\.cpp \*/", HEADER), name
